@@ -1,0 +1,53 @@
+// Shared host/device helpers of the sm_100a kernel library.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <atomic>
+#include <string>
+
+#include "ctorch_b200.h"
+
+namespace ctk {
+
+// Thread-local message of the last failure; returns `code` so launchers can `return fail(...)`.
+ctk_status fail(ctk_status code, const std::string& msg);
+extern std::atomic<uint64_t> g_launches;
+inline void count_launch(int n = 1) { g_launches.fetch_add(static_cast<uint64_t>(n), std::memory_order_relaxed); }
+
+// Number of SMs of the current device (cached per device ordinal).
+int sm_count();
+// Library-owned per-device scratch, grown on demand (never shrinks).  slot 0: reductions,
+// slot 1: matmul workspace.
+ctk_status device_scratch(int slot, size_t bytes, void** out);
+
+inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+
+}  // namespace ctk
+
+#define CTK_CUDA(call)                                                                          \
+    do {                                                                                        \
+        cudaError_t _e = (call);                                                                \
+        if (_e != cudaSuccess)                                                                  \
+            return ctk::fail(CTK_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(_e)); \
+    } while (0)
+
+#define CTK_LAUNCH_CHECK(name)                                                                    \
+    do {                                                                                          \
+        cudaError_t _e = cudaGetLastError();                                                      \
+        if (_e != cudaSuccess)                                                                    \
+            return ctk::fail(CTK_ERR_CUDA, std::string(name) + " launch: " + cudaGetErrorString(_e)); \
+        ctk::count_launch();                                                                      \
+    } while (0)
+
+#define CTK_REQUIRE(cond, msg)                                    \
+    do {                                                          \
+        if (!(cond)) return ctk::fail(CTK_ERR_INVALID, (msg));    \
+    } while (0)
+
+// Grid size for a grid-stride streaming kernel: a whole number of waves of the SM count.
+static inline int ctk_stream_grid(int64_t work_items, int threads, int ctas_per_sm) {
+    int64_t need = (work_items + threads - 1) / threads;
+    int64_t cap = static_cast<int64_t>(ctk::sm_count()) * ctas_per_sm;
+    if (need < 1) need = 1;
+    return static_cast<int>(need < cap ? need : cap);
+}

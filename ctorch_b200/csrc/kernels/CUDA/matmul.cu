@@ -1,0 +1,651 @@
+// MatMul for sm_100a: C[m,n] = sum_l A[i*sa0 + l*sa1] * B[l*sb0 + j*sb1], fp32 in / fp32 out.
+//
+// Replaces MatMul_BASIC_kernel (src/kernels/CPU-BASIC/MatMul_BASIC_kernel.cpp:13-57).  Strides are
+// taken as that kernel reads them, so C = A.B, dA = dC.B^T and dB = A^T.dC (src/AutoDiff.cpp:
+// 1702-1704, 1808-1810, where B^T / A^T are stride-swapped views) are one entry point.
+//
+// Tensor-core path (the product): a persistent, warp-specialised tcgen05 kernel.
+//   warp 0     : TMA producer -- cp.async.bulk.tensor (no multicast) into 128B-swizzled shared
+//                memory, a ring of stages guarded by full/empty mbarriers;
+//   warp 1     : MMA issuer -- one elected lane issues tcgen05.mma.kind::tf32 (M=128, N=BN, K=8)
+//                from shared-memory descriptors into a TMEM accumulator, tcgen05.commit frees the
+//                stage; owns the TMEM allocation (two accumulators, so the epilogue of tile i
+//                overlaps the main loop of tile i+1);
+//   warps 2..5 : epilogue -- tcgen05.ld the accumulator (each warp its 32-lane quarter), store C.
+//   Either operand may be K-major (row of K contiguous) or MN-major (row of M/N contiguous): the
+//   major-ness goes into the instruction descriptor and the shared-memory descriptors, no
+//   transposed copy is made.  M/N/K tails are zero-filled by TMA and masked at the store.
+//   TF32 mode multiplies the fp32 operands as they are (the tensor core reads the top 19 bits).
+//   3xTF32 mode first splits each operand x into hi = tf32(x) (round to nearest) and
+//   lo = tf32(x - hi) in a scratch buffer, then accumulates lo.hi + hi.lo + hi.hi in TMEM:
+//   the dropped term lo.lo is ~2^-22 of the product, i.e. fp32-level accuracy.
+//   Every mbarrier wait is bounded; a wait that runs out sets a device status word, the CTA drains
+//   its copies, frees its TMEM and returns.
+//
+// CUDA-core path: a plain fp32-FMA tiled kernel for operands TMA cannot address (a row pitch that
+// is not a multiple of 16 bytes, e.g. the 10-class layer) and on request (mode FP32_SIMT).
+#include <cuda.h>
+#include <math.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace {
+using namespace ctk;
+
+__device__ int g_tc_status = 0;  // first bounded wait that ran out: (role << 8) | barrier id, else 0
+
+// ================================================================================================
+// CUDA-core path
+// ================================================================================================
+constexpr int SM_TILE = 64, SM_BK = 16, SM_THREADS = 256;
+
+__global__ void __launch_bounds__(SM_THREADS) simt_matmul_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                                                  float* __restrict__ c, int64_t m, int64_t n, int64_t k,
+                                                                  int64_t sa0, int64_t sa1, int64_t sb0, int64_t sb1) {
+    __shared__ float As[SM_BK][SM_TILE + 4];
+    __shared__ float Bs[SM_BK][SM_TILE + 4];
+    const int tid = threadIdx.x;
+    const int64_t m0 = static_cast<int64_t>(blockIdx.y) * SM_TILE, n0 = static_cast<int64_t>(blockIdx.x) * SM_TILE;
+    const int tx = tid % 16, ty = tid / 16;  // 16 x 16 threads, 4 x 4 outputs each
+    float acc[4][4] = {};
+    const bool a_kfast = (sa1 == 1), b_nfast = (sb1 == 1);
+    for (int64_t k0 = 0; k0 < k; k0 += SM_BK) {
+        // A tile: 64 rows x 16 k, each thread 4 elements; the fastest-varying thread index follows
+        // the contiguous dimension so global loads coalesce for both major-nesses.
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            int i, l;
+            if (a_kfast) { l = tid % SM_BK; i = tid / SM_BK + r * (SM_THREADS / SM_BK); }
+            else { i = tid % SM_TILE; l = tid / SM_TILE + r * (SM_THREADS / SM_TILE); }
+            const int64_t gi = m0 + i, gl = k0 + l;
+            As[l][i] = (gi < m && gl < k) ? __ldg(a + gi * sa0 + gl * sa1) : 0.0f;
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            int j, l;
+            if (b_nfast) { j = tid % SM_TILE; l = tid / SM_TILE + r * (SM_THREADS / SM_TILE); }
+            else { l = tid % SM_BK; j = tid / SM_BK + r * (SM_THREADS / SM_BK); }
+            const int64_t gj = n0 + j, gl = k0 + l;
+            Bs[l][j] = (gj < n && gl < k) ? __ldg(b + gl * sb0 + gj * sb1) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int l = 0; l < SM_BK; ++l) {
+            float av[4], bv[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) { av[u] = As[l][ty * 4 + u]; bv[u] = Bs[l][tx * 4 + u]; }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int v = 0; v < 4; ++v) acc[u][v] = fmaf(av[u], bv[v], acc[u][v]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int64_t gi = m0 + ty * 4 + u;
+        if (gi >= m) continue;
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            const int64_t gj = n0 + tx * 4 + v;
+            if (gj < n) c[gi * n + gj] = acc[u][v];
+        }
+    }
+}
+
+// ================================================================================================
+// hi/lo split for 3xTF32
+// ================================================================================================
+__device__ __forceinline__ float to_tf32_rna(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+
+// x viewed as [outer, inner] with row pitch ld -> dense hi[outer, inner], lo[outer, inner].
+__global__ void __launch_bounds__(256) split_tf32_kernel(const float* __restrict__ x, float* __restrict__ hi, float* __restrict__ lo,
+                                                         int64_t outer, int64_t inner, int64_t ld) {
+    const int64_t inner4 = inner >> 2;  // inner % 4 == 0 is a precondition of the tensor-core path
+    const int64_t total = outer * inner4;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t r = i / inner4, c4 = i - r * inner4;
+        float4 v = __ldg(reinterpret_cast<const float4*>(x + r * ld) + c4);
+        float4 h, l;
+        h.x = to_tf32_rna(v.x); h.y = to_tf32_rna(v.y); h.z = to_tf32_rna(v.z); h.w = to_tf32_rna(v.w);
+        l.x = to_tf32_rna(v.x - h.x); l.y = to_tf32_rna(v.y - h.y); l.z = to_tf32_rna(v.z - h.z); l.w = to_tf32_rna(v.w - h.w);
+        reinterpret_cast<float4*>(hi + r * inner)[c4] = h;
+        reinterpret_cast<float4*>(lo + r * inner)[c4] = l;
+    }
+}
+
+// ================================================================================================
+// tcgen05 path
+// ================================================================================================
+namespace tc {
+
+constexpr int BM = 128;
+constexpr int BK = 32;               // 32 fp32 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 8;            // K of one tcgen05.mma.kind::tf32
+constexpr int THREADS = 192;         // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+constexpr int SMEM_BUDGET = 200 * 1024;
+constexpr uint32_t WAIT_LIMIT = 4u << 20;  // polls per bounded wait (each poll may itself block a few us)
+
+template <int BN, int TERMS>
+struct Cfg {
+    static constexpr int A_BYTES = BM * BK * 4;
+    static constexpr int B_BYTES = BN * BK * 4;
+    static constexpr int PARTS = (TERMS == 1) ? 1 : 2;           // hi only / hi + lo
+    static constexpr int STAGE_BYTES = PARTS * (A_BYTES + B_BYTES);
+    static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+    static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;  // two accumulators, power of two
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;  // + slack for 1024-byte alignment
+    static_assert(STAGES >= 2, "need at least two stages");
+    static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns must be a power of two <= 512");
+};
+
+struct Params {
+    int64_t m, n, k;
+    int tiles_m, tiles_n, num_kb;
+    float* c;
+    int vec_store;  // n % 4 == 0 and c 16-byte aligned
+};
+
+// ---- PTX wrappers --------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  On running out (or when another role already gave up) records `code` and raises
+// the CTA-wide abort flag; every role then leaves its loops and the CTA tears down normally.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u) {
+            if (*abort_flag) return false;
+            __nanosleep(64);
+        }
+    }
+    *abort_flag = 1;
+    atomicCAS(&g_tc_status, 0, code);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (sm_100 format): start address >> 4 in bits [0,14), leading byte
+// offset >> 4 in [16,30), stride byte offset >> 4 in [32,46), version 1 in [46,48), 128-byte
+// swizzle (code 2) in [61,64).
+//   K-major tile  [rows][32 fp32]: rows 128 B apart, 8-row groups 1024 B apart -> SBO = 1024;
+//                 a K=8 step advances the start address by 32 B inside the swizzle row.
+//   MN-major tile [k][32 fp32 of M/N] in 32-wide column groups: 8 k-rows (1024 B) form one atom,
+//                 column groups are 4096 B apart -> LBO = 4096, SBO = 1024; a K=8 step advances the
+//                 start address by 1024 B.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
+// Instruction descriptor for kind::tf32: D fp32 (bits [4,6) = 1), A/B TF32 (format 2 in [7,10) and
+// [10,13)), A/B major-ness in bits 15/16 (1 = MN-major), N >> 3 in [17,23), M >> 4 in [24,29).
+__host__ __device__ constexpr uint32_t make_idesc(int n, bool a_mn_major, bool b_mn_major) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
+           (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(n >> 3) << 17) |
+           (static_cast<uint32_t>(BM >> 4) << 24);
+}
+
+// ---- the kernel ----------------------------------------------------------------------------------
+// A_MN / B_MN: operand is MN-major (its M/N index is the contiguous one).  Tensor maps describe the
+// operand as a 2-D array {contiguous dim, other dim}; box = {32, rows} for a K-major operand and
+// {32, 32} per 32-wide column group for an MN-major one.
+template <int BN, int TERMS, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(THREADS, 1)
+tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+                      const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+                      const Params P) {
+    using C = Cfg<BN, TERMS>;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t bars[2 * 8 + 4];  // full[8], empty[8], tmem_full[2], tmem_empty[2]
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile int abort_flag;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar0 = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (8 + s); };
+    auto tfull_bar = [&](int a) { return bar0 + 8u * (16 + a); };
+    auto tempty_bar = [&](int a) { return bar0 + 8u * (18 + a); };
+    // stage layout: [A_hi][A_lo?][B_hi][B_lo?]
+    auto a_addr = [&](int s, int part) { return smem_base + s * C::STAGE_BYTES + part * C::A_BYTES; };
+    auto b_addr = [&](int s, int part) { return smem_base + s * C::STAGE_BYTES + C::PARTS * C::A_BYTES + part * C::B_BYTES; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        prefetch_tmap(&map_a_hi);
+        prefetch_tmap(&map_b_hi);
+        if (TERMS == 3) { prefetch_tmap(&map_a_lo); prefetch_tmap(&map_b_lo); }
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_base_slot), C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    const int num_tiles = P.tiles_m * P.tiles_n;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t issued = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile / P.tiles_n) * BM, n0 = (tile % P.tiles_n) * BN;
+                for (int kb = 0; kb < P.num_kb; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, &abort_flag, 0x100 | stage)) { ok = false; break; }
+                    mbar_expect_tx(full_bar(stage), C::STAGE_BYTES);
+                    const int k0 = kb * BK;
+#pragma unroll
+                    for (int part = 0; part < C::PARTS; ++part) {
+                        const CUtensorMap* ma = part ? &map_a_lo : &map_a_hi;
+                        const CUtensorMap* mb = part ? &map_b_lo : &map_b_hi;
+                        if (A_MN) {
+#pragma unroll
+                            for (int g = 0; g < BM / 32; ++g) tma_load_2d(a_addr(stage, part) + g * 4096, ma, full_bar(stage), m0 + 32 * g, k0);
+                        } else {
+                            tma_load_2d(a_addr(stage, part), ma, full_bar(stage), k0, m0);
+                        }
+                        if (B_MN) {
+#pragma unroll
+                            for (int g = 0; g < BN / 32; ++g) tma_load_2d(b_addr(stage, part) + g * 4096, mb, full_bar(stage), n0 + 32 * g, k0);
+                        } else {
+                            tma_load_2d(b_addr(stage, part), mb, full_bar(stage), k0, n0);
+                        }
+                    }
+                    ++issued;
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) {
+                // Gave up: let the copies already issued land before the CTA's shared memory goes away.
+                const uint32_t pending = issued < static_cast<uint32_t>(C::STAGES) ? issued : C::STAGES;
+                int s = stage;
+                uint32_t ph = phase;
+                for (uint32_t i = 0; i < pending; ++i) {
+                    if (--s < 0) { s = C::STAGES - 1; ph ^= 1u; }
+                    for (uint32_t spin = 0; spin < (1u << 16) && !mbar_try_wait(full_bar(s), ph); ++spin) __nanosleep(64);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BN, A_MN, B_MN);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, &abort_flag, 0x200 | (18 + acc))) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+                for (int kb = 0; kb < P.num_kb; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase, &abort_flag, 0x200 | stage)) { ok = false; break; }
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+                        const uint32_t a_step = A_MN ? ks * 1024u : ks * 32u;
+                        const uint32_t b_step = B_MN ? ks * 1024u : ks * 32u;
+                        const uint32_t a_lbo = A_MN ? 4096u : 0u, b_lbo = B_MN ? 4096u : 0u;
+                        const uint64_t a_hi = make_desc(a_addr(stage, 0) + a_step, a_lbo, 1024u);
+                        const uint64_t b_hi = make_desc(b_addr(stage, 0) + b_step, b_lbo, 1024u);
+                        const uint32_t first = (kb > 0 || ks > 0) ? 1u : 0u;
+                        if (TERMS == 3) {
+                            const uint64_t a_lo = make_desc(a_addr(stage, 1) + a_step, a_lbo, 1024u);
+                            const uint64_t b_lo = make_desc(b_addr(stage, 1) + b_step, b_lbo, 1024u);
+                            tc_mma_tf32(d_tmem, a_lo, b_hi, idesc, first);  // small terms first
+                            tc_mma_tf32(d_tmem, a_hi, b_lo, idesc, 1u);
+                            tc_mma_tf32(d_tmem, a_hi, b_hi, idesc, 1u);
+                        } else {
+                            tc_mma_tf32(d_tmem, a_hi, b_hi, idesc, first);
+                        }
+                    }
+                    tc_commit(empty_bar(stage));  // arrives when the MMAs above have read the stage
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                tc_commit(tfull_bar(acc));        // accumulator complete
+                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            }
+        }
+    } else {
+        // ------------------------------ epilogue ------------------------------
+        const int quarter = warp & 3;  // TMEM lanes this warp may read: [32*quarter, 32*quarter+32)
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            const int64_t m0 = static_cast<int64_t>(tile / P.tiles_n) * BM, n0 = static_cast<int64_t>(tile % P.tiles_n) * BN;
+            if (!mbar_wait(tfull_bar(acc), acc_phase, &abort_flag, 0x300 | (16 + acc))) { ok = false; break; }
+            tc_fence_after();
+            const int64_t row = m0 + quarter * 32 + lane;
+            float* crow = P.c + row * P.n;
+#pragma unroll 1
+            for (int cc = 0; cc < BN / 32; ++cc) {
+                uint32_t r[32];
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN + cc * 32);
+                tmem_ld32(taddr, r);
+                tmem_ld_wait();
+                const int64_t col0 = n0 + cc * 32;
+                if (row < P.m && col0 < P.n) {
+                    if (P.vec_store && col0 + 32 <= P.n) {
+#pragma unroll
+                        for (int v = 0; v < 8; ++v)
+                            __stcs(reinterpret_cast<float4*>(crow + col0) + v,
+                                   make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                               __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3])));
+                    } else {
+#pragma unroll
+                        for (int v = 0; v < 32; ++v)
+                            if (col0 + v < P.n) crow[col0 + v] = __uint_as_float(r[v]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// ---- host side -------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+std::mutex g_encode_mu;
+
+ctk_status get_encoder(EncodeTiledFn* out) {
+    std::lock_guard<std::mutex> lock(g_encode_mu);
+    if (!g_encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        CTK_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+        if (!fn || q != cudaDriverEntryPointSuccess) return fail(CTK_ERR_CUDA, "cuTensorMapEncodeTiled not available from the driver");
+        g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    *out = g_encode;
+    return CTK_OK;
+}
+
+// 2-D fp32 tensor {inner (contiguous), outer} with row pitch ld elements; box {32, box_outer};
+// 128-byte swizzle; out-of-range elements read as zero.
+ctk_status make_map(CUtensorMap* map, const float* base, int64_t inner, int64_t outer, int64_t ld, int box_outer) {
+    EncodeTiledFn enc;
+    ctk_status st = get_encoder(&enc);
+    if (st) return st;
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 4};
+    cuuint32_t box[2] = {32u, static_cast<cuuint32_t>(box_outer)};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(CTK_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(r)));
+    return CTK_OK;
+}
+
+// One operand as the tensor-core path sees it.
+struct Operand {
+    const float* p;
+    bool mn_major;   // the M/N index is the contiguous one
+    int64_t mn, k;   // extents
+    int64_t ld;      // pitch of the non-contiguous dim, in elements
+    int64_t inner() const { return mn_major ? mn : k; }
+    int64_t outer() const { return mn_major ? k : mn; }
+};
+
+bool tma_ok(const Operand& o) {
+    return (reinterpret_cast<uintptr_t>(o.p) & 15u) == 0 && o.ld % 4 == 0 && o.ld >= o.inner() && o.inner() % 4 == 0;
+}
+
+template <int BN, int TERMS, bool A_MN, bool B_MN>
+ctk_status launch_tc(const CUtensorMap maps[4], const Params& P, cudaStream_t st) {
+    using C = Cfg<BN, TERMS>;
+    auto kernel = tcgen05_matmul_kernel<BN, TERMS, A_MN, B_MN>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        CTK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+        attr_set = true;
+    }
+    const int tiles = P.tiles_m * P.tiles_n;
+    const int sms = ctk::sm_count();
+    const int grid = tiles < sms ? tiles : sms;  // persistent: one CTA per SM
+    kernel<<<grid, THREADS, C::SMEM_BYTES, st>>>(maps[0], maps[1], maps[2], maps[3], P);
+    CTK_LAUNCH_CHECK("tcgen05_matmul_kernel");
+    return CTK_OK;
+}
+
+template <int BN, int TERMS>
+ctk_status launch_tc_major(bool a_mn, bool b_mn, const CUtensorMap maps[4], const Params& P, cudaStream_t st) {
+    if (a_mn && b_mn) return launch_tc<BN, TERMS, true, true>(maps, P, st);
+    if (a_mn) return launch_tc<BN, TERMS, true, false>(maps, P, st);
+    if (b_mn) return launch_tc<BN, TERMS, false, true>(maps, P, st);
+    return launch_tc<BN, TERMS, false, false>(maps, P, st);
+}
+
+int pick_bn(int64_t n) { return n > 128 ? 256 : (n > 64 ? 128 : 64); }
+
+}  // namespace tc
+
+// Classifies one operand: returns false if neither stride is 1.
+bool classify(const float* p, int64_t mn, int64_t k, int64_t s_mn, int64_t s_k, tc::Operand* o) {
+    o->p = p; o->mn = mn; o->k = k;
+    if (s_k == 1 && (s_mn >= k || mn == 1)) { o->mn_major = false; o->ld = (mn == 1 && s_mn < k) ? k : s_mn; return true; }
+    if (s_mn == 1 && (s_k >= mn || k == 1)) { o->mn_major = true; o->ld = (k == 1 && s_k < mn) ? mn : s_k; return true; }
+    return false;
+}
+
+int g_default_mode = CTK_MATMUL_3XTF32;
+
+int resolve_mode(int mode) { return mode < 0 ? g_default_mode : mode; }
+
+// 0 = tcgen05, 1 = SIMT
+int choose_path(const float* a, const float* b, int64_t m, int64_t n, int64_t k, int64_t sa0, int64_t sa1, int64_t sb0,
+                int64_t sb1, int mode, tc::Operand* oa, tc::Operand* ob) {
+    if (resolve_mode(mode) == CTK_MATMUL_FP32_SIMT) return 1;
+    tc::Operand A, B;
+    if (!classify(a, m, k, sa0, sa1, &A) || !classify(b, n, k, sb1, sb0, &B)) return 1;
+    if (!tc::tma_ok(A) || !tc::tma_ok(B)) return 1;
+    if (n < 16 || k < 8) return 1;  // degenerate tiles: the tensor-core tile would be mostly padding
+    if (oa) *oa = A;
+    if (ob) *ob = B;
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+ctk_status ctk_set_matmul_mode(int mode) {
+    CTK_REQUIRE(mode >= CTK_MATMUL_3XTF32 && mode <= CTK_MATMUL_FP32_SIMT, "ctk_set_matmul_mode: unknown mode");
+    g_default_mode = mode;
+    return CTK_OK;
+}
+int ctk_get_matmul_mode(void) { return g_default_mode; }
+
+size_t ctk_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k, int mode) {
+    if (resolve_mode(mode) != CTK_MATMUL_3XTF32) return 0;
+    return static_cast<size_t>(2 * (m * k + k * n)) * sizeof(float) + 1024;
+}
+
+int ctk_matmul_path(const float* a, const float* b, int64_t m, int64_t n, int64_t k, int64_t sa0, int64_t sa1,
+                    int64_t sb0, int64_t sb1, int mode) {
+    return choose_path(a, b, m, n, k, sa0, sa1, sb0, sb1, mode, nullptr, nullptr);
+}
+
+ctk_status ctk_matmul_status(int* status) {
+    CTK_REQUIRE(status, "ctk_matmul_status: null");
+    CTK_CUDA(cudaDeviceSynchronize());
+    CTK_CUDA(cudaMemcpyFromSymbol(status, g_tc_status, sizeof(int)));
+    return CTK_OK;
+}
+
+ctk_status ctk_matmul_f32(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k, int64_t sa0,
+                          int64_t sa1, int64_t sb0, int64_t sb1, int mode, void* workspace, void* stream) {
+    CTK_REQUIRE(m >= 0 && n >= 0 && k >= 0, "ctk_matmul_f32: negative extent");
+    if (m == 0 || n == 0) return CTK_OK;
+    CTK_REQUIRE(c, "ctk_matmul_f32: null output");
+    cudaStream_t st = as_stream(stream);
+    if (k == 0) {
+        CTK_CUDA(cudaMemsetAsync(c, 0, static_cast<size_t>(m * n) * sizeof(float), st));
+        return CTK_OK;
+    }
+    CTK_REQUIRE(a && b, "ctk_matmul_f32: null operand");
+    const int md = resolve_mode(mode);
+    CTK_REQUIRE(md >= CTK_MATMUL_3XTF32 && md <= CTK_MATMUL_FP32_SIMT, "ctk_matmul_f32: unknown mode");
+    CTK_REQUIRE(m < (int64_t(1) << 31) && n < (int64_t(1) << 31) && k < (int64_t(1) << 31), "ctk_matmul_f32: extent >= 2^31");
+
+    tc::Operand A, B;
+    if (choose_path(a, b, m, n, k, sa0, sa1, sb0, sb1, md, &A, &B) == 1) {
+        dim3 grid(static_cast<unsigned>((n + SM_TILE - 1) / SM_TILE), static_cast<unsigned>((m + SM_TILE - 1) / SM_TILE));
+        CTK_REQUIRE(grid.y <= 65535u, "ctk_matmul_f32: m too large for the CUDA-core path");
+        simt_matmul_kernel<<<grid, SM_THREADS, 0, st>>>(a, b, c, m, n, k, sa0, sa1, sb0, sb1);
+        CTK_LAUNCH_CHECK("simt_matmul_kernel");
+        return CTK_OK;
+    }
+
+    const int terms = (md == CTK_MATMUL_3XTF32) ? 3 : 1;
+    const float *a_hi = A.p, *a_lo = A.p, *b_hi = B.p, *b_lo = B.p;
+    int64_t a_ld = A.ld, b_ld = B.ld;
+    if (terms == 3) {
+        void* ws = workspace;
+        const size_t need = ctk_matmul_workspace_bytes(m, n, k, md);
+        if (!ws) {
+            ctk_status rc = device_scratch(1, need, &ws);
+            if (rc) return rc;
+        }
+        float* w = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(ws) + 255u) & ~static_cast<uintptr_t>(255u));
+        float* ah = w;
+        float* al = ah + m * k;
+        float* bh = al + m * k;
+        float* bl = bh + k * n;
+        const int grid_a = ctk_stream_grid(m * k / 4, 256, 8), grid_b = ctk_stream_grid(k * n / 4, 256, 8);
+        split_tf32_kernel<<<grid_a, 256, 0, st>>>(A.p, ah, al, A.outer(), A.inner(), A.ld);
+        CTK_LAUNCH_CHECK("split_tf32_kernel");
+        split_tf32_kernel<<<grid_b, 256, 0, st>>>(B.p, bh, bl, B.outer(), B.inner(), B.ld);
+        CTK_LAUNCH_CHECK("split_tf32_kernel");
+        a_hi = ah; a_lo = al; b_hi = bh; b_lo = bl;
+        a_ld = A.inner(); b_ld = B.inner();
+    }
+
+    const int bn = tc::pick_bn(n);
+    CUtensorMap maps[4];
+    const int a_box = A.mn_major ? tc::BK : tc::BM;
+    const int b_box = B.mn_major ? tc::BK : bn;
+    ctk_status rc;
+    if ((rc = tc::make_map(&maps[0], a_hi, A.inner(), A.outer(), a_ld, a_box))) return rc;
+    if ((rc = tc::make_map(&maps[1], a_lo, A.inner(), A.outer(), a_ld, a_box))) return rc;
+    if ((rc = tc::make_map(&maps[2], b_hi, B.inner(), B.outer(), b_ld, b_box))) return rc;
+    if ((rc = tc::make_map(&maps[3], b_lo, B.inner(), B.outer(), b_ld, b_box))) return rc;
+
+    tc::Params P;
+    P.m = m; P.n = n; P.k = k;
+    P.tiles_m = static_cast<int>((m + tc::BM - 1) / tc::BM);
+    P.tiles_n = static_cast<int>((n + bn - 1) / bn);
+    P.num_kb = static_cast<int>((k + tc::BK - 1) / tc::BK);
+    P.c = c;
+    P.vec_store = (n % 4 == 0) && ((reinterpret_cast<uintptr_t>(c) & 15u) == 0);
+    CTK_REQUIRE(static_cast<int64_t>(P.tiles_m) * P.tiles_n < (int64_t(1) << 31), "ctk_matmul_f32: too many tiles");
+
+#define CTK_TC(BN_)                                                                                 \
+    (terms == 3 ? tc::launch_tc_major<BN_, 3>(A.mn_major, B.mn_major, maps, P, st)                  \
+                : tc::launch_tc_major<BN_, 1>(A.mn_major, B.mn_major, maps, P, st))
+    if (bn == 256) return CTK_TC(256);
+    if (bn == 128) return CTK_TC(128);
+    return CTK_TC(64);
+#undef CTK_TC
+}
+
+}  // extern "C"

@@ -1,0 +1,166 @@
+// Reductions to a scalar (Sum, Dot, MSE, MAE) and the elementwise backward of the two mean
+// losses.  HBM-bound: 128-bit streaming loads, four independent fp32 accumulators per thread,
+// shuffle reduction per warp, fp64 across warps and CTAs, one launch (the last CTA to finish adds
+// the per-CTA partials in a fixed order).  Compiled with -fmad=false.
+//
+// The reference adds sequentially in fp32 (src/Tensor.cpp:638-666, MSE/MAE/Dot_BASIC_kernel.cpp);
+// the tree used here is at least as accurate, which is how parity of these sums is judged.
+#include <math.h>
+
+#include "reduce_common.cuh"
+
+namespace ctk {
+
+ctk_status reduce_scratch(void* user, cudaStream_t st, ReduceScratch** out) {
+    void* p = user;
+    if (!p) {
+        ctk_status s = device_scratch(0, sizeof(ReduceScratch), &p);
+        if (s) return s;
+    }
+    CTK_REQUIRE((reinterpret_cast<uintptr_t>(p) & 7u) == 0, "reduction scratch must be 8-byte aligned");
+    *out = static_cast<ReduceScratch*>(p);
+    // The ticket must start at zero; a caller-supplied block is not trusted to be clean.
+    CTK_CUDA(cudaMemsetAsync(&(*out)->ticket, 0, sizeof(unsigned int), st));
+    return CTK_OK;
+}
+
+}  // namespace ctk
+
+namespace {
+using namespace ctk;
+
+constexpr int kThreads = 256;
+constexpr int kCtasPerSm = 4;
+
+enum { R_SUM = 0, R_DOT = 1, R_MSE = 2, R_MAE = 3 };
+
+template <int KIND>
+__device__ __forceinline__ float term(float x, float y) {
+    if (KIND == R_SUM) return x;
+    if (KIND == R_DOT) return x * y;
+    float d = x - y;
+    if (KIND == R_MSE) return d * d;
+    return fabsf(d);
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(kThreads) reduce_kernel(const float* __restrict__ a, const float* __restrict__ b, int64_t n,
+                                                          bool vec_ok, float post_div, ReduceScratch* scratch, float* out) {
+    __shared__ double smem[33];
+    const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+    if (vec_ok) {
+        const int64_t n4 = n >> 2;
+#pragma unroll 4
+        for (int64_t i = tid; i < n4; i += nthreads) {
+            float4 x = __ldcs(reinterpret_cast<const float4*>(a) + i);
+            float4 y = (KIND == R_SUM) ? x : __ldcs(reinterpret_cast<const float4*>(b) + i);
+            acc0 += term<KIND>(x.x, y.x);
+            acc1 += term<KIND>(x.y, y.y);
+            acc2 += term<KIND>(x.z, y.z);
+            acc3 += term<KIND>(x.w, y.w);
+        }
+        for (int64_t j = (n4 << 2) + tid; j < n; j += nthreads) acc0 += term<KIND>(a[j], KIND == R_SUM ? 0.f : b[j]);
+    } else {
+        for (int64_t j = tid; j < n; j += nthreads) acc0 += term<KIND>(a[j], KIND == R_SUM ? 0.f : b[j]);
+    }
+    double v = (static_cast<double>(acc0) + static_cast<double>(acc1)) + (static_cast<double>(acc2) + static_cast<double>(acc3));
+    v = block_sum(v, smem);
+    grid_finish(v, scratch, out, post_div, false, smem);
+}
+
+// src/AutoDiff.cpp:1491-1516: (((p - t) * 2) / n) * g ;  :1602-1642: (sign(p - t) / n) * g
+template <bool MSE>
+__global__ void __launch_bounds__(kThreads) mean_loss_bwd_kernel(const float* __restrict__ p, const float* __restrict__ t,
+                                                                 const float* __restrict__ gdev, float* __restrict__ dp,
+                                                                 int64_t n, float fn, bool vec_ok) {
+    const float g = gdev ? __ldg(gdev) : 1.0f;
+    auto one = [&](float x, float y) {
+        float d = x - y;
+        float c;
+        if (MSE) {
+            float d2 = d * 2.0f;
+            c = d2 / fn;
+        } else {
+            float s = d > 0.0f ? 1.0f : (d < 0.0f ? -1.0f : 0.0f);
+            c = s / fn;
+        }
+        return c * g;
+    };
+    const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    if (vec_ok) {
+        const int64_t n4 = n >> 2;
+        for (int64_t i = tid; i < n4; i += nthreads) {
+            float4 x = __ldcs(reinterpret_cast<const float4*>(p) + i), y = __ldcs(reinterpret_cast<const float4*>(t) + i), r;
+            r.x = one(x.x, y.x); r.y = one(x.y, y.y); r.z = one(x.z, y.z); r.w = one(x.w, y.w);
+            __stcs(reinterpret_cast<float4*>(dp) + i, r);
+        }
+        for (int64_t j = (n4 << 2) + tid; j < n; j += nthreads) dp[j] = one(p[j], t[j]);
+    } else {
+        for (int64_t j = tid; j < n; j += nthreads) dp[j] = one(p[j], t[j]);
+    }
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <int KIND>
+ctk_status launch_reduce(const char* name, const float* a, const float* b, int64_t n, float post_div, float* out, void* scratch, void* stream) {
+    CTK_REQUIRE(n >= 0 && out, "reduction: bad arguments");
+    CTK_REQUIRE(n == 0 || (a && (KIND == R_SUM || b)), "reduction: null input");
+    cudaStream_t st = as_stream(stream);
+    ReduceScratch* s = nullptr;
+    ctk_status rc = reduce_scratch(scratch, st, &s);
+    if (rc) return rc;
+    int grid = ctk_stream_grid((n + 3) / 4, kThreads * 4, kCtasPerSm);
+    if (grid > kMaxReduceBlocks) grid = kMaxReduceBlocks;
+    bool vec_ok = aligned16(a) && (KIND == R_SUM || aligned16(b));
+    reduce_kernel<KIND><<<grid, kThreads, 0, st>>>(a, b, n, vec_ok, post_div, s, out);
+    CTK_LAUNCH_CHECK(name);
+    return CTK_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t ctk_reduce_scratch_bytes(void) { return sizeof(ctk::ReduceScratch); }
+
+ctk_status ctk_sum_f32(const float* a, int64_t n, float* out, void* scratch, void* stream) {
+    return launch_reduce<R_SUM>("sum", a, nullptr, n, 0.0f, out, scratch, stream);
+}
+ctk_status ctk_dot_f32(const float* a, const float* b, int64_t n, float* out, void* scratch, void* stream) {
+    return launch_reduce<R_DOT>("dot", a, b, n, 0.0f, out, scratch, stream);
+}
+ctk_status ctk_mse_f32(const float* a, const float* b, int64_t n, float* out, void* scratch, void* stream) {
+    CTK_REQUIRE(n > 0, "ctk_mse_f32: empty input");
+    return launch_reduce<R_MSE>("mse", a, b, n, static_cast<float>(n), out, scratch, stream);
+}
+ctk_status ctk_mae_f32(const float* a, const float* b, int64_t n, float* out, void* scratch, void* stream) {
+    CTK_REQUIRE(n > 0, "ctk_mae_f32: empty input");
+    return launch_reduce<R_MAE>("mae", a, b, n, static_cast<float>(n), out, scratch, stream);
+}
+
+ctk_status ctk_mse_backward_f32(const float* p, const float* t, const float* g, float* dp, int64_t n, void* stream) {
+    CTK_REQUIRE(n >= 0, "ctk_mse_backward_f32: negative size");
+    if (n == 0) return CTK_OK;
+    CTK_REQUIRE(p && t && dp, "ctk_mse_backward_f32: null pointer");
+    int grid = ctk_stream_grid((n + 3) / 4, kThreads * 2, 8);
+    mean_loss_bwd_kernel<true><<<grid, kThreads, 0, ctk::as_stream(stream)>>>(p, t, g, dp, n, static_cast<float>(n),
+                                                                                aligned16(p) && aligned16(t) && aligned16(dp));
+    CTK_LAUNCH_CHECK("mse_backward");
+    return CTK_OK;
+}
+ctk_status ctk_mae_backward_f32(const float* p, const float* t, const float* g, float* dp, int64_t n, void* stream) {
+    CTK_REQUIRE(n >= 0, "ctk_mae_backward_f32: negative size");
+    if (n == 0) return CTK_OK;
+    CTK_REQUIRE(p && t && dp, "ctk_mae_backward_f32: null pointer");
+    int grid = ctk_stream_grid((n + 3) / 4, kThreads * 2, 8);
+    mean_loss_bwd_kernel<false><<<grid, kThreads, 0, ctk::as_stream(stream)>>>(p, t, g, dp, n, static_cast<float>(n),
+                                                                                 aligned16(p) && aligned16(t) && aligned16(dp));
+    CTK_LAUNCH_CHECK("mae_backward");
+    return CTK_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,188 @@
+"""One Python function per C-ABI compute entry point, on DeviceArray operands.
+
+Names follow the reference's operators.  Nothing here computes: each function allocates the result
+buffer and forwards to libctorch_b200.so.
+"""
+import ctypes
+
+import numpy as np
+
+from ._lib import lib, check
+from .device import DeviceArray, _sh
+
+OP = dict(Add=0, Sub=1, Neg=2, Mul=3, Div=4, MatMul=5, Dot=6, Cos=7, Sin=8, ReLU=11, Tanh=12, Sigmoid=13,
+          Softmax=14, MSE=17, MAE=18, CE=19, Sum=21)
+B_SAME, B_SCALAR, B_ROW, A_SCALAR = 0, 1, 2, 3
+MODE_3XTF32, MODE_TF32, MODE_FP32_SIMT = 0, 1, 2
+MODES = {"3xtf32": 0, "tf32": 1, "fp32_simt": 2}
+
+_i64 = ctypes.c_int64
+_f = ctypes.c_float
+
+
+def binary(op, a, b, layout=B_SAME, out=None, stream=None):
+    big = b if layout == A_SCALAR else a
+    out = out or DeviceArray(big.shape)
+    inner = b.size if layout == B_ROW else 1
+    check(lib.ctk_binary_f32(OP[op], a.p, b.p, out.p, _i64(big.size), layout, _i64(inner), _sh(stream)))
+    return out
+
+
+def unary(op, a, out=None, stream=None):
+    out = out or DeviceArray(a.shape)
+    check(lib.ctk_unary_f32(OP[op], a.p, out.p, _i64(a.size), _sh(stream)))
+    return out
+
+
+def scalar(kind, a, s, out=None, stream=None):
+    out = out or DeviceArray(a.shape)
+    check(lib.ctk_scalar_f32(kind, a.p, _f(s), out.p, _i64(a.size), _sh(stream)))
+    return out
+
+
+def fill(a, value, stream=None):
+    check(lib.ctk_fill_f32(a.p, _f(value), None, _i64(a.size), _sh(stream)))
+    return a
+
+
+def tile(src, n, stream=None):
+    out = DeviceArray((n,))
+    check(lib.ctk_tile_f32(src.p, _i64(src.size), out.p, _i64(n), _sh(stream)))
+    return out
+
+
+def unary_backward(op, x, g, stream=None):
+    dx = DeviceArray(g.shape)
+    check(lib.ctk_unary_backward_f32(OP[op], x.p if x is not None else None, g.p, dx.p, _i64(g.size), _sh(stream)))
+    return dx
+
+
+def binary_backward(op, a, b, g, layout=B_SAME, want_da=True, want_db=True, stream=None):
+    da = DeviceArray(a.shape) if want_da else None
+    db = DeviceArray(b.shape) if want_db else None
+    inner = b.size if layout == B_ROW else 1
+    check(lib.ctk_binary_backward_f32(OP[op], a.p, b.p, g.p, da.p if da else None, db.p if db else None, _i64(g.size),
+                                      layout, _i64(inner), _sh(stream)))
+    return da, db
+
+
+def accumulate(dst, src, stream=None):
+    check(lib.ctk_accumulate_f32(dst.p, src.p, _i64(dst.size), _sh(stream)))
+    return dst
+
+
+def sgd_update(p, g, lr, stream=None):
+    check(lib.ctk_sgd_update_f32(p.p, g.p, _f(lr), _i64(p.size), _sh(stream)))
+    return p
+
+
+def _scalar_out():
+    return DeviceArray(())
+
+
+def sum(a, scratch=None, stream=None):  # noqa: A001 (mirrors Tensor::sum)
+    out = _scalar_out()
+    check(lib.ctk_sum_f32(a.p, _i64(a.size), out.p, scratch.p if scratch else None, _sh(stream)))
+    return out
+
+
+def dot(a, b, stream=None):
+    out = _scalar_out()
+    check(lib.ctk_dot_f32(a.p, b.p, _i64(a.size), out.p, None, _sh(stream)))
+    return out
+
+
+def mse(a, b, stream=None):
+    out = _scalar_out()
+    check(lib.ctk_mse_f32(a.p, b.p, _i64(a.size), out.p, None, _sh(stream)))
+    return out
+
+
+def mae(a, b, stream=None):
+    out = _scalar_out()
+    check(lib.ctk_mae_f32(a.p, b.p, _i64(a.size), out.p, None, _sh(stream)))
+    return out
+
+
+def mse_backward(p, t, g=None, stream=None):
+    dp = DeviceArray(p.shape)
+    check(lib.ctk_mse_backward_f32(p.p, t.p, g.p if g else None, dp.p, _i64(p.size), _sh(stream)))
+    return dp
+
+
+def mae_backward(p, t, g=None, stream=None):
+    dp = DeviceArray(p.shape)
+    check(lib.ctk_mae_backward_f32(p.p, t.p, g.p if g else None, dp.p, _i64(p.size), _sh(stream)))
+    return dp
+
+
+def _rc(a):
+    return (1, a.shape[0]) if len(a.shape) == 1 else (a.shape[0], a.shape[1])
+
+
+def softmax(x, out=None, stream=None):
+    r, c = _rc(x)
+    out = out or DeviceArray(x.shape)
+    check(lib.ctk_softmax_rows_f32(x.p, out.p, _i64(r), _i64(c), _sh(stream)))
+    return out
+
+
+def softmax_backward(y, g, stream=None):
+    r, c = _rc(y)
+    dx = DeviceArray(y.shape)
+    check(lib.ctk_softmax_backward_rows_f32(y.p, g.p, dx.p, _i64(r), _i64(c), _sh(stream)))
+    return dx
+
+
+def cross_entropy(logits, target, stream=None, bad_flag=None):
+    """target: one-hot of logits' shape, or [rows] class indices stored as floats."""
+    r, c = _rc(logits)
+    out = _scalar_out()
+    if target.shape == logits.shape:
+        check(lib.ctk_ce_onehot_f32(logits.p, target.p, _i64(r), _i64(c), out.p, None, _sh(stream)))
+    else:
+        check(lib.ctk_ce_index_f32(logits.p, target.p, _i64(r), _i64(c), out.p, bad_flag.p if bad_flag else None, None, _sh(stream)))
+    return out
+
+
+def cross_entropy_backward(logits, onehot, g=None, stream=None):
+    r, c = _rc(logits)
+    d = DeviceArray(logits.shape)
+    check(lib.ctk_ce_backward_f32(logits.p, onehot.p, g.p if g else None, d.p, _i64(r), _i64(c), _sh(stream)))
+    return d
+
+
+def cross_entropy_fused(logits, labels, stream=None, bad_flag=None):
+    r, c = _rc(logits)
+    out = _scalar_out()
+    d = DeviceArray(logits.shape)
+    check(lib.ctk_ce_fused_index_f32(logits.p, labels.p, _i64(r), _i64(c), out.p, d.p, bad_flag.p if bad_flag else None, None, _sh(stream)))
+    return out, d
+
+
+def matmul(a, b, ta=False, tb=False, mode=-1, out=None, workspace=None, stream=None):
+    """a stored [m,k] (or [k,m] viewed through t() if ta); b stored [k,n] (or [n,k] if tb)."""
+    mode = MODES.get(mode, mode)
+    m, k = (a.shape[1], a.shape[0]) if ta else a.shape
+    n = b.shape[0] if tb else b.shape[1]
+    sa = (1, m) if ta else (k, 1)
+    sb = (1, k) if tb else (n, 1)
+    out = out or DeviceArray((m, n))
+    check(lib.ctk_matmul_f32(a.p, b.p, out.p, _i64(m), _i64(n), _i64(k), _i64(sa[0]), _i64(sa[1]), _i64(sb[0]),
+                             _i64(sb[1]), mode, workspace.p if workspace else None, _sh(stream)))
+    return out
+
+
+def matmul_path(a, b, ta=False, tb=False, mode=-1):
+    mode = MODES.get(mode, mode)
+    m, k = (a.shape[1], a.shape[0]) if ta else a.shape
+    n = b.shape[0] if tb else b.shape[1]
+    sa = (1, m) if ta else (k, 1)
+    sb = (1, k) if tb else (n, 1)
+    return lib.ctk_matmul_path(a.p, b.p, _i64(m), _i64(n), _i64(k), _i64(sa[0]), _i64(sa[1]), _i64(sb[0]), _i64(sb[1]), mode)
+
+
+def matmul_status():
+    s = ctypes.c_int()
+    check(lib.ctk_matmul_status(ctypes.byref(s)))
+    return s.value

@@ -1,0 +1,221 @@
+/*
+ * ctorch_b200 -- C ABI of the B200 (sm_100a) kernel library behind CTorch's reserved
+ * DeviceType::kCUDA slot.
+ *
+ * This is the boundary the reference's `*_CUDA_kernel(const Tensor&, ...)` adapters bind to
+ * (prototypes reserved in the reference at src/kernels/kernels.h:42-242, dispatched by
+ * include/Ctorch_Scheduler.h:86-166).  Plain pointers and sizes only: every pointer named
+ * "device" is a CUDA device pointer of the current device, every `stream` is a cudaStream_t
+ * passed as void* (NULL = the legacy default stream).
+ *
+ * Conventions
+ *   - every function returns 0 on success or a non-zero ctk_status; ctk_last_error() gives the
+ *     message of the calling thread's last failure;
+ *   - launches are asynchronous on `stream`; nothing synchronises unless its comment says so;
+ *   - all data are fp32 (the reference path is fp32 only); labels are floats holding integers,
+ *     as in the reference;
+ *   - operator codes are the numeric values of the reference's `enum class op`
+ *     (include/Ctools.h:175-209), so an adapter can pass `static_cast<int>(op)`;
+ *   - there is no CPU fallback anywhere: without a usable CUDA device every call fails with
+ *     CTK_ERR_CUDA.
+ */
+#ifndef CTORCH_B200_H
+#define CTORCH_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int ctk_status;
+enum {
+    CTK_OK = 0,
+    CTK_ERR_INVALID = 1,  /* bad argument (shape, stride, mode, null pointer)      */
+    CTK_ERR_CUDA = 2,     /* a CUDA runtime / driver call failed                   */
+    CTK_ERR_NCCL = 3,     /* an NCCL call failed                                   */
+    CTK_ERR_KERNEL = 4,   /* a kernel reported a bounded wait that ran out         */
+    CTK_ERR_LIMIT = 5     /* size beyond a documented maximum                      */
+};
+
+/* Values of the reference's `enum class op` that this library implements. */
+enum {
+    CTK_OP_ADD = 0, CTK_OP_SUB = 1, CTK_OP_NEG = 2, CTK_OP_MUL = 3, CTK_OP_DIV = 4,
+    CTK_OP_MATMUL = 5, CTK_OP_DOT = 6, CTK_OP_COS = 7, CTK_OP_SIN = 8, CTK_OP_RELU = 11,
+    CTK_OP_TANH = 12, CTK_OP_SIGMOID = 13, CTK_OP_SOFTMAX = 14, CTK_OP_MSE = 17, CTK_OP_MAE = 18,
+    CTK_OP_CE = 19, CTK_OP_SUM = 21
+};
+
+/* Layout of the operands of a binary elementwise op with n result elements. */
+enum {
+    CTK_B_SAME = 0,   /* a[n], b[n]                                                       */
+    CTK_B_SCALAR = 1, /* a[n], b[1]           (reference: b.numel()==1 / 0-D operand)     */
+    CTK_B_ROW = 2,    /* a[n/inner, inner], b[inner]   (reference: [N,H] op [H])           */
+    CTK_A_SCALAR = 3  /* a[1], b[n]           (reference: 0-D left operand of Sub/Mul)     */
+};
+
+/* MatMul precision modes (north star: 3xTF32 for fp32-level accuracy, plain TF32). */
+enum { CTK_MATMUL_3XTF32 = 0, CTK_MATMUL_TF32 = 1, CTK_MATMUL_FP32_SIMT = 2 };
+
+/* ------------------------------------------------------------------------------------------- */
+/* Errors, device, memory, streams, events.                                                     */
+/* Replaces the host-only allocation of the reference's Storage (include/Storage.h:77, 88-93,   */
+/* 175-181): device allocation from a stream-ordered pool plus pinned host staging.             */
+/* ------------------------------------------------------------------------------------------- */
+const char* ctk_last_error(void);
+int ctk_version(void);
+ctk_status ctk_device_count(int* count);
+ctk_status ctk_set_device(int ordinal);
+ctk_status ctk_get_device(int* ordinal);
+ctk_status ctk_device_sync(void);
+/* SM count, total and free device memory of the current device (any pointer may be NULL). */
+ctk_status ctk_device_info(int* sm_count, size_t* total_bytes, size_t* free_bytes);
+
+ctk_status ctk_malloc(void** device_ptr, size_t bytes);      /* pooled; bytes==0 gives NULL    */
+ctk_status ctk_free(void* device_ptr);
+ctk_status ctk_malloc_host(void** pinned_ptr, size_t bytes); /* page-locked staging memory     */
+ctk_status ctk_free_host(void* pinned_ptr);
+ctk_status ctk_memcpy_h2d(void* device_dst, const void* host_src, size_t bytes, void* stream);
+ctk_status ctk_memcpy_d2h(void* host_dst, const void* device_src, size_t bytes, void* stream);
+ctk_status ctk_memcpy_d2d(void* device_dst, const void* device_src, size_t bytes, void* stream);
+ctk_status ctk_memset(void* device_ptr, int byte_value, size_t bytes, void* stream);
+
+ctk_status ctk_stream_create(void** stream);
+ctk_status ctk_stream_destroy(void* stream);
+ctk_status ctk_stream_sync(void* stream);
+ctk_status ctk_event_create(void** event);
+ctk_status ctk_event_destroy(void* event);
+ctk_status ctk_event_record(void* event, void* stream);
+ctk_status ctk_event_sync(void* event);
+ctk_status ctk_event_elapsed_ms(void* start_event, void* stop_event, float* ms);
+ctk_status ctk_stream_wait_event(void* stream, void* event);
+/* Number of kernels this library has launched in this process (bench bookkeeping). */
+uint64_t ctk_launch_count(void);
+
+/* ------------------------------------------------------------------------------------------- */
+/* Elementwise, forward.                                                                        */
+/* ------------------------------------------------------------------------------------------- */
+/* out = a (op) b, op in {ADD,SUB,MUL,DIV}.  Replaces Add/Sub/Mul/Div_BASIC_kernel
+ * (src/kernels/CPU-BASIC/Add_BASIC_kernel.cpp:11-71, Sub_..:12-62, Mul_..:13-63, Div_..:12-47).
+ * `inner` is only read for CTK_B_ROW.  Division is IEEE (x/0 = inf, 0/0 = NaN), as the reference
+ * stores. */
+ctk_status ctk_binary_f32(int op, const float* a, const float* b, float* out, int64_t n, int layout,
+                          int64_t inner, void* stream);
+/* out = op(a), op in {NEG,RELU,SIGMOID,TANH,SIN,COS}.  Replaces Neg/ReLU/Sigmoid/Tanh/Sin/
+ * Cos_BASIC_kernel (src/kernels/CPU-BASIC/*.cpp).  Tanh uses the reference's
+ * (e^x - e^-x)/(e^x + e^-x), not tanhf. */
+ctk_status ctk_unary_f32(int op, const float* a, float* out, int64_t n, void* stream);
+/* Tensor-op-float forms that the reference computes with host loops, not through the scheduler
+ * (src/Tensor.cpp:751-973, 1416-1453).  kind: 0 a*s, 1 a+s, 2 a/s, 3 s-a, 4 s/a. */
+ctk_status ctk_scalar_f32(int kind, const float* a, float s, float* out, int64_t n, void* stream);
+/* p[i] = value.  Replaces Tensor::zero/ones host loops (src/Tensor.cpp:390-455) and the 0-D
+ * gradient fill of AutoDiff::check_and_adjust_grad_shape (src/AutoDiff.cpp:579-627).
+ * If value_device is non-NULL the value is read from that device scalar instead. */
+ctk_status ctk_fill_f32(float* p, float value, const float* value_device, int64_t n, void* stream);
+/* dst[i] = src[i % src_n]: Tensor::broadcast_to for a trailing-dims broadcast
+ * (src/Tensor.cpp:289-387) and the lower-rank tiling of the grad-shape adjustment
+ * (src/AutoDiff.cpp:633-687). */
+ctk_status ctk_tile_f32(const float* src, int64_t src_n, float* dst, int64_t n, void* stream);
+
+/* ------------------------------------------------------------------------------------------- */
+/* Elementwise, backward (the per-op rules of AutoDiff::backward, src/AutoDiff.cpp:1216-1416),  */
+/* each fused into one pass; intermediate roundings follow the reference's operator chain.      */
+/* ------------------------------------------------------------------------------------------- */
+/* dx = g * d op(x)/dx for op in {NEG,RELU,SIGMOID,TANH,SIN,COS}. */
+ctk_status ctk_unary_backward_f32(int op, const float* x, const float* g, float* dx, int64_t n, void* stream);
+/* da, db (either may be NULL) for op in {ADD,SUB,MUL,DIV}; g has n elements.  For CTK_B_ROW db has
+ * `inner` elements and receives ROW 0 of the full gradient, for CTK_B_SCALAR db has one element
+ * and receives element 0: the reference's grad-shape adjustment gathers with index 0 on the
+ * broadcast dims, it does not sum (src/AutoDiff.cpp:690-757). */
+ctk_status ctk_binary_backward_f32(int op, const float* a, const float* b, const float* g, float* da,
+                                   float* db, int64_t n, int layout, int64_t inner, void* stream);
+/* dst[i] += src[i]: the gradient accumulation loop (src/AutoDiff.cpp:1868-1907). */
+ctk_status ctk_accumulate_f32(float* dst, const float* src, int64_t n, void* stream);
+/* p[i] = fma(-g[i], lr, p[i]): the SGD loop of mnist/mnist.cpp:80-92 (one rounding, as compiled). */
+ctk_status ctk_sgd_update_f32(float* p, const float* g, float lr, int64_t n, void* stream);
+
+/* ------------------------------------------------------------------------------------------- */
+/* Reductions to a scalar and row-wise losses.                                                  */
+/* `out` is a DEVICE scalar.  `scratch` is device memory of at least ctk_reduce_scratch_bytes() */
+/* bytes that no other running kernel uses; pass NULL to use the library's per-device scratch   */
+/* (allocated on first use; calls that share it must be ordered on the GPU).                    */
+/* ------------------------------------------------------------------------------------------- */
+size_t ctk_reduce_scratch_bytes(void);
+/* Tensor::sum (src/Tensor.cpp:638-666). */
+ctk_status ctk_sum_f32(const float* a, int64_t n, float* out, void* scratch, void* stream);
+/* Dot_BASIC_kernel (src/kernels/CPU-BASIC/Dot_BASIC_kernel.cpp:12-46). */
+ctk_status ctk_dot_f32(const float* a, const float* b, int64_t n, float* out, void* scratch, void* stream);
+/* MSE_BASIC_kernel / MAE_BASIC_kernel (:12-46 each): mean over ALL elements. */
+ctk_status ctk_mse_f32(const float* a, const float* b, int64_t n, float* out, void* scratch, void* stream);
+ctk_status ctk_mae_f32(const float* a, const float* b, int64_t n, float* out, void* scratch, void* stream);
+/* dp = ((p - t) * 2 / n) * g and dp = (sign(p - t) / n) * g (src/AutoDiff.cpp:1491-1516,
+ * 1602-1642); g is a device scalar (the upstream 0-D gradient). */
+ctk_status ctk_mse_backward_f32(const float* p, const float* t, const float* g_device, float* dp, int64_t n, void* stream);
+ctk_status ctk_mae_backward_f32(const float* p, const float* t, const float* g_device, float* dp, int64_t n, void* stream);
+
+/* Row softmax over the last dim of [rows, cols]: Softmax_BASIC_kernel
+ * (src/kernels/CPU-BASIC/Softmax_BASIC_kernel.cpp:16-101) == Tensor::softmax row path
+ * (src/Tensor.cpp:1712-1727). */
+ctk_status ctk_softmax_rows_f32(const float* x, float* y, int64_t rows, int64_t cols, void* stream);
+/* dx = y * (g - sum_j g_j y_j) per row, from the saved OUTPUT y (src/AutoDiff.cpp:1417-1490). */
+ctk_status ctk_softmax_backward_rows_f32(const float* y, const float* g, float* dx, int64_t rows, int64_t cols, void* stream);
+/* Softmax + cross entropy SUMMED over rows, clamp max(p, 1e-10): CrossEntropy_BASIC_kernel
+ * one-hot path (CrossEntropy_BASIC_kernel.cpp:36-66) and index-label path (:88-120). */
+ctk_status ctk_ce_onehot_f32(const float* logits, const float* onehot, int64_t rows, int64_t cols,
+                             float* out, void* scratch, void* stream);
+/* An out-of-range label makes the reference return an empty tensor; here *out becomes NaN and
+ * the device word `bad_label_flag` (may be NULL) is set to 1. */
+ctk_status ctk_ce_index_f32(const float* logits, const float* labels, int64_t rows, int64_t cols,
+                            float* out, int* bad_label_flag, void* scratch, void* stream);
+/* dlogits = (softmax(logits) - onehot) * g (src/AutoDiff.cpp:1517-1601); g is a device scalar,
+ * or NULL for 1. */
+ctk_status ctk_ce_backward_f32(const float* logits, const float* onehot, const float* g_device,
+                               float* dlogits, int64_t rows, int64_t cols, void* stream);
+/* Forward and backward in one pass over the logits, index labels: loss (summed) to *out and
+ * dlogits = softmax - onehot(label).  Checked against the one-hot reference path. */
+ctk_status ctk_ce_fused_index_f32(const float* logits, const float* labels, int64_t rows, int64_t cols,
+                                  float* out, float* dlogits, int* bad_label_flag, void* scratch, void* stream);
+
+/* ------------------------------------------------------------------------------------------- */
+/* MatMul.  Replaces MatMul_BASIC_kernel (src/kernels/CPU-BASIC/MatMul_BASIC_kernel.cpp:13-57): */
+/* C[i,j] = sum_l A[i*sa0 + l*sa1] * B[l*sb0 + j*sb1], C row-major [m,n]; strides in ELEMENTS,   */
+/* exactly as that kernel reads them, so the stride-swapped views made by Tensor::t() (used by   */
+/* the backward rule for dA = dC.B^T and dB = A^T.dC, src/AutoDiff.cpp:1702-1704, 1808-1810)     */
+/* need no copy.                                                                                 */
+/*   mode  CTK_MATMUL_3XTF32: three tcgen05 TF32 products of an exact hi/lo split, fp32 TMEM      */
+/*         accumulation (fp32-level accuracy);  CTK_MATMUL_TF32: one TF32 product;                */
+/*         CTK_MATMUL_FP32_SIMT: fp32 FMA on CUDA cores (also taken automatically when an         */
+/*         operand cannot be addressed by TMA: a stride-1 dim is required and the other stride    */
+/*         must be a multiple of 4 elements, base 16-byte aligned);  -1: the process default.     */
+/*   workspace: device scratch for the hi/lo split, at least ctk_matmul_workspace_bytes() bytes;  */
+/*         NULL uses the library's per-device workspace (grown on demand; calls sharing it must   */
+/*         be ordered on the GPU).                                                                */
+/* ------------------------------------------------------------------------------------------- */
+ctk_status ctk_set_matmul_mode(int mode);
+int ctk_get_matmul_mode(void);
+size_t ctk_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k, int mode);
+ctk_status ctk_matmul_f32(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
+                          int64_t sa0, int64_t sa1, int64_t sb0, int64_t sb1, int mode,
+                          void* workspace, void* stream);
+/* Which path the call above would take: 0 tcgen05, 1 SIMT. */
+int ctk_matmul_path(const float* a, const float* b, int64_t m, int64_t n, int64_t k,
+                    int64_t sa0, int64_t sa1, int64_t sb0, int64_t sb1, int mode);
+/* Device status word of the tensor-core kernel's bounded waits: 0 = none ran out.  Reading it
+ * synchronises the device. */
+ctk_status ctk_matmul_status(int* status);
+
+/* ------------------------------------------------------------------------------------------- */
+/* Data-parallel gradient exchange (no counterpart in the reference, which is single-process):  */
+/* one NCCL communicator per process, fp32 sum.                                                  */
+/* ------------------------------------------------------------------------------------------- */
+#define CTK_COMM_ID_BYTES 128
+ctk_status ctk_comm_unique_id(void* id_out_128_bytes);
+ctk_status ctk_comm_init_rank(void** comm, const void* id_128_bytes, int world_size, int rank);
+ctk_status ctk_comm_destroy(void* comm);
+ctk_status ctk_allreduce_sum_f32(void* comm, float* device_buf, int64_t n, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CTORCH_B200_H */

@@ -1,0 +1,341 @@
+"""TEST INFRASTRUCTURE ONLY: the parity oracle.
+
+Two CPU implementations behind one numpy-facing interface:
+
+* ``Oracle``    -- ``libctorch_oracle.so``, the plain-C restatement in ``ctorch_oracle.c``.
+* ``Reference`` -- ``_ref/libctorch_ref.so``, the UNMODIFIED reference sources compiled where they
+  lie plus ``ref_shim.cpp``.  Only exists where it has been built (``make -C oracle``).
+
+Only ``tests/``, ``__graft_entry__.smoke()`` and ``bench.py``'s CPU-baseline leg may import this
+package; the product package never does.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SO = os.path.join(HERE, "libctorch_oracle.so")
+REF_SO = os.path.join(HERE, "_ref", "libctorch_ref.so")
+
+OP = dict(Add=0, Sub=1, Neg=2, Mul=3, Div=4, MatMul=5, Dot=6, Cos=7, Sin=8, ReLU=11, Tanh=12,
+          Sigmoid=13, Softmax=14, MSE=17, MAE=18, CE=19, Sum=21)
+B_SAME, B_SCALAR, B_ROW, A_SCALAR = 0, 1, 2, 3
+
+_f32p = ctypes.POINTER(ctypes.c_float)
+_i64p = ctypes.POINTER(ctypes.c_int64)
+_i32p = ctypes.POINTER(ctypes.c_int)
+
+
+def _fp(a):
+    return a.ctypes.data_as(_f32p) if a is not None else None
+
+
+def _f32(a):
+    # np.ascontiguousarray would promote a 0-D array to shape (1,); 0-D operands matter here.
+    return np.require(a, dtype=np.float32, requirements="C")
+
+
+def _shape(a):
+    s = np.asarray(a.shape, dtype=np.int64)
+    return s, s.ctypes.data_as(_i64p), a.ndim
+
+
+def build(ref_root="/root/reference"):
+    """Compile the C restatement (always) and the reference library (if its sources are there)."""
+    subprocess.run(["make", "-s", "-C", HERE, f"REF={ref_root}"], check=True)
+
+
+def pack_params(Ws, bs):
+    return np.concatenate([np.concatenate([_f32(W).ravel(), _f32(b).ravel()]) for W, b in zip(Ws, bs)])
+
+
+def unpack_params(p, dims):
+    Ws, bs, o = [], [], 0
+    for i, j in zip(dims[:-1], dims[1:]):
+        Ws.append(p[o:o + i * j].reshape(i, j)); o += i * j
+        bs.append(p[o:o + j]); o += j
+    return Ws, bs
+
+
+class Oracle:
+    """ctypes face of ctorch_oracle.c."""
+
+    kind = "port"
+
+    def __init__(self):
+        if not os.path.exists(ORACLE_SO):
+            build()
+        L = self.L = ctypes.CDLL(ORACLE_SO)
+        for name in ("orc_sum", "orc_dot", "orc_mse", "orc_mae", "orc_ce_onehot"):
+            getattr(L, name).restype = ctypes.c_float
+
+    # ---- forward ----
+    def binary(self, op, a, b, bmode=B_SAME):
+        a, b = _f32(a), _f32(b)
+        big = b if bmode == A_SCALAR else a
+        out = np.empty_like(big)
+        inner = b.size if bmode == B_ROW else 1
+        self.L.orc_binary(OP[op], _fp(a), _fp(b), _fp(out), ctypes.c_int64(big.size), bmode, ctypes.c_int64(inner))
+        return out
+
+    def unary(self, op, a):
+        a = _f32(a)
+        out = np.empty_like(a)
+        self.L.orc_unary(OP[op], _fp(a), _fp(out), ctypes.c_int64(a.size))
+        return out
+
+    def scalar(self, kind, a, s):
+        a = _f32(a)
+        out = np.empty_like(a)
+        self.L.orc_scalar(kind, _fp(a), ctypes.c_int64(a.size), ctypes.c_float(s), _fp(out))
+        return out
+
+    def matmul(self, a, b, ta=False, tb=False):
+        """a stored [m,k] (or [k,m] if ta), b stored [k,n] (or [n,k] if tb)."""
+        a, b = _f32(a), _f32(b)
+        m, k = (a.shape[1], a.shape[0]) if ta else a.shape
+        n = b.shape[0] if tb else b.shape[1]
+        sa = (1, m) if ta else (k, 1)
+        sb = (1, k) if tb else (n, 1)
+        c = np.empty((m, n), np.float32)
+        i64 = ctypes.c_int64
+        self.L.orc_matmul(_fp(a), _fp(b), _fp(c), i64(m), i64(k), i64(n), i64(sa[0]), i64(sa[1]), i64(sb[0]), i64(sb[1]))
+        return c
+
+    def matmul_rows(self, a, b, rows, ta=False, tb=False):
+        a, b = _f32(a), _f32(b)
+        rows = np.ascontiguousarray(rows, dtype=np.int64)
+        m, k = (a.shape[1], a.shape[0]) if ta else a.shape
+        n = b.shape[0] if tb else b.shape[1]
+        sa = (1, m) if ta else (k, 1)
+        sb = (1, k) if tb else (n, 1)
+        c = np.empty((rows.size, n), np.float32)
+        i64 = ctypes.c_int64
+        self.L.orc_matmul_rows(_fp(a), _fp(b), _fp(c), rows.ctypes.data_as(_i64p), i64(rows.size), i64(k), i64(n),
+                               i64(sa[0]), i64(sa[1]), i64(sb[0]), i64(sb[1]))
+        return c
+
+    def sum(self, a):
+        a = _f32(a)
+        return np.float32(self.L.orc_sum(_fp(a), ctypes.c_int64(a.size)))
+
+    def dot(self, a, b):
+        a, b = _f32(a), _f32(b)
+        return np.float32(self.L.orc_dot(_fp(a), _fp(b), ctypes.c_int64(a.size)))
+
+    def mse(self, a, b):
+        a, b = _f32(a), _f32(b)
+        return np.float32(self.L.orc_mse(_fp(a), _fp(b), ctypes.c_int64(a.size)))
+
+    def mae(self, a, b):
+        a, b = _f32(a), _f32(b)
+        return np.float32(self.L.orc_mae(_fp(a), _fp(b), ctypes.c_int64(a.size)))
+
+    def softmax(self, x):
+        x = _f32(x)
+        x2 = x.reshape(1, -1) if x.ndim == 1 else x
+        out = np.empty_like(x2)
+        self.L.orc_softmax_rows(_fp(x2), _fp(out), ctypes.c_int64(x2.shape[0]), ctypes.c_int64(x2.shape[1]))
+        return out.reshape(x.shape)
+
+    def ce(self, logits, target):
+        """target: one-hot of logits' shape, or a [rows] vector of class indices stored as floats."""
+        logits, target = _f32(logits), _f32(target)
+        l2 = logits.reshape(1, -1) if logits.ndim == 1 else logits
+        r, c = l2.shape
+        if target.shape == logits.shape:
+            return np.float32(self.L.orc_ce_onehot(_fp(l2), _fp(target), ctypes.c_int64(r), ctypes.c_int64(c)))
+        loss = ctypes.c_float()
+        rc = self.L.orc_ce_index(_fp(l2), _fp(target), ctypes.c_int64(r), ctypes.c_int64(c), ctypes.byref(loss))
+        if rc:
+            raise ValueError("label out of range")
+        return np.float32(loss.value)
+
+    # ---- backward ----
+    def grad_unary(self, op, x, g):
+        x, g = _f32(x), _f32(g)
+        dx = np.empty_like(x)
+        if op == "Softmax":
+            y = self.softmax(x)
+            y2 = y.reshape(1, -1) if y.ndim == 1 else y
+            self.L.orc_softmax_backward_rows(_fp(y2), _fp(g), _fp(dx), ctypes.c_int64(y2.shape[0]), ctypes.c_int64(y2.shape[1]))
+            return dx
+        self.L.orc_grad_unary(OP[op], _fp(x), _fp(g), _fp(dx), ctypes.c_int64(x.size))
+        return dx
+
+    def grad_binary(self, op, a, b, g, bmode=B_SAME):
+        a, b, g = _f32(a), _f32(b), _f32(g)
+        da, db = np.empty_like(a), np.empty_like(b)
+        inner = b.size if bmode == B_ROW else 1
+        self.L.orc_grad_binary(OP[op], _fp(a), _fp(b), _fp(g), _fp(da), _fp(db), ctypes.c_int64(a.size), bmode, ctypes.c_int64(inner))
+        return da, db
+
+    def grad_loss(self, op, p, t, g=1.0):
+        p, t = _f32(p), _f32(t)
+        dp = np.empty_like(p)
+        if op == "CE":
+            p2 = p.reshape(1, -1) if p.ndim == 1 else p
+            self.L.orc_ce_backward(_fp(p2), _fp(t), ctypes.c_float(g), _fp(dp), ctypes.c_int64(p2.shape[0]), ctypes.c_int64(p2.shape[1]))
+        elif op == "MSE":
+            self.L.orc_mse_backward(_fp(p), _fp(t), ctypes.c_float(g), _fp(dp), ctypes.c_int64(p.size))
+        elif op == "MAE":
+            self.L.orc_mae_backward(_fp(p), _fp(t), ctypes.c_float(g), _fp(dp), ctypes.c_int64(p.size))
+        else:
+            raise ValueError(op)
+        return dp
+
+    # ---- training step ----
+    _mlp = "orc_mlp_train"
+
+    def mlp_train(self, dims, x, labels, params, lr, steps, grad_steps=(), want_logits=True):
+        """x [replicas, n_batches, batch, dims[0]], labels [replicas, n_batches, batch] (floats).
+        Returns dict(params, losses [steps, replicas], grads [len(grad_steps), n_params], logits)."""
+        x, labels = _f32(x), _f32(labels)
+        replicas, n_batches, batch, _ = x.shape
+        dims_a = np.asarray(dims, dtype=np.int64)
+        p = _f32(params).copy()
+        losses = np.zeros((steps, replicas), np.float32)
+        gs = np.asarray(list(grad_steps), dtype=np.int32)
+        grads = np.zeros((max(len(gs), 1), p.size), np.float32)
+        logits = np.zeros((replicas, batch, dims[-1]), np.float32)
+        rc = getattr(self.L, self._mlp)(
+            len(dims) - 1, dims_a.ctypes.data_as(_i64p), ctypes.c_int64(batch), steps, replicas, _fp(x), _fp(labels),
+            n_batches, _fp(p), ctypes.c_float(lr), _fp(losses), gs.ctypes.data_as(_i32p), len(gs), _fp(grads),
+            _fp(logits) if want_logits else None)
+        if rc:
+            raise RuntimeError(self.last_error())
+        return dict(params=p, losses=losses, grads=grads[:len(gs)], logits=logits)
+
+    def last_error(self):
+        return "oracle error"
+
+
+class Reference(Oracle):
+    """ctypes face of ref_shim.cpp: the reference's own CPU-BASIC results."""
+
+    kind = "reference"
+    _mlp = "ref_mlp_train"
+
+    @staticmethod
+    def available():
+        return os.path.exists(REF_SO)
+
+    def __init__(self):
+        if not os.path.exists(REF_SO):
+            raise FileNotFoundError(REF_SO + " (build it with `make -C oracle` where the reference checkout exists)")
+        L = self.L = ctypes.CDLL(REF_SO)
+        L.ref_last_error.restype = ctypes.c_char_p
+        self._chk(L.ref_init())
+
+    def last_error(self):
+        return self.L.ref_last_error().decode("utf-8", "replace")
+
+    def _chk(self, rc):
+        if rc:
+            raise RuntimeError("reference threw: " + self.last_error())
+
+    def _bin(self, op, a, b):
+        a, b = _f32(a), _f32(b)
+        _, ap, ar = _shape(a)
+        _, bp, br = _shape(b)
+        out = np.empty(max(a.size, b.size), np.float32)
+        n = ctypes.c_int64()
+        sa, sb = _shape(a), _shape(b)
+        self._chk(self.L.ref_binary(OP[op], _fp(a), sa[1], ar, _fp(b), sb[1], br, _fp(out), ctypes.byref(n)))
+        return out[:n.value]
+
+    def binary(self, op, a, b, bmode=B_SAME):
+        a, b = _f32(a), _f32(b)
+        if bmode == B_SCALAR:
+            b = b.reshape(())       # a 0-D operand is the only scalar form Sub/Mul accept
+        if bmode == A_SCALAR:
+            a = a.reshape(())
+        big = b if bmode == A_SCALAR else a
+        return self._bin(op, a, b).reshape(big.shape)
+
+    def unary(self, op, a):
+        a = _f32(a)
+        s = _shape(a)
+        out = np.empty(a.size, np.float32)
+        n = ctypes.c_int64()
+        self._chk(self.L.ref_unary(OP[op], _fp(a), s[1], s[2], _fp(out), ctypes.byref(n)))
+        return out[:n.value].reshape(a.shape if n.value == a.size else ())
+
+    def scalar(self, kind, a, s):
+        a = _f32(a)
+        out = np.empty_like(a)
+        self._chk(self.L.ref_scalar(kind, _fp(a), ctypes.c_int64(a.size), ctypes.c_float(s), _fp(out)))
+        return out
+
+    def matmul(self, a, b, ta=False, tb=False):
+        a, b = _f32(a), _f32(b)
+        m, k = (a.shape[1], a.shape[0]) if ta else a.shape
+        n = b.shape[0] if tb else b.shape[1]
+        c = np.empty((m, n), np.float32)
+        i64 = ctypes.c_int64
+        self._chk(self.L.ref_matmul(_fp(a), _fp(b), i64(m), i64(k), i64(n), int(ta), int(tb), _fp(c)))
+        return c
+
+    def matmul_rows(self, a, b, rows, ta=False, tb=False):
+        return self.matmul(a, b, ta, tb)[np.asarray(rows)]
+
+    def sum(self, a):
+        return np.float32(self.unary("Sum", a).reshape(-1)[0])
+
+    def dot(self, a, b):
+        return np.float32(self._bin("Dot", a, b)[0])
+
+    def mse(self, a, b):
+        return np.float32(self._bin("MSE", a, b)[0])
+
+    def mae(self, a, b):
+        return np.float32(self._bin("MAE", a, b)[0])
+
+    def softmax(self, x):
+        return self.unary("Softmax", x)
+
+    def softmax_kernel(self, x):
+        x = _f32(x)
+        s = _shape(x)
+        out = np.empty_like(x)
+        self._chk(self.L.ref_softmax_kernel(_fp(x), s[1], s[2], _fp(out)))
+        return out
+
+    def ce(self, logits, target):
+        r = self._bin("CE", logits, target)
+        if r.size == 0:
+            raise ValueError("label out of range")
+        return np.float32(r[0])
+
+    def grad_unary(self, op, x, g):
+        x, g = _f32(x), _f32(g)
+        s = _shape(x)
+        dx = np.empty_like(x)
+        self._chk(self.L.ref_grad_unary(OP[op], _fp(x), s[1], s[2], _fp(g), _fp(dx)))
+        return dx
+
+    def grad_binary(self, op, a, b, g, bmode=B_SAME):
+        a, b, g = _f32(a), _f32(b), _f32(g)
+        if bmode == B_SCALAR:
+            b = b.reshape(())
+        sa, sb = _shape(a), _shape(b)
+        da, db = np.empty_like(a), np.empty_like(b)
+        self._chk(self.L.ref_grad_binary(OP[op], _fp(a), sa[1], sa[2], _fp(b), sb[1], sb[2], _fp(g), _fp(da), _fp(db)))
+        return da, db
+
+    def grad_loss(self, op, p, t, g=1.0):
+        p, t = _f32(p), _f32(t)
+        sp, st = _shape(p), _shape(t)
+        dp = np.empty_like(p)
+        gg = np.asarray([g], np.float32)
+        self._chk(self.L.ref_grad_binary(OP[op], _fp(p), sp[1], sp[2], _fp(t), st[1], st[2], _fp(gg), _fp(dp), None))
+        return dp
+
+    def grad_matmul(self, a, b, g):
+        a, b, g = _f32(a), _f32(b), _f32(g)
+        sa, sb = _shape(a), _shape(b)
+        da, db = np.empty_like(a), np.empty_like(b)
+        self._chk(self.L.ref_grad_binary(OP["MatMul"], _fp(a), sa[1], sa[2], _fp(b), sb[1], sb[2], _fp(g), _fp(da), _fp(db)))
+        return da, db
