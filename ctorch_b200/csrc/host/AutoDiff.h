@@ -1,0 +1,99 @@
+// AutoDiff: the tape.  Same interface and graph semantics as the reference's include/AutoDiff.h
+// and src/AutoDiff.cpp (thread-local context + RAII Guard :35-66; Node owns a copy of the tensor
+// and of its gradient :79-102; deferred record / commit; DFS topological order; per-op rules),
+// with gradients and saved tensors resident on the device and every rule a kernel launch.
+#pragma once
+#include <functional>
+#include <memory>
+#include <mutex>
+#include <unordered_map>
+#include <unordered_set>
+#include <vector>
+
+#include "Ctools.h"
+
+namespace ctorch {
+
+class Tensor;
+class AutoDiff;
+
+class AutoDiffContext {
+public:
+    static AutoDiff*& current() {
+        static thread_local AutoDiff* ctx = nullptr;
+        return ctx;
+    }
+    class Guard {
+    public:
+        explicit Guard(AutoDiff* new_ctx) : prev_ctx(current()) { current() = new_ctx; }
+        ~Guard() { current() = prev_ctx; }
+        Guard(const Guard&) = delete;
+        Guard& operator=(const Guard&) = delete;
+
+    private:
+        AutoDiff* prev_ctx;
+    };
+};
+
+class AutoDiff {
+    struct Node {
+        size_t tensor_id;
+        std::unique_ptr<Tensor> tensor;  // value at registration time (shares storage until someone writes)
+        std::unique_ptr<Tensor> grad;
+        std::vector<size_t> input_ids;
+        op operation = op::Add;
+        int op_param_i = 0;
+        bool requires_grad;
+        bool is_leaf;
+        Node(size_t id, std::unique_ptr<Tensor> t, bool req_grad, bool leaf);
+        ~Node();
+    };
+    struct PendingRecord {
+        op operation;
+        std::vector<size_t> input_ids;
+        int op_param_i = 0;
+        bool committed = false;
+    };
+
+    std::unordered_map<size_t, std::unique_ptr<Node>> id_to_node;
+    std::unordered_map<size_t, PendingRecord> pending_records;
+    std::mutex records_mutex;
+    bool retain_graph = false;
+
+    Node* get_node_by_id(size_t id);
+    void dfs_topological_sort(Node* node, std::unordered_set<Node*>& visited, std::vector<Node*>& result);
+    Tensor check_and_adjust_grad_shape(const Tensor& grad, const std::vector<size_t>& target_shape);
+    Tensor rule(Node* node, size_t input_id, Node& input_node, bool& skip);
+
+public:
+    AutoDiff();
+    ~AutoDiff();
+
+    Tensor get_grad(const Tensor* t);
+    void make_leaf(Tensor& t, bool requires_grad);
+    void zero_grad(Tensor& t);
+    void defer_record(size_t output_id, op operation, const std::vector<Tensor*>& inputs, int op_param_i = 0);
+    void commit_record(Tensor& output);
+    void update_requires_grad(Tensor& t, bool requires_grad);
+    void set_retain_graph(bool retain);
+    void backward(Tensor& root);
+    void backward(Tensor& root, Tensor grad_output);
+    void clear_graph();
+
+    // ---- additions (no counterpart in the reference) ----
+    // Called during backward right after a leaf's gradient received a contribution; a data-parallel
+    // driver uses it to start that gradient's all-reduce while the rest of backward still runs.
+    std::function<void(size_t tensor_id, Tensor& grad)> on_leaf_grad;
+    // Drops every node that a future root can no longer reach: all non-leaf nodes and all leaves that
+    // do not require grad (each step's inputs and activations, which the reference keeps forever).
+    // Leaves that require grad -- the parameters, including the snapshot taken when they were first
+    // registered, which backward keeps using -- stay, so results do not change.
+    void release_step_nodes();
+    size_t node_count();
+    // In-place access to a leaf's gradient buffer (nullptr if none).
+    Tensor* grad_buffer(const Tensor& t);
+};
+
+Tensor create_empty_tensor();
+
+}  // namespace ctorch

@@ -131,7 +131,7 @@ constexpr int BK = 32;               // 32 fp32 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 8;            // K of one tcgen05.mma.kind::tf32
 constexpr int THREADS = 192;         // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
 constexpr int SMEM_BUDGET = 200 * 1024;
-constexpr uint32_t WAIT_LIMIT = 4u << 20;  // polls per bounded wait (each poll may itself block a few us)
+constexpr uint32_t WAIT_LIMIT = 1u << 20;  // polls per bounded wait (each poll may itself block a few us)
 
 template <int BN, int TERMS>
 struct Cfg {
@@ -233,20 +233,24 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor (sm_100 format): start address >> 4 in bits [0,14), leading byte
-// offset >> 4 in [16,30), stride byte offset >> 4 in [32,46), version 1 in [46,48), 128-byte
-// swizzle (code 2) in [61,64).
-//   K-major tile  [rows][32 fp32]: rows 128 B apart, 8-row groups 1024 B apart -> SBO = 1024;
-//                 a K=8 step advances the start address by 32 B inside the swizzle row.
-//   MN-major tile [k][32 fp32 of M/N] in 32-wide column groups: 8 k-rows (1024 B) form one atom,
-//                 column groups are 4096 B apart -> LBO = 4096, SBO = 1024; a K=8 step advances the
-//                 start address by 1024 B.
-__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// offset >> 4 in [16,30), stride byte offset >> 4 in [32,46), version 1 in [46,48), swizzle code
+// in [61,64).
+//   K-major tile  [rows][32 fp32], 128-byte swizzle (16-byte chunks XOR row%8, code 2): rows 128 B
+//                 apart, 8-row groups 1024 B apart -> SBO = 1024; a K=8 step advances the start
+//                 address by 32 B inside the swizzle row.
+//   MN-major tile [k][32 fp32 of M/N] in 32-wide column groups.  For 32-bit operands the tensor
+//                 core only takes the "128-byte swizzle with 32-byte atoms" layout (32-byte chunks
+//                 XOR k%4, code 1; TMA writes it with SWIZZLE_128B_ATOM_32B): 4 k-rows (512 B) form
+//                 one atom -> SBO = 512, column groups are 4096 B apart -> LBO = 4096; a K=8 step
+//                 advances the start address by 1024 B.
+constexpr uint32_t kSwizzle128B = 2, kSwizzle128BAtom32B = 1;
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t swizzle_code) {
     uint64_t d = 0;
     d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
     d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
     d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
     d |= static_cast<uint64_t>(1) << 46;
-    d |= static_cast<uint64_t>(2) << 61;
+    d |= static_cast<uint64_t>(swizzle_code) << 61;
     return d;
 }
 
@@ -370,12 +374,14 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
                         const uint32_t a_step = A_MN ? ks * 1024u : ks * 32u;
                         const uint32_t b_step = B_MN ? ks * 1024u : ks * 32u;
                         const uint32_t a_lbo = A_MN ? 4096u : 0u, b_lbo = B_MN ? 4096u : 0u;
-                        const uint64_t a_hi = make_desc(a_addr(stage, 0) + a_step, a_lbo, 1024u);
-                        const uint64_t b_hi = make_desc(b_addr(stage, 0) + b_step, b_lbo, 1024u);
+                        const uint32_t a_sbo = A_MN ? 512u : 1024u, b_sbo = B_MN ? 512u : 1024u;
+                        const uint32_t a_sw = A_MN ? kSwizzle128BAtom32B : kSwizzle128B, b_sw = B_MN ? kSwizzle128BAtom32B : kSwizzle128B;
+                        const uint64_t a_hi = make_desc(a_addr(stage, 0) + a_step, a_lbo, a_sbo, a_sw);
+                        const uint64_t b_hi = make_desc(b_addr(stage, 0) + b_step, b_lbo, b_sbo, b_sw);
                         const uint32_t first = (kb > 0 || ks > 0) ? 1u : 0u;
                         if (TERMS == 3) {
-                            const uint64_t a_lo = make_desc(a_addr(stage, 1) + a_step, a_lbo, 1024u);
-                            const uint64_t b_lo = make_desc(b_addr(stage, 1) + b_step, b_lbo, 1024u);
+                            const uint64_t a_lo = make_desc(a_addr(stage, 1) + a_step, a_lbo, a_sbo, a_sw);
+                            const uint64_t b_lo = make_desc(b_addr(stage, 1) + b_step, b_lbo, b_sbo, b_sw);
                             tc_mma_tf32(d_tmem, a_lo, b_hi, idesc, first);  // small terms first
                             tc_mma_tf32(d_tmem, a_hi, b_lo, idesc, 1u);
                             tc_mma_tf32(d_tmem, a_hi, b_hi, idesc, 1u);
@@ -460,8 +466,9 @@ ctk_status get_encoder(EncodeTiledFn* out) {
 }
 
 // 2-D fp32 tensor {inner (contiguous), outer} with row pitch ld elements; box {32, box_outer};
-// 128-byte swizzle; out-of-range elements read as zero.
-ctk_status make_map(CUtensorMap* map, const float* base, int64_t inner, int64_t outer, int64_t ld, int box_outer) {
+// 128-byte swizzle (16-byte chunks for a K-major operand, 32-byte atoms for an MN-major one);
+// out-of-range elements read as zero.
+ctk_status make_map(CUtensorMap* map, const float* base, int64_t inner, int64_t outer, int64_t ld, int box_outer, bool mn_major) {
     EncodeTiledFn enc;
     ctk_status st = get_encoder(&enc);
     if (st) return st;
@@ -470,7 +477,8 @@ ctk_status make_map(CUtensorMap* map, const float* base, int64_t inner, int64_t 
     cuuint32_t box[2] = {32u, static_cast<cuuint32_t>(box_outer)};
     cuuint32_t estr[2] = {1u, 1u};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(CTK_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(r)));
     return CTK_OK;
@@ -625,10 +633,10 @@ ctk_status ctk_matmul_f32(const float* a, const float* b, float* c, int64_t m, i
     const int a_box = A.mn_major ? tc::BK : tc::BM;
     const int b_box = B.mn_major ? tc::BK : bn;
     ctk_status rc;
-    if ((rc = tc::make_map(&maps[0], a_hi, A.inner(), A.outer(), a_ld, a_box))) return rc;
-    if ((rc = tc::make_map(&maps[1], a_lo, A.inner(), A.outer(), a_ld, a_box))) return rc;
-    if ((rc = tc::make_map(&maps[2], b_hi, B.inner(), B.outer(), b_ld, b_box))) return rc;
-    if ((rc = tc::make_map(&maps[3], b_lo, B.inner(), B.outer(), b_ld, b_box))) return rc;
+    if ((rc = tc::make_map(&maps[0], a_hi, A.inner(), A.outer(), a_ld, a_box, A.mn_major))) return rc;
+    if ((rc = tc::make_map(&maps[1], a_lo, A.inner(), A.outer(), a_ld, a_box, A.mn_major))) return rc;
+    if ((rc = tc::make_map(&maps[2], b_hi, B.inner(), B.outer(), b_ld, b_box, B.mn_major))) return rc;
+    if ((rc = tc::make_map(&maps[3], b_lo, B.inner(), B.outer(), b_ld, b_box, B.mn_major))) return rc;
 
     tc::Params P;
     P.m = m; P.n = n; P.k = k;

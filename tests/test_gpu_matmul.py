@@ -1,0 +1,119 @@
+"""GPU parity: MatMul forward and the two backward products, every operand major-ness, both tensor
+core modes and the CUDA-core path, vs the oracle's fp32 recurrence.
+
+Tolerances (normwise, max|C - C_ref| / max|C_ref|): 1e-4 for 3xTF32, 5e-3 for TF32, 1e-5 for the
+fp32 CUDA-core path."""
+import numpy as np
+import pytest
+
+from conftest import assert_matmul_close
+
+pytestmark = pytest.mark.gpu
+
+TOL = {"3xtf32": 1e-4, "tf32": 5e-3, "fp32_simt": 1e-5}
+
+
+def _mats(m, k, n, seed=0):
+    rng = np.random.default_rng(seed)
+    return (rng.standard_normal((m, k)).astype(np.float32), rng.standard_normal((k, n)).astype(np.float32),
+            rng.standard_normal((m, n)).astype(np.float32))
+
+
+def _check_status(cb):
+    assert cb.ops.matmul_status() == 0, "a bounded wait in the tensor-core kernel ran out"
+
+
+@pytest.mark.parametrize("mode", ["tf32", "3xtf32"])
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("m,k,n", [(128, 32, 64), (128, 64, 128), (256, 96, 256), (384, 256, 512)])
+def test_tensor_core_all_major_combinations(cb, orc, mode, ta, tb, m, k, n):
+    A, B, _ = _mats(m, k, n, 1)
+    sa = A.T.copy() if ta else A   # stored [k,m], viewed through t()
+    sb = B.T.copy() if tb else B   # stored [n,k], viewed through t()
+    dA, dB = cb.to_device(sa), cb.to_device(sb)
+    assert cb.ops.matmul_path(dA, dB, ta, tb, mode) == 0, "expected the tcgen05 path"
+    C = cb.ops.matmul(dA, dB, ta, tb, mode).numpy()
+    _check_status(cb)
+    assert_matmul_close(C, orc.matmul(sa, sb, ta, tb), TOL[mode], f"{mode} ta={ta} tb={tb} {m}x{k}x{n}")
+
+
+@pytest.mark.parametrize("mode", ["tf32", "3xtf32"])
+@pytest.mark.parametrize("m,k,n", [(64, 784, 128), (100, 40, 72), (129, 36, 260), (1, 8, 16), (300, 1000, 20), (130, 784, 4096)])
+def test_tensor_core_ragged_extents(cb, orc, mode, m, k, n):
+    """M, N, K that are not multiples of the tile: TMA zero fill on load, masked store."""
+    A, B, _ = _mats(m, k, n, 2)
+    dA, dB = cb.to_device(A), cb.to_device(B)
+    assert cb.ops.matmul_path(dA, dB, False, False, mode) == 0
+    C = cb.ops.matmul(dA, dB, mode=mode).numpy()
+    _check_status(cb)
+    assert_matmul_close(C, orc.matmul(A, B), TOL[mode], f"{mode} {m}x{k}x{n}")
+
+
+@pytest.mark.parametrize("mode", ["tf32", "3xtf32"])
+def test_forward_and_both_backward_products(cb, orc, mode):
+    """C = A.B, dA = dC.B^T, dB = A^T.dC with the transposes as stride-swapped views (no copies)."""
+    m, k, n = 320, 200, 264
+    A, B, dC = _mats(m, k, n, 3)
+    dA_, dB_, dC_ = cb.to_device(A), cb.to_device(B), cb.to_device(dC)
+    assert_matmul_close(cb.ops.matmul(dA_, dB_, mode=mode).numpy(), orc.matmul(A, B), TOL[mode], "C")
+    assert_matmul_close(cb.ops.matmul(dC_, dB_, tb=True, mode=mode).numpy(), orc.matmul(dC, B, tb=True), TOL[mode], "dA")
+    assert_matmul_close(cb.ops.matmul(dA_, dC_, ta=True, mode=mode).numpy(), orc.matmul(A, dC, ta=True), TOL[mode], "dB")
+    _check_status(cb)
+
+
+def test_persistent_scheduler_many_tiles(cb, orc):
+    """More tiles than SMs so each CTA loops over several tiles and both TMEM accumulators are used."""
+    m, k, n = 2560, 64, 2304   # 20 x 9 = 180 tiles of 128 x 256
+    A, B, _ = _mats(m, k, n, 4)
+    rows = np.asarray([0, 1, 127, 128, 1279, 2559])
+    for mode in ("tf32", "3xtf32"):
+        C = cb.ops.matmul(cb.to_device(A), cb.to_device(B), mode=mode).numpy()
+        _check_status(cb)
+        assert_matmul_close(C[rows], orc.matmul_rows(A, B, rows), TOL[mode], mode + " sampled rows")
+        # every tile against an fp64 product (catches a mis-addressed tile anywhere)
+        ref64 = A.astype(np.float64) @ B.astype(np.float64)
+        assert_matmul_close(C, ref64, TOL[mode] * 1.5, mode + " all tiles vs fp64")
+
+
+def test_three_tf32_terms_reach_fp32_accuracy(cb, orc):
+    """K = 4096, N(0,1): 3xTF32 must sit with the fp32 recurrence, TF32 visibly must not need to."""
+    m, k, n = 128, 4096, 256
+    A, B, _ = _mats(m, k, n, 5)
+    ref64 = A.astype(np.float64) @ B.astype(np.float64)
+    e3 = assert_matmul_close(cb.ops.matmul(cb.to_device(A), cb.to_device(B), mode="3xtf32").numpy(), ref64, 1e-4, "3xtf32 vs fp64")
+    e1 = assert_matmul_close(cb.ops.matmul(cb.to_device(A), cb.to_device(B), mode="tf32").numpy(), ref64, 5e-3, "tf32 vs fp64")
+    eref = np.abs(orc.matmul(A, B) - ref64).max() / np.abs(ref64).max()
+    assert e3 < 20 * max(eref, 1e-7), (e3, eref)
+    assert e1 > e3
+    _check_status(cb)
+
+
+@pytest.mark.parametrize("m,k,n,ta,tb", [(64, 128, 10, False, False), (64, 10, 128, False, True), (128, 64, 10, True, False),
+                                          (5, 7, 3, False, False), (70, 33, 65, True, True), (1, 1, 1, False, False)])
+def test_cuda_core_path_for_operands_tma_cannot_address(cb, orc, m, k, n, ta, tb):
+    """The 10-class layer: row pitches of 40 bytes.  fp32 FMA, so rel 1e-5."""
+    A, B, _ = _mats(m, k, n, 6)
+    sa = A.T.copy() if ta else A
+    sb = B.T.copy() if tb else B
+    dA, dB = cb.to_device(sa), cb.to_device(sb)
+    assert cb.ops.matmul_path(dA, dB, ta, tb, "3xtf32") == 1
+    assert_matmul_close(cb.ops.matmul(dA, dB, ta, tb).numpy(), orc.matmul(sa, sb, ta, tb), 1e-5, "SIMT")
+    assert_matmul_close(cb.ops.matmul(dA, dB, ta, tb, "fp32_simt").numpy(), orc.matmul(sa, sb, ta, tb), 1e-5, "SIMT forced")
+
+
+def test_degenerate_extents(cb):
+    A = cb.to_device(np.ones((4, 0), np.float32).reshape(4, 0))
+    B = cb.to_device(np.ones((0, 8), np.float32).reshape(0, 8))
+    C = cb.ops.matmul(cb.empty((4, 0)), cb.empty((0, 8)))
+    assert (C.numpy() == 0).all()
+    assert cb.ops.matmul(cb.empty((0, 5)), cb.empty((5, 3))).numpy().shape == (0, 3)
+
+
+def test_against_golden_fixture(cb, golden):
+    G = golden
+    for tag in ("mm33x47x29", "mm64x100x16"):
+        A, B, dC = cb.to_device(G[tag + ".A"]), cb.to_device(G[tag + ".B"]), cb.to_device(G[tag + ".dC"])
+        assert_matmul_close(cb.ops.matmul(A, B).numpy(), G[tag + ".C"], 1e-4, tag + " C")
+        assert_matmul_close(cb.ops.matmul(dC, B, tb=True).numpy(), G[tag + ".dA"], 1e-4, tag + " dA")
+        assert_matmul_close(cb.ops.matmul(A, dC, ta=True).numpy(), G[tag + ".dB"], 1e-4, tag + " dB")
+    _check_status(cb)
