@@ -8,6 +8,7 @@ fallback: loading fails loudly if the library has not been built.
 from ._lib import lib, load, LIB_PATH, CtkError, check  # noqa: F401
 from .device import DeviceArray, Stream, Event, to_device, empty, zeros, synchronize, launch_count  # noqa: F401
 from . import ops  # noqa: F401
+from . import frontend  # noqa: F401
 
 __all__ = ["lib", "load", "LIB_PATH", "CtkError", "check", "DeviceArray", "Stream", "Event", "to_device", "empty",
-           "zeros", "synchronize", "launch_count", "ops"]
+           "zeros", "synchronize", "launch_count", "ops", "frontend"]

@@ -5,7 +5,8 @@ import re
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "lib", "libctorch_b200.so")
-HEADER = os.path.join(os.path.dirname(HERE), "include", "ctorch_b200.h")
+INCLUDE = os.path.join(os.path.dirname(HERE), "include")
+HEADERS = [os.path.join(INCLUDE, "ctorch_b200.h"), os.path.join(INCLUDE, "ctorch_b200_frontend.h")]
 
 _lib = None
 
@@ -16,11 +17,14 @@ class CtkError(RuntimeError):
         self.code = code
 
 
-def declared_symbols(header=HEADER):
-    """Names of every function the public header declares."""
-    text = open(header).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(ctk_[a-z0-9_]+)\s*\(", text)))
+def declared_symbols(headers=None):
+    """Names of every function the public headers declare."""
+    names = set()
+    for header in headers or HEADERS:
+        text = open(header).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names.update(re.findall(r"\b(ct[kh]_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
 
 
 def load():
@@ -38,6 +42,8 @@ def load():
     L.ctk_reduce_scratch_bytes.restype = ctypes.c_size_t
     L.ctk_matmul_workspace_bytes.restype = ctypes.c_size_t
     L.ctk_matmul_workspace_bytes.argtypes = [ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int]
+    L.cth_last_error.restype = ctypes.c_char_p
+    L.cth_error_count.restype = ctypes.c_uint64
     _lib = L
     return L
 

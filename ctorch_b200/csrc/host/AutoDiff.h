@@ -62,7 +62,7 @@ class AutoDiff {
 
     Node* get_node_by_id(size_t id);
     void dfs_topological_sort(Node* node, std::unordered_set<Node*>& visited, std::vector<Node*>& result);
-    Tensor check_and_adjust_grad_shape(const Tensor& grad, const std::vector<size_t>& target_shape);
+    Tensor check_and_adjust_grad_shape(const Tensor& grad, const std::vector<size_t>& target_shape, DeviceType target_device);
     Tensor rule(Node* node, size_t input_id, Node& input_node, bool& skip);
 
 public:

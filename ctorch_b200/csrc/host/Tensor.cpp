@@ -1,0 +1,561 @@
+// Tensor implementation: the op wrappers have the reference's shape (src/Tensor.cpp:482-497 and the
+// 15 sibling call sites): check dtype/device, dispatch through Ctorch_Scheduler, defer_record on
+// the tape, commit when the result requires grad.  The operations the reference computes with
+// host loops outside the scheduler (scalar forms :751-973, sum :638-666, softmax :1645-1803,
+// zero/ones :390-455, broadcast_to :289-387, item :154-165) launch device kernels here.
+#include "Tensor.h"
+
+#include <algorithm>
+#include <cmath>
+#include <limits>
+#include <mutex>
+
+#include "Ctorch_Scheduler.h"
+#include "ctorch_b200.h"
+
+namespace ctorch {
+
+std::atomic<size_t> Tensor::global_tensor_id(1);
+
+void cuda_check(int status, const char* what) {
+    if (status != 0) {
+        Ctorch_Error::throwException(ErrorPlatform::kCUDA, status == CTK_ERR_INVALID ? ErrorType::DIMENSION : ErrorType::KERNEL_LAUNCH,
+                                     std::string(what) + ": " + ctk_last_error());
+    }
+}
+
+static thread_local void* t_stream = nullptr;
+void* current_stream() { return t_stream; }
+void set_current_stream(void* s) { t_stream = s; }
+
+// ---- pinned staging for host <-> device copies --------------------------------------------------
+// Two page-locked buffers per thread: while one is in flight on the copy engine the host fills (or
+// drains) the other.
+namespace {
+struct Staging {
+    static constexpr size_t kChunk = 8u << 20;
+    void* buf[2] = {nullptr, nullptr};
+    void* ev[2] = {nullptr, nullptr};
+    bool ready = false;
+    void ensure() {
+        if (ready) return;
+        for (int i = 0; i < 2; ++i) {
+            cuda_check(ctk_malloc_host(&buf[i], kChunk), "pinned staging allocation");
+            cuda_check(ctk_event_create(&ev[i]), "staging event");
+        }
+        ready = true;
+    }
+    ~Staging() {
+        for (int i = 0; i < 2; ++i) {
+            if (buf[i]) ctk_free_host(buf[i]);
+            if (ev[i]) ctk_event_destroy(ev[i]);
+        }
+    }
+};
+thread_local Staging t_staging;
+}  // namespace
+
+void Storage::copy_from_host(const void* src, size_t bytes) {
+    if (bytes == 0) return;
+    if (bytes > nbytes()) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::MEMORY, "Storage::copy_from_host: too many bytes");
+    if (_device != DeviceType::kCUDA) {
+        std::memcpy(_data->ptr, src, bytes);
+        return;
+    }
+    Staging& S = t_staging;
+    S.ensure();
+    const char* s = static_cast<const char*>(src);
+    char* d = static_cast<char*>(_data->ptr);
+    bool used[2] = {false, false};
+    int slot = 0;
+    for (size_t off = 0; off < bytes; off += Staging::kChunk, slot ^= 1) {
+        const size_t n = std::min(Staging::kChunk, bytes - off);
+        if (used[slot]) cuda_check(ctk_event_sync(S.ev[slot]), "staging wait");
+        std::memcpy(S.buf[slot], s + off, n);
+        cuda_check(ctk_memcpy_h2d(d + off, S.buf[slot], n, t_stream), "host-to-device copy");
+        cuda_check(ctk_event_record(S.ev[slot], t_stream), "staging record");
+        used[slot] = true;
+    }
+    for (int i = 0; i < 2; ++i)
+        if (used[i]) cuda_check(ctk_event_sync(S.ev[i]), "staging wait");  // the staging buffers are reused by the next call
+}
+
+void Storage::copy_to_host(void* dst, size_t bytes) const {
+    if (bytes == 0) return;
+    if (bytes > nbytes()) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::MEMORY, "Storage::copy_to_host: too many bytes");
+    if (_device != DeviceType::kCUDA) {
+        std::memcpy(dst, _data->ptr, bytes);
+        return;
+    }
+    Staging& S = t_staging;
+    S.ensure();
+    char* out = static_cast<char*>(dst);
+    const char* s = static_cast<const char*>(_data->ptr);
+    size_t pending_off[2] = {0, 0}, pending_n[2] = {0, 0};
+    int slot = 0;
+    for (size_t off = 0; off < bytes; off += Staging::kChunk, slot ^= 1) {
+        const size_t n = std::min(Staging::kChunk, bytes - off);
+        if (pending_n[slot]) {
+            cuda_check(ctk_event_sync(S.ev[slot]), "staging wait");
+            std::memcpy(out + pending_off[slot], S.buf[slot], pending_n[slot]);
+        }
+        cuda_check(ctk_memcpy_d2h(S.buf[slot], s + off, n, t_stream), "device-to-host copy");
+        cuda_check(ctk_event_record(S.ev[slot], t_stream), "staging record");
+        pending_off[slot] = off;
+        pending_n[slot] = n;
+    }
+    for (int i = 0; i < 2; ++i) {
+        const int sl = slot ^ i;  // older one first
+        if (pending_n[sl]) {
+            cuda_check(ctk_event_sync(S.ev[sl]), "staging wait");
+            std::memcpy(out + pending_off[sl], S.buf[sl], pending_n[sl]);
+        }
+    }
+}
+
+// ---- construction ---------------------------------------------------------------------------------
+Tensor::Tensor() : tensor_id_(global_tensor_id++) { computeStrides(); }
+
+Tensor::Tensor(float value) : tensor_id_(global_tensor_id++) {
+    _shape = {};
+    computeStrides();
+    _storage = Storage(&value, 1, _dtype, _device);
+}
+
+Tensor::Tensor(std::initializer_list<float> values) : tensor_id_(global_tensor_id++) {
+    _shape = {values.size()};
+    computeStrides();
+    _storage = Storage(values.begin(), values.size(), _dtype, _device);
+}
+
+Tensor::Tensor(ShapeTag, const std::vector<size_t>& shape, DType dtype, DeviceType device, bool zero_init)
+    : tensor_id_(global_tensor_id++), _device(device), _dtype(dtype) {
+    _shape = shape;
+    computeStrides();
+    _storage = Storage(numel(), _dtype, _device);
+    if (zero_init) zero();
+}
+
+Tensor::Tensor(size_t size, DType dtype, DeviceType device, bool zero_init) : tensor_id_(global_tensor_id++), _device(device), _dtype(dtype) {
+    _shape = {size};
+    computeStrides();
+    _storage = Storage(size, _dtype, _device);
+    if (zero_init) zero();
+}
+
+// Copy: a new id and the same value (the reference clones the storage here, include/Tensor.h:320-338;
+// sharing until the first write is indistinguishable).
+Tensor::Tensor(const Tensor& o)
+    : tensor_id_(global_tensor_id++), record_committed_(false), _requires_grad(o._requires_grad), _strides(o._strides),
+      _storage_offset(o._storage_offset), _device(o._device), _dtype(o._dtype), _storage(o._storage), _shape(o._shape) {}
+
+Tensor& Tensor::operator=(const Tensor& o) {
+    if (this != &o) {
+        commit_pending_record();
+        tensor_id_ = global_tensor_id++;
+        _shape = o._shape;
+        _strides = o._strides;
+        _storage_offset = o._storage_offset;
+        _device = o._device;
+        _dtype = o._dtype;
+        _storage = o._storage;
+        _requires_grad = o._requires_grad;
+        record_committed_ = false;
+    }
+    return *this;
+}
+
+// Move keeps the id -- this is what lets `Tensor h = (x.matmul(W) + b).relu();` stay on the tape.
+Tensor::Tensor(Tensor&& o) noexcept
+    : tensor_id_(o.tensor_id_), record_committed_(o.record_committed_), _requires_grad(o._requires_grad), _strides(std::move(o._strides)),
+      _storage_offset(o._storage_offset), _device(o._device), _dtype(o._dtype), _storage(std::move(o._storage)), _shape(std::move(o._shape)) {
+    o.tensor_id_ = 0;
+    o.record_committed_ = false;
+}
+
+Tensor& Tensor::operator=(Tensor&& o) noexcept {
+    if (this != &o) {
+        tensor_id_ = o.tensor_id_;
+        _shape = std::move(o._shape);
+        _strides = std::move(o._strides);
+        _storage_offset = o._storage_offset;
+        _device = o._device;
+        _dtype = o._dtype;
+        _storage = std::move(o._storage);
+        _requires_grad = o._requires_grad;
+        record_committed_ = o.record_committed_;
+        o.tensor_id_ = 0;
+        o.record_committed_ = false;
+    }
+    return *this;
+}
+
+// ---- accessors ------------------------------------------------------------------------------------
+void Tensor::requires_grad(bool key) {
+    _requires_grad = key;
+    if (key && AutoDiffContext::current()) {
+        AutoDiffContext::current()->make_leaf(*this, key);
+        AutoDiffContext::current()->update_requires_grad(*this, key);
+    }
+}
+
+size_t Tensor::numel() const {
+    size_t n = 1;
+    for (size_t s : _shape) n *= s;
+    return n;
+}
+
+size_t Tensor::size(int d) const {
+    if (d < 0) d += static_cast<int>(_shape.size());
+    if (d < 0 || d >= static_cast<int>(_shape.size())) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DIMENSION, "invalid dimension");
+    return _shape[d];
+}
+
+size_t Tensor::stride(int d) const {
+    if (d < 0) d += static_cast<int>(_strides.size());
+    if (d < 0 || d >= static_cast<int>(_strides.size())) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DIMENSION, "invalid dimension");
+    return _strides[d];
+}
+
+void Tensor::computeStrides() {
+    _strides.resize(_shape.size());
+    if (_shape.empty()) return;
+    _strides.back() = 1;
+    for (int i = static_cast<int>(_shape.size()) - 2; i >= 0; --i) _strides[i] = _strides[i + 1] * _shape[i + 1];
+}
+
+bool Tensor::is_contiguous() const {
+    size_t expect = 1;
+    for (int i = static_cast<int>(_shape.size()) - 1; i >= 0; --i) {
+        if (_shape[i] != 1 && _strides[i] != expect) return false;
+        expect *= _shape[i];
+    }
+    return true;
+}
+
+template <typename T>
+void Tensor::checkDType() const {
+    bool ok = (std::is_same<T, float>::value && _dtype == DType::kFloat) || (std::is_same<T, double>::value && _dtype == DType::kDouble) ||
+              (std::is_same<T, int32_t>::value && _dtype == DType::kInt) || (std::is_same<T, int64_t>::value && _dtype == DType::kLong) ||
+              (std::is_same<T, bool>::value && _dtype == DType::kBool);
+    if (!ok) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DATATYPE, std::string("dtype mismatch, tensor is ") + dtypeToString(_dtype));
+}
+
+template <typename T>
+T* Tensor::data() {
+    checkDType<T>();
+    _storage.make_unique();
+    T* p = _storage.data<T>();
+    return p ? p + _storage_offset : nullptr;
+}
+template <typename T>
+const T* Tensor::data() const {
+    checkDType<T>();
+    const T* p = _storage.data<T>();
+    return p ? p + _storage_offset : nullptr;
+}
+template float* Tensor::data<float>();
+template const float* Tensor::data<float>() const;
+template int32_t* Tensor::data<int32_t>();
+template const int32_t* Tensor::data<int32_t>() const;
+
+template <typename T>
+T Tensor::item() const {
+    if (numel() != 1) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::TENSOR_STATE, "item(): tensor is not a scalar");
+    const T* p = data<T>();
+    if (!p) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::TENSOR_STATE, "item(): tensor has no data");
+    if (_device != DeviceType::kCUDA) return *p;
+    T v;
+    cuda_check(ctk_memcpy_d2h(&v, p, sizeof(T), t_stream), "item()");
+    cuda_check(t_stream ? ctk_stream_sync(t_stream) : ctk_device_sync(), "item() sync");
+    return v;
+}
+template float Tensor::item<float>() const;
+template int32_t Tensor::item<int32_t>() const;
+
+void Tensor::commit_pending_record() {
+    if (AutoDiffContext::current() && has_pending_record()) AutoDiffContext::current()->commit_record(*this);
+    record_committed_ = true;
+}
+
+// ---- host <-> device ----------------------------------------------------------------------------------
+void Tensor::copy_from_host(const float* src, size_t count) {
+    if (count != numel() || !is_contiguous()) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DIMENSION, "copy_from_host: size mismatch or non-contiguous tensor");
+    if (count == 0) return;
+    _storage.make_unique();
+    if (_storage_offset == 0) {
+        _storage.copy_from_host(src, count * sizeof(float));
+    } else if (_device == DeviceType::kCUDA) {
+        cuda_check(ctk_memcpy_h2d(data<float>(), src, count * sizeof(float), t_stream), "copy_from_host");
+        cuda_check(t_stream ? ctk_stream_sync(t_stream) : ctk_device_sync(), "copy_from_host sync");
+    } else {
+        std::memcpy(data<float>(), src, count * sizeof(float));
+    }
+}
+
+void Tensor::copy_to_host(float* dst, size_t count) const {
+    if (count != numel()) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DIMENSION, "copy_to_host: size mismatch");
+    if (count == 0) return;
+    if (!is_contiguous()) {
+        contiguous().copy_to_host(dst, count);
+        return;
+    }
+    if (_storage_offset == 0) {
+        _storage.copy_to_host(dst, count * sizeof(float));
+    } else if (_device == DeviceType::kCUDA) {
+        cuda_check(ctk_memcpy_d2h(dst, data<float>(), count * sizeof(float), t_stream), "copy_to_host");
+        cuda_check(t_stream ? ctk_stream_sync(t_stream) : ctk_device_sync(), "copy_to_host sync");
+    } else {
+        std::memcpy(dst, data<float>(), count * sizeof(float));
+    }
+}
+
+std::vector<float> Tensor::to_vector() const {
+    std::vector<float> v(numel());
+    copy_to_host(v.data(), v.size());
+    return v;
+}
+
+Tensor Tensor::to(DeviceType device) const {
+    Tensor r(*this);
+    if (device == _device) return r;
+    if (!is_contiguous() || _storage_offset != 0) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::TENSOR_STATE, "to(device): contiguous tensor expected");
+    r._storage = _storage.to(device);
+    r._device = device;
+    return r;
+}
+
+// ---- shape ops --------------------------------------------------------------------------------------------
+Tensor Tensor::clone() const {
+    Tensor r(*this);
+    r._storage = _storage.clone();
+    return r;
+}
+
+// src/Tensor.cpp:246-261: a copy with two dims and two strides swapped (no data movement here).
+Tensor Tensor::transpose(int d0, int d1) const {
+    const int rank = static_cast<int>(_shape.size());
+    if (d0 < 0 || d0 >= rank || d1 < 0 || d1 >= rank) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DIMENSION, "transpose: dimension out of range");
+    Tensor r(*this);
+    std::swap(r._shape[d0], r._shape[d1]);
+    std::swap(r._strides[d0], r._strides[d1]);
+    return r;
+}
+Tensor Tensor::t() const { return transpose(0, 1); }
+
+Tensor Tensor::reshape(const std::vector<size_t>& new_shape) const {
+    size_t n = 1;
+    for (size_t s : new_shape) n *= s;
+    if (n != numel()) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DIMENSION, "reshape: element count differs");
+    Tensor r(*this);
+    r._shape = new_shape;
+    r.computeStrides();
+    return r;
+}
+
+// Materialises a 2-D strided view (what t() makes) into row-major order with one GEMM-free pass:
+// out = view * 1 is not needed -- a transposed copy is a MatMul-shaped read, done by the SIMT
+// matmul against nothing; here it is only used for host read-back of small views.
+Tensor Tensor::contiguous() const {
+    if (is_contiguous()) return *this;
+    if (_shape.size() != 2) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DIMENSION, "contiguous(): only 2-D views are supported");
+    // Read back the underlying buffer and permute on the host (views are small: tests and debugging).
+    Tensor base(*this);
+    base._shape = {_storage.size()};
+    base._strides = {1};
+    base._storage_offset = 0;
+    std::vector<float> raw = base.to_vector();
+    std::vector<float> out(numel());
+    for (size_t i = 0; i < _shape[0]; ++i)
+        for (size_t j = 0; j < _shape[1]; ++j) out[i * _shape[1] + j] = raw[_storage_offset + i * _strides[0] + j * _strides[1]];
+    Tensor r(ShapeTag{}, _shape, _dtype, _device, false);
+    r.copy_from_host(out.data(), out.size());
+    r._requires_grad = _requires_grad;
+    return r;
+}
+
+// src/Tensor.cpp:289-387.  NumPy-style broadcast by materialising; on the device the cases the
+// training path produces (one element -> any shape, trailing dims equal -> tiled rows) are one
+// fill / tile launch.
+Tensor Tensor::broadcast_to(const std::vector<size_t>& shape) const {
+    if (shape.empty()) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DIMENSION, "broadcast_to: empty target shape");
+    std::vector<size_t> cur = _shape, tgt = shape;
+    while (cur.size() < tgt.size()) cur.insert(cur.begin(), 1);
+    while (tgt.size() < cur.size()) tgt.insert(tgt.begin(), 1);
+    for (size_t i = 0; i < cur.size(); ++i)
+        if (cur[i] != tgt[i] && cur[i] != 1) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DIMENSION, "broadcast_to: incompatible shapes");
+    Tensor result(ShapeTag{}, shape, _dtype, _device, false);
+    const size_t n = result.numel(), src_n = numel();
+    if (n == 0) return result;
+    // trailing-dims broadcast: every broadcast dim is a leading one
+    bool trailing = true;
+    {
+        bool seen_real = false;
+        for (size_t i = 0; i < cur.size(); ++i) {
+            if (cur[i] == tgt[i] && cur[i] != 1) seen_real = true;
+            else if (cur[i] == 1 && tgt[i] != 1 && seen_real) trailing = false;
+        }
+    }
+    if (_device == DeviceType::kCUDA) {
+        if (src_n == 1) cuda_check(ctk_fill_f32(result.data<float>(), 0.0f, data<float>(), static_cast<int64_t>(n), t_stream), "broadcast_to");
+        else if (trailing) cuda_check(ctk_tile_f32(data<float>(), static_cast<int64_t>(src_n), result.data<float>(), static_cast<int64_t>(n), t_stream), "broadcast_to");
+        else Ctorch_Error::throwException(ErrorPlatform::kCUDA, ErrorType::DIMENSION, "broadcast_to: only scalar and trailing-dims broadcasts are implemented on the device");
+    } else {
+        const float* s = data<float>();
+        float* d = result.data<float>();
+        if (src_n == 1) std::fill(d, d + n, s[0]);
+        else if (trailing) for (size_t i = 0; i < n; ++i) d[i] = s[i % src_n];
+        else Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DIMENSION, "broadcast_to: only scalar and trailing-dims broadcasts are implemented");
+    }
+    return result;
+}
+
+void Tensor::fill(float v) {
+    const size_t n = numel();
+    if (n == 0) return;
+    if (_dtype != DType::kFloat) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DATATYPE, "fill: float tensors only");
+    if (_device == DeviceType::kCUDA) cuda_check(ctk_fill_f32(data<float>(), v, nullptr, static_cast<int64_t>(n), t_stream), "fill");
+    else std::fill(data<float>(), data<float>() + n, v);
+}
+void Tensor::zero() {
+    if (numel() == 0) return;
+    if (_dtype == DType::kFloat) { fill(0.0f); return; }
+    _storage.make_unique();
+    if (_device == DeviceType::kCUDA) cuda_check(ctk_memset(_storage.raw(), 0, _storage.nbytes(), t_stream), "zero");
+    else std::memset(_storage.raw(), 0, _storage.nbytes());
+}
+void Tensor::ones() { fill(1.0f); }
+
+// ---- op wrappers ------------------------------------------------------------------------------------------
+void Tensor::record(Tensor& result, op o, std::vector<Tensor*> inputs, bool rg, int op_param) const {
+    if (AutoDiffContext::current()) {
+        AutoDiffContext::current()->defer_record(result.id(), o, inputs, op_param);
+        result._requires_grad = rg;
+        if (result._requires_grad) result.commit_pending_record();
+    } else {
+        result._requires_grad = rg;
+    }
+}
+
+Tensor Tensor::binary_dispatch(const Tensor& other, op o) const {
+    if (_dtype != other.dtype()) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DATATYPE, "tensor dtypes differ");
+    const bool scalar_mix = (dim() == 0 && _device == DeviceType::kCPU) || (other.dim() == 0 && other.device() == DeviceType::kCPU);
+    if (_device != other.device() && !scalar_mix) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DEVICE_COMPAT, "tensors are on different devices");
+    Tensor result = Ctorch_Scheduler::getInstance().dispatch(*this, other, o);
+    record(result, o, {const_cast<Tensor*>(this), const_cast<Tensor*>(&other)}, _requires_grad || other.requires_grad());
+    return result;
+}
+
+Tensor Tensor::unary_dispatch(op o, int op_param) const {
+    Tensor result = Ctorch_Scheduler::getInstance().dispatch(*this, o);
+    record(result, o, {const_cast<Tensor*>(this)}, _requires_grad, op_param);
+    return result;
+}
+
+Tensor Tensor::matmul(const Tensor& other) const {
+    Tensor result = Ctorch_Scheduler::getInstance().dispatch(*this, other, op::MatMul);
+    record(result, op::MatMul, {const_cast<Tensor*>(this), const_cast<Tensor*>(&other)}, _requires_grad || other.requires_grad());
+    return result;
+}
+Tensor Tensor::dot(const Tensor& other) const {
+    Tensor result = Ctorch_Scheduler::getInstance().dispatch(*this, other, op::Dot);
+    record(result, op::Dot, {const_cast<Tensor*>(this)}, _requires_grad);
+    return result;
+}
+Tensor Tensor::operator+(const Tensor& o) const { return binary_dispatch(o, op::Add); }
+Tensor Tensor::operator-(const Tensor& o) const { return binary_dispatch(o, op::Sub); }
+Tensor Tensor::operator*(const Tensor& o) const { return binary_dispatch(o, op::Mul); }
+Tensor Tensor::operator/(const Tensor& o) const { return binary_dispatch(o, op::Div); }
+Tensor Tensor::operator-() const { return unary_dispatch(op::Neg); }
+Tensor Tensor::relu() const { return unary_dispatch(op::ReLU); }
+Tensor Tensor::sigmoid() const { return unary_dispatch(op::Sigmoid); }
+Tensor Tensor::tanh() const { return unary_dispatch(op::Tanh); }
+Tensor Tensor::sin() const { return unary_dispatch(op::Sin); }
+Tensor Tensor::cos() const { return unary_dispatch(op::Cos); }
+
+static Tensor loss_dispatch(const Tensor& a, const Tensor& target, op o) { return Ctorch_Scheduler::getInstance().dispatch(a, target, o); }
+Tensor Tensor::mse_loss(const Tensor& target) const {
+    Tensor r = loss_dispatch(*this, target, op::MSE);
+    record(r, op::MSE, {const_cast<Tensor*>(this), const_cast<Tensor*>(&target)}, _requires_grad || target.requires_grad());
+    return r;
+}
+Tensor Tensor::mae_loss(const Tensor& target) const {
+    Tensor r = loss_dispatch(*this, target, op::MAE);
+    record(r, op::MAE, {const_cast<Tensor*>(this), const_cast<Tensor*>(&target)}, _requires_grad || target.requires_grad());
+    return r;
+}
+Tensor Tensor::cross_entropy(const Tensor& target) const {
+    Tensor r = loss_dispatch(*this, target, op::CE);
+    record(r, op::CE, {const_cast<Tensor*>(this), const_cast<Tensor*>(&target)}, _requires_grad || target.requires_grad());
+    return r;
+}
+
+// The reference's Tensor::softmax is inline and throws off the CPU (src/Tensor.cpp:1645-1664); here
+// the last-dim case goes to the registered Softmax kernel, which it is bit-identical to.
+Tensor Tensor::softmax(int dim) const {
+    if (_shape.empty()) Ctorch_Error::throwException(ErrorPlatform::kCPU, ErrorType::DIMENSION, "softmax: scalars are not supported");
+    const int rank = static_cast<int>(_shape.size());
+    if (dim < 0) dim += rank;
+    if (dim < 0 || dim >= rank) Ctorch_Error::throwException(ErrorPlatform::kCPU, ErrorType::DIMENSION, "softmax: dim out of range");
+    if (rank > 2) Ctorch_Error::throwException(ErrorPlatform::kCPU, ErrorType::DIMENSION, "softmax: only 1-D and 2-D tensors");
+    if (dim != rank - 1) Ctorch_Error::throwException(DeviceTypeToErrorPlatform(_device), ErrorType::DIMENSION, "softmax: only the last dim is implemented on the device");
+    return unary_dispatch(op::Softmax, dim);
+}
+
+// src/Tensor.cpp:638-666 (not dispatched in the reference either).
+Tensor Tensor::sum() const {
+    if (_device != DeviceType::kCUDA) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DEVICE_COMPAT, "sum: no kernel for this device");
+    Tensor result(ShapeTag{}, {}, _dtype, _device, false);
+    cuda_check(ctk_sum_f32(data<float>(), static_cast<int64_t>(numel()), result.data<float>(), nullptr, t_stream), "sum");
+    record(result, op::Sum, {const_cast<Tensor*>(this)}, _requires_grad);
+    return result;
+}
+
+// src/Tensor.cpp:751-806 (t*s), 855-910 (t+s), 913-973 (t/s): recorded as Mul/Add/Div with a host
+// scalar tensor as second input.
+Tensor Tensor::scalar_form(int kind, float s, op recorded) const {
+    if (_device != DeviceType::kCUDA) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DEVICE_COMPAT, "scalar op: no kernel for this device");
+    if (!is_contiguous()) Ctorch_Error::throwException(ErrorPlatform::kCUDA, ErrorType::TENSOR_STATE, "scalar op: contiguous tensor expected");
+    Tensor result(ShapeTag{}, _shape, _dtype, _device, false);
+    cuda_check(ctk_scalar_f32(kind, data<float>(), s, result.data<float>(), static_cast<int64_t>(numel()), t_stream), "scalar op");
+    Tensor scalar_tensor(s);
+    record(result, recorded, {const_cast<Tensor*>(this), &scalar_tensor}, _requires_grad);
+    return result;
+}
+Tensor Tensor::operator*(float s) const { return scalar_form(0, s, op::Mul); }
+Tensor Tensor::operator+(float s) const { return scalar_form(1, s, op::Add); }
+Tensor Tensor::operator/(float s) const {
+    if (std::abs(s) < std::numeric_limits<float>::epsilon())
+        Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::TENSOR_STATE, "division by zero in tensor / scalar");
+    return scalar_form(2, s, op::Div);
+}
+
+void Tensor::backward() const {
+    if (AutoDiffContext::current()) AutoDiffContext::current()->backward(const_cast<Tensor&>(*this));
+}
+
+void Tensor::sgd_update_(const Tensor& g, float lr) {
+    if (g.numel() != numel()) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DIMENSION, "sgd_update_: gradient has a different size");
+    if (_device != DeviceType::kCUDA || g.device() != DeviceType::kCUDA)
+        Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DEVICE_COMPAT, "sgd_update_: device tensors expected");
+    cuda_check(ctk_sgd_update_f32(data<float>(), g.data<float>(), lr, static_cast<int64_t>(numel()), t_stream), "sgd_update_");
+}
+
+// ---- free functions (src/Tensor.cpp:1373-1453) ---------------------------------------------------------------
+void backward(Tensor& root) {
+    if (AutoDiffContext::current()) AutoDiffContext::current()->backward(root);
+}
+void backward(Tensor& root, Tensor grad_output) {
+    if (AutoDiffContext::current()) AutoDiffContext::current()->backward(root, grad_output);
+}
+Tensor grad(const Tensor& t) {
+    if (AutoDiffContext::current()) return AutoDiffContext::current()->get_grad(&t);
+    return Tensor();
+}
+Tensor matMul(const Tensor& a, const Tensor& b) { return Ctorch_Scheduler::getInstance().dispatch(a, b, op::MatMul); }
+Tensor operator+(float s, const Tensor& t) { return t + s; }
+Tensor operator*(float s, const Tensor& t) { return t * s; }
+Tensor operator-(float s, const Tensor& t) { return Tensor(s) - t; }
+Tensor operator/(float s, const Tensor& t) { return Tensor(s) / t; }
+
+}  // namespace ctorch

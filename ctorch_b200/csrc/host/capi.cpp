@@ -1,0 +1,395 @@
+// C ABI over the C++ front end (Tensor / AutoDiff / Ctorch_Scheduler on DeviceType::kCUDA), so that
+// a host written in another language -- here the Python tests and the benchmark -- can drive exactly
+// the path user C++ code takes: op wrappers -> scheduler dispatch -> `*_CUDA_kernel` -> kernels,
+// with the tape recording and back-propagating on the device.
+//
+// Also holds MlpTrainer: the training step of the reference's mnist/mnist.cpp:44-92 written against
+// this front end for any layer list, with an optional NCCL gradient all-reduce that overlaps
+// backward (data-parallel replicas; the reference is single-process).
+#include <cstring>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "AutoDiff.h"
+#include "Ctorch_Error.h"
+#include "Ctorch_Scheduler.h"
+#include "Tensor.h"
+#include "ctorch_b200.h"
+#include "ctorch_b200_frontend.h"
+
+using namespace ctorch;
+
+namespace {
+
+thread_local std::string t_err;
+
+template <typename F>
+int guarded(F&& f) {
+    try {
+        f();
+        return 0;
+    } catch (const std::exception& e) {
+        t_err = e.what();
+        return 1;
+    } catch (...) {
+        t_err = "unknown exception";
+        return 1;
+    }
+}
+
+Tensor* T(void* h) { return static_cast<Tensor*>(h); }
+
+// ---------------------------------------------------------------------------------------------------
+// MlpTrainer: x -> (matmul W + b -> relu)* -> matmul W + b -> cross_entropy(one-hot) -> backward -> SGD
+// ---------------------------------------------------------------------------------------------------
+class MlpTrainer {
+public:
+    std::vector<int64_t> dims;
+    std::vector<Tensor> W, b;
+    AutoDiff ctx;
+    float lr;
+    void* comm = nullptr;         // ctk communicator (not owned)
+    void* comm_stream = nullptr;  // non-blocking stream for the gradient all-reduce
+    void* ev_grad = nullptr;      // compute -> comm: "this gradient is final"
+    void* ev_comm = nullptr;      // comm -> compute: "all gradients are reduced"
+    void* pinned_loss = nullptr;  // page-locked slot the loss is copied into
+    void* pinned_x = nullptr;     // page-locked staging for host inputs
+    size_t pinned_x_bytes = 0;
+    Tensor last_logits;
+    bool keep_logits = false;
+    uint64_t steps_done = 0;
+
+    MlpTrainer(int n_layers, const int64_t* d, const float* params, float lr_) : dims(d, d + n_layers + 1), lr(lr_) {
+        const float* p = params;
+        for (int l = 0; l < n_layers; ++l) {
+            const size_t in = static_cast<size_t>(dims[l]), out = static_cast<size_t>(dims[l + 1]);
+            Tensor w(ShapeTag{}, {in, out}, DType::kFloat, DeviceType::kCUDA, false);
+            w.copy_from_host(p, in * out);
+            p += in * out;
+            Tensor bias(ShapeTag{}, {out}, DType::kFloat, DeviceType::kCUDA, false);
+            bias.copy_from_host(p, out);
+            p += out;
+            W.push_back(std::move(w));
+            b.push_back(std::move(bias));
+        }
+        cuda_check(ctk_malloc_host(&pinned_loss, 64), "pinned loss slot");
+    }
+
+    ~MlpTrainer() {
+        ctk_device_sync();
+        if (comm_stream) ctk_stream_destroy(comm_stream);
+        if (ev_grad) ctk_event_destroy(ev_grad);
+        if (ev_comm) ctk_event_destroy(ev_comm);
+        if (pinned_loss) ctk_free_host(pinned_loss);
+        if (pinned_x) ctk_free_host(pinned_x);
+    }
+
+    int64_t n_params() const {
+        int64_t n = 0;
+        for (size_t l = 0; l + 1 < dims.size(); ++l) n += dims[l] * dims[l + 1] + dims[l + 1];
+        return n;
+    }
+
+    void set_comm(void* c) {
+        comm = c;
+        if (c && !comm_stream) {
+            cuda_check(ctk_stream_create_ex(&comm_stream, 1), "comm stream");
+            cuda_check(ctk_event_create(&ev_grad), "event");
+            cuda_check(ctk_event_create(&ev_comm), "event");
+        }
+        if (c) {
+            ctx.on_leaf_grad = [this](size_t, Tensor& g) {
+                // The gradient of this leaf just received its (only) contribution: reduce it across
+                // replicas on the communication stream while backward carries on.
+                void* compute = current_stream();
+                cuda_check(ctk_event_record(ev_grad, compute), "record");
+                cuda_check(ctk_stream_wait_event(comm_stream, ev_grad), "wait");
+                cuda_check(ctk_allreduce_sum_f32(comm, g.data<float>(), static_cast<int64_t>(g.numel()), comm_stream), "gradient all-reduce");
+            };
+        } else {
+            ctx.on_leaf_grad = nullptr;
+        }
+    }
+
+    Tensor forward(const Tensor& x) {
+        Tensor h = x;
+        const size_t L = W.size();
+        for (size_t l = 0; l < L; ++l) {
+            if (l + 1 < L) h = (h.matmul(W[l]) + b[l]).relu();
+            else h = h.matmul(W[l]) + b[l];
+        }
+        return h;
+    }
+
+    // One training step on device-resident inputs; returns the loss read back from the device.
+    float step(const Tensor& x, const Tensor& y_one_hot) {
+        AutoDiffContext::Guard guard(&ctx);
+        void* st = current_stream();
+        for (size_t l = 0; l < W.size(); ++l) {
+            ctx.make_leaf(W[l], true);
+            ctx.make_leaf(b[l], true);
+        }
+        for (size_t l = 0; l < W.size(); ++l) {
+            W[l].requires_grad(true);
+            b[l].requires_grad(true);
+        }
+        for (size_t l = 0; l < W.size(); ++l) {
+            ctx.zero_grad(W[l]);
+            ctx.zero_grad(b[l]);
+        }
+        Tensor logits = forward(x);
+        Tensor loss = logits.cross_entropy(y_one_hot);
+        // loss.item() of the reference step, without stalling the GPU between forward and backward:
+        // the value is copied to a page-locked slot now and read once the step has been issued.
+        cuda_check(ctk_memcpy_d2h(pinned_loss, loss.data<float>(), sizeof(float), st), "loss read-back");
+        backward(loss);
+        if (comm) {
+            cuda_check(ctk_event_record(ev_comm, comm_stream), "record");
+            cuda_check(ctk_stream_wait_event(st, ev_comm), "wait");
+        }
+        for (size_t l = 0; l < W.size(); ++l) {
+            W[l].sgd_update_(grad(W[l]), lr);
+            b[l].sgd_update_(grad(b[l]), lr);
+        }
+        if (keep_logits) last_logits = logits;
+        cuda_check(st ? ctk_stream_sync(st) : ctk_device_sync(), "step sync");
+        ctx.release_step_nodes();
+        ++steps_done;
+        return *static_cast<float*>(pinned_loss);
+    }
+
+    // The same step from HOST inputs: pixels and integer labels (as floats) in caller memory.
+    float step_host(const float* x_host, const float* labels_host, int64_t batch) {
+        const size_t in = static_cast<size_t>(dims.front()), classes = static_cast<size_t>(dims.back());
+        Tensor x(ShapeTag{}, {static_cast<size_t>(batch), in}, DType::kFloat, DeviceType::kCUDA, false);
+        x.copy_from_host(x_host, static_cast<size_t>(batch) * in);
+        // one-hot on the host, as mnist/mnist.cpp:67-72
+        std::vector<float> oh(static_cast<size_t>(batch) * classes, 0.0f);
+        for (int64_t i = 0; i < batch; ++i) {
+            const int lab = static_cast<int>(labels_host[i]);
+            if (lab >= 0 && lab < static_cast<int>(classes)) oh[static_cast<size_t>(i) * classes + lab] = 1.0f;
+        }
+        Tensor y(ShapeTag{}, {static_cast<size_t>(batch), classes}, DType::kFloat, DeviceType::kCUDA, false);
+        y.copy_from_host(oh.data(), oh.size());
+        return step(x, y);
+    }
+
+    void get_params(float* out) {
+        for (size_t l = 0; l < W.size(); ++l) {
+            W[l].copy_to_host(out, W[l].numel());
+            out += W[l].numel();
+            b[l].copy_to_host(out, b[l].numel());
+            out += b[l].numel();
+        }
+    }
+    void get_grads(float* out) {
+        AutoDiffContext::Guard guard(&ctx);
+        for (size_t l = 0; l < W.size(); ++l) {
+            Tensor gw = grad(W[l]);
+            gw.copy_to_host(out, gw.numel());
+            out += gw.numel();
+            Tensor gb = grad(b[l]);
+            gb.copy_to_host(out, gb.numel());
+            out += gb.numel();
+        }
+    }
+};
+
+}  // namespace
+
+extern "C" {
+
+const char* cth_last_error(void) { return t_err.c_str(); }
+void cth_set_quiet(int q) { Ctorch_Error::setQuiet(q != 0); }
+uint64_t cth_error_count(void) { return Ctorch_Error::errorCount(); }
+int cth_cuda_available(void) { return Ctorch_Scheduler::isDeviceAvailable(DeviceType::kCUDA) ? 1 : 0; }
+
+// ---- tensors ----
+int cth_tensor_from_host(const float* data, const int64_t* shape, int rank, int device, void** out) {
+    return guarded([&] {
+        std::vector<size_t> s(shape, shape + rank);
+        auto t = std::make_unique<Tensor>(ShapeTag{}, s, DType::kFloat, static_cast<DeviceType>(device), data == nullptr);
+        if (data) t->copy_from_host(data, t->numel());
+        *out = t.release();
+    });
+}
+int cth_tensor_scalar(float v, void** out) {
+    return guarded([&] { *out = new Tensor(v); });
+}
+int cth_tensor_free(void* t) {
+    return guarded([&] { delete T(t); });
+}
+int cth_tensor_info(void* t, int64_t* shape_out8, int* rank, int* device, int* requires_grad, uint64_t* id) {
+    return guarded([&] {
+        const Tensor& x = *T(t);
+        if (rank) *rank = x.dim();
+        if (shape_out8) for (int i = 0; i < x.dim() && i < 8; ++i) shape_out8[i] = static_cast<int64_t>(x.sizes()[i]);
+        if (device) *device = static_cast<int>(x.device());
+        if (requires_grad) *requires_grad = x.requires_grad() ? 1 : 0;
+        if (id) *id = x.id();
+    });
+}
+int cth_tensor_to_host(void* t, float* out) {
+    return guarded([&] { T(t)->copy_to_host(out, T(t)->numel()); });
+}
+int cth_tensor_item(void* t, float* out) {
+    return guarded([&] { *out = T(t)->item<float>(); });
+}
+int cth_tensor_requires_grad(void* t, int flag) {
+    return guarded([&] { T(t)->requires_grad(flag != 0); });
+}
+int cth_tensor_to_device(void* t, int device, void** out) {
+    return guarded([&] { *out = new Tensor(T(t)->to(static_cast<DeviceType>(device))); });
+}
+int cth_tensor_copy(void* t, void** out) {  // copy constructor: new id, same value
+    return guarded([&] { *out = new Tensor(*T(t)); });
+}
+int cth_tensor_fill(void* t, float v) {
+    return guarded([&] { T(t)->fill(v); });
+}
+
+// ---- ops (the reference's Tensor methods / operators) ----
+// op codes: values of `enum class op`; Sum = 21, Softmax = 14 (param = dim), Neg = 2.
+int cth_unary(void* t, int opc, int param, void** out) {
+    return guarded([&] {
+        const Tensor& x = *T(t);
+        Tensor r;
+        switch (static_cast<op>(opc)) {
+            case op::Neg: r = -x; break;
+            case op::ReLU: r = x.relu(); break;
+            case op::Sigmoid: r = x.sigmoid(); break;
+            case op::Tanh: r = x.tanh(); break;
+            case op::Sin: r = x.sin(); break;
+            case op::Cos: r = x.cos(); break;
+            case op::Softmax: r = x.softmax(param); break;
+            case op::Sum: r = x.sum(); break;
+            default: throw std::runtime_error("cth_unary: unsupported op");
+        }
+        *out = new Tensor(std::move(r));
+    });
+}
+int cth_binary(void* a, void* b, int opc, void** out) {
+    return guarded([&] {
+        const Tensor &x = *T(a), &y = *T(b);
+        Tensor r;
+        switch (static_cast<op>(opc)) {
+            case op::Add: r = x + y; break;
+            case op::Sub: r = x - y; break;
+            case op::Mul: r = x * y; break;
+            case op::Div: r = x / y; break;
+            case op::MatMul: r = x.matmul(y); break;
+            case op::Dot: r = x.dot(y); break;
+            case op::MSE: r = x.mse_loss(y); break;
+            case op::MAE: r = x.mae_loss(y); break;
+            case op::CE: r = x.cross_entropy(y); break;
+            default: throw std::runtime_error("cth_binary: unsupported op");
+        }
+        *out = new Tensor(std::move(r));
+    });
+}
+// kind: 0 t*s, 1 t+s, 2 t/s, 3 s-t, 4 s/t, 5 s*t, 6 s+t
+int cth_scalar(void* t, float s, int kind, void** out) {
+    return guarded([&] {
+        const Tensor& x = *T(t);
+        Tensor r;
+        switch (kind) {
+            case 0: r = x * s; break;
+            case 1: r = x + s; break;
+            case 2: r = x / s; break;
+            case 3: r = s - x; break;
+            case 4: r = s / x; break;
+            case 5: r = s * x; break;
+            case 6: r = s + x; break;
+            default: throw std::runtime_error("cth_scalar: bad kind");
+        }
+        *out = new Tensor(std::move(r));
+    });
+}
+int cth_transpose(void* t, void** out) {
+    return guarded([&] { *out = new Tensor(T(t)->t()); });
+}
+
+// ---- tape ----
+int cth_ctx_create(void** out) {
+    return guarded([&] { *out = new AutoDiff(); });
+}
+int cth_ctx_destroy(void* c) {
+    return guarded([&] {
+        if (AutoDiffContext::current() == c) AutoDiffContext::current() = nullptr;
+        delete static_cast<AutoDiff*>(c);
+    });
+}
+int cth_ctx_set_current(void* c) {  // NULL switches recording off
+    return guarded([&] { AutoDiffContext::current() = static_cast<AutoDiff*>(c); });
+}
+int cth_ctx_node_count(void* c, uint64_t* n) {
+    return guarded([&] { *n = static_cast<AutoDiff*>(c)->node_count(); });
+}
+int cth_ctx_clear(void* c) {
+    return guarded([&] { static_cast<AutoDiff*>(c)->clear_graph(); });
+}
+int cth_ctx_release_step_nodes(void* c) {
+    return guarded([&] { static_cast<AutoDiff*>(c)->release_step_nodes(); });
+}
+int cth_ctx_make_leaf(void* c, void* t, int requires_grad) {
+    return guarded([&] { static_cast<AutoDiff*>(c)->make_leaf(*T(t), requires_grad != 0); });
+}
+int cth_ctx_zero_grad(void* c, void* t) {
+    return guarded([&] { static_cast<AutoDiff*>(c)->zero_grad(*T(t)); });
+}
+int cth_backward(void* root, void* grad_or_null) {
+    return guarded([&] {
+        if (grad_or_null) backward(*T(root), *T(grad_or_null));
+        else backward(*T(root));
+    });
+}
+int cth_grad(void* t, void** out) {
+    return guarded([&] { *out = new Tensor(grad(*T(t))); });
+}
+int cth_sgd_update(void* p, void* g, float lr) {
+    return guarded([&] { T(p)->sgd_update_(*T(g), lr); });
+}
+
+// ---- MLP trainer ----
+int cth_mlp_create(int n_layers, const int64_t* dims, const float* params, float lr, void** out) {
+    return guarded([&] {
+        if (n_layers < 1) throw std::runtime_error("cth_mlp_create: need at least one layer");
+        *out = new MlpTrainer(n_layers, dims, params, lr);
+    });
+}
+int cth_mlp_destroy(void* m) {
+    return guarded([&] { delete static_cast<MlpTrainer*>(m); });
+}
+int cth_mlp_set_comm(void* m, void* comm) {
+    return guarded([&] { static_cast<MlpTrainer*>(m)->set_comm(comm); });
+}
+int cth_mlp_keep_logits(void* m, int keep) {
+    return guarded([&] { static_cast<MlpTrainer*>(m)->keep_logits = keep != 0; });
+}
+int cth_mlp_step_host(void* m, const float* x_host, const float* labels_host, int64_t batch, float* loss) {
+    return guarded([&] { *loss = static_cast<MlpTrainer*>(m)->step_host(x_host, labels_host, batch); });
+}
+int cth_mlp_step_device(void* m, void* x, void* onehot, float* loss) {
+    return guarded([&] { *loss = static_cast<MlpTrainer*>(m)->step(*T(x), *T(onehot)); });
+}
+int cth_mlp_get_params(void* m, float* out) {
+    return guarded([&] { static_cast<MlpTrainer*>(m)->get_params(out); });
+}
+int cth_mlp_get_grads(void* m, float* out) {
+    return guarded([&] { static_cast<MlpTrainer*>(m)->get_grads(out); });
+}
+int cth_mlp_get_logits(void* m, float* out) {
+    return guarded([&] {
+        auto* t = static_cast<MlpTrainer*>(m);
+        t->last_logits.copy_to_host(out, t->last_logits.numel());
+    });
+}
+int cth_mlp_n_params(void* m, int64_t* n) {
+    return guarded([&] { *n = static_cast<MlpTrainer*>(m)->n_params(); });
+}
+int cth_mlp_node_count(void* m, uint64_t* n) {
+    return guarded([&] { *n = static_cast<MlpTrainer*>(m)->ctx.node_count(); });
+}
+
+}  // extern "C"

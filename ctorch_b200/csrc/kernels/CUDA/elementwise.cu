@@ -257,6 +257,31 @@ __global__ void __launch_bounds__(kThreads) sgd_kernel(float* __restrict__ p, co
     stream_loop(n, vec_ok, vec, tail);
 }
 
+struct GatherArgs {
+    int64_t shape[8];
+    int64_t stride[8];
+    int rank;
+};
+__global__ void __launch_bounds__(kThreads) gather_nd_kernel(const float* __restrict__ src, float* __restrict__ dst, int64_t n, GatherArgs g) {
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        int64_t rem = i, off = 0;
+        for (int j = g.rank - 1; j >= 0; --j) {
+            const int64_t idx = rem % g.shape[j];
+            rem /= g.shape[j];
+            off += idx * g.stride[j];
+        }
+        dst[i] = __ldg(src + off);
+    }
+}
+
+__global__ void __launch_bounds__(kThreads) onehot_kernel(const float* __restrict__ labels, int64_t rows, int64_t classes, float* __restrict__ out) {
+    const int64_t n = rows * classes;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t r = i / classes, j = i - r * classes;
+        out[i] = (static_cast<int>(__ldg(labels + r)) == static_cast<int>(j)) ? 1.0f : 0.0f;
+    }
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline int grid_for(int64_t n) { return ctk_stream_grid((n + 3) / 4, kThreads * kUnroll, kCtasPerSm); }
 
@@ -348,6 +373,33 @@ ctk_status ctk_tile_f32(const float* src, int64_t src_n, float* dst, int64_t n, 
     bool vec_ok = aligned16(src) && aligned16(dst) && src_n % 4 == 0;
     tile_kernel<<<grid_for(n), kThreads, 0, ctk::as_stream(stream)>>>(src, src_n, dst, n, vec_ok);
     CTK_LAUNCH_CHECK("tile_kernel");
+    return CTK_OK;
+}
+
+ctk_status ctk_onehot_f32(const float* labels, int64_t rows, int64_t classes, float* onehot, void* stream) {
+    CTK_REQUIRE(rows >= 0 && classes >= 0, "ctk_onehot_f32: negative shape");
+    if (rows == 0 || classes == 0) return CTK_OK;
+    CTK_REQUIRE(labels && onehot, "ctk_onehot_f32: null pointer");
+    onehot_kernel<<<ctk_stream_grid(rows * classes, kThreads, kCtasPerSm), kThreads, 0, ctk::as_stream(stream)>>>(labels, rows, classes, onehot);
+    CTK_LAUNCH_CHECK("onehot_kernel");
+    return CTK_OK;
+}
+
+ctk_status ctk_gather_nd_f32(const float* src, float* dst, int rank, const int64_t* dst_shape, const int64_t* src_strides, void* stream) {
+    CTK_REQUIRE(rank >= 0 && rank <= 8, "ctk_gather_nd_f32: rank must be 0..8");
+    CTK_REQUIRE(src && dst && (rank == 0 || (dst_shape && src_strides)), "ctk_gather_nd_f32: null pointer");
+    GatherArgs g{};
+    g.rank = rank;
+    int64_t n = 1;
+    for (int j = 0; j < rank; ++j) {
+        CTK_REQUIRE(dst_shape[j] >= 0 && src_strides[j] >= 0, "ctk_gather_nd_f32: negative extent or stride");
+        g.shape[j] = dst_shape[j];
+        g.stride[j] = src_strides[j];
+        n *= dst_shape[j];
+    }
+    if (n == 0) return CTK_OK;
+    gather_nd_kernel<<<ctk_stream_grid(n, kThreads, kCtasPerSm), kThreads, 0, ctk::as_stream(stream)>>>(src, dst, n, g);
+    CTK_LAUNCH_CHECK("gather_nd_kernel");
     return CTK_OK;
 }
 

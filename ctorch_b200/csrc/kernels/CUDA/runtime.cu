@@ -173,6 +173,13 @@ ctk_status ctk_stream_create(void** s) {
     *s = st;
     return CTK_OK;
 }
+ctk_status ctk_stream_create_ex(void** s, int non_blocking) {
+    CTK_REQUIRE(s, "ctk_stream_create_ex: null");
+    cudaStream_t st;
+    CTK_CUDA(cudaStreamCreateWithFlags(&st, non_blocking ? cudaStreamNonBlocking : cudaStreamDefault));
+    *s = st;
+    return CTK_OK;
+}
 ctk_status ctk_stream_destroy(void* s) {
     if (s) CTK_CUDA(cudaStreamDestroy(as_stream(s)));
     return CTK_OK;

@@ -1,0 +1,249 @@
+"""Python face of the C++ front end (ctorch_b200_frontend.h): Tensor, AutoDiff context, MLP trainer.
+
+Mirrors the reference's user-level API so tests read like the reference's own: operators, relu(),
+matmul(), cross_entropy(), backward(loss), grad(t).  No compute happens in Python.
+"""
+import ctypes
+
+import numpy as np
+
+from ._lib import lib, CtkError
+
+OP = dict(Add=0, Sub=1, Neg=2, Mul=3, Div=4, MatMul=5, Dot=6, Cos=7, Sin=8, ReLU=11, Tanh=12, Sigmoid=13,
+          Softmax=14, MSE=17, MAE=18, CE=19, Sum=21)
+CPU, CUDA = 0, 1
+_vp = ctypes.c_void_p
+
+
+class FrontendError(RuntimeError):
+    pass
+
+
+def _chk(rc):
+    if rc:
+        raise FrontendError(lib.cth_last_error().decode("utf-8", "replace"))
+
+
+def cuda_available():
+    return bool(lib.cth_cuda_available())
+
+
+def set_quiet(q=True):
+    lib.cth_set_quiet(1 if q else 0)
+
+
+class Tensor:
+    def __init__(self, handle):
+        self.h = handle
+
+    @staticmethod
+    def from_numpy(a, device=CUDA):
+        a = np.require(a, dtype=np.float32, requirements="C")
+        shape = np.asarray(a.shape, dtype=np.int64)
+        h = _vp()
+        _chk(lib.cth_tensor_from_host(a.ctypes.data_as(_vp), shape.ctypes.data_as(_vp), a.ndim, device, ctypes.byref(h)))
+        return Tensor(h)
+
+    @staticmethod
+    def zeros(shape, device=CUDA):
+        s = np.asarray(shape, dtype=np.int64)
+        h = _vp()
+        _chk(lib.cth_tensor_from_host(None, s.ctypes.data_as(_vp), len(shape), device, ctypes.byref(h)))
+        return Tensor(h)
+
+    @staticmethod
+    def scalar(v):
+        h = _vp()
+        _chk(lib.cth_tensor_scalar(ctypes.c_float(v), ctypes.byref(h)))
+        return Tensor(h)
+
+    def info(self):
+        shape = (ctypes.c_int64 * 8)()
+        rank, dev, rg = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        tid = ctypes.c_uint64()
+        _chk(lib.cth_tensor_info(self.h, shape, ctypes.byref(rank), ctypes.byref(dev), ctypes.byref(rg), ctypes.byref(tid)))
+        return dict(shape=tuple(shape[i] for i in range(rank.value)), device=dev.value, requires_grad=bool(rg.value), id=tid.value)
+
+    @property
+    def shape(self):
+        return self.info()["shape"]
+
+    def numpy(self):
+        out = np.empty(self.shape, np.float32)
+        _chk(lib.cth_tensor_to_host(self.h, out.ctypes.data_as(_vp)))
+        return out
+
+    def item(self):
+        v = ctypes.c_float()
+        _chk(lib.cth_tensor_item(self.h, ctypes.byref(v)))
+        return np.float32(v.value)
+
+    def requires_grad(self, flag=True):
+        _chk(lib.cth_tensor_requires_grad(self.h, 1 if flag else 0))
+        return self
+
+    def to(self, device):
+        h = _vp()
+        _chk(lib.cth_tensor_to_device(self.h, device, ctypes.byref(h)))
+        return Tensor(h)
+
+    def copy(self):
+        h = _vp()
+        _chk(lib.cth_tensor_copy(self.h, ctypes.byref(h)))
+        return Tensor(h)
+
+    def fill(self, v):
+        _chk(lib.cth_tensor_fill(self.h, ctypes.c_float(v)))
+        return self
+
+    def t(self):
+        h = _vp()
+        _chk(lib.cth_transpose(self.h, ctypes.byref(h)))
+        return Tensor(h)
+
+    def _un(self, op, param=0):
+        h = _vp()
+        _chk(lib.cth_unary(self.h, OP[op], param, ctypes.byref(h)))
+        return Tensor(h)
+
+    def _bin(self, other, op):
+        h = _vp()
+        _chk(lib.cth_binary(self.h, other.h, OP[op], ctypes.byref(h)))
+        return Tensor(h)
+
+    def _sc(self, s, kind):
+        h = _vp()
+        _chk(lib.cth_scalar(self.h, ctypes.c_float(s), kind, ctypes.byref(h)))
+        return Tensor(h)
+
+    def relu(self): return self._un("ReLU")
+    def sigmoid(self): return self._un("Sigmoid")
+    def tanh(self): return self._un("Tanh")
+    def sin(self): return self._un("Sin")
+    def cos(self): return self._un("Cos")
+    def softmax(self, dim=-1): return self._un("Softmax", dim)
+    def sum(self): return self._un("Sum")
+    def __neg__(self): return self._un("Neg")
+    def matmul(self, o): return self._bin(o, "MatMul")
+    def dot(self, o): return self._bin(o, "Dot")
+    def mse_loss(self, o): return self._bin(o, "MSE")
+    def mae_loss(self, o): return self._bin(o, "MAE")
+    def cross_entropy(self, o): return self._bin(o, "CE")
+    def __add__(self, o): return self._bin(o, "Add") if isinstance(o, Tensor) else self._sc(o, 1)
+    def __sub__(self, o): return self._bin(o, "Sub")
+    def __mul__(self, o): return self._bin(o, "Mul") if isinstance(o, Tensor) else self._sc(o, 0)
+    def __truediv__(self, o): return self._bin(o, "Div") if isinstance(o, Tensor) else self._sc(o, 2)
+    def __radd__(self, s): return self._sc(s, 6)
+    def __rmul__(self, s): return self._sc(s, 5)
+    def __rsub__(self, s): return self._sc(s, 3)
+    def __rtruediv__(self, s): return self._sc(s, 4)
+
+    def sgd_update_(self, g, lr):
+        _chk(lib.cth_sgd_update(self.h, g.h, ctypes.c_float(lr)))
+
+    def __del__(self):
+        try:
+            if self.h:
+                lib.cth_tensor_free(self.h)
+        except Exception:
+            pass
+
+
+class AutoDiff:
+    """`AutoDiff ctx; AutoDiffContext::Guard guard(&ctx);` as a Python context manager."""
+
+    def __init__(self):
+        h = _vp()
+        _chk(lib.cth_ctx_create(ctypes.byref(h)))
+        self.h = h
+
+    def __enter__(self):
+        _chk(lib.cth_ctx_set_current(self.h))
+        return self
+
+    def __exit__(self, *a):
+        _chk(lib.cth_ctx_set_current(None))
+
+    def make_leaf(self, t, requires_grad=True): _chk(lib.cth_ctx_make_leaf(self.h, t.h, 1 if requires_grad else 0))
+    def zero_grad(self, t): _chk(lib.cth_ctx_zero_grad(self.h, t.h))
+    def clear_graph(self): _chk(lib.cth_ctx_clear(self.h))
+    def release_step_nodes(self): _chk(lib.cth_ctx_release_step_nodes(self.h))
+
+    def node_count(self):
+        n = ctypes.c_uint64()
+        _chk(lib.cth_ctx_node_count(self.h, ctypes.byref(n)))
+        return n.value
+
+    def __del__(self):
+        try:
+            lib.cth_ctx_destroy(self.h)
+        except Exception:
+            pass
+
+
+def backward(root, grad_output=None):
+    _chk(lib.cth_backward(root.h, grad_output.h if grad_output is not None else None))
+
+
+def grad(t):
+    h = _vp()
+    _chk(lib.cth_grad(t.h, ctypes.byref(h)))
+    return Tensor(h)
+
+
+class MlpTrainer:
+    """The training step of mnist/mnist.cpp for any layer list (see ctorch_b200_frontend.h)."""
+
+    def __init__(self, dims, params, lr):
+        self.dims = [int(d) for d in dims]
+        d = np.asarray(self.dims, dtype=np.int64)
+        p = np.require(params, dtype=np.float32, requirements="C")
+        h = _vp()
+        _chk(lib.cth_mlp_create(len(self.dims) - 1, d.ctypes.data_as(_vp), p.ctypes.data_as(_vp), ctypes.c_float(lr), ctypes.byref(h)))
+        self.h = h
+        n = ctypes.c_int64()
+        _chk(lib.cth_mlp_n_params(self.h, ctypes.byref(n)))
+        self.n_params = n.value
+
+    def set_comm(self, comm_handle):
+        _chk(lib.cth_mlp_set_comm(self.h, comm_handle))
+
+    def keep_logits(self, keep=True):
+        _chk(lib.cth_mlp_keep_logits(self.h, 1 if keep else 0))
+
+    def step_host(self, x, labels):
+        """x, labels: numpy arrays or raw host pointers (ints) with an explicit batch via x.shape[0]."""
+        loss = ctypes.c_float()
+        _chk(lib.cth_mlp_step_host(self.h, x.ctypes.data_as(_vp), labels.ctypes.data_as(_vp), ctypes.c_int64(x.shape[0]), ctypes.byref(loss)))
+        return loss.value
+
+    def step_device(self, x, onehot):
+        loss = ctypes.c_float()
+        _chk(lib.cth_mlp_step_device(self.h, x.h, onehot.h, ctypes.byref(loss)))
+        return loss.value
+
+    def params(self):
+        out = np.empty(self.n_params, np.float32)
+        _chk(lib.cth_mlp_get_params(self.h, out.ctypes.data_as(_vp)))
+        return out
+
+    def grads(self):
+        out = np.empty(self.n_params, np.float32)
+        _chk(lib.cth_mlp_get_grads(self.h, out.ctypes.data_as(_vp)))
+        return out
+
+    def logits(self, batch):
+        out = np.empty((batch, self.dims[-1]), np.float32)
+        _chk(lib.cth_mlp_get_logits(self.h, out.ctypes.data_as(_vp)))
+        return out
+
+    def node_count(self):
+        n = ctypes.c_uint64()
+        _chk(lib.cth_mlp_node_count(self.h, ctypes.byref(n)))
+        return n.value
+
+    def __del__(self):
+        try:
+            lib.cth_mlp_destroy(self.h)
+        except Exception:
+            pass

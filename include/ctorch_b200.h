@@ -82,6 +82,8 @@ ctk_status ctk_memcpy_d2d(void* device_dst, const void* device_src, size_t bytes
 ctk_status ctk_memset(void* device_ptr, int byte_value, size_t bytes, void* stream);
 
 ctk_status ctk_stream_create(void** stream);
+/* non_blocking != 0: the stream does not synchronise with the legacy default stream. */
+ctk_status ctk_stream_create_ex(void** stream, int non_blocking);
 ctk_status ctk_stream_destroy(void* stream);
 ctk_status ctk_stream_sync(void* stream);
 ctk_status ctk_event_create(void** event);
@@ -117,6 +119,16 @@ ctk_status ctk_fill_f32(float* p, float value, const float* value_device, int64_
  * (src/Tensor.cpp:289-387) and the lower-rank tiling of the grad-shape adjustment
  * (src/AutoDiff.cpp:633-687). */
 ctk_status ctk_tile_f32(const float* src, int64_t src_n, float* dst, int64_t n, void* stream);
+
+/* onehot[r, j] = (j == (int)labels[r]) ? 1 : 0 for labels stored as floats: the host loop of
+ * mnist/mnist.cpp:67-72, for labels that already live on the device. */
+ctk_status ctk_onehot_f32(const float* labels, int64_t rows, int64_t classes, float* onehot, void* stream);
+
+/* dst[r] = src[sum_j r_j * src_strides[j]] over the row-major index r of dst_shape (rank <= 8, a
+ * stride of 0 repeats index 0): the gather of AutoDiff::check_and_adjust_grad_shape's broadcast
+ * branch (src/AutoDiff.cpp:690-890), which takes index 0 on every broadcast dim. */
+ctk_status ctk_gather_nd_f32(const float* src, float* dst, int rank, const int64_t* dst_shape,
+                             const int64_t* src_strides, void* stream);
 
 /* ------------------------------------------------------------------------------------------- */
 /* Elementwise, backward (the per-op rules of AutoDiff::backward, src/AutoDiff.cpp:1216-1416),  */

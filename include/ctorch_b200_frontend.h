@@ -1,0 +1,87 @@
+/*
+ * ctorch_b200_frontend -- C ABI over the C++ front end (Tensor / AutoDiff / Ctorch_Scheduler with
+ * DeviceType::kCUDA filled in), for hosts that are not C++.
+ *
+ * Every call goes through the same path as user C++ code written against the reference's API:
+ * Tensor op wrapper (src/Tensor.cpp:482-497 and its 15 siblings) -> Ctorch_Scheduler::dispatch
+ * (include/Ctorch_Scheduler.h:86-166) -> `*_CUDA_kernel` (src/kernels/kernels.h:42-242) -> the
+ * kernels of ctorch_b200.h, recording on the current AutoDiff tape (include/AutoDiff.h:156-219).
+ *
+ * Handles are opaque pointers (tensor: a heap-allocated Tensor; ctx: an AutoDiff; mlp: a trainer).
+ * Every function returns 0 on success, 1 if the front end threw; cth_last_error() has the message.
+ * Operator codes are the numeric values of the reference's `enum class op` (include/Ctools.h:175-209);
+ * device codes those of DeviceType (0 = kCPU, 1 = kCUDA).
+ */
+#ifndef CTORCH_B200_FRONTEND_H
+#define CTORCH_B200_FRONTEND_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+const char* cth_last_error(void);
+void cth_set_quiet(int quiet);          /* silence Ctorch_Error::log printing (errors are still counted) */
+uint64_t cth_error_count(void);         /* number of log(ERROR) calls so far */
+int cth_cuda_available(void);           /* Ctorch_Scheduler::isDeviceAvailable(kCUDA), include/Ctorch_Scheduler.h:67-75 */
+
+/* ---- Tensor (include/Tensor.h) ---- */
+/* Tensor(ShapeTag, shape, kFloat, device); data == NULL leaves it zero-filled. */
+int cth_tensor_from_host(const float* data, const int64_t* shape, int rank, int device, void** tensor);
+int cth_tensor_scalar(float value, void** tensor);   /* Tensor(float): 0-D, on the host (include/Tensor.h:239-264) */
+int cth_tensor_free(void* tensor);
+int cth_tensor_info(void* tensor, int64_t* shape_out8, int* rank, int* device, int* requires_grad, uint64_t* id);
+int cth_tensor_to_host(void* tensor, float* out);     /* row-major values, also of a strided view */
+int cth_tensor_item(void* tensor, float* out);        /* Tensor::item<float>, src/Tensor.cpp:154-165 */
+int cth_tensor_requires_grad(void* tensor, int flag); /* Tensor::requires_grad(bool), src/Tensor.cpp:28-39 */
+int cth_tensor_to_device(void* tensor, int device, void** out);
+int cth_tensor_copy(void* tensor, void** out);        /* copy constructor: new id, same value */
+int cth_tensor_fill(void* tensor, float value);
+int cth_transpose(void* tensor, void** out);          /* Tensor::t(), src/Tensor.cpp:246-261 */
+
+/* ---- operators ---- */
+/* relu/sigmoid/tanh/sin/cos/unary minus/softmax(param = dim)/sum */
+int cth_unary(void* tensor, int op, int param, void** out);
+/* + - * / matmul dot mse_loss mae_loss cross_entropy */
+int cth_binary(void* a, void* b, int op, void** out);
+/* kind: 0 t*s, 1 t+s, 2 t/s, 3 s-t, 4 s/t, 5 s*t, 6 s+t (src/Tensor.cpp:751-973, 1416-1453) */
+int cth_scalar(void* tensor, float s, int kind, void** out);
+
+/* ---- AutoDiff (include/AutoDiff.h) ---- */
+int cth_ctx_create(void** ctx);
+int cth_ctx_destroy(void* ctx);
+int cth_ctx_set_current(void* ctx_or_null);           /* AutoDiffContext::current() of the calling thread */
+int cth_ctx_make_leaf(void* ctx, void* tensor, int requires_grad);
+int cth_ctx_zero_grad(void* ctx, void* tensor);
+int cth_ctx_clear(void* ctx);                         /* AutoDiff::clear_graph */
+int cth_ctx_release_step_nodes(void* ctx);            /* drop nodes no future root can reach (no counterpart) */
+int cth_ctx_node_count(void* ctx, uint64_t* n);
+int cth_backward(void* root, void* grad_output_or_null); /* free backward(root[, grad]), src/Tensor.cpp:1373-1384 */
+int cth_grad(void* tensor, void** out);                /* free grad(t), src/Tensor.cpp:1387-1392 */
+int cth_sgd_update(void* param, void* grad, float lr); /* p -= g*lr on the device (mnist/mnist.cpp:80-92) */
+
+/* ---- the MLP training step of mnist/mnist.cpp:44-92 for any layer list ----
+ * dims[0..n_layers]; params packed W1,b1,W2,b2,... (W row-major [in,out]).  A step is
+ * make_leaf/requires_grad/zero_grad, forward (matmul + bias, ReLU between layers), one-hot
+ * cross entropy (summed over the batch), backward, SGD; it returns the loss. */
+int cth_mlp_create(int n_layers, const int64_t* dims, const float* params, float lr, void** mlp);
+int cth_mlp_destroy(void* mlp);
+/* Data parallel: all-reduce (sum) every parameter gradient over `comm` (a ctk_comm_init_rank
+ * communicator), started per gradient while backward is still running.  NULL switches it off. */
+int cth_mlp_set_comm(void* mlp, void* comm);
+int cth_mlp_keep_logits(void* mlp, int keep);
+/* x_host [batch, dims[0]] and labels_host [batch] (class indices as floats) in HOST memory. */
+int cth_mlp_step_host(void* mlp, const float* x_host, const float* labels_host, int64_t batch, float* loss);
+/* x and onehot are device tensors ([batch, dims[0]] and [batch, classes]). */
+int cth_mlp_step_device(void* mlp, void* x, void* onehot, float* loss);
+int cth_mlp_n_params(void* mlp, int64_t* n);
+int cth_mlp_get_params(void* mlp, float* out);
+int cth_mlp_get_grads(void* mlp, float* out);         /* gradients of the last step (after the all-reduce) */
+int cth_mlp_get_logits(void* mlp, float* out);        /* logits of the last step, if kept */
+int cth_mlp_node_count(void* mlp, uint64_t* n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CTORCH_B200_FRONTEND_H */
