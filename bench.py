@@ -1,0 +1,468 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 CUDA backend for CTorch.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Default workload (the headline): the data-parallel MLP training step -- 784-4096-4096-4096-10,
+fp32, ReLU, Softmax+CrossEntropy (summed), SGD lr 0.01, 8192 synthetic rows per GPU (pixels k/255,
+labels 0..9), Kaiming-uniform weights from a fixed seed, one process per GPU, gradients all-reduced
+with NCCL while backward runs.  Prints ONE JSON line (rank 0).
+
+  value   samples/s of the whole job with the step's inputs already resident on the device
+  e2e     the same step through the public call that takes HOST buffers: the host-to-device copy of
+          the batch (from page-locked memory) and the device-to-host read of the loss are inside
+          the timed region
+  roofline  the dominant kernel (the tcgen05 MatMul): algorithmic flops (2*M*N*K per product) over
+          its launch durations, timed with CUDA events on the launching stream during the timed steps
+  cpu_baseline  the reference's own CPU path (single-threaded by construction) on a bounded sample
+          of the same workload, N=1 only
+
+`--impl reference` times that CPU path alone (rank 0; other ranks exit).
+Other workloads (single GPU): elementwise, rowwise, matmul -- the single-op sweeps of the other
+benchmark configs, one JSON line each with achieved GB/s or TFLOP/s.
+"""
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+DIMS = [784, 4096, 4096, 4096, 10]
+BATCH = 8192
+LR = 0.01
+WORKLOAD = "dp-mlp-784-4096-4096-4096-10_batch8192-per-gpu_fp32_sgd"
+CPU_SAMPLE_BATCH = 4  # rows per reference step: the reference's cost is linear in rows (~0.2 GFLOP/s)
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm_gbs=d["hbm_gbs"], bf16=d["bf16_tflops"], bf16_sustained=d["bf16_tflops_sustained"], source="measured")
+    return dict(hbm_gbs=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+def make_params(seed=42):
+    rng = np.random.default_rng(seed)
+    parts = []
+    for i, j in zip(DIMS[:-1], DIMS[1:]):
+        lim = np.sqrt(6.0 / i)
+        parts.append(rng.uniform(-lim, lim, (i, j)).astype(np.float32).ravel())
+        parts.append(np.zeros(j, np.float32))
+    return np.concatenate(parts)
+
+
+def make_batch(rank, rows=BATCH, seed=1234):
+    rng = np.random.default_rng(seed + 1000 * rank)
+    x = rng.integers(0, 256, (rows, DIMS[0])).astype(np.float32) / np.float32(255.0)
+    labels = rng.integers(0, DIMS[-1], rows).astype(np.float32)
+    return x, labels
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(self.gpu)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [v.strip() for v in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        if not sm:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["no samples"])
+        return dict(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), power_w_max=max(power), samples=len(sm), reasons=sorted(reasons))
+
+
+# ------------------------------------------------------------------------------------------------
+# the reference arm: the reference's own CPU implementation, single-threaded by construction
+# ------------------------------------------------------------------------------------------------
+def cpu_reference_step_time(steps, warmup, batch=CPU_SAMPLE_BATCH):
+    """Times `steps` training steps of the same architecture at `batch` rows on one host core.
+    Uses the unmodified reference library when it was built, else the plain-C port."""
+    import oracle
+    # the reference prints a banner and log lines on stdout: keep stdout for the one JSON line
+    sys.stdout.flush()
+    saved = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        return _cpu_reference_step_time(oracle, steps, warmup, batch)
+    finally:
+        sys.stdout.flush()
+        os.dup2(saved, 1)
+        os.close(saved)
+
+
+def _cpu_reference_step_time(oracle, steps, warmup, batch):
+    if oracle.Reference.available():
+        impl = oracle.Reference()
+    else:
+        impl = oracle.Oracle()
+    p = make_params()
+    x, lab = make_batch(0, batch)
+    x4 = x.reshape(1, 1, batch, DIMS[0])
+    l4 = lab.reshape(1, 1, batch)
+    times = []
+    # every call rebuilds the model from `p`, so each call is timed as setup + n steps and the setup
+    # (a zero-step call) is subtracted
+    t0 = time.perf_counter(); impl.mlp_train(DIMS, x4, l4, p, LR, 0, want_logits=False); setup = time.perf_counter() - t0
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        impl.mlp_train(DIMS, x4, l4, p, LR, 1, want_logits=False)
+        dt = max(time.perf_counter() - t0 - setup, 1e-9)
+        if i >= warmup:
+            times.append(dt)
+    return impl.kind, statistics.median(times), sum(times), batch
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    kind, t_step, total, batch = cpu_reference_step_time(args.steps, args.warmup)
+    v = batch / t_step
+    cpu = dict(value=v, unit="samples/s", cores=1, kind=kind,
+               sample=f"{args.steps} timed steps of the same 784-4096-4096-4096-10 training step at batch {batch} (cost is linear in rows), median step {t_step:.3f} s, host {host_cpu()}")
+    print(json.dumps(dict(impl="reference", metric="mlp_train_samples_per_s", value=v, unit="samples/s", n_gpus=args.gpus, steps=args.steps,
+                          warmup=args.warmup, ms_per_step=t_step * 1e3, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32",
+                          data="synthetic", config=dict(workload=WORKLOAD, sample_batch=batch, threads=1),
+                          cpu_baseline=cpu, e2e=dict(value=v, unit="samples/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))))
+
+
+def host_cpu():
+    try:
+        for ln in open("/proc/cpuinfo"):
+            if ln.startswith("model name"):
+                return ln.split(":", 1)[1].strip() + f" x{os.cpu_count()}"
+    except Exception:
+        pass
+    return f"unknown x{os.cpu_count()}"
+
+
+# ------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------
+def run_mlp(args, rank, world, local_rank, dist):
+    import ctorch_b200 as cb
+    from ctorch_b200 import frontend as F
+    from ctorch_b200.device import PinnedArray
+    cb.check(cb.lib.ctk_set_device(local_rank))
+    F.set_quiet(True)
+    peaks = measured_peaks()
+
+    comm = None
+    if world > 1:
+        import torch
+        idbuf = np.zeros(128, np.uint8)
+        if rank == 0:
+            cb.check(cb.lib.ctk_comm_unique_id(idbuf.ctypes.data_as(ctypes.c_void_p)))
+        t = torch.from_numpy(idbuf)
+        dist.broadcast(t, src=0)
+        comm = ctypes.c_void_p()
+        cb.check(cb.lib.ctk_comm_init_rank(ctypes.byref(comm), idbuf.ctypes.data_as(ctypes.c_void_p), world, rank))
+
+    params = make_params()
+    x, labels = make_batch(rank)
+    onehot = np.zeros((BATCH, DIMS[-1]), np.float32)
+    onehot[np.arange(BATCH), labels.astype(int)] = 1
+    trainer = F.MlpTrainer(DIMS, params, LR)
+    if comm is not None:
+        trainer.set_comm(comm)
+    X, Y = F.Tensor.from_numpy(x), F.Tensor.from_numpy(onehot)
+    px, pl = PinnedArray(x.shape), PinnedArray(labels.shape)
+    px.array[...] = x
+    pl.array[...] = labels
+
+    def barrier():
+        cb.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(v):
+        if world == 1:
+            return v
+        import torch
+        t = torch.tensor([v], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    def timed(step_fn, profile):
+        for _ in range(args.warmup):
+            step_fn()
+        barrier()
+        if profile:
+            cb.check(cb.lib.ctk_matmul_profile_enable(1))
+        e0, e1 = cb.Event(), cb.Event()
+        l0 = cb.launch_count()
+        e0.record()
+        loss = None
+        for _ in range(args.steps):
+            loss = step_fn()
+        e1.record()
+        e1.sync()
+        cb.synchronize()
+        launches = cb.launch_count() - l0
+        ms = e0.elapsed_ms(e1)
+        prof = None
+        if profile:
+            n, tms, fl = ctypes.c_int64(), ctypes.c_double(), ctypes.c_double()
+            cb.check(cb.lib.ctk_matmul_profile_read(ctypes.byref(n), ctypes.byref(tms), ctypes.byref(fl)))
+            cb.check(cb.lib.ctk_matmul_profile_enable(0))
+            prof = (n.value, tms.value, fl.value)
+        barrier()
+        return max_over_ranks(ms), launches, loss, prof
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms_dev, launches, loss_dev, prof = timed(lambda: trainer.step_device(X, Y), True)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_e2e, _, loss_e2e, _ = timed(lambda: trainer.step_host(px.array, pl.array), False)
+    status = cb.ops.matmul_status()
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        kind, t_step, total, b = cpu_reference_step_time(2, 0)
+        cpu = dict(value=b / t_step, unit="samples/s", cores=1, kind=kind,
+                   sample=f"2 steps of the same training step at batch {b} (cost linear in rows), median step {t_step:.2f} s, single thread (the reference has no threading), host {host_cpu()}")
+
+    if rank == 0:
+        per_step = ms_dev / args.steps
+        value = BATCH * world / (per_step * 1e-3)
+        e2e_v = BATCH * world / (ms_e2e / args.steps * 1e-3)
+        n, tms, fl = prof
+        achieved = fl / (tms * 1e-3) / 1e12 if tms > 0 else 0.0
+        tf32_peak = peaks["bf16_sustained"] / 2.0
+        peak = tf32_peak / 3.0
+        flops_step = sum(2.0 * BATCH * i * j for i, j in zip(DIMS[:-1], DIMS[1:])) * 2 + sum(2.0 * BATCH * i * j for i, j in zip(DIMS[1:-1], DIMS[2:]))
+        out = dict(
+            metric="mlp_train_samples_per_s", value=value, unit="samples/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
+            ms_per_step=per_step, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",
+            config=dict(workload=WORKLOAD, global_batch=BATCH * world, parallelism=f"dp{world}", matmul_mode="3xtf32",
+                        l2="per-step working set (weights 147 MB + activations 3x134 MB per layer pass) exceeds the 126 MB L2",
+                        loss_first=float(loss_dev) if loss_dev is not None else None, matmul_status=status),
+            clocks=clocks,
+            e2e=dict(value=e2e_v, unit="samples/s", ms_per_step=ms_e2e / args.steps,
+                     h2d_bytes_per_step=int(x.nbytes + labels.nbytes), d2h_bytes_per_step=4),
+            gpu_launches=int(launches),
+            roofline=dict(bound="tensor", achieved=achieved, peak=peak, unit="TFLOP/s", frac=achieved / peak if peak else None, traffic=None,
+                          kernel="tcgen05_matmul_kernel (3xTF32)", launches=int(n), avg_launch_ms=tms / n if n else None,
+                          peak_source=f"{peaks['source']}: bf16_tflops_sustained {peaks['bf16_sustained']} / 2 (TF32 runs at half the bf16 rate; no TF32 figure was measured) / 3 (three TF32 products per fp32 product); algorithmic flops 2*M*N*K",
+                          step_model_flops=flops_step, step_tflops=flops_step / (per_step * 1e-3) / 1e12),
+            cpu_baseline=cpu,
+        )
+        print(json.dumps(out))
+    if comm is not None:
+        trainer.set_comm(None)
+        del trainer
+        cb.synchronize()
+        cb.lib.ctk_comm_destroy(comm)
+
+
+def run_single_op(args):
+    """The single-op sweeps (one GPU): prints one JSON line per measurement."""
+    import ctorch_b200 as cb
+    cb.check(cb.lib.ctk_set_device(0))
+    peaks = measured_peaks()
+
+    def timeit(fn, iters, warm=3):
+        for _ in range(warm):
+            fn()
+        e0, e1 = cb.Event(), cb.Event()
+        cb.synchronize()
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        e1.sync()
+        return e0.elapsed_ms(e1) / iters
+
+    def emit(name, ms, work, unit, peak, extra=None):
+        ach = work / (ms * 1e-3) / (1e9 if unit == "GB/s" else 1e12)
+        d = dict(metric=name, value=ach, unit=unit, n_gpus=1, ms=ms, higher_is_better=True, data="synthetic",
+                 roofline=dict(bound="hbm" if unit == "GB/s" else "tensor", achieved=ach, peak=peak, unit=unit, frac=ach / peak, traffic=None,
+                               peak_source=peaks["source"]))
+        if extra:
+            d["config"] = extra
+        print(json.dumps(d), flush=True)
+
+    rng = np.random.default_rng(0)
+    if args.workload == "elementwise":
+        for logn in (20, 24, 28):
+            n = 1 << logn
+            # two rotating buffer sets larger than L2 at 2^24 and above
+            a = cb.to_device(rng.uniform(-4, 4, n).astype(np.float32)); b = cb.to_device(rng.uniform(0.5, 4, n).astype(np.float32))
+            g = cb.to_device(rng.standard_normal(n).astype(np.float32)); o, o2 = cb.empty((n,)), cb.empty((n,))
+            row = cb.to_device(rng.uniform(0.5, 4, 1024).astype(np.float32))
+            it = 20
+            for op in ("Add", "Sub", "Mul", "Div"):
+                emit(f"{op}_fwd_2^{logn}", timeit(lambda: cb.ops.binary(op, a, b, out=o), it), 12 * n, "GB/s", peaks["hbm_gbs"])
+                emit(f"{op}_scalar_2^{logn}", timeit(lambda: cb.ops.binary(op, a, b.view(0, (1,)), cb.ops.B_SCALAR, out=o), it), 8 * n, "GB/s", peaks["hbm_gbs"])
+                emit(f"{op}_row1024_2^{logn}", timeit(lambda: cb.ops.binary(op, a, row, cb.ops.B_ROW, out=o), it), 8 * n + 4096, "GB/s", peaks["hbm_gbs"])
+                bwd_bytes = 12 * n if op in ("Add", "Sub") else 20 * n
+                emit(f"{op}_bwd_2^{logn}", timeit(lambda: lib_binary_bwd(cb, op, a, b, g, o, o2), it), bwd_bytes, "GB/s", peaks["hbm_gbs"])
+            for op in ("Neg", "ReLU", "Sigmoid", "Tanh", "Sin", "Cos"):
+                emit(f"{op}_fwd_2^{logn}", timeit(lambda: cb.ops.unary(op, a, out=o), it), 8 * n, "GB/s", peaks["hbm_gbs"])
+                emit(f"{op}_bwd_2^{logn}", timeit(lambda: lib_unary_bwd(cb, op, a, g, o), it), (8 if op == "Neg" else 12) * n, "GB/s", peaks["hbm_gbs"])
+            del a, b, g, o, o2
+    elif args.workload == "rowwise":
+        rows = 65536
+        for C in (10, 1000, 32000):
+            x = cb.empty((rows, C)); cb.ops.fill(x, 0.0)
+            xs = cb.to_device((2 * rng.standard_normal((rows, min(C, 1000)))).astype(np.float32)) if C <= 1000 else None
+            if xs is not None:
+                x = xs
+            else:
+                tile = cb.to_device((2 * rng.standard_normal(C * 64)).astype(np.float32))
+                x = cb.ops.tile(tile, rows * C).reshape(rows, C)
+            y = cb.empty((rows, C))
+            lab = cb.to_device(rng.integers(0, C, rows).astype(np.float32))
+            it = 10 if C < 32000 else 3
+            emit(f"softmax_fwd_C{C}", timeit(lambda: cb.ops.softmax(x, out=y), it), 8 * rows * C, "GB/s", peaks["hbm_gbs"])
+            emit(f"softmax_bwd_C{C}", timeit(lambda: lib_softmax_bwd(cb, y, x, rows, C), it), 12 * rows * C, "GB/s", peaks["hbm_gbs"])
+            emit(f"ce_index_fwd_C{C}", timeit(lambda: cb.ops.cross_entropy(x, lab), it), 4 * rows * C + 4 * rows, "GB/s", peaks["hbm_gbs"])
+            emit(f"ce_fused_fwd_bwd_C{C}", timeit(lambda: lib_ce_fused(cb, x, lab, y, rows, C), it), 8 * rows * C + 4 * rows, "GB/s", peaks["hbm_gbs"])
+            del x, y
+        n = 65536 * 1024
+        a = cb.to_device(rng.standard_normal(n).astype(np.float32)); b = cb.to_device(rng.standard_normal(n).astype(np.float32)); o = cb.empty((n,))
+        emit("mse_fwd_65536x1024", timeit(lambda: cb.ops.mse(a, b), 10), 8 * n, "GB/s", peaks["hbm_gbs"])
+        emit("mae_fwd_65536x1024", timeit(lambda: cb.ops.mae(a, b), 10), 8 * n, "GB/s", peaks["hbm_gbs"])
+        emit("mse_bwd_65536x1024", timeit(lambda: cb.check(cb.lib.ctk_mse_backward_f32(a.p, b.p, None, o.p, ctypes.c_int64(n), None)), 10), 12 * n, "GB/s", peaks["hbm_gbs"])
+        del a, b, o
+        n = 1 << 28
+        a = cb.ops.tile(cb.to_device(rng.uniform(-4, 4, 1 << 20).astype(np.float32)), n)
+        emit("sum_2^28", timeit(lambda: cb.ops.sum(a), 10), 4 * n, "GB/s", peaks["hbm_gbs"])
+    elif args.workload == "matmul":
+        tf32_peak = peaks["bf16"] / 2.0
+        for mode, peak in (("tf32", tf32_peak), ("3xtf32", tf32_peak / 3.0)):
+            for (m, k, n) in ((512, 512, 512), (1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096), (8192, 8192, 8192), (65536, 784, 4096)):
+                A = cb.to_device(rng.standard_normal((m, k)).astype(np.float32)); B = cb.to_device(rng.standard_normal((k, n)).astype(np.float32))
+                dC = cb.to_device(rng.standard_normal((m, n)).astype(np.float32))
+                C, dA, dB = cb.empty((m, n)), cb.empty((m, k)), cb.empty((k, n))
+                it = 20 if m <= 2048 else 5
+                fl = 2.0 * m * n * k
+                cfg = dict(m=m, n=n, k=k, mode=mode, peak_source=f"{peaks['source']} bf16_tflops/2" + ("/3" if mode == "3xtf32" else ""))
+                emit(f"matmul_fwd_{mode}_{m}x{k}x{n}", timeit(lambda: cb.ops.matmul(A, B, mode=mode, out=C), it), fl, "TFLOP/s", peak, cfg)
+                emit(f"matmul_dA_{mode}_{m}x{k}x{n}", timeit(lambda: cb.ops.matmul(dC, B, tb=True, mode=mode, out=dA), it), fl, "TFLOP/s", peak, cfg)
+                emit(f"matmul_dB_{mode}_{m}x{k}x{n}", timeit(lambda: cb.ops.matmul(A, dC, ta=True, mode=mode, out=dB), it), fl, "TFLOP/s", peak, cfg)
+                del A, B, dC, C, dA, dB
+        print(json.dumps(dict(matmul_status=cb.ops.matmul_status())))
+    else:
+        raise SystemExit("unknown workload " + args.workload)
+
+
+def lib_binary_bwd(cb, op, a, b, g, da, db):
+    cb.check(cb.lib.ctk_binary_backward_f32(cb.ops.OP[op], a.p, b.p, g.p, da.p, db.p, ctypes.c_int64(a.size), 0, ctypes.c_int64(1), None))
+
+
+def lib_unary_bwd(cb, op, x, g, dx):
+    cb.check(cb.lib.ctk_unary_backward_f32(cb.ops.OP[op], x.p, g.p, dx.p, ctypes.c_int64(x.size), None))
+
+
+def lib_softmax_bwd(cb, y, g, rows, C):
+    dx = _scratch_like(cb, y)
+    cb.check(cb.lib.ctk_softmax_backward_rows_f32(y.p, g.p, dx.p, ctypes.c_int64(rows), ctypes.c_int64(C), None))
+
+
+_scratch = {}
+
+
+def _scratch_like(cb, t):
+    key = t.size
+    if key not in _scratch:
+        _scratch.clear()
+        _scratch[key] = cb.empty((t.size,))
+    return _scratch[key]
+
+
+def lib_ce_fused(cb, x, lab, d, rows, C):
+    out = _scratch_like(cb, lab)
+    cb.check(cb.lib.ctk_ce_fused_index_f32(x.p, lab.p, ctypes.c_int64(rows), ctypes.c_int64(C), out.p, d.p, None, None, None))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="mlp", choices=["mlp", "elementwise", "rowwise", "matmul"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours" and args.workload == "mlp":
+        args.warmup = 3  # timing rule: at least three warm-up steps
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if args.workload != "mlp":
+        if rank == 0:
+            run_single_op(args)
+        return
+
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        # control plane only (barrier, id broadcast, max over ranks); gradients travel over the
+        # library's own NCCL communicator
+        dist.init_process_group(backend="gloo", rank=rank, world_size=world)
+    try:
+        run_mlp(args, rank, world, local_rank, dist)
+    finally:
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -159,20 +159,25 @@ public:
         return *static_cast<float*>(pinned_loss);
     }
 
-    // The same step from HOST inputs: pixels and integer labels (as floats) in caller memory.
+    // The same step from HOST inputs: pixels and integer labels (as floats) in caller memory.  The
+    // one-hot matrix of mnist/mnist.cpp:67-72 is built on the device from the uploaded labels (same
+    // 0/1 values).  Page-locked caller buffers are copied straight from where they are, without
+    // blocking; pageable ones go through the staging buffers.
     float step_host(const float* x_host, const float* labels_host, int64_t batch) {
         const size_t in = static_cast<size_t>(dims.front()), classes = static_cast<size_t>(dims.back());
+        void* st = current_stream();
         Tensor x(ShapeTag{}, {static_cast<size_t>(batch), in}, DType::kFloat, DeviceType::kCUDA, false);
-        x.copy_from_host(x_host, static_cast<size_t>(batch) * in);
-        // one-hot on the host, as mnist/mnist.cpp:67-72
-        std::vector<float> oh(static_cast<size_t>(batch) * classes, 0.0f);
-        for (int64_t i = 0; i < batch; ++i) {
-            const int lab = static_cast<int>(labels_host[i]);
-            if (lab >= 0 && lab < static_cast<int>(classes)) oh[static_cast<size_t>(i) * classes + lab] = 1.0f;
-        }
+        Tensor labels(ShapeTag{}, {static_cast<size_t>(batch)}, DType::kFloat, DeviceType::kCUDA, false);
+        int px = 0, pl = 0;
+        ctk_host_is_pinned(x_host, &px);
+        ctk_host_is_pinned(labels_host, &pl);
+        if (px) cuda_check(ctk_memcpy_h2d(x.data<float>(), x_host, static_cast<size_t>(batch) * in * sizeof(float), st), "input upload");
+        else x.copy_from_host(x_host, static_cast<size_t>(batch) * in);
+        if (pl) cuda_check(ctk_memcpy_h2d(labels.data<float>(), labels_host, static_cast<size_t>(batch) * sizeof(float), st), "label upload");
+        else labels.copy_from_host(labels_host, static_cast<size_t>(batch));
         Tensor y(ShapeTag{}, {static_cast<size_t>(batch), classes}, DType::kFloat, DeviceType::kCUDA, false);
-        y.copy_from_host(oh.data(), oh.size());
-        return step(x, y);
+        cuda_check(ctk_onehot_f32(labels.data<float>(), batch, static_cast<int64_t>(classes), y.data<float>(), st), "one-hot");
+        return step(x, y);  // ends with a stream synchronisation: the caller's buffers are free again
     }
 
     void get_params(float* out) {

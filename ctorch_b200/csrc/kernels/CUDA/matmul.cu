@@ -28,6 +28,7 @@
 #include <math.h>
 
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 
@@ -537,6 +538,35 @@ bool classify(const float* p, int64_t mn, int64_t k, int64_t s_mn, int64_t s_k, 
 
 int g_default_mode = CTK_MATMUL_3XTF32;
 
+// ---- optional per-launch timing of the tensor-core kernel ----
+struct TcProfile {
+    static constexpr int kMax = 8192;
+    bool on = false;
+    std::vector<cudaEvent_t> ev;  // 2 per launch, created on demand, reused
+    std::vector<double> flops;
+    int used = 0;
+};
+TcProfile g_prof;
+std::mutex g_prof_mu;
+
+// Returns the event pair for the next launch, or false when profiling is off / the record is full.
+bool prof_begin(double flops, cudaStream_t st, cudaEvent_t* stop) {
+    std::lock_guard<std::mutex> lock(g_prof_mu);
+    if (!g_prof.on || g_prof.used >= TcProfile::kMax) return false;
+    const int i = g_prof.used;
+    while (static_cast<int>(g_prof.ev.size()) < 2 * (i + 1)) {
+        cudaEvent_t e;
+        if (cudaEventCreate(&e) != cudaSuccess) return false;
+        g_prof.ev.push_back(e);
+    }
+    if (static_cast<int>(g_prof.flops.size()) <= i) g_prof.flops.resize(i + 1);
+    g_prof.flops[i] = flops;
+    g_prof.used = i + 1;
+    cudaEventRecord(g_prof.ev[2 * i], st);
+    *stop = g_prof.ev[2 * i + 1];
+    return true;
+}
+
 int resolve_mode(int mode) { return mode < 0 ? g_default_mode : mode; }
 
 // 0 = tcgen05, 1 = SIMT
@@ -571,6 +601,31 @@ size_t ctk_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k, int mode) {
 int ctk_matmul_path(const float* a, const float* b, int64_t m, int64_t n, int64_t k, int64_t sa0, int64_t sa1,
                     int64_t sb0, int64_t sb1, int mode) {
     return choose_path(a, b, m, n, k, sa0, sa1, sb0, sb1, mode, nullptr, nullptr);
+}
+
+ctk_status ctk_matmul_profile_enable(int on) {
+    std::lock_guard<std::mutex> lock(g_prof_mu);
+    g_prof.on = on != 0;
+    g_prof.used = 0;
+    return CTK_OK;
+}
+
+ctk_status ctk_matmul_profile_read(int64_t* launches, double* total_ms, double* total_flops) {
+    CTK_REQUIRE(launches && total_ms && total_flops, "ctk_matmul_profile_read: null");
+    CTK_CUDA(cudaDeviceSynchronize());
+    std::lock_guard<std::mutex> lock(g_prof_mu);
+    double ms = 0.0, fl = 0.0;
+    for (int i = 0; i < g_prof.used; ++i) {
+        float t = 0.0f;
+        CTK_CUDA(cudaEventElapsedTime(&t, g_prof.ev[2 * i], g_prof.ev[2 * i + 1]));
+        ms += t;
+        fl += g_prof.flops[i];
+    }
+    *launches = g_prof.used;
+    *total_ms = ms;
+    *total_flops = fl;
+    g_prof.used = 0;
+    return CTK_OK;
 }
 
 ctk_status ctk_matmul_status(int* status) {
@@ -647,12 +702,14 @@ ctk_status ctk_matmul_f32(const float* a, const float* b, float* c, int64_t m, i
     P.vec_store = (n % 4 == 0) && ((reinterpret_cast<uintptr_t>(c) & 15u) == 0);
     CTK_REQUIRE(static_cast<int64_t>(P.tiles_m) * P.tiles_n < (int64_t(1) << 31), "ctk_matmul_f32: too many tiles");
 
-#define CTK_TC(BN_)                                                                                 \
+ #define CTK_TC(BN_)                                                                                 \
     (terms == 3 ? tc::launch_tc_major<BN_, 3>(A.mn_major, B.mn_major, maps, P, st)                  \
                 : tc::launch_tc_major<BN_, 1>(A.mn_major, B.mn_major, maps, P, st))
-    if (bn == 256) return CTK_TC(256);
-    if (bn == 128) return CTK_TC(128);
-    return CTK_TC(64);
+    cudaEvent_t stop_ev;
+    const bool timed = prof_begin(2.0 * static_cast<double>(m) * static_cast<double>(n) * static_cast<double>(k), st, &stop_ev);
+    rc = (bn == 256) ? CTK_TC(256) : (bn == 128) ? CTK_TC(128) : CTK_TC(64);
+    if (timed) cudaEventRecord(stop_ev, st);
+    return rc;
 #undef CTK_TC
 }
 

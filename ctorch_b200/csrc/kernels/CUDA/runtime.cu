@@ -145,6 +145,18 @@ ctk_status ctk_free_host(void* p) {
     CTK_CUDA(cudaFreeHost(p));
     return CTK_OK;
 }
+ctk_status ctk_host_is_pinned(const void* p, int* is_pinned) {
+    CTK_REQUIRE(p && is_pinned, "ctk_host_is_pinned: null");
+    cudaPointerAttributes attr;
+    cudaError_t e = cudaPointerGetAttributes(&attr, p);
+    if (e != cudaSuccess) {
+        cudaGetLastError();  // plain pageable memory on old drivers: not an error for the caller
+        *is_pinned = 0;
+        return CTK_OK;
+    }
+    *is_pinned = (attr.type == cudaMemoryTypeHost) ? 1 : 0;
+    return CTK_OK;
+}
 ctk_status ctk_memcpy_h2d(void* dst, const void* src, size_t bytes, void* stream) {
     if (bytes == 0) return CTK_OK;
     CTK_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, as_stream(stream)));

@@ -92,6 +92,8 @@ ctk_status ctk_event_record(void* event, void* stream);
 ctk_status ctk_event_sync(void* event);
 ctk_status ctk_event_elapsed_ms(void* start_event, void* stop_event, float* ms);
 ctk_status ctk_stream_wait_event(void* stream, void* event);
+/* *is_pinned = 1 if host_ptr lies in page-locked (or registered) host memory. */
+ctk_status ctk_host_is_pinned(const void* host_ptr, int* is_pinned);
 /* Number of kernels this library has launched in this process (bench bookkeeping). */
 uint64_t ctk_launch_count(void);
 
@@ -213,6 +215,12 @@ ctk_status ctk_matmul_f32(const float* a, const float* b, float* c, int64_t m, i
 /* Which path the call above would take: 0 tcgen05, 1 SIMT. */
 int ctk_matmul_path(const float* a, const float* b, int64_t m, int64_t n, int64_t k,
                     int64_t sa0, int64_t sa1, int64_t sb0, int64_t sb1, int mode);
+/* Per-launch timing of the tensor-core kernel with CUDA events on the launching stream (off by
+ * default).  ctk_matmul_profile_read synchronises, returns the number of launches timed since the
+ * last enable/read, their summed duration and their summed algorithmic flops (2*m*n*k each), and
+ * clears the record.  At most 8192 launches are kept per interval. */
+ctk_status ctk_matmul_profile_enable(int on);
+ctk_status ctk_matmul_profile_read(int64_t* launches, double* total_ms, double* total_flops);
 /* Device status word of the tensor-core kernel's bounded waits: 0 = none ran out.  Reading it
  * synchronises the device. */
 ctk_status ctk_matmul_status(int* status);
