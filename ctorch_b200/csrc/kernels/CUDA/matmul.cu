@@ -582,6 +582,37 @@ int choose_path(const float* a, const float* b, int64_t m, int64_t n, int64_t k,
     return 0;
 }
 
+// ---- fixed scratch for callers that must not allocate -------------------------------------------
+// Some hosts cannot let a library allocate device memory behind their back: code running inside a
+// CUDA stream capture (an allocation there is either illegal or becomes part of the graph), services
+// that hand the whole GPU to their own arena allocator at start-up and treat any later cudaMalloc as
+// a bug, and latency-sensitive loops where a growing workspace would mean a device synchronisation
+// in the middle of a step.  For them the hi/lo split of the 3xTF32 product can live in this
+// fixed-size array, which is part of the loaded module: every GPU that loads the library holds these
+// 16 MiB (+1 KiB) until the process exits.
+constexpr size_t kStaticWorkspaceBytes = (16u << 20) + 1024;  // 4 Mi split floats + the 1 KiB alignment slack
+static __device__ __align__(256) unsigned char g_static_workspace[kStaticWorkspaceBytes];
+
+// In host code the name above is only a handle for the runtime, not an address a kernel could use:
+// the device address is looked up once per device (with that device current) and cached.
+void* g_static_workspace_ptr[64] = {nullptr};
+std::mutex g_static_workspace_mu;
+
+ctk_status static_workspace(void** out) {
+    int dev = 0;
+    CTK_CUDA(cudaGetDevice(&dev));
+    CTK_REQUIRE(dev >= 0 && dev < 64, "device ordinal out of range");
+    std::lock_guard<std::mutex> lock(g_static_workspace_mu);
+    if (!g_static_workspace_ptr[dev]) {
+        void* p = nullptr;
+        CTK_CUDA(cudaGetSymbolAddress(&p, g_static_workspace));
+        CTK_REQUIRE(p != nullptr, "cudaGetSymbolAddress returned a null address for the static workspace");
+        g_static_workspace_ptr[dev] = p;
+    }
+    *out = g_static_workspace_ptr[dev];
+    return CTK_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -711,6 +742,36 @@ ctk_status ctk_matmul_f32(const float* a, const float* b, float* c, int64_t m, i
     if (timed) cudaEventRecord(stop_ev, st);
     return rc;
 #undef CTK_TC
+}
+
+// 3xTF32 MatMul that allocates nothing: same arguments and same result as ctk_matmul_f32 in mode
+// CTK_MATMUL_3XTF32, with the hi/lo split kept in the library's fixed 16 MiB array instead of a
+// workspace that is allocated or passed in.
+//   - Operands whose split does not fit -- 2*(m*k + k*n) floats may take at most 16 MiB, which
+//     1024x1024 by 1024x1024 just reaches -- are refused with CTK_ERR_LIMIT; nothing is launched.
+//   - The first call on each device looks up the array's device address and sets the kernel's
+//     shared-memory attribute; make that first call outside any stream capture.
+//   - No byte of the array has to be zero on entry: each call writes the part it reads before it
+//     reads it, so stale contents of the previous call do not matter.
+//   - All calls on one GPU share the one array: two calls whose kernels may overlap (different
+//     streams, no ordering between them) race on it.  Order them on the GPU.
+//   - Launch timing (ctk_matmul_profile_enable) creates events on demand, so it must be off.
+ctk_status ctk_matmul_3xtf32_noalloc_f32(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
+                                         int64_t sa0, int64_t sa1, int64_t sb0, int64_t sb1, void* stream) {
+    CTK_REQUIRE(m >= 0 && n >= 0 && k >= 0, "ctk_matmul_3xtf32_noalloc_f32: negative extent");
+    const size_t need = ctk_matmul_workspace_bytes(m, n, k, CTK_MATMUL_3XTF32);
+    if (need > kStaticWorkspaceBytes)
+        return fail(CTK_ERR_LIMIT, "ctk_matmul_3xtf32_noalloc_f32: operands need " + std::to_string(need) +
+                                       " bytes of split scratch, the fixed array holds " + std::to_string(kStaticWorkspaceBytes) +
+                                       " (2*(m*k + k*n) floats may take at most 16 MiB); use ctk_matmul_f32 with a workspace instead");
+    {
+        std::lock_guard<std::mutex> lock(g_prof_mu);
+        if (g_prof.on) return fail(CTK_ERR_INVALID, "ctk_matmul_3xtf32_noalloc_f32: switch launch timing off first (it creates events)");
+    }
+    void* ws = nullptr;
+    ctk_status rc = static_workspace(&ws);
+    if (rc) return rc;
+    return ctk_matmul_f32(a, b, c, m, n, k, sa0, sa1, sb0, sb1, CTK_MATMUL_3XTF32, ws, stream);
 }
 
 }  // extern "C"

@@ -212,6 +212,16 @@ size_t ctk_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k, int mode);
 ctk_status ctk_matmul_f32(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
                           int64_t sa0, int64_t sa1, int64_t sb0, int64_t sb1, int mode,
                           void* workspace, void* stream);
+/* No counterpart in the reference.  The 3xTF32 product for callers that must not allocate device
+ * memory (inside a stream capture, under an arena allocator that owns the whole GPU, or in a loop
+ * that cannot afford a workspace growing under it): identical arguments and result to
+ * ctk_matmul_f32(..., CTK_MATMUL_3XTF32, ...), but the hi/lo split lives in a fixed 16 MiB array that
+ * is part of the library (held by every GPU that loads it).  Limit: the 2*(m*k + k*n) split floats
+ * may take at most 16 MiB (1024x1024 by 1024x1024 just fits), otherwise CTK_ERR_LIMIT and nothing runs.  The first call per device does a
+ * one-time set-up and belongs outside any stream capture; calls that may overlap on the GPU race on
+ * the shared array; launch timing must be off. */
+ctk_status ctk_matmul_3xtf32_noalloc_f32(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
+                                         int64_t sa0, int64_t sa1, int64_t sb0, int64_t sb1, void* stream);
 /* Which path the call above would take: 0 tcgen05, 1 SIMT. */
 int ctk_matmul_path(const float* a, const float* b, int64_t m, int64_t n, int64_t k,
                     int64_t sa0, int64_t sa1, int64_t sb0, int64_t sb1, int mode);
