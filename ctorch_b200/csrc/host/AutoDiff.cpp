@@ -411,23 +411,27 @@ void AutoDiff::backward(Tensor& root, Tensor grad_output) {
             auto in_it = id_to_node.find(input_id);
             if (in_it == id_to_node.end() || !in_it->second || !in_it->second->requires_grad) continue;
             Node& input_node = *in_it->second;
-            if (!input_node.grad)
-                input_node.grad = zeros_like_shape(input_node.tensor->sizes(), input_node.tensor->dtype(), input_node.tensor->device());
             bool skip = false;
             Tensor val = rule(node, input_id, input_node, skip);
             if (skip) continue;
             Tensor adjusted = check_and_adjust_grad_shape(val, input_node.tensor->sizes(), input_node.tensor->device());
-            Tensor& g = *input_node.grad;
-            if (g.device() == DeviceType::kCUDA) {
-                Tensor adj_dev = adjusted.device() == DeviceType::kCUDA ? adjusted : adjusted.to(DeviceType::kCUDA);
-                cuda_check(ctk_accumulate_f32(g.data<float>(), adj_dev.data<float>(), static_cast<int64_t>(g.numel()), current_stream()), "gradient accumulate");
+            if (adjusted.device() != input_node.tensor->device()) adjusted = adjusted.to(input_node.tensor->device());
+            if (!input_node.grad) {
+                // First contribution to a gradient that does not exist yet: the reference allocates
+                // zeros and adds (:1202-1208, :1868-1907); 0 + x is x, so the value is adopted as is
+                // (shared until someone writes) and a full zero-fill + read-modify-write pass is saved.
+                input_node.grad = std::make_unique<Tensor>(adjusted);
+            } else if (input_node.grad->device() == DeviceType::kCUDA) {
+                Tensor& acc = *input_node.grad;
+                cuda_check(ctk_accumulate_f32(acc.data<float>(), adjusted.data<float>(), static_cast<int64_t>(acc.numel()), current_stream()), "gradient accumulate");
             } else {
                 // host gradients only exist for host 0-D operands (Tensor(float) inputs)
-                Tensor adj_host = adjusted.device() == DeviceType::kCPU ? adjusted : adjusted.to(DeviceType::kCPU);
-                float* gp = g.data<float>();
-                const float* ap = adj_host.data<float>();
-                for (size_t i = 0; i < g.numel(); ++i) gp[i] += ap[i];
+                Tensor& acc = *input_node.grad;
+                float* gp = acc.data<float>();
+                const float* ap = adjusted.data<float>();
+                for (size_t i = 0; i < acc.numel(); ++i) gp[i] += ap[i];
             }
+            Tensor& g = *input_node.grad;
             if (input_node.is_leaf && on_leaf_grad) on_leaf_grad(input_id, g);
         }
     }

@@ -105,20 +105,49 @@ __device__ __forceinline__ float to_tf32_rna(float x) {
     return __uint_as_float(r);
 }
 
-// x viewed as [outer, inner] with row pitch ld -> dense hi[outer, inner], lo[outer, inner].
-__global__ void __launch_bounds__(256) split_tf32_kernel(const float* __restrict__ x, float* __restrict__ hi, float* __restrict__ lo,
-                                                         int64_t outer, int64_t inner, int64_t ld) {
-    const int64_t inner4 = inner >> 2;  // inner % 4 == 0 is a precondition of the tensor-core path
+// x viewed as [outer, inner] with row pitch ld_in -> hi, lo of shape [outer, inner] with row pitch
+// ld_out (a multiple of 4, so the copies are addressable by TMA whatever the source pitch was; pad
+// columns are never read: the tensor map's extent stays `inner`).
+// One tile of 256 x 4 vectors per CTA: with this many bytes in flight per CTA and the hardware block
+// scheduler walking memory in order, streaming kernels on B200 run above the plain-copy rate.
+constexpr int SPLIT_THREADS = 256, SPLIT_UNROLL = 4;
+__global__ void __launch_bounds__(SPLIT_THREADS) split_tf32_vec_kernel(const float* __restrict__ x, float* __restrict__ hi, float* __restrict__ lo,
+                                                                       int64_t outer, int64_t inner4, int64_t ld_in, int64_t ld_out) {
     const int64_t total = outer * inner4;
-    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        const int64_t r = i / inner4, c4 = i - r * inner4;
-        float4 v = __ldg(reinterpret_cast<const float4*>(x + r * ld) + c4);
-        float4 h, l;
-        h.x = to_tf32_rna(v.x); h.y = to_tf32_rna(v.y); h.z = to_tf32_rna(v.z); h.w = to_tf32_rna(v.w);
-        l.x = to_tf32_rna(v.x - h.x); l.y = to_tf32_rna(v.y - h.y); l.z = to_tf32_rna(v.z - h.z); l.w = to_tf32_rna(v.w - h.w);
-        reinterpret_cast<float4*>(hi + r * inner)[c4] = h;
-        reinterpret_cast<float4*>(lo + r * inner)[c4] = l;
+    const int64_t base = static_cast<int64_t>(blockIdx.x) * (SPLIT_THREADS * SPLIT_UNROLL) + threadIdx.x;
+    float4 v[SPLIT_UNROLL];
+    int64_t r[SPLIT_UNROLL], c4[SPLIT_UNROLL];
+#pragma unroll
+    for (int u = 0; u < SPLIT_UNROLL; ++u) {
+        const int64_t i = base + u * SPLIT_THREADS;
+        if (i < total) {
+            r[u] = i / inner4;
+            c4[u] = i - r[u] * inner4;
+            v[u] = __ldg(reinterpret_cast<const float4*>(x + r[u] * ld_in) + c4[u]);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < SPLIT_UNROLL; ++u) {
+        const int64_t i = base + u * SPLIT_THREADS;
+        if (i < total) {
+            float4 h, l;
+            h.x = to_tf32_rna(v[u].x); h.y = to_tf32_rna(v[u].y); h.z = to_tf32_rna(v[u].z); h.w = to_tf32_rna(v[u].w);
+            l.x = to_tf32_rna(v[u].x - h.x); l.y = to_tf32_rna(v[u].y - h.y); l.z = to_tf32_rna(v[u].z - h.z); l.w = to_tf32_rna(v[u].w - h.w);
+            reinterpret_cast<float4*>(hi + r[u] * ld_out)[c4[u]] = h;
+            reinterpret_cast<float4*>(lo + r[u] * ld_out)[c4[u]] = l;
+        }
+    }
+}
+// Any pitch, any alignment (e.g. the 10-class layer's rows of 40 bytes): one element per thread.
+__global__ void __launch_bounds__(SPLIT_THREADS) split_tf32_scalar_kernel(const float* __restrict__ x, float* __restrict__ hi, float* __restrict__ lo,
+                                                                          int64_t outer, int64_t inner, int64_t ld_in, int64_t ld_out) {
+    const int64_t total = outer * inner;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t r = i / inner, c = i - r * inner;
+        const float v = __ldg(x + r * ld_in + c);
+        const float h = to_tf32_rna(v);
+        hi[r * ld_out + c] = h;
+        lo[r * ld_out + c] = to_tf32_rna(v - h);
     }
 }
 
@@ -569,14 +598,21 @@ bool prof_begin(double flops, cudaStream_t st, cudaEvent_t* stop) {
 
 int resolve_mode(int mode) { return mode < 0 ? g_default_mode : mode; }
 
-// 0 = tcgen05, 1 = SIMT
+// 0 = tcgen05, 1 = SIMT.
+// TF32 mode reads the caller's operands in place, so both must be addressable by TMA (unit stride in
+// one dim, the other pitch a multiple of 16 bytes, 16-byte aligned base).  3xTF32 mode reads its own
+// hi/lo copies, which are laid out for TMA whatever the source pitch: a unit stride is enough, so
+// the 10-wide layer (40-byte rows) also runs on the tensor cores.
 int choose_path(const float* a, const float* b, int64_t m, int64_t n, int64_t k, int64_t sa0, int64_t sa1, int64_t sb0,
                 int64_t sb1, int mode, tc::Operand* oa, tc::Operand* ob) {
-    if (resolve_mode(mode) == CTK_MATMUL_FP32_SIMT) return 1;
+    const int md = resolve_mode(mode);
+    if (md == CTK_MATMUL_FP32_SIMT) return 1;
     tc::Operand A, B;
     if (!classify(a, m, k, sa0, sa1, &A) || !classify(b, n, k, sb1, sb0, &B)) return 1;
-    if (!tc::tma_ok(A) || !tc::tma_ok(B)) return 1;
-    if (n < 16 || k < 8) return 1;  // degenerate tiles: the tensor-core tile would be mostly padding
+    if (md == CTK_MATMUL_TF32) {
+        if (!tc::tma_ok(A) || !tc::tma_ok(B)) return 1;
+        if (n < 16 || k < 8) return 1;  // a tile of mostly padding: not worth a pass over unsplit operands
+    }
     if (oa) *oa = A;
     if (ob) *ob = B;
     return 0;
@@ -624,9 +660,15 @@ ctk_status ctk_set_matmul_mode(int mode) {
 }
 int ctk_get_matmul_mode(void) { return g_default_mode; }
 
+// Split copies have their contiguous extent padded to a multiple of 4 floats; which extent that is
+// depends on the operand's major-ness, so the larger of the two possibilities is reserved.
+static int64_t padded_elems(int64_t mn, int64_t k) {
+    const int64_t a = mn * ((k + 3) / 4 * 4), b = k * ((mn + 3) / 4 * 4);
+    return a > b ? a : b;
+}
 size_t ctk_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k, int mode) {
     if (resolve_mode(mode) != CTK_MATMUL_3XTF32) return 0;
-    return static_cast<size_t>(2 * (m * k + k * n)) * sizeof(float) + 1024;
+    return static_cast<size_t>(2 * (padded_elems(m, k) + padded_elems(n, k))) * sizeof(float) + 1024;
 }
 
 int ctk_matmul_path(const float* a, const float* b, int64_t m, int64_t n, int64_t k, int64_t sa0, int64_t sa1,
@@ -701,17 +743,28 @@ ctk_status ctk_matmul_f32(const float* a, const float* b, float* c, int64_t m, i
             if (rc) return rc;
         }
         float* w = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(ws) + 255u) & ~static_cast<uintptr_t>(255u));
+        const int64_t a_pitch = (A.inner() + 3) / 4 * 4, b_pitch = (B.inner() + 3) / 4 * 4;
         float* ah = w;
-        float* al = ah + m * k;
-        float* bh = al + m * k;
-        float* bl = bh + k * n;
-        const int grid_a = ctk_stream_grid(m * k / 4, 256, 8), grid_b = ctk_stream_grid(k * n / 4, 256, 8);
-        split_tf32_kernel<<<grid_a, 256, 0, st>>>(A.p, ah, al, A.outer(), A.inner(), A.ld);
-        CTK_LAUNCH_CHECK("split_tf32_kernel");
-        split_tf32_kernel<<<grid_b, 256, 0, st>>>(B.p, bh, bl, B.outer(), B.inner(), B.ld);
-        CTK_LAUNCH_CHECK("split_tf32_kernel");
+        float* al = ah + A.outer() * a_pitch;
+        float* bh = al + A.outer() * a_pitch;
+        float* bl = bh + B.outer() * b_pitch;
+        auto split = [&](const tc::Operand& O, float* h, float* l, int64_t pitch) -> ctk_status {
+            const bool vec = (reinterpret_cast<uintptr_t>(O.p) & 15u) == 0 && O.ld % 4 == 0 && O.inner() % 4 == 0;
+            if (vec) {
+                const int64_t total = O.outer() * (O.inner() / 4);
+                const int64_t per_cta = SPLIT_THREADS * SPLIT_UNROLL;
+                split_tf32_vec_kernel<<<static_cast<unsigned>((total + per_cta - 1) / per_cta), SPLIT_THREADS, 0, st>>>(O.p, h, l, O.outer(), O.inner() / 4, O.ld, pitch);
+            } else {
+                split_tf32_scalar_kernel<<<ctk_stream_grid(O.outer() * O.inner(), SPLIT_THREADS, 8), SPLIT_THREADS, 0, st>>>(O.p, h, l, O.outer(), O.inner(), O.ld, pitch);
+            }
+            CTK_LAUNCH_CHECK("split_tf32_kernel");
+            return CTK_OK;
+        };
+        ctk_status rc2;
+        if ((rc2 = split(A, ah, al, a_pitch))) return rc2;
+        if ((rc2 = split(B, bh, bl, b_pitch))) return rc2;
         a_hi = ah; a_lo = al; b_hi = bh; b_lo = bl;
-        a_ld = A.inner(); b_ld = B.inner();
+        a_ld = a_pitch; b_ld = b_pitch;
     }
 
     const int bn = tc::pick_bn(n);

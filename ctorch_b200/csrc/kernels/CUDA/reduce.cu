@@ -7,6 +7,7 @@
 // the tree used here is at least as accurate, which is how parity of these sums is judged.
 #include <math.h>
 
+#include "ew_skeleton.cuh"
 #include "reduce_common.cuh"
 
 namespace ctk {
@@ -71,13 +72,13 @@ __global__ void __launch_bounds__(kThreads) reduce_kernel(const float* __restric
 }
 
 // src/AutoDiff.cpp:1491-1516: (((p - t) * 2) / n) * g ;  :1602-1642: (sign(p - t) / n) * g
+// x[0] = p, x[1] = t, x[2] = upstream scalar.
 template <bool MSE>
-__global__ void __launch_bounds__(kThreads) mean_loss_bwd_kernel(const float* __restrict__ p, const float* __restrict__ t,
-                                                                 const float* __restrict__ gdev, float* __restrict__ dp,
-                                                                 int64_t n, float fn, bool vec_ok) {
-    const float g = gdev ? __ldg(gdev) : 1.0f;
-    auto one = [&](float x, float y) {
-        float d = x - y;
+struct MeanLossBwdF {
+    float fn;
+    bool use_g;
+    __device__ __forceinline__ void operator()(const float* x, float* y) const {
+        float d = x[0] - x[1];
         float c;
         if (MSE) {
             float d2 = d * 2.0f;
@@ -86,22 +87,9 @@ __global__ void __launch_bounds__(kThreads) mean_loss_bwd_kernel(const float* __
             float s = d > 0.0f ? 1.0f : (d < 0.0f ? -1.0f : 0.0f);
             c = s / fn;
         }
-        return c * g;
-    };
-    const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
-    if (vec_ok) {
-        const int64_t n4 = n >> 2;
-        for (int64_t i = tid; i < n4; i += nthreads) {
-            float4 x = __ldcs(reinterpret_cast<const float4*>(p) + i), y = __ldcs(reinterpret_cast<const float4*>(t) + i), r;
-            r.x = one(x.x, y.x); r.y = one(x.y, y.y); r.z = one(x.z, y.z); r.w = one(x.w, y.w);
-            __stcs(reinterpret_cast<float4*>(dp) + i, r);
-        }
-        for (int64_t j = (n4 << 2) + tid; j < n; j += nthreads) dp[j] = one(p[j], t[j]);
-    } else {
-        for (int64_t j = tid; j < n; j += nthreads) dp[j] = one(p[j], t[j]);
+        y[0] = c * (use_g ? x[2] : 1.0f);
     }
-}
+};
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -142,25 +130,27 @@ ctk_status ctk_mae_f32(const float* a, const float* b, int64_t n, float* out, vo
     return launch_reduce<R_MAE>("mae", a, b, n, static_cast<float>(n), out, scratch, stream);
 }
 
-ctk_status ctk_mse_backward_f32(const float* p, const float* t, const float* g, float* dp, int64_t n, void* stream) {
-    CTK_REQUIRE(n >= 0, "ctk_mse_backward_f32: negative size");
+static ctk_status mean_loss_backward(bool mse, const float* p, const float* t, const float* g, float* dp, int64_t n, void* stream) {
+    CTK_REQUIRE(n >= 0, "mean loss backward: negative size");
     if (n == 0) return CTK_OK;
-    CTK_REQUIRE(p && t && dp, "ctk_mse_backward_f32: null pointer");
-    int grid = ctk_stream_grid((n + 3) / 4, kThreads * 2, 8);
-    mean_loss_bwd_kernel<true><<<grid, kThreads, 0, ctk::as_stream(stream)>>>(p, t, g, dp, n, static_cast<float>(n),
-                                                                                aligned16(p) && aligned16(t) && aligned16(dp));
-    CTK_LAUNCH_CHECK("mse_backward");
-    return CTK_OK;
+    CTK_REQUIRE(p && t && dp, "mean loss backward: null pointer");
+    // Without an upstream scalar the third input is the prediction again, read as a broadcast
+    // scalar and ignored by the functor (use_g == false multiplies by exactly 1).
+    ctk::EwArgs<3, 1> A{};
+    A.n = n; A.inner = 1; A.out_limit[0] = n;
+    A.in[0] = p; A.in[1] = t; A.in[2] = g ? g : p;
+    A.mode[0] = A.mode[1] = ctk::EW_STREAM; A.mode[2] = ctk::EW_SCALAR;
+    A.out[0] = dp;
+    const bool use_g = g != nullptr;
+    if (mse) return ctk::ew_launch("mse_backward", A, MeanLossBwdF<true>{static_cast<float>(n), use_g}, ctk::as_stream(stream));
+    return ctk::ew_launch("mae_backward", A, MeanLossBwdF<false>{static_cast<float>(n), use_g}, ctk::as_stream(stream));
+}
+
+ctk_status ctk_mse_backward_f32(const float* p, const float* t, const float* g, float* dp, int64_t n, void* stream) {
+    return mean_loss_backward(true, p, t, g, dp, n, stream);
 }
 ctk_status ctk_mae_backward_f32(const float* p, const float* t, const float* g, float* dp, int64_t n, void* stream) {
-    CTK_REQUIRE(n >= 0, "ctk_mae_backward_f32: negative size");
-    if (n == 0) return CTK_OK;
-    CTK_REQUIRE(p && t && dp, "ctk_mae_backward_f32: null pointer");
-    int grid = ctk_stream_grid((n + 3) / 4, kThreads * 2, 8);
-    mean_loss_bwd_kernel<false><<<grid, kThreads, 0, ctk::as_stream(stream)>>>(p, t, g, dp, n, static_cast<float>(n),
-                                                                                 aligned16(p) && aligned16(t) && aligned16(dp));
-    CTK_LAUNCH_CHECK("mae_backward");
-    return CTK_OK;
+    return mean_loss_backward(false, p, t, g, dp, n, stream);
 }
 
 }  // extern "C"

@@ -88,17 +88,38 @@ def test_three_tf32_terms_reach_fp32_accuracy(cb, orc):
     _check_status(cb)
 
 
-@pytest.mark.parametrize("m,k,n,ta,tb", [(64, 128, 10, False, False), (64, 10, 128, False, True), (128, 64, 10, True, False),
-                                          (5, 7, 3, False, False), (70, 33, 65, True, True), (1, 1, 1, False, False)])
-def test_cuda_core_path_for_operands_tma_cannot_address(cb, orc, m, k, n, ta, tb):
-    """The 10-class layer: row pitches of 40 bytes.  fp32 FMA, so rel 1e-5."""
+SKINNY = [(64, 128, 10, False, False), (64, 10, 128, False, True), (128, 64, 10, True, False), (5, 7, 3, False, False),
+          (70, 33, 65, True, True), (1, 1, 1, False, False), (8192, 64, 10, False, False), (96, 2048, 10, True, False)]
+
+
+@pytest.mark.parametrize("m,k,n,ta,tb", SKINNY)
+def test_operands_tma_cannot_address_in_place(cb, orc, m, k, n, ta, tb):
+    """The 10-class layer: row pitches of 40 bytes.  3xTF32 reads its own hi/lo copies, which are
+    laid out for TMA whatever the source pitch, so these still run on the tensor cores; TF32 reads the
+    caller's operands in place and hands them to the CUDA-core kernel (fp32 FMA, rel 1e-5)."""
     A, B, _ = _mats(m, k, n, 6)
     sa = A.T.copy() if ta else A
     sb = B.T.copy() if tb else B
     dA, dB = cb.to_device(sa), cb.to_device(sb)
-    assert cb.ops.matmul_path(dA, dB, ta, tb, "3xtf32") == 1
-    assert_matmul_close(cb.ops.matmul(dA, dB, ta, tb).numpy(), orc.matmul(sa, sb, ta, tb), 1e-5, "SIMT")
-    assert_matmul_close(cb.ops.matmul(dA, dB, ta, tb, "fp32_simt").numpy(), orc.matmul(sa, sb, ta, tb), 1e-5, "SIMT forced")
+    ref = orc.matmul(sa, sb, ta, tb)
+    assert cb.ops.matmul_path(dA, dB, ta, tb, "3xtf32") == 0
+    assert_matmul_close(cb.ops.matmul(dA, dB, ta, tb, "3xtf32").numpy(), ref, 1e-4, "3xTF32 through padded split copies")
+    assert cb.ops.matmul_path(dA, dB, ta, tb, "tf32") == 1
+    assert_matmul_close(cb.ops.matmul(dA, dB, ta, tb, "tf32").numpy(), ref, 1e-5, "CUDA cores (TF32 mode, not TMA-addressable)")
+    assert_matmul_close(cb.ops.matmul(dA, dB, ta, tb, "fp32_simt").numpy(), ref, 1e-5, "CUDA cores forced")
+    _check_status(cb)
+
+
+def test_unaligned_base_pointers(cb, orc):
+    """Operands that start 4 bytes into an allocation: no 16-byte alignment anywhere."""
+    A, B, _ = _mats(130, 72, 40, 7)
+    bufA = cb.to_device(np.concatenate([[0], A.ravel()]).astype(np.float32))
+    bufB = cb.to_device(np.concatenate([[0], B.ravel()]).astype(np.float32))
+    vA, vB = bufA.view(1, (130, 72)), bufB.view(1, (72, 40))
+    ref = orc.matmul(A, B)
+    assert_matmul_close(cb.ops.matmul(vA, vB, mode="3xtf32").numpy(), ref, 1e-4, "3xTF32, unaligned operands")
+    assert_matmul_close(cb.ops.matmul(vA, vB, mode="tf32").numpy(), ref, 1e-5, "TF32 mode falls to CUDA cores")
+    _check_status(cb)
 
 
 def test_degenerate_extents(cb):
