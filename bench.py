@@ -62,7 +62,8 @@ def make_params(seed=42):
 
 
 def make_batch(rank, rows=BATCH, seed=1234):
-    rng = np.random.default_rng(seed + 1000 * rank)
+    from ctorch_b200.dp import shard_seed
+    rng = np.random.default_rng(shard_seed(seed, rank))
     x = rng.integers(0, 256, (rows, DIMS[0])).astype(np.float32) / np.float32(255.0)
     labels = rng.integers(0, DIMS[-1], rows).astype(np.float32)
     return x, labels
@@ -186,7 +187,8 @@ def host_cpu():
 # ------------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------------
-def run_mlp(args, rank, world, local_rank, dist):
+def run_mlp(args, cp):
+    rank, world, local_rank = cp.rank, cp.world, cp.local_rank
     import ctorch_b200 as cb
     from ctorch_b200 import frontend as F
     from ctorch_b200.device import PinnedArray
@@ -196,14 +198,8 @@ def run_mlp(args, rank, world, local_rank, dist):
 
     comm = None
     if world > 1:
-        import torch
-        idbuf = np.zeros(128, np.uint8)
-        if rank == 0:
-            cb.check(cb.lib.ctk_comm_unique_id(idbuf.ctypes.data_as(ctypes.c_void_p)))
-        t = torch.from_numpy(idbuf)
-        dist.broadcast(t, src=0)
-        comm = ctypes.c_void_p()
-        cb.check(cb.lib.ctk_comm_init_rank(ctypes.byref(comm), idbuf.ctypes.data_as(ctypes.c_void_p), world, rank))
+        from ctorch_b200 import dp
+        comm = dp.make_comm(cb, cp)
 
     params = make_params()
     x, labels = make_batch(rank)
@@ -219,16 +215,9 @@ def run_mlp(args, rank, world, local_rank, dist):
 
     def barrier():
         cb.synchronize()
-        if world > 1:
-            dist.barrier()
+        cp.barrier()
 
-    def max_over_ranks(v):
-        if world == 1:
-            return v
-        import torch
-        t = torch.tensor([v], dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t[0])
+    max_over_ranks = cp.max_over_ranks
 
     def timed(step_fn, profile):
         for _ in range(args.warmup):
@@ -498,20 +487,14 @@ def main():
             run_single_op(args)
         return
 
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ.setdefault("MASTER_PORT", "29500")
-        # control plane only (barrier, id broadcast, max over ranks); gradients travel over the
-        # library's own NCCL communicator
-        dist.init_process_group(backend="gloo", rank=rank, world_size=world)
+    # control plane only (barrier, id broadcast, max over ranks) over gloo; gradients travel over the
+    # library's own NCCL communicator
+    from ctorch_b200 import dp
+    cp = dp.ControlPlane(rank, world)
     try:
-        run_mlp(args, rank, world, local_rank, dist)
+        run_mlp(args, cp)
     finally:
-        if dist is not None:
-            dist.barrier()
-            dist.destroy_process_group()
+        cp.close()
 
 
 if __name__ == "__main__":

@@ -5,7 +5,7 @@
 // 1702-1704, 1808-1810, where B^T / A^T are stride-swapped views) are one entry point.
 //
 // Tensor-core path (the product): a persistent, warp-specialised tcgen05 kernel.
-//   warp 0     : TMA producer -- cp.async.bulk.tensor (no multicast) into 128B-swizzled shared
+//   warp 0     : TMA producer -- plain per-CTA cp.async.bulk.tensor loads into 128B-swizzled shared
 //                memory, a ring of stages guarded by full/empty mbarriers;
 //   warp 1     : MMA issuer -- one elected lane issues tcgen05.mma.kind::tf32 (M=128, N=BN, K=8)
 //                from shared-memory descriptors into a TMEM accumulator, tcgen05.commit frees the

@@ -1,0 +1,77 @@
+"""Control plane of the data-parallel run: one process per GPU, launched by torchrun.
+
+Gradients travel over the library's own NCCL communicator (ctk_comm_*); this module only carries the
+128-byte NCCL id, barriers and small host-side reductions, over torch.distributed with the gloo
+backend, and decides which rows a rank owns.
+"""
+import os
+
+import numpy as np
+
+
+class ControlPlane:
+    def __init__(self, rank=None, world=None, init=True):
+        self.rank = int(os.environ.get("RANK", "0")) if rank is None else rank
+        self.world = int(os.environ.get("WORLD_SIZE", "1")) if world is None else world
+        self.local_rank = int(os.environ.get("LOCAL_RANK", str(self.rank)))
+        self.dist = None
+        if self.world > 1 and init:
+            import torch.distributed as dist
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            os.environ.setdefault("MASTER_PORT", "29500")
+            if not dist.is_initialized():
+                dist.init_process_group(backend="gloo", rank=self.rank, world_size=self.world)
+            self.dist = dist
+
+    def barrier(self):
+        if self.dist is not None:
+            self.dist.barrier()
+
+    def broadcast_bytes(self, buf, src=0):
+        """buf: a numpy uint8 array, filled on `src`; returns it filled on every rank."""
+        if self.dist is None:
+            return buf
+        import torch
+        t = torch.from_numpy(buf)
+        self.dist.broadcast(t, src=src)
+        return buf
+
+    def max_over_ranks(self, value):
+        if self.dist is None:
+            return float(value)
+        import torch
+        t = torch.tensor([float(value)], dtype=torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t[0])
+
+    def sum_over_ranks(self, array):
+        """Element-wise sum of a float32 numpy array over ranks (host side; used by tests)."""
+        if self.dist is None:
+            return array
+        import torch
+        t = torch.from_numpy(np.ascontiguousarray(array, dtype=np.float32).copy())
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
+        return t.numpy()
+
+    def close(self):
+        if self.dist is not None:
+            self.dist.barrier()
+            self.dist.destroy_process_group()
+            self.dist = None
+
+
+def shard_seed(base_seed, rank):
+    """Each rank draws its own rows: weak scaling, a different data seed per rank."""
+    return base_seed + 1000 * rank
+
+
+def make_comm(cb, cp):
+    """Creates the NCCL communicator of this rank (ctk_comm_init_rank) from an id made on rank 0."""
+    import ctypes
+    idbuf = np.zeros(128, np.uint8)
+    if cp.rank == 0:
+        cb.check(cb.lib.ctk_comm_unique_id(idbuf.ctypes.data_as(ctypes.c_void_p)))
+    cp.broadcast_bytes(idbuf, 0)
+    comm = ctypes.c_void_p()
+    cb.check(cb.lib.ctk_comm_init_rank(ctypes.byref(comm), idbuf.ctypes.data_as(ctypes.c_void_p), cp.world, cp.rank))
+    return comm
