@@ -30,14 +30,26 @@ struct EwArgs {
     int64_t inner;            // period of EW_ROW inputs
 };
 
-template <int NIN, int NOUT, class F>
+// MODES packs the indexing mode of input k in bits [2k, 2k+2): a compile-time constant, so a kernel
+// carries only the address arithmetic it needs (with run-time modes the compiler kept the 64-bit
+// modulo of the row mode on every path, and the one-stream broadcast forms ran at 5.0 TB/s instead
+// of 6.9).
+template <int NIN, int NOUT, class F, int MODES>
 __global__ void __launch_bounds__(kEwThreads) ew_vec_kernel(EwArgs<NIN, NOUT> A, F f) {
     const int64_t n4 = A.n >> 2;
     const int64_t base = static_cast<int64_t>(blockIdx.x) * kEwTile + threadIdx.x;
     float4 v[NIN > 0 ? NIN : 1][kEwUnroll];
     float s[NIN > 0 ? NIN : 1];
+    bool any_row = false;
 #pragma unroll
-    for (int k = 0; k < NIN; ++k) s[k] = (A.mode[k] == EW_SCALAR) ? __ldg(A.in[k]) : 0.0f;
+    for (int k = 0; k < NIN; ++k) {
+        const int mode = (MODES >> (2 * k)) & 3;
+        s[k] = (mode == EW_SCALAR) ? __ldg(A.in[k]) : 0.0f;
+        any_row |= (mode == EW_ROW);
+    }
+    // position of this thread's first vector inside the row period (one 64-bit modulo per thread)
+    const uint32_t inner32 = static_cast<uint32_t>(A.inner);
+    const uint32_t row0 = any_row ? static_cast<uint32_t>((base << 2) % A.inner) : 0u;
     // phase 1: every load of the tile
 #pragma unroll
     for (int u = 0; u < kEwUnroll; ++u) {
@@ -45,8 +57,9 @@ __global__ void __launch_bounds__(kEwThreads) ew_vec_kernel(EwArgs<NIN, NOUT> A,
         if (i4 < n4) {
 #pragma unroll
             for (int k = 0; k < NIN; ++k) {
-                if (A.mode[k] == EW_STREAM) v[k][u] = __ldcs(reinterpret_cast<const float4*>(A.in[k]) + i4);
-                else if (A.mode[k] == EW_ROW) v[k][u] = __ldg(reinterpret_cast<const float4*>(A.in[k] + ((i4 << 2) % A.inner)));
+                const int mode = (MODES >> (2 * k)) & 3;
+                if (mode == EW_STREAM) v[k][u] = __ldcs(reinterpret_cast<const float4*>(A.in[k]) + i4);
+                else if (mode == EW_ROW) v[k][u] = __ldg(reinterpret_cast<const float4*>(A.in[k] + (row0 + static_cast<uint32_t>(u * kEwThreads * 4)) % inner32));
                 else v[k][u] = make_float4(s[k], s[k], s[k], s[k]);
             }
         }
@@ -85,8 +98,10 @@ __global__ void __launch_bounds__(kEwThreads) ew_vec_kernel(EwArgs<NIN, NOUT> A,
         if (i < A.n) {
             float x[NIN > 0 ? NIN : 1], y[NOUT];
 #pragma unroll
-            for (int k = 0; k < NIN; ++k)
-                x[k] = (A.mode[k] == EW_STREAM) ? A.in[k][i] : (A.mode[k] == EW_ROW) ? __ldg(A.in[k] + (i % A.inner)) : s[k];
+            for (int k = 0; k < NIN; ++k) {
+                const int mode = (MODES >> (2 * k)) & 3;
+                x[k] = (mode == EW_STREAM) ? A.in[k][i] : (mode == EW_ROW) ? __ldg(A.in[k] + (i % A.inner)) : s[k];
+            }
             f(x, y);
 #pragma unroll
             for (int k = 0; k < NOUT; ++k)
@@ -126,12 +141,28 @@ ctk_status ew_launch(const char* name, EwArgs<NIN, NOUT> A, F f, cudaStream_t st
     }
     for (int k = 0; k < NOUT; ++k)
         if (A.out[k] && !ew_aligned16(A.out[k])) vec = false;
+    // Instantiated mode patterns: all inputs streamed; the LAST input a broadcast scalar or a row
+    // (the second operand of a binary op, the upstream scalar of a loss gradient, the source of a
+    // fill / tile); the FIRST input a broadcast scalar (0-D left operand).  Anything else takes the
+    // element-wise kernel.
+    int packed = 0;
+    for (int k = 0; k < NIN; ++k) packed |= (A.mode[k] & 3) << (2 * k);
+    constexpr int kLast = NIN > 0 ? 2 * (NIN - 1) : 0;
+    constexpr int kLastScalar = NIN > 0 ? (EW_SCALAR << kLast) : -1;
+    constexpr int kLastRow = NIN > 0 ? (EW_ROW << kLast) : -2;
+    constexpr int kFirstScalar = NIN > 1 ? EW_SCALAR : -3;
+    if (vec && A.inner >= (int64_t(1) << 31)) vec = false;
+    if (vec && packed != 0 && packed != kLastScalar && packed != kLastRow && packed != kFirstScalar) vec = false;
     if (vec) {
         const int64_t n4 = A.n >> 2;
         int64_t grid = (n4 + kEwTile - 1) / kEwTile;
         if (grid < 1) grid = 1;
         CTK_REQUIRE(grid < (int64_t(1) << 31), "elementwise kernel: too many elements for one launch");
-        ew_vec_kernel<NIN, NOUT, F><<<static_cast<unsigned>(grid), kEwThreads, 0, st>>>(A, f);
+        const unsigned g = static_cast<unsigned>(grid);
+        if (packed == 0) ew_vec_kernel<NIN, NOUT, F, 0><<<g, kEwThreads, 0, st>>>(A, f);
+        else if (packed == kLastScalar) ew_vec_kernel<NIN, NOUT, F, (NIN > 0 ? (EW_SCALAR << kLast) : 0)><<<g, kEwThreads, 0, st>>>(A, f);
+        else if (packed == kLastRow) ew_vec_kernel<NIN, NOUT, F, (NIN > 0 ? (EW_ROW << kLast) : 0)><<<g, kEwThreads, 0, st>>>(A, f);
+        else ew_vec_kernel<NIN, NOUT, F, (NIN > 1 ? EW_SCALAR : 0)><<<g, kEwThreads, 0, st>>>(A, f);
     } else {
         ew_scalar_kernel<NIN, NOUT, F><<<ctk_stream_grid(A.n, kEwThreads, 8), kEwThreads, 0, st>>>(A, f);
     }

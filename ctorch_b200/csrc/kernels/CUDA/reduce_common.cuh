@@ -5,7 +5,7 @@
 
 namespace ctk {
 
-constexpr int kMaxReduceBlocks = 2048;
+constexpr int kMaxReduceBlocks = 16384;
 
 // Layout of the reduction scratch: kMaxReduceBlocks per-block partial sums, then a ticket counter.
 struct ReduceScratch {
