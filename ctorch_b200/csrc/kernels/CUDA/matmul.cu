@@ -475,6 +475,293 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
     }
 }
 
+// ---- CTA-pair variant --------------------------------------------------------------------------------
+// Two CTAs of a cluster (ranks 0 and 1, on neighbouring SMs) compute one 256 x 256 tile with
+// tcgen05.mma.cta_group::2 (M=256, N=256, K=8).  Each CTA stages its own 128 rows of A and its own
+// 128 columns of B, so a 128 x 256 accumulator costs 32 KB of shared-memory fill and read per
+// k-block instead of 48 KB: the single-CTA kernel is bound by shared-memory bandwidth, this one is
+// not, and each B tile crosses L2 once per 256 rows of C instead of once per 128.
+//   * both producers load with cp.async.bulk.tensor...cta_group::2 (each CTA its own half; no
+//     load is shared between CTAs) and signal the full barrier of rank 0, whose producer posts the
+//     expected byte count of both halves;
+//   * rank 0's warp 1 issues the MMAs; tcgen05.commit signals the empty / accumulator-full
+//     barriers of both CTAs;
+//   * the epilogue warps of both CTAs read their own TMEM (lanes = their 128 rows) and arrive on
+//     rank 0's accumulator-empty barrier (count 8);
+//   * TMEM is allocated and freed with cta_group::2 by warp 1 of both CTAs; a cluster barrier after
+//     set-up and before tear-down keeps either CTA from touching a peer that is not there.
+namespace pair {
+
+constexpr int BN = 256;     // tile width of the pair
+constexpr int BN_CTA = 128; // columns of B each CTA stages
+
+template <int TERMS>
+struct Cfg {
+    static constexpr int A_BYTES = BM * BK * 4;
+    static constexpr int B_BYTES = BN_CTA * BK * 4;
+    static constexpr int PARTS = (TERMS == 1) ? 1 : 2;
+    static constexpr int STAGE_BYTES = PARTS * (A_BYTES + B_BYTES);  // per CTA
+    static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+    static constexpr int TMEM_COLS = 512;  // two 256-column accumulators
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+    static_assert(STAGES >= 2, "need at least two stages");
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Address of the same shared-memory object in CTA `rank` of this cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    __syncwarp();
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+// Per-CTA load of this CTA's half; the completion bytes go to the barrier at `cluster_bar`
+// (a shared::cluster address: rank 0's full barrier).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// Arrives on the barrier at this shared-memory offset in both CTAs of the pair once the MMAs
+// issued so far have completed.
+__device__ __forceinline__ void tc_commit_both(uint32_t bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(mask) : "memory");
+}
+__device__ __forceinline__ void tc_mma_tf32_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// M = 256 across the pair.
+__host__ __device__ constexpr uint32_t make_idesc_pair(bool a_mn_major, bool b_mn_major) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
+           (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(BN >> 3) << 17) |
+           (static_cast<uint32_t>((2 * BM) >> 4) << 24);
+}
+
+// P.tiles_m / P.tiles_n count 256 x 256 tiles.  Grid = 2 x number of resident clusters.
+template <int TERMS, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(THREADS, 1)
+tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+                           const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+                           const Params P) {
+    using C = Cfg<TERMS>;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t bars[2 * 8 + 4];  // full[8], empty[8], tmem_full[2], tmem_empty[2]
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile int abort_flag;
+
+    const uint32_t rank = cluster_ctarank();      // 0 = issues the MMAs
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar0 = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (8 + s); };
+    auto tfull_bar = [&](int a) { return bar0 + 8u * (16 + a); };
+    auto tempty_bar = [&](int a) { return bar0 + 8u * (18 + a); };
+    auto a_addr = [&](int s, int part) { return smem_base + s * C::STAGE_BYTES + part * C::A_BYTES; };
+    auto b_addr = [&](int s, int part) { return smem_base + s * C::STAGE_BYTES + C::PARTS * C::A_BYTES + part * C::B_BYTES; };
+    const uint32_t peer_abort = map_to_cta(smem_u32(const_cast<int*>(&abort_flag)), rank ^ 1u);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 8); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        prefetch_tmap(&map_a_hi);
+        prefetch_tmap(&map_b_hi);
+        if (TERMS == 3) { prefetch_tmap(&map_a_lo); prefetch_tmap(&map_b_lo); }
+    }
+    if (warp == 1) {
+        tmem_alloc2(smem_u32(&tmem_base_slot), C::TMEM_COLS);
+        tmem_relinquish2();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // the peer's barriers exist before anything is signalled across
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    const int num_tiles = P.tiles_m * P.tiles_n;
+    const int first_tile = blockIdx.x >> 1, tile_step = gridDim.x >> 1;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer (both CTAs) ------------------------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t issued = 0;
+            bool ok = true;
+            for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+                const int m0 = (tile / P.tiles_n) * (2 * BM) + static_cast<int>(rank) * BM;
+                const int n0 = (tile % P.tiles_n) * BN + static_cast<int>(rank) * BN_CTA;
+                for (int kb = 0; kb < P.num_kb; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, &abort_flag, 0x500 | stage)) { ok = false; break; }
+                    if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * C::STAGE_BYTES);
+                    const uint32_t fb = map_to_cta(full_bar(stage), 0);
+                    const int k0 = kb * BK;
+#pragma unroll
+                    for (int part = 0; part < C::PARTS; ++part) {
+                        const CUtensorMap* ma = part ? &map_a_lo : &map_a_hi;
+                        const CUtensorMap* mb = part ? &map_b_lo : &map_b_hi;
+                        if (A_MN) {
+#pragma unroll
+                            for (int g = 0; g < BM / 32; ++g) tma_load_2d_pair(a_addr(stage, part) + g * 4096, ma, fb, m0 + 32 * g, k0);
+                        } else {
+                            tma_load_2d_pair(a_addr(stage, part), ma, fb, k0, m0);
+                        }
+                        if (B_MN) {
+#pragma unroll
+                            for (int g = 0; g < BN_CTA / 32; ++g) tma_load_2d_pair(b_addr(stage, part) + g * 4096, mb, fb, n0 + 32 * g, k0);
+                        } else {
+                            tma_load_2d_pair(b_addr(stage, part), mb, fb, k0, n0);
+                        }
+                    }
+                    ++issued;
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (ok) {
+                // Tail: every stage this CTA filled has been released, i.e. the MMAs that read it are
+                // done and no arrival on this CTA's empty barriers is still on its way.
+                const uint32_t pending = issued < static_cast<uint32_t>(C::STAGES) ? issued : C::STAGES;
+                for (uint32_t i = 0; i < pending && ok; ++i) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1u, &abort_flag, 0x580 | stage)) ok = false;
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) {
+                // Gave up.  The completion of this CTA's copies is counted on rank 0's barriers, so
+                // there is nothing local to wait on: give the copies in flight a bounded ~2 ms to land.
+                st_cluster_u32(peer_abort, 1u);
+                for (int i = 0; i < 2048; ++i) __nanosleep(1000);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer (rank 0 only) ------------------------------
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = make_idesc_pair(A_MN, B_MN);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, &abort_flag, 0x600 | (18 + acc))) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+                for (int kb = 0; kb < P.num_kb; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase, &abort_flag, 0x600 | stage)) { ok = false; break; }
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+                        const uint32_t a_step = A_MN ? ks * 1024u : ks * 32u;
+                        const uint32_t b_step = B_MN ? ks * 1024u : ks * 32u;
+                        const uint32_t a_lbo = A_MN ? 4096u : 0u, b_lbo = B_MN ? 4096u : 0u;
+                        const uint32_t a_sbo = A_MN ? 512u : 1024u, b_sbo = B_MN ? 512u : 1024u;
+                        const uint32_t a_sw = A_MN ? kSwizzle128BAtom32B : kSwizzle128B, b_sw = B_MN ? kSwizzle128BAtom32B : kSwizzle128B;
+                        const uint64_t a_hi = make_desc(a_addr(stage, 0) + a_step, a_lbo, a_sbo, a_sw);
+                        const uint64_t b_hi = make_desc(b_addr(stage, 0) + b_step, b_lbo, b_sbo, b_sw);
+                        const uint32_t first = (kb > 0 || ks > 0) ? 1u : 0u;
+                        if (TERMS == 3) {
+                            const uint64_t a_lo = make_desc(a_addr(stage, 1) + a_step, a_lbo, a_sbo, a_sw);
+                            const uint64_t b_lo = make_desc(b_addr(stage, 1) + b_step, b_lbo, b_sbo, b_sw);
+                            tc_mma_tf32_pair(d_tmem, a_lo, b_hi, idesc, first);  // small terms first
+                            tc_mma_tf32_pair(d_tmem, a_hi, b_lo, idesc, 1u);
+                            tc_mma_tf32_pair(d_tmem, a_hi, b_hi, idesc, 1u);
+                        } else {
+                            tc_mma_tf32_pair(d_tmem, a_hi, b_hi, idesc, first);
+                        }
+                    }
+                    tc_commit_both(empty_bar(stage));  // both CTAs' stage is free once these MMAs have read it
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                tc_commit_both(tfull_bar(acc));        // accumulator complete, in both CTAs' TMEM
+                if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            }
+            if (!ok) st_cluster_u32(peer_abort, 1u);
+        }
+    } else {
+        // ------------------------------ epilogue (both CTAs) ------------------------------
+        const int quarter = warp & 3;
+        const uint32_t tempty0 = map_to_cta(tempty_bar(0), 0), tempty1 = map_to_cta(tempty_bar(1), 0);
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+            const int64_t m0 = static_cast<int64_t>(tile / P.tiles_n) * (2 * BM) + static_cast<int64_t>(rank) * BM;
+            const int64_t n0 = static_cast<int64_t>(tile % P.tiles_n) * BN;
+            if (!mbar_wait(tfull_bar(acc), acc_phase, &abort_flag, 0x700 | (16 + acc))) { ok = false; break; }
+            tc_fence_after();
+            const int64_t row = m0 + quarter * 32 + lane;
+            float* crow = P.c + row * P.n;
+#pragma unroll 1
+            for (int cc = 0; cc < BN / 32; ++cc) {
+                uint32_t r[32];
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN + cc * 32);
+                tmem_ld32(taddr, r);
+                tmem_ld_wait();
+                const int64_t col0 = n0 + cc * 32;
+                if (row < P.m && col0 < P.n) {
+                    if (P.vec_store && col0 + 32 <= P.n) {
+#pragma unroll
+                        for (int v = 0; v < 8; ++v)
+                            __stcs(reinterpret_cast<float4*>(crow + col0) + v,
+                                   make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                               __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3])));
+                    } else {
+#pragma unroll
+                        for (int v = 0; v < 32; ++v)
+                            if (col0 + v < P.n) crow[col0 + v] = __uint_as_float(r[v]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acc ? tempty1 : tempty0);
+            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        }
+        if (!ok && lane == 0) st_cluster_u32(peer_abort, 1u);
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // neither CTA leaves (or frees TMEM) while the other may still signal it
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc2(tmem_base, C::TMEM_COLS);
+    }
+}
+
+}  // namespace pair
+
 // ---- host side -------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -555,6 +842,51 @@ ctk_status launch_tc_major(bool a_mn, bool b_mn, const CUtensorMap maps[4], cons
 
 int pick_bn(int64_t n) { return n > 128 ? 256 : (n > 64 ? 128 : 64); }
 
+// ---- CTA-pair launch ----
+// Resident clusters of two per device, asked of the driver once (the kernels differ only in code, not in resources).
+template <int TERMS, bool A_MN, bool B_MN>
+ctk_status launch_pair(const CUtensorMap maps[4], const Params& P, cudaStream_t st) {
+    using C = pair::Cfg<TERMS>;
+    auto kernel = pair::tcgen05_matmul_pair_kernel<TERMS, A_MN, B_MN>;
+    static int max_clusters[64] = {0};
+    int dev = 0;
+    CTK_CUDA(cudaGetDevice(&dev));
+    CTK_REQUIRE(dev >= 0 && dev < 64, "device ordinal out of range");
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (!max_clusters[dev]) {
+        CTK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+        cfg.gridDim = dim3(2 * static_cast<unsigned>(ctk::sm_count()));
+        int n = 0;
+        CTK_CUDA(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
+        CTK_REQUIRE(n > 0, "the device cannot hold a cluster of two CTAs of the MatMul kernel");
+        max_clusters[dev] = n;
+    }
+    const int tiles = P.tiles_m * P.tiles_n;
+    const int clusters = tiles < max_clusters[dev] ? tiles : max_clusters[dev];
+    cfg.gridDim = dim3(2 * static_cast<unsigned>(clusters));
+    CTK_CUDA(cudaLaunchKernelEx(&cfg, kernel, maps[0], maps[1], maps[2], maps[3], P));
+    CTK_LAUNCH_CHECK("tcgen05_matmul_pair_kernel");
+    return CTK_OK;
+}
+
+template <int TERMS>
+ctk_status launch_pair_major(bool a_mn, bool b_mn, const CUtensorMap maps[4], const Params& P, cudaStream_t st) {
+    if (a_mn && b_mn) return launch_pair<TERMS, true, true>(maps, P, st);
+    if (a_mn) return launch_pair<TERMS, true, false>(maps, P, st);
+    if (b_mn) return launch_pair<TERMS, false, true>(maps, P, st);
+    return launch_pair<TERMS, false, false>(maps, P, st);
+}
+
 }  // namespace tc
 
 // Classifies one operand: returns false if neither stride is 1.
@@ -566,6 +898,7 @@ bool classify(const float* p, int64_t mn, int64_t k, int64_t s_mn, int64_t s_k, 
 }
 
 int g_default_mode = CTK_MATMUL_3XTF32;
+int g_pairing = 0;  // 0: CTA pairs where the shape allows, 1: single-CTA kernel only
 
 // ---- optional per-launch timing of the tensor-core kernel ----
 struct TcProfile {
@@ -659,6 +992,12 @@ ctk_status ctk_set_matmul_mode(int mode) {
     return CTK_OK;
 }
 int ctk_get_matmul_mode(void) { return g_default_mode; }
+
+ctk_status ctk_set_matmul_pairing(int pairing) {
+    CTK_REQUIRE(pairing == 0 || pairing == 1, "ctk_set_matmul_pairing: 0 (CTA pairs where possible) or 1 (single-CTA kernel only)");
+    g_pairing = pairing;
+    return CTK_OK;
+}
 
 // Split copies have their contiguous extent padded to a multiple of 4 floats; which extent that is
 // depends on the operand's major-ness, so the larger of the two possibilities is reserved.
@@ -768,9 +1107,11 @@ ctk_status ctk_matmul_f32(const float* a, const float* b, float* c, int64_t m, i
     }
 
     const int bn = tc::pick_bn(n);
+    // Two CTAs per 256 x 256 tile once there is more than one 128-row block to pair up.
+    const bool paired = (g_pairing == 0) && bn == 256 && m > tc::BM;
     CUtensorMap maps[4];
     const int a_box = A.mn_major ? tc::BK : tc::BM;
-    const int b_box = B.mn_major ? tc::BK : bn;
+    const int b_box = B.mn_major ? tc::BK : (paired ? tc::pair::BN_CTA : bn);
     ctk_status rc;
     if ((rc = tc::make_map(&maps[0], a_hi, A.inner(), A.outer(), a_ld, a_box, A.mn_major))) return rc;
     if ((rc = tc::make_map(&maps[1], a_lo, A.inner(), A.outer(), a_ld, a_box, A.mn_major))) return rc;
@@ -779,7 +1120,8 @@ ctk_status ctk_matmul_f32(const float* a, const float* b, float* c, int64_t m, i
 
     tc::Params P;
     P.m = m; P.n = n; P.k = k;
-    P.tiles_m = static_cast<int>((m + tc::BM - 1) / tc::BM);
+    const int tile_m = paired ? 2 * tc::BM : tc::BM;
+    P.tiles_m = static_cast<int>((m + tile_m - 1) / tile_m);
     P.tiles_n = static_cast<int>((n + bn - 1) / bn);
     P.num_kb = static_cast<int>((k + tc::BK - 1) / tc::BK);
     P.c = c;
@@ -791,7 +1133,10 @@ ctk_status ctk_matmul_f32(const float* a, const float* b, float* c, int64_t m, i
                 : tc::launch_tc_major<BN_, 1>(A.mn_major, B.mn_major, maps, P, st))
     cudaEvent_t stop_ev;
     const bool timed = prof_begin(2.0 * static_cast<double>(m) * static_cast<double>(n) * static_cast<double>(k), st, &stop_ev);
-    rc = (bn == 256) ? CTK_TC(256) : (bn == 128) ? CTK_TC(128) : CTK_TC(64);
+    if (paired)
+        rc = terms == 3 ? tc::launch_pair_major<3>(A.mn_major, B.mn_major, maps, P, st) : tc::launch_pair_major<1>(A.mn_major, B.mn_major, maps, P, st);
+    else
+        rc = (bn == 256) ? CTK_TC(256) : (bn == 128) ? CTK_TC(128) : CTK_TC(64);
     if (timed) cudaEventRecord(stop_ev, st);
     return rc;
 #undef CTK_TC

@@ -208,6 +208,11 @@ ctk_status ctk_ce_fused_index_f32(const float* logits, const float* labels, int6
 /* ------------------------------------------------------------------------------------------- */
 ctk_status ctk_set_matmul_mode(int mode);
 int ctk_get_matmul_mode(void);
+/* Tile scheduling of the tensor-core path (no counterpart in the reference): 0 (default) computes   */
+/* 256 x 256 tiles on pairs of CTAs (tcgen05 cta_group::2) whenever m > 128 and n > 128, 1 keeps     */
+/* every product on the single-CTA kernel.  Both kernels accumulate k in the same order in fp32   */
+/* TMEM, so the result does not depend on the choice.                                              */
+ctk_status ctk_set_matmul_pairing(int pairing);
 size_t ctk_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k, int mode);
 ctk_status ctk_matmul_f32(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
                           int64_t sa0, int64_t sa1, int64_t sb0, int64_t sb1, int mode,

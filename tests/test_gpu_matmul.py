@@ -75,6 +75,33 @@ def test_persistent_scheduler_many_tiles(cb, orc):
         assert_matmul_close(C, ref64, TOL[mode] * 1.5, mode + " all tiles vs fp64")
 
 
+@pytest.mark.parametrize("mode", ["tf32", "3xtf32"])
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+def test_cta_pair_kernel_agrees_with_single_cta_kernel(cb, orc, mode, ta, tb):
+    """The 256 x 256 CTA-pair kernel (default when m > 128 and n > 128) against the single-CTA kernel
+    on the same operands: odd tile counts, ragged M/N/K, enough tiles that clusters loop and both
+    accumulators are used; then both against the fp64 product and sampled oracle rows."""
+    m, k, n = 2 * 256 * 5 + 130, 232, 256 * 17 + 72
+    A, B, _ = _mats(m, k, n, 11)
+    sa = A.T.copy() if ta else A
+    sb = B.T.copy() if tb else B
+    dA, dB = cb.to_device(sa), cb.to_device(sb)
+    try:
+        cb.ops.set_matmul_pairing(1)
+        single = cb.ops.matmul(dA, dB, ta, tb, mode).numpy()
+        cb.ops.set_matmul_pairing(0)
+        paired = cb.ops.matmul(dA, dB, ta, tb, mode).numpy()
+    finally:
+        cb.ops.set_matmul_pairing(0)
+    _check_status(cb)
+    ref64 = A.astype(np.float64) @ B.astype(np.float64)
+    assert_matmul_close(paired, ref64, TOL[mode] * 1.5, f"pair kernel vs fp64 {mode} ta={ta} tb={tb}")
+    assert_matmul_close(single, ref64, TOL[mode] * 1.5, f"single-CTA kernel vs fp64 {mode} ta={ta} tb={tb}")
+    assert_matmul_close(paired, single, 1e-6, "pair vs single-CTA kernel")
+    rows = np.asarray([0, 127, 128, 255, 256, m - 1])
+    assert_matmul_close(paired[rows], orc.matmul_rows(A, B, rows), TOL[mode], "sampled oracle rows")
+
+
 def test_three_tf32_terms_reach_fp32_accuracy(cb, orc):
     """K = 4096, N(0,1): 3xTF32 must sit with the fp32 recurrence, TF32 visibly must not need to."""
     m, k, n = 128, 4096, 256
