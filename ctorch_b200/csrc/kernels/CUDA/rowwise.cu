@@ -2,13 +2,15 @@
 //
 // HBM-bound.  Each row is read from HBM once and kept on chip while its max, exp-sum and outputs
 // are computed:
-//   cols <= 128  : a group of G <= 32 lanes owns a row, values live in registers, reductions are
-//                  warp shuffles (G = 8/16/32 so several short rows share a warp);
+//   cols <= 16   : a thread owns a row; a CTA moves its 256 rows between HBM and shared memory as one
+//                  contiguous block with coalesced 128-bit accesses (the 10-class layer);
+//   cols <= 128  : a warp owns a row, values live in registers, reductions are warp shuffles;
 //   cols <= 4096 : a CTA of 128/256 threads owns a row in registers (128-bit loads), reductions by
 //                  shuffle + one shared-memory hop, many CTAs per SM;
-//   cols <= 32K  : a CTA of 512 threads owns a row in registers while the NEXT row is already being
-//                  fetched into shared memory by a bulk asynchronous copy (cp.async.bulk + mbarrier),
-//                  so HBM reads overlap the arithmetic and the stores of the current row;
+//   cols <= 32K  : one CTA per SM; a producer warp streams this CTA's rows through a 208 KiB ring of
+//                  shared memory with bulk asynchronous copies (cp.async.bulk + mbarriers) and runs
+//                  more than a row ahead, 512 consumer threads keep the current row in registers,
+//                  so HBM reads never stop for the arithmetic and the stores of the current row;
 //   otherwise    : (rows that are not 16-byte aligned, or longer) a CTA stages the row in shared
 //                  memory with plain loads, or re-reads it from L2.
 // exp() is evaluated once per element and kept; it is ex2.approx((x - max) * log2 e) and the
@@ -31,9 +33,9 @@
 namespace {
 using namespace ctk;
 
-constexpr int kRegThreads = 256;   // register-row kernels: 8 warps per CTA
 constexpr int kRowThreads = 512;   // CTA-per-row kernels
 constexpr int kSmemRowMaxCols = 48 * 1024;
+constexpr int kConsumers = 512;    // consumer threads of the streamed long-row kernel
 
 enum { ALG_SOFTMAX = 0, ALG_SOFTMAX_BWD = 1, ALG_CE_ONEHOT = 2, ALG_CE_INDEX = 3, ALG_CE_BWD = 4, ALG_CE_FUSED = 5 };
 
@@ -53,62 +55,169 @@ __device__ __forceinline__ float fast_exp(float x) {
     return y;
 }
 
-// ---- group reductions over G lanes of a warp -------------------------------------------------
-template <int G>
-__device__ __forceinline__ float group_max(float v) {
-#pragma unroll
-    for (int o = G / 2; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-    return v;
-}
-template <int G>
-__device__ __forceinline__ float group_sum(float v) {
-#pragma unroll
-    for (int o = G / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
-
 // ---- row holders -----------------------------------------------------------------------------
-// The three holders expose the same interface: load(row), rmax(), rsum(partial), and
-// each(f) / update(f) over the elements this thread owns.
-template <int G, int ITEMS>
-struct RegRow {
+// Every holder exposes: load(src), rmax(), rsum(partial), each(f) / update(f) / store(out, f) over
+// the elements this thread owns, each2 / store2 that also hand f the matching element of a second
+// operand row, and pick(c, w) -- whether this thread owns element c, and its value.
+
+// Cross-warp reductions for a CTA (or the consumer threads of one): one barrier per reduction, the
+// scratch alternates between two halves so a slow reader of the previous result is never overwritten.
+struct CtaReducer {
+    float* red;   // 64 floats of shared memory
+    int flip;
+    bool named;   // true: barrier 1 over kStreamConsumers threads; false: __syncthreads
+    __device__ __forceinline__ void sync() const {
+        if (named) asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory");
+        else __syncthreads();
+    }
+    template <bool IS_MAX>
+    __device__ __forceinline__ float run(float v, int nwarps) {
+        v = IS_MAX ? warp_max(v) : warp_sum(v);
+        float* buf = red + 32 * flip;
+        flip ^= 1;
+        const int lane = threadIdx.x & 31;
+        if (lane == 0) buf[threadIdx.x >> 5] = v;
+        sync();
+        float t = lane < nwarps ? buf[lane] : (IS_MAX ? -INFINITY : 0.0f);
+        return IS_MAX ? warp_max(t) : warp_sum(t);
+    }
+};
+
+// Elements of one row held in registers by a group of LANES threads (a warp, or all threads of a
+// CTA).  VEC: member t holds the 128-bit vectors t, t + LANES, ... (cols % 4 == 0, 16-byte aligned
+// rows); otherwise the elements t, t + LANES, ...  Guards are per vector and in 32-bit arithmetic:
+// the per-element index arithmetic is what otherwise makes these kernels issue-bound.
+template <int LANES, int ITEMS, bool VEC>
+struct StridedRow {
+    static_assert(!VEC || ITEMS % 4 == 0, "vector form holds whole vectors");
     static constexpr bool kCached = true;
+    static constexpr int kSteps = VEC ? ITEMS / 4 : ITEMS;
     float v[ITEMS];
-    int lane;
-    int64_t cols;
-    __device__ __forceinline__ void load(const float* __restrict__ row) {
+    int cols;
+    int t;
+    __device__ __forceinline__ int first(int s) const { return VEC ? (t + s * LANES) << 2 : t + s * LANES; }
+    __device__ __forceinline__ void load(const float* __restrict__ src) {
 #pragma unroll
-        for (int it = 0; it < ITEMS; ++it) {
-            int64_t j = lane + it * G;
-            v[it] = j < cols ? __ldcs(row + j) : -INFINITY;
+        for (int s = 0; s < kSteps; ++s) {
+            const int j = first(s);
+            if (VEC) {
+                float4 w = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+                if (j < cols) w = __ldcs(reinterpret_cast<const float4*>(src + j));
+                v[4 * s] = w.x; v[4 * s + 1] = w.y; v[4 * s + 2] = w.z; v[4 * s + 3] = w.w;
+            } else {
+                v[s] = j < cols ? __ldcs(src + j) : -INFINITY;
+            }
         }
     }
     template <class F> __device__ __forceinline__ void each(F f) const {
 #pragma unroll
-        for (int it = 0; it < ITEMS; ++it) {
-            int64_t j = lane + it * G;
-            if (j < cols) f(j, v[it]);
+        for (int s = 0; s < kSteps; ++s) {
+            const int j = first(s);
+            if (j < cols) {
+                if (VEC) { f(j, v[4 * s]); f(j + 1, v[4 * s + 1]); f(j + 2, v[4 * s + 2]); f(j + 3, v[4 * s + 3]); }
+                else f(j, v[s]);
+            }
         }
     }
     template <class F> __device__ __forceinline__ void update(F f) {
 #pragma unroll
-        for (int it = 0; it < ITEMS; ++it) {
-            int64_t j = lane + it * G;
-            if (j < cols) v[it] = f(j, v[it]);
+        for (int s = 0; s < kSteps; ++s) {
+            const int j = first(s);
+            if (j < cols) {
+                if (VEC) { v[4 * s] = f(j, v[4 * s]); v[4 * s + 1] = f(j + 1, v[4 * s + 1]); v[4 * s + 2] = f(j + 2, v[4 * s + 2]); v[4 * s + 3] = f(j + 3, v[4 * s + 3]); }
+                else v[s] = f(j, v[s]);
+            }
         }
     }
     template <class F> __device__ __forceinline__ void store(float* __restrict__ out, F f) const {
-        each([&](int64_t j, float w) { __stcs(out + j, f(j, w)); });
+#pragma unroll
+        for (int s = 0; s < kSteps; ++s) {
+            const int j = first(s);
+            if (j < cols) {
+                if (VEC) __stcs(reinterpret_cast<float4*>(out + j), make_float4(f(j, v[4 * s]), f(j + 1, v[4 * s + 1]), f(j + 2, v[4 * s + 2]), f(j + 3, v[4 * s + 3])));
+                else __stcs(out + j, f(j, v[s]));
+            }
+        }
     }
-    __device__ __forceinline__ float rmax() const {
+    // aux rows are 16-byte aligned too in the vector form (the launchers check)
+    template <class F> __device__ __forceinline__ void each2(const float* __restrict__ aux, F f) const {
+#pragma unroll
+        for (int s = 0; s < kSteps; ++s) {
+            const int j = first(s);
+            if (j < cols) {
+                if (VEC) {
+                    const float4 a = __ldg(reinterpret_cast<const float4*>(aux + j));
+                    f(j, v[4 * s], a.x); f(j + 1, v[4 * s + 1], a.y); f(j + 2, v[4 * s + 2], a.z); f(j + 3, v[4 * s + 3], a.w);
+                } else {
+                    f(j, v[s], __ldg(aux + j));
+                }
+            }
+        }
+    }
+    template <class F> __device__ __forceinline__ void store2(float* __restrict__ out, const float* __restrict__ aux, F f) const {
+#pragma unroll
+        for (int s = 0; s < kSteps; ++s) {
+            const int j = first(s);
+            if (j < cols) {
+                if (VEC) {
+                    const float4 a = __ldcs(reinterpret_cast<const float4*>(aux + j));
+                    __stcs(reinterpret_cast<float4*>(out + j), make_float4(f(j, v[4 * s], a.x), f(j + 1, v[4 * s + 1], a.y), f(j + 2, v[4 * s + 2], a.z), f(j + 3, v[4 * s + 3], a.w)));
+                } else {
+                    __stcs(out + j, f(j, v[s], __ldcs(aux + j)));
+                }
+            }
+        }
+    }
+    __device__ __forceinline__ bool pick(int c, float& w) const {
+        bool mine = false;
+#pragma unroll
+        for (int s = 0; s < kSteps; ++s) {
+            const int j = first(s);
+            if (VEC) {
+                if (j == (c & ~3)) {
+                    const int k = c & 3;
+                    w = k == 0 ? v[4 * s] : k == 1 ? v[4 * s + 1] : k == 2 ? v[4 * s + 2] : v[4 * s + 3];
+                    mine = true;
+                }
+            } else if (j == c) {
+                w = v[s];
+                mine = true;
+            }
+        }
+        return mine;
+    }
+    __device__ __forceinline__ float local_max() const {
         float m = -INFINITY;
 #pragma unroll
         for (int it = 0; it < ITEMS; ++it) m = fmaxf(m, v[it]);
-        return group_max<G>(m);
+        return m;
     }
-    __device__ __forceinline__ float rsum(float partial) const { return group_sum<G>(partial); }
-    __device__ __forceinline__ bool leader() const { return lane == 0; }
 };
+
+// A warp owns the row: reductions are shuffles, no barrier and no shared memory anywhere.
+template <int ITEMS, bool VEC>
+struct WarpRow : StridedRow<32, ITEMS, VEC> {
+    __device__ __forceinline__ float rmax() const { return warp_max(this->local_max()); }
+    __device__ __forceinline__ float rsum(float partial) const { return warp_sum(partial); }
+};
+
+// All THREADS threads of a CTA own the row.
+template <int THREADS, int ITEMS, bool VEC>
+struct CtaRow : StridedRow<THREADS, ITEMS, VEC> {
+    CtaReducer rd;
+    __device__ __forceinline__ float rmax() { return rd.template run<true>(this->local_max(), THREADS / 32); }
+    __device__ __forceinline__ float rsum(float partial) { return rd.template run<false>(partial, THREADS / 32); }
+};
+
+// Generic pick for the holders that walk their elements with each().
+template <class Row>
+__device__ __forceinline__ bool pick_by_each(const Row& r, int c, float& w) {
+    bool mine = false;
+    r.each([&](int64_t j, float x) {
+        if (static_cast<int>(j) == c) { w = x; mine = true; }
+    });
+    return mine;
+}
 
 struct SmemRow {
     static constexpr bool kCached = true;
@@ -137,13 +246,19 @@ struct SmemRow {
     template <class F> __device__ __forceinline__ void store(float* __restrict__ out, F f) const {
         each([&](int64_t j, float w) { __stcs(out + j, f(j, w)); });
     }
+    template <class F> __device__ __forceinline__ void each2(const float* __restrict__ aux, F f) const {
+        each([&](int64_t j, float w) { f(j, w, __ldg(aux + j)); });
+    }
+    template <class F> __device__ __forceinline__ void store2(float* __restrict__ out, const float* __restrict__ aux, F f) const {
+        store(out, [&](int64_t j, float w) { return f(j, w, __ldcs(aux + j)); });
+    }
+    __device__ __forceinline__ bool pick(int c, float& w) const { return pick_by_each(*this, c, w); }
     __device__ __forceinline__ float rmax() const {
         float m = -INFINITY;
         for (int64_t j = threadIdx.x; j < cols; j += blockDim.x) m = fmaxf(m, buf[j]);
         return block_max(m, red_f);
     }
     __device__ __forceinline__ float rsum(float partial) const { return static_cast<float>(block_sum(static_cast<double>(partial), red_d)); }
-    __device__ __forceinline__ bool leader() const { return threadIdx.x == 0; }
 };
 
 // Row too long for shared memory: every pass re-reads it (L2 absorbs most of the re-reads).
@@ -163,97 +278,49 @@ struct GlobalRow {
     template <class F> __device__ __forceinline__ void store(float* __restrict__ out, F f) const {
         each([&](int64_t j, float w) { __stcs(out + j, f(j, w)); });
     }
+    template <class F> __device__ __forceinline__ void each2(const float* __restrict__ aux, F f) const {
+        each([&](int64_t j, float w) { f(j, w, __ldg(aux + j)); });
+    }
+    template <class F> __device__ __forceinline__ void store2(float* __restrict__ out, const float* __restrict__ aux, F f) const {
+        store(out, [&](int64_t j, float w) { return f(j, w, __ldcs(aux + j)); });
+    }
+    __device__ __forceinline__ bool pick(int c, float& w) const { return pick_by_each(*this, c, w); }
     __device__ __forceinline__ float rmax() const {
         float m = -INFINITY;
         for (int64_t j = threadIdx.x; j < cols; j += blockDim.x) m = fmaxf(m, __ldg(row + j));
         return block_max(m, red_f);
     }
     __device__ __forceinline__ float rsum(float partial) const { return static_cast<float>(block_sum(static_cast<double>(partial), red_d)); }
-    __device__ __forceinline__ bool leader() const { return threadIdx.x == 0; }
-};
-
-// A CTA of THREADS threads owns a row in registers.  VEC: thread t holds the 128-bit vectors
-// t, t + THREADS, ... (cols % 4 == 0, 16-byte aligned rows); otherwise the elements t, t + THREADS, ...
-template <int THREADS, int ITEMS, bool VEC>
-struct CtaRow {
-    static constexpr bool kCached = true;
-    float v[ITEMS];
-    float* red_f;
-    double* red_d;
-    int64_t cols;
-    __device__ __forceinline__ int64_t index(int it) const {
-        return VEC ? (static_cast<int64_t>(threadIdx.x + (it >> 2) * THREADS) << 2) + (it & 3) : threadIdx.x + static_cast<int64_t>(it) * THREADS;
-    }
-    // src: the row in global memory, or its copy in shared memory
-    __device__ __forceinline__ void load(const float* __restrict__ src) {
-        if (VEC) {
-#pragma unroll
-            for (int q = 0; q < ITEMS / 4; ++q) {
-                const int64_t j = static_cast<int64_t>(threadIdx.x + q * THREADS) << 2;
-                float4 t = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-                if (j < cols) t = *reinterpret_cast<const float4*>(src + j);
-                v[4 * q] = t.x; v[4 * q + 1] = t.y; v[4 * q + 2] = t.z; v[4 * q + 3] = t.w;
-            }
-        } else {
-#pragma unroll
-            for (int it = 0; it < ITEMS; ++it) {
-                const int64_t j = threadIdx.x + static_cast<int64_t>(it) * THREADS;
-                v[it] = j < cols ? src[j] : -INFINITY;
-            }
-        }
-    }
-    template <class F> __device__ __forceinline__ void each(F f) const {
-#pragma unroll
-        for (int it = 0; it < ITEMS; ++it) {
-            const int64_t j = index(it);
-            if (j < cols) f(j, v[it]);
-        }
-    }
-    template <class F> __device__ __forceinline__ void update(F f) {
-#pragma unroll
-        for (int it = 0; it < ITEMS; ++it) {
-            const int64_t j = index(it);
-            if (j < cols) v[it] = f(j, v[it]);
-        }
-    }
-    // out[j] = f(j, value) for every owned element, as 128-bit stores when VEC
-    template <class F> __device__ __forceinline__ void store(float* __restrict__ out, F f) const {
-        if (VEC) {
-#pragma unroll
-            for (int q = 0; q < ITEMS / 4; ++q) {
-                const int64_t j = static_cast<int64_t>(threadIdx.x + q * THREADS) << 2;
-                if (j < cols) __stcs(reinterpret_cast<float4*>(out + j), make_float4(f(j, v[4 * q]), f(j + 1, v[4 * q + 1]), f(j + 2, v[4 * q + 2]), f(j + 3, v[4 * q + 3])));
-            }
-        } else {
-            each([&](int64_t j, float w) { __stcs(out + j, f(j, w)); });
-        }
-    }
-    __device__ __forceinline__ float rmax() const {
-        float m = -INFINITY;
-#pragma unroll
-        for (int it = 0; it < ITEMS; ++it) m = fmaxf(m, v[it]);
-        return block_max(m, red_f);
-    }
-    __device__ __forceinline__ float rsum(float partial) const { return static_cast<float>(block_sum(static_cast<double>(partial), red_d)); }
-    __device__ __forceinline__ bool leader() const { return threadIdx.x == 0; }
 };
 
 // ---- the row algorithms, written once over a holder --------------------------------------------
 // Returns THIS THREAD's share of the row's loss for the CE forms (the caller adds the shares of all
 // its threads), 0 otherwise.
 // `src` is where the holder loads the row from (global memory, or a staged copy in shared memory).
+template <int ALG> __host__ __device__ constexpr bool alg_has_loss() { return ALG == ALG_CE_ONEHOT || ALG == ALG_CE_INDEX || ALG == ALG_CE_FUSED; }
+template <int ALG> __host__ __device__ constexpr bool alg_two_operands() { return ALG == ALG_SOFTMAX_BWD || ALG == ALG_CE_ONEHOT || ALG == ALG_CE_BWD; }
+template <int ALG> __host__ __device__ constexpr bool alg_has_output() { return ALG != ALG_CE_ONEHOT && ALG != ALG_CE_INDEX; }
+template <int ALG> __host__ __device__ constexpr bool alg_has_label() { return ALG == ALG_CE_INDEX || ALG == ALG_CE_FUSED; }
+
+// The row's class label for the index forms, fetched BEFORE the row itself so that its latency
+// overlaps the row's; 0 for the other algorithms.
+template <int ALG>
+__device__ __forceinline__ float row_label(const RowArgs& A, int64_t row) {
+    return alg_has_label<ALG>() ? __ldg(A.t + row) : 0.0f;
+}
+
 template <int ALG, class Row>
-__device__ __forceinline__ float process_loaded(Row& r, const RowArgs& A, int64_t row, bool& poison) {
+__device__ __forceinline__ float process_loaded(Row& r, const RowArgs& A, int64_t row, float label, bool& poison) {
     const int64_t cols = A.cols;
     const float* xrow = A.x + row * cols;
     float* orow = A.out ? A.out + row * cols : nullptr;
     if (ALG == ALG_SOFTMAX_BWD) {
-        // holder caches y; g is streamed twice (second pass hits L1/L2)
+        // holder caches y; g is read twice (the second time out of L1/L2)
         const float* grow = A.t + row * cols;
         float part = 0.0f;
-        r.each([&](int64_t j, float y) { part += __ldg(grow + j) * y; });
+        r.each2(grow, [&](int64_t, float y, float g) { part += g * y; });
         const float dot = r.rsum(part);
-        r.store(orow, [&](int64_t j, float y) { return y * (__ldg(grow + j) - dot); });
+        r.store2(orow, grow, [&](int64_t, float y, float g) { return y * (g - dot); });
         return 0.0f;
     }
     const float m = r.rmax();
@@ -274,8 +341,7 @@ __device__ __forceinline__ float process_loaded(Row& r, const RowArgs& A, int64_
     if (ALG == ALG_CE_ONEHOT) {
         const float* trow = A.t + row * cols;
         float loss = 0.0f;
-        r.each([&](int64_t j, float w) {
-            float t = __ldcs(trow + j);
+        r.each2(trow, [&](int64_t, float w, float t) {
             if (t != 0.0f) {  // a zero target adds exactly zero: log(max(p,1e-10)) is finite
                 float p = fmaxf(prob(w), 1e-10f);
                 loss = fmaf(-t, logf(p), loss);
@@ -286,24 +352,23 @@ __device__ __forceinline__ float process_loaded(Row& r, const RowArgs& A, int64_
     if (ALG == ALG_CE_BWD) {
         const float* trow = A.t + row * cols;
         const float g = A.gdev ? __ldg(A.gdev) : 1.0f;
-        r.store(orow, [&](int64_t j, float w) {
-            float d = prob(w) - __ldcs(trow + j);
+        r.store2(orow, trow, [&](int64_t, float w, float t) {
+            float d = prob(w) - t;
             return d * g;
         });
         return 0.0f;
     }
     // index-label forms
-    const int c = static_cast<int>(__ldg(A.t + row));
+    const int c = static_cast<int>(label);
     const bool ok = (c >= 0 && c < static_cast<int>(cols));
     if (!ok) poison = true;
-    // The thread that holds element c contributes the row's loss: no extra global read and no
+    // The thread that holds element c contributes the row's loss: no dependent global read and no
     // per-row reduction on the critical path.
-    float loss = 0.0f;
-    if (ok) {
-        r.each([&](int64_t j, float w) {
-            if (static_cast<int>(j) == c) loss = -logf(fmaxf(prob(w), 1e-10f));
-        });
-    }
+    // (Select the element first and take ONE logarithm per thread and row: written inside the loop,
+    // the logarithm is evaluated for every element once the compiler turns the branch into selects.)
+    float wc = 0.0f;
+    const bool mine = r.pick(c, wc);
+    const float loss = (ok && mine) ? -logf(fmaxf(prob(wc), 1e-10f)) : 0.0f;
     if (ALG == ALG_CE_FUSED) {
         r.store(orow, [&](int64_t j, float w) { return prob(w) - (static_cast<int>(j) == c ? 1.0f : 0.0f); });
     }
@@ -312,45 +377,206 @@ __device__ __forceinline__ float process_loaded(Row& r, const RowArgs& A, int64_
 
 template <int ALG, class Row>
 __device__ __forceinline__ float process_row(Row& r, const RowArgs& A, int64_t row, const float* src, bool& poison) {
+    const float label = row_label<ALG>(A, row);
     r.load(src);
-    return process_loaded<ALG>(r, A, row, poison);
+    return process_loaded<ALG>(r, A, row, label, poison);
 }
 
-template <int ALG> __host__ __device__ constexpr bool alg_has_loss() { return ALG == ALG_CE_ONEHOT || ALG == ALG_CE_INDEX || ALG == ALG_CE_FUSED; }
+// ---- short rows (cols <= 16): a thread per row ------------------------------------------------------
+// A CTA takes 256 consecutive rows, i.e. one contiguous block of 256 * cols floats: the block is
+// copied to shared memory with coalesced 128-bit loads, every thread then owns one row in registers
+// (no shuffles, no barriers inside the row), results go back to the shared tile and leave with
+// coalesced 128-bit stores.  A thread walks its row starting at column (row mod cols), so that the
+// threads of a warp hit different banks although their rows are cols words apart.
+constexpr int kTileRows = 256;
 
-template <int ALG, int G, int ITEMS>
-__global__ void __launch_bounds__(kRegThreads) reg_rows_kernel(RowArgs A, ReduceScratch* scratch, float* loss_out) {
-    __shared__ double smem[33];
-    constexpr int kGroupsPerCta = kRegThreads / G;
-    RegRow<G, ITEMS> r;
-    r.lane = threadIdx.x % G;
-    r.cols = A.cols;
-    const int64_t group = static_cast<int64_t>(blockIdx.x) * kGroupsPerCta + threadIdx.x / G;
-    const int64_t ngroups = static_cast<int64_t>(gridDim.x) * kGroupsPerCta;
+template <int MAXC>
+struct TileRow {
+    static constexpr bool kCached = true;
+    float v[MAXC];
+    float* mine;        // this thread's row in the x / out tile
+    const float* aux;   // this thread's row in the second operand's tile
+    int cols, rot;
+    __device__ __forceinline__ int col(int k) const {
+        const int j = k + rot;
+        return j >= cols ? j - cols : j;
+    }
+    __device__ __forceinline__ void load(const float*) {
+#pragma unroll
+        for (int k = 0; k < MAXC; ++k) v[k] = k < cols ? mine[col(k)] : -INFINITY;
+    }
+    template <class F> __device__ __forceinline__ void each(F f) const {
+#pragma unroll
+        for (int k = 0; k < MAXC; ++k)
+            if (k < cols) f(static_cast<int64_t>(col(k)), v[k]);
+    }
+    template <class F> __device__ __forceinline__ void update(F f) {
+#pragma unroll
+        for (int k = 0; k < MAXC; ++k)
+            if (k < cols) v[k] = f(static_cast<int64_t>(col(k)), v[k]);
+    }
+    template <class F> __device__ __forceinline__ void store(float*, F f) const {
+#pragma unroll
+        for (int k = 0; k < MAXC; ++k)
+            if (k < cols) { const int j = col(k); mine[j] = f(static_cast<int64_t>(j), v[k]); }
+    }
+    template <class F> __device__ __forceinline__ void each2(const float*, F f) const {
+#pragma unroll
+        for (int k = 0; k < MAXC; ++k)
+            if (k < cols) { const int j = col(k); f(static_cast<int64_t>(j), v[k], aux[j]); }
+    }
+    template <class F> __device__ __forceinline__ void store2(float*, const float*, F f) const {
+#pragma unroll
+        for (int k = 0; k < MAXC; ++k)
+            if (k < cols) { const int j = col(k); mine[j] = f(static_cast<int64_t>(j), v[k], aux[j]); }
+    }
+    __device__ __forceinline__ float rmax() const {
+        float m = -INFINITY;
+#pragma unroll
+        for (int k = 0; k < MAXC; ++k) m = fmaxf(m, v[k]);
+        return m;
+    }
+    __device__ __forceinline__ float rsum(float partial) const { return partial; }
+    __device__ __forceinline__ bool pick(int c, float& w) const {
+        // element c sits in register (c - rot) mod cols
+        int k = c - rot;
+        if (k < 0) k += cols;
+#pragma unroll
+        for (int i = 0; i < MAXC; ++i)
+            if (i == k) w = v[i];
+        return true;
+    }
+};
+
+// Contiguous n floats global <-> shared, 128-bit where the block starts on a 16-byte boundary.
+__device__ __forceinline__ void tile_in(float* __restrict__ dst, const float* __restrict__ src, int n) {
+    if ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
+        const int n4 = n >> 2;
+        for (int i = threadIdx.x; i < n4; i += kTileRows) reinterpret_cast<float4*>(dst)[i] = __ldcs(reinterpret_cast<const float4*>(src) + i);
+        for (int i = (n4 << 2) + threadIdx.x; i < n; i += kTileRows) dst[i] = __ldcs(src + i);
+    } else {
+        for (int i = threadIdx.x; i < n; i += kTileRows) dst[i] = __ldcs(src + i);
+    }
+}
+__device__ __forceinline__ void tile_out(float* __restrict__ dst, const float* __restrict__ src, int n) {
+    if ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+        const int n4 = n >> 2;
+        for (int i = threadIdx.x; i < n4; i += kTileRows) __stcs(reinterpret_cast<float4*>(dst) + i, reinterpret_cast<const float4*>(src)[i]);
+        for (int i = (n4 << 2) + threadIdx.x; i < n; i += kTileRows) __stcs(dst + i, src[i]);
+    } else {
+        for (int i = threadIdx.x; i < n; i += kTileRows) __stcs(dst + i, src[i]);
+    }
+}
+
+template <int ALG, int MAXC>
+__global__ void __launch_bounds__(kTileRows) tile_rows_kernel(RowArgs A, ReduceScratch* scratch, float* loss_out) {
+    extern __shared__ __align__(16) float tiles[];  // [256 * cols] x / out, then [256 * cols] second operand
+    __shared__ double red_d[33];
+    const int cols = static_cast<int>(A.cols);
+    float* tile_x = tiles;
+    float* tile_t = tiles + kTileRows * cols;
+    TileRow<MAXC> r;
+    r.cols = cols;
+    r.rot = static_cast<int>(threadIdx.x) % cols;
+    r.mine = tile_x + threadIdx.x * cols;
+    r.aux = tile_t + threadIdx.x * cols;
     double acc = 0.0;
     bool poison = false;
-    // Every group of a warp runs the same trip count so the shuffles stay converged; a group with
-    // no row left owns zero elements (loads, stores and sums nothing) and its result is dropped.
-    const int64_t trips = (A.rows + ngroups - 1) / ngroups;
-    for (int64_t it = 0; it < trips; ++it) {
-        const int64_t row = group + it * ngroups;
-        const bool live = row < A.rows;
-        r.cols = live ? A.cols : 0;
-        bool p = false;
-        const int64_t rr = live ? row : A.rows - 1;
-        const float l = process_row<ALG>(r, A, rr, A.x + rr * A.cols, p);
+    const int64_t ntiles = (A.rows + kTileRows - 1) / kTileRows;
+    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        const int64_t row0 = tile * kTileRows;
+        const int rows_here = static_cast<int>(A.rows - row0 < kTileRows ? A.rows - row0 : kTileRows);
+        const int n = rows_here * cols;
+        const bool live = static_cast<int>(threadIdx.x) < rows_here;
+        const float label = live ? row_label<ALG>(A, row0 + threadIdx.x) : 0.0f;
+        tile_in(tile_x, A.x + row0 * cols, n);
+        if (alg_two_operands<ALG>()) tile_in(tile_t, A.t + row0 * cols, n);
+        __syncthreads();
         if (live) {
-            poison |= p;
+            r.load(nullptr);
+            const float l = process_loaded<ALG>(r, A, row0 + threadIdx.x, label, poison);
             if (alg_has_loss<ALG>()) acc += static_cast<double>(l);
         }
+        __syncthreads();
+        if (alg_has_output<ALG>()) tile_out(A.out + row0 * cols, tile_x, n);
+        __syncthreads();
     }
     if (alg_has_loss<ALG>()) {
         if (poison && A.bad) *A.bad = 1;
         int any_poison = __syncthreads_or(poison ? 1 : 0);
-        double total = block_sum(acc, smem);
-        // A poisoned CTA contributes NaN so the final value is NaN whichever CTA finishes last.
-        grid_finish(any_poison ? NAN : total, scratch, loss_out, 0.0f, false, smem);
+        double total = block_sum(acc, red_d);
+        grid_finish(any_poison ? NAN : total, scratch, loss_out, 0.0f, false, red_d);
     }
+}
+
+template <int ALG, int MAXC>
+void launch_tile(const RowArgs& A, ReduceScratch* s, float* loss_out, cudaStream_t st) {
+    int64_t grid = (A.rows + kTileRows - 1) / kTileRows;
+    if (alg_has_loss<ALG>()) {
+        const int64_t resident = static_cast<int64_t>(ctk::sm_count()) * 8;
+        if (grid > resident) grid = resident;
+        if (grid > kMaxReduceBlocks) grid = kMaxReduceBlocks;
+    }
+    if (grid > 0x7fffffff) grid = 0x7fffffff;
+    const size_t smem = static_cast<size_t>(kTileRows) * A.cols * sizeof(float) * (alg_two_operands<ALG>() ? 2 : 1);
+    tile_rows_kernel<ALG, MAXC><<<static_cast<unsigned>(grid), kTileRows, smem, st>>>(A, s, loss_out);
+}
+
+// ---- rows up to 1024 columns: a warp per row ---------------------------------------------------------
+// Each warp of a 128-thread CTA walks its own rows: the row sits in the warp's registers (up to 32
+// values per lane, 128-bit loads when the rows are aligned), max and sum are five shuffles each, and
+// nothing in the row's life touches shared memory or a barrier.  Rows of different warps overlap
+// freely, so HBM latency is hidden by the ~32 rows in flight per SM.
+constexpr int kWarpRowThreads = 128;
+
+template <int ALG, int ITEMS, bool VEC>
+__global__ void __launch_bounds__(kWarpRowThreads) warp_rows_kernel(RowArgs A, ReduceScratch* scratch, float* loss_out) {
+    __shared__ double red_d[33];
+    WarpRow<ITEMS, VEC> r;
+    r.cols = static_cast<int>(A.cols);
+    r.t = threadIdx.x & 31;
+    constexpr int kWarps = kWarpRowThreads / 32;
+    const int64_t first = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+    const int64_t step = static_cast<int64_t>(gridDim.x) * kWarps;
+    double acc = 0.0;
+    bool poison = false;
+    for (int64_t row = first; row < A.rows; row += step) {
+        const float l = process_row<ALG>(r, A, row, A.x + row * A.cols, poison);
+        if (alg_has_loss<ALG>()) acc += static_cast<double>(l);
+    }
+    if (alg_has_loss<ALG>()) {
+        if (poison && A.bad) *A.bad = 1;
+        int any_poison = __syncthreads_or(poison ? 1 : 0);
+        double total = block_sum(acc, red_d);
+        // A poisoned CTA contributes NaN so the final value is NaN whichever CTA finishes last.
+        grid_finish(any_poison ? NAN : total, scratch, loss_out, 0.0f, false, red_d);
+    }
+}
+
+// 16-byte alignment of every row of every operand the vector forms touch.
+template <int ALG>
+bool rows_aligned(const RowArgs& A) {
+    return (A.cols % 4 == 0) && ((reinterpret_cast<uintptr_t>(A.x) & 15u) == 0) && (!A.out || (reinterpret_cast<uintptr_t>(A.out) & 15u) == 0) &&
+           (!alg_two_operands<ALG>() || (reinterpret_cast<uintptr_t>(A.t) & 15u) == 0);
+}
+
+template <int ALG, int ITEMS>
+void launch_warp(const RowArgs& A, ReduceScratch* s, float* loss_out, cudaStream_t st) {
+    constexpr int kWarps = kWarpRowThreads / 32;
+    int64_t grid = (A.rows + kWarps - 1) / kWarps;
+    if (alg_has_loss<ALG>()) {
+        const int64_t resident = static_cast<int64_t>(ctk::sm_count()) * (ITEMS > 16 ? 8 : 16);
+        if (grid > resident) grid = resident;
+        if (grid > kMaxReduceBlocks) grid = kMaxReduceBlocks;
+    }
+    if (grid > 0x7fffffff) grid = 0x7fffffff;
+    if constexpr (ITEMS % 4 == 0) {
+        if (rows_aligned<ALG>(A)) {
+            warp_rows_kernel<ALG, ITEMS, true><<<static_cast<unsigned>(grid), kWarpRowThreads, 0, st>>>(A, s, loss_out);
+            return;
+        }
+    }
+    warp_rows_kernel<ALG, ITEMS, false><<<static_cast<unsigned>(grid), kWarpRowThreads, 0, st>>>(A, s, loss_out);
 }
 
 template <int ALG, class Row>
@@ -377,77 +603,22 @@ __global__ void __launch_bounds__(kRowThreads) cta_rows_kernel(RowArgs A, Reduce
     }
 }
 
-// ---- bulk asynchronous copy of one row into shared memory -----------------------------------------
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-__device__ __forceinline__ void row_bar_init(uint32_t bar) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar) : "memory");
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-}
-__device__ __forceinline__ void row_fetch(uint32_t dst, const float* src, uint32_t bytes, uint32_t bar) {
-    // the previous contents were read through ordinary loads: order them before the async write
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar) : "memory");
-}
-// Bounded: gives up after ~2^22 polls and reports it (the caller poisons the result and leaves).
-__device__ __forceinline__ bool row_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < (1u << 22); ++i) {
-        uint32_t ok;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-    }
-    return false;
-}
-
-// A CTA per row, row in registers.  PREFETCH: while row r is processed from registers, row r + grid is
-// already on its way into shared memory (one bulk copy, completion on an mbarrier), so the HBM read
-// of the next row overlaps the arithmetic and the stores of this one.  Needs 16-byte aligned rows.
-template <int ALG, int THREADS, int ITEMS, bool VEC, bool PREFETCH>
+// A CTA per row, row in registers, many CTAs per SM (the other resident CTAs hide each one's latency).
+// Forms without a loss launch one CTA per row and let the hardware scheduler walk the rows; forms
+// with a loss run a resident grid that strides over the rows, so the per-CTA finish of the loss
+// (fp64 block sum + ticket) is paid once per ~30 rows rather than once per row.
+template <int ALG, int THREADS, int ITEMS, bool VEC>
 __global__ void __launch_bounds__(THREADS) cta_reg_rows_kernel(RowArgs A, ReduceScratch* scratch, float* loss_out) {
-    extern __shared__ __align__(128) float stage[];
     __shared__ double red_d[33];
-    __shared__ float red_f[33];
-    __shared__ __align__(8) uint64_t bar;
-    __shared__ int gave_up;
+    __shared__ float red_f[64];
     CtaRow<THREADS, ITEMS, VEC> r;
-    r.cols = A.cols;
-    r.red_f = red_f;
-    r.red_d = red_d;
+    r.cols = static_cast<int>(A.cols);
+    r.t = threadIdx.x;
+    r.rd = CtaReducer{red_f, 0, false};
     double acc = 0.0;
     bool poison = false;
-    const uint32_t row_bytes = static_cast<uint32_t>(A.cols * sizeof(float));
-    uint32_t parity = 0;
-    int64_t row = blockIdx.x;
-    if (PREFETCH) {
-        if (threadIdx.x == 0) {
-            gave_up = 0;
-            row_bar_init(smem_addr(&bar));
-            if (row < A.rows) row_fetch(smem_addr(stage), A.x + row * A.cols, row_bytes, smem_addr(&bar));
-        }
-        __syncthreads();
-    }
-    for (; row < A.rows; row += gridDim.x) {
-        const float* src = A.x + row * A.cols;
-        if (PREFETCH) {
-            if (threadIdx.x == 0 && !row_wait(smem_addr(&bar), parity)) gave_up = 1;
-            __syncthreads();
-            if (gave_up) { poison = true; break; }
-            parity ^= 1u;
-            src = stage;
-        }
-        float l;
-        if (PREFETCH) {
-            // copy to registers first, then hand the staging buffer to the next row's copy
-            r.load(src);
-            __syncthreads();
-            const int64_t next = row + gridDim.x;
-            if (threadIdx.x == 0 && next < A.rows) row_fetch(smem_addr(stage), A.x + next * A.cols, row_bytes, smem_addr(&bar));
-            l = process_loaded<ALG>(r, A, row, poison);
-        } else {
-            l = process_row<ALG>(r, A, row, src, poison);
-        }
+    for (int64_t row = blockIdx.x; row < A.rows; row += gridDim.x) {
+        const float l = process_row<ALG>(r, A, row, A.x + row * A.cols, poison);
         if (alg_has_loss<ALG>()) acc += static_cast<double>(l);
     }
     if (alg_has_loss<ALG>()) {
@@ -458,48 +629,250 @@ __global__ void __launch_bounds__(THREADS) cta_reg_rows_kernel(RowArgs A, Reduce
     }
 }
 
-template <int ALG, int THREADS, int ITEMS, bool PREFETCH>
+template <int ALG, int THREADS, int ITEMS>
 ctk_status launch_cta_reg(const RowArgs& A, ReduceScratch* s, float* loss_out, cudaStream_t st) {
-    const bool vec = (A.cols % 4 == 0) && ((reinterpret_cast<uintptr_t>(A.x) & 15u) == 0) && (!A.out || (reinterpret_cast<uintptr_t>(A.out) & 15u) == 0);
-    const size_t smem = PREFETCH ? static_cast<size_t>(A.cols) * sizeof(float) : 0;
-    // resident CTAs per SM: by threads (2048) and by staging memory (~200 KiB)
-    int per_sm = 2048 / THREADS;
-    if (PREFETCH) {
-        const int by_smem = static_cast<int>((200u * 1024u) / (smem + 1024));
-        per_sm = per_sm < by_smem ? per_sm : by_smem;
-        if (per_sm < 1) per_sm = 1;
+    const bool vec = rows_aligned<ALG>(A);
+    int64_t grid = A.rows;
+    if (alg_has_loss<ALG>()) {
+        const int64_t resident = static_cast<int64_t>(ctk::sm_count()) * (2048 / THREADS);
+        if (grid > resident) grid = resident;
+        if (grid > kMaxReduceBlocks) grid = kMaxReduceBlocks;
     }
-    int64_t cap = static_cast<int64_t>(ctk::sm_count()) * per_sm;
-    if (!PREFETCH) cap = A.rows;  // one row per CTA, the hardware scheduler walks the rows in order
-    int64_t grid = A.rows < cap ? A.rows : cap;
-    if (alg_has_loss<ALG>() && grid > kMaxReduceBlocks) grid = kMaxReduceBlocks;
     if (grid > 0x7fffffff) grid = 0x7fffffff;
-    if (PREFETCH) {
-        CTK_REQUIRE(vec, "row kernel: the prefetching form needs 16-byte aligned rows");
-        auto k = cta_reg_rows_kernel<ALG, THREADS, ITEMS, true, true>;
-        static bool attr_set = false;
-        if (!attr_set) {
-            CTK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * static_cast<int>(sizeof(float))));
-            attr_set = true;
-        }
-        k<<<static_cast<unsigned>(grid), THREADS, smem, st>>>(A, s, loss_out);
-    } else if (vec) {
-        cta_reg_rows_kernel<ALG, THREADS, ITEMS, true, false><<<static_cast<unsigned>(grid), THREADS, 0, st>>>(A, s, loss_out);
-    } else {
-        cta_reg_rows_kernel<ALG, THREADS, ITEMS, false, false><<<static_cast<unsigned>(grid), THREADS, 0, st>>>(A, s, loss_out);
-    }
+    if (vec) cta_reg_rows_kernel<ALG, THREADS, ITEMS, true><<<static_cast<unsigned>(grid), THREADS, 0, st>>>(A, s, loss_out);
+    else cta_reg_rows_kernel<ALG, THREADS, ITEMS, false><<<static_cast<unsigned>(grid), THREADS, 0, st>>>(A, s, loss_out);
     return CTK_OK;
 }
 
-template <int ALG, int G, int ITEMS>
-void launch_reg(const RowArgs& A, ReduceScratch* s, float* loss_out, cudaStream_t st) {
-    constexpr int kGroupsPerCta = kRegThreads / G;
-    int64_t need = (A.rows + kGroupsPerCta - 1) / kGroupsPerCta;
-    int64_t cap = static_cast<int64_t>(ctk::sm_count()) * 8;
-    int grid = static_cast<int>(need < cap ? need : cap);
-    if (grid < 1) grid = 1;
-    if (grid > kMaxReduceBlocks) grid = kMaxReduceBlocks;
-    reg_rows_kernel<ALG, G, ITEMS><<<grid, kRegThreads, 0, st>>>(A, s, loss_out);
+// ---- streamed rows: long rows through a ring of bulk asynchronous copies ---------------------------
+// One CTA per SM.  A producer warp walks this CTA's rows and copies them, 16 KiB at a time
+// (cp.async.bulk, completion on an mbarrier), into a ring of 13 slots of shared memory; 512 consumer
+// threads take each chunk as it lands (thread t owns vectors t and t + 512 of every chunk).  The
+// row itself goes straight into registers, so its slots are free again at once and the producer runs
+// up to 208 KiB -- more than a row -- ahead, across row boundaries: the reads of the following rows
+// overlap the arithmetic and the stores of the current one without any occupancy to lean on.
+// A second operand row (one-hot targets; the upstream gradient of the softmax backward, which is
+// needed twice and streamed twice, the second time out of L2) flows through the same ring and is
+// used from shared memory in place.
+// Every wait is bounded; a wait that runs out raises a CTA-wide flag, the roles leave their loops,
+// the producer lets its copies land, and the loss (or a flag word) reports the failure.
+constexpr int kChunkBytes = 16384;
+constexpr int kChunkFloats = kChunkBytes / 4;
+constexpr int kRingSlots = 13;
+constexpr int kStreamThreads = kConsumers + 32;
+constexpr uint32_t kStreamWaitLimit = 1u << 22;
+
+__device__ int g_row_status = 0;  // set when a bounded wait of the streamed kernel ran out
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void sbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void sbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool sbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool sbar_wait(uint32_t bar, uint32_t parity, volatile int* gave_up) {
+    for (uint32_t i = 0; i < kStreamWaitLimit; ++i) {
+        if (sbar_try(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *gave_up) return false;
+    }
+    *gave_up = 1;
+    atomicExch(&g_row_status, 1);
+    return false;
+}
+__device__ __forceinline__ void chunk_fetch(uint32_t dst, const float* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar) : "memory");
+}
+// How many operand rows per row of the problem pass through the ring, and from where.
+template <int ALG> __host__ __device__ constexpr int alg_streams() {
+    return ALG == ALG_SOFTMAX_BWD ? 3 : (ALG == ALG_CE_ONEHOT || ALG == ALG_CE_BWD) ? 2 : 1;
+}
+
+// Consumer side of the ring: hands out, chunk after chunk, the two 128-bit vectors this thread owns
+// (vectors t and t + 512 of the chunk's 1024).
+struct RingReader {
+    uint32_t ring, full0, empty0;
+    int slot;
+    uint32_t phase;
+    volatile int* gave_up;
+    // Waits (bounded) for the next chunk, reads this thread's vectors as far as the chunk reaches
+    // (`fill` beyond, and when the wait ran out), and hands the slot back to the producer.
+    __device__ __forceinline__ void next(uint32_t chunk_bytes, float fill, float4& a, float4& b) {
+        a = make_float4(fill, fill, fill, fill);
+        b = a;
+        const uint32_t bar = full0 + 8u * slot;
+        bool ok = sbar_try(bar, phase);
+        if (!ok) ok = sbar_wait(bar, phase, gave_up);
+        const uint32_t off = 16u * threadIdx.x;
+        const uint32_t src = ring + slot * kChunkBytes + off;
+        if (ok && off < chunk_bytes)
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w) : "r"(src) : "memory");
+        if (ok && off + kChunkBytes / 2 < chunk_bytes)
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(b.x), "=f"(b.y), "=f"(b.z), "=f"(b.w) : "r"(src + kChunkBytes / 2) : "memory");
+        __syncwarp();
+        if ((threadIdx.x & 31) == 0) sbar_arrive(empty0 + 8u * slot);
+        if (++slot == kRingSlots) { slot = 0; phase ^= 1u; }
+    }
+};
+
+// The row holder of the streamed kernel: the register layout of a 512-thread CTA row, filled from
+// the ring, reductions over the consumer threads only, second operand from the ring.
+template <int ITEMS>
+struct StreamRow : StridedRow<kConsumers, ITEMS, true> {
+    static_assert(ITEMS % 8 == 0, "a chunk carries two vectors per thread");
+    static constexpr int kChunks = ITEMS / 8;
+    RingReader* ring;
+    CtaReducer rd;
+    uint32_t row_bytes;
+    __device__ __forceinline__ uint32_t chunk_bytes(int c) const {
+        const uint32_t start = static_cast<uint32_t>(c) * kChunkBytes;
+        return start >= row_bytes ? 0u : (row_bytes - start < static_cast<uint32_t>(kChunkBytes) ? row_bytes - start : kChunkBytes);
+    }
+    __device__ __forceinline__ void load_from_ring(float fill) {
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+            float4 a = make_float4(fill, fill, fill, fill), b = a;
+            const uint32_t cb = chunk_bytes(c);
+            if (cb) ring->next(cb, fill, a, b);
+            float* w = this->v + 8 * c;
+            w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+        }
+    }
+    __device__ __forceinline__ float rmax() { return rd.template run<true>(this->local_max(), kConsumers / 32); }
+    __device__ __forceinline__ float rsum(float partial) { return rd.template run<false>(partial, kConsumers / 32); }
+    template <class F> __device__ __forceinline__ void each2(const float*, F f) {
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+            const uint32_t cb = chunk_bytes(c);
+            if (cb) {
+                float4 a, b;
+                ring->next(cb, 0.0f, a, b);
+                const float* w = this->v + 8 * c;
+                const int j0 = this->first(2 * c), j1 = this->first(2 * c + 1);
+                if (j0 < this->cols) { f(j0, w[0], a.x); f(j0 + 1, w[1], a.y); f(j0 + 2, w[2], a.z); f(j0 + 3, w[3], a.w); }
+                if (j1 < this->cols) { f(j1, w[4], b.x); f(j1 + 1, w[5], b.y); f(j1 + 2, w[6], b.z); f(j1 + 3, w[7], b.w); }
+            }
+        }
+    }
+    template <class F> __device__ __forceinline__ void store2(float* __restrict__ out, const float*, F f) {
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+            const uint32_t cb = chunk_bytes(c);
+            if (cb) {
+                float4 a, b;
+                ring->next(cb, 0.0f, a, b);
+                const float* w = this->v + 8 * c;
+                const int j0 = this->first(2 * c), j1 = this->first(2 * c + 1);
+                if (j0 < this->cols) __stcs(reinterpret_cast<float4*>(out + j0), make_float4(f(j0, w[0], a.x), f(j0 + 1, w[1], a.y), f(j0 + 2, w[2], a.z), f(j0 + 3, w[3], a.w)));
+                if (j1 < this->cols) __stcs(reinterpret_cast<float4*>(out + j1), make_float4(f(j1, w[4], b.x), f(j1 + 1, w[5], b.y), f(j1 + 2, w[6], b.z), f(j1 + 3, w[7], b.w)));
+            }
+        }
+    }
+};
+
+template <int ALG, int ITEMS>
+__global__ void __launch_bounds__(kStreamThreads, 1) streamed_rows_kernel(RowArgs A, ReduceScratch* scratch, float* loss_out) {
+    extern __shared__ __align__(128) uint8_t ring_raw[];
+    __shared__ __align__(8) uint64_t bars[2 * kRingSlots];
+    __shared__ double red_d[33];
+    __shared__ float red_f[64];
+    __shared__ volatile int gave_up;
+    const uint32_t ring = smem_addr(ring_raw), full0 = smem_addr(bars), empty0 = full0 + 8u * kRingSlots;
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        gave_up = 0;
+        for (int s = 0; s < kRingSlots; ++s) { sbar_init(full0 + 8u * s, 1); sbar_init(empty0 + 8u * s, kConsumers / 32); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const uint32_t row_bytes = static_cast<uint32_t>(A.cols * sizeof(float));
+    const int nch = static_cast<int>((row_bytes + kChunkBytes - 1) / kChunkBytes);
+    double acc = 0.0;
+    bool poison = false;
+
+    if (tid >= kConsumers) {
+        // ------------------------------ producer ------------------------------
+        if (tid == kConsumers) {
+            int slot = 0;
+            uint32_t phase = 0, issued = 0;
+            bool ok = true;
+            for (int64_t row = blockIdx.x; row < A.rows && ok; row += gridDim.x) {
+                for (int s = 0; s < alg_streams<ALG>() && ok; ++s) {
+                    const float* src = (s == 0 ? A.x : A.t) + row * A.cols;
+                    for (int c = 0; c < nch; ++c) {
+                        if (!sbar_wait(empty0 + 8u * slot, phase ^ 1u, &gave_up)) { ok = false; break; }
+                        // (the consumers' reads of this slot are ordered before the copy by their arrival on
+                        // the empty barrier and this wait: release / acquire)
+                        const uint32_t left = row_bytes - static_cast<uint32_t>(c) * kChunkBytes;
+                        chunk_fetch(ring + slot * kChunkBytes, src + static_cast<int64_t>(c) * kChunkFloats, left < static_cast<uint32_t>(kChunkBytes) ? left : kChunkBytes,
+                                    full0 + 8u * slot);
+                        ++issued;
+                        if (++slot == kRingSlots) { slot = 0; phase ^= 1u; }
+                    }
+                }
+            }
+            if (!ok) {
+                // let the copies still in flight land before this CTA's shared memory is given up
+                const uint32_t pending = issued < static_cast<uint32_t>(kRingSlots) ? issued : kRingSlots;
+                int s = slot;
+                uint32_t ph = phase;
+                for (uint32_t i = 0; i < pending; ++i) {
+                    if (--s < 0) { s = kRingSlots - 1; ph ^= 1u; }
+                    for (uint32_t spin = 0; spin < (1u << 16) && !sbar_try(full0 + 8u * s, ph); ++spin) __nanosleep(64);
+                }
+            }
+        }
+    } else {
+        // ------------------------------ consumers ------------------------------
+        RingReader reader{ring, full0, empty0, 0, 0u, &gave_up};
+        StreamRow<ITEMS> r;
+        r.cols = static_cast<int>(A.cols);
+        r.t = tid;
+        r.ring = &reader;
+        r.rd = CtaReducer{red_f, 0, true};
+        r.row_bytes = row_bytes;
+        for (int64_t row = blockIdx.x; row < A.rows; row += gridDim.x) {
+            const float label = row_label<ALG>(A, row);
+            r.load_from_ring(ALG == ALG_SOFTMAX_BWD ? 0.0f : -INFINITY);
+            const float l = process_loaded<ALG>(r, A, row, label, poison);
+            if (alg_has_loss<ALG>()) acc += static_cast<double>(l);
+            // leave together: the OR over all consumers of "a wait ran out" is taken at a barrier
+            uint32_t any;
+            asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.or.pred p, 1, %2, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                         : "=r"(any) : "r"(static_cast<uint32_t>(gave_up)), "n"(kConsumers) : "memory");
+            if (any) { poison = true; break; }
+        }
+    }
+    __syncthreads();
+    if (alg_has_loss<ALG>()) {
+        if (poison && A.bad && tid == 0) *A.bad = 1;
+        int any_poison = __syncthreads_or(poison ? 1 : 0);
+        double total = block_sum(acc, red_d);
+        grid_finish(any_poison ? NAN : total, scratch, loss_out, 0.0f, false, red_d);
+    }
+}
+
+template <int ALG, int ITEMS>
+ctk_status launch_streamed(const RowArgs& A, ReduceScratch* s, float* loss_out, cudaStream_t st) {
+    auto k = streamed_rows_kernel<ALG, ITEMS>;
+    constexpr int smem = kRingSlots * kChunkBytes;
+    static bool attr_set = false;  // raises the opt-in shared-memory limit once per process, per instantiation
+    if (!attr_set) {
+        CTK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        attr_set = true;
+    }
+    const int64_t sms = ctk::sm_count();
+    const int64_t grid = A.rows < sms ? A.rows : sms;
+    k<<<static_cast<unsigned>(grid), kStreamThreads, smem, st>>>(A, s, loss_out);
+    return CTK_OK;
 }
 
 template <int ALG>
@@ -518,18 +891,23 @@ ctk_status launch_rows(const char* name, const RowArgs& A, float* loss_out, void
     }
     CTK_REQUIRE(A.x && A.cols < (int64_t(1) << 31), "row kernel: null input or cols >= 2^31");
     const int64_t c = A.cols;
-    const bool aligned_rows = (c % 4 == 0) && ((reinterpret_cast<uintptr_t>(A.x) & 15u) == 0) && (!A.out || (reinterpret_cast<uintptr_t>(A.out) & 15u) == 0);
+    // the streamed kernel moves rows with 16-byte bulk copies and 128-bit stores
+    const bool aligned_rows = (c % 4 == 0) && ((reinterpret_cast<uintptr_t>(A.x) & 15u) == 0) && (!A.out || (reinterpret_cast<uintptr_t>(A.out) & 15u) == 0) &&
+                              (alg_streams<ALG>() == 1 || (reinterpret_cast<uintptr_t>(A.t) & 15u) == 0);
     ctk_status rc = CTK_OK;
-    if (c <= 8) launch_reg<ALG, 8, 1>(A, s, loss_out, st);
-    else if (c <= 16) launch_reg<ALG, 16, 1>(A, s, loss_out, st);
-    else if (c <= 32) launch_reg<ALG, 32, 1>(A, s, loss_out, st);
-    else if (c <= 64) launch_reg<ALG, 32, 2>(A, s, loss_out, st);
-    else if (c <= 128) launch_reg<ALG, 32, 4>(A, s, loss_out, st);
-    else if (c <= 1024) rc = launch_cta_reg<ALG, 128, 8, false>(A, s, loss_out, st);
-    else if (c <= 4096) rc = launch_cta_reg<ALG, 256, 16, false>(A, s, loss_out, st);
-    else if (c <= 8192 && aligned_rows) rc = launch_cta_reg<ALG, 512, 16, true>(A, s, loss_out, st);
-    else if (c <= 16384 && aligned_rows) rc = launch_cta_reg<ALG, 512, 32, true>(A, s, loss_out, st);
-    else if (c <= 32768 && aligned_rows) rc = launch_cta_reg<ALG, 512, 64, true>(A, s, loss_out, st);
+    if (c <= 8) launch_tile<ALG, 8>(A, s, loss_out, st);
+    else if (c <= 16) launch_tile<ALG, 16>(A, s, loss_out, st);
+    else if (c <= 32) launch_warp<ALG, 1>(A, s, loss_out, st);
+    else if (c <= 64) launch_warp<ALG, 2>(A, s, loss_out, st);
+    else if (c <= 128) launch_warp<ALG, 4>(A, s, loss_out, st);
+    else if (c <= 256) launch_warp<ALG, 8>(A, s, loss_out, st);
+    else if (c <= 512) launch_warp<ALG, 16>(A, s, loss_out, st);
+    else if (c <= 1024) launch_warp<ALG, 32>(A, s, loss_out, st);
+    else if (c <= 2048) rc = launch_cta_reg<ALG, 128, 16>(A, s, loss_out, st);
+    else if (c <= 4096) rc = launch_cta_reg<ALG, 256, 16>(A, s, loss_out, st);
+    else if (c <= 8192 && aligned_rows) rc = launch_streamed<ALG, 16>(A, s, loss_out, st);
+    else if (c <= 16384 && aligned_rows) rc = launch_streamed<ALG, 32>(A, s, loss_out, st);
+    else if (c <= 32768 && aligned_rows) rc = launch_streamed<ALG, 64>(A, s, loss_out, st);
     else {
         int64_t cap = static_cast<int64_t>(ctk::sm_count()) * (c <= 12 * 1024 ? 4 : 1);
         int grid = static_cast<int>(A.rows < cap ? A.rows : cap);
@@ -555,6 +933,13 @@ ctk_status launch_rows(const char* name, const RowArgs& A, float* loss_out, void
 }  // namespace
 
 extern "C" {
+
+ctk_status ctk_rowwise_status(int* status) {
+    CTK_REQUIRE(status, "ctk_rowwise_status: null");
+    CTK_CUDA(cudaDeviceSynchronize());
+    CTK_CUDA(cudaMemcpyFromSymbol(status, g_row_status, sizeof(int)));
+    return CTK_OK;
+}
 
 ctk_status ctk_softmax_rows_f32(const float* x, float* y, int64_t rows, int64_t cols, void* stream) {
     CTK_REQUIRE((x && y) || rows == 0 || cols == 0, "ctk_softmax_rows_f32: null pointer");

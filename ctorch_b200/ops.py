@@ -182,6 +182,12 @@ def matmul_path(a, b, ta=False, tb=False, mode=-1):
     return lib.ctk_matmul_path(a.p, b.p, _i64(m), _i64(n), _i64(k), _i64(sa[0]), _i64(sa[1]), _i64(sb[0]), _i64(sb[1]), mode)
 
 
+def rowwise_status():
+    s = ctypes.c_int()
+    check(lib.ctk_rowwise_status(ctypes.byref(s)))
+    return s.value
+
+
 def set_matmul_pairing(pairing):
     """0: 256 x 256 tiles on CTA pairs where the shape allows (default); 1: single-CTA kernel only."""
     check(lib.ctk_set_matmul_pairing(int(pairing)))

@@ -168,6 +168,11 @@ ctk_status ctk_mae_f32(const float* a, const float* b, int64_t n, float* out, vo
 ctk_status ctk_mse_backward_f32(const float* p, const float* t, const float* g_device, float* dp, int64_t n, void* stream);
 ctk_status ctk_mae_backward_f32(const float* p, const float* t, const float* g_device, float* dp, int64_t n, void* stream);
 
+/* Synchronises the device and reads the row kernels' status word (no counterpart in the reference):
+ * 0, or 1 once a bounded wait of the long-row kernel (rows of 4097..32768 floats, streamed through
+ * shared memory with asynchronous copies) ran out; the outputs of that launch are then invalid and
+ * its loss, if any, is NaN. */
+ctk_status ctk_rowwise_status(int* status);
 /* Row softmax over the last dim of [rows, cols]: Softmax_BASIC_kernel
  * (src/kernels/CPU-BASIC/Softmax_BASIC_kernel.cpp:16-101) == Tensor::softmax row path
  * (src/Tensor.cpp:1712-1727). */

@@ -6,10 +6,12 @@ from conftest import assert_close, assert_exact
 
 pytestmark = pytest.mark.gpu
 
-# cols chosen to hit every kernel shape: sub-warp groups (<=8, <=16, <=32), register rows up to
-# 1024, shared-memory rows (1025..48K), and the re-reading path (>48K); odd values exercise the
-# unaligned-row loads.
-SHAPES = [(1, 1), (5, 3), (300, 10), (7, 16), (9, 31), (33, 100), (64, 1000), (17, 1024), (6, 1025), (5, 32000), (3, 50001)]
+# cols chosen to hit every kernel shape: sub-warp groups (<=8, <=16, <=32), CTA register rows up to
+# 4096, the streamed long-row kernel (4097..32768, rows 16-byte aligned: whole and ragged 8 KiB
+# chunks, more rows than SMs so every CTA walks several rows and the ring wraps), shared-memory rows
+# (unaligned, up to 48K) and the re-reading path (>48K); odd values exercise the unaligned-row loads.
+SHAPES = [(1, 1), (5, 3), (300, 10), (7, 16), (9, 31), (33, 100), (64, 1000), (17, 1024), (6, 1025), (700, 2048), (5, 4095),
+          (310, 4100), (160, 8196), (40, 16384), (21, 20000), (5, 32000), (300, 32768), (4, 5001), (3, 50001)]
 
 
 def _case(rows, cols, seed=0):
@@ -33,6 +35,7 @@ def test_softmax_forward_backward(cb, orc, rows, cols):
     # y*(g - dot) cancels: bound the error by the size of the terms, rel 1e-5 of max|g|*y
     refdx = orc.grad_unary("Softmax", L, g)
     assert np.abs(dx.numpy() - refdx).max() <= 1e-5 * np.abs(g).max() * ref.max() + 1e-9, "softmax backward"
+    assert cb.ops.rowwise_status() == 0, "a bounded wait in the long-row kernel ran out"
 
 
 @pytest.mark.parametrize("rows,cols", SHAPES)
@@ -48,6 +51,7 @@ def test_cross_entropy_forward_backward(cb, orc, rows, cols):
     loss, d = cb.ops.cross_entropy_fused(dL, dlab)
     assert_close(loss.numpy(), orc.ce(L, oh), 1e-5, 1e-6, "fused loss == one-hot reference")
     assert_close(d.numpy(), ref_d, 1e-5, 1e-7, "fused dlogits == one-hot reference")
+    assert cb.ops.rowwise_status() == 0, "a bounded wait in the long-row kernel ran out"
 
 
 def test_soft_targets_and_probability_clamp(cb, orc):
