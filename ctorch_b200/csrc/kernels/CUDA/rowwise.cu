@@ -55,6 +55,38 @@ __device__ __forceinline__ float fast_exp(float x) {
     return y;
 }
 
+// ---- mbarrier / bulk-copy helpers of the two pipelined kernels ------------------------------------------
+constexpr uint32_t kStreamWaitLimit = 1u << 22;
+
+__device__ int g_row_status = 0;  // set when a bounded wait of a pipelined row kernel ran out
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void sbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void sbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool sbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool sbar_wait(uint32_t bar, uint32_t parity, volatile int* gave_up) {
+    for (uint32_t i = 0; i < kStreamWaitLimit; ++i) {
+        if (sbar_try(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *gave_up) return false;
+    }
+    *gave_up = 1;
+    atomicExch(&g_row_status, 1);
+    return false;
+}
+__device__ __forceinline__ void chunk_fetch(uint32_t dst, const float* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar) : "memory");
+}
 // ---- row holders -----------------------------------------------------------------------------
 // Every holder exposes: load(src), rmax(), rsum(partial), each(f) / update(f) / store(out, f) over
 // the elements this thread owns, each2 / store2 that also hand f the matching element of a second
@@ -382,15 +414,27 @@ __device__ __forceinline__ float process_row(Row& r, const RowArgs& A, int64_t r
     return process_loaded<ALG>(r, A, row, label, poison);
 }
 
+// CTAs of `kernel` that are resident on the whole device at once (asked of the runtime once per
+// instantiation): the grid of the persistent forms, so that no CTA waits for another to finish.
+template <class K>
+int64_t resident_ctas(K kernel, int threads, size_t smem) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) != cudaSuccess || per_sm < 1) per_sm = 1;
+    return static_cast<int64_t>(ctk::sm_count()) * per_sm;
+}
+
 // ---- short rows (cols <= 16): a thread per row ------------------------------------------------------
-// A CTA takes 256 consecutive rows, i.e. one contiguous block of 256 * cols floats: the block is
+// A CTA takes 512 consecutive rows, i.e. one contiguous block of 512 * cols floats: the block is
 // copied to shared memory with coalesced 128-bit loads, every thread then owns one row in registers
 // (no shuffles, no barriers inside the row), results go back to the shared tile and leave with
-// coalesced 128-bit stores.  A thread walks its row starting at column (row mod cols), so that the
-// threads of a warp hit different banks although their rows are cols words apart.
-constexpr int kTileRows = 256;
+// coalesced 128-bit stores.  Where cols is a multiple of 4 (rows 16, 32, 48 or 64 bytes apart would
+// put a warp's threads on 2 to 8 banks) a thread walks its row starting at column (row mod cols),
+// which spreads the warp over the banks again.
+constexpr int kTileThreads = 256;
+constexpr int kTileRowsPerThread = 2;  // two rows per thread: twice the bytes in flight per resident thread
+constexpr int kTileRows = kTileThreads * kTileRowsPerThread;
 
-template <int MAXC>
+template <int MAXC, bool ROT>
 struct TileRow {
     static constexpr bool kCached = true;
     float v[MAXC];
@@ -398,6 +442,7 @@ struct TileRow {
     const float* aux;   // this thread's row in the second operand's tile
     int cols, rot;
     __device__ __forceinline__ int col(int k) const {
+        if (!ROT) return k;
         const int j = k + rot;
         return j >= cols ? j - cols : j;
     }
@@ -439,7 +484,7 @@ struct TileRow {
     __device__ __forceinline__ float rsum(float partial) const { return partial; }
     __device__ __forceinline__ bool pick(int c, float& w) const {
         // element c sits in register (c - rot) mod cols
-        int k = c - rot;
+        int k = ROT ? c - rot : c;
         if (k < 0) k += cols;
 #pragma unroll
         for (int i = 0; i < MAXC; ++i)
@@ -452,54 +497,138 @@ struct TileRow {
 __device__ __forceinline__ void tile_in(float* __restrict__ dst, const float* __restrict__ src, int n) {
     if ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
         const int n4 = n >> 2;
-        for (int i = threadIdx.x; i < n4; i += kTileRows) reinterpret_cast<float4*>(dst)[i] = __ldcs(reinterpret_cast<const float4*>(src) + i);
-        for (int i = (n4 << 2) + threadIdx.x; i < n; i += kTileRows) dst[i] = __ldcs(src + i);
+        for (int i = threadIdx.x; i < n4; i += kTileThreads) reinterpret_cast<float4*>(dst)[i] = __ldcs(reinterpret_cast<const float4*>(src) + i);
+        for (int i = (n4 << 2) + threadIdx.x; i < n; i += kTileThreads) dst[i] = __ldcs(src + i);
     } else {
-        for (int i = threadIdx.x; i < n; i += kTileRows) dst[i] = __ldcs(src + i);
+        for (int i = threadIdx.x; i < n; i += kTileThreads) dst[i] = __ldcs(src + i);
     }
 }
 __device__ __forceinline__ void tile_out(float* __restrict__ dst, const float* __restrict__ src, int n) {
     if ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
         const int n4 = n >> 2;
-        for (int i = threadIdx.x; i < n4; i += kTileRows) __stcs(reinterpret_cast<float4*>(dst) + i, reinterpret_cast<const float4*>(src)[i]);
-        for (int i = (n4 << 2) + threadIdx.x; i < n; i += kTileRows) __stcs(dst + i, src[i]);
+        for (int i = threadIdx.x; i < n4; i += kTileThreads) __stcs(reinterpret_cast<float4*>(dst) + i, reinterpret_cast<const float4*>(src)[i]);
+        for (int i = (n4 << 2) + threadIdx.x; i < n; i += kTileThreads) __stcs(dst + i, src[i]);
     } else {
-        for (int i = threadIdx.x; i < n; i += kTileRows) __stcs(dst + i, src[i]);
+        for (int i = threadIdx.x; i < n; i += kTileThreads) __stcs(dst + i, src[i]);
     }
 }
 
-template <int ALG, int MAXC>
-__global__ void __launch_bounds__(kTileRows) tile_rows_kernel(RowArgs A, ReduceScratch* scratch, float* loss_out) {
-    extern __shared__ __align__(16) float tiles[];  // [256 * cols] x / out, then [256 * cols] second operand
+// Bulk store of a finished tile, shared -> global, and the waits that go with it.
+__device__ __forceinline__ void tile_store_async(float* dst, uint32_t src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(reinterpret_cast<uint64_t>(dst)), "r"(src), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void tile_stores_done_reading() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tile_stores_done() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// A resident grid walks the tiles.  PIPE: whole tiles move with bulk asynchronous copies through two
+// buffers -- tile i+1 is on its way in and tile i-1 on its way out while tile i is worked on -- so a
+// handful of resident CTAs keep HBM busy (the kernel needs ~50 registers per thread, which rules out
+// hiding latency by occupancy).  That needs 16-byte aligned operands; otherwise, and for the ragged
+// last tile, a tile moves with ordinary coalesced loads and stores.
+template <int ALG, int MAXC, bool ROT, bool PIPE>
+__global__ void __launch_bounds__(kTileThreads) tile_rows_kernel(RowArgs A, ReduceScratch* scratch, float* loss_out) {
+    extern __shared__ __align__(128) float tiles[];  // per buffer: [512 * cols] x / out, then [512 * cols] second operand
     __shared__ double red_d[33];
+    __shared__ __align__(8) uint64_t full[2];
+    __shared__ volatile int gave_up;
     const int cols = static_cast<int>(A.cols);
-    float* tile_x = tiles;
-    float* tile_t = tiles + kTileRows * cols;
-    TileRow<MAXC> r;
+    constexpr int kOperands = alg_two_operands<ALG>() ? 2 : 1;
+    const int buf_floats = kTileRows * cols * kOperands;
+    const uint32_t tile_bytes = static_cast<uint32_t>(kTileRows * cols * sizeof(float));
+    TileRow<MAXC, ROT> r;
     r.cols = cols;
-    r.rot = static_cast<int>(threadIdx.x) % cols;
-    r.mine = tile_x + threadIdx.x * cols;
-    r.aux = tile_t + threadIdx.x * cols;
+    r.rot = ROT ? static_cast<int>(threadIdx.x) % cols : 0;
     double acc = 0.0;
     bool poison = false;
-    const int64_t ntiles = (A.rows + kTileRows - 1) / kTileRows;
-    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    const int64_t full_tiles = A.rows / kTileRows;
+    const int64_t all_tiles = (A.rows + kTileRows - 1) / kTileRows;
+
+    auto labels_of = [&](int64_t tile, float (&lab)[kTileRowsPerThread]) {
+#pragma unroll
+        for (int u = 0; u < kTileRowsPerThread; ++u) {
+            const int64_t row = tile * kTileRows + threadIdx.x + u * kTileThreads;
+            lab[u] = row < A.rows ? row_label<ALG>(A, row) : 0.0f;
+        }
+    };
+    // the rows of one tile that is in shared memory, in place
+    auto work = [&](float* tile_x, int64_t row0, int rows_here, const float (&lab)[kTileRowsPerThread]) {
+#pragma unroll
+        for (int u = 0; u < kTileRowsPerThread; ++u) {
+            const int lr = static_cast<int>(threadIdx.x) + u * kTileThreads;  // rows t and t + 256: same banks per warp
+            if (lr < rows_here) {
+                r.mine = tile_x + lr * cols;
+                r.aux = tile_x + kTileRows * cols + lr * cols;
+                r.load(nullptr);
+                const float l = process_loaded<ALG>(r, A, row0 + lr, lab[u], poison);
+                if (alg_has_loss<ALG>()) acc += static_cast<double>(l);
+            }
+        }
+    };
+    // one tile with ordinary loads and stores, through buffer 0
+    auto plain_tile = [&](int64_t tile) {
         const int64_t row0 = tile * kTileRows;
         const int rows_here = static_cast<int>(A.rows - row0 < kTileRows ? A.rows - row0 : kTileRows);
         const int n = rows_here * cols;
-        const bool live = static_cast<int>(threadIdx.x) < rows_here;
-        const float label = live ? row_label<ALG>(A, row0 + threadIdx.x) : 0.0f;
-        tile_in(tile_x, A.x + row0 * cols, n);
-        if (alg_two_operands<ALG>()) tile_in(tile_t, A.t + row0 * cols, n);
+        float lab[kTileRowsPerThread];
+        labels_of(tile, lab);
+        tile_in(tiles, A.x + row0 * cols, n);
+        if (kOperands == 2) tile_in(tiles + kTileRows * cols, A.t + row0 * cols, n);
         __syncthreads();
-        if (live) {
-            r.load(nullptr);
-            const float l = process_loaded<ALG>(r, A, row0 + threadIdx.x, label, poison);
-            if (alg_has_loss<ALG>()) acc += static_cast<double>(l);
+        work(tiles, row0, rows_here, lab);
+        __syncthreads();
+        if (alg_has_output<ALG>()) tile_out(A.out + row0 * cols, tiles, n);
+        __syncthreads();
+    };
+
+    if (PIPE) {
+        auto fetch = [&](int64_t tile, int b) {  // thread 0 only
+            const uint32_t bar = smem_addr(&full[b]);
+            float* dst = tiles + b * buf_floats;
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(tile_bytes * kOperands) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(smem_addr(dst)), "l"(reinterpret_cast<uint64_t>(A.x + tile * kTileRows * cols)), "r"(tile_bytes), "r"(bar) : "memory");
+            if (kOperands == 2)
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(smem_addr(dst + kTileRows * cols)), "l"(reinterpret_cast<uint64_t>(A.t + tile * kTileRows * cols)), "r"(tile_bytes), "r"(bar) : "memory");
+        };
+        const int64_t first = blockIdx.x;
+        if (threadIdx.x == 0) {
+            gave_up = 0;
+            sbar_init(smem_addr(&full[0]), 1);
+            sbar_init(smem_addr(&full[1]), 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            if (first < full_tiles) fetch(first, 0);
         }
         __syncthreads();
-        if (alg_has_output<ALG>()) tile_out(A.out + row0 * cols, tile_x, n);
+        float label[kTileRowsPerThread], next_label[kTileRowsPerThread];
+        if (first < full_tiles) labels_of(first, label);
+        int it = 0;
+        for (int64_t tile = first; tile < full_tiles; tile += gridDim.x, ++it) {
+            const int b = it & 1;
+            float* tile_x = tiles + b * buf_floats;
+            const int64_t next = tile + gridDim.x;
+            if (next < full_tiles) {
+                // the other buffer is still being read by the store of the previous tile: let that finish
+                if (threadIdx.x == 0) { tile_stores_done_reading(); fetch(next, b ^ 1); }
+                labels_of(next, next_label);
+            }
+            const bool landed = sbar_wait(smem_addr(&full[b]), static_cast<uint32_t>(it >> 1) & 1u, &gave_up);
+            if (__syncthreads_or(landed ? 0 : 1)) { poison = true; break; }
+            work(tile_x, tile * kTileRows, kTileRows, label);
+            if (alg_has_output<ALG>()) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // results visible to the bulk store
+            __syncthreads();
+            if (alg_has_output<ALG>() && threadIdx.x == 0) tile_store_async(A.out + tile * kTileRows * cols, smem_addr(tile_x), tile_bytes);
+#pragma unroll
+            for (int u = 0; u < kTileRowsPerThread; ++u) label[u] = next_label[u];
+        }
+        if (threadIdx.x == 0) tile_stores_done_reading();
         __syncthreads();
+        // the ragged last tile: one CTA, ordinary loads and stores
+        if (all_tiles > full_tiles && static_cast<int64_t>(blockIdx.x) == full_tiles % gridDim.x && !poison) plain_tile(full_tiles);
+        if (threadIdx.x == 0) tile_stores_done();
+    } else {
+        for (int64_t tile = blockIdx.x; tile < all_tiles; tile += gridDim.x) plain_tile(tile);
     }
     if (alg_has_loss<ALG>()) {
         if (poison && A.bad) *A.bad = 1;
@@ -509,17 +638,32 @@ __global__ void __launch_bounds__(kTileRows) tile_rows_kernel(RowArgs A, ReduceS
     }
 }
 
-template <int ALG, int MAXC>
-void launch_tile(const RowArgs& A, ReduceScratch* s, float* loss_out, cudaStream_t st) {
-    int64_t grid = (A.rows + kTileRows - 1) / kTileRows;
-    if (alg_has_loss<ALG>()) {
-        const int64_t resident = static_cast<int64_t>(ctk::sm_count()) * 8;
-        if (grid > resident) grid = resident;
-        if (grid > kMaxReduceBlocks) grid = kMaxReduceBlocks;
+template <int ALG, int MAXC, bool ROT, bool PIPE>
+ctk_status launch_tile_form(const RowArgs& A, ReduceScratch* s, float* loss_out, cudaStream_t st) {
+    auto k = tile_rows_kernel<ALG, MAXC, ROT, PIPE>;
+    constexpr int kOperands = alg_two_operands<ALG>() ? 2 : 1;
+    const size_t smem = static_cast<size_t>(kTileRows) * A.cols * sizeof(float) * kOperands * (PIPE ? 2 : 1);
+    static bool attr_set = false;  // up to 128 KiB (two operands, two buffers, 16 columns): above the default limit
+    if (!attr_set) {
+        CTK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kTileRows * MAXC * kOperands * (PIPE ? 2 : 1) * static_cast<int>(sizeof(float))));
+        attr_set = true;
     }
-    if (grid > 0x7fffffff) grid = 0x7fffffff;
-    const size_t smem = static_cast<size_t>(kTileRows) * A.cols * sizeof(float) * (alg_two_operands<ALG>() ? 2 : 1);
-    tile_rows_kernel<ALG, MAXC><<<static_cast<unsigned>(grid), kTileRows, smem, st>>>(A, s, loss_out);
+    int64_t grid = (A.rows + kTileRows - 1) / kTileRows;
+    static int64_t resident[MAXC + 1] = {0};  // by column count (it sets the shared-memory need)
+    if (!resident[A.cols]) resident[A.cols] = resident_ctas(k, kTileThreads, smem);
+    if (grid > resident[A.cols]) grid = resident[A.cols];
+    if (alg_has_loss<ALG>() && grid > kMaxReduceBlocks) grid = kMaxReduceBlocks;
+    k<<<static_cast<unsigned>(grid), kTileThreads, smem, st>>>(A, s, loss_out);
+    return CTK_OK;
+}
+
+template <int ALG, int MAXC>
+ctk_status launch_tile(const RowArgs& A, ReduceScratch* s, float* loss_out, cudaStream_t st) {
+    const bool aligned = ((reinterpret_cast<uintptr_t>(A.x) & 15u) == 0) && (!alg_has_output<ALG>() || (reinterpret_cast<uintptr_t>(A.out) & 15u) == 0) &&
+                         (!alg_two_operands<ALG>() || (reinterpret_cast<uintptr_t>(A.t) & 15u) == 0);
+    const bool rot = A.cols % 4 == 0;
+    if (aligned) return rot ? launch_tile_form<ALG, MAXC, true, true>(A, s, loss_out, st) : launch_tile_form<ALG, MAXC, false, true>(A, s, loss_out, st);
+    return rot ? launch_tile_form<ALG, MAXC, true, false>(A, s, loss_out, st) : launch_tile_form<ALG, MAXC, false, false>(A, s, loss_out, st);
 }
 
 // ---- rows up to 1024 columns: a warp per row ---------------------------------------------------------
@@ -532,17 +676,33 @@ constexpr int kWarpRowThreads = 128;
 template <int ALG, int ITEMS, bool VEC>
 __global__ void __launch_bounds__(kWarpRowThreads) warp_rows_kernel(RowArgs A, ReduceScratch* scratch, float* loss_out) {
     __shared__ double red_d[33];
-    WarpRow<ITEMS, VEC> r;
-    r.cols = static_cast<int>(A.cols);
-    r.t = threadIdx.x & 31;
+    WarpRow<ITEMS, VEC> r, next;
+    r.cols = next.cols = static_cast<int>(A.cols);
+    r.t = next.t = threadIdx.x & 31;
     constexpr int kWarps = kWarpRowThreads / 32;
     const int64_t first = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
     const int64_t step = static_cast<int64_t>(gridDim.x) * kWarps;
     double acc = 0.0;
     bool poison = false;
+    // The loads of the warp's next row are issued before the current row is worked on, so a warp
+    // always has a row in flight (the persistent, loss-carrying forms loop here; the others run once).
+    float label = 0.0f;
+    if (first < A.rows) {
+        label = row_label<ALG>(A, first);
+        r.load(A.x + first * A.cols);
+    }
     for (int64_t row = first; row < A.rows; row += step) {
-        const float l = process_row<ALG>(r, A, row, A.x + row * A.cols, poison);
+        const int64_t nrow = row + step;
+        float nlabel = 0.0f;
+        if (nrow < A.rows) {
+            nlabel = row_label<ALG>(A, nrow);
+            next.load(A.x + nrow * A.cols);
+        }
+        const float l = process_loaded<ALG>(r, A, row, label, poison);
         if (alg_has_loss<ALG>()) acc += static_cast<double>(l);
+#pragma unroll
+        for (int it = 0; it < ITEMS; ++it) r.v[it] = next.v[it];
+        label = nlabel;
     }
     if (alg_has_loss<ALG>()) {
         if (poison && A.bad) *A.bad = 1;
@@ -560,23 +720,29 @@ bool rows_aligned(const RowArgs& A) {
            (!alg_two_operands<ALG>() || (reinterpret_cast<uintptr_t>(A.t) & 15u) == 0);
 }
 
-template <int ALG, int ITEMS>
-void launch_warp(const RowArgs& A, ReduceScratch* s, float* loss_out, cudaStream_t st) {
+template <int ALG, int ITEMS, bool VEC>
+void launch_warp_form(const RowArgs& A, ReduceScratch* s, float* loss_out, cudaStream_t st) {
     constexpr int kWarps = kWarpRowThreads / 32;
+    auto k = warp_rows_kernel<ALG, ITEMS, VEC>;
     int64_t grid = (A.rows + kWarps - 1) / kWarps;
     if (alg_has_loss<ALG>()) {
-        const int64_t resident = static_cast<int64_t>(ctk::sm_count()) * (ITEMS > 16 ? 8 : 16);
+        static const int64_t resident = resident_ctas(k, kWarpRowThreads, 0);
         if (grid > resident) grid = resident;
         if (grid > kMaxReduceBlocks) grid = kMaxReduceBlocks;
     }
     if (grid > 0x7fffffff) grid = 0x7fffffff;
+    k<<<static_cast<unsigned>(grid), kWarpRowThreads, 0, st>>>(A, s, loss_out);
+}
+
+template <int ALG, int ITEMS>
+void launch_warp(const RowArgs& A, ReduceScratch* s, float* loss_out, cudaStream_t st) {
     if constexpr (ITEMS % 4 == 0) {
         if (rows_aligned<ALG>(A)) {
-            warp_rows_kernel<ALG, ITEMS, true><<<static_cast<unsigned>(grid), kWarpRowThreads, 0, st>>>(A, s, loss_out);
+            launch_warp_form<ALG, ITEMS, true>(A, s, loss_out, st);
             return;
         }
     }
-    warp_rows_kernel<ALG, ITEMS, false><<<static_cast<unsigned>(grid), kWarpRowThreads, 0, st>>>(A, s, loss_out);
+    launch_warp_form<ALG, ITEMS, false>(A, s, loss_out, st);
 }
 
 template <int ALG, class Row>
@@ -629,18 +795,23 @@ __global__ void __launch_bounds__(THREADS) cta_reg_rows_kernel(RowArgs A, Reduce
     }
 }
 
-template <int ALG, int THREADS, int ITEMS>
-ctk_status launch_cta_reg(const RowArgs& A, ReduceScratch* s, float* loss_out, cudaStream_t st) {
-    const bool vec = rows_aligned<ALG>(A);
+template <int ALG, int THREADS, int ITEMS, bool VEC>
+void launch_cta_reg_form(const RowArgs& A, ReduceScratch* s, float* loss_out, cudaStream_t st) {
+    auto k = cta_reg_rows_kernel<ALG, THREADS, ITEMS, VEC>;
     int64_t grid = A.rows;
     if (alg_has_loss<ALG>()) {
-        const int64_t resident = static_cast<int64_t>(ctk::sm_count()) * (2048 / THREADS);
+        static const int64_t resident = resident_ctas(k, THREADS, 0);
         if (grid > resident) grid = resident;
         if (grid > kMaxReduceBlocks) grid = kMaxReduceBlocks;
     }
     if (grid > 0x7fffffff) grid = 0x7fffffff;
-    if (vec) cta_reg_rows_kernel<ALG, THREADS, ITEMS, true><<<static_cast<unsigned>(grid), THREADS, 0, st>>>(A, s, loss_out);
-    else cta_reg_rows_kernel<ALG, THREADS, ITEMS, false><<<static_cast<unsigned>(grid), THREADS, 0, st>>>(A, s, loss_out);
+    k<<<static_cast<unsigned>(grid), THREADS, 0, st>>>(A, s, loss_out);
+}
+
+template <int ALG, int THREADS, int ITEMS>
+ctk_status launch_cta_reg(const RowArgs& A, ReduceScratch* s, float* loss_out, cudaStream_t st) {
+    if (rows_aligned<ALG>(A)) launch_cta_reg_form<ALG, THREADS, ITEMS, true>(A, s, loss_out, st);
+    else launch_cta_reg_form<ALG, THREADS, ITEMS, false>(A, s, loss_out, st);
     return CTK_OK;
 }
 
@@ -660,37 +831,6 @@ constexpr int kChunkBytes = 16384;
 constexpr int kChunkFloats = kChunkBytes / 4;
 constexpr int kRingSlots = 13;
 constexpr int kStreamThreads = kConsumers + 32;
-constexpr uint32_t kStreamWaitLimit = 1u << 22;
-
-__device__ int g_row_status = 0;  // set when a bounded wait of the streamed kernel ran out
-
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-__device__ __forceinline__ void sbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void sbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool sbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool sbar_wait(uint32_t bar, uint32_t parity, volatile int* gave_up) {
-    for (uint32_t i = 0; i < kStreamWaitLimit; ++i) {
-        if (sbar_try(bar, parity)) return true;
-        if ((i & 1023u) == 1023u && *gave_up) return false;
-    }
-    *gave_up = 1;
-    atomicExch(&g_row_status, 1);
-    return false;
-}
-__device__ __forceinline__ void chunk_fetch(uint32_t dst, const float* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar) : "memory");
-}
 // How many operand rows per row of the problem pass through the ring, and from where.
 template <int ALG> __host__ __device__ constexpr int alg_streams() {
     return ALG == ALG_SOFTMAX_BWD ? 3 : (ALG == ALG_CE_ONEHOT || ALG == ALG_CE_BWD) ? 2 : 1;
@@ -748,6 +888,38 @@ struct StreamRow : StridedRow<kConsumers, ITEMS, true> {
     }
     __device__ __forceinline__ float rmax() { return rd.template run<true>(this->local_max(), kConsumers / 32); }
     __device__ __forceinline__ float rsum(float partial) { return rd.template run<false>(partial, kConsumers / 32); }
+    // Index-label CrossEntropy forward needs only max, sum of exponentials and the labelled logit:
+    // they are folded chunk by chunk as the chunks land (a running maximum, the running sum rescaled
+    // when the maximum moves), nothing is kept, every slot goes back to the producer at once and the
+    // copies never pause for a whole row's arithmetic.  Returns this thread's share of the loss.
+    __device__ __forceinline__ float online_ce(int c, bool& poison) {
+        const bool ok = c >= 0 && c < this->cols;
+        if (!ok) poison = true;
+        float m = -INFINITY, ssum = 0.0f, xc = 0.0f;
+        bool mine = false;
+#pragma unroll
+        for (int ch = 0; ch < kChunks; ++ch) {
+            const uint32_t cb = chunk_bytes(ch);
+            if (cb) {
+                float4 a, b;
+                ring->next(cb, -INFINITY, a, b);
+                const float cm = fmaxf(fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)), fmaxf(fmaxf(b.x, b.y), fmaxf(b.z, b.w)));
+                const float mn = fmaxf(m, cm);
+                if (mn > -INFINITY) {
+                    const float part = ((fast_exp(a.x - mn) + fast_exp(a.y - mn)) + (fast_exp(a.z - mn) + fast_exp(a.w - mn))) +
+                                       ((fast_exp(b.x - mn) + fast_exp(b.y - mn)) + (fast_exp(b.z - mn) + fast_exp(b.w - mn)));
+                    ssum = ssum * fast_exp(m - mn) + part;
+                    m = mn;
+                }
+                const int k = c & 3, j0 = this->first(2 * ch), j1 = this->first(2 * ch + 1);
+                if (j0 == (c & ~3)) { xc = k == 0 ? a.x : k == 1 ? a.y : k == 2 ? a.z : a.w; mine = true; }
+                if (j1 == (c & ~3)) { xc = k == 0 ? b.x : k == 1 ? b.y : k == 2 ? b.z : b.w; mine = true; }
+            }
+        }
+        const float row_max = rd.template run<true>(m, kConsumers / 32);
+        const float s = rd.template run<false>(m > -INFINITY ? ssum * fast_exp(m - row_max) : 0.0f, kConsumers / 32);
+        return (ok && mine) ? -logf(fmaxf(fast_exp(xc - row_max) * (1.0f / s), 1e-10f)) : 0.0f;
+    }
     template <class F> __device__ __forceinline__ void each2(const float*, F f) {
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) {
@@ -841,8 +1013,13 @@ __global__ void __launch_bounds__(kStreamThreads, 1) streamed_rows_kernel(RowArg
         r.row_bytes = row_bytes;
         for (int64_t row = blockIdx.x; row < A.rows; row += gridDim.x) {
             const float label = row_label<ALG>(A, row);
-            r.load_from_ring(ALG == ALG_SOFTMAX_BWD ? 0.0f : -INFINITY);
-            const float l = process_loaded<ALG>(r, A, row, label, poison);
+            float l;
+            if constexpr (ALG == ALG_CE_INDEX) {
+                l = r.online_ce(static_cast<int>(label), poison);
+            } else {
+                r.load_from_ring(ALG == ALG_SOFTMAX_BWD ? 0.0f : -INFINITY);
+                l = process_loaded<ALG>(r, A, row, label, poison);
+            }
             if (alg_has_loss<ALG>()) acc += static_cast<double>(l);
             // leave together: the OR over all consumers of "a wait ran out" is taken at a barrier
             uint32_t any;
@@ -895,8 +1072,9 @@ ctk_status launch_rows(const char* name, const RowArgs& A, float* loss_out, void
     const bool aligned_rows = (c % 4 == 0) && ((reinterpret_cast<uintptr_t>(A.x) & 15u) == 0) && (!A.out || (reinterpret_cast<uintptr_t>(A.out) & 15u) == 0) &&
                               (alg_streams<ALG>() == 1 || (reinterpret_cast<uintptr_t>(A.t) & 15u) == 0);
     ctk_status rc = CTK_OK;
-    if (c <= 8) launch_tile<ALG, 8>(A, s, loss_out, st);
-    else if (c <= 16) launch_tile<ALG, 16>(A, s, loss_out, st);
+    if (c <= 8) rc = launch_tile<ALG, 8>(A, s, loss_out, st);
+    else if (c <= 12) rc = launch_tile<ALG, 12>(A, s, loss_out, st);
+    else if (c <= 16) rc = launch_tile<ALG, 16>(A, s, loss_out, st);
     else if (c <= 32) launch_warp<ALG, 1>(A, s, loss_out, st);
     else if (c <= 64) launch_warp<ALG, 2>(A, s, loss_out, st);
     else if (c <= 128) launch_warp<ALG, 4>(A, s, loss_out, st);
