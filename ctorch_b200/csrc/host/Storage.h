@@ -10,7 +10,9 @@
 // commit_record, t(), get_grad) cost nothing until someone writes.
 #pragma once
 #include <cstring>
+#include <map>
 #include <memory>
+#include <mutex>
 
 #include "Ctools.h"
 #include "Ctorch_Error.h"
@@ -20,11 +22,73 @@ namespace ctorch {
 
 void cuda_check(int status, const char* what);  // throws on a non-zero ctk_status
 
+// The hi/lo split of a buffer's contents that the 3xTF32 MatMul made on first use, kept with the
+// buffer so that later products of the same values (the same view, or its transpose) reuse it.
+// `view` identifies the 2-D view it was made for; `valid` is the flag the kernel library fills in.
+// Split buffers are large (twice the operand) and come and go with every activation of every step.
+// They are plain device allocations, outside the stream-ordered pool the tensors live in (mixed in
+// there, their different sizes and lifetimes fragment it until it has to map new memory in the
+// middle of a step), parked here by size when their operand dies and handed out again.
+// Reuse is ordered by the compute stream: a parked buffer may still be read by queued kernels, and
+// whoever gets it next only touches it with kernels queued after them.
+class SplitBufferCache {
+    std::mutex mu_;
+    std::multimap<size_t, void*> free_;
+    size_t parked_bytes_ = 0;
+    static constexpr size_t kMaxParked = size_t(16) << 30;
+
+public:
+    static SplitBufferCache& instance() {
+        static SplitBufferCache* c = new SplitBufferCache();  // never destroyed: outlives every tensor
+        return *c;
+    }
+    static size_t rounded(size_t bytes) { return (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1); }
+    void* get(size_t bytes) {
+        bytes = rounded(bytes);
+        {
+            std::lock_guard<std::mutex> lock(mu_);
+            auto it = free_.find(bytes);
+            if (it != free_.end()) {
+                void* p = it->second;
+                free_.erase(it);
+                parked_bytes_ -= bytes;
+                return p;
+            }
+        }
+        void* p = nullptr;
+        cuda_check(ctk_malloc_longlived(&p, bytes), "Storage: split buffer");  // a miss: warm-up only
+        return p;
+    }
+    void put(void* p, size_t bytes) {
+        bytes = rounded(bytes);
+        {
+            std::lock_guard<std::mutex> lock(mu_);
+            if (parked_bytes_ + bytes <= kMaxParked) {
+                free_.emplace(bytes, p);
+                parked_bytes_ += bytes;
+                return;
+            }
+        }
+        ctk_free_longlived(p);
+    }
+};
+
+struct KeptSplit {
+    void* buf = nullptr;
+    size_t bytes = 0;
+    int valid = 0;
+    int64_t view[4] = {0, 0, 0, 0};  // element offset, outer extent, inner (contiguous) extent, outer pitch
+    ~KeptSplit() {
+        if (buf) SplitBufferCache::instance().put(buf, bytes);
+    }
+};
+
 class Storage {
     struct Block {
         void* ptr = nullptr;
         size_t bytes = 0;
         DeviceType device = DeviceType::kCPU;
+        std::unique_ptr<KeptSplit> split;  // dropped whenever the buffer is about to be written
         Block(size_t b, DeviceType d) : bytes(b), device(d) {
             if (b == 0) return;
             if (d == DeviceType::kCUDA) cuda_check(ctk_malloc(&ptr, b), "Storage: device allocation");
@@ -98,9 +162,25 @@ public:
         }
         return s;
     }
-    // Detach from other holders of the same buffer before a write.
+    // Detach from other holders of the same buffer before a write (every write path of Tensor goes
+    // through here, so this is also where a kept split of the old contents is dropped).
     void make_unique() {
-        if (_data && _data.use_count() > 1) *this = clone();
+        if (!_data) return;
+        if (_data.use_count() > 1) *this = clone();
+        else _data->split.reset();
+    }
+    // The kept split of this buffer for the given 2-D view, created (invalid) if there is none or it
+    // was made for another view.  Device buffers only.
+    KeptSplit* kept_split(int64_t offset, int64_t outer, int64_t inner, int64_t pitch, size_t bytes) const {
+        if (!_data || _device != DeviceType::kCUDA) return nullptr;
+        KeptSplit* k = _data->split.get();
+        if (k && k->view[0] == offset && k->view[1] == outer && k->view[2] == inner && k->view[3] == pitch) return k;
+        auto fresh = std::make_unique<KeptSplit>();
+        fresh->buf = SplitBufferCache::instance().get(bytes);
+        fresh->bytes = bytes;
+        fresh->view[0] = offset; fresh->view[1] = outer; fresh->view[2] = inner; fresh->view[3] = pitch;
+        _data->split = std::move(fresh);
+        return _data->split.get();
     }
     // Same contents on another device.
     Storage to(DeviceType device) const {

@@ -74,6 +74,7 @@ public:
     DType dtype() const { return _dtype; }
     bool is_contiguous() const;
     bool is_cleared() const { return _storage.empty(); }
+    const Storage& storage() const { return _storage; }
     void clear_storage() { _storage.clear(); }
     bool has_pending_record() const { return !record_committed_; }
     void commit_pending_record();

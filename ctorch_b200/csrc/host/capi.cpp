@@ -59,6 +59,16 @@ public:
     Tensor last_logits;
     bool keep_logits = false;
     uint64_t steps_done = 0;
+    // Input staging: up to two uploaded batches wait on the device, each with an event that says
+    // its copy has landed, so the upload of batch k+1 (on its own stream) overlaps step k.
+    struct Staged {
+        Tensor x, labels;
+        void* ready = nullptr;
+        int64_t batch = -1;
+    };
+    Staged staged[2];
+    uint64_t n_staged = 0, n_consumed = 0;
+    void* copy_stream = nullptr;
 
     MlpTrainer(int n_layers, const int64_t* d, const float* params, float lr_) : dims(d, d + n_layers + 1), lr(lr_) {
         const float* p = params;
@@ -83,6 +93,9 @@ public:
         if (ev_comm) ctk_event_destroy(ev_comm);
         if (pinned_loss) ctk_free_host(pinned_loss);
         if (pinned_x) ctk_free_host(pinned_x);
+        for (Staged& s : staged)
+            if (s.ready) ctk_event_destroy(s.ready);
+        if (copy_stream) ctk_stream_destroy(copy_stream);
     }
 
     int64_t n_params() const {
@@ -178,6 +191,54 @@ public:
         Tensor y(ShapeTag{}, {static_cast<size_t>(batch), classes}, DType::kFloat, DeviceType::kCUDA, false);
         cuda_check(ctk_onehot_f32(labels.data<float>(), batch, static_cast<int64_t>(classes), y.data<float>(), st), "one-hot");
         return step(x, y);  // ends with a stream synchronisation: the caller's buffers are free again
+    }
+
+    // Starts the upload of one batch (HOST pixels and labels) on the copy stream and returns at once
+    // when the buffers are page-locked; the caller keeps them unchanged until the step that consumes
+    // the batch has returned.  Pageable buffers are copied through the staging buffers before returning.
+    void stage_host(const float* x_host, const float* labels_host, int64_t batch) {
+        if (n_staged - n_consumed >= 2) throw std::runtime_error("cth_mlp_stage_host: two batches are already staged; run a step first");
+        const size_t in = static_cast<size_t>(dims.front());
+        Staged& s = staged[n_staged % 2];
+        if (!copy_stream) cuda_check(ctk_stream_create_ex(&copy_stream, 1), "copy stream");
+        if (!s.ready) cuda_check(ctk_event_create(&s.ready), "event");
+        if (s.batch != batch) {
+            s.x = Tensor(ShapeTag{}, {static_cast<size_t>(batch), in}, DType::kFloat, DeviceType::kCUDA, false);
+            s.labels = Tensor(ShapeTag{}, {static_cast<size_t>(batch)}, DType::kFloat, DeviceType::kCUDA, false);
+            s.batch = batch;
+            cuda_check(ctk_device_sync(), "staging allocation");  // the allocation is ordered on another stream than the copies
+        }
+        int px = 0, pl = 0;
+        ctk_host_is_pinned(x_host, &px);
+        ctk_host_is_pinned(labels_host, &pl);
+        void* saved = current_stream();
+        set_current_stream(copy_stream);
+        try {
+            if (px) cuda_check(ctk_memcpy_h2d(s.x.data<float>(), x_host, static_cast<size_t>(batch) * in * sizeof(float), copy_stream), "input upload");
+            else s.x.copy_from_host(x_host, static_cast<size_t>(batch) * in);
+            if (pl) cuda_check(ctk_memcpy_h2d(s.labels.data<float>(), labels_host, static_cast<size_t>(batch) * sizeof(float), copy_stream), "label upload");
+            else s.labels.copy_from_host(labels_host, static_cast<size_t>(batch));
+        } catch (...) {
+            set_current_stream(saved);
+            throw;
+        }
+        set_current_stream(saved);
+        cuda_check(ctk_event_record(s.ready, copy_stream), "record");
+        ++n_staged;
+    }
+
+    // The training step on the oldest staged batch.
+    float step_staged() {
+        if (n_consumed == n_staged) throw std::runtime_error("cth_mlp_step_staged: no batch is staged");
+        Staged& s = staged[n_consumed % 2];
+        ++n_consumed;
+        const size_t classes = static_cast<size_t>(dims.back());
+        void* st = current_stream();
+        cuda_check(ctk_stream_wait_event(st, s.ready), "wait for the upload");
+        Tensor y(ShapeTag{}, {static_cast<size_t>(s.batch), classes}, DType::kFloat, DeviceType::kCUDA, false);
+        const Tensor& labels = s.labels;
+        cuda_check(ctk_onehot_f32(labels.data<float>(), s.batch, static_cast<int64_t>(classes), y.data<float>(), st), "one-hot");
+        return step(s.x, y);
     }
 
     void get_params(float* out) {
@@ -374,6 +435,12 @@ int cth_mlp_keep_logits(void* m, int keep) {
 }
 int cth_mlp_step_host(void* m, const float* x_host, const float* labels_host, int64_t batch, float* loss) {
     return guarded([&] { *loss = static_cast<MlpTrainer*>(m)->step_host(x_host, labels_host, batch); });
+}
+int cth_mlp_stage_host(void* m, const float* x_host, const float* labels_host, int64_t batch) {
+    return guarded([&] { static_cast<MlpTrainer*>(m)->stage_host(x_host, labels_host, batch); });
+}
+int cth_mlp_step_staged(void* m, float* loss) {
+    return guarded([&] { *loss = static_cast<MlpTrainer*>(m)->step_staged(); });
 }
 int cth_mlp_step_device(void* m, void* x, void* onehot, float* loss) {
     return guarded([&] { *loss = static_cast<MlpTrainer*>(m)->step(*T(x), *T(onehot)); });

@@ -9,6 +9,8 @@
 // device kernel evaluates the NumPy-style broadcast instead.
 #include "Ctorch_Error.h"
 #include "Tensor.h"
+#include <cstdlib>
+
 #include "ctorch_b200.h"
 #include "kernels.h"
 
@@ -105,9 +107,34 @@ Tensor MatMul_CUDA_kernel(const Tensor& a, const Tensor& b) {
     if (a.shape()[1] != b.shape()[0]) Ctorch_Error::throwException(ErrorPlatform::kCUDA, ErrorType::DIMENSION, "MatMul: inner dimensions do not match");
     const int64_t m = static_cast<int64_t>(a.shape()[0]), k = static_cast<int64_t>(a.shape()[1]), n = static_cast<int64_t>(b.shape()[1]);
     Tensor r(ShapeTag{}, {static_cast<size_t>(m), static_cast<size_t>(n)}, a.dtype(), DeviceType::kCUDA, false);
-    cuda_check(ctk_matmul_f32(a.data<float>(), b.data<float>(), r.data<float>(), m, n, k, static_cast<int64_t>(a.strides()[0]),
-                              static_cast<int64_t>(a.strides()[1]), static_cast<int64_t>(b.strides()[0]), static_cast<int64_t>(b.strides()[1]), -1,
-                              nullptr, current_stream()),
+    const int64_t sa0 = static_cast<int64_t>(a.strides()[0]), sa1 = static_cast<int64_t>(a.strides()[1]);
+    const int64_t sb0 = static_cast<int64_t>(b.strides()[0]), sb1 = static_cast<int64_t>(b.strides()[1]);
+    // CTORCH_KEEP_SPLITS=0 in the environment switches the kept splits off (they cost up to twice the
+    // operand's size in device memory for as long as the operand lives).
+    static const bool keep_splits = [] {
+        const char* e = std::getenv("CTORCH_KEEP_SPLITS");
+        return !(e && e[0] == '0');
+    }();
+    if (!keep_splits || ctk_get_matmul_mode() != CTK_MATMUL_3XTF32 || m < 2 || n < 2 || k < 2) {
+        cuda_check(ctk_matmul_f32(a.data<float>(), b.data<float>(), r.data<float>(), m, n, k, sa0, sa1, sb0, sb1, -1, nullptr, current_stream()), who);
+        return r;
+    }
+    // 3xTF32: the hi/lo split of each operand stays with the operand's buffer (Storage drops it when
+    // the buffer is written), so X in X.W and X^T.dY, dY in dY.W^T and X^T.dY, and the weights the
+    // tape holds are each split once.  The view is named by its contiguous ("inner") extent, the
+    // other extent and its pitch, so a t() view of the same memory finds the same split.
+    auto kept = [&](const Tensor& t, int64_t mn, int64_t s_mn, int64_t s_k) -> KeptSplit* {
+        int64_t outer, inner, pitch;
+        if (s_k == 1 && s_mn >= k) { outer = mn; inner = k; pitch = s_mn; }
+        else if (s_mn == 1 && s_k >= mn) { outer = k; inner = mn; pitch = s_k; }
+        else return nullptr;
+        return t.storage().kept_split(static_cast<int64_t>(t.storage_offset()), outer, inner, pitch, ctk_matmul_split_bytes(mn, k));
+    };
+    KeptSplit* ka = kept(a, m, sa0, sa1);
+    // one split per buffer: when both operands are views of the same buffer only A's is kept
+    KeptSplit* kb = (b.storage().raw() == a.storage().raw()) ? nullptr : kept(b, n, sb1, sb0);
+    cuda_check(ctk_matmul_3xtf32_kept_f32(a.data<float>(), b.data<float>(), r.data<float>(), m, n, k, sa0, sa1, sb0, sb1, ka ? ka->buf : nullptr,
+                                          ka ? &ka->valid : nullptr, kb ? kb->buf : nullptr, kb ? &kb->valid : nullptr, nullptr, current_stream()),
                who);
     return r;
 }

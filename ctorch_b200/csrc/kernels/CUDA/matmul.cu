@@ -1047,8 +1047,15 @@ ctk_status ctk_matmul_status(int* status) {
     return CTK_OK;
 }
 
-ctk_status ctk_matmul_f32(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k, int64_t sa0,
-                          int64_t sa1, int64_t sb0, int64_t sb1, int mode, void* workspace, void* stream) {
+// A caller-kept split of one operand: `buf` holds hi then lo ([outer, pitch] each), `valid` says
+// whether it matches the operand's current contents (0: the product fills it and sets 1).
+struct KeptSplit {
+    void* buf;
+    int* valid;
+};
+
+static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k, int64_t sa0,
+                              int64_t sa1, int64_t sb0, int64_t sb1, int mode, void* workspace, KeptSplit ka, KeptSplit kb, void* stream) {
     CTK_REQUIRE(m >= 0 && n >= 0 && k >= 0, "ctk_matmul_f32: negative extent");
     if (m == 0 || n == 0) return CTK_OK;
     CTK_REQUIRE(c, "ctk_matmul_f32: null output");
@@ -1075,18 +1082,22 @@ ctk_status ctk_matmul_f32(const float* a, const float* b, float* c, int64_t m, i
     const float *a_hi = A.p, *a_lo = A.p, *b_hi = B.p, *b_lo = B.p;
     int64_t a_ld = A.ld, b_ld = B.ld;
     if (terms == 3) {
-        void* ws = workspace;
-        const size_t need = ctk_matmul_workspace_bytes(m, n, k, md);
-        if (!ws) {
-            ctk_status rc = device_scratch(1, need, &ws);
-            if (rc) return rc;
-        }
-        float* w = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(ws) + 255u) & ~static_cast<uintptr_t>(255u));
         const int64_t a_pitch = (A.inner() + 3) / 4 * 4, b_pitch = (B.inner() + 3) / 4 * 4;
-        float* ah = w;
-        float* al = ah + A.outer() * a_pitch;
-        float* bh = al + A.outer() * a_pitch;
-        float* bl = bh + B.outer() * b_pitch;
+        float *ah, *al, *bh, *bl;
+        auto aligned256 = [](void* p) { return reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(p) + 255u) & ~static_cast<uintptr_t>(255u)); };
+        if (!ka.buf || !kb.buf) {
+            void* ws = workspace;
+            if (!ws) {
+                ctk_status rc = device_scratch(1, ctk_matmul_workspace_bytes(m, n, k, md), &ws);
+                if (rc) return rc;
+            }
+            ah = aligned256(ws);
+            al = ah + A.outer() * a_pitch;
+            bh = al + A.outer() * a_pitch;
+            bl = bh + B.outer() * b_pitch;
+        }
+        if (ka.buf) { ah = aligned256(ka.buf); al = ah + A.outer() * a_pitch; }
+        if (kb.buf) { bh = aligned256(kb.buf); bl = bh + B.outer() * b_pitch; }
         auto split = [&](const tc::Operand& O, float* h, float* l, int64_t pitch) -> ctk_status {
             const bool vec = (reinterpret_cast<uintptr_t>(O.p) & 15u) == 0 && O.ld % 4 == 0 && O.inner() % 4 == 0;
             if (vec) {
@@ -1100,8 +1111,14 @@ ctk_status ctk_matmul_f32(const float* a, const float* b, float* c, int64_t m, i
             return CTK_OK;
         };
         ctk_status rc2;
-        if ((rc2 = split(A, ah, al, a_pitch))) return rc2;
-        if ((rc2 = split(B, bh, bl, b_pitch))) return rc2;
+        if (!(ka.buf && ka.valid && *ka.valid)) {
+            if ((rc2 = split(A, ah, al, a_pitch))) return rc2;
+            if (ka.buf && ka.valid) *ka.valid = 1;
+        }
+        if (!(kb.buf && kb.valid && *kb.valid)) {
+            if ((rc2 = split(B, bh, bl, b_pitch))) return rc2;
+            if (kb.buf && kb.valid) *kb.valid = 1;
+        }
         a_hi = ah; a_lo = al; b_hi = bh; b_lo = bl;
         a_ld = a_pitch; b_ld = b_pitch;
     }
@@ -1140,6 +1157,30 @@ ctk_status ctk_matmul_f32(const float* a, const float* b, float* c, int64_t m, i
     if (timed) cudaEventRecord(stop_ev, st);
     return rc;
 #undef CTK_TC
+}
+
+ctk_status ctk_matmul_f32(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k, int64_t sa0,
+                          int64_t sa1, int64_t sb0, int64_t sb1, int mode, void* workspace, void* stream) {
+    return matmul_impl(a, b, c, m, n, k, sa0, sa1, sb0, sb1, mode, workspace, KeptSplit{nullptr, nullptr}, KeptSplit{nullptr, nullptr}, stream);
+}
+
+// hi + lo of an operand with extents (mn, k), whichever of the two is contiguous, + alignment slack.
+size_t ctk_matmul_split_bytes(int64_t mn, int64_t k) { return static_cast<size_t>(2 * padded_elems(mn, k)) * sizeof(float) + 256; }
+
+// The 3xTF32 product with the hi/lo split of either operand kept by the caller between calls.
+// An operand that enters several products unchanged (an activation in its layer's forward product
+// and again, transposed, in the weight-gradient product; an upstream gradient in both backward
+// products) is then split once instead of once per product: 12 bytes of HBM traffic per element saved
+// each time.  a_split / b_split: device buffers of ctk_matmul_split_bytes(m, k) / (n, k) bytes, or
+// NULL to use the workspace for that operand; *a_valid / *b_valid: 0 = fill the buffer in this call
+// (set to 1 on return), 1 = the buffer already holds the split of exactly these values, viewed with
+// exactly this shape and these strides.  Keeping that promise is the caller's job: the buffer must
+// be discarded when the operand's memory is written.
+ctk_status ctk_matmul_3xtf32_kept_f32(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k, int64_t sa0,
+                                      int64_t sa1, int64_t sb0, int64_t sb1, void* a_split, int* a_valid, void* b_split,
+                                      int* b_valid, void* workspace, void* stream) {
+    CTK_REQUIRE((!a_split || a_valid) && (!b_split || b_valid), "ctk_matmul_3xtf32_kept_f32: a split buffer needs its valid flag");
+    return matmul_impl(a, b, c, m, n, k, sa0, sa1, sb0, sb1, CTK_MATMUL_3XTF32, workspace, KeptSplit{a_split, a_valid}, KeptSplit{b_split, b_valid}, stream);
 }
 
 // 3xTF32 MatMul that allocates nothing: same arguments and same result as ctk_matmul_f32 in mode

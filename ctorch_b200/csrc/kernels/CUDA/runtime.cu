@@ -133,6 +133,20 @@ ctk_status ctk_free(void* p) {
     CTK_CUDA(cudaFreeAsync(p, static_cast<cudaStream_t>(0)));
     return CTK_OK;
 }
+// Long-lived buffers (caches that a caller manages itself): plain cudaMalloc / cudaFree, outside the
+// stream-ordered pool, so they neither fragment it nor pin its high-water mark.  Both synchronise.
+ctk_status ctk_malloc_longlived(void** p, size_t bytes) {
+    CTK_REQUIRE(p, "ctk_malloc_longlived: null out pointer");
+    *p = nullptr;
+    if (bytes == 0) return CTK_OK;
+    CTK_CUDA(cudaMalloc(p, bytes));
+    return CTK_OK;
+}
+ctk_status ctk_free_longlived(void* p) {
+    if (!p) return CTK_OK;
+    CTK_CUDA(cudaFree(p));
+    return CTK_OK;
+}
 ctk_status ctk_malloc_host(void** p, size_t bytes) {
     CTK_REQUIRE(p, "ctk_malloc_host: null out pointer");
     *p = nullptr;

@@ -217,6 +217,16 @@ class MlpTrainer:
         _chk(lib.cth_mlp_step_host(self.h, x.ctypes.data_as(_vp), labels.ctypes.data_as(_vp), ctypes.c_int64(x.shape[0]), ctypes.byref(loss)))
         return loss.value
 
+    def stage_host(self, x, labels):
+        """Starts the upload of a batch; returns at once for page-locked arrays."""
+        _chk(lib.cth_mlp_stage_host(self.h, x.ctypes.data_as(_vp), labels.ctypes.data_as(_vp), ctypes.c_int64(x.shape[0])))
+
+    def step_staged(self):
+        """The step on the oldest staged batch."""
+        loss = ctypes.c_float()
+        _chk(lib.cth_mlp_step_staged(self.h, ctypes.byref(loss)))
+        return loss.value
+
     def step_device(self, x, onehot):
         loss = ctypes.c_float()
         _chk(lib.cth_mlp_step_device(self.h, x.h, onehot.h, ctypes.byref(loss)))

@@ -73,6 +73,10 @@ ctk_status ctk_device_sync(void);
 ctk_status ctk_device_info(int* sm_count, size_t* total_bytes, size_t* free_bytes);
 
 ctk_status ctk_malloc(void** device_ptr, size_t bytes);      /* pooled; bytes==0 gives NULL    */
+/* For buffers a caller keeps and recycles itself over many steps: plain device allocations outside
+ * the pool (they would fragment it).  Both calls synchronise the device. */
+ctk_status ctk_malloc_longlived(void** device_ptr, size_t bytes);
+ctk_status ctk_free_longlived(void* device_ptr);
 ctk_status ctk_free(void* device_ptr);
 ctk_status ctk_malloc_host(void** pinned_ptr, size_t bytes); /* page-locked staging memory     */
 ctk_status ctk_free_host(void* pinned_ptr);
@@ -222,6 +226,22 @@ size_t ctk_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k, int mode);
 ctk_status ctk_matmul_f32(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
                           int64_t sa0, int64_t sa1, int64_t sb0, int64_t sb1, int mode,
                           void* workspace, void* stream);
+/* No counterpart in the reference.  The 3xTF32 product with the hi/lo split of either operand kept
+ * by the caller between calls: an operand that enters several products unchanged (an activation
+ * in its layer's forward product and, transposed, in the weight-gradient product; an upstream
+ * gradient in both backward products; the weights a tape holds) is split once, not once per
+ * product.  a_split / b_split: device buffers of ctk_matmul_split_bytes(m, k) / (n, k) bytes, or
+ * NULL (that operand is split into the workspace as usual).  *a_valid / *b_valid: 0 = fill the
+ * buffer in this call (set to 1 on return); 1 = it already holds the split of exactly these
+ * values viewed with exactly these extents and strides (a transposed view of the same memory
+ * counts as the same).  The caller discards the buffer when the operand's memory is written.
+ * Operands the tensor cores cannot take (no unit stride) run on the CUDA cores; the flags are
+ * then left alone. */
+size_t ctk_matmul_split_bytes(int64_t mn, int64_t k);
+ctk_status ctk_matmul_3xtf32_kept_f32(const float* a, const float* b, float* c, int64_t m, int64_t n,
+                                      int64_t k, int64_t sa0, int64_t sa1, int64_t sb0, int64_t sb1,
+                                      void* a_split, int* a_valid, void* b_split, int* b_valid,
+                                      void* workspace, void* stream);
 /* No counterpart in the reference.  The 3xTF32 product for callers that must not allocate device
  * memory (inside a stream capture, under an arena allocator that owns the whole GPU, or in a loop
  * that cannot afford a workspace growing under it): identical arguments and result to

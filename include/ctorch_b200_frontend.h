@@ -73,6 +73,14 @@ int cth_mlp_set_comm(void* mlp, void* comm);
 int cth_mlp_keep_logits(void* mlp, int keep);
 /* x_host [batch, dims[0]] and labels_host [batch] (class indices as floats) in HOST memory. */
 int cth_mlp_step_host(void* mlp, const float* x_host, const float* labels_host, int64_t batch, float* loss);
+/* The same step with the upload taken off the critical path, as an input pipeline would run it:
+ * cth_mlp_stage_host starts the host-to-device copy of one batch on a copy stream and returns (page-locked
+ * buffers; pageable ones are copied before it returns); cth_mlp_step_staged runs the step on the
+ * oldest staged batch once its copy has landed.  Up to two batches may be staged, so calling
+ * stage(k+1) before step_staged() of batch k overlaps the upload of k+1 with the compute of k.
+ * A staged host buffer must stay unchanged until the step that consumes it has returned. */
+int cth_mlp_stage_host(void* mlp, const float* x_host, const float* labels_host, int64_t batch);
+int cth_mlp_step_staged(void* mlp, float* loss);
 /* x and onehot are device tensors ([batch, dims[0]] and [batch, classes]). */
 int cth_mlp_step_device(void* mlp, void* x, void* onehot, float* loss);
 int cth_mlp_n_params(void* mlp, int64_t* n);

@@ -301,3 +301,67 @@ def test_step_on_device_resident_inputs_equals_step_from_host(F):
         la, lb = a.step_host(x[0, 0], lab[0, 0]), b.step_device(X, Y)
         assert la == lb
     assert_exact(a.params(), b.params(), "same weights either way")
+
+
+def test_staged_uploads_equal_steps_from_host(F, cb):
+    """stage_host / step_staged (upload of the next batch overlapped with the current step) against
+    step_host on the same sequence of batches: pageable and page-locked host buffers, two batches
+    staged ahead, a third refused."""
+    from ctorch_b200.device import PinnedArray
+    dims = [64, 32, 10]
+    rng = np.random.default_rng(21)
+    _, _, p = _mlp_case(dims, 16, 1, 9, 10)
+    batches = [(rng.uniform(0, 1, (16, 64)).astype(np.float32), rng.integers(0, 10, 16).astype(np.float32)) for _ in range(4)]
+    a, b = F.MlpTrainer(dims, p, 0.01), F.MlpTrainer(dims, p, 0.01)
+    ref = [a.step_host(x, l) for x, l in batches]
+    pinned = []
+    for x, l in batches[:2]:
+        px, pl = PinnedArray(x.shape), PinnedArray(l.shape)
+        px.array[...] = x
+        pl.array[...] = l
+        pinned.append((px, pl))
+    b.stage_host(pinned[0][0].array, pinned[0][1].array)
+    b.stage_host(pinned[1][0].array, pinned[1][1].array)
+    with pytest.raises(F.FrontendError):
+        b.stage_host(batches[2][0], batches[2][1])   # only two may wait
+    got = [b.step_staged()]
+    b.stage_host(batches[2][0], batches[2][1])       # pageable
+    got.append(b.step_staged())
+    b.stage_host(batches[3][0], batches[3][1])
+    got.append(b.step_staged())
+    got.append(b.step_staged())
+    with pytest.raises(F.FrontendError):
+        b.step_staged()                              # nothing staged
+    assert got == ref
+    assert_exact(a.params(), b.params(), "same weights either way")
+
+
+def test_kept_operand_splits_follow_every_write(F, orc):
+    """The 3xTF32 MatMul keeps the hi/lo split of an operand with the operand's buffer.  A write to
+    the buffer (fill, in-place SGD, upload) must drop it, a copy made before the write must keep
+    seeing the old values, and transposed views and both operands from one buffer must work."""
+    rng = np.random.default_rng(31)
+    x = rng.standard_normal((40, 24)).astype(np.float32)
+    w = rng.standard_normal((24, 36)).astype(np.float32)
+    X, W = dev(F, x), dev(F, w)
+    y1 = X.matmul(W).numpy()
+    y1_again = X.matmul(W).numpy()            # both splits reused
+    assert_exact(y1, y1_again, "reusing kept splits changes nothing")
+    assert_matmul_close(y1, orc.matmul(x, w), 1e-4, "first product")
+    W_old = W.copy()                          # shares the buffer and its split
+    W.sgd_update_(dev(F, np.ones_like(w)), 0.5)   # in place: W <- W - 0.5
+    assert_matmul_close(X.matmul(W).numpy(), orc.matmul(x, w - 0.5), 1e-4, "product after the in-place update")
+    assert_exact(X.matmul(W_old).numpy(), y1, "the copy made before the write still multiplies the old values")
+    W.fill(2.0)
+    assert_matmul_close(X.matmul(W).numpy(), orc.matmul(x, np.full_like(w, 2.0)), 1e-4, "product after fill")
+    # the transposed view finds the split of the plain one and the other way round
+    g = rng.standard_normal((40, 36)).astype(np.float32)
+    G = dev(F, g)
+    assert_matmul_close(X.t().matmul(G).numpy(), orc.matmul(x, g, ta=True), 1e-4, "X^T.G with X's kept split")
+    assert_matmul_close(G.matmul(W_old.t()).numpy(), orc.matmul(g, w, tb=True), 1e-4, "G.W^T with W's kept split")
+    assert_matmul_close(G.t().matmul(X).numpy(), orc.matmul(g, x, ta=True), 1e-4, "G^T.X")
+    # both operands views of one buffer
+    assert_matmul_close(X.matmul(X.t()).numpy(), orc.matmul(x, x, tb=True), 1e-4, "X.X^T")
+    sq = rng.standard_normal((32, 32)).astype(np.float32)
+    S = dev(F, sq)
+    assert_matmul_close(S.matmul(S).numpy(), orc.matmul(sq, sq), 1e-4, "S.S")
