@@ -193,6 +193,7 @@ def run_mlp(args, cp):
     from ctorch_b200 import frontend as F
     from ctorch_b200.device import PinnedArray
     cb.check(cb.lib.ctk_set_device(local_rank))
+    cb.ops.set_matmul_pairing(args.pairing)
     F.set_quiet(True)
     peaks = measured_peaks()
 
@@ -314,6 +315,7 @@ def run_single_op(args):
     """The single-op sweeps (one GPU): prints one JSON line per measurement."""
     import ctorch_b200 as cb
     cb.check(cb.lib.ctk_set_device(0))
+    cb.ops.set_matmul_pairing(args.pairing)
     peaks = measured_peaks()
 
     def timeit(fn, iters, warm=3):
@@ -481,6 +483,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--pairing", type=int, default=0, choices=[0, 1], help="MatMul tile scheduling: 0 = CTA pairs where possible (default), 1 = single-CTA kernel only")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="mlp", choices=["mlp", "elementwise", "rowwise", "matmul", "kernel"])
     ap.add_argument("--case", default="matmul_3xtf32_4096x4096x4096", help="for --workload kernel")
