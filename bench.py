@@ -93,6 +93,11 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
+    def wait_first_sample(self, limit_s=10.0):
+        t0 = time.time()
+        while self.proc and not self.lines and time.time() - t0 < limit_s:
+            time.sleep(0.05)
+
     def stop(self):
         if not self.proc:
             return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
@@ -197,6 +202,10 @@ def run_mlp(args, cp):
     F.set_quiet(True)
     peaks = measured_peaks()
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+
     comm = None
     if world > 1:
         from ctorch_b200 import dp
@@ -246,9 +255,10 @@ def run_mlp(args, cp):
         barrier()
         return max_over_ranks(ms), launches, loss, prof
 
-    sampler = ClockSampler(local_rank)
+    # nvidia-smi takes a few hundred ms to come up (and holds driver locks while it does): it was started
+    # before the model was built, and timing begins only once it has delivered its first sample
     if rank == 0:
-        sampler.start()
+        sampler.wait_first_sample()
     ms_dev, launches, loss_dev, prof = timed(lambda: trainer.step_device(X, Y), True)
     clocks = sampler.stop() if rank == 0 else None
     # End to end, from HOST buffers.  Plain form: upload, step, loss read-back, one after the other.

@@ -115,11 +115,17 @@ void AutoDiff::commit_record(Tensor& output) {
     pending_records.erase(output_id);
 }
 
+void AutoDiff::Node::materialize_grad() {
+    if (grad_is_zero && grad) grad->zero();
+    grad_is_zero = false;
+}
+
 void AutoDiff::zero_grad(Tensor& t) {
     if (t.id() == 0) return;
     std::lock_guard<std::mutex> lock(records_mutex);
     auto it = id_to_node.find(t.id());
-    if (it != id_to_node.end() && it->second && it->second->grad) it->second->grad->zero();
+    // (:502-510 zero-fills here; the fill is deferred, see Node::grad_is_zero)
+    if (it != id_to_node.end() && it->second && it->second->grad) it->second->grad_is_zero = true;
 }
 
 void AutoDiff::update_requires_grad(Tensor& t, bool requires_grad) {
@@ -137,7 +143,10 @@ Tensor AutoDiff::get_grad(const Tensor* t) {
     if (!t || t->id() == 0) return Tensor();
     std::lock_guard<std::mutex> lock(records_mutex);
     auto it = id_to_node.find(t->id());
-    if (it != id_to_node.end() && it->second && it->second->requires_grad && it->second->grad) return Tensor(*it->second->grad);
+    if (it != id_to_node.end() && it->second && it->second->requires_grad && it->second->grad) {
+        it->second->materialize_grad();
+        return Tensor(*it->second->grad);
+    }
     return Tensor(ShapeTag{}, t->shape(), t->dtype(), t->device(), true);  // no gradient: zeros of the input's shape (:203-246)
 }
 
@@ -145,6 +154,7 @@ Tensor* AutoDiff::grad_buffer(const Tensor& t) {
     std::lock_guard<std::mutex> lock(records_mutex);
     auto it = id_to_node.find(t.id());
     if (it == id_to_node.end() || !it->second || !it->second->grad) return nullptr;
+    it->second->materialize_grad();
     return it->second->grad.get();
 }
 
@@ -398,6 +408,7 @@ void AutoDiff::backward(Tensor& root, Tensor grad_output) {
         // The root gradient lives where the root lives (the default Tensor(1.0f) is a host tensor).
         Tensor g0 = check_and_adjust_grad_shape(grad_output, root.sizes(), root.device());
         root_node->grad = std::make_unique<Tensor>(g0.device() == root.device() ? g0 : g0.to(root.device()));
+        root_node->grad_is_zero = false;
     }
 
     std::unordered_set<Node*> visited;
@@ -407,28 +418,39 @@ void AutoDiff::backward(Tensor& root, Tensor grad_output) {
 
     for (Node* node : order) {
         if (!node->requires_grad || !node->grad) continue;
+        node->materialize_grad();  // an upstream gradient that was only flagged zero is read as zeros
         for (size_t input_id : node->input_ids) {
             auto in_it = id_to_node.find(input_id);
             if (in_it == id_to_node.end() || !in_it->second || !in_it->second->requires_grad) continue;
             Node& input_node = *in_it->second;
-            bool skip = false;
-            Tensor val = rule(node, input_id, input_node, skip);
-            if (skip) continue;
-            Tensor adjusted = check_and_adjust_grad_shape(val, input_node.tensor->sizes(), input_node.tensor->device());
-            if (adjusted.device() != input_node.tensor->device()) adjusted = adjusted.to(input_node.tensor->device());
-            if (!input_node.grad) {
-                // First contribution to a gradient that does not exist yet: the reference allocates
-                // zeros and adds (:1202-1208, :1868-1907); 0 + x is x, so the value is adopted as is
-                // (shared until someone writes) and a full zero-fill + read-modify-write pass is saved.
-                input_node.grad = std::make_unique<Tensor>(adjusted);
+            // The contribution, alone in its scope so that no temporary still shares its buffer when
+            // it becomes the gradient (a hook that reduces the gradient in place would otherwise
+            // have to detach it with a full copy).
+            std::unique_ptr<Tensor> contribution;
+            {
+                bool skip = false;
+                Tensor val = rule(node, input_id, input_node, skip);
+                if (skip) continue;
+                Tensor adjusted = check_and_adjust_grad_shape(val, input_node.tensor->sizes(), input_node.tensor->device());
+                if (adjusted.device() != input_node.tensor->device()) adjusted = adjusted.to(input_node.tensor->device());
+                contribution = std::make_unique<Tensor>(std::move(adjusted));
+            }
+            if (!input_node.grad || input_node.grad_is_zero) {
+                // First contribution to a gradient that does not exist yet or was zeroed: the
+                // reference allocates / keeps zeros and adds (:1202-1208, :1868-1907); 0 + x is x, so
+                // the value is adopted as is and a zero-fill + read-modify-write pass is saved.
+                input_node.grad = std::move(contribution);
+                input_node.grad_is_zero = false;
             } else if (input_node.grad->device() == DeviceType::kCUDA) {
                 Tensor& acc = *input_node.grad;
-                cuda_check(ctk_accumulate_f32(acc.data<float>(), adjusted.data<float>(), static_cast<int64_t>(acc.numel()), current_stream()), "gradient accumulate");
+                const Tensor& add = *contribution;
+                cuda_check(ctk_accumulate_f32(acc.data<float>(), add.data<float>(), static_cast<int64_t>(acc.numel()), current_stream()), "gradient accumulate");
             } else {
                 // host gradients only exist for host 0-D operands (Tensor(float) inputs)
                 Tensor& acc = *input_node.grad;
+                const Tensor& add = *contribution;
                 float* gp = acc.data<float>();
-                const float* ap = adjusted.data<float>();
+                const float* ap = add.data<float>();
                 for (size_t i = 0; i < acc.numel(); ++i) gp[i] += ap[i];
             }
             Tensor& g = *input_node.grad;

@@ -40,6 +40,11 @@ class AutoDiff {
         size_t tensor_id;
         std::unique_ptr<Tensor> tensor;  // value at registration time (shares storage until someone writes)
         std::unique_ptr<Tensor> grad;
+        // zero_grad() only raises this flag: the zeros are written when someone reads the gradient
+        // before backward has replaced it (backward adopts its first contribution instead of adding
+        // it to zeros: 0 + x is x).
+        bool grad_is_zero = false;
+        void materialize_grad();
         std::vector<size_t> input_ids;
         op operation = op::Add;
         int op_param_i = 0;

@@ -136,9 +136,23 @@ public:
     }
 
     // One training step on device-resident inputs; returns the loss read back from the device.
+    // Live device memory of one step, estimated generously: per layer the product, the biased sum,
+    // the activation and their three gradients, [batch, width] each, plus parameters, gradients and the
+    // tape's snapshot.  The pool is grown to that once, before the first step of a batch size.
+    int64_t reserved_batch = -1;
+    void reserve_for(int64_t batch) {
+        if (batch == reserved_batch) return;
+        reserved_batch = batch;
+        size_t widths = 0;
+        for (int64_t d : dims) widths += static_cast<size_t>(d);
+        const size_t bytes = static_cast<size_t>(batch) * widths * sizeof(float) * 8 + static_cast<size_t>(n_params()) * sizeof(float) * 4;
+        cuda_check(ctk_pool_reserve(bytes), "pool reservation");
+    }
+
     float step(const Tensor& x, const Tensor& y_one_hot) {
         AutoDiffContext::Guard guard(&ctx);
         void* st = current_stream();
+        reserve_for(static_cast<int64_t>(x.sizes()[0]));
         for (size_t l = 0; l < W.size(); ++l) {
             ctx.make_leaf(W[l], true);
             ctx.make_leaf(b[l], true);

@@ -133,6 +133,26 @@ ctk_status ctk_free(void* p) {
     CTK_CUDA(cudaFreeAsync(p, static_cast<cudaStream_t>(0)));
     return CTK_OK;
 }
+// Grows the pool to at least `bytes` of backing memory now (one allocation, freed at once; the pool
+// keeps what it maps), so the first steps of a loop do not stop for the driver to map memory piece
+// by piece.  Synchronises the device.
+ctk_status ctk_pool_reserve(size_t bytes) {
+    if (bytes == 0) return CTK_OK;
+    ctk_status st = ensure_pool();
+    if (st) return st;
+    int dev = 0;
+    CTK_CUDA(cudaGetDevice(&dev));
+    cudaMemPool_t pool;
+    CTK_CUDA(cudaDeviceGetDefaultMemPool(&pool, dev));
+    uint64_t have = 0;
+    CTK_CUDA(cudaMemPoolGetAttribute(pool, cudaMemPoolAttrReservedMemCurrent, &have));
+    if (have >= bytes) return CTK_OK;
+    void* p = nullptr;
+    CTK_CUDA(cudaMallocAsync(&p, bytes - have, static_cast<cudaStream_t>(0)));
+    CTK_CUDA(cudaFreeAsync(p, static_cast<cudaStream_t>(0)));
+    CTK_CUDA(cudaDeviceSynchronize());
+    return CTK_OK;
+}
 // Long-lived buffers (caches that a caller manages itself): plain cudaMalloc / cudaFree, outside the
 // stream-ordered pool, so they neither fragment it nor pin its high-water mark.  Both synchronise.
 ctk_status ctk_malloc_longlived(void** p, size_t bytes) {

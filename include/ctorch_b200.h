@@ -73,6 +73,9 @@ ctk_status ctk_device_sync(void);
 ctk_status ctk_device_info(int* sm_count, size_t* total_bytes, size_t* free_bytes);
 
 ctk_status ctk_malloc(void** device_ptr, size_t bytes);      /* pooled; bytes==0 gives NULL    */
+/* Grows the pool's backing memory to at least `bytes` now, so that a training loop's first steps do
+ * not stop for the driver to map memory piece by piece.  Synchronises the device. */
+ctk_status ctk_pool_reserve(size_t bytes);
 /* For buffers a caller keeps and recycles itself over many steps: plain device allocations outside
  * the pool (they would fragment it).  Both calls synchronise the device. */
 ctk_status ctk_malloc_longlived(void** device_ptr, size_t bytes);

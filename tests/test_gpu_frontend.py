@@ -365,3 +365,28 @@ def test_kept_operand_splits_follow_every_write(F, orc):
     sq = rng.standard_normal((32, 32)).astype(np.float32)
     S = dev(F, sq)
     assert_matmul_close(S.matmul(S).numpy(), orc.matmul(sq, sq), 1e-4, "S.S")
+
+
+def test_zero_grad_then_read_then_accumulate(F):
+    """zero_grad (src/AutoDiff.cpp:502-510) followed by a read gives zeros; backward after zero_grad
+    gives one contribution, backward twice without it gives the sum of both."""
+    w = np.asarray([[1.0, -2.0], [3.0, 0.5]], np.float32)
+    x = np.asarray([[2.0, 5.0]], np.float32)
+    ctx = F.AutoDiff()
+    with ctx:
+        W = dev(F, w)
+        ctx.make_leaf(W, True)
+        W.requires_grad(True)
+        F.backward(dev(F, x).matmul(W).sum())
+        g1 = F.grad(W).numpy()
+        assert_exact(g1, np.repeat(x.T, 2, axis=1), "dW = x^T . 1")
+        F.backward((dev(F, 3 * x)).matmul(W).sum())
+        assert_exact(F.grad(W).numpy(), 4 * g1, "a second backward adds to the first")
+        ctx.zero_grad(W)
+        assert_exact(F.grad(W).numpy(), np.zeros_like(w), "zeroed gradient reads as zeros")
+        F.backward((dev(F, 3 * x)).matmul(W).sum())
+        assert_exact(F.grad(W).numpy(), 3 * g1, "backward after zero_grad holds one contribution")
+        ctx.zero_grad(W)
+        F.backward(dev(F, x).matmul(W).sum())
+        F.backward(dev(F, x).matmul(W).sum())
+        assert_exact(F.grad(W).numpy(), 2 * g1, "zero, then two contributions")
