@@ -343,6 +343,15 @@ Tensor Tensor::transpose(int d0, int d1) const {
 }
 Tensor Tensor::t() const { return transpose(0, 1); }
 
+Tensor Tensor::narrow_rows(size_t start, size_t count) const {
+    if (_shape.empty() || _shape.size() > 2) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DIMENSION, "narrow_rows: 1-D or 2-D tensors only");
+    if (start > _shape[0] || count > _shape[0] - start) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DIMENSION, "narrow_rows: range outside the tensor");
+    Tensor r(*this);
+    r._shape[0] = count;
+    r._storage_offset = _storage_offset + start * _strides[0];
+    return r;
+}
+
 Tensor Tensor::reshape(const std::vector<size_t>& new_shape) const {
     size_t n = 1;
     for (size_t s : new_shape) n *= s;

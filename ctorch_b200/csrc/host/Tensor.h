@@ -97,6 +97,9 @@ public:
     Tensor clone() const;
     Tensor transpose(int dim0, int dim1) const;
     Tensor t() const;
+    // Rows [start, start + count) of a 2-D (or 1-D) tensor as a view of the same buffer: what
+    // get_batch of mnist/mnist.cpp:160-188 copies element by element.
+    Tensor narrow_rows(size_t start, size_t count) const;
     Tensor reshape(const std::vector<size_t>& new_shape) const;
     Tensor reshape(std::initializer_list<size_t> new_shape) const { return reshape(std::vector<size_t>(new_shape)); }
     Tensor broadcast_to(const std::vector<size_t>& shape) const;

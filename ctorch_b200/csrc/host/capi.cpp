@@ -15,6 +15,7 @@
 #include "Ctorch_Error.h"
 #include "Ctorch_Scheduler.h"
 #include "Tensor.h"
+#include "mnist_loader.h"
 #include "ctorch_b200.h"
 #include "ctorch_b200_frontend.h"
 
@@ -255,6 +256,50 @@ public:
         return step(s.x, y);
     }
 
+    // Class probabilities of a batch without recording anything: NeuralNetwork::predict of
+    // mnist/mnist.cpp:94-131 (forward, then a row softmax).
+    Tensor predict(const Tensor& x) {
+        AutoDiffContext::Guard guard(nullptr);
+        Tensor logits = forward(x);
+        return logits.softmax(1);
+    }
+
+    // calculate_accuracy of mnist/mnist.cpp:134-158: per row the first class whose probability exceeds
+    // -1 and every earlier one, compared with (int)label; correct / total in float.  Runs on the
+    // device; one float comes back.
+    float accuracy(const Tensor& x, const Tensor& labels) {
+        const Tensor probs = predict(x);
+        const int64_t rows = static_cast<int64_t>(probs.sizes()[0]), classes = static_cast<int64_t>(probs.sizes()[1]);
+        if (static_cast<int64_t>(labels.numel()) != rows) throw std::runtime_error("accuracy: one label per row expected");
+        void* st = current_stream();
+        Tensor pred(ShapeTag{}, {static_cast<size_t>(rows)}, DType::kFloat, DeviceType::kCUDA, false);
+        Tensor count(ShapeTag{}, std::vector<size_t>{}, DType::kFloat, DeviceType::kCUDA, false);
+        cuda_check(ctk_argmax_rows_f32(probs.data<float>(), rows, classes, -1.0f, pred.data<float>(), st), "argmax");
+        const Tensor& pred_c = pred;
+        cuda_check(ctk_count_matches_f32(pred_c.data<float>(), labels.data<float>(), rows, count.data<float>(), nullptr, st), "count matches");
+        const int correct = static_cast<int>(count.item<float>());
+        return static_cast<float>(correct) / static_cast<float>(rows);
+    }
+
+    // One pass over a device-resident data set in batches of `batch_size` rows, in order, as the
+    // epoch loop of mnist/mnist.cpp:246-262 (the remainder that does not fill a batch is skipped, as
+    // there).  Batches are views of the data set, not copies.  Returns the mean of the step losses.
+    float train_epoch(const Tensor& images, const Tensor& labels, int64_t batch_size) {
+        if (batch_size <= 0) throw std::runtime_error("train_epoch: batch size must be positive");
+        const int64_t n = static_cast<int64_t>(images.sizes()[0]);
+        const int64_t num_batches = n / batch_size;
+        const size_t classes = static_cast<size_t>(dims.back());
+        float epoch_loss = 0.0f;
+        for (int64_t bi = 0; bi < num_batches; ++bi) {
+            const Tensor xb = images.narrow_rows(static_cast<size_t>(bi * batch_size), static_cast<size_t>(batch_size));
+            const Tensor lb = labels.narrow_rows(static_cast<size_t>(bi * batch_size), static_cast<size_t>(batch_size));
+            Tensor y(ShapeTag{}, {static_cast<size_t>(batch_size), classes}, DType::kFloat, DeviceType::kCUDA, false);
+            cuda_check(ctk_onehot_f32(lb.data<float>(), batch_size, static_cast<int64_t>(classes), y.data<float>(), current_stream()), "one-hot");
+            epoch_loss += step(xb, y);
+        }
+        return num_batches ? epoch_loss / static_cast<float>(num_batches) : 0.0f;
+    }
+
     void get_params(float* out) {
         for (size_t l = 0; l < W.size(); ++l) {
             W[l].copy_to_host(out, W[l].numel());
@@ -458,6 +503,33 @@ int cth_mlp_step_staged(void* m, float* loss) {
 }
 int cth_mlp_step_device(void* m, void* x, void* onehot, float* loss) {
     return guarded([&] { *loss = static_cast<MlpTrainer*>(m)->step(*T(x), *T(onehot)); });
+}
+int cth_mlp_predict(void* m, void* x, void** probs) {
+    return guarded([&] { *probs = new Tensor(static_cast<MlpTrainer*>(m)->predict(*T(x))); });
+}
+int cth_mlp_accuracy(void* m, void* x, void* labels, float* acc) {
+    return guarded([&] { *acc = static_cast<MlpTrainer*>(m)->accuracy(*T(x), *T(labels)); });
+}
+int cth_mlp_train_epoch(void* m, void* images, void* labels, int64_t batch_size, float* mean_loss) {
+    return guarded([&] { *mean_loss = static_cast<MlpTrainer*>(m)->train_epoch(*T(images), *T(labels), batch_size); });
+}
+int cth_mnist_load(const char* dir, const char* image_file, const char* label_file, int device, void** images, void** labels) {
+    return guarded([&] {
+        MNISTLoader loader(dir, static_cast<DeviceType>(device));
+        auto im = std::make_unique<Tensor>();
+        auto lb = std::make_unique<Tensor>();
+        if (image_file && label_file) loader.load(image_file, label_file, *im, *lb);
+        else if (image_file && std::string(image_file) == "test") loader.load_test_data(*im, *lb);
+        else loader.load_training_data(*im, *lb);
+        *images = im.release();
+        *labels = lb.release();
+    });
+}
+int cth_tensor_narrow_rows(void* t, int64_t start, int64_t count, void** out) {
+    return guarded([&] {
+        if (start < 0 || count < 0) throw std::runtime_error("cth_tensor_narrow_rows: negative range");
+        *out = new Tensor(T(t)->narrow_rows(static_cast<size_t>(start), static_cast<size_t>(count)));
+    });
 }
 int cth_mlp_get_params(void* m, float* out) {
     return guarded([&] { static_cast<MlpTrainer*>(m)->get_params(out); });

@@ -134,6 +134,63 @@ __global__ void __launch_bounds__(kEwThreads) onehot_kernel(const float* __restr
     }
 }
 
+// dst[i] = float(src[i]) / divisor, IEEE division: the pixel normalisation of the IDX image reader
+// (mnist/mnist_loader.cpp:38-40, `pixel / 255.0f`), done on the device so that images cross PCIe as
+// bytes.  16 pixels per thread where the pointers allow 128-bit accesses.
+__global__ void __launch_bounds__(kEwThreads) u8_to_f32_kernel(const uint8_t* __restrict__ src, int64_t n, float divisor, float* __restrict__ dst, int vec) {
+    const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    if (vec) {
+        const int64_t n16 = n >> 4;
+        for (int64_t i = tid; i < n16; i += stride) {
+            const uint4 w = __ldcs(reinterpret_cast<const uint4*>(src) + i);
+            const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                float4 o;
+                o.x = __fdiv_rn(static_cast<float>(words[q] & 0xffu), divisor);
+                o.y = __fdiv_rn(static_cast<float>((words[q] >> 8) & 0xffu), divisor);
+                o.z = __fdiv_rn(static_cast<float>((words[q] >> 16) & 0xffu), divisor);
+                o.w = __fdiv_rn(static_cast<float>(words[q] >> 24), divisor);
+                __stcs(reinterpret_cast<float4*>(dst) + i * 4 + q, o);
+            }
+        }
+        for (int64_t i = (n16 << 4) + tid; i < n; i += stride) dst[i] = __fdiv_rn(static_cast<float>(src[i]), divisor);
+    } else {
+        for (int64_t i = tid; i < n; i += stride) dst[i] = __fdiv_rn(static_cast<float>(src[i]), divisor);
+    }
+}
+
+// out[r] = index of the first element of row r that is strictly greater than everything before it,
+// starting from (`init`, index 0): the prediction loop of mnist/mnist.cpp:140-147 (init -1 on
+// probabilities); init = -inf gives the plain first-maximum argmax.  A warp per row; a lane keeps
+// its first maximum, lanes are merged preferring the larger value, then the smaller index.
+__global__ void __launch_bounds__(kEwThreads) argmax_rows_kernel(const float* __restrict__ x, int64_t rows, int64_t cols, float init, float* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+    for (int64_t r = warp; r < rows; r += nwarps) {
+        const float* row = x + r * cols;
+        float best = init;
+        int64_t idx = 0;
+        for (int64_t j = lane; j < cols; j += 32) {
+            const float v = __ldg(row + j);
+            if (v > best) { best = v; idx = j; }
+        }
+        // a lane that found nothing above `init` must not win with index 0 over a lane that did
+        bool found = best > init;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int64_t oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            const bool of = __shfl_xor_sync(0xffffffffu, found ? 1 : 0, o) != 0;
+            const bool take = of && (!found || ob > best || (ob == best && oi < idx));
+            if (take) { best = ob; idx = oi; found = true; }
+        }
+        if (lane == 0) out[r] = found ? static_cast<float>(idx) : 0.0f;
+    }
+}
+
 template <int NIN, int NOUT>
 EwArgs<NIN, NOUT> make_args(int64_t n, int64_t inner = 1) {
     EwArgs<NIN, NOUT> A{};
@@ -231,6 +288,25 @@ ctk_status ctk_onehot_f32(const float* labels, int64_t rows, int64_t classes, fl
     CTK_REQUIRE(labels && onehot, "ctk_onehot_f32: null pointer");
     onehot_kernel<<<ctk_stream_grid(rows * classes, kEwThreads, 8), kEwThreads, 0, as_stream(stream)>>>(labels, rows, classes, onehot);
     CTK_LAUNCH_CHECK("onehot_kernel");
+    return CTK_OK;
+}
+
+ctk_status ctk_u8_to_f32(const uint8_t* src, int64_t n, float divisor, float* dst, void* stream) {
+    CTK_REQUIRE(n >= 0, "ctk_u8_to_f32: negative size");
+    if (n == 0) return CTK_OK;
+    CTK_REQUIRE(src && dst, "ctk_u8_to_f32: null pointer");
+    const int vec = ((reinterpret_cast<uintptr_t>(src) & 15u) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) ? 1 : 0;
+    u8_to_f32_kernel<<<ctk_stream_grid((n + 15) / 16, kEwThreads, 8), kEwThreads, 0, as_stream(stream)>>>(src, n, divisor, dst, vec);
+    CTK_LAUNCH_CHECK("u8_to_f32_kernel");
+    return CTK_OK;
+}
+
+ctk_status ctk_argmax_rows_f32(const float* x, int64_t rows, int64_t cols, float init, float* out_index, void* stream) {
+    CTK_REQUIRE(rows >= 0 && cols >= 0, "ctk_argmax_rows_f32: negative shape");
+    if (rows == 0) return CTK_OK;
+    CTK_REQUIRE(out_index && (x || cols == 0), "ctk_argmax_rows_f32: null pointer");
+    argmax_rows_kernel<<<ctk_stream_grid(rows * 32, kEwThreads, 8), kEwThreads, 0, as_stream(stream)>>>(x, rows, cols, init, out_index);
+    CTK_LAUNCH_CHECK("argmax_rows_kernel");
     return CTK_OK;
 }
 

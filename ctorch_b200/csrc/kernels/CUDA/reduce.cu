@@ -33,12 +33,13 @@ using namespace ctk;
 constexpr int kThreads = 256;
 constexpr int kCtasPerSm = 4;
 
-enum { R_SUM = 0, R_DOT = 1, R_MSE = 2, R_MAE = 3 };
+enum { R_SUM = 0, R_DOT = 1, R_MSE = 2, R_MAE = 3, R_MATCH = 4 };
 
 template <int KIND>
 __device__ __forceinline__ float term(float x, float y) {
     if (KIND == R_SUM) return x;
     if (KIND == R_DOT) return x * y;
+    if (KIND == R_MATCH) return static_cast<int>(x) == static_cast<int>(y) ? 1.0f : 0.0f;
     float d = x - y;
     if (KIND == R_MSE) return d * d;
     return fabsf(d);
@@ -128,6 +129,10 @@ ctk_status ctk_mse_f32(const float* a, const float* b, int64_t n, float* out, vo
 ctk_status ctk_mae_f32(const float* a, const float* b, int64_t n, float* out, void* scratch, void* stream) {
     CTK_REQUIRE(n > 0, "ctk_mae_f32: empty input");
     return launch_reduce<R_MAE>("mae", a, b, n, static_cast<float>(n), out, scratch, stream);
+}
+
+ctk_status ctk_count_matches_f32(const float* a, const float* b, int64_t n, float* out, void* scratch, void* stream) {
+    return launch_reduce<R_MATCH>("count_matches", a, b, n, 0.0f, out, scratch, stream);
 }
 
 static ctk_status mean_loss_backward(bool mse, const float* p, const float* t, const float* g, float* dp, int64_t n, void* stream) {

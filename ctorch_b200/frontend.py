@@ -57,6 +57,12 @@ class Tensor:
         _chk(lib.cth_tensor_scalar(ctypes.c_float(v), ctypes.byref(h)))
         return Tensor(h)
 
+    def narrow_rows(self, start, count):
+        """Rows [start, start+count) as a view of the same buffer."""
+        h = _vp()
+        _chk(lib.cth_tensor_narrow_rows(self.h, ctypes.c_int64(start), ctypes.c_int64(count), ctypes.byref(h)))
+        return Tensor(h)
+
     def info(self):
         shape = (ctypes.c_int64 * 8)()
         rank, dev, rg = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
@@ -149,6 +155,20 @@ class Tensor:
             pass
 
 
+def mnist_load(directory, which="train", device=CUDA, image_file=None, label_file=None):
+    """MNISTLoader: (images [n, rows*cols] of pixel/255, labels [n] as floats) from the IDX files of
+    `directory`: the training pair, the test pair (which="test") or a named pair."""
+    im, lb = _vp(), _vp()
+    if image_file is not None and label_file is not None:
+        a, b = image_file.encode(), label_file.encode()
+    elif which == "test":
+        a, b = b"test", None
+    else:
+        a, b = None, None
+    _chk(lib.cth_mnist_load(str(directory).encode(), a, b, device, ctypes.byref(im), ctypes.byref(lb)))
+    return Tensor(im), Tensor(lb)
+
+
 class AutoDiff:
     """`AutoDiff ctx; AutoDiffContext::Guard guard(&ctx);` as a Python context manager."""
 
@@ -225,6 +245,24 @@ class MlpTrainer:
         """The step on the oldest staged batch."""
         loss = ctypes.c_float()
         _chk(lib.cth_mlp_step_staged(self.h, ctypes.byref(loss)))
+        return loss.value
+
+    def predict(self, x):
+        """Class probabilities of a device batch (NeuralNetwork::predict)."""
+        h = _vp()
+        _chk(lib.cth_mlp_predict(self.h, x.h, ctypes.byref(h)))
+        return Tensor(h)
+
+    def accuracy(self, x, labels):
+        """calculate_accuracy on the device: fraction of rows whose first-maximum class equals the label."""
+        a = ctypes.c_float()
+        _chk(lib.cth_mlp_accuracy(self.h, x.h, labels.h, ctypes.byref(a)))
+        return a.value
+
+    def train_epoch(self, images, labels, batch_size):
+        """One pass over a device-resident data set in consecutive batches; returns the mean step loss."""
+        loss = ctypes.c_float()
+        _chk(lib.cth_mlp_train_epoch(self.h, images.h, labels.h, ctypes.c_int64(batch_size), ctypes.byref(loss)))
         return loss.value
 
     def step_device(self, x, onehot):

@@ -182,6 +182,26 @@ def matmul_path(a, b, ta=False, tb=False, mode=-1):
     return lib.ctk_matmul_path(a.p, b.p, _i64(m), _i64(n), _i64(k), _i64(sa[0]), _i64(sa[1]), _i64(sb[0]), _i64(sb[1]), mode)
 
 
+def u8_to_f32(src_u8, divisor, out=None):
+    """src_u8: a DeviceArray of dtype uint8; returns float(src) / divisor."""
+    out = out or DeviceArray(src_u8.shape)
+    check(lib.ctk_u8_to_f32(src_u8.p, _i64(src_u8.size), ctypes.c_float(divisor), out.p, None))
+    return out
+
+
+def argmax_rows(x, init=float("-inf")):
+    r, c = _rc(x)
+    out = DeviceArray((r,))
+    check(lib.ctk_argmax_rows_f32(x.p, _i64(r), _i64(c), ctypes.c_float(init), out.p, None))
+    return out
+
+
+def count_matches(a, b):
+    out = _scalar_out()
+    check(lib.ctk_count_matches_f32(a.p, b.p, _i64(a.size), out.p, None, None))
+    return out
+
+
 def rowwise_status():
     s = ctypes.c_int()
     check(lib.ctk_rowwise_status(ctypes.byref(s)))

@@ -133,6 +133,20 @@ ctk_status ctk_tile_f32(const float* src, int64_t src_n, float* dst, int64_t n, 
  * mnist/mnist.cpp:67-72, for labels that already live on the device. */
 ctk_status ctk_onehot_f32(const float* labels, int64_t rows, int64_t classes, float* onehot, void* stream);
 
+/* dst[i] = (float)src[i] / divisor (IEEE division): the pixel normalisation of the IDX image reader
+ * (mnist/mnist_loader.cpp:34-41, `pixel / 255.0f`) on the device, so images cross PCIe as bytes. */
+ctk_status ctk_u8_to_f32(const uint8_t* src, int64_t n, float divisor, float* dst, void* stream);
+
+/* out_index[r] = first index j of row r with x[r,j] greater than `init` and than every earlier
+ * element, 0 if there is none: the prediction loop of mnist/mnist.cpp:140-147 (init = -1 on
+ * probabilities); init = -INFINITY is the plain first-maximum argmax.  Indices as floats, like
+ * the labels they are compared with. */
+ctk_status ctk_argmax_rows_f32(const float* x, int64_t rows, int64_t cols, float init, float* out_index, void* stream);
+
+/* out = number of i with (int)a[i] == (int)b[i] (as a float): the comparison of predicted and true
+ * labels of mnist/mnist.cpp:150-153.  Exact up to 2^24 matches. */
+ctk_status ctk_count_matches_f32(const float* a, const float* b, int64_t n, float* out, void* scratch, void* stream);
+
 /* dst[r] = src[sum_j r_j * src_strides[j]] over the row-major index r of dst_shape (rank <= 8, a
  * stride of 0 repeats index 0): the gather of AutoDiff::check_and_adjust_grad_shape's broadcast
  * branch (src/AutoDiff.cpp:690-890), which takes index 0 on every broadcast dim. */

@@ -83,6 +83,24 @@ int cth_mlp_stage_host(void* mlp, const float* x_host, const float* labels_host,
 int cth_mlp_step_staged(void* mlp, float* loss);
 /* x and onehot are device tensors ([batch, dims[0]] and [batch, classes]). */
 int cth_mlp_step_device(void* mlp, void* x, void* onehot, float* loss);
+/* NeuralNetwork::predict (mnist/mnist.cpp:94-131): class probabilities [batch, classes] of a device
+ * batch, nothing recorded on the tape.  calculate_accuracy (:134-158): first-maximum class per row
+ * against (int)label, correct / total; computed on the device.  The epoch loop (:246-262): batches
+ * of `batch_size` consecutive rows of a device-resident data set (views, no copies; a trailing
+ * partial batch is skipped as there), one training step each; returns the mean step loss. */
+int cth_mlp_predict(void* mlp, void* x, void** probs);
+int cth_mlp_accuracy(void* mlp, void* x, void* labels, float* accuracy);
+int cth_mlp_train_epoch(void* mlp, void* images, void* labels, int64_t batch_size, float* mean_loss);
+/* MNISTLoader (mnist/mnist_loader.h): reads an IDX image file (magic 2051) and label file (magic
+ * 2049) of directory `dir` into an [n, rows*cols] tensor of pixel/255 and an [n] tensor of labels
+ * as floats, on `device` (0 host, 1 CUDA: the bytes are uploaded and converted on the device).
+ * image_file / label_file NULL: the training pair "train-images-idx3-ubyte" /
+ * "train-labels-idx1-ubyte"; image_file "test" with label_file NULL: the "t10k-..." pair.
+ * Fails (message in cth_last_error) if a file cannot be opened, has the wrong magic number or is
+ * shorter than its header says. */
+int cth_mnist_load(const char* dir, const char* image_file, const char* label_file, int device, void** images, void** labels);
+/* Rows [start, start+count) as a view of the same buffer (the batch of get_batch, :160-188, without its copy). */
+int cth_tensor_narrow_rows(void* tensor, int64_t start, int64_t count, void** out);
 int cth_mlp_n_params(void* mlp, int64_t* n);
 int cth_mlp_get_params(void* mlp, float* out);
 int cth_mlp_get_grads(void* mlp, float* out);         /* gradients of the last step (after the all-reduce) */

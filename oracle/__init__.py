@@ -59,6 +59,69 @@ def unpack_params(p, dims):
     return Ws, bs
 
 
+# ---- the MNIST application path: IDX files, prediction, accuracy (byte / integer work: numpy) ----
+def idx_write_images(path, pixels_u8):
+    """Writes an IDX3 image file ([n, rows, cols] uint8): big-endian magic 2051 and extents, then bytes."""
+    a = np.require(pixels_u8, dtype=np.uint8, requirements="C")
+    with open(path, "wb") as f:
+        f.write(np.asarray([2051, a.shape[0], a.shape[1], a.shape[2]], ">i4").tobytes())
+        f.write(a.tobytes())
+
+
+def idx_write_labels(path, labels_u8):
+    a = np.require(labels_u8, dtype=np.uint8, requirements="C")
+    with open(path, "wb") as f:
+        f.write(np.asarray([2049, a.shape[0]], ">i4").tobytes())
+        f.write(a.tobytes())
+
+
+def idx_read_images(path):
+    """MNISTLoader::read_images (mnist/mnist_loader.cpp:7-44): magic 2051, n, rows, cols as big-endian
+    int32, then one byte per pixel, each stored as pixel / 255.0f.  Returns [n, rows*cols] float32."""
+    raw = open(path, "rb").read()
+    magic, n, rows, cols = (int(v) for v in np.frombuffer(raw[:16], ">i4"))
+    if magic != 2051:
+        raise ValueError("not an IDX image file")
+    px = np.frombuffer(raw[16:16 + n * rows * cols], np.uint8)
+    return (px.astype(np.float32) / np.float32(255.0)).reshape(n, rows * cols)
+
+
+def idx_read_images_from_bytes(pixels_u8):
+    """The same normalisation on an in-memory [n, rows, cols] uint8 array."""
+    a = np.asarray(pixels_u8, np.uint8)
+    return (a.astype(np.float32) / np.float32(255.0)).reshape(a.shape[0], -1)
+
+
+def idx_read_labels(path):
+    """MNISTLoader::read_labels (:46-73) + the float copy of load_training_data (:113-115)."""
+    raw = open(path, "rb").read()
+    magic, n = (int(v) for v in np.frombuffer(raw[:8], ">i4"))
+    if magic != 2049:
+        raise ValueError("not an IDX label file")
+    return np.frombuffer(raw[8:8 + n], np.uint8).astype(np.float32)
+
+
+def predicted_labels(probs):
+    """The prediction loop of calculate_accuracy (mnist/mnist.cpp:140-147): per row the first class whose
+    probability exceeds -1 and every earlier one (NaN never does); 0 if none."""
+    p = np.asarray(probs, np.float32)
+    out = np.zeros(p.shape[0], np.int64)
+    for i in range(p.shape[0]):
+        best, lab = np.float32(-1.0), 0
+        for j in range(p.shape[1]):
+            if p[i, j] > best:
+                best, lab = p[i, j], j
+        out[i] = lab
+    return out
+
+
+def accuracy(probs, labels):
+    """calculate_accuracy (:134-158): float(correct) / total with (int)label."""
+    pred = predicted_labels(probs)
+    correct = int((pred == np.asarray(labels, np.float32).astype(np.int64)).sum())
+    return np.float32(correct) / np.float32(len(pred))
+
+
 class Oracle:
     """ctypes face of ctorch_oracle.c."""
 
@@ -231,6 +294,16 @@ class Reference(Oracle):
 
     def last_error(self):
         return self.L.ref_last_error().decode("utf-8", "replace")
+
+    def mnist_load(self, directory, test=False):
+        """The reference's own MNISTLoader on `directory`: (images [n, rows*cols], labels [n])."""
+        n, sz, nl = ctypes.c_int64(), ctypes.c_int64(), ctypes.c_int64()
+        d = str(directory).encode()
+        self._chk(self.L.ref_mnist_load(d, int(test), None, ctypes.c_int64(0), ctypes.byref(n), ctypes.byref(sz), None, ctypes.c_int64(0), ctypes.byref(nl)))
+        im = np.empty((n.value, sz.value), np.float32)
+        lb = np.empty(nl.value, np.float32)
+        self._chk(self.L.ref_mnist_load(d, int(test), _fp(im), ctypes.c_int64(im.size), ctypes.byref(n), ctypes.byref(sz), _fp(lb), ctypes.c_int64(lb.size), ctypes.byref(nl)))
+        return im, lb
 
     def _chk(self, rc):
         if rc:

@@ -21,6 +21,7 @@
 #include <vector>
 
 #include "Tensor.h"
+#include "mnist_loader.h"
 #include "AutoDiff.h"
 #include "Ctorch_Error.h"
 #include "../src/kernels/kernels.h"
@@ -334,6 +335,24 @@ int ref_mlp_train(int n_layers, const int64_t* dims, int64_t batch, int steps, i
             p += copy_out(reps[0].W[l], p);
             p += copy_out(reps[0].b[l], p);
         }
+    });
+}
+
+// MNISTLoader of the reference (mnist/mnist_loader.{h,cpp}, compiled from where it lies): the
+// training pair (test = 0) or the test pair (test = 1) of directory `dir`.  Sizes always come back;
+// data is copied only when the caller's capacities (in elements) suffice.
+int ref_mnist_load(const char* dir, int test, float* images, int64_t cap_images, int64_t* n_images,
+                   int64_t* image_size, float* labels, int64_t cap_labels, int64_t* n_labels) {
+    return guarded([&] {
+        MNISTLoader loader(dir);
+        Tensor im, lb;
+        if (test) loader.load_test_data(im, lb);
+        else loader.load_training_data(im, lb);
+        *n_images = static_cast<int64_t>(im.shape()[0]);
+        *image_size = static_cast<int64_t>(im.shape()[1]);
+        *n_labels = static_cast<int64_t>(lb.shape()[0]);
+        if (images && cap_images >= static_cast<int64_t>(im.numel())) copy_out(im, images);
+        if (labels && cap_labels >= static_cast<int64_t>(lb.numel())) copy_out(lb, labels);
     });
 }
 

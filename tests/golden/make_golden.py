@@ -102,6 +102,44 @@ def main():
         G[tag + ".steps"] = np.asarray(steps)
         for k in ("params", "losses", "grads", "logits"):
             G[tag + "." + k] = r[k]
+    # the MNIST application path: an IDX image/label pair through the reference's own MNISTLoader, an
+    # epoch loop over it (batches in file order), then prediction and accuracy on the whole set
+    import tempfile
+    n_img, bsz, dims = 96, 32, [784, 16, 12, 10]
+    labels_u8 = rng.integers(0, 10, n_img).astype(np.uint8)
+    pixels = rng.integers(0, 48, (n_img, 28, 28)).astype(np.uint8)   # dim noise ...
+    pixels[0].reshape(-1)[-256:] = np.arange(256, dtype=np.uint8)     # (every byte value once)
+    for i in range(n_img):                                            # ... and a bright mark per class
+        pixels[i, labels_u8[i] * 2: labels_u8[i] * 2 + 2, :] = 255
+    with tempfile.TemporaryDirectory() as d:
+        oracle.idx_write_images(os.path.join(d, "train-images-idx3-ubyte"), pixels)
+        oracle.idx_write_labels(os.path.join(d, "train-labels-idx1-ubyte"), labels_u8)
+        im, lb = R.mnist_load(d)
+    assert np.array_equal(im, oracle.idx_read_images_from_bytes(pixels)) and np.array_equal(lb, labels_u8.astype(np.float32))
+    Ws, bs = [], []
+    for i, j in zip(dims[:-1], dims[1:]):
+        lim = np.sqrt(6.0 / i)
+        Ws.append(rng.uniform(-lim, lim, (i, j)).astype(np.float32))
+        bs.append(np.zeros(j, np.float32))
+    p0 = oracle.pack_params(Ws, bs)
+    epochs, nb = 8, n_img // bsz
+    lr = 0.002
+    r = R.mlp_train(dims, im.reshape(1, nb, bsz, 784), lb.reshape(1, nb, bsz), p0, lr, epochs * nb)
+    Wf, bf = oracle.unpack_params(r["params"], dims)
+    h = im
+    for l, (W, b) in enumerate(zip(Wf, bf)):
+        h = R.binary("Add", R.matmul(h, W), b, B_ROW)
+        if l + 1 < len(Wf):
+            h = R.unary("ReLU", h)
+    probs = R.softmax(h)
+    G["mnist.pixels"], G["mnist.labels_u8"] = pixels, labels_u8
+    G["mnist.images"], G["mnist.labels"] = im, lb
+    G["mnist.dims"], G["mnist.batch"], G["mnist.epochs"] = np.asarray(dims, np.int64), np.asarray(bsz), np.asarray(epochs)
+    G["mnist.lr"] = np.asarray(lr, np.float32)
+    G["mnist.params0"], G["mnist.params"], G["mnist.losses"] = p0, r["params"], r["losses"]
+    G["mnist.probs"] = probs
+    G["mnist.pred"] = oracle.predicted_labels(probs)
+    G["mnist.accuracy"] = np.asarray(oracle.accuracy(probs, lb), np.float32)
     out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden.npz")
     np.savez_compressed(out, **G)
     print("wrote", out, os.path.getsize(out), "bytes,", len(G), "arrays")
