@@ -410,10 +410,70 @@ def run_single_op(args):
                 emit(f"matmul_dB_{mode}_{m}x{k}x{n}", timeit(lambda: cb.ops.matmul(A, dC, ta=True, mode=mode, out=dB), it), fl, "TFLOP/s", peak, cfg)
                 del A, B, dC, C, dA, dB
         print(json.dumps(dict(matmul_status=cb.ops.matmul_status())))
+    elif args.workload == "mnist":
+        run_mnist_app(cb, args, rng)
     elif args.workload == "kernel":
         run_one_kernel(cb, args.case, rng)
     else:
         raise SystemExit("unknown workload " + args.workload)
+
+
+def run_mnist_app(cb, args, rng):
+    """The reference application (mnist/mnist.cpp:218-275): 784-128-64-10, batch 128, lr 0.01, 5 epochs over
+    60000 training images in file order, then accuracy on the training and the 10000 test images.  The
+    MNIST image files are not available here: a synthetic set in the same IDX format stands in (dim
+    noise plus a bright band whose position encodes the class, shifted at random), read by the
+    product's IDX loader.  The data set lives in HBM; an epoch is 468 steps on views of it."""
+    import tempfile
+    from ctorch_b200 import frontend as F
+    F.set_quiet(True)
+    dims, batch, epochs, lr = [784, 128, 64, 10], 128, 5, 0.01
+
+    def synth(n):
+        lab = rng.integers(0, 10, n).astype(np.uint8)
+        px = rng.integers(0, 64, (n, 28, 28)).astype(np.uint8)
+        shift = rng.integers(0, 3, n)
+        for c in range(10):
+            for sft in range(3):
+                idx = np.nonzero((lab == c) & (shift == sft))[0]
+                px[idx, 2 * c + sft: 2 * c + sft + 3, 4:24] = 255
+        return px, lab
+
+    with tempfile.TemporaryDirectory() as d:
+        for names, n in ((("train-images-idx3-ubyte", "train-labels-idx1-ubyte"), 60000), (("t10k-images-idx3-ubyte", "t10k-labels-idx1-ubyte"), 10000)):
+            px, lab = synth(n)
+            with open(os.path.join(d, names[0]), "wb") as f:   # IDX3: big-endian magic 2051, n, rows, cols, then the bytes
+                f.write(np.asarray([2051, n, 28, 28], ">i4").tobytes() + px.tobytes())
+            with open(os.path.join(d, names[1]), "wb") as f:   # IDX1: magic 2049, n, then the bytes
+                f.write(np.asarray([2049, n], ">i4").tobytes() + lab.tobytes())
+        t0 = time.perf_counter()
+        train_x, train_y = F.mnist_load(d, "train")
+        test_x, test_y = F.mnist_load(d, "test")
+        cb.synchronize()
+        load_s = time.perf_counter() - t0
+    parts = []
+    for i, j in zip(dims[:-1], dims[1:]):
+        lim = np.sqrt(6.0 / i)
+        parts += [rng.uniform(-lim, lim, (i, j)).astype(np.float32).ravel(), np.zeros(j, np.float32)]
+    tr = F.MlpTrainer(dims, np.concatenate(parts), lr)
+    tr.train_epoch(train_x.narrow_rows(0, 10 * batch), train_y.narrow_rows(0, 10 * batch), batch)   # warm-up: 10 untimed steps
+    tr = F.MlpTrainer(dims, np.concatenate(parts), lr)
+    e0, e1 = cb.Event(), cb.Event()
+    cb.synchronize()
+    e0.record()
+    losses = [tr.train_epoch(train_x, train_y, batch) for _ in range(epochs)]
+    e1.record()
+    e1.sync()
+    train_s = e0.elapsed_ms(e1) * 1e-3
+    t0 = time.perf_counter()
+    acc_train, acc_test = tr.accuracy(train_x, train_y), tr.accuracy(test_x, test_y)
+    eval_s = time.perf_counter() - t0
+    steps = epochs * (60000 // batch)
+    print(json.dumps(dict(metric="mnist_app_train_samples_per_s", value=steps * batch / train_s, unit="samples/s", n_gpus=1, higher_is_better=True,
+                          data="synthetic IDX files (60000 + 10000 images of 28x28 bytes)", dtype="f32",
+                          config=dict(workload="mnist-app-784-128-64-10_batch128_lr0.01_5epochs", steps=steps, us_per_step=train_s / steps * 1e6),
+                          load_s=load_s, train_s=train_s, eval_s=eval_s, epoch_mean_loss=[float(v) for v in losses],
+                          accuracy_train=float(acc_train), accuracy_test=float(acc_test))))
 
 
 def run_one_kernel(cb, case, rng):

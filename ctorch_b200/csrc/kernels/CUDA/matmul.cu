@@ -181,8 +181,28 @@ struct Params {
     int64_t m, n, k;
     int tiles_m, tiles_n, num_kb;
     float* c;
-    int vec_store;  // n % 4 == 0 and c 16-byte aligned
+    int vec_store;    // n % 4 == 0 and c 16-byte aligned
+    int whole_tiles;  // tiles [0, whole_tiles) are computed whole; each later tile as two K-halves
 };
+
+// A unit of work: a whole output tile, or one K-half of a tile of the last, partly filled wave.
+// Halves let twice as many SMs work on that wave; both halves add their accumulator into C, which
+// the launcher zeroed for those tiles.  Two addends commute, so the result does not depend on which
+// half lands first.
+struct Unit {
+    int tile, kb0, kb1;
+    bool half;
+};
+__device__ __forceinline__ int unit_count(const Params& P) {
+    const int tiles = P.tiles_m * P.tiles_n;
+    return P.whole_tiles + 2 * (tiles - P.whole_tiles);
+}
+__device__ __forceinline__ Unit unit_of(int u, const Params& P) {
+    if (u < P.whole_tiles) return Unit{u, 0, P.num_kb, false};
+    const int v = u - P.whole_tiles;
+    const int mid = (P.num_kb + 1) >> 1;
+    return (v & 1) ? Unit{P.whole_tiles + (v >> 1), mid, P.num_kb, true} : Unit{P.whole_tiles + (v >> 1), 0, mid, true};
+}
 
 // ---- PTX wrappers --------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -336,7 +356,7 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
 
-    const int num_tiles = P.tiles_m * P.tiles_n;
+    const int num_units = unit_count(P);
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -345,9 +365,10 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
             uint32_t phase = 0;
             uint32_t issued = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile / P.tiles_n) * BM, n0 = (tile % P.tiles_n) * BN;
-                for (int kb = 0; kb < P.num_kb; ++kb) {
+            for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+                const Unit U = unit_of(u, P);
+                const int m0 = (U.tile / P.tiles_n) * BM, n0 = (U.tile % P.tiles_n) * BN;
+                for (int kb = U.kb0; kb < U.kb1; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, &abort_flag, 0x100 | stage)) { ok = false; break; }
                     mbar_expect_tx(full_bar(stage), C::STAGE_BYTES);
                     const int k0 = kb * BK;
@@ -392,11 +413,12 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+                const Unit U = unit_of(u, P);
                 if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, &abort_flag, 0x200 | (18 + acc))) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-                for (int kb = 0; kb < P.num_kb; ++kb) {
+                for (int kb = U.kb0; kb < U.kb1; ++kb) {
                     if (!mbar_wait(full_bar(stage), phase, &abort_flag, 0x200 | stage)) { ok = false; break; }
                     tc_fence_after();
 #pragma unroll
@@ -408,7 +430,7 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
                         const uint32_t a_sw = A_MN ? kSwizzle128BAtom32B : kSwizzle128B, b_sw = B_MN ? kSwizzle128BAtom32B : kSwizzle128B;
                         const uint64_t a_hi = make_desc(a_addr(stage, 0) + a_step, a_lbo, a_sbo, a_sw);
                         const uint64_t b_hi = make_desc(b_addr(stage, 0) + b_step, b_lbo, b_sbo, b_sw);
-                        const uint32_t first = (kb > 0 || ks > 0) ? 1u : 0u;
+                        const uint32_t first = (kb > U.kb0 || ks > 0) ? 1u : 0u;
                         if (TERMS == 3) {
                             const uint64_t a_lo = make_desc(a_addr(stage, 1) + a_step, a_lbo, a_sbo, a_sw);
                             const uint64_t b_lo = make_desc(b_addr(stage, 1) + b_step, b_lbo, b_sbo, b_sw);
@@ -433,8 +455,9 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-            const int64_t m0 = static_cast<int64_t>(tile / P.tiles_n) * BM, n0 = static_cast<int64_t>(tile % P.tiles_n) * BN;
+        for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+            const Unit U = unit_of(u, P);
+            const int64_t m0 = static_cast<int64_t>(U.tile / P.tiles_n) * BM, n0 = static_cast<int64_t>(U.tile % P.tiles_n) * BN;
             if (!mbar_wait(tfull_bar(acc), acc_phase, &abort_flag, 0x300 | (16 + acc))) { ok = false; break; }
             tc_fence_after();
             const int64_t row = m0 + quarter * 32 + lane;
@@ -447,7 +470,20 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
                 tmem_ld_wait();
                 const int64_t col0 = n0 + cc * 32;
                 if (row < P.m && col0 < P.n) {
-                    if (P.vec_store && col0 + 32 <= P.n) {
+                    if (U.half) {
+                        // one K-half of the tile: add into the zeroed C
+                        if (P.vec_store && col0 + 32 <= P.n) {
+#pragma unroll
+                            for (int v = 0; v < 8; ++v)
+                                atomicAdd(reinterpret_cast<float4*>(crow + col0) + v,
+                                          make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                                      __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3])));
+                        } else {
+#pragma unroll
+                            for (int v = 0; v < 32; ++v)
+                                if (col0 + v < P.n) atomicAdd(crow + col0 + v, __uint_as_float(r[v]));
+                        }
+                    } else if (P.vec_store && col0 + 32 <= P.n) {
 #pragma unroll
                         for (int v = 0; v < 8; ++v)
                             __stcs(reinterpret_cast<float4*>(crow + col0) + v,
@@ -608,8 +644,8 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
 
-    const int num_tiles = P.tiles_m * P.tiles_n;
-    const int first_tile = blockIdx.x >> 1, tile_step = gridDim.x >> 1;
+    const int num_units = unit_count(P);
+    const int first_unit = blockIdx.x >> 1, unit_step = gridDim.x >> 1;
 
     if (warp == 0) {
         // ------------------------------ TMA producer (both CTAs) ------------------------------
@@ -618,10 +654,11 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
             uint32_t phase = 0;
             uint32_t issued = 0;
             bool ok = true;
-            for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
-                const int m0 = (tile / P.tiles_n) * (2 * BM) + static_cast<int>(rank) * BM;
-                const int n0 = (tile % P.tiles_n) * BN + static_cast<int>(rank) * BN_CTA;
-                for (int kb = 0; kb < P.num_kb; ++kb) {
+            for (int u = first_unit; u < num_units && ok; u += unit_step) {
+                const Unit U = unit_of(u, P);
+                const int m0 = (U.tile / P.tiles_n) * (2 * BM) + static_cast<int>(rank) * BM;
+                const int n0 = (U.tile % P.tiles_n) * BN + static_cast<int>(rank) * BN_CTA;
+                for (int kb = U.kb0; kb < U.kb1; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, &abort_flag, 0x500 | stage)) { ok = false; break; }
                     if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * C::STAGE_BYTES);
                     const uint32_t fb = map_to_cta(full_bar(stage), 0);
@@ -672,11 +709,12 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+            for (int u = first_unit; u < num_units && ok; u += unit_step) {
+                const Unit U = unit_of(u, P);
                 if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, &abort_flag, 0x600 | (18 + acc))) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-                for (int kb = 0; kb < P.num_kb; ++kb) {
+                for (int kb = U.kb0; kb < U.kb1; ++kb) {
                     if (!mbar_wait(full_bar(stage), phase, &abort_flag, 0x600 | stage)) { ok = false; break; }
                     tc_fence_after();
 #pragma unroll
@@ -688,7 +726,7 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
                         const uint32_t a_sw = A_MN ? kSwizzle128BAtom32B : kSwizzle128B, b_sw = B_MN ? kSwizzle128BAtom32B : kSwizzle128B;
                         const uint64_t a_hi = make_desc(a_addr(stage, 0) + a_step, a_lbo, a_sbo, a_sw);
                         const uint64_t b_hi = make_desc(b_addr(stage, 0) + b_step, b_lbo, b_sbo, b_sw);
-                        const uint32_t first = (kb > 0 || ks > 0) ? 1u : 0u;
+                        const uint32_t first = (kb > U.kb0 || ks > 0) ? 1u : 0u;
                         if (TERMS == 3) {
                             const uint64_t a_lo = make_desc(a_addr(stage, 1) + a_step, a_lbo, a_sbo, a_sw);
                             const uint64_t b_lo = make_desc(b_addr(stage, 1) + b_step, b_lbo, b_sbo, b_sw);
@@ -715,9 +753,10 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
-        for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
-            const int64_t m0 = static_cast<int64_t>(tile / P.tiles_n) * (2 * BM) + static_cast<int64_t>(rank) * BM;
-            const int64_t n0 = static_cast<int64_t>(tile % P.tiles_n) * BN;
+        for (int u = first_unit; u < num_units && ok; u += unit_step) {
+            const Unit U = unit_of(u, P);
+            const int64_t m0 = static_cast<int64_t>(U.tile / P.tiles_n) * (2 * BM) + static_cast<int64_t>(rank) * BM;
+            const int64_t n0 = static_cast<int64_t>(U.tile % P.tiles_n) * BN;
             if (!mbar_wait(tfull_bar(acc), acc_phase, &abort_flag, 0x700 | (16 + acc))) { ok = false; break; }
             tc_fence_after();
             const int64_t row = m0 + quarter * 32 + lane;
@@ -730,7 +769,20 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
                 tmem_ld_wait();
                 const int64_t col0 = n0 + cc * 32;
                 if (row < P.m && col0 < P.n) {
-                    if (P.vec_store && col0 + 32 <= P.n) {
+                    if (U.half) {
+                        // one K-half of the tile: add into the zeroed C
+                        if (P.vec_store && col0 + 32 <= P.n) {
+#pragma unroll
+                            for (int v = 0; v < 8; ++v)
+                                atomicAdd(reinterpret_cast<float4*>(crow + col0) + v,
+                                          make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                                      __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3])));
+                        } else {
+#pragma unroll
+                            for (int v = 0; v < 32; ++v)
+                                if (col0 + v < P.n) atomicAdd(crow + col0 + v, __uint_as_float(r[v]));
+                        }
+                    } else if (P.vec_store && col0 + 32 <= P.n) {
 #pragma unroll
                         for (int v = 0; v < 8; ++v)
                             __stcs(reinterpret_cast<float4*>(crow + col0) + v,
@@ -824,9 +876,9 @@ ctk_status launch_tc(const CUtensorMap maps[4], const Params& P, cudaStream_t st
         CTK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
         attr_set = true;
     }
-    const int tiles = P.tiles_m * P.tiles_n;
+    const int units = P.whole_tiles + 2 * (P.tiles_m * P.tiles_n - P.whole_tiles);
     const int sms = ctk::sm_count();
-    const int grid = tiles < sms ? tiles : sms;  // persistent: one CTA per SM
+    const int grid = units < sms ? units : sms;  // persistent: one CTA per SM
     kernel<<<grid, THREADS, C::SMEM_BYTES, st>>>(maps[0], maps[1], maps[2], maps[3], P);
     CTK_LAUNCH_CHECK("tcgen05_matmul_kernel");
     return CTK_OK;
@@ -841,6 +893,23 @@ ctk_status launch_tc_major(bool a_mn, bool b_mn, const CUtensorMap maps[4], cons
 }
 
 int pick_bn(int64_t n) { return n > 128 ? 256 : (n > 64 ? 128 : 64); }
+
+// Zeroes the output tiles [first, first + count) (tile_m x tile_n each, row-major tile order):
+// the tiles whose K-halves are added into C.
+__global__ void __launch_bounds__(256) zero_tiles_kernel(float* __restrict__ c, int64_t m, int64_t n, int tile_m, int tile_n, int tiles_n, int first, int parts) {
+    const int tile = first + blockIdx.x / parts, part = blockIdx.x % parts;
+    const int64_t m0 = static_cast<int64_t>(tile / tiles_n) * tile_m, n0 = static_cast<int64_t>(tile % tiles_n) * tile_n;
+    const int rows_per = (tile_m + parts - 1) / parts;
+    const int64_t r0 = m0 + static_cast<int64_t>(part) * rows_per;
+    const int64_t r1 = r0 + rows_per < m0 + tile_m ? r0 + rows_per : m0 + tile_m;
+    const int64_t c1 = n0 + tile_n < n ? n0 + tile_n : n;
+    for (int64_t r = r0 + (threadIdx.x >> 6); r < r1 && r < m; r += 4)
+        for (int64_t j = n0 + (threadIdx.x & 63); j < c1; j += 64) c[r * n + j] = 0.0f;
+}
+
+// Number of CTA pairs resident on the device (all instantiations of the pair kernel use the same
+// threads and shared memory, so one of them is asked).
+ctk_status resident_pairs(int* out);
 
 // ---- CTA-pair launch ----
 // Resident clusters of two per device, asked of the driver once (the kernels differ only in code, not in resources).
@@ -871,11 +940,40 @@ ctk_status launch_pair(const CUtensorMap maps[4], const Params& P, cudaStream_t 
         CTK_REQUIRE(n > 0, "the device cannot hold a cluster of two CTAs of the MatMul kernel");
         max_clusters[dev] = n;
     }
-    const int tiles = P.tiles_m * P.tiles_n;
-    const int clusters = tiles < max_clusters[dev] ? tiles : max_clusters[dev];
+    const int units = P.whole_tiles + 2 * (P.tiles_m * P.tiles_n - P.whole_tiles);
+    const int clusters = units < max_clusters[dev] ? units : max_clusters[dev];
     cfg.gridDim = dim3(2 * static_cast<unsigned>(clusters));
     CTK_CUDA(cudaLaunchKernelEx(&cfg, kernel, maps[0], maps[1], maps[2], maps[3], P));
     CTK_LAUNCH_CHECK("tcgen05_matmul_pair_kernel");
+    return CTK_OK;
+}
+
+ctk_status resident_pairs(int* out) {
+    static int pairs[64] = {0};
+    int dev = 0;
+    CTK_CUDA(cudaGetDevice(&dev));
+    CTK_REQUIRE(dev >= 0 && dev < 64, "device ordinal out of range");
+    if (!pairs[dev]) {
+        using C = pair::Cfg<3>;
+        auto kernel = pair::tcgen05_matmul_pair_kernel<3, false, false>;
+        CTK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+        cudaLaunchConfig_t cfg = {};
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.gridDim = dim3(2 * static_cast<unsigned>(ctk::sm_count()));
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = C::SMEM_BYTES;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        CTK_CUDA(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
+        CTK_REQUIRE(n > 0, "the device cannot hold a cluster of two CTAs of the MatMul kernel");
+        pairs[dev] = n;
+    }
+    *out = pairs[dev];
     return CTK_OK;
 }
 
@@ -899,6 +997,7 @@ bool classify(const float* p, int64_t mn, int64_t k, int64_t s_mn, int64_t s_k, 
 
 int g_default_mode = CTK_MATMUL_3XTF32;
 int g_pairing = 0;  // 0: CTA pairs where the shape allows, 1: single-CTA kernel only
+int g_split_tail = 1;  // 1: K-halves for the tiles of a last wave that fills at most half the machine
 
 // ---- optional per-launch timing of the tensor-core kernel ----
 struct TcProfile {
@@ -992,6 +1091,12 @@ ctk_status ctk_set_matmul_mode(int mode) {
     return CTK_OK;
 }
 int ctk_get_matmul_mode(void) { return g_default_mode; }
+
+ctk_status ctk_set_matmul_tail_split(int on) {
+    CTK_REQUIRE(on == 0 || on == 1, "ctk_set_matmul_tail_split: 0 or 1");
+    g_split_tail = on;
+    return CTK_OK;
+}
 
 ctk_status ctk_set_matmul_pairing(int pairing) {
     CTK_REQUIRE(pairing == 0 || pairing == 1, "ctk_set_matmul_pairing: 0 (CTA pairs where possible) or 1 (single-CTA kernel only)");
@@ -1143,7 +1248,22 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
     P.num_kb = static_cast<int>((k + tc::BK - 1) / tc::BK);
     P.c = c;
     P.vec_store = (n % 4 == 0) && ((reinterpret_cast<uintptr_t>(c) & 15u) == 0);
-    CTK_REQUIRE(static_cast<int64_t>(P.tiles_m) * P.tiles_n < (int64_t(1) << 31), "ctk_matmul_f32: too many tiles");
+    CTK_REQUIRE(static_cast<int64_t>(P.tiles_m) * P.tiles_n < (int64_t(1) << 30), "ctk_matmul_f32: too many tiles");
+    // The last wave: when at most half of the SMs (or CTA pairs) would have a tile, its tiles are
+    // computed as two K-halves each, added into zeroed C, so that twice as many work on it.
+    {
+        const int tiles = P.tiles_m * P.tiles_n;
+        int workers = ctk::sm_count();
+        if (paired && (rc = tc::resident_pairs(&workers))) return rc;
+        P.whole_tiles = tiles;
+        const int tail = tiles % workers;
+        if (g_split_tail && P.num_kb >= 16 && tail > 0 && 2 * tail <= workers) {
+            P.whole_tiles = tiles - tail;
+            const int parts = 4;
+            tc::zero_tiles_kernel<<<tail * parts, 256, 0, st>>>(c, m, n, tile_m, bn, P.tiles_n, P.whole_tiles, parts);
+            CTK_LAUNCH_CHECK("zero_tiles_kernel");
+        }
+    }
 
  #define CTK_TC(BN_)                                                                                 \
     (terms == 3 ? tc::launch_tc_major<BN_, 3>(A.mn_major, B.mn_major, maps, P, st)                  \

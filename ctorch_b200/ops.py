@@ -213,6 +213,10 @@ def set_matmul_pairing(pairing):
     check(lib.ctk_set_matmul_pairing(int(pairing)))
 
 
+def set_matmul_tail_split(on):
+    check(lib.ctk_set_matmul_tail_split(int(on)))
+
+
 def matmul_status():
     s = ctypes.c_int()
     check(lib.ctk_matmul_status(ctypes.byref(s)))

@@ -239,6 +239,11 @@ int ctk_get_matmul_mode(void);
 /* every product on the single-CTA kernel.  Both kernels accumulate k in the same order in fp32   */
 /* TMEM, so the result does not depend on the choice.                                              */
 ctk_status ctk_set_matmul_pairing(int pairing);
+/* 1 (default): when the last wave of output tiles would occupy at most half of the SMs (or CTA    */
+/* pairs) -- which includes every product with few tiles, like the 10-class layer -- each of its   */
+/* tiles is computed as two halves of K that are added into the zeroed output (two addends: the    */
+/* result does not depend on their order).  0: every tile whole.                                   */
+ctk_status ctk_set_matmul_tail_split(int on);
 size_t ctk_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k, int mode);
 ctk_status ctk_matmul_f32(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
                           int64_t sa0, int64_t sa1, int64_t sb0, int64_t sb1, int mode,

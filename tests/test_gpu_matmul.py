@@ -102,6 +102,41 @@ def test_cta_pair_kernel_agrees_with_single_cta_kernel(cb, orc, mode, ta, tb):
     assert_matmul_close(paired[rows], orc.matmul_rows(A, B, rows), TOL[mode], "sampled oracle rows")
 
 
+@pytest.mark.parametrize("mode", ["tf32", "3xtf32"])
+@pytest.mark.parametrize("pairing,m,k,n,ta,tb", [
+    (0, 384, 520, 600, False, False),      # 4 pair tiles: every tile computed as two K-halves
+    (0, 2560, 552, 2304, False, True),     # 90 pair tiles on 74 pairs: 74 whole + 16 halved
+    (0, 2304, 1000, 2560, True, False),    # the weight-gradient shape: A^T.dC
+    (1, 2560, 520, 2304, False, False),    # single-CTA kernel: 180 tiles on 148 SMs, 148 whole + 32 halved
+    (0, 8192, 640, 10, False, False),      # the 10-class layer forward: 64 tiles of 128 x 64, all halved
+    (0, 1024, 4100, 10, True, False),      # its weight gradient: 8 tiles, ragged K
+])
+def test_last_wave_in_k_halves(cb, orc, mode, pairing, m, k, n, ta, tb):
+    """Tiles of a last wave that would fill at most half the machine are computed as two K-halves added
+    into zeroed C: same result as whole tiles up to the order of two additions, and right."""
+    A, B, _ = _mats(m, k, n, 12)
+    sa = A.T.copy() if ta else A
+    sb = B.T.copy() if tb else B
+    dA, dB = cb.to_device(sa), cb.to_device(sb)
+    out = cb.empty((m, n))
+    cb.ops.fill(out, 7.0)                  # stale contents must not leak into the sum
+    try:
+        cb.ops.set_matmul_pairing(pairing)
+        cb.ops.set_matmul_tail_split(0)
+        whole = cb.ops.matmul(dA, dB, ta, tb, mode).numpy()
+        cb.ops.set_matmul_tail_split(1)
+        halves = cb.ops.matmul(dA, dB, ta, tb, mode, out=out).numpy()
+        again = cb.ops.matmul(dA, dB, ta, tb, mode, out=out).numpy()
+    finally:
+        cb.ops.set_matmul_pairing(0)
+        cb.ops.set_matmul_tail_split(1)
+    _check_status(cb)
+    ref64 = A.astype(np.float64) @ B.astype(np.float64)
+    assert_matmul_close(halves, ref64, TOL[mode] * 1.5, f"K-halves vs fp64 {mode} {m}x{k}x{n}")
+    assert_matmul_close(halves, whole, 1e-6, "K-halves vs whole tiles")
+    assert np.array_equal(halves, again), "two addends: the result does not depend on which half lands first"
+
+
 def test_three_tf32_terms_reach_fp32_accuracy(cb, orc):
     """K = 4096, N(0,1): 3xTF32 must sit with the fp32 recurrence, TF32 visibly must not need to."""
     m, k, n = 128, 4096, 256
