@@ -19,7 +19,10 @@ with NCCL while backward runs.  Prints ONE JSON line (rank 0).
 
 `--impl reference` times that CPU path alone (rank 0; other ranks exit).
 Other workloads (single GPU): elementwise, rowwise, matmul -- the single-op sweeps of the other
-benchmark configs, one JSON line each with achieved GB/s or TFLOP/s.
+benchmark configs, one JSON line each with achieved GB/s or TFLOP/s; mlp_small -- the 784-128-10,
+batch-64, 100-step configuration the reference itself can run, timed next to the reference's CPU
+path; mnist -- the reference application (IDX files, 784-128-64-10, batch 128, 5 epochs, accuracy)
+on a synthetic data set in the same file format.
 """
 import argparse
 import ctypes
@@ -412,10 +415,71 @@ def run_single_op(args):
         print(json.dumps(dict(matmul_status=cb.ops.matmul_status())))
     elif args.workload == "mnist":
         run_mnist_app(cb, args, rng)
+    elif args.workload == "mlp_small":
+        run_mlp_small(cb, args)
     elif args.workload == "kernel":
         run_one_kernel(cb, args.case, rng)
     else:
         raise SystemExit("unknown workload " + args.workload)
+
+
+def run_mlp_small(cb, args):
+    """Benchmark config 1, the reference's own CPU-runnable case: 784-128-10, batch 64, SGD lr 0.01, a fixed
+    seeded sequence of 100 batches, 100 steps (launch-bound on a GPU: reported as samples/s and us per step).
+    The reference's CPU path runs the same 100 steps on one host core next to it."""
+    from ctorch_b200 import frontend as F
+    from ctorch_b200.device import PinnedArray
+    F.set_quiet(True)
+    dims, batch, steps, lr = [784, 128, 10], 64, 100, 0.01
+    rng = np.random.default_rng(1234)
+    xs = (rng.integers(0, 256, (steps, batch, 784)) / 255.0).astype(np.float32)
+    labs = rng.integers(0, 10, (steps, batch)).astype(np.float32)
+    wr = np.random.default_rng(42)
+    parts = []
+    for i, j in zip(dims[:-1], dims[1:]):
+        lim = np.sqrt(6.0 / i)
+        parts += [wr.uniform(-lim, lim, (i, j)).astype(np.float32).ravel(), np.zeros(j, np.float32)]
+    p0 = np.concatenate(parts)
+    px, pl = PinnedArray(xs.shape), PinnedArray(labs.shape)
+    px.array[...] = xs
+    pl.array[...] = labs
+
+    def run():
+        tr = F.MlpTrainer(dims, p0, lr)
+        e0, e1 = cb.Event(), cb.Event()
+        cb.synchronize()
+        e0.record()
+        loss = 0.0
+        for s in range(steps):
+            loss = tr.step_host(px.array[s], pl.array[s])
+        e1.record()
+        e1.sync()
+        return e0.elapsed_ms(e1) * 1e-3, loss
+
+    for _ in range(3):
+        run()
+    t, loss = run()
+    cpu = None
+    if not args.no_cpu_baseline:
+        import oracle
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)   # the reference prints a banner on stdout
+        try:
+            impl = oracle.Reference() if oracle.Reference.available() else oracle.Oracle()
+            n_cpu = 10
+            t0 = time.perf_counter()
+            impl.mlp_train(dims, xs[:n_cpu].reshape(1, n_cpu, batch, 784), labs[:n_cpu].reshape(1, n_cpu, batch), p0, lr, n_cpu, want_logits=False)
+            t_cpu = (time.perf_counter() - t0) / n_cpu
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved, 1)
+            os.close(saved)
+        cpu = dict(value=batch / t_cpu, unit="samples/s", cores=1, kind=impl.kind, sample=f"{n_cpu} steps of the same run, {t_cpu * 1e3:.1f} ms per step, host {host_cpu()}")
+    print(json.dumps(dict(metric="mlp_small_train_samples_per_s", value=steps * batch / t, unit="samples/s", n_gpus=1, steps=steps, higher_is_better=True,
+                          dtype="f32", data="synthetic", config=dict(workload="mlp-784-128-10_batch64_100-steps_from-host-batches", us_per_step=t / steps * 1e6, final_loss=float(loss)),
+                          e2e=dict(value=steps * batch / t, unit="samples/s", h2d_bytes_per_step=int(xs[0].nbytes + labs[0].nbytes), d2h_bytes_per_step=4),
+                          cpu_baseline=cpu)))
 
 
 def run_mnist_app(cb, args, rng):
@@ -427,7 +491,10 @@ def run_mnist_app(cb, args, rng):
     import tempfile
     from ctorch_b200 import frontend as F
     F.set_quiet(True)
-    dims, batch, epochs, lr = [784, 128, 64, 10], 128, 5, 0.01
+    # lr: the application's 0.01 acts on a loss SUMMED over the 128 rows of a batch; on this synthetic set
+    # that diverges (it is the reference's behaviour too), so the run uses 0.01 / 128, i.e. the same step
+    # on the mean loss, and says so in its config
+    dims, batch, epochs, lr = [784, 128, 64, 10], 128, 5, 0.01 / 128
 
     def synth(n):
         lab = rng.integers(0, 10, n).astype(np.uint8)
@@ -471,7 +538,7 @@ def run_mnist_app(cb, args, rng):
     steps = epochs * (60000 // batch)
     print(json.dumps(dict(metric="mnist_app_train_samples_per_s", value=steps * batch / train_s, unit="samples/s", n_gpus=1, higher_is_better=True,
                           data="synthetic IDX files (60000 + 10000 images of 28x28 bytes)", dtype="f32",
-                          config=dict(workload="mnist-app-784-128-64-10_batch128_lr0.01_5epochs", steps=steps, us_per_step=train_s / steps * 1e6),
+                          config=dict(workload="mnist-app-784-128-64-10_batch128_5epochs", lr=lr, steps=steps, us_per_step=train_s / steps * 1e6),
                           load_s=load_s, train_s=train_s, eval_s=eval_s, epoch_mean_loss=[float(v) for v in losses],
                           accuracy_train=float(acc_train), accuracy_test=float(acc_test))))
 
@@ -555,7 +622,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--pairing", type=int, default=0, choices=[0, 1], help="MatMul tile scheduling: 0 = CTA pairs where possible (default), 1 = single-CTA kernel only")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="mlp", choices=["mlp", "elementwise", "rowwise", "matmul", "kernel"])
+    ap.add_argument("--workload", default="mlp", choices=["mlp", "mlp_small", "mnist", "elementwise", "rowwise", "matmul", "kernel"])
     ap.add_argument("--case", default="matmul_3xtf32_4096x4096x4096", help="for --workload kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()

@@ -113,7 +113,8 @@ def test_cta_pair_kernel_agrees_with_single_cta_kernel(cb, orc, mode, ta, tb):
 ])
 def test_last_wave_in_k_halves(cb, orc, mode, pairing, m, k, n, ta, tb):
     """Tiles of a last wave that would fill at most half the machine are computed as two K-halves added
-    into zeroed C: same result as whole tiles up to the order of two additions, and right."""
+    into zeroed C: right, as close to the whole-tile result as two ways of cutting a long fp32 sum are,
+    and bit-identical from call to call."""
     A, B, _ = _mats(m, k, n, 12)
     sa = A.T.copy() if ta else A
     sb = B.T.copy() if tb else B
@@ -133,7 +134,8 @@ def test_last_wave_in_k_halves(cb, orc, mode, pairing, m, k, n, ta, tb):
     _check_status(cb)
     ref64 = A.astype(np.float64) @ B.astype(np.float64)
     assert_matmul_close(halves, ref64, TOL[mode] * 1.5, f"K-halves vs fp64 {mode} {m}x{k}x{n}")
-    assert_matmul_close(halves, whole, 1e-6, "K-halves vs whole tiles")
+    # (the tensor core's running fp32 sum is not correctly rounded, so where K is cut shows at the 1e-6..2e-5 level)
+    assert_matmul_close(halves, whole, 5e-5, "K-halves vs whole tiles")
     assert np.array_equal(halves, again), "two addends: the result does not depend on which half lands first"
 
 
