@@ -503,7 +503,7 @@ def run_mnist_app(cb, args, rng):
         for c in range(10):
             for sft in range(3):
                 idx = np.nonzero((lab == c) & (shift == sft))[0]
-                px[idx, 2 * c + sft: 2 * c + sft + 3, 4:24] = 255
+                px[idx, 2 * c + sft: 2 * c + sft + 3, 2 + 2 * c: 8 + 2 * c] = 255   # rows shift, columns name the class
         return px, lab
 
     with tempfile.TemporaryDirectory() as d:
