@@ -227,8 +227,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  On running out (or when another role already gave up) records `code` and raises
 // the CTA-wide abort flag; every role then leaves its loops and the CTA tears down normally.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, uint32_t limit = WAIT_LIMIT) {
+    for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 255u) == 255u) {
             if (*abort_flag) return false;
@@ -814,6 +814,29 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
 
 }  // namespace pair
 
+// ---- self-test of the bounded wait -------------------------------------------------------------------
+// One CTA waits, with the kernels' own wait routine and a short limit, on a barrier that nothing ever
+// arrives on.  The wait has to run out, record its code in the status word, raise the abort flag and
+// let the kernel return normally -- the path a real time-out would take -- without any fault.
+__global__ void wait_timeout_selftest_kernel(int* observed) {
+    __shared__ uint64_t bar;
+    __shared__ volatile int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    bool ok = true;
+    if (threadIdx.x == 0) ok = mbar_wait(smem_u32(&bar), 0u, &abort_flag, 0x7e57, 1u << 12);
+    __syncthreads();
+    // a second role sees the flag and gives up at once instead of running out itself
+    if (threadIdx.x == 32) ok = mbar_wait(smem_u32(&bar), 0u, &abort_flag, 0x7e58, 1u << 30);
+    __syncthreads();
+    if (threadIdx.x == 0) { observed[0] = ok ? 1 : 0; observed[1] = abort_flag; }
+    if (threadIdx.x == 32) observed[2] = ok ? 1 : 0;
+}
+
 // ---- host side -------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -1142,6 +1165,28 @@ ctk_status ctk_matmul_profile_read(int64_t* launches, double* total_ms, double* 
     *total_ms = ms;
     *total_flops = fl;
     g_prof.used = 0;
+    return CTK_OK;
+}
+
+// Runs the bounded-wait self-test: returns through `result` {wait returned ok (0 expected), abort flag
+// (1 expected), second waiter ok (0 expected), status word (0x7e57 expected)} and clears the status
+// word again.  No MatMul may be in flight.
+ctk_status ctk_matmul_selftest_wait_timeout(int result[4]) {
+    CTK_REQUIRE(result, "ctk_matmul_selftest_wait_timeout: null");
+    CTK_CUDA(cudaDeviceSynchronize());
+    int saved = 0;
+    CTK_CUDA(cudaMemcpyFromSymbol(&saved, g_tc_status, sizeof(int)));
+    const int zero = 0;
+    CTK_CUDA(cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int)));
+    int* dev = nullptr;
+    CTK_CUDA(cudaMalloc(&dev, 3 * sizeof(int)));
+    tc::wait_timeout_selftest_kernel<<<1, 64>>>(dev);
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpy(result, dev, 3 * sizeof(int), cudaMemcpyDeviceToHost);
+    cudaFree(dev);
+    CTK_CUDA(e);
+    CTK_CUDA(cudaMemcpyFromSymbol(&result[3], g_tc_status, sizeof(int)));
+    CTK_CUDA(cudaMemcpyToSymbol(g_tc_status, &saved, sizeof(int)));
     return CTK_OK;
 }
 

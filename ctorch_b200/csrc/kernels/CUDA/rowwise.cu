@@ -676,35 +676,40 @@ constexpr int kWarpRowThreads = 128;
 template <int ALG, int ITEMS, bool VEC>
 __global__ void __launch_bounds__(kWarpRowThreads) warp_rows_kernel(RowArgs A, ReduceScratch* scratch, float* loss_out) {
     __shared__ double red_d[33];
-    WarpRow<ITEMS, VEC> r, next;
-    r.cols = next.cols = static_cast<int>(A.cols);
-    r.t = next.t = threadIdx.x & 31;
+    WarpRow<ITEMS, VEC> r;
+    r.cols = static_cast<int>(A.cols);
+    r.t = threadIdx.x & 31;
     constexpr int kWarps = kWarpRowThreads / 32;
     const int64_t first = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
     const int64_t step = static_cast<int64_t>(gridDim.x) * kWarps;
     double acc = 0.0;
     bool poison = false;
-    // The loads of the warp's next row are issued before the current row is worked on, so a warp
-    // always has a row in flight (the persistent, loss-carrying forms loop here; the others run once).
-    float label = 0.0f;
-    if (first < A.rows) {
-        label = row_label<ALG>(A, first);
-        r.load(A.x + first * A.cols);
-    }
-    for (int64_t row = first; row < A.rows; row += step) {
-        const int64_t nrow = row + step;
-        float nlabel = 0.0f;
-        if (nrow < A.rows) {
-            nlabel = row_label<ALG>(A, nrow);
-            next.load(A.x + nrow * A.cols);
-        }
-        const float l = process_loaded<ALG>(r, A, row, label, poison);
-        if (alg_has_loss<ALG>()) acc += static_cast<double>(l);
+    if constexpr (!alg_has_loss<ALG>()) {
+        // one row per warp (the launcher sizes the grid so); the other resident warps hide its latency
+        for (int64_t row = first; row < A.rows; row += step) process_row<ALG>(r, A, row, A.x + row * A.cols, poison);
+    } else {
+        // Resident grid: a warp walks many rows, and the loads of its next TWO rows are in flight while
+        // the current one is worked on, so the few warps that fit (the three register sets cost
+        // occupancy) still keep ~8 KB each on their way from HBM.
+        WarpRow<ITEMS, VEC> n1, n2;
+        n1.cols = n2.cols = r.cols;
+        n1.t = n2.t = r.t;
+        float label = 0.0f, label1 = 0.0f, label2 = 0.0f;
+        if (first < A.rows) { label = row_label<ALG>(A, first); r.load(A.x + first * A.cols); }
+        if (first + step < A.rows) { label1 = row_label<ALG>(A, first + step); n1.load(A.x + (first + step) * A.cols); }
+        for (int64_t row = first; row < A.rows; row += step) {
+            const int64_t row2 = row + 2 * step;
+            if (row2 < A.rows) {
+                label2 = row_label<ALG>(A, row2);
+                n2.load(A.x + row2 * A.cols);
+            }
+            const float l = process_loaded<ALG>(r, A, row, label, poison);
+            acc += static_cast<double>(l);
 #pragma unroll
-        for (int it = 0; it < ITEMS; ++it) r.v[it] = next.v[it];
-        label = nlabel;
-    }
-    if (alg_has_loss<ALG>()) {
+            for (int it = 0; it < ITEMS; ++it) { r.v[it] = n1.v[it]; n1.v[it] = n2.v[it]; }
+            label = label1;
+            label1 = label2;
+        }
         if (poison && A.bad) *A.bad = 1;
         int any_poison = __syncthreads_or(poison ? 1 : 0);
         double total = block_sum(acc, red_d);

@@ -244,6 +244,11 @@ ctk_status ctk_set_matmul_pairing(int pairing);
 /* tiles is computed as two halves of K that are added into the zeroed output (two addends: the    */
 /* result does not depend on their order).  0: every tile whole.                                   */
 ctk_status ctk_set_matmul_tail_split(int on);
+/* Self-test of the kernels' bounded waits (no counterpart in the reference): one CTA waits with a  */
+/* short limit on a barrier nothing arrives on.  result = {first wait ok (expected 0), CTA abort     */
+/* flag (1), second waiter ok (0: it leaves as soon as it sees the flag), status word (0x7e57)}.    */
+/* The kernel returns normally; the status word is restored afterwards.                            */
+ctk_status ctk_matmul_selftest_wait_timeout(int result[4]);
 size_t ctk_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k, int mode);
 ctk_status ctk_matmul_f32(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
                           int64_t sa0, int64_t sa1, int64_t sb0, int64_t sb1, int mode,

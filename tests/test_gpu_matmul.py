@@ -202,3 +202,17 @@ def test_against_golden_fixture(cb, golden):
         assert_matmul_close(cb.ops.matmul(dC, B, tb=True).numpy(), G[tag + ".dA"], 1e-4, tag + " dA")
         assert_matmul_close(cb.ops.matmul(A, dC, ta=True).numpy(), G[tag + ".dB"], 1e-4, tag + " dB")
     _check_status(cb)
+
+
+def test_a_wait_that_runs_out_is_reported_not_hung(cb):
+    """Failure detection without a fault: the kernels' own bounded wait, on a barrier that nothing ever
+    arrives on, gives up after its limit, records a code, raises the CTA-wide abort flag (which a second
+    waiter honours at once), and the kernel returns normally: the context stays usable."""
+    import ctypes
+    res = (ctypes.c_int * 4)()
+    cb.check(cb.lib.ctk_matmul_selftest_wait_timeout(res))
+    assert list(res) == [0, 1, 0, 0x7e57]
+    assert cb.ops.matmul_status() == 0, "the self-test restores the status word"
+    A, B, _ = _mats(128, 64, 64, 13)
+    C = cb.ops.matmul(cb.to_device(A), cb.to_device(B)).numpy()       # the device still works
+    assert_matmul_close(C, A.astype(np.float64) @ B.astype(np.float64), 1e-4, "product after the self-test")
