@@ -311,9 +311,13 @@ def run_mlp(args, cp):
                      serial_call="cth_mlp_step_host: upload, step and loss read-back in sequence"),
             gpu_launches=int(launches),
             roofline=dict(bound="tensor", achieved=achieved, peak=peak, unit="TFLOP/s", frac=achieved / peak if peak else None, traffic=None,
-                          kernel="tcgen05_matmul_kernel (3xTF32)", launches=int(n), avg_launch_ms=tms / n if n else None,
+                          kernel="tcgen05_matmul_pair_kernel / tcgen05_matmul_kernel (3xTF32)", launches=int(n), avg_launch_ms=tms / n if n else None,
                           peak_source=f"{peaks['source']}: {bf16_key} {bf16_val} / 2 (TF32 runs at half the bf16 rate; no TF32 figure was measured) / 3 (three TF32 products per fp32 product); algorithmic flops 2*M*N*K",
-                          step_model_flops=flops_step, step_tflops=flops_step / (per_step * 1e-3) / 1e12),
+                          step_model_flops=flops_step, step_tflops=flops_step / (per_step * 1e-3) / 1e12,
+                          # context for a fraction above 1: the measured ceiling is cuBLAS bf16 (73 % of the nominal 2250) scaled
+                          # to TF32; against the nominal dense TF32 rate (1125 TFLOP/s, a third of it per fp32 product):
+                          nominal_peak=375.0, frac_of_nominal=achieved / 375.0,
+                          tensor_pipe_active="97.5 % of active SM cycles (ncu, profiles/tcgen05_matmul_pair_3xtf32_4096.md)"),
             cpu_baseline=cpu,
         )
         print(json.dumps(out))
