@@ -9,10 +9,13 @@
 // (make_unique) before any write, so the reference's deep copies (copy ctor, make_leaf,
 // commit_record, t(), get_grad) cost nothing until someone writes.
 #pragma once
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <memory>
 #include <mutex>
+#include <unordered_map>
+#include <vector>
 
 #include "Ctools.h"
 #include "Ctorch_Error.h"
@@ -73,6 +76,70 @@ public:
     }
 };
 
+// Device buffers of tensors: every op allocates its result and frees its temporaries, the same sizes
+// step after step.  Freed buffers are parked here by size and handed out again without a call into
+// the CUDA runtime (a stream-ordered allocate / free pair costs 2-3 us of host time, which is most of
+// a small training step); misses and overflow go to the device pool.  As with the pool, reuse is
+// ordered by the compute stream: a parked buffer may still be read by queued kernels, and its next
+// owner only touches it with kernels queued after them.
+class DeviceBlockCache {
+    std::mutex mu_;
+    std::unordered_map<size_t, std::vector<void*>> free_;
+    size_t parked_bytes_ = 0;
+    static constexpr size_t kMaxParked = size_t(32) << 30;
+
+public:
+    static DeviceBlockCache& instance() {
+        static DeviceBlockCache* c = new DeviceBlockCache();  // never destroyed: outlives every tensor
+        return *c;
+    }
+    static size_t rounded(size_t bytes) { return (bytes + 511) & ~size_t(511); }
+    // CTORCH_BLOCK_CACHE=0 in the environment sends every allocation straight to the device pool.
+    static bool enabled() {
+        static const bool on = [] {
+            const char* e = std::getenv("CTORCH_BLOCK_CACHE");
+            return !(e && e[0] == '0');
+        }();
+        return on;
+    }
+    void* get(size_t bytes) {
+        bytes = rounded(bytes);
+        if (enabled()) {
+            std::lock_guard<std::mutex> lock(mu_);
+            auto it = free_.find(bytes);
+            if (it != free_.end() && !it->second.empty()) {
+                void* p = it->second.back();
+                it->second.pop_back();
+                parked_bytes_ -= bytes;
+                return p;
+            }
+        }
+        void* p = nullptr;
+        cuda_check(ctk_malloc(&p, bytes), "Storage: device allocation");
+        return p;
+    }
+    void put(void* p, size_t bytes) {
+        bytes = rounded(bytes);
+        if (enabled()) {
+            std::lock_guard<std::mutex> lock(mu_);
+            if (parked_bytes_ + bytes <= kMaxParked) {
+                free_[bytes].push_back(p);
+                parked_bytes_ += bytes;
+                return;
+            }
+        }
+        ctk_free(p);
+    }
+    // Gives every parked buffer back to the device pool.
+    void trim() {
+        std::lock_guard<std::mutex> lock(mu_);
+        for (auto& kv : free_)
+            for (void* p : kv.second) ctk_free(p);
+        free_.clear();
+        parked_bytes_ = 0;
+    }
+};
+
 struct KeptSplit {
     void* buf = nullptr;
     size_t bytes = 0;
@@ -91,12 +158,12 @@ class Storage {
         std::unique_ptr<KeptSplit> split;  // dropped whenever the buffer is about to be written
         Block(size_t b, DeviceType d) : bytes(b), device(d) {
             if (b == 0) return;
-            if (d == DeviceType::kCUDA) cuda_check(ctk_malloc(&ptr, b), "Storage: device allocation");
+            if (d == DeviceType::kCUDA) ptr = DeviceBlockCache::instance().get(b);
             else ptr = ::operator new(b);
         }
         ~Block() {
             if (!ptr) return;
-            if (device == DeviceType::kCUDA) ctk_free(ptr);
+            if (device == DeviceType::kCUDA) DeviceBlockCache::instance().put(ptr, bytes);
             else ::operator delete(ptr);
         }
         Block(const Block&) = delete;
