@@ -204,6 +204,14 @@ void AutoDiff::dfs_topological_sort(Node* node, std::unordered_set<Node*>& visit
 
 void AutoDiff::backward(Tensor& root) {
     AutoDiffContext::Guard guard(nullptr);  // no recording while gradients are computed
+    if (root.device() == DeviceType::kCUDA) {
+        // the reference's Tensor(1.0f) (:551), made where the root lives: one fill launch instead of an
+        // upload through the staging buffers (which waits on the host, and cannot be captured)
+        Tensor one(ShapeTag{}, std::vector<size_t>{}, DType::kFloat, DeviceType::kCUDA, false);
+        one.fill(1.0f);
+        backward(root, one);
+        return;
+    }
     Tensor grad_output(1.0f);               // a host 0-D tensor, as in the reference (:551)
     backward(root, grad_output);
 }

@@ -15,6 +15,7 @@
 #include <memory>
 #include <mutex>
 #include <unordered_map>
+#include <unordered_set>
 #include <vector>
 
 #include "Ctools.h"
@@ -24,119 +25,149 @@
 namespace ctorch {
 
 void cuda_check(int status, const char* what);  // throws on a non-zero ctk_status
+void* current_stream();                          // the calling thread's compute stream (Tensor.cpp)
 
 // The hi/lo split of a buffer's contents that the 3xTF32 MatMul made on first use, kept with the
 // buffer so that later products of the same values (the same view, or its transpose) reuse it.
 // `view` identifies the 2-D view it was made for; `valid` is the flag the kernel library fills in.
-// Split buffers are large (twice the operand) and come and go with every activation of every step.
-// They are plain device allocations, outside the stream-ordered pool the tensors live in (mixed in
-// there, their different sizes and lifetimes fragment it until it has to map new memory in the
-// middle of a step), parked here by size when their operand dies and handed out again.
-// Reuse is ordered by the compute stream: a parked buffer may still be read by queued kernels, and
-// whoever gets it next only touches it with kernels queued after them.
-class SplitBufferCache {
+// Size-keyed cache of device buffers, the common part of the two caches below.  Freed buffers are
+// parked by (rounded) size and handed out again without a call into the CUDA runtime.  Reuse is
+// ordered by the compute stream: a parked buffer may still be read by queued kernels, and its next
+// owner only touches it with kernels queued after them.
+//
+// While a training step is being captured into a CUDA graph, every buffer that is handed out or
+// given back becomes "pinned" to the graph: the graph's kernels have its address baked in, so until
+// the graph is released such a buffer is only ever reused inside the captured sequence (through a
+// private free list), never by anyone else.  A miss during capture is remembered -- the capture is
+// then abandoned by its owner -- because allocating in the middle of a capture is not allowed.
+class SizeKeyedCache {
     std::mutex mu_;
-    std::multimap<size_t, void*> free_;
+    std::unordered_map<size_t, std::vector<void*>> free_;      // anyone's
+    std::unordered_map<size_t, std::vector<void*>> pinned_free_;  // the graph's
+    std::unordered_set<void*> pinned_;
     size_t parked_bytes_ = 0;
-    static constexpr size_t kMaxParked = size_t(16) << 30;
+    bool capturing_ = false, missed_ = false;
+
+protected:
+    virtual ~SizeKeyedCache() = default;
+    virtual size_t rounded(size_t bytes) const = 0;
+    virtual size_t max_parked() const = 0;
+    virtual void* fresh(size_t bytes) = 0;
+    virtual void release(void* p) = 0;
+    virtual bool enabled() const { return true; }
+
+public:
+    void* get(size_t bytes) {
+        bytes = rounded(bytes);
+        if (enabled()) {
+            std::lock_guard<std::mutex> lock(mu_);
+            if (capturing_) {
+                auto it = pinned_free_.find(bytes);
+                if (it != pinned_free_.end() && !it->second.empty()) {
+                    void* p = it->second.back();
+                    it->second.pop_back();
+                    return p;
+                }
+            }
+            auto it = free_.find(bytes);
+            if (it != free_.end() && !it->second.empty()) {
+                void* p = it->second.back();
+                it->second.pop_back();
+                parked_bytes_ -= bytes;
+                if (capturing_) pinned_.insert(p);
+                return p;
+            }
+            if (capturing_) missed_ = true;
+        }
+        return fresh(bytes);
+    }
+    void put(void* p, size_t bytes) {
+        bytes = rounded(bytes);
+        if (enabled()) {
+            std::lock_guard<std::mutex> lock(mu_);
+            if (capturing_) pinned_.insert(p);
+            if (pinned_.count(p)) {
+                pinned_free_[bytes].push_back(p);
+                return;
+            }
+            if (parked_bytes_ + bytes <= max_parked()) {
+                free_[bytes].push_back(p);
+                parked_bytes_ += bytes;
+                return;
+            }
+        }
+        release(p);
+    }
+    void begin_capture() {
+        std::lock_guard<std::mutex> lock(mu_);
+        capturing_ = true;
+        missed_ = false;
+    }
+    // Returns false if a buffer had to be allocated during the capture.
+    bool end_capture() {
+        std::lock_guard<std::mutex> lock(mu_);
+        capturing_ = false;
+        return !missed_;
+    }
+    // The graph is gone: its buffers are anyone's again.
+    void release_graph() {
+        std::lock_guard<std::mutex> lock(mu_);
+        for (auto& kv : pinned_free_)
+            for (void* p : kv.second) {
+                free_[kv.first].push_back(p);
+                parked_bytes_ += kv.first;
+            }
+        pinned_free_.clear();
+        pinned_.clear();
+    }
+};
+
+// Split buffers (hi/lo copies of MatMul operands) are large -- twice the operand -- and come and go
+// with every activation of every step.  They are plain device allocations, outside the
+// stream-ordered pool the tensors live in: mixed in there, their different sizes and lifetimes
+// fragment it until it has to map new memory in the middle of a step.
+class SplitBufferCache : public SizeKeyedCache {
+    size_t rounded(size_t bytes) const override { return (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1); }
+    size_t max_parked() const override { return size_t(16) << 30; }
+    void* fresh(size_t bytes) override {
+        void* p = nullptr;
+        cuda_check(ctk_malloc_longlived(&p, bytes), "Storage: split buffer");  // a miss: warm-up only
+        return p;
+    }
+    void release(void* p) override { ctk_free_longlived(p); }
 
 public:
     static SplitBufferCache& instance() {
         static SplitBufferCache* c = new SplitBufferCache();  // never destroyed: outlives every tensor
         return *c;
     }
-    static size_t rounded(size_t bytes) { return (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1); }
-    void* get(size_t bytes) {
-        bytes = rounded(bytes);
-        {
-            std::lock_guard<std::mutex> lock(mu_);
-            auto it = free_.find(bytes);
-            if (it != free_.end()) {
-                void* p = it->second;
-                free_.erase(it);
-                parked_bytes_ -= bytes;
-                return p;
-            }
-        }
-        void* p = nullptr;
-        cuda_check(ctk_malloc_longlived(&p, bytes), "Storage: split buffer");  // a miss: warm-up only
-        return p;
-    }
-    void put(void* p, size_t bytes) {
-        bytes = rounded(bytes);
-        {
-            std::lock_guard<std::mutex> lock(mu_);
-            if (parked_bytes_ + bytes <= kMaxParked) {
-                free_.emplace(bytes, p);
-                parked_bytes_ += bytes;
-                return;
-            }
-        }
-        ctk_free_longlived(p);
-    }
 };
 
 // Device buffers of tensors: every op allocates its result and frees its temporaries, the same sizes
-// step after step.  Freed buffers are parked here by size and handed out again without a call into
-// the CUDA runtime (a stream-ordered allocate / free pair costs 2-3 us of host time, which is most of
-// a small training step); misses and overflow go to the device pool.  As with the pool, reuse is
-// ordered by the compute stream: a parked buffer may still be read by queued kernels, and its next
-// owner only touches it with kernels queued after them.
-class DeviceBlockCache {
-    std::mutex mu_;
-    std::unordered_map<size_t, std::vector<void*>> free_;
-    size_t parked_bytes_ = 0;
-    static constexpr size_t kMaxParked = size_t(32) << 30;
-
-public:
-    static DeviceBlockCache& instance() {
-        static DeviceBlockCache* c = new DeviceBlockCache();  // never destroyed: outlives every tensor
-        return *c;
+// step after step; a stream-ordered allocate / free pair costs 2-3 us of host time, which is most
+// of a small training step.  Misses and overflow go to the device pool.
+// CTORCH_BLOCK_CACHE=0 in the environment sends every allocation straight to the pool.
+class DeviceBlockCache : public SizeKeyedCache {
+    size_t rounded(size_t bytes) const override { return (bytes + 511) & ~size_t(511); }
+    size_t max_parked() const override { return size_t(32) << 30; }
+    void* fresh(size_t bytes) override {
+        void* p = nullptr;
+        cuda_check(ctk_malloc(&p, bytes), "Storage: device allocation");
+        return p;
     }
-    static size_t rounded(size_t bytes) { return (bytes + 511) & ~size_t(511); }
-    // CTORCH_BLOCK_CACHE=0 in the environment sends every allocation straight to the device pool.
-    static bool enabled() {
+    void release(void* p) override { ctk_free(p); }
+    bool enabled() const override {
         static const bool on = [] {
             const char* e = std::getenv("CTORCH_BLOCK_CACHE");
             return !(e && e[0] == '0');
         }();
         return on;
     }
-    void* get(size_t bytes) {
-        bytes = rounded(bytes);
-        if (enabled()) {
-            std::lock_guard<std::mutex> lock(mu_);
-            auto it = free_.find(bytes);
-            if (it != free_.end() && !it->second.empty()) {
-                void* p = it->second.back();
-                it->second.pop_back();
-                parked_bytes_ -= bytes;
-                return p;
-            }
-        }
-        void* p = nullptr;
-        cuda_check(ctk_malloc(&p, bytes), "Storage: device allocation");
-        return p;
-    }
-    void put(void* p, size_t bytes) {
-        bytes = rounded(bytes);
-        if (enabled()) {
-            std::lock_guard<std::mutex> lock(mu_);
-            if (parked_bytes_ + bytes <= kMaxParked) {
-                free_[bytes].push_back(p);
-                parked_bytes_ += bytes;
-                return;
-            }
-        }
-        ctk_free(p);
-    }
-    // Gives every parked buffer back to the device pool.
-    void trim() {
-        std::lock_guard<std::mutex> lock(mu_);
-        for (auto& kv : free_)
-            for (void* p : kv.second) ctk_free(p);
-        free_.clear();
-        parked_bytes_ = 0;
+
+public:
+    static DeviceBlockCache& instance() {
+        static DeviceBlockCache* c = new DeviceBlockCache();  // never destroyed: outlives every tensor
+        return *c;
     }
 };
 
@@ -224,7 +255,7 @@ public:
     Storage clone() const {
         Storage s(_size, _dtype, _device);
         if (_size > 0 && _data) {
-            if (_device == DeviceType::kCUDA) cuda_check(ctk_memcpy_d2d(s._data->ptr, _data->ptr, nbytes(), nullptr), "Storage::clone");
+            if (_device == DeviceType::kCUDA) cuda_check(ctk_memcpy_d2d(s._data->ptr, _data->ptr, nbytes(), current_stream()), "Storage::clone");
             else std::memcpy(s._data->ptr, _data->ptr, nbytes());
         }
         return s;

@@ -89,6 +89,8 @@ public:
 
     ~MlpTrainer() {
         ctk_device_sync();
+        release_graph();
+        if (graph.stream) ctk_stream_destroy(graph.stream);
         if (comm_stream) ctk_stream_destroy(comm_stream);
         if (ev_grad) ctk_event_destroy(ev_grad);
         if (ev_comm) ctk_event_destroy(ev_comm);
@@ -150,10 +152,15 @@ public:
         cuda_check(ctk_pool_reserve(bytes), "pool reservation");
     }
 
-    float step(const Tensor& x, const Tensor& y_one_hot) {
+    // capturing: the step is being recorded into a graph -- nothing may wait on the device, and the
+    // loss is read by whoever launches the graph.
+    float step(const Tensor& x, const Tensor& y_one_hot, bool capturing = false) {
         AutoDiffContext::Guard guard(&ctx);
         void* st = current_stream();
-        reserve_for(static_cast<int64_t>(x.sizes()[0]));
+        if (!capturing) {
+            if (graph.exec && st != graph.stream) release_graph();  // an eager step changes what the graph's buffers hold
+            reserve_for(static_cast<int64_t>(x.sizes()[0]));
+        }
         for (size_t l = 0; l < W.size(); ++l) {
             ctx.make_leaf(W[l], true);
             ctx.make_leaf(b[l], true);
@@ -170,7 +177,10 @@ public:
         Tensor loss = logits.cross_entropy(y_one_hot);
         // loss.item() of the reference step, without stalling the GPU between forward and backward:
         // the value is copied to a page-locked slot now and read once the step has been issued.
-        cuda_check(ctk_memcpy_d2h(pinned_loss, loss.data<float>(), sizeof(float), st), "loss read-back");
+        {
+            const Tensor& loss_value = loss;  // read-only access: the tape shares this buffer, a writable pointer would copy it
+            cuda_check(ctk_memcpy_d2h(pinned_loss, loss_value.data<float>(), sizeof(float), st), "loss read-back");
+        }
         backward(loss);
         if (comm) {
             cuda_check(ctk_event_record(ev_comm, comm_stream), "record");
@@ -181,10 +191,144 @@ public:
             b[l].sgd_update_(grad(b[l]), lr);
         }
         if (keep_logits) last_logits = logits;
-        cuda_check(st ? ctk_stream_sync(st) : ctk_device_sync(), "step sync");
+        if (!capturing) cuda_check(st ? ctk_stream_sync(st) : ctk_device_sync(), "step sync");
         ctx.release_step_nodes();
         ++steps_done;
+        return capturing ? 0.0f : *static_cast<float*>(pinned_loss);
+    }
+
+    // ---- the step as a CUDA graph -------------------------------------------------------------------
+    // For steps that are bound by launch latency (small layers, small batches): the third step of a
+    // batch size is recorded -- ~20 kernels, their buffers and tensor maps -- and every later step
+    // replays it with one launch.  The first two run eagerly: they set up everything that may not
+    // happen during a capture (kernel attributes, scratch, the caches' buffers).  Inputs enter through two
+    // fixed device tensors.  The recorded kernels have their buffers' addresses baked in, so those
+    // buffers stay pinned to the graph in the caches until the graph is released (a different batch
+    // size, an eager step, the trainer's end).  Not available with a communicator.
+    struct GraphStep {
+        void* exec = nullptr;
+        void* stream = nullptr;
+        Tensor x, labels;
+        int64_t batch = -1;
+        int warm_steps = 0;
+        int kernels = 0;
+        bool first_launch = false;
+    } graph;
+    // The caches keep one set of graph-pinned buffers per process: one trainer at a time owns it.
+    static MlpTrainer*& graph_owner() {
+        static MlpTrainer* owner = nullptr;
+        return owner;
+    }
+
+    void release_graph() {
+        if (!graph.exec) return;
+        ctk_device_sync();
+        ctk_graph_destroy(graph.exec);
+        graph.exec = nullptr;
+        graph.warm_steps = 0;
+        DeviceBlockCache::instance().release_graph();
+        SplitBufferCache::instance().release_graph();
+        if (graph_owner() == this) graph_owner() = nullptr;
+    }
+
+    // Uploads (or copies, for device sources) one batch into the graph's input tensors.
+    void graph_inputs(const float* x_src, const float* labels_src, int64_t batch, bool src_on_device) {
+        const size_t in = static_cast<size_t>(dims.front());
+        if (graph.batch != batch) {
+            release_graph();
+            graph.x = Tensor(ShapeTag{}, {static_cast<size_t>(batch), in}, DType::kFloat, DeviceType::kCUDA, false);
+            graph.labels = Tensor(ShapeTag{}, {static_cast<size_t>(batch)}, DType::kFloat, DeviceType::kCUDA, false);
+            graph.batch = batch;
+            graph.warm_steps = 0;
+            cuda_check(ctk_device_sync(), "graph input allocation");
+        }
+        const size_t xb = static_cast<size_t>(batch) * in * sizeof(float), lb = static_cast<size_t>(batch) * sizeof(float);
+        if (src_on_device) {
+            cuda_check(ctk_memcpy_d2d(graph.x.data<float>(), x_src, xb, graph.stream), "batch copy");
+            cuda_check(ctk_memcpy_d2d(graph.labels.data<float>(), labels_src, lb, graph.stream), "label copy");
+            return;
+        }
+        int px = 0, pl = 0;
+        ctk_host_is_pinned(x_src, &px);
+        ctk_host_is_pinned(labels_src, &pl);
+        if (px) cuda_check(ctk_memcpy_h2d(graph.x.data<float>(), x_src, xb, graph.stream), "input upload");
+        else graph.x.copy_from_host(x_src, static_cast<size_t>(batch) * in);
+        if (pl) cuda_check(ctk_memcpy_h2d(graph.labels.data<float>(), labels_src, lb, graph.stream), "label upload");
+        else graph.labels.copy_from_host(labels_src, static_cast<size_t>(batch));
+    }
+
+    // One step on the batch that graph_inputs put in place: eager (first), capture + launch (second),
+    // launch (from then on).
+    float graph_step() {
+        const size_t classes = static_cast<size_t>(dims.back());
+        auto eager = [&](bool capturing) {
+            Tensor y(ShapeTag{}, {static_cast<size_t>(graph.batch), classes}, DType::kFloat, DeviceType::kCUDA, false);
+            const Tensor& labels = graph.labels;
+            cuda_check(ctk_onehot_f32(labels.data<float>(), graph.batch, static_cast<int64_t>(classes), y.data<float>(), graph.stream), "one-hot");
+            return step(graph.x, y, capturing);
+        };
+        // two eager steps first: the very first step of a trainer allocates things no later step does
+        // (gradient buffers, the split of the weight snapshot), so only from the second step on does a
+        // step take from the caches exactly what the previous one gave back
+        if (!graph.exec && graph.warm_steps < 2) {
+            ++graph.warm_steps;
+            return eager(false);
+        }
+        if (!graph.exec) {
+            if (graph_owner() && graph_owner() != this)
+                throw std::runtime_error("cth_mlp_step_graph_*: another trainer of this process holds a recorded step; destroy it or run an eager step on it first");
+            graph_owner() = this;
+            const uint64_t launches0 = ctk_launch_count();
+            DeviceBlockCache::instance().begin_capture();
+            SplitBufferCache::instance().begin_capture();
+            int rc = ctk_stream_begin_capture(graph.stream);
+            bool threw = false;
+            std::string what;
+            if (!rc) {
+                try {
+                    eager(true);
+                } catch (const std::exception& e) {
+                    threw = true;
+                    what = e.what();
+                }
+                void* exec = nullptr;
+                rc = ctk_stream_end_capture(graph.stream, &exec);
+                graph.exec = exec;
+            }
+            const bool hit_a = DeviceBlockCache::instance().end_capture();
+            const bool hit_b = SplitBufferCache::instance().end_capture();
+            graph.kernels = static_cast<int>(ctk_launch_count() - launches0);
+            if (rc || threw || !hit_a || !hit_b || !graph.exec) {
+                if (graph.exec) { ctk_graph_destroy(graph.exec); graph.exec = nullptr; }
+                DeviceBlockCache::instance().release_graph();
+                SplitBufferCache::instance().release_graph();
+                graph_owner() = nullptr;
+                // (the recorded step never ran: this trainer's weights and gradients are no longer defined)
+                throw std::runtime_error("the training step could not be captured into a graph: " +
+                                         (threw ? what : rc ? std::string(ctk_last_error()) : std::string("a buffer had to be allocated during the capture")));
+            }
+            graph.first_launch = true;  // its kernels were already counted while they were recorded
+        }
+        cuda_check(ctk_graph_launch(graph.exec, graph.stream, graph.first_launch ? 0 : graph.kernels), "graph launch");
+        graph.first_launch = false;
+        cuda_check(ctk_stream_sync(graph.stream), "step sync");
         return *static_cast<float*>(pinned_loss);
+    }
+
+    float step_graph(const float* x_src, const float* labels_src, int64_t batch, bool src_on_device) {
+        if (comm) throw std::runtime_error("cth_mlp_step_graph_*: not available with a communicator");
+        if (!graph.stream) cuda_check(ctk_stream_create_ex(&graph.stream, 0), "graph stream");
+        void* saved = current_stream();
+        set_current_stream(graph.stream);
+        try {
+            graph_inputs(x_src, labels_src, batch, src_on_device);
+            const float loss = graph_step();
+            set_current_stream(saved);
+            return loss;
+        } catch (...) {
+            set_current_stream(saved);
+            throw;
+        }
     }
 
     // The same step from HOST inputs: pixels and integer labels (as floats) in caller memory.  The
@@ -284,8 +428,17 @@ public:
     // One pass over a device-resident data set in batches of `batch_size` rows, in order, as the
     // epoch loop of mnist/mnist.cpp:246-262 (the remainder that does not fill a batch is skipped, as
     // there).  Batches are views of the data set, not copies.  Returns the mean of the step losses.
-    float train_epoch(const Tensor& images, const Tensor& labels, int64_t batch_size) {
+    float train_epoch(const Tensor& images, const Tensor& labels, int64_t batch_size, bool use_graph = false) {
         if (batch_size <= 0) throw std::runtime_error("train_epoch: batch size must be positive");
+        if (use_graph) {
+            const int64_t n = static_cast<int64_t>(images.sizes()[0]);
+            const int64_t num_batches = n / batch_size;
+            const size_t in = static_cast<size_t>(dims.front());
+            float epoch_loss = 0.0f;
+            for (int64_t bi = 0; bi < num_batches; ++bi)
+                epoch_loss += step_graph(images.data<float>() + static_cast<size_t>(bi * batch_size) * in, labels.data<float>() + bi * batch_size, batch_size, true);
+            return num_batches ? epoch_loss / static_cast<float>(num_batches) : 0.0f;
+        }
         const int64_t n = static_cast<int64_t>(images.sizes()[0]);
         const int64_t num_batches = n / batch_size;
         const size_t classes = static_cast<size_t>(dims.back());
@@ -500,6 +653,12 @@ int cth_mlp_stage_host(void* m, const float* x_host, const float* labels_host, i
 }
 int cth_mlp_step_staged(void* m, float* loss) {
     return guarded([&] { *loss = static_cast<MlpTrainer*>(m)->step_staged(); });
+}
+int cth_mlp_step_graph_host(void* m, const float* x_host, const float* labels_host, int64_t batch, float* loss) {
+    return guarded([&] { *loss = static_cast<MlpTrainer*>(m)->step_graph(x_host, labels_host, batch, false); });
+}
+int cth_mlp_train_epoch_graph(void* m, void* images, void* labels, int64_t batch_size, float* mean_loss) {
+    return guarded([&] { *mean_loss = static_cast<MlpTrainer*>(m)->train_epoch(*T(images), *T(labels), batch_size, true); });
 }
 int cth_mlp_step_device(void* m, void* x, void* onehot, float* loss) {
     return guarded([&] { *loss = static_cast<MlpTrainer*>(m)->step(*T(x), *T(onehot)); });

@@ -234,6 +234,45 @@ ctk_status ctk_stream_sync(void* s) {
     CTK_CUDA(cudaStreamSynchronize(as_stream(s)));
     return CTK_OK;
 }
+// ---- stream capture into an executable graph ----
+// begin: starts capturing the work issued to `stream` (not the legacy default stream) by this thread.
+// end: ends the capture and instantiates the graph; *graph_exec is NULL and an error is returned if
+// the capture was invalidated.  launch / destroy: the executable graph.
+ctk_status ctk_stream_begin_capture(void* stream) {
+    CTK_REQUIRE(stream, "ctk_stream_begin_capture: a stream of its own is needed (the default stream cannot be captured)");
+    CTK_CUDA(cudaStreamBeginCapture(static_cast<cudaStream_t>(stream), cudaStreamCaptureModeThreadLocal));
+    return CTK_OK;
+}
+ctk_status ctk_stream_end_capture(void* stream, void** graph_exec) {
+    CTK_REQUIRE(stream && graph_exec, "ctk_stream_end_capture: null");
+    *graph_exec = nullptr;
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(static_cast<cudaStream_t>(stream), &graph);
+    if (e != cudaSuccess || !graph) {
+        cudaGetLastError();
+        return fail(CTK_ERR_CUDA, std::string("stream capture failed: ") + cudaGetErrorString(e));
+    }
+    cudaGraphExec_t exec = nullptr;
+    e = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(CTK_ERR_CUDA, std::string("graph instantiation failed: ") + cudaGetErrorString(e));
+    }
+    *graph_exec = exec;
+    return CTK_OK;
+}
+ctk_status ctk_graph_launch(void* graph_exec, void* stream, int kernels_in_graph) {
+    CTK_REQUIRE(graph_exec && stream, "ctk_graph_launch: null");
+    CTK_CUDA(cudaGraphLaunch(static_cast<cudaGraphExec_t>(graph_exec), static_cast<cudaStream_t>(stream)));
+    if (kernels_in_graph > 0) g_launches.fetch_add(static_cast<uint64_t>(kernels_in_graph), std::memory_order_relaxed);
+    return CTK_OK;
+}
+ctk_status ctk_graph_destroy(void* graph_exec) {
+    if (graph_exec) CTK_CUDA(cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(graph_exec)));
+    return CTK_OK;
+}
+
 ctk_status ctk_event_create(void** e) {
     CTK_REQUIRE(e, "ctk_event_create: null");
     cudaEvent_t ev;

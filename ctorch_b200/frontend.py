@@ -265,6 +265,17 @@ class MlpTrainer:
         _chk(lib.cth_mlp_train_epoch(self.h, images.h, labels.h, ctypes.c_int64(batch_size), ctypes.byref(loss)))
         return loss.value
 
+    def step_graph_host(self, x, labels):
+        """The step replayed as a CUDA graph (recorded on the second call of a batch size)."""
+        loss = ctypes.c_float()
+        _chk(lib.cth_mlp_step_graph_host(self.h, x.ctypes.data_as(_vp), labels.ctypes.data_as(_vp), ctypes.c_int64(x.shape[0]), ctypes.byref(loss)))
+        return loss.value
+
+    def train_epoch_graph(self, images, labels, batch_size):
+        loss = ctypes.c_float()
+        _chk(lib.cth_mlp_train_epoch_graph(self.h, images.h, labels.h, ctypes.c_int64(batch_size), ctypes.byref(loss)))
+        return loss.value
+
     def step_device(self, x, onehot):
         loss = ctypes.c_float()
         _chk(lib.cth_mlp_step_device(self.h, x.h, onehot.h, ctypes.byref(loss)))

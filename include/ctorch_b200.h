@@ -93,6 +93,15 @@ ctk_status ctk_stream_create(void** stream);
 ctk_status ctk_stream_create_ex(void** stream, int non_blocking);
 ctk_status ctk_stream_destroy(void* stream);
 ctk_status ctk_stream_sync(void* stream);
+/* Stream capture (no counterpart in the reference): the work this thread issues to `stream` between
+ * begin and end is recorded instead of run, and comes back as an executable graph that replays it
+ * with one launch.  `stream` must be a created stream (the default stream cannot be captured); nothing
+ * that allocates or synchronises may be called in between.  kernels_in_graph is added to
+ * ctk_launch_count() per replay. */
+ctk_status ctk_stream_begin_capture(void* stream);
+ctk_status ctk_stream_end_capture(void* stream, void** graph_exec);
+ctk_status ctk_graph_launch(void* graph_exec, void* stream, int kernels_in_graph);
+ctk_status ctk_graph_destroy(void* graph_exec);
 ctk_status ctk_event_create(void** event);
 ctk_status ctk_event_destroy(void* event);
 ctk_status ctk_event_record(void* event, void* stream);

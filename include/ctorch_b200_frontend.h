@@ -81,6 +81,14 @@ int cth_mlp_step_host(void* mlp, const float* x_host, const float* labels_host, 
  * A staged host buffer must stay unchanged until the step that consumes it has returned. */
 int cth_mlp_stage_host(void* mlp, const float* x_host, const float* labels_host, int64_t batch);
 int cth_mlp_step_staged(void* mlp, float* loss);
+/* The same step replayed as a CUDA graph, for steps bound by launch latency: the first two calls of a
+ * batch size run eagerly, the third records the step (its ~20 kernels, buffers and tensor maps) and every
+ * later call replays it with one launch; inputs pass through two fixed device tensors.  Results are
+ * the eager step's, bit for bit.  An eager step, another batch size or the trainer's end release
+ * the graph.  Not available while a communicator is set.  cth_mlp_train_epoch_graph is
+ * cth_mlp_train_epoch with every step taken this way (batches copied device-to-device). */
+int cth_mlp_step_graph_host(void* mlp, const float* x_host, const float* labels_host, int64_t batch, float* loss);
+int cth_mlp_train_epoch_graph(void* mlp, void* images, void* labels, int64_t batch_size, float* mean_loss);
 /* x and onehot are device tensors ([batch, dims[0]] and [batch, classes]). */
 int cth_mlp_step_device(void* mlp, void* x, void* onehot, float* loss);
 /* NeuralNetwork::predict (mnist/mnist.cpp:94-131): class probabilities [batch, classes] of a device

@@ -390,3 +390,55 @@ def test_zero_grad_then_read_then_accumulate(F):
         F.backward(dev(F, x).matmul(W).sum())
         F.backward(dev(F, x).matmul(W).sum())
         assert_exact(F.grad(W).numpy(), 2 * g1, "zero, then two contributions")
+
+
+def test_graph_replayed_steps_equal_eager_steps(F, cb):
+    """cth_mlp_step_graph_host: two eager calls, the third records the step into a CUDA graph, later calls
+    replay it.  Losses and weights must equal the eager trainer's bit for bit, across a change of batch
+    size (new graph), an interleaved eager step (graph released, recorded again) and pageable as well
+    as page-locked inputs."""
+    from ctorch_b200.device import PinnedArray
+    dims = [784, 128, 64, 10]
+    rng = np.random.default_rng(41)
+    _, _, p = _mlp_case(dims, 16, 1, 9, 10)
+
+    def batch(n):
+        return rng.integers(0, 256, (n, 784)).astype(np.float32) / np.float32(255.0), rng.integers(0, 10, n).astype(np.float32)
+
+    a, b = F.MlpTrainer(dims, p, 0.001), F.MlpTrainer(dims, p, 0.001)
+    seq = [batch(128) for _ in range(6)] + [batch(64) for _ in range(5)]
+    for i, (x, l) in enumerate(seq):
+        la = a.step_host(x, l)
+        if i == 3:
+            px, pl = PinnedArray(x.shape), PinnedArray(l.shape)
+            px.array[...] = x
+            pl.array[...] = l
+            lb = b.step_graph_host(px.array, pl.array)
+        else:
+            lb = b.step_graph_host(x, l)
+        assert la == lb, f"step {i}: eager {la} graph {lb}"
+    assert_exact(a.params(), b.params(), "weights after graph-replayed steps")
+    assert_exact(a.grads(), b.grads(), "gradients of the last step")
+    # an eager step in between releases the graph; the next graph steps record a new one
+    x, l = batch(64)
+    assert a.step_host(x, l) == b.step_host(x, l)
+    for _ in range(5):
+        x, l = batch(64)
+        assert a.step_host(x, l) == b.step_graph_host(x, l)
+    assert_exact(a.params(), b.params(), "weights after eager and graph steps interleaved")
+    assert cb.ops.matmul_status() == 0
+
+
+def test_graph_epoch_equals_eager_epoch(F, cb, golden, tmp_path):
+    import oracle as _o
+    import os
+    G = golden
+    _o.idx_write_images(os.path.join(tmp_path, "train-images-idx3-ubyte"), G["mnist.pixels"])
+    _o.idx_write_labels(os.path.join(tmp_path, "train-labels-idx1-ubyte"), G["mnist.labels_u8"])
+    im, lb = F.mnist_load(tmp_path)
+    dims = [int(v) for v in G["mnist.dims"]]
+    a, b = F.MlpTrainer(dims, G["mnist.params0"], 0.002), F.MlpTrainer(dims, G["mnist.params0"], 0.002)
+    for _ in range(3):
+        assert a.train_epoch(im, lb, 32) == b.train_epoch_graph(im, lb, 32)
+    assert_exact(a.params(), b.params(), "weights after three epochs")
+    assert a.accuracy(im, lb) == b.accuracy(im, lb)
