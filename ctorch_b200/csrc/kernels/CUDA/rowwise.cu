@@ -2,11 +2,14 @@
 //
 // HBM-bound.  Each row is read from HBM once and kept on chip while its max, exp-sum and outputs
 // are computed:
-//   cols <= 16   : a thread owns a row; a CTA moves its 256 rows between HBM and shared memory as one
-//                  contiguous block with coalesced 128-bit accesses (the 10-class layer);
-//   cols <= 128  : a warp owns a row, values live in registers, reductions are warp shuffles;
-//   cols <= 4096 : a CTA of 128/256 threads owns a row in registers (128-bit loads), reductions by
-//                  shuffle + one shared-memory hop, many CTAs per SM;
+//   cols <= 16   : a thread owns a row; a CTA moves its 512 rows between HBM and shared memory as one
+//                  contiguous block, with bulk asynchronous copies through two buffers so that the
+//                  load of the next block and the store of the previous one overlap the work on
+//                  the current one (the 10-class layer);
+//   cols <= 1024 : a warp owns a row, values live in registers (128-bit loads), reductions are warp
+//                  shuffles; the loss-carrying forms run a resident grid in which every warp keeps
+//                  its next two rows in flight;
+//   cols <= 4096 : a CTA of 128/256 threads owns a row in registers, one barrier per reduction;
 //   cols <= 32K  : one CTA per SM; a producer warp streams this CTA's rows through a 208 KiB ring of
 //                  shared memory with bulk asynchronous copies (cp.async.bulk + mbarriers) and runs
 //                  more than a row ahead, 512 consumer threads keep the current row in registers,
