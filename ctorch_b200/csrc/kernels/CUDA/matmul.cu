@@ -4,26 +4,32 @@
 // taken as that kernel reads them, so C = A.B, dA = dC.B^T and dB = A^T.dC (src/AutoDiff.cpp:
 // 1702-1704, 1808-1810, where B^T / A^T are stride-swapped views) are one entry point.
 //
-// Tensor-core path (the product): a persistent, warp-specialised tcgen05 kernel.
-//   warp 0     : TMA producer -- plain per-CTA cp.async.bulk.tensor loads into 128B-swizzled shared
+// Tensor-core path (the product): persistent, warp-specialised tcgen05 kernels.
+//   warp 0     : TMA producer -- per-CTA cp.async.bulk.tensor loads into 128B-swizzled shared
 //                memory, a ring of stages guarded by full/empty mbarriers;
-//   warp 1     : MMA issuer -- one elected lane issues tcgen05.mma.kind::tf32 (M=128, N=BN, K=8)
-//                from shared-memory descriptors into a TMEM accumulator, tcgen05.commit frees the
-//                stage; owns the TMEM allocation (two accumulators, so the epilogue of tile i
-//                overlaps the main loop of tile i+1);
+//   warp 1     : MMA issuer -- one elected lane issues tcgen05.mma.kind::tf32 from shared-memory
+//                descriptors into a TMEM accumulator, tcgen05.commit frees the stage; owns the TMEM
+//                allocation (two accumulators, so the epilogue of tile i overlaps the main loop of
+//                tile i+1);
 //   warps 2..5 : epilogue -- tcgen05.ld the accumulator (each warp its 32-lane quarter), store C.
+//   Two kernels share that skeleton: the CTA-pair kernel (a cluster of two CTAs, cta_group::2,
+//   M=256 N=256 K=8 per instruction, each CTA staging half of A's rows and half of B's columns) for
+//   every product with m, n > 128, and the single-CTA kernel (M=128, N in {64,128,256}) for the rest.
 //   Either operand may be K-major (row of K contiguous) or MN-major (row of M/N contiguous): the
 //   major-ness goes into the instruction descriptor and the shared-memory descriptors, no
 //   transposed copy is made.  M/N/K tails are zero-filled by TMA and masked at the store.
+//   The tiles of a last wave that would occupy at most half the machine are computed as two halves
+//   of K each, added into the zeroed output.
 //   TF32 mode multiplies the fp32 operands as they are (the tensor core reads the top 19 bits).
 //   3xTF32 mode first splits each operand x into hi = tf32(x) (round to nearest) and
-//   lo = tf32(x - hi) in a scratch buffer, then accumulates lo.hi + hi.lo + hi.hi in TMEM:
-//   the dropped term lo.lo is ~2^-22 of the product, i.e. fp32-level accuracy.
+//   lo = tf32(x - hi) in a scratch buffer (or one the caller keeps with the operand), then
+//   accumulates lo.hi + hi.lo + hi.hi in TMEM: the dropped term lo.lo is ~2^-22 of the product, i.e.
+//   fp32-level accuracy.
 //   Every mbarrier wait is bounded; a wait that runs out sets a device status word, the CTA drains
 //   its copies, frees its TMEM and returns.
 //
-// CUDA-core path: a plain fp32-FMA tiled kernel for operands TMA cannot address (a row pitch that
-// is not a multiple of 16 bytes, e.g. the 10-class layer) and on request (mode FP32_SIMT).
+// CUDA-core path: a plain fp32-FMA tiled kernel for operands without a unit stride, for TF32 mode on
+// operands TMA cannot address in place, and on request (mode FP32_SIMT).
 #include <cuda.h>
 #include <math.h>
 
