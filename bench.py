@@ -169,10 +169,17 @@ def _cpu_reference_step_time(oracle, steps, warmup, batch):
     return impl.kind, statistics.median(times), sum(times), batch
 
 
+def reference_sample_batch(n_steps):
+    """Rows per reference step such that warm-up + timed steps end in roughly 2-3 minutes: a step of the
+    reference at this width costs about 0.6 s + 1.5 s per row on one core."""
+    per_step = 150.0 / max(1, n_steps)
+    return int(min(CPU_SAMPLE_BATCH, max(1, (per_step - 0.6) // 1.5)))
+
+
 def run_reference(args, rank):
     if rank != 0:
         return
-    kind, t_step, total, batch = cpu_reference_step_time(args.steps, args.warmup)
+    kind, t_step, total, batch = cpu_reference_step_time(args.steps, args.warmup, batch=reference_sample_batch(args.steps + args.warmup))
     v = batch / t_step
     cpu = dict(value=v, unit="samples/s", cores=1, kind=kind,
                sample=f"{args.steps} timed steps of the same 784-4096-4096-4096-10 training step at batch {batch} (cost is linear in rows), median step {t_step:.3f} s, host {host_cpu()}")
