@@ -338,13 +338,16 @@ Tensor AutoDiff::rule(Node* node, size_t input_id, Node& input_node, bool& skip)
             const size_t rank = y.sizes().size();
             int dim = node->op_param_i;
             if (dim < 0) dim += static_cast<int>(rank);
-            if (rank == 0 || rank > 2 || dim != static_cast<int>(rank) - 1)
-                Ctorch_Error::throwException(ErrorPlatform::kAutoDiff, ErrorType::DIMENSION, "Softmax backward: only the last dim of 1-D/2-D tensors is implemented on the device");
+            if (rank == 0 || rank > 2 || dim < 0 || dim >= static_cast<int>(rank))
+                Ctorch_Error::throwException(ErrorPlatform::kAutoDiff, ErrorType::DIMENSION, "Softmax backward: 1-D and 2-D tensors, dim 0 or 1");
             const int64_t rows = rank == 1 ? 1 : static_cast<int64_t>(y.sizes()[0]);
             const int64_t cols = static_cast<int64_t>(y.sizes()[rank - 1]);
             Tensor g = check_and_adjust_grad_shape(node_grad, y.sizes(), y.device());
             Tensor dx(ShapeTag{}, y.sizes(), y.dtype(), y.device(), false);
-            cuda_check(ctk_softmax_backward_rows_f32(y.data<float>(), g.data<float>(), dx.data<float>(), rows, cols, st), "softmax backward");
+            if (dim == static_cast<int>(rank) - 1)   // along the rows (:1461-1472)
+                cuda_check(ctk_softmax_backward_rows_f32(y.data<float>(), g.data<float>(), dx.data<float>(), rows, cols, st), "softmax backward");
+            else                                     // down the columns (:1473-1484)
+                cuda_check(ctk_softmax_backward_cols_f32(y.data<float>(), g.data<float>(), dx.data<float>(), rows, cols, st), "softmax backward (dim 0)");
             return dx;
         }
         case op::MSE:

@@ -507,7 +507,17 @@ Tensor Tensor::softmax(int dim) const {
     if (dim < 0) dim += rank;
     if (dim < 0 || dim >= rank) Ctorch_Error::throwException(ErrorPlatform::kCPU, ErrorType::DIMENSION, "softmax: dim out of range");
     if (rank > 2) Ctorch_Error::throwException(ErrorPlatform::kCPU, ErrorType::DIMENSION, "softmax: only 1-D and 2-D tensors");
-    if (dim != rank - 1) Ctorch_Error::throwException(DeviceTypeToErrorPlatform(_device), ErrorType::DIMENSION, "softmax: only the last dim is implemented on the device");
+    if (dim != rank - 1) {
+        // dim 0 of a 2-D tensor: down the columns (src/Tensor.cpp:1728-1743); like the reference's
+        // Tensor::softmax this form is not dispatched through the scheduler
+        if (_device != DeviceType::kCUDA) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DEVICE_COMPAT, "softmax: no kernel for this device");
+        if (_dtype != DType::kFloat) Ctorch_Error::throwException(ErrorPlatform::kCUDA, ErrorType::DATATYPE, "softmax: float tensors only");
+        if (!is_contiguous()) Ctorch_Error::throwException(ErrorPlatform::kCUDA, ErrorType::TENSOR_STATE, "softmax: contiguous tensor expected");
+        Tensor result(ShapeTag{}, _shape, _dtype, _device, false);
+        cuda_check(ctk_softmax_cols_f32(data<float>(), result.data<float>(), static_cast<int64_t>(_shape[0]), static_cast<int64_t>(_shape[1]), t_stream), "softmax(dim 0)");
+        record(result, op::Softmax, {const_cast<Tensor*>(this)}, _requires_grad, dim);
+        return result;
+    }
     return unary_dispatch(op::Softmax, dim);
 }
 

@@ -1060,6 +1060,62 @@ ctk_status launch_streamed(const RowArgs& A, ReduceScratch* s, float* loss_out, 
     return CTK_OK;
 }
 
+// ---- softmax down the columns of a row-major [rows, cols] matrix (dim 0) -----------------------------
+// Tensor::softmax(0) of the reference (src/Tensor.cpp:1728-1743) and its backward rule
+// (src/AutoDiff.cpp:1473-1484).  A CTA of 32 x 32 threads owns a strip of 32 columns: a warp reads one
+// 128-byte row segment at a time, every thread keeps a running maximum and a rescaled running sum for
+// its column over the rows it visits (one pass), the 32 row-lanes of a column are merged through
+// shared memory, and a second pass writes exp(x - max) / sum.  12 bytes per element instead of the 8 of
+// a kernel that could keep its strip on chip: this form is not on any benchmark path.
+constexpr int kColTile = 32;
+
+__global__ void __launch_bounds__(kColTile * kColTile) softmax_cols_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t rows, int64_t cols) {
+    __shared__ float sm_m[kColTile][kColTile + 1], sm_s[kColTile][kColTile + 1];
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    const int64_t col = static_cast<int64_t>(blockIdx.x) * kColTile + tx;
+    float m = -INFINITY, sum = 0.0f;
+    if (col < cols)
+        for (int64_t r = ty; r < rows; r += kColTile) {
+            const float v = __ldg(x + r * cols + col);
+            const float mn = fmaxf(m, v);
+            if (mn > -INFINITY) {
+                sum = sum * fast_exp(m - mn) + fast_exp(v - mn);
+                m = mn;
+            }
+        }
+    sm_m[ty][tx] = m;
+    sm_s[ty][tx] = sum;
+    __syncthreads();
+    float cm = -INFINITY;
+#pragma unroll 8
+    for (int i = 0; i < kColTile; ++i) cm = fmaxf(cm, sm_m[i][tx]);
+    float cs = 0.0f;
+#pragma unroll 8
+    for (int i = 0; i < kColTile; ++i) cs += sm_m[i][tx] > -INFINITY ? sm_s[i][tx] * fast_exp(sm_m[i][tx] - cm) : 0.0f;
+    const float inv = 1.0f / cs;
+    if (col < cols)
+        for (int64_t r = ty; r < rows; r += kColTile) y[r * cols + col] = fast_exp(__ldg(x + r * cols + col) - cm) * inv;
+}
+
+__global__ void __launch_bounds__(kColTile * kColTile) softmax_cols_backward_kernel(const float* __restrict__ y, const float* __restrict__ g, float* __restrict__ dx, int64_t rows, int64_t cols) {
+    __shared__ float sm_d[kColTile][kColTile + 1];
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    const int64_t col = static_cast<int64_t>(blockIdx.x) * kColTile + tx;
+    float dot = 0.0f;
+    if (col < cols)
+        for (int64_t r = ty; r < rows; r += kColTile) dot += __ldg(g + r * cols + col) * __ldg(y + r * cols + col);
+    sm_d[ty][tx] = dot;
+    __syncthreads();
+    float cd = 0.0f;
+#pragma unroll 8
+    for (int i = 0; i < kColTile; ++i) cd += sm_d[i][tx];
+    if (col < cols)
+        for (int64_t r = ty; r < rows; r += kColTile) {
+            const int64_t i = r * cols + col;
+            dx[i] = __ldg(y + i) * (__ldg(g + i) - cd);
+        }
+}
+
 template <int ALG>
 ctk_status launch_rows(const char* name, const RowArgs& A, float* loss_out, void* scratch, void* stream) {
     CTK_REQUIRE(A.rows >= 0 && A.cols >= 0, "row kernel: negative shape");
@@ -1131,6 +1187,28 @@ ctk_status ctk_softmax_rows_f32(const float* x, float* y, int64_t rows, int64_t 
     CTK_REQUIRE((x && y) || rows == 0 || cols == 0, "ctk_softmax_rows_f32: null pointer");
     RowArgs A{x, nullptr, y, nullptr, nullptr, rows, cols};
     return launch_rows<ALG_SOFTMAX>("softmax_rows", A, nullptr, nullptr, stream);
+}
+
+ctk_status ctk_softmax_cols_f32(const float* x, float* y, int64_t rows, int64_t cols, void* stream) {
+    CTK_REQUIRE(rows >= 0 && cols >= 0, "ctk_softmax_cols_f32: negative shape");
+    if (rows == 0 || cols == 0) return CTK_OK;
+    CTK_REQUIRE(x && y, "ctk_softmax_cols_f32: null pointer");
+    const int64_t grid = (cols + kColTile - 1) / kColTile;
+    CTK_REQUIRE(grid <= 0x7fffffff, "ctk_softmax_cols_f32: too many columns");
+    softmax_cols_kernel<<<static_cast<unsigned>(grid), dim3(kColTile, kColTile), 0, as_stream(stream)>>>(x, y, rows, cols);
+    CTK_LAUNCH_CHECK("softmax_cols_kernel");
+    return CTK_OK;
+}
+
+ctk_status ctk_softmax_backward_cols_f32(const float* y, const float* g, float* dx, int64_t rows, int64_t cols, void* stream) {
+    CTK_REQUIRE(rows >= 0 && cols >= 0, "ctk_softmax_backward_cols_f32: negative shape");
+    if (rows == 0 || cols == 0) return CTK_OK;
+    CTK_REQUIRE(y && g && dx, "ctk_softmax_backward_cols_f32: null pointer");
+    const int64_t grid = (cols + kColTile - 1) / kColTile;
+    CTK_REQUIRE(grid <= 0x7fffffff, "ctk_softmax_backward_cols_f32: too many columns");
+    softmax_cols_backward_kernel<<<static_cast<unsigned>(grid), dim3(kColTile, kColTile), 0, as_stream(stream)>>>(y, g, dx, rows, cols);
+    CTK_LAUNCH_CHECK("softmax_cols_backward_kernel");
+    return CTK_OK;
 }
 
 ctk_status ctk_softmax_backward_rows_f32(const float* y, const float* g, float* dx, int64_t rows, int64_t cols, void* stream) {

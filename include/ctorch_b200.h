@@ -207,6 +207,11 @@ ctk_status ctk_rowwise_status(int* status);
  * (src/kernels/CPU-BASIC/Softmax_BASIC_kernel.cpp:16-101) == Tensor::softmax row path
  * (src/Tensor.cpp:1712-1727). */
 ctk_status ctk_softmax_rows_f32(const float* x, float* y, int64_t rows, int64_t cols, void* stream);
+/* Softmax down the columns (dim 0) of a row-major [rows, cols] matrix: Tensor::softmax(0)
+ * (src/Tensor.cpp:1728-1743), and its backward dx = y * (g - sum_i g_i y_i) per column
+ * (src/AutoDiff.cpp:1473-1484). */
+ctk_status ctk_softmax_cols_f32(const float* x, float* y, int64_t rows, int64_t cols, void* stream);
+ctk_status ctk_softmax_backward_cols_f32(const float* y, const float* g, float* dx, int64_t rows, int64_t cols, void* stream);
 /* dx = y * (g - sum_j g_j y_j) per row, from the saved OUTPUT y (src/AutoDiff.cpp:1417-1490). */
 ctk_status ctk_softmax_backward_rows_f32(const float* y, const float* g, float* dx, int64_t rows, int64_t cols, void* stream);
 /* Softmax + cross entropy SUMMED over rows, clamp max(p, 1e-10): CrossEntropy_BASIC_kernel

@@ -203,6 +203,20 @@ class Oracle:
         self.L.orc_softmax_rows(_fp(x2), _fp(out), ctypes.c_int64(x2.shape[0]), ctypes.c_int64(x2.shape[1]))
         return out.reshape(x.shape)
 
+    def softmax_dim0(self, x, g=None):
+        """Softmax down the columns of a 2-D array (src/Tensor.cpp:1728-1743): the same recurrence per
+        column as the row form per row, so it is the row form of the transpose; with g also the backward
+        rule of src/AutoDiff.cpp:1473-1484 (dot accumulated down the column in order)."""
+        x = _f32(x)
+        y = np.ascontiguousarray(self.softmax(np.ascontiguousarray(x.T)).T)
+        if g is None:
+            return y
+        g = _f32(g)
+        dot = np.zeros(x.shape[1], np.float32)
+        for i in range(x.shape[0]):
+            dot = (dot + g[i] * y[i]).astype(np.float32)
+        return y, (y * (g - dot)).astype(np.float32)
+
     def ce(self, logits, target):
         """target: one-hot of logits' shape, or a [rows] vector of class indices stored as floats."""
         logits, target = _f32(logits), _f32(target)
@@ -294,6 +308,19 @@ class Reference(Oracle):
 
     def last_error(self):
         return self.L.ref_last_error().decode("utf-8", "replace")
+
+    def softmax_dim(self, x, dim, g=None):
+        """Tensor::softmax(dim) of the reference; with g also the gradient of sum(g * softmax(x, dim))."""
+        x = _f32(x)
+        s = _shape(x)
+        out = np.empty_like(x)
+        if g is None:
+            self._chk(self.L.ref_softmax_dim(_fp(x), s[1], s[2], int(dim), _fp(out), None, None))
+            return out
+        g = _f32(g)
+        dx = np.empty_like(x)
+        self._chk(self.L.ref_softmax_dim(_fp(x), s[1], s[2], int(dim), _fp(out), _fp(g), _fp(dx)))
+        return out, dx
 
     def mnist_load(self, directory, test=False):
         """The reference's own MNISTLoader on `directory`: (images [n, rows*cols], labels [n])."""

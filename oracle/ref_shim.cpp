@@ -338,6 +338,28 @@ int ref_mlp_train(int n_layers, const int64_t* dims, int64_t batch, int steps, i
     });
 }
 
+// Tensor::softmax(dim) (src/Tensor.cpp:1645-1803) and, if g and dx are given, the gradient of
+// sum(g * softmax(x, dim)) through the reference's backward rule (src/AutoDiff.cpp:1417-1490).
+int ref_softmax_dim(const float* x, const int64_t* shape, int rank, int dim, float* out, const float* g, float* dx) {
+    return guarded([&] {
+        AutoDiff ctx;
+        AutoDiffContext::Guard guard(&ctx);
+        Tensor X = make(x, shape, rank);
+        X.requires_grad(g != nullptr);
+        Tensor Y = X.softmax(dim);
+        copy_out(Y, out);
+        if (g && dx) {
+            std::vector<int64_t> ys(Y.sizes().begin(), Y.sizes().end());
+            Tensor G = make(g, ys.data(), static_cast<int>(ys.size()));
+            {
+                AutoDiffContext::Guard off(nullptr);
+                ctx.backward(Y, G);
+            }
+            copy_out(grad(X), dx);
+        }
+    });
+}
+
 // MNISTLoader of the reference (mnist/mnist_loader.{h,cpp}, compiled from where it lies): the
 // training pair (test = 0) or the test pair (test = 1) of directory `dir`.  Sizes always come back;
 // data is copied only when the caller's capacities (in elements) suffice.

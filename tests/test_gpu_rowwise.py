@@ -105,3 +105,22 @@ def test_against_golden_fixture(cb, golden):
     z, t = cb.to_device(G["ka.ce.z"]), cb.to_device(G["ka.ce.t"])
     assert_close(cb.ops.cross_entropy(z, t).numpy(), G["ka.ce"], 1e-5, 1e-6, "CE({2,1,0.1},{1,0,0})")
     assert np.abs(cb.ops.cross_entropy_backward(z, t).numpy() - G["ka.ce.grad"]).max() < 1e-4
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 1), (2, 3), (37, 19), (1000, 10), (64, 33), (5, 1000), (4099, 70)])
+def test_softmax_down_the_columns(cb, orc, rows, cols):
+    """Tensor::softmax(0) (src/Tensor.cpp:1728-1743) and its backward (src/AutoDiff.cpp:1473-1484),
+    through the kernels and through the front end's tape."""
+    from ctorch_b200 import frontend as F
+    rng = np.random.default_rng(rows * 31 + cols)
+    x = (2 * rng.standard_normal((rows, cols))).astype(np.float32)
+    g = rng.standard_normal((rows, cols)).astype(np.float32)
+    ref_y, ref_dx = orc.softmax_dim0(x, g)
+    with F.AutoDiff():
+        X = F.Tensor.from_numpy(x).requires_grad()
+        Y = X.softmax(0)
+        assert_close(Y.numpy(), ref_y, 1e-5, 1e-9, f"softmax(0) {rows}x{cols}")
+        assert_close(Y.numpy().sum(axis=0), np.ones(cols), 1e-5, 0, "columns sum to 1")
+        F.backward(Y, F.Tensor.from_numpy(g))
+        dx = F.grad(X).numpy()
+    assert np.abs(dx - ref_dx).max() <= 1e-5 * np.abs(g).max() * ref_y.max() * max(1.0, np.sqrt(rows) / 8) + 1e-9, "softmax(0) backward"

@@ -179,3 +179,18 @@ def test_oracle_matches_reference_library_bit_for_bit(orc):
     o, r = orc.mlp_train(dims, x, lab, p, 0.01, 4, (0, 3)), R.mlp_train(dims, x, lab, p, 0.01, 4, (0, 3))
     for k in ("losses", "grads", "params", "logits"):
         assert_exact(o[k], r[k], "mlp " + k)
+
+
+def test_softmax_down_the_columns_matches_reference_library(orc):
+    """Tensor::softmax(0) and its backward rule: the restatement against the reference library."""
+    if not oracle.Reference.available():
+        pytest.skip("reference library not built here")
+    R = oracle.Reference()
+    rng = np.random.default_rng(77)
+    for shape in ((37, 19), (1, 8), (64, 1), (5, 130)):
+        x = (2 * rng.standard_normal(shape)).astype(np.float32)
+        g = rng.standard_normal(shape).astype(np.float32)
+        y, dx = R.softmax_dim(x, 0, g)
+        y2, dx2 = orc.softmax_dim0(x, g)
+        assert np.array_equal(y, y2) and np.array_equal(dx, dx2), shape
+        assert np.array_equal(R.softmax_dim(x, 1), orc.softmax(x))
