@@ -328,7 +328,15 @@ Tensor AutoDiff::rule(Node* node, size_t input_id, Node& input_node, bool& skip)
             return -a * node_grad / (b * b);
         }
         case op::Neg: return -node_grad;
-        case op::ReLU: return fused_unary(CTK_OP_RELU);        // g * (x > 0)            :1320-1371
+        case op::ReLU: {
+            // g * (x > 0) (:1320-1371).  The mask is taken from the node's OUTPUT y = max(0, x): y > 0
+            // exactly when x > 0, and the fused MatMul+bias+ReLU never materialises x.
+            const Tensor& y = *node->tensor;
+            Tensor g = check_and_adjust_grad_shape(node_grad, y.sizes(), y.device());
+            Tensor dx(ShapeTag{}, y.sizes(), y.dtype(), y.device(), false);
+            cuda_check(ctk_unary_backward_f32(CTK_OP_RELU, y.data<float>(), g.data<float>(), dx.data<float>(), static_cast<int64_t>(y.numel()), st), "ReLU backward");
+            return dx;
+        }
         case op::Sigmoid: return fused_unary(CTK_OP_SIGMOID);  // (s * (1 - s)) * g      :1372-1383
         case op::Tanh: return fused_unary(CTK_OP_TANH);        // (1 - t*t) * g          :1384-1398
         case op::Sin: return fused_unary(CTK_OP_SIN);          // cos(x) * g             :1399-1407

@@ -3,6 +3,8 @@
 // the tape, commit when the result requires grad.  The operations the reference computes with
 // host loops outside the scheduler (scalar forms :751-973, sum :638-666, softmax :1645-1803,
 // zero/ones :390-455, broadcast_to :289-387, item :154-165) launch device kernels here.
+#include <cstdlib>
+
 #include "Tensor.h"
 
 #include <algorithm>
@@ -466,6 +468,67 @@ Tensor Tensor::matmul(const Tensor& other) const {
     record(result, op::MatMul, {const_cast<Tensor*>(this), const_cast<Tensor*>(&other)}, _requires_grad || other.requires_grad());
     return result;
 }
+Tensor Tensor::shape_only(const std::vector<size_t>& shape, DType dtype, DeviceType device) {
+    Tensor t;
+    t._shape = shape;
+    t._dtype = dtype;
+    t._device = device;
+    t.computeStrides();
+    return t;
+}
+
+Tensor Tensor::linear(const Tensor& W, const Tensor& bias, bool relu) const {
+    static const bool fuse = [] {
+        const char* e = std::getenv("CTORCH_FUSE_LINEAR");
+        return !(e && e[0] == '0');
+    }();
+    const bool fusable = fuse && _device == DeviceType::kCUDA && W.device() == DeviceType::kCUDA && bias.device() == DeviceType::kCUDA &&
+                         _dtype == DType::kFloat && W.dtype() == DType::kFloat && bias.dtype() == DType::kFloat && _shape.size() == 2 &&
+                         W.shape().size() == 2 && _shape[1] == W.shape()[0] && bias.shape().size() == 1 && bias.shape()[0] == W.shape()[1] &&
+                         bias.is_contiguous() && ctk_get_matmul_mode() == CTK_MATMUL_3XTF32 && _shape[0] >= 2 && _shape[1] >= 2 && W.shape()[1] >= 2 &&
+                         W.shape()[1] % 4 == 0;
+    const int64_t m = fusable ? static_cast<int64_t>(_shape[0]) : 0, k = fusable ? static_cast<int64_t>(_shape[1]) : 0,
+                  n = fusable ? static_cast<int64_t>(W.shape()[1]) : 0;
+    const int64_t sa0 = fusable ? static_cast<int64_t>(_strides[0]) : 0, sa1 = fusable ? static_cast<int64_t>(_strides[1]) : 0;
+    const int64_t sb0 = fusable ? static_cast<int64_t>(W.strides()[0]) : 0, sb1 = fusable ? static_cast<int64_t>(W.strides()[1]) : 0;
+    if (!fusable || ctk_matmul_path(data<float>(), W.data<float>(), m, n, k, sa0, sa1, sb0, sb1, CTK_MATMUL_3XTF32) != 0) {
+        // (a returned temporary or moved local keeps its id, which is its key on the tape; a copy would not)
+        if (relu) return (matmul(W) + bias).relu();
+        return matmul(W) + bias;
+    }
+    auto kept = [&](const Tensor& t, int64_t mn, int64_t s_mn, int64_t s_k) -> KeptSplit* {
+        int64_t outer, inner, pitch;
+        if (s_k == 1 && s_mn >= k) { outer = mn; inner = k; pitch = s_mn; }
+        else if (s_mn == 1 && s_k >= mn) { outer = k; inner = mn; pitch = s_k; }
+        else return nullptr;
+        return t.storage().kept_split(static_cast<int64_t>(t.storage_offset()), outer, inner, pitch, ctk_matmul_split_bytes(mn, k));
+    };
+    KeptSplit* ka = kept(*this, m, sa0, sa1);
+    KeptSplit* kb = (W.storage().raw() == _storage.raw()) ? nullptr : kept(W, n, sb1, sb0);
+    Tensor y(ShapeTag{}, {static_cast<size_t>(m), static_cast<size_t>(n)}, _dtype, DeviceType::kCUDA, false);
+    // y enters the next product as its K-major A operand and, transposed, the weight-gradient product:
+    // its split is written by this kernel's epilogue
+    KeptSplit* ky = y.storage().kept_split(0, m, n, n, ctk_matmul_split_bytes(m, n));
+    cuda_check(ctk_matmul_3xtf32_fused_f32(data<float>(), W.data<float>(), y.data<float>(), m, n, k, sa0, sa1, sb0, sb1, ka ? ka->buf : nullptr,
+                                           ka ? &ka->valid : nullptr, kb ? kb->buf : nullptr, kb ? &kb->valid : nullptr, bias.data<float>(),
+                                           relu ? 1 : 0, ky ? ky->buf : nullptr, nullptr, t_stream),
+               "fused MatMul + bias" );
+    if (ky) ky->valid = 1;
+    // the tape sees the three operations
+    const bool rg = _requires_grad || W.requires_grad() || bias.requires_grad();
+    const std::vector<size_t> out_shape = {static_cast<size_t>(m), static_cast<size_t>(n)};
+    Tensor mm = shape_only(out_shape, _dtype, DeviceType::kCUDA);
+    record(mm, op::MatMul, {const_cast<Tensor*>(this), const_cast<Tensor*>(&W)}, _requires_grad || W.requires_grad());
+    if (!relu) {
+        record(y, op::Add, {&mm, const_cast<Tensor*>(&bias)}, rg);
+        return y;
+    }
+    Tensor z = shape_only(out_shape, _dtype, DeviceType::kCUDA);
+    record(z, op::Add, {&mm, const_cast<Tensor*>(&bias)}, rg);
+    record(y, op::ReLU, {&z}, rg);
+    return y;
+}
+
 Tensor Tensor::dot(const Tensor& other) const {
     Tensor result = Ctorch_Scheduler::getInstance().dispatch(*this, other, op::Dot);
     record(result, op::Dot, {const_cast<Tensor*>(this)}, _requires_grad);

@@ -40,6 +40,7 @@ class Tensor {
     Tensor binary_dispatch(const Tensor& other, op o) const;
     Tensor unary_dispatch(op o, int op_param = 0) const;
     Tensor scalar_form(int kind, float s, op recorded) const;
+    static Tensor shape_only(const std::vector<size_t>& shape, DType dtype, DeviceType device);  // no storage
     void record(Tensor& result, op o, std::vector<Tensor*> inputs, bool rg, int op_param = 0) const;
 
 public:
@@ -110,6 +111,12 @@ public:
 
     // ---- math (dispatched + recorded) ----
     Tensor matmul(const Tensor& other) const;
+    // (this.matmul(W) + bias)[.relu()] as ONE kernel where the device path allows it (2-D float device
+    // tensors, 3xTF32 mode, bias of W's column count), recorded on the tape as the same MatMul, Add
+    // and ReLU nodes the three calls would record -- the two intermediate results exist there as
+    // shapes only, no rule reads their values -- and equal to them bit for bit.  Anything else runs
+    // the three calls.  No counterpart in the reference.
+    Tensor linear(const Tensor& W, const Tensor& bias, bool relu) const;
     Tensor dot(const Tensor& other) const;
     Tensor relu() const;
     Tensor sigmoid() const;

@@ -131,10 +131,9 @@ public:
     Tensor forward(const Tensor& x) {
         Tensor h = x;
         const size_t L = W.size();
-        for (size_t l = 0; l < L; ++l) {
-            if (l + 1 < L) h = (h.matmul(W[l]) + b[l]).relu();
-            else h = h.matmul(W[l]) + b[l];
-        }
+        // (h.matmul(W) + b).relu() of the reference step; linear() runs the three as one kernel where it
+        // can and records the same three tape nodes
+        for (size_t l = 0; l < L; ++l) h = h.linear(W[l], b[l], l + 1 < L);
         return h;
     }
 
@@ -624,6 +623,9 @@ int cth_backward(void* root, void* grad_or_null) {
 }
 int cth_grad(void* t, void** out) {
     return guarded([&] { *out = new Tensor(grad(*T(t))); });
+}
+int cth_linear(void* x, void* w, void* bias, int relu, void** out) {
+    return guarded([&] { *out = new Tensor(T(x)->linear(*T(w), *T(bias), relu != 0)); });
 }
 int cth_sgd_update(void* p, void* g, float lr) {
     return guarded([&] { T(p)->sgd_update_(*T(g), lr); });

@@ -189,6 +189,13 @@ struct Params {
     float* c;
     int vec_store;    // n % 4 == 0 and c 16-byte aligned
     int whole_tiles;  // tiles [0, whole_tiles) are computed whole; each later tile as two K-halves
+    // Epilogue of the fused forms (all optional; whole tiles only): c = [relu](acc + bias[col]), and the
+    // hi/lo split of c written next to it ([m, split_pitch] each) for the products c enters next.
+    const float* bias;
+    int relu;
+    float* out_hi;
+    float* out_lo;
+    int64_t split_pitch;
 };
 
 // A unit of work: a whole output tile, or one K-half of a tile of the last, partly filled wave.
@@ -318,6 +325,88 @@ __host__ __device__ constexpr uint32_t make_idesc(int n, bool a_mn_major, bool b
            (static_cast<uint32_t>(BM >> 4) << 24);
 }
 
+// One 32-column chunk of one accumulator row (this lane's) on its way to memory.
+constexpr int STAGE_PITCH = 36;  // floats per staged row: 16-byte aligned, conflict-free for 128-bit accesses
+using EpilogueStage = float[32][STAGE_PITCH];
+
+// One 32 x 32 chunk of an accumulator leaves the CTA.  Each lane holds 32 columns of ITS row (the
+// shape tcgen05.ld.32x32b delivers), so a direct store writes 16 bytes to each of 32 different lines
+// per instruction.  Whole chunks therefore go through `stage` (one per epilogue warp): the lane
+// writes its row there, and the warp reads it back with 8 lanes across a row, so that every store
+// instruction writes 4 complete 128-byte lines.  `row_base` is the chunk's first row, `lane` the
+// caller's lane (= its row within the chunk).
+__device__ __forceinline__ void emit_chunk(const Params& P, bool half, int64_t row_base, int lane, int64_t col0, uint32_t (&r)[32],
+                                           EpilogueStage& stage) {
+    if (col0 >= P.n) return;  // same for the whole warp
+    const int64_t row = row_base + lane;
+    const bool full = P.vec_store && col0 + 32 <= P.n;
+    if (!half && full) {
+        if (P.bias != nullptr || P.relu) {
+#pragma unroll
+            for (int v = 0; v < 32; ++v) {
+                float x = __uint_as_float(r[v]);
+                if (P.bias != nullptr) x += __ldg(P.bias + col0 + v);  // Add_BASIC_kernel's [N,H] + [H]
+                if (P.relu) x = x > 0.0f ? x : 0.0f;                    // ReLU_BASIC_kernel (NaN -> 0)
+                r[v] = __float_as_uint(x);
+            }
+        }
+#pragma unroll
+        for (int v = 0; v < 8; ++v)
+            *reinterpret_cast<float4*>(&stage[lane][4 * v]) =
+                make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+        __syncwarp();
+        const int sub = lane >> 3, c4 = (lane & 7) * 4;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int rr = i * 4 + sub;
+            const int64_t grow = row_base + rr;
+            if (grow < P.m) {
+                const float4 x = *reinterpret_cast<const float4*>(&stage[rr][c4]);
+                __stcs(reinterpret_cast<float4*>(P.c + grow * P.n + col0 + c4), x);
+                if (P.out_hi != nullptr) {
+                    float4 h, l;
+                    h.x = to_tf32_rna(x.x); h.y = to_tf32_rna(x.y); h.z = to_tf32_rna(x.z); h.w = to_tf32_rna(x.w);
+                    l.x = to_tf32_rna(x.x - h.x); l.y = to_tf32_rna(x.y - h.y); l.z = to_tf32_rna(x.z - h.z); l.w = to_tf32_rna(x.w - h.w);
+                    __stcs(reinterpret_cast<float4*>(P.out_hi + grow * P.split_pitch + col0 + c4), h);
+                    __stcs(reinterpret_cast<float4*>(P.out_lo + grow * P.split_pitch + col0 + c4), l);
+                }
+            }
+        }
+        __syncwarp();  // the stage is free again
+        return;
+    }
+    if (row >= P.m) return;
+    float* crow = P.c + row * P.n;
+    if (half) {
+        // one K-half of the tile: add into the zeroed C
+        if (full) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+                atomicAdd(reinterpret_cast<float4*>(crow + col0) + v,
+                          make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3])));
+        } else {
+#pragma unroll
+            for (int v = 0; v < 32; ++v)
+                if (col0 + v < P.n) atomicAdd(crow + col0 + v, __uint_as_float(r[v]));
+        }
+        return;
+    }
+    // a ragged chunk (or an unaligned C): element by element
+#pragma unroll
+    for (int v = 0; v < 32; ++v)
+        if (col0 + v < P.n) {
+            float x = __uint_as_float(r[v]);
+            if (P.bias != nullptr) x += __ldg(P.bias + col0 + v);
+            if (P.relu) x = x > 0.0f ? x : 0.0f;
+            crow[col0 + v] = x;
+            if (P.out_hi != nullptr) {
+                const float h = to_tf32_rna(x);
+                P.out_hi[row * P.split_pitch + col0 + v] = h;
+                P.out_lo[row * P.split_pitch + col0 + v] = to_tf32_rna(x - h);
+            }
+        }
+}
+
 // ---- the kernel ----------------------------------------------------------------------------------
 // A_MN / B_MN: operand is MN-major (its M/N index is the contiguous one).  Tensor maps describe the
 // operand as a 2-D array {contiguous dim, other dim}; box = {32, rows} for a K-major operand and
@@ -331,6 +420,7 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bars[2 * 8 + 4];  // full[8], empty[8], tmem_full[2], tmem_empty[2]
     __shared__ uint32_t tmem_base_slot;
+    __shared__ __align__(16) EpilogueStage stages[4];  // one per epilogue warp
     __shared__ volatile int abort_flag;
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -466,8 +556,7 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
             const int64_t m0 = static_cast<int64_t>(U.tile / P.tiles_n) * BM, n0 = static_cast<int64_t>(U.tile % P.tiles_n) * BN;
             if (!mbar_wait(tfull_bar(acc), acc_phase, &abort_flag, 0x300 | (16 + acc))) { ok = false; break; }
             tc_fence_after();
-            const int64_t row = m0 + quarter * 32 + lane;
-            float* crow = P.c + row * P.n;
+            const int64_t row_base = m0 + quarter * 32;
 #pragma unroll 1
             for (int cc = 0; cc < BN / 32; ++cc) {
                 uint32_t r[32];
@@ -475,32 +564,7 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
                 tmem_ld32(taddr, r);
                 tmem_ld_wait();
                 const int64_t col0 = n0 + cc * 32;
-                if (row < P.m && col0 < P.n) {
-                    if (U.half) {
-                        // one K-half of the tile: add into the zeroed C
-                        if (P.vec_store && col0 + 32 <= P.n) {
-#pragma unroll
-                            for (int v = 0; v < 8; ++v)
-                                atomicAdd(reinterpret_cast<float4*>(crow + col0) + v,
-                                          make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
-                                                      __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3])));
-                        } else {
-#pragma unroll
-                            for (int v = 0; v < 32; ++v)
-                                if (col0 + v < P.n) atomicAdd(crow + col0 + v, __uint_as_float(r[v]));
-                        }
-                    } else if (P.vec_store && col0 + 32 <= P.n) {
-#pragma unroll
-                        for (int v = 0; v < 8; ++v)
-                            __stcs(reinterpret_cast<float4*>(crow + col0) + v,
-                                   make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
-                                               __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3])));
-                    } else {
-#pragma unroll
-                        for (int v = 0; v < 32; ++v)
-                            if (col0 + v < P.n) crow[col0 + v] = __uint_as_float(r[v]);
-                    }
-                }
+                emit_chunk(P, U.half, row_base, lane, col0, r, stages[warp - 2]);
             }
             tc_fence_before();
             __syncwarp();
@@ -617,6 +681,7 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bars[2 * 8 + 4];  // full[8], empty[8], tmem_full[2], tmem_empty[2]
     __shared__ uint32_t tmem_base_slot;
+    __shared__ __align__(16) EpilogueStage stages[4];  // one per epilogue warp
     __shared__ volatile int abort_flag;
 
     const uint32_t rank = cluster_ctarank();      // 0 = issues the MMAs
@@ -765,8 +830,7 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
             const int64_t n0 = static_cast<int64_t>(U.tile % P.tiles_n) * BN;
             if (!mbar_wait(tfull_bar(acc), acc_phase, &abort_flag, 0x700 | (16 + acc))) { ok = false; break; }
             tc_fence_after();
-            const int64_t row = m0 + quarter * 32 + lane;
-            float* crow = P.c + row * P.n;
+            const int64_t row_base = m0 + quarter * 32;
 #pragma unroll 1
             for (int cc = 0; cc < BN / 32; ++cc) {
                 uint32_t r[32];
@@ -774,32 +838,7 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
                 tmem_ld32(taddr, r);
                 tmem_ld_wait();
                 const int64_t col0 = n0 + cc * 32;
-                if (row < P.m && col0 < P.n) {
-                    if (U.half) {
-                        // one K-half of the tile: add into the zeroed C
-                        if (P.vec_store && col0 + 32 <= P.n) {
-#pragma unroll
-                            for (int v = 0; v < 8; ++v)
-                                atomicAdd(reinterpret_cast<float4*>(crow + col0) + v,
-                                          make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
-                                                      __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3])));
-                        } else {
-#pragma unroll
-                            for (int v = 0; v < 32; ++v)
-                                if (col0 + v < P.n) atomicAdd(crow + col0 + v, __uint_as_float(r[v]));
-                        }
-                    } else if (P.vec_store && col0 + 32 <= P.n) {
-#pragma unroll
-                        for (int v = 0; v < 8; ++v)
-                            __stcs(reinterpret_cast<float4*>(crow + col0) + v,
-                                   make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
-                                               __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3])));
-                    } else {
-#pragma unroll
-                        for (int v = 0; v < 32; ++v)
-                            if (col0 + v < P.n) crow[col0 + v] = __uint_as_float(r[v]);
-                    }
-                }
+                emit_chunk(P, U.half, row_base, lane, col0, r, stages[warp - 2]);
             }
             tc_fence_before();
             __syncwarp();
@@ -1210,8 +1249,17 @@ struct KeptSplit {
     int* valid;
 };
 
+// What a fused call adds to the product: c = [relu](a.b + bias) and, optionally, c's own hi/lo split
+// (layout of a K-major [m, n] operand) for the products c enters next.
+struct FusedEpilogue {
+    const float* bias = nullptr;
+    int relu = 0;
+    void* c_split = nullptr;
+};
+
 static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k, int64_t sa0,
-                              int64_t sa1, int64_t sb0, int64_t sb1, int mode, void* workspace, KeptSplit ka, KeptSplit kb, void* stream) {
+                              int64_t sa1, int64_t sb0, int64_t sb1, int mode, void* workspace, KeptSplit ka, KeptSplit kb, void* stream,
+                              FusedEpilogue fe = FusedEpilogue()) {
     CTK_REQUIRE(m >= 0 && n >= 0 && k >= 0, "ctk_matmul_f32: negative extent");
     if (m == 0 || n == 0) return CTK_OK;
     CTK_REQUIRE(c, "ctk_matmul_f32: null output");
@@ -1226,7 +1274,9 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
     CTK_REQUIRE(m < (int64_t(1) << 31) && n < (int64_t(1) << 31) && k < (int64_t(1) << 31), "ctk_matmul_f32: extent >= 2^31");
 
     tc::Operand A, B;
+    const bool fused = fe.bias != nullptr || fe.relu || fe.c_split != nullptr;
     if (choose_path(a, b, m, n, k, sa0, sa1, sb0, sb1, md, &A, &B) == 1) {
+        if (fused) return fail(CTK_ERR_INVALID, "fused MatMul: the operands need the tensor-core path (a unit stride each)");
         dim3 grid(static_cast<unsigned>((n + SM_TILE - 1) / SM_TILE), static_cast<unsigned>((m + SM_TILE - 1) / SM_TILE));
         CTK_REQUIRE(grid.y <= 65535u, "ctk_matmul_f32: m too large for the CUDA-core path");
         simt_matmul_kernel<<<grid, SM_THREADS, 0, st>>>(a, b, c, m, n, k, sa0, sa1, sb0, sb1);
@@ -1299,6 +1349,15 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
     P.num_kb = static_cast<int>((k + tc::BK - 1) / tc::BK);
     P.c = c;
     P.vec_store = (n % 4 == 0) && ((reinterpret_cast<uintptr_t>(c) & 15u) == 0);
+    P.bias = fe.bias;
+    P.relu = fe.relu;
+    P.out_hi = P.out_lo = nullptr;
+    P.split_pitch = (n + 3) / 4 * 4;
+    if (fe.c_split) {
+        float* h = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(fe.c_split) + 255u) & ~static_cast<uintptr_t>(255u));
+        P.out_hi = h;
+        P.out_lo = h + m * P.split_pitch;
+    }
     CTK_REQUIRE(static_cast<int64_t>(P.tiles_m) * P.tiles_n < (int64_t(1) << 30), "ctk_matmul_f32: too many tiles");
     // The last wave: when at most half of the SMs (or CTA pairs) would have a tile, its tiles are
     // computed as two K-halves each, added into zeroed C, so that twice as many work on it.
@@ -1308,7 +1367,7 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
         if (paired && (rc = tc::resident_pairs(&workers))) return rc;
         P.whole_tiles = tiles;
         const int tail = tiles % workers;
-        if (g_split_tail && P.num_kb >= 16 && tail > 0 && 2 * tail <= workers) {
+        if (g_split_tail && !fused && P.num_kb >= 16 && tail > 0 && 2 * tail <= workers) {  // (a fused epilogue needs the whole sum)
             P.whole_tiles = tiles - tail;
             const int parts = 4;
             tc::zero_tiles_kernel<<<tail * parts, 256, 0, st>>>(c, m, n, tile_m, bn, P.tiles_n, P.whole_tiles, parts);
@@ -1352,6 +1411,24 @@ ctk_status ctk_matmul_3xtf32_kept_f32(const float* a, const float* b, float* c, 
                                       int* b_valid, void* workspace, void* stream) {
     CTK_REQUIRE((!a_split || a_valid) && (!b_split || b_valid), "ctk_matmul_3xtf32_kept_f32: a split buffer needs its valid flag");
     return matmul_impl(a, b, c, m, n, k, sa0, sa1, sb0, sb1, CTK_MATMUL_3XTF32, workspace, KeptSplit{a_split, a_valid}, KeptSplit{b_split, b_valid}, stream);
+}
+
+// c = [relu](a.b + bias[col]) in one launch, with c's own hi/lo split written by the same epilogue.
+// The bias add and the ReLU are the single fp32 operations of Add_BASIC_kernel's [N,H] + [H] form and
+// of ReLU_BASIC_kernel applied to the rounded accumulator, so the result equals MatMul, Add, ReLU run
+// one after the other bit for bit; what is saved is their two passes over c and the read of the later
+// split.  bias: n floats or NULL; c_split: ctk_matmul_split_bytes(m, n) bytes or NULL (valid for c
+// viewed as [m, n] with pitch n afterwards).  Needs the tensor-core path for both operands.
+ctk_status ctk_matmul_3xtf32_fused_f32(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k, int64_t sa0,
+                                       int64_t sa1, int64_t sb0, int64_t sb1, void* a_split, int* a_valid, void* b_split,
+                                       int* b_valid, const float* bias, int relu, void* c_split, void* workspace, void* stream) {
+    CTK_REQUIRE((!a_split || a_valid) && (!b_split || b_valid), "ctk_matmul_3xtf32_fused_f32: a split buffer needs its valid flag");
+    CTK_REQUIRE(m > 0 && n > 0 && k > 0, "ctk_matmul_3xtf32_fused_f32: empty product");
+    FusedEpilogue fe;
+    fe.bias = bias;
+    fe.relu = relu ? 1 : 0;
+    fe.c_split = c_split;
+    return matmul_impl(a, b, c, m, n, k, sa0, sa1, sb0, sb1, CTK_MATMUL_3XTF32, workspace, KeptSplit{a_split, a_valid}, KeptSplit{b_split, b_valid}, stream, fe);
 }
 
 // 3xTF32 MatMul that allocates nothing: same arguments and same result as ctk_matmul_f32 in mode

@@ -128,6 +128,13 @@ class Tensor:
     def sin(self): return self._un("Sin")
     def cos(self): return self._un("Cos")
     def softmax(self, dim=-1): return self._un("Softmax", dim)
+
+    def linear(self, w, bias, relu=False):
+        """(self.matmul(w) + bias)[.relu()] in one kernel where possible."""
+        h = _vp()
+        _chk(lib.cth_linear(self.h, w.h, bias.h, 1 if relu else 0, ctypes.byref(h)))
+        return Tensor(h)
+
     def sum(self): return self._un("Sum")
     def __neg__(self): return self._un("Neg")
     def matmul(self, o): return self._bin(o, "MatMul")

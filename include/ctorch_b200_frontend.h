@@ -59,6 +59,9 @@ int cth_ctx_release_step_nodes(void* ctx);            /* drop nodes no future ro
 int cth_ctx_node_count(void* ctx, uint64_t* n);
 int cth_backward(void* root, void* grad_output_or_null); /* free backward(root[, grad]), src/Tensor.cpp:1373-1384 */
 int cth_grad(void* tensor, void** out);                /* free grad(t), src/Tensor.cpp:1387-1392 */
+/* (x.matmul(w) + bias)[.relu()] as one kernel where possible, recorded as the same MatMul, Add and
+ * ReLU nodes and equal to the three calls bit for bit (Tensor::linear). */
+int cth_linear(void* x, void* w, void* bias, int relu, void** out);
 int cth_sgd_update(void* param, void* grad, float lr); /* p -= g*lr on the device (mnist/mnist.cpp:80-92) */
 
 /* ---- the MLP training step of mnist/mnist.cpp:44-92 for any layer list ----

@@ -442,3 +442,78 @@ def test_graph_epoch_equals_eager_epoch(F, cb, golden, tmp_path):
         assert a.train_epoch(im, lb, 32) == b.train_epoch_graph(im, lb, 32)
     assert_exact(a.params(), b.params(), "weights after three epochs")
     assert a.accuracy(im, lb) == b.accuracy(im, lb)
+
+
+@pytest.mark.parametrize("relu", [True, False])
+@pytest.mark.parametrize("m,k,n", [(256, 96, 320), (130, 64, 132), (384, 520, 600), (8192, 784, 128), (64, 40, 10)])
+def test_fused_linear_equals_the_three_calls(F, cb, orc, m, k, n, relu):
+    """Tensor::linear: MatMul + bias [+ ReLU] in the product's epilogue (with the result's hi/lo split)
+    against x.matmul(w) + b [.relu()]: values, every gradient, and a following product that uses the
+    split the epilogue wrote -- all bit for bit (with every tile computed whole: a fused epilogue needs
+    the whole sum, so the unfused twin must not cut its last wave's K in two either).  n = 10 is not
+    fusable (not a multiple of 4) and takes the three calls."""
+    rng = np.random.default_rng(m + k + n)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    w = (rng.standard_normal((k, n)) / np.sqrt(k)).astype(np.float32)
+    b = rng.standard_normal(n).astype(np.float32)
+    w2 = rng.standard_normal((n, 8)).astype(np.float32)
+    out = {}
+    for fused in (False, True):
+        cb.ops.set_matmul_tail_split(0)
+        with F.AutoDiff():
+            X, W, B, W2 = (dev(F, a).requires_grad() for a in (x, w, b, w2))
+            if fused:
+                Y = X.linear(W, B, relu)
+            else:
+                Y = X.matmul(W) + B
+                Y = Y.relu() if relu else Y
+            Z = Y.matmul(W2)            # a product whose A operand split came from the epilogue
+            F.backward(Z.sum())
+            out[fused] = [Y.numpy(), Z.numpy(), F.grad(X).numpy(), F.grad(W).numpy(), F.grad(B).numpy(), F.grad(W2).numpy()]
+        cb.ops.set_matmul_tail_split(1)
+    for a, c, name in zip(out[False], out[True], ("y", "z", "dx", "dw", "db", "dw2")):
+        assert_exact(c, a, f"{name}: fused == three calls")
+    ref = orc.matmul(x, w) + b
+    ref = np.maximum(ref, 0) if relu else ref
+    assert_matmul_close(out[True][0], ref, 1e-4, "fused linear vs oracle")
+
+
+def test_trainer_with_and_without_fused_linear_is_bit_identical(F, cb):
+    """The trainer's forward uses linear(); CTORCH_FUSE_LINEAR=0 (read once per process) cannot be
+    toggled here, so the unfused twin is the op-by-op front end driven from this test."""
+    dims = [784, 128, 64, 12]
+    rng = np.random.default_rng(5)
+    parts = []
+    Ws, bs = [], []
+    for i, j in zip(dims[:-1], dims[1:]):
+        lim = np.sqrt(6.0 / i)
+        Ws.append(rng.uniform(-lim, lim, (i, j)).astype(np.float32))
+        bs.append(rng.uniform(-0.1, 0.1, j).astype(np.float32))
+        parts += [Ws[-1].ravel(), bs[-1]]
+    p = np.concatenate(parts)
+    x = rng.integers(0, 256, (256, 784)).astype(np.float32) / np.float32(255.0)
+    lab = rng.integers(0, 12, 256).astype(np.float32)
+    oh = np.zeros((256, 12), np.float32)
+    oh[np.arange(256), lab.astype(int)] = 1
+    cb.ops.set_matmul_tail_split(0)   # the fused product computes whole tiles: so must its twin
+    try:
+        tr = F.MlpTrainer(dims, p, 0.001)
+        loss = tr.step_host(x, lab)
+        with F.AutoDiff() as ctx:
+            W = [dev(F, a) for a in Ws]
+            B = [dev(F, a) for a in bs]
+            for t in W + B:
+                ctx.make_leaf(t, True)
+                t.requires_grad(True)
+            h = dev(F, x)
+            for l in range(3):
+                h = h.matmul(W[l]) + B[l]
+                if l < 2:
+                    h = h.relu()
+            L = h.cross_entropy(dev(F, oh))
+            F.backward(L)
+            grads = np.concatenate([np.concatenate([F.grad(W[l]).numpy().ravel(), F.grad(B[l]).numpy().ravel()]) for l in range(3)])
+            assert float(L.numpy()) == loss
+    finally:
+        cb.ops.set_matmul_tail_split(1)
+    assert_exact(tr.grads(), grads, "gradients: trainer (fused forward) == op-by-op front end")
