@@ -42,6 +42,8 @@ def load():
     L.ctk_reduce_scratch_bytes.restype = ctypes.c_size_t
     L.ctk_matmul_workspace_bytes.restype = ctypes.c_size_t
     L.ctk_matmul_workspace_bytes.argtypes = [ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int]
+    L.ctk_matmul_split_bytes.restype = ctypes.c_size_t
+    L.ctk_matmul_split_bytes.argtypes = [ctypes.c_int64, ctypes.c_int64]
     L.cth_last_error.restype = ctypes.c_char_p
     L.cth_error_count.restype = ctypes.c_uint64
     _lib = L

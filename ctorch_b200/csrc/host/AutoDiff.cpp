@@ -332,6 +332,7 @@ Tensor AutoDiff::rule(Node* node, size_t input_id, Node& input_node, bool& skip)
             // g * (x > 0) (:1320-1371).  The mask is taken from the node's OUTPUT y = max(0, x): y > 0
             // exactly when x > 0, and the fused MatMul+bias+ReLU never materialises x.
             const Tensor& y = *node->tensor;
+            if (node->grad_premasked) return node_grad;  // g * mask was applied where g was made
             Tensor g = check_and_adjust_grad_shape(node_grad, y.sizes(), y.device());
             Tensor dx(ShapeTag{}, y.sizes(), y.dtype(), y.device(), false);
             cuda_check(ctk_unary_backward_f32(CTK_OP_RELU, y.data<float>(), g.data<float>(), dx.data<float>(), static_cast<int64_t>(y.numel()), st), "ReLU backward");
@@ -406,7 +407,18 @@ Tensor AutoDiff::rule(Node* node, size_t input_id, Node& input_node, bool& skip)
             if (node_grad.sizes().size() != 2)
                 Ctorch_Error::throwException(ErrorPlatform::kAutoDiff, ErrorType::DIMENSION, "MatMul gradient must be a 2-D tensor or a scalar");
             // dA = g . B^T ; dB = A^T . g -- the transposes are stride-swapped views, the kernel reads them in place.
-            if (first) return node_grad.matmul(other_tensor.t());
+            if (first) {
+                // the operand is a ReLU's output that only this product reads: its gradient goes through
+                // the ReLU's rule next and nowhere else, so the product applies that rule itself
+                auto cons = consumers.find(input_id);
+                if (fuse_relu_backward && input_node.operation == op::ReLU && !input_node.is_leaf && cons != consumers.end() &&
+                    cons->second == 1 && (!input_node.grad || input_node.grad_is_zero) && node_grad.device() == DeviceType::kCUDA &&
+                    input_node.tensor->device() == DeviceType::kCUDA && input_node.tensor->sizes() == in_shape && input_node.tensor->is_contiguous()) {
+                    input_node.grad_premasked = true;
+                    return node_grad.matmul_masked(other_tensor.t(), *input_node.tensor);
+                }
+                return node_grad.matmul(other_tensor.t());
+            }
             return other_tensor.t().matmul(node_grad);
         }
         default:
@@ -434,6 +446,11 @@ void AutoDiff::backward(Tensor& root, Tensor grad_output) {
     std::vector<Node*> order;
     dfs_topological_sort(root_node, visited, order);
     std::reverse(order.begin(), order.end());
+    consumers.clear();
+    for (Node* node : order) {
+        node->grad_premasked = false;
+        for (size_t input_id : node->input_ids) ++consumers[input_id];
+    }
 
     for (Node* node : order) {
         if (!node->requires_grad || !node->grad) continue;

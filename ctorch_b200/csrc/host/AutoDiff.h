@@ -44,6 +44,9 @@ class AutoDiff {
         // before backward has replaced it (backward adopts its first contribution instead of adding
         // it to zeros: 0 + x is x).
         bool grad_is_zero = false;
+        // the gradient of this ReLU node already went through the node's own backward rule (in the
+        // epilogue of the product that made it): the rule passes it on
+        bool grad_premasked = false;
         void materialize_grad();
         std::vector<size_t> input_ids;
         op operation = op::Add;
@@ -64,6 +67,8 @@ class AutoDiff {
     std::unordered_map<size_t, PendingRecord> pending_records;
     std::mutex records_mutex;
     bool retain_graph = false;
+    bool fuse_relu_backward = false;
+    std::unordered_map<size_t, int> consumers;  // per tensor id, within the backward pass that is running
 
     Node* get_node_by_id(size_t id);
     void dfs_topological_sort(Node* node, std::unordered_set<Node*>& visited, std::vector<Node*>& result);
@@ -94,6 +99,12 @@ public:
     // Leaves that require grad -- the parameters, including the snapshot taken when they were first
     // registered, which backward keeps using -- stay, so results do not change.
     void release_step_nodes();
+    // When a ReLU's output enters exactly one MatMul (as its first operand) and nothing else, let the
+    // product g.W^T that computes the output's gradient apply the ReLU's backward rule in its epilogue.
+    // The gradients of everything upstream are bit for bit the same; what get_grad returns for that
+    // ReLU output itself is then the masked gradient (the reference: the unmasked one), which is why
+    // this is off unless asked for.
+    void set_fuse_relu_backward(bool on) { fuse_relu_backward = on; }
     size_t node_count();
     // In-place access to a leaf's gradient buffer (nullptr if none).
     Tensor* grad_buffer(const Tensor& t);

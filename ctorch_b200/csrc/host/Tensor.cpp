@@ -477,25 +477,26 @@ Tensor Tensor::shape_only(const std::vector<size_t>& shape, DType dtype, DeviceT
     return t;
 }
 
-Tensor Tensor::linear(const Tensor& W, const Tensor& bias, bool relu) const {
+// y = [relu](A.B + bias) * (mask > 0) in one launch of the 3xTF32 product, operand splits kept with
+// their buffers and y's own split written by the epilogue.  False (nothing launched) when the fused
+// form does not apply: another device, dtype or mode, operands the tensor cores cannot take.
+static bool fused_product(const Tensor& A, const Tensor& B, const Tensor* bias, bool relu, const Tensor* mask, Tensor& y) {
     static const bool fuse = [] {
         const char* e = std::getenv("CTORCH_FUSE_LINEAR");
         return !(e && e[0] == '0');
     }();
-    const bool fusable = fuse && _device == DeviceType::kCUDA && W.device() == DeviceType::kCUDA && bias.device() == DeviceType::kCUDA &&
-                         _dtype == DType::kFloat && W.dtype() == DType::kFloat && bias.dtype() == DType::kFloat && _shape.size() == 2 &&
-                         W.shape().size() == 2 && _shape[1] == W.shape()[0] && bias.shape().size() == 1 && bias.shape()[0] == W.shape()[1] &&
-                         bias.is_contiguous() && ctk_get_matmul_mode() == CTK_MATMUL_3XTF32 && _shape[0] >= 2 && _shape[1] >= 2 && W.shape()[1] >= 2 &&
-                         W.shape()[1] % 4 == 0;
-    const int64_t m = fusable ? static_cast<int64_t>(_shape[0]) : 0, k = fusable ? static_cast<int64_t>(_shape[1]) : 0,
-                  n = fusable ? static_cast<int64_t>(W.shape()[1]) : 0;
-    const int64_t sa0 = fusable ? static_cast<int64_t>(_strides[0]) : 0, sa1 = fusable ? static_cast<int64_t>(_strides[1]) : 0;
-    const int64_t sb0 = fusable ? static_cast<int64_t>(W.strides()[0]) : 0, sb1 = fusable ? static_cast<int64_t>(W.strides()[1]) : 0;
-    if (!fusable || ctk_matmul_path(data<float>(), W.data<float>(), m, n, k, sa0, sa1, sb0, sb1, CTK_MATMUL_3XTF32) != 0) {
-        // (a returned temporary or moved local keeps its id, which is its key on the tape; a copy would not)
-        if (relu) return (matmul(W) + bias).relu();
-        return matmul(W) + bias;
-    }
+    auto plain = [](const Tensor& t, size_t rank) {
+        return t.device() == DeviceType::kCUDA && t.dtype() == DType::kFloat && t.shape().size() == rank;
+    };
+    if (!fuse || !plain(A, 2) || !plain(B, 2) || A.shape()[1] != B.shape()[0] || ctk_get_matmul_mode() != CTK_MATMUL_3XTF32) return false;
+    const int64_t m = static_cast<int64_t>(A.shape()[0]), k = static_cast<int64_t>(A.shape()[1]), n = static_cast<int64_t>(B.shape()[1]);
+    if (m < 2 || k < 2 || n < 2 || n % 4 != 0) return false;
+    if (bias && !(plain(*bias, 1) && static_cast<int64_t>(bias->shape()[0]) == n && bias->is_contiguous())) return false;
+    if (mask && !(plain(*mask, 2) && static_cast<int64_t>(mask->shape()[0]) == m && static_cast<int64_t>(mask->shape()[1]) == n && mask->is_contiguous()))
+        return false;
+    const int64_t sa0 = static_cast<int64_t>(A.strides()[0]), sa1 = static_cast<int64_t>(A.strides()[1]);
+    const int64_t sb0 = static_cast<int64_t>(B.strides()[0]), sb1 = static_cast<int64_t>(B.strides()[1]);
+    if (ctk_matmul_path(A.data<float>(), B.data<float>(), m, n, k, sa0, sa1, sb0, sb1, CTK_MATMUL_3XTF32) != 0) return false;
     auto kept = [&](const Tensor& t, int64_t mn, int64_t s_mn, int64_t s_k) -> KeptSplit* {
         int64_t outer, inner, pitch;
         if (s_k == 1 && s_mn >= k) { outer = mn; inner = k; pitch = s_mn; }
@@ -503,17 +504,40 @@ Tensor Tensor::linear(const Tensor& W, const Tensor& bias, bool relu) const {
         else return nullptr;
         return t.storage().kept_split(static_cast<int64_t>(t.storage_offset()), outer, inner, pitch, ctk_matmul_split_bytes(mn, k));
     };
-    KeptSplit* ka = kept(*this, m, sa0, sa1);
-    KeptSplit* kb = (W.storage().raw() == _storage.raw()) ? nullptr : kept(W, n, sb1, sb0);
-    Tensor y(ShapeTag{}, {static_cast<size_t>(m), static_cast<size_t>(n)}, _dtype, DeviceType::kCUDA, false);
-    // y enters the next product as its K-major A operand and, transposed, the weight-gradient product:
+    KeptSplit* ka = kept(A, m, sa0, sa1);
+    KeptSplit* kb = (B.storage().raw() == A.storage().raw()) ? nullptr : kept(B, n, sb1, sb0);
+    y = Tensor(ShapeTag{}, {static_cast<size_t>(m), static_cast<size_t>(n)}, A.dtype(), DeviceType::kCUDA, false);
+    float* yp = y.data<float>();  // (the mutable pointer first: asking for it drops a kept split)
+    // y enters the next product as its K-major A operand and, transposed, a weight-gradient product:
     // its split is written by this kernel's epilogue
     KeptSplit* ky = y.storage().kept_split(0, m, n, n, ctk_matmul_split_bytes(m, n));
-    cuda_check(ctk_matmul_3xtf32_fused_f32(data<float>(), W.data<float>(), y.data<float>(), m, n, k, sa0, sa1, sb0, sb1, ka ? ka->buf : nullptr,
-                                           ka ? &ka->valid : nullptr, kb ? kb->buf : nullptr, kb ? &kb->valid : nullptr, bias.data<float>(),
-                                           relu ? 1 : 0, ky ? ky->buf : nullptr, nullptr, t_stream),
-               "fused MatMul + bias" );
+    cuda_check(ctk_matmul_3xtf32_fused_f32(A.data<float>(), B.data<float>(), yp, m, n, k, sa0, sa1, sb0, sb1, ka ? ka->buf : nullptr,
+                                           ka ? &ka->valid : nullptr, kb ? kb->buf : nullptr, kb ? &kb->valid : nullptr,
+                                           bias ? bias->data<float>() : nullptr, relu ? 1 : 0, mask ? mask->data<float>() : nullptr,
+                                           ky ? ky->buf : nullptr, nullptr, t_stream),
+               "fused MatMul epilogue");
     if (ky) ky->valid = 1;
+    return true;
+}
+
+Tensor Tensor::matmul_masked(const Tensor& other, const Tensor& mask) const {
+    Tensor y;
+    if (fused_product(*this, other, nullptr, false, &mask, y)) return y;
+    Tensor p = matmul(other);
+    Tensor r(ShapeTag{}, p.sizes(), p.dtype(), p.device(), false);
+    cuda_check(ctk_unary_backward_f32(CTK_OP_RELU, mask.data<float>(), p.data<float>(), r.data<float>(), static_cast<int64_t>(p.numel()), t_stream),
+               "ReLU backward");
+    return r;
+}
+
+Tensor Tensor::linear(const Tensor& W, const Tensor& bias, bool relu) const {
+    Tensor y;
+    if (!fused_product(*this, W, &bias, relu, nullptr, y)) {
+        // (a returned temporary or moved local keeps its id, which is its key on the tape; a copy would not)
+        if (relu) return (matmul(W) + bias).relu();
+        return matmul(W) + bias;
+    }
+    const size_t m = _shape[0], n = W.shape()[1];
     // the tape sees the three operations
     const bool rg = _requires_grad || W.requires_grad() || bias.requires_grad();
     const std::vector<size_t> out_shape = {static_cast<size_t>(m), static_cast<size_t>(n)};

@@ -117,6 +117,10 @@ public:
     // shapes only, no rule reads their values -- and equal to them bit for bit.  Anything else runs
     // the three calls.  No counterpart in the reference.
     Tensor linear(const Tensor& W, const Tensor& bias, bool relu) const;
+    // this.matmul(other) * (mask > 0 ? 1 : 0): a gradient product followed by ReLU's backward rule with
+    // mask the ReLU's output, in one kernel where the device path allows it (else the two kernels);
+    // not recorded on the tape (backward calls it).  No counterpart in the reference.
+    Tensor matmul_masked(const Tensor& other, const Tensor& mask) const;
     Tensor dot(const Tensor& other) const;
     Tensor relu() const;
     Tensor sigmoid() const;

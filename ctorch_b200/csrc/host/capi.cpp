@@ -72,6 +72,10 @@ public:
     void* copy_stream = nullptr;
 
     MlpTrainer(int n_layers, const int64_t* d, const float* params, float lr_) : dims(d, d + n_layers + 1), lr(lr_) {
+        // hidden activations are read by the next layer's product only, and nobody asks for their
+        // gradients: their ReLU's backward rule runs in the epilogue of the product g.W^T
+        const char* frb = std::getenv("CTORCH_FUSE_RELU_BACKWARD");
+        ctx.set_fuse_relu_backward(!(frb && frb[0] == '0'));
         const float* p = params;
         for (int l = 0; l < n_layers; ++l) {
             const size_t in = static_cast<size_t>(dims[l]), out = static_cast<size_t>(dims[l + 1]);
@@ -608,6 +612,9 @@ int cth_ctx_clear(void* c) {
 }
 int cth_ctx_release_step_nodes(void* c) {
     return guarded([&] { static_cast<AutoDiff*>(c)->release_step_nodes(); });
+}
+int cth_ctx_set_fuse_relu_backward(void* c, int on) {
+    return guarded([&] { static_cast<AutoDiff*>(c)->set_fuse_relu_backward(on != 0); });
 }
 int cth_ctx_make_leaf(void* c, void* t, int requires_grad) {
     return guarded([&] { static_cast<AutoDiff*>(c)->make_leaf(*T(t), requires_grad != 0); });

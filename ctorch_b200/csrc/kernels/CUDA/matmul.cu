@@ -189,10 +189,13 @@ struct Params {
     float* c;
     int vec_store;    // n % 4 == 0 and c 16-byte aligned
     int whole_tiles;  // tiles [0, whole_tiles) are computed whole; each later tile as two K-halves
-    // Epilogue of the fused forms (all optional; whole tiles only): c = [relu](acc + bias[col]), and the
-    // hi/lo split of c written next to it ([m, split_pitch] each) for the products c enters next.
+    // Epilogue of the fused forms (all optional; whole tiles only): c = [relu](acc + bias[col]), then
+    // c *= (mask > 0 ? 1 : 0) with mask an [m, n] array of pitch n (ReLU's backward rule applied to a
+    // gradient product), and the hi/lo split of c written next to it ([m, split_pitch] each) for the
+    // products c enters next.
     const float* bias;
     int relu;
+    const float* mask;
     float* out_hi;
     float* out_lo;
     int64_t split_pitch;
@@ -361,7 +364,12 @@ __device__ __forceinline__ void emit_chunk(const Params& P, bool half, int64_t r
             const int rr = i * 4 + sub;
             const int64_t grow = row_base + rr;
             if (grow < P.m) {
-                const float4 x = *reinterpret_cast<const float4*>(&stage[rr][c4]);
+                float4 x = *reinterpret_cast<const float4*>(&stage[rr][c4]);
+                if (P.mask != nullptr) {  // g * (y > 0 ? 1 : 0): the backward rule of ReLU, y its output
+                    const float4 y = __ldcs(reinterpret_cast<const float4*>(P.mask + grow * P.n + col0 + c4));
+                    x.x *= y.x > 0.0f ? 1.0f : 0.0f; x.y *= y.y > 0.0f ? 1.0f : 0.0f;
+                    x.z *= y.z > 0.0f ? 1.0f : 0.0f; x.w *= y.w > 0.0f ? 1.0f : 0.0f;
+                }
                 __stcs(reinterpret_cast<float4*>(P.c + grow * P.n + col0 + c4), x);
                 if (P.out_hi != nullptr) {
                     float4 h, l;
@@ -398,6 +406,7 @@ __device__ __forceinline__ void emit_chunk(const Params& P, bool half, int64_t r
             float x = __uint_as_float(r[v]);
             if (P.bias != nullptr) x += __ldg(P.bias + col0 + v);
             if (P.relu) x = x > 0.0f ? x : 0.0f;
+            if (P.mask != nullptr) x *= P.mask[row * P.n + col0 + v] > 0.0f ? 1.0f : 0.0f;
             crow[col0 + v] = x;
             if (P.out_hi != nullptr) {
                 const float h = to_tf32_rna(x);
@@ -1254,6 +1263,7 @@ struct KeptSplit {
 struct FusedEpilogue {
     const float* bias = nullptr;
     int relu = 0;
+    const float* mask = nullptr;
     void* c_split = nullptr;
 };
 
@@ -1274,7 +1284,7 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
     CTK_REQUIRE(m < (int64_t(1) << 31) && n < (int64_t(1) << 31) && k < (int64_t(1) << 31), "ctk_matmul_f32: extent >= 2^31");
 
     tc::Operand A, B;
-    const bool fused = fe.bias != nullptr || fe.relu || fe.c_split != nullptr;
+    const bool fused = fe.bias != nullptr || fe.relu || fe.mask != nullptr || fe.c_split != nullptr;
     if (choose_path(a, b, m, n, k, sa0, sa1, sb0, sb1, md, &A, &B) == 1) {
         if (fused) return fail(CTK_ERR_INVALID, "fused MatMul: the operands need the tensor-core path (a unit stride each)");
         dim3 grid(static_cast<unsigned>((n + SM_TILE - 1) / SM_TILE), static_cast<unsigned>((m + SM_TILE - 1) / SM_TILE));
@@ -1351,6 +1361,7 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
     P.vec_store = (n % 4 == 0) && ((reinterpret_cast<uintptr_t>(c) & 15u) == 0);
     P.bias = fe.bias;
     P.relu = fe.relu;
+    P.mask = fe.mask;
     P.out_hi = P.out_lo = nullptr;
     P.split_pitch = (n + 3) / 4 * 4;
     if (fe.c_split) {
@@ -1417,16 +1428,21 @@ ctk_status ctk_matmul_3xtf32_kept_f32(const float* a, const float* b, float* c, 
 // The bias add and the ReLU are the single fp32 operations of Add_BASIC_kernel's [N,H] + [H] form and
 // of ReLU_BASIC_kernel applied to the rounded accumulator, so the result equals MatMul, Add, ReLU run
 // one after the other bit for bit; what is saved is their two passes over c and the read of the later
-// split.  bias: n floats or NULL; c_split: ctk_matmul_split_bytes(m, n) bytes or NULL (valid for c
-// viewed as [m, n] with pitch n afterwards).  Needs the tensor-core path for both operands.
+// split.  mask (an [m, n] array of pitch n, or NULL) multiplies the result by (mask > 0 ? 1 : 0), the
+// single operation of ReLU's backward rule with mask the ReLU's output: a gradient product g.W^T that
+// feeds that rule leaves the kernel already masked and split.  bias: n floats or NULL; c_split:
+// ctk_matmul_split_bytes(m, n) bytes or NULL (valid for c viewed as [m, n] with pitch n afterwards).
+// Needs the tensor-core path for both operands.
 ctk_status ctk_matmul_3xtf32_fused_f32(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k, int64_t sa0,
                                        int64_t sa1, int64_t sb0, int64_t sb1, void* a_split, int* a_valid, void* b_split,
-                                       int* b_valid, const float* bias, int relu, void* c_split, void* workspace, void* stream) {
+                                       int* b_valid, const float* bias, int relu, const float* mask, void* c_split, void* workspace,
+                                       void* stream) {
     CTK_REQUIRE((!a_split || a_valid) && (!b_split || b_valid), "ctk_matmul_3xtf32_fused_f32: a split buffer needs its valid flag");
     CTK_REQUIRE(m > 0 && n > 0 && k > 0, "ctk_matmul_3xtf32_fused_f32: empty product");
     FusedEpilogue fe;
     fe.bias = bias;
     fe.relu = relu ? 1 : 0;
+    fe.mask = mask;
     fe.c_split = c_split;
     return matmul_impl(a, b, c, m, n, k, sa0, sa1, sb0, sb1, CTK_MATMUL_3XTF32, workspace, KeptSplit{a_split, a_valid}, KeptSplit{b_split, b_valid}, stream, fe);
 }

@@ -195,6 +195,7 @@ class AutoDiff:
     def zero_grad(self, t): _chk(lib.cth_ctx_zero_grad(self.h, t.h))
     def clear_graph(self): _chk(lib.cth_ctx_clear(self.h))
     def release_step_nodes(self): _chk(lib.cth_ctx_release_step_nodes(self.h))
+    def set_fuse_relu_backward(self, on): _chk(lib.cth_ctx_set_fuse_relu_backward(self.h, 1 if on else 0))
 
     def node_count(self):
         n = ctypes.c_uint64()

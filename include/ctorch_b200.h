@@ -288,14 +288,17 @@ ctk_status ctk_matmul_3xtf32_kept_f32(const float* a, const float* b, float* c, 
  * the epilogue of the 3xTF32 product adds the bias to the rounded fp32 accumulator, applies
  * x > 0 ? x : 0, stores c and -- if c_split is given -- c's own hi/lo split for the products c enters
  * next.  Bit-identical to the three kernels run in sequence (on whole tiles: this call never cuts a
- * tile's K in two).  bias: n floats or NULL; relu: 0/1;
+ * tile's K in two).  mask, an [m, n] array of pitch n or NULL, multiplies the result by
+ * (mask > 0 ? 1 : 0) before it is stored and split: with mask the output of a ReLU this is the ReLU's
+ * backward rule (AutoDiff.cpp:1320-1371) applied to a gradient product g.W^T in its epilogue.
+ * bias: n floats or NULL; relu: 0/1;
  * c_split: ctk_matmul_split_bytes(m, n) bytes or NULL; the other arguments as in
  * ctk_matmul_3xtf32_kept_f32.  Fails with CTK_ERR_INVALID if an operand has no unit stride. */
 ctk_status ctk_matmul_3xtf32_fused_f32(const float* a, const float* b, float* c, int64_t m, int64_t n,
                                        int64_t k, int64_t sa0, int64_t sa1, int64_t sb0, int64_t sb1,
                                        void* a_split, int* a_valid, void* b_split, int* b_valid,
-                                       const float* bias, int relu, void* c_split, void* workspace,
-                                       void* stream);
+                                       const float* bias, int relu, const float* mask, void* c_split,
+                                       void* workspace, void* stream);
 /* No counterpart in the reference.  The 3xTF32 product for callers that must not allocate device
  * memory (inside a stream capture, under an arena allocator that owns the whole GPU, or in a loop
  * that cannot afford a workspace growing under it): identical arguments and result to

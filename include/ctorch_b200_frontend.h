@@ -57,6 +57,11 @@ int cth_ctx_zero_grad(void* ctx, void* tensor);
 int cth_ctx_clear(void* ctx);                         /* AutoDiff::clear_graph */
 int cth_ctx_release_step_nodes(void* ctx);            /* drop nodes no future root can reach (no counterpart) */
 int cth_ctx_node_count(void* ctx, uint64_t* n);
+/* No counterpart.  on != 0: a ReLU output that exactly one MatMul reads (as its first operand) gets its
+ * backward rule (src/AutoDiff.cpp:1320-1371) applied in the epilogue of the product g.W^T that computes
+ * its gradient.  Every gradient upstream is bit for bit the same; cth_grad of that ReLU output itself
+ * then returns the masked gradient.  Off by default; the MLP trainer switches it on for its own tape. */
+int cth_ctx_set_fuse_relu_backward(void* ctx, int on);
 int cth_backward(void* root, void* grad_output_or_null); /* free backward(root[, grad]), src/Tensor.cpp:1373-1384 */
 int cth_grad(void* tensor, void** out);                /* free grad(t), src/Tensor.cpp:1387-1392 */
 /* (x.matmul(w) + bias)[.relu()] as one kernel where possible, recorded as the same MatMul, Add and

@@ -517,3 +517,59 @@ def test_trainer_with_and_without_fused_linear_is_bit_identical(F, cb):
     finally:
         cb.ops.set_matmul_tail_split(1)
     assert_exact(tr.grads(), grads, "gradients: trainer (fused forward) == op-by-op front end")
+
+
+@pytest.mark.parametrize("batch,dims", [(256, [96, 128, 64, 12]), (130, [64, 132, 260, 10]), (8192, [784, 128, 128, 10])])
+def test_relu_backward_in_the_gradient_products_epilogue(F, cb, batch, dims):
+    """set_fuse_relu_backward: the product g.W^T whose result only feeds a ReLU's backward rule applies
+    the rule (and writes the hi/lo split the next two products read) in its epilogue.  Loss and every
+    parameter gradient are bit for bit those of the unfused tape; the gradient stored for the hidden
+    activation itself is the masked one."""
+    rng = np.random.default_rng(batch + dims[1])
+    Ws = [(rng.standard_normal((i, j)) / np.sqrt(i)).astype(np.float32) for i, j in zip(dims[:-1], dims[1:])]
+    bs = [rng.uniform(-0.1, 0.1, j).astype(np.float32) for j in dims[1:]]
+    x = rng.standard_normal((batch, dims[0])).astype(np.float32)
+    oh = np.zeros((batch, dims[-1]), np.float32)
+    oh[np.arange(batch), rng.integers(0, dims[-1], batch)] = 1
+    out = {}
+    cb.ops.set_matmul_tail_split(0)
+    try:
+        for fused in (False, True):
+            with F.AutoDiff() as ctx:
+                ctx.set_fuse_relu_backward(fused)
+                W = [dev(F, a).requires_grad() for a in Ws]
+                B = [dev(F, a).requires_grad() for a in bs]
+                h = dev(F, x)
+                hidden = []
+                for l in range(len(Ws)):
+                    h = h.linear(W[l], B[l], l + 1 < len(Ws))
+                    hidden.append(h)
+                L = h.cross_entropy(dev(F, oh))
+                F.backward(L)
+                out[fused] = [L.numpy()] + [F.grad(t).numpy() for t in W + B] + [F.grad(hidden[0]).numpy(), hidden[0].numpy()]
+    finally:
+        cb.ops.set_matmul_tail_split(1)
+    for i, (a, c) in enumerate(zip(out[False][:-2], out[True][:-2])):
+        assert_exact(c, a, f"loss / parameter gradient {i}: fused == unfused")
+    g_plain, y = out[False][-2], out[False][-1]
+    assert_exact(out[True][-2], g_plain * (y > 0).astype(np.float32), "stored gradient of the hidden activation: the masked one")
+
+
+def test_relu_backward_fusion_is_skipped_when_the_activation_has_two_readers(F, cb):
+    """A ReLU output read by two products keeps the plain rule: its gradient is a sum of two
+    contributions and the mask applies to the sum."""
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((128, 64)).astype(np.float32)
+    w, w2, w3 = (rng.standard_normal(s).astype(np.float32) / 8 for s in ((64, 64), (64, 32), (64, 32)))
+    b = rng.standard_normal(64).astype(np.float32)
+    out = {}
+    for fused in (False, True):
+        with F.AutoDiff() as ctx:
+            ctx.set_fuse_relu_backward(fused)
+            X, W, W2, W3, B = (dev(F, a).requires_grad() for a in (x, w, w2, w3, b))
+            h = X.linear(W, B, True)
+            L = (h.matmul(W2) * h.matmul(W3)).sum()
+            F.backward(L)
+            out[fused] = [F.grad(t).numpy() for t in (X, W, W2, W3, B)] + [F.grad(h).numpy()]
+    for a, c in zip(out[False], out[True]):
+        assert_exact(c, a, "two readers: nothing changes")

@@ -6,7 +6,7 @@ fp32 CUDA-core path."""
 import numpy as np
 import pytest
 
-from conftest import assert_matmul_close
+from conftest import assert_exact, assert_matmul_close
 
 pytestmark = pytest.mark.gpu
 
@@ -216,3 +216,58 @@ def test_a_wait_that_runs_out_is_reported_not_hung(cb):
     A, B, _ = _mats(128, 64, 64, 13)
     C = cb.ops.matmul(cb.to_device(A), cb.to_device(B)).numpy()       # the device still works
     assert_matmul_close(C, A.astype(np.float64) @ B.astype(np.float64), 1e-4, "product after the self-test")
+
+
+@pytest.mark.parametrize("pairing", [0, 1])
+@pytest.mark.parametrize("m,k,n,ta,tb", [
+    (256, 96, 320, False, False),
+    (130, 64, 132, False, True),        # ragged rows, last column chunk of 4
+    (384, 520, 600, True, False),
+    (700, 40, 1000, False, True),       # the gradient product's shape: g.W^T
+    (96, 33, 36, False, False),
+])
+def test_fused_epilogue_equals_the_separate_kernels(cb, m, k, n, ta, tb, pairing):
+    """ctk_matmul_3xtf32_fused_f32: bias add, ReLU, the ReLU backward mask and the hi/lo split of the
+    result in the product's epilogue, against the same product followed by the separate kernels (whole
+    tiles on both sides) -- bit for bit, for every combination the front end uses."""
+    A, B, _ = _mats(m, k, n, 21)
+    rng = np.random.default_rng(m * n)
+    bias = rng.standard_normal(n).astype(np.float32)
+    y_act = np.maximum(rng.standard_normal((m, n)), 0).astype(np.float32)     # a ReLU output: zeros and positives
+    dA, dB = cb.to_device(A.T.copy() if ta else A), cb.to_device(B.T.copy() if tb else B)
+    dbias, dmask = cb.to_device(bias), cb.to_device(y_act)
+    try:
+        cb.ops.set_matmul_pairing(pairing)
+        cb.ops.set_matmul_tail_split(0)
+        plain = cb.ops.matmul(dA, dB, ta, tb, "3xtf32")
+        biased = cb.ops.binary("Add", plain, dbias, cb.ops.B_ROW)
+        relu = cb.ops.unary("ReLU", biased).numpy()
+        masked = cb.ops.unary_backward("ReLU", dmask, plain).numpy()
+        f_relu, hi, lo = cb.ops.matmul_fused(dA, dB, bias=dbias, relu=True, want_split=True, ta=ta, tb=tb)
+        f_bias = cb.ops.matmul_fused(dA, dB, bias=dbias, ta=ta, tb=tb).numpy()
+        f_mask, mhi, mlo = cb.ops.matmul_fused(dA, dB, mask=dmask, want_split=True, ta=ta, tb=tb)
+    finally:
+        cb.ops.set_matmul_pairing(0)
+        cb.ops.set_matmul_tail_split(1)
+    _check_status(cb)
+    assert_exact(f_bias, biased.numpy(), "product + bias")
+    assert_exact(f_relu.numpy(), relu, "relu(product + bias)")
+    assert_exact(f_mask.numpy(), masked, "product * (y > 0)")
+    for c, h, l, name in ((relu, hi, lo, "relu"), (masked, mhi, mlo, "masked")):
+        eh, el = oracle_split(c)
+        assert_exact(h, eh, f"{name}: hi part written by the epilogue")
+        assert_exact(l, el, f"{name}: lo part written by the epilogue")
+
+
+def oracle_split(x):
+    """cvt.rna.tf32.f32 of x and of x - hi: round to nearest, ties away from zero, 10 mantissa bits."""
+    def rna(v):
+        u = v.view(np.uint32).astype(np.uint64)
+        r = ((u + 0x1000) & 0xFFFFE000).astype(np.uint32)
+        out = r.view(np.float32).copy()
+        special = ~np.isfinite(v)
+        out[special] = v[special]
+        return out
+    x = np.ascontiguousarray(x, np.float32)
+    hi = rna(x)
+    return hi, rna((x - hi).astype(np.float32))
