@@ -455,7 +455,13 @@ void AutoDiff::backward(Tensor& root, Tensor grad_output) {
     for (Node* node : order) {
         if (!node->requires_grad || !node->grad) continue;
         node->materialize_grad();  // an upstream gradient that was only flagged zero is read as zeros
-        for (size_t input_id : node->input_ids) {
+        // The reference visits the inputs in recorded order (:1189).  The contributions of one node do
+        // not depend on one another, so a product's second operand -- the weights, a leaf whose
+        // gradient a data-parallel driver starts reducing the moment it exists -- goes first: its
+        // all-reduce then overlaps the product for the first operand as well.
+        std::vector<size_t> visit(node->input_ids);
+        if (node->operation == op::MatMul && visit.size() == 2 && visit[0] != visit[1]) std::swap(visit[0], visit[1]);
+        for (size_t input_id : visit) {
             auto in_it = id_to_node.find(input_id);
             if (in_it == id_to_node.end() || !in_it->second || !in_it->second->requires_grad) continue;
             Node& input_node = *in_it->second;

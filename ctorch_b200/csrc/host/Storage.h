@@ -248,6 +248,7 @@ public:
     DType dtype() const { return _dtype; }
     DeviceType device() const { return _device; }
     bool empty() const { return _size == 0 || !_data; }
+    bool has_split() const { return _data && _data->split; }
     void clear() { _data.reset(); _size = 0; }
     bool unique() const { return !_data || _data.use_count() == 1; }
 

@@ -521,8 +521,10 @@ static bool fused_product(const Tensor& A, const Tensor& B, const Tensor* bias, 
 }
 
 Tensor Tensor::matmul_masked(const Tensor& other, const Tensor& mask) const {
+    // A short K (the 10-class layer's g.W^T has K = 10) leaves the product nothing to hide a four-array
+    // epilogue behind: below 256 the two kernels are faster.
     Tensor y;
-    if (fused_product(*this, other, nullptr, false, &mask, y)) return y;
+    if (_shape.size() == 2 && _shape[1] >= 256 && fused_product(*this, other, nullptr, false, &mask, y)) return y;
     Tensor p = matmul(other);
     Tensor r(ShapeTag{}, p.sizes(), p.dtype(), p.device(), false);
     cuda_check(ctk_unary_backward_f32(CTK_OP_RELU, mask.data<float>(), p.data<float>(), r.data<float>(), static_cast<int64_t>(p.numel()), t_stream),
@@ -644,7 +646,21 @@ void Tensor::sgd_update_(const Tensor& g, float lr) {
     if (g.numel() != numel()) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DIMENSION, "sgd_update_: gradient has a different size");
     if (_device != DeviceType::kCUDA || g.device() != DeviceType::kCUDA)
         Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DEVICE_COMPAT, "sgd_update_: device tensors expected");
-    cuda_check(ctk_sgd_update_f32(data<float>(), g.data<float>(), lr, static_cast<int64_t>(numel()), t_stream), "sgd_update_");
+    // A weight matrix that enters products (its buffer carries a kept hi/lo split) gets the split of
+    // its new value from the update kernel itself instead of a separate pass before the next product.
+    const bool resplit = _storage.has_split() && _shape.size() == 2 && is_contiguous() && g.is_contiguous() && _shape[1] % 4 == 0 &&
+                         _storage_offset % 4 == 0 && g.storage_offset() % 4 == 0;
+    float* p = data<float>();  // detaches from sharers, drops the split of the old value
+    if (resplit) {
+        const int64_t outer = static_cast<int64_t>(_shape[0]), inner = static_cast<int64_t>(_shape[1]);
+        KeptSplit* ks = _storage.kept_split(static_cast<int64_t>(_storage_offset), outer, inner, inner, ctk_matmul_split_bytes(inner, outer));
+        if (ks) {
+            cuda_check(ctk_sgd_update_split_f32(p, g.data<float>(), lr, outer, inner, inner, ks->buf, t_stream), "sgd_update_ (with split)");
+            ks->valid = 1;
+            return;
+        }
+    }
+    cuda_check(ctk_sgd_update_f32(p, g.data<float>(), lr, static_cast<int64_t>(numel()), t_stream), "sgd_update_");
 }
 
 // ---- free functions (src/Tensor.cpp:1373-1453) ---------------------------------------------------------------

@@ -144,6 +144,39 @@ __global__ void __launch_bounds__(SPLIT_THREADS) split_tf32_vec_kernel(const flo
         }
     }
 }
+// The SGD update of a weight matrix with its hi/lo split rewritten in the same pass: p -= g*lr as in
+// ctk_sgd_update_f32 (one fused multiply-add), then the split of the NEW value for the product the
+// weights enter next.  p viewed [outer, inner] with pitch ld_in, g contiguous.
+__global__ void __launch_bounds__(SPLIT_THREADS) sgd_split_vec_kernel(float* __restrict__ p, const float* __restrict__ g, float lr, float* __restrict__ hi,
+                                                                      float* __restrict__ lo, int64_t outer, int64_t inner4, int64_t ld_in, int64_t ld_out) {
+    const int64_t total = outer * inner4;
+    const int64_t base = static_cast<int64_t>(blockIdx.x) * (SPLIT_THREADS * SPLIT_UNROLL) + threadIdx.x;
+    float4 v[SPLIT_UNROLL], d[SPLIT_UNROLL];
+    int64_t r[SPLIT_UNROLL], c4[SPLIT_UNROLL];
+#pragma unroll
+    for (int u = 0; u < SPLIT_UNROLL; ++u) {
+        const int64_t i = base + u * SPLIT_THREADS;
+        if (i < total) {
+            r[u] = i / inner4;
+            c4[u] = i - r[u] * inner4;
+            v[u] = *(reinterpret_cast<const float4*>(p + r[u] * ld_in) + c4[u]);
+            d[u] = __ldcs(reinterpret_cast<const float4*>(g) + i);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < SPLIT_UNROLL; ++u) {
+        const int64_t i = base + u * SPLIT_THREADS;
+        if (i < total) {
+            float4 x, h, l;
+            x.x = fmaf(-d[u].x, lr, v[u].x); x.y = fmaf(-d[u].y, lr, v[u].y); x.z = fmaf(-d[u].z, lr, v[u].z); x.w = fmaf(-d[u].w, lr, v[u].w);
+            h.x = to_tf32_rna(x.x); h.y = to_tf32_rna(x.y); h.z = to_tf32_rna(x.z); h.w = to_tf32_rna(x.w);
+            l.x = to_tf32_rna(x.x - h.x); l.y = to_tf32_rna(x.y - h.y); l.z = to_tf32_rna(x.z - h.z); l.w = to_tf32_rna(x.w - h.w);
+            *(reinterpret_cast<float4*>(p + r[u] * ld_in) + c4[u]) = x;
+            reinterpret_cast<float4*>(hi + r[u] * ld_out)[c4[u]] = h;
+            reinterpret_cast<float4*>(lo + r[u] * ld_out)[c4[u]] = l;
+        }
+    }
+}
 // Any pitch, any alignment (e.g. the 10-class layer's rows of 40 bytes): one element per thread.
 __global__ void __launch_bounds__(SPLIT_THREADS) split_tf32_scalar_kernel(const float* __restrict__ x, float* __restrict__ hi, float* __restrict__ lo,
                                                                           int64_t outer, int64_t inner, int64_t ld_in, int64_t ld_out) {
@@ -1445,6 +1478,28 @@ ctk_status ctk_matmul_3xtf32_fused_f32(const float* a, const float* b, float* c,
     fe.mask = mask;
     fe.c_split = c_split;
     return matmul_impl(a, b, c, m, n, k, sa0, sa1, sb0, sb1, CTK_MATMUL_3XTF32, workspace, KeptSplit{a_split, a_valid}, KeptSplit{b_split, b_valid}, stream, fe);
+}
+
+// p -= g*lr (ctk_sgd_update_f32's arithmetic) and, in the same pass, the hi/lo split of the updated p
+// into `split` -- a buffer of ctk_matmul_split_bytes(inner, outer) bytes that ctk_matmul_3xtf32_kept_f32
+// then takes as valid for p viewed as [outer, inner] with pitch ld (or, transposed, with the strides
+// swapped).  Saves the split's own read of the weights before their next product.  p and g 16-byte
+// aligned, inner and ld multiples of 4, g contiguous; anything else is refused (CTK_ERR_INVALID) and the
+// caller runs the plain update.
+ctk_status ctk_sgd_update_split_f32(float* p, const float* g, float lr, int64_t outer, int64_t inner, int64_t ld, void* split, void* stream) {
+    CTK_REQUIRE(outer >= 0 && inner >= 0 && ld >= inner, "ctk_sgd_update_split_f32: bad extents");
+    if (outer == 0 || inner == 0) return CTK_OK;
+    CTK_REQUIRE(p && g && split, "ctk_sgd_update_split_f32: null pointer");
+    CTK_REQUIRE(((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g)) & 15u) == 0 && inner % 4 == 0 && ld % 4 == 0,
+                "ctk_sgd_update_split_f32: needs 16-byte aligned rows (use ctk_sgd_update_f32)");
+    float* hi = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(split) + 255u) & ~static_cast<uintptr_t>(255u));
+    float* lo = hi + outer * inner;  // (pitch of the copies = inner, already a multiple of 4)
+    const int64_t total = outer * (inner / 4);
+    const int64_t per_cta = SPLIT_THREADS * SPLIT_UNROLL;
+    sgd_split_vec_kernel<<<static_cast<unsigned>((total + per_cta - 1) / per_cta), SPLIT_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+        p, g, lr, hi, lo, outer, inner / 4, ld, inner);
+    CTK_LAUNCH_CHECK("sgd_split_vec_kernel");
+    return CTK_OK;
 }
 
 // 3xTF32 MatMul that allocates nothing: same arguments and same result as ctk_matmul_f32 in mode

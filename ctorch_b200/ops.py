@@ -198,6 +198,16 @@ def matmul_fused(a, b, bias=None, relu=False, mask=None, want_split=False, ta=Fa
     return out, hi, lo
 
 
+def sgd_update_split(p, g, lr, stream=None):
+    """p -= g*lr on a 2-D array and the hi/lo split of the new p in the same pass; returns (hi, lo)."""
+    outer, inner = p.shape
+    split = DeviceArray((int(lib.ctk_matmul_split_bytes(inner, outer)) // 4,))
+    check(lib.ctk_sgd_update_split_f32(p.p, g.p, _f(lr), _i64(outer), _i64(inner), _i64(inner), split.p, _sh(stream)))
+    pad = (-split.ptr) % 256 // 4
+    flat = split.numpy()
+    return flat[pad:pad + outer * inner].reshape(outer, inner), flat[pad + outer * inner:pad + 2 * outer * inner].reshape(outer, inner)
+
+
 def matmul_path(a, b, ta=False, tb=False, mode=-1):
     mode = MODES.get(mode, mode)
     m, k = (a.shape[1], a.shape[0]) if ta else a.shape

@@ -299,6 +299,13 @@ ctk_status ctk_matmul_3xtf32_fused_f32(const float* a, const float* b, float* c,
                                        void* a_split, int* a_valid, void* b_split, int* b_valid,
                                        const float* bias, int relu, const float* mask, void* c_split,
                                        void* workspace, void* stream);
+/* The SGD loop of mnist/mnist.cpp:80-92 on a weight matrix, with the hi/lo split of the updated
+ * weights written in the same pass: p = fma(-g, lr, p) exactly as ctk_sgd_update_f32, then hi/lo of the
+ * new p into `split` (ctk_matmul_split_bytes(inner, outer) bytes), which ctk_matmul_3xtf32_kept_f32
+ * accepts as valid for p viewed [outer, inner] with pitch ld, or its t() view.  p, g 16-byte aligned,
+ * inner % 4 == 0, ld % 4 == 0, g contiguous; otherwise CTK_ERR_INVALID and nothing is launched. */
+ctk_status ctk_sgd_update_split_f32(float* p, const float* g, float lr, int64_t outer, int64_t inner,
+                                    int64_t ld, void* split, void* stream);
 /* No counterpart in the reference.  The 3xTF32 product for callers that must not allocate device
  * memory (inside a stream capture, under an arena allocator that owns the whole GPU, or in a loop
  * that cannot afford a workspace growing under it): identical arguments and result to

@@ -271,3 +271,21 @@ def oracle_split(x):
     x = np.ascontiguousarray(x, np.float32)
     hi = rna(x)
     return hi, rna((x - hi).astype(np.float32))
+
+
+@pytest.mark.parametrize("outer,inner", [(784, 4096), (130, 132), (3, 4)])
+def test_sgd_update_with_split_equals_update_then_split(cb, outer, inner):
+    """ctk_sgd_update_split_f32: the same p as ctk_sgd_update_f32 bit for bit, and the hi/lo parts of
+    that p; a product that takes the buffer as a kept split equals one that splits p itself."""
+    rng = np.random.default_rng(outer)
+    p0 = rng.standard_normal((outer, inner)).astype(np.float32)
+    g = rng.standard_normal((outer, inner)).astype(np.float32)
+    a, b, dg = cb.to_device(p0), cb.to_device(p0), cb.to_device(g)
+    cb.ops.sgd_update(a, dg, 0.0123)
+    hi, lo = cb.ops.sgd_update_split(b, dg, 0.0123)
+    assert_exact(b.numpy(), a.numpy(), "updated weights")
+    eh, el = oracle_split(a.numpy())
+    assert_exact(hi, eh, "hi part of the updated weights")
+    assert_exact(lo, el, "lo part of the updated weights")
+    with pytest.raises(cb.CtkError):
+        cb.ops.sgd_update_split(cb.to_device(p0[:, :inner - 1].copy()), dg, 0.1)   # rows not 16-byte aligned
