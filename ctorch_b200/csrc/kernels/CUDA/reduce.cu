@@ -7,10 +7,15 @@
 // the tree used here is at least as accurate, which is how parity of these sums is judged.
 #include <math.h>
 
+#include <atomic>
+
 #include "ew_skeleton.cuh"
 #include "reduce_common.cuh"
 
 namespace ctk {
+
+static std::atomic<bool> g_library_scratch_dirty{false};
+void mark_reduce_scratch_dirty() { g_library_scratch_dirty.store(true); }
 
 ctk_status reduce_scratch(void* user, cudaStream_t st, ReduceScratch** out) {
     void* p = user;
@@ -20,8 +25,10 @@ ctk_status reduce_scratch(void* user, cudaStream_t st, ReduceScratch** out) {
     }
     CTK_REQUIRE((reinterpret_cast<uintptr_t>(p) & 7u) == 0, "reduction scratch must be 8-byte aligned");
     *out = static_cast<ReduceScratch*>(p);
-    // The ticket must start at zero; a caller-supplied block is not trusted to be clean.
-    CTK_CUDA(cudaMemsetAsync(&(*out)->ticket, 0, sizeof(unsigned int), st));
+    // The ticket must start at zero.  The library's own block is zeroed when it is allocated and every
+    // kernel rewinds the ticket it used, so only a caller-supplied block (not trusted to be clean) or
+    // a kernel that gave up on a bounded wait (reported through the status word) costs a memset.
+    if (user || g_library_scratch_dirty.exchange(false)) CTK_CUDA(cudaMemsetAsync(&(*out)->ticket, 0, sizeof(unsigned int), st));
     return CTK_OK;
 }
 

@@ -88,5 +88,7 @@ __device__ __forceinline__ void grid_finish(double cta_total, ReduceScratch* s, 
 }
 
 ctk_status reduce_scratch(void* user, cudaStream_t st, ReduceScratch** out);
+// A kernel left the library's own scratch block with a ticket it did not rewind: zero it before the next use.
+void mark_reduce_scratch_dirty();
 
 }  // namespace ctk

@@ -1180,6 +1180,7 @@ ctk_status ctk_rowwise_status(int* status) {
     CTK_REQUIRE(status, "ctk_rowwise_status: null");
     CTK_CUDA(cudaDeviceSynchronize());
     CTK_CUDA(cudaMemcpyFromSymbol(status, g_row_status, sizeof(int)));
+    if (*status != 0) mark_reduce_scratch_dirty();  // a CTA that gave up did not take its ticket
     return CTK_OK;
 }
 
