@@ -381,7 +381,18 @@ def run_single_op(args):
             for op in ("Neg", "ReLU", "Sigmoid", "Tanh", "Sin", "Cos"):
                 emit(f"{op}_fwd_2^{logn}", timeit(lambda: cb.ops.unary(op, a, out=o), it), 8 * n, "GB/s", peaks["hbm_gbs"])
                 emit(f"{op}_bwd_2^{logn}", timeit(lambda: lib_unary_bwd(cb, op, a, g, o), it), (8 if op == "Neg" else 12) * n, "GB/s", peaks["hbm_gbs"])
-            del a, b, g, o, o2
+            # comparisons (float -> bool bytes), conversions out of float, uniform random numbers
+            ob = cb.DeviceArray((n,), np.uint8)
+            emit(f"cmp_gt_tensor_2^{logn}", timeit(lambda: cb.check(cb.lib.ctk_compare_f32(0, 0, a.p, b.p, ctypes.c_float(0), ob.p, ctypes.c_int64(n), None)), it), 9 * n, "GB/s", peaks["hbm_gbs"])
+            emit(f"cmp_gt_scalar_2^{logn}", timeit(lambda: cb.check(cb.lib.ctk_compare_f32(0, 1, a.p, None, ctypes.c_float(1.0), ob.p, ctypes.c_int64(n), None)), it), 5 * n, "GB/s", peaks["hbm_gbs"])
+            for code, name, size in ((1, "f64", 8), (2, "i32", 4), (3, "i64", 8), (4, "bool", 1)):
+                od = ob if size == 1 else (o if size == 4 else None)
+                if od is None:
+                    od = cb.DeviceArray((n,), np.float64)
+                emit(f"cast_f32_{name}_2^{logn}", timeit(lambda: cb.check(cb.lib.ctk_cast_f32(code, a.p, od.p, ctypes.c_int64(n), None)), it), (4 + size) * n, "GB/s", peaks["hbm_gbs"])
+                del od
+            emit(f"rand_uniform_2^{logn}", timeit(lambda: cb.check(cb.lib.ctk_rand_uniform_f32(o.p, ctypes.c_int64(n), ctypes.c_uint64(1), ctypes.c_uint64(0), None)), it), 4 * n, "GB/s", peaks["hbm_gbs"])
+            del a, b, g, o, o2, ob
     elif args.workload == "rowwise":
         for C in (10, 1000, 32000):
             rows = (1 << 22) if C == 10 else 65536  # every operand larger than the 126 MB L2

@@ -7,6 +7,8 @@
 
 #include "Tensor.h"
 
+#include <random>
+
 #include <algorithm>
 #include <cmath>
 #include <limits>
@@ -260,6 +262,12 @@ template float* Tensor::data<float>();
 template const float* Tensor::data<float>() const;
 template int32_t* Tensor::data<int32_t>();
 template const int32_t* Tensor::data<int32_t>() const;
+template double* Tensor::data<double>();
+template const double* Tensor::data<double>() const;
+template int64_t* Tensor::data<int64_t>();
+template const int64_t* Tensor::data<int64_t>() const;
+template bool* Tensor::data<bool>();
+template const bool* Tensor::data<bool>() const;
 
 template <typename T>
 T Tensor::item() const {
@@ -435,7 +443,148 @@ void Tensor::zero() {
     if (_device == DeviceType::kCUDA) cuda_check(ctk_memset(_storage.raw(), 0, _storage.nbytes(), t_stream), "zero");
     else std::memset(_storage.raw(), 0, _storage.nbytes());
 }
-void Tensor::ones() { fill(1.0f); }
+void Tensor::ones() {
+    if (_dtype == DType::kFloat) { fill(1.0f); return; }
+    const size_t n = numel();
+    if (n == 0) return;
+    _storage.make_unique();
+    unsigned char* base = static_cast<unsigned char*>(_storage.raw()) + _storage_offset * dtypeSize(_dtype);
+    if (_device == DeviceType::kCUDA) {
+        cuda_check(ctk_fill_dtype(static_cast<int>(_dtype), base, 1.0, static_cast<int64_t>(n), t_stream), "ones");
+        return;
+    }
+    switch (_dtype) {
+        case DType::kDouble: std::fill_n(reinterpret_cast<double*>(base), n, 1.0); break;
+        case DType::kInt: std::fill_n(reinterpret_cast<int32_t*>(base), n, 1); break;
+        case DType::kLong: std::fill_n(reinterpret_cast<int64_t*>(base), n, int64_t(1)); break;
+        default: std::fill_n(reinterpret_cast<bool*>(base), n, true); break;
+    }
+}
+
+// ---- rand (src/Tensor.cpp:458-479) --------------------------------------------------------------------------
+static std::atomic<uint64_t> g_rand_seed{0}, g_rand_offset{0};
+static std::atomic<bool> g_rand_seeded{false};
+void Tensor::manual_seed(uint64_t seed) {
+    g_rand_seed.store(seed);
+    g_rand_offset.store(0);
+    g_rand_seeded.store(true);
+}
+void Tensor::rand() {
+    const size_t n = numel();
+    if (n == 0 || (_dtype != DType::kFloat && _dtype != DType::kDouble)) return;  // other dtypes: untouched, as in the reference
+    if (!g_rand_seeded.exchange(true)) {
+        std::random_device rd;
+        g_rand_seed.store((static_cast<uint64_t>(rd()) << 32) | rd());
+    }
+    if (_device != DeviceType::kCUDA) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DEVICE_COMPAT, "rand: device tensors only");
+    const uint64_t offset = g_rand_offset.fetch_add(n);
+    if (_dtype == DType::kFloat) {
+        cuda_check(ctk_rand_uniform_f32(data<float>(), static_cast<int64_t>(n), g_rand_seed.load(), offset, t_stream), "rand");
+        return;
+    }
+    // double: the same 24-bit uniforms, widened
+    Tensor f(ShapeTag{}, {n}, DType::kFloat, DeviceType::kCUDA, false);
+    cuda_check(ctk_rand_uniform_f32(f.data<float>(), static_cast<int64_t>(n), g_rand_seed.load(), offset, t_stream), "rand");
+    cuda_check(ctk_cast_f32(CTK_DTYPE_F64, static_cast<const Tensor&>(f).data<float>(), data<double>(), static_cast<int64_t>(n), t_stream), "rand (double)");
+}
+
+// ---- to(DType) (src/Tensor.cpp:199-243) ---------------------------------------------------------------------
+Tensor Tensor::to(DType dtype) const {
+    if (_dtype == dtype) return *this;
+    const bool converts = _dtype == DType::kFloat && dtype != DType::kFloat;  // only float sources convert
+    Tensor result(ShapeTag{}, _shape, dtype, _device, !converts);
+    const size_t n = numel();
+    if (!converts || n == 0) return result;
+    const float* src = data<float>();
+    void* dst = result._storage.raw();
+    if (_device == DeviceType::kCUDA) {
+        cuda_check(ctk_cast_f32(static_cast<int>(dtype), src, dst, static_cast<int64_t>(n), t_stream), "to(dtype)");
+        return result;
+    }
+    for (size_t i = 0; i < n; ++i) {
+        switch (dtype) {
+            case DType::kDouble: static_cast<double*>(dst)[i] = static_cast<double>(src[i]); break;
+            case DType::kInt: static_cast<int32_t*>(dst)[i] = static_cast<int32_t>(src[i]); break;
+            case DType::kLong: static_cast<int64_t*>(dst)[i] = static_cast<int64_t>(src[i]); break;
+            default: static_cast<bool*>(dst)[i] = static_cast<bool>(src[i]); break;
+        }
+    }
+    return result;
+}
+
+// ---- operator[] (src/Tensor.cpp:175-189) --------------------------------------------------------------------
+Tensor Tensor::operator[](size_t index) const {
+    if (_shape.size() != 1) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DIMENSION, "operator[]: 1-D tensors only");
+    if (index >= _shape[0]) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DIMENSION, "operator[]: index out of range");
+    Tensor result(*this);
+    result._shape = {1};
+    result._strides = {0};
+    result._storage_offset += index * _strides[0];
+    return result;
+}
+
+void Tensor::copy_raw_to_host(void* dst, size_t nbytes) const {
+    if (nbytes != numel() * dtypeSize(_dtype)) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DIMENSION, "copy_raw_to_host: size mismatch");
+    if (nbytes == 0) return;
+    const unsigned char* base = static_cast<const unsigned char*>(_storage.raw()) + _storage_offset * dtypeSize(_dtype);
+    if (_device == DeviceType::kCUDA) {
+        cuda_check(ctk_memcpy_d2h(dst, base, nbytes, t_stream), "copy_raw_to_host");
+        cuda_check(t_stream ? ctk_stream_sync(t_stream) : ctk_device_sync(), "copy_raw_to_host sync");
+    } else {
+        std::memcpy(dst, base, nbytes);
+    }
+}
+
+// ---- comparisons (src/Tensor.cpp:985-1309, 1462-1591) -----------------------------------------------------------
+template <typename F>
+static void host_compare(const float* a, const float* b, float s, int form, bool* out, size_t n, F f) {
+    for (size_t i = 0; i < n; ++i) out[i] = form == CTK_CMP_TENSOR ? f(a[i], b[i]) : form == CTK_CMP_SCALAR_RIGHT ? f(a[i], s) : f(s, a[i]);
+}
+Tensor Tensor::compare(int cmp, int form, const Tensor* other, float s) const {
+    Tensor result(ShapeTag{}, _shape, DType::kBool, _device, _dtype != DType::kFloat);
+    if (form == CTK_CMP_TENSOR) {
+        if (!other) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::TENSOR_STATE, "comparison: missing operand");
+        if (_shape != other->shape()) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DIMENSION, "comparison: tensor shapes differ");
+        if (_dtype != other->dtype()) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DATATYPE, "comparison: tensor dtypes differ");
+        if (_device != other->device()) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DEVICE_COMPAT, "comparison: tensors are on different devices");
+    }
+    const size_t n = numel();
+    if (_dtype != DType::kFloat || n == 0) return result;  // the reference compares float tensors only
+    const float* a = data<float>();
+    const float* b = form == CTK_CMP_TENSOR ? other->data<float>() : nullptr;
+    if (_device == DeviceType::kCUDA) {
+        cuda_check(ctk_compare_f32(cmp, form, a, b, s, static_cast<unsigned char*>(result._storage.raw()), static_cast<int64_t>(n), t_stream), "comparison");
+        return result;
+    }
+    bool* out = static_cast<bool*>(result._storage.raw());
+    switch (cmp) {
+        case CTK_CMP_GT: host_compare(a, b, s, form, out, n, [](float x, float y) { return x > y; }); break;
+        case CTK_CMP_LT: host_compare(a, b, s, form, out, n, [](float x, float y) { return x < y; }); break;
+        case CTK_CMP_EQ: host_compare(a, b, s, form, out, n, [](float x, float y) { return x == y; }); break;
+        case CTK_CMP_GE: host_compare(a, b, s, form, out, n, [](float x, float y) { return x >= y; }); break;
+        case CTK_CMP_LE: host_compare(a, b, s, form, out, n, [](float x, float y) { return x <= y; }); break;
+        default: host_compare(a, b, s, form, out, n, [](float x, float y) { return x != y; }); break;
+    }
+    return result;
+}
+Tensor Tensor::operator>(float s) const { return compare(CTK_CMP_GT, CTK_CMP_SCALAR_RIGHT, nullptr, s); }
+Tensor Tensor::operator<(float s) const { return compare(CTK_CMP_LT, CTK_CMP_SCALAR_RIGHT, nullptr, s); }
+Tensor Tensor::operator==(float s) const { return compare(CTK_CMP_EQ, CTK_CMP_SCALAR_RIGHT, nullptr, s); }
+Tensor Tensor::operator>=(float s) const { return compare(CTK_CMP_GE, CTK_CMP_SCALAR_RIGHT, nullptr, s); }
+Tensor Tensor::operator<=(float s) const { return compare(CTK_CMP_LE, CTK_CMP_SCALAR_RIGHT, nullptr, s); }
+Tensor Tensor::operator!=(float s) const { return compare(CTK_CMP_NE, CTK_CMP_SCALAR_RIGHT, nullptr, s); }
+Tensor Tensor::operator>(const Tensor& o) const { return compare(CTK_CMP_GT, CTK_CMP_TENSOR, &o, 0.0f); }
+Tensor Tensor::operator<(const Tensor& o) const { return compare(CTK_CMP_LT, CTK_CMP_TENSOR, &o, 0.0f); }
+Tensor Tensor::operator==(const Tensor& o) const { return compare(CTK_CMP_EQ, CTK_CMP_TENSOR, &o, 0.0f); }
+Tensor Tensor::operator>=(const Tensor& o) const { return compare(CTK_CMP_GE, CTK_CMP_TENSOR, &o, 0.0f); }
+Tensor Tensor::operator<=(const Tensor& o) const { return compare(CTK_CMP_LE, CTK_CMP_TENSOR, &o, 0.0f); }
+Tensor Tensor::operator!=(const Tensor& o) const { return compare(CTK_CMP_NE, CTK_CMP_TENSOR, &o, 0.0f); }
+Tensor operator>(float s, const Tensor& t) { return t.compare(CTK_CMP_GT, CTK_CMP_SCALAR_LEFT, nullptr, s); }
+Tensor operator<(float s, const Tensor& t) { return t.compare(CTK_CMP_LT, CTK_CMP_SCALAR_LEFT, nullptr, s); }
+Tensor operator==(float s, const Tensor& t) { return t.compare(CTK_CMP_EQ, CTK_CMP_SCALAR_LEFT, nullptr, s); }
+Tensor operator>=(float s, const Tensor& t) { return t.compare(CTK_CMP_GE, CTK_CMP_SCALAR_LEFT, nullptr, s); }
+Tensor operator<=(float s, const Tensor& t) { return t.compare(CTK_CMP_LE, CTK_CMP_SCALAR_LEFT, nullptr, s); }
+Tensor operator!=(float s, const Tensor& t) { return t.compare(CTK_CMP_NE, CTK_CMP_SCALAR_LEFT, nullptr, s); }
 
 // ---- op wrappers ------------------------------------------------------------------------------------------
 void Tensor::record(Tensor& result, op o, std::vector<Tensor*> inputs, bool rg, int op_param) const {

@@ -90,7 +90,12 @@ public:
     void copy_from_host(const float* src, size_t count);
     void copy_to_host(float* dst, size_t count) const;
     std::vector<float> to_vector() const;
+    // numel() * dtypeSize bytes, in memory order from element [storage_offset] (any dtype).
+    void copy_raw_to_host(void* dst, size_t nbytes) const;
     Tensor to(DeviceType device) const;
+    // Conversion out of float (src/Tensor.cpp:199-243): same dtype -> a copy; float -> double / int /
+    // long / bool by static_cast per element; any other source leaves the zero-initialised result.
+    Tensor to(DType dtype) const;
     Tensor cuda() const { return to(DeviceType::kCUDA); }
     Tensor cpu() const { return to(DeviceType::kCPU); }
 
@@ -106,8 +111,15 @@ public:
     Tensor broadcast_to(const std::vector<size_t>& shape) const;
     Tensor contiguous() const;
     void zero();
-    void ones();
+    void ones();  // every dtype (src/Tensor.cpp:422-450)
     void fill(float v);
+    // Uniform [0, 1) for float and double tensors (src/Tensor.cpp:458-479).  The reference seeds a
+    // thread-local mt19937 from std::random_device; here a process-wide counter-based generator,
+    // seeded the same way unless manual_seed() fixed the seed.
+    void rand();
+    static void manual_seed(uint64_t seed);
+    // Element `index` of a 1-D tensor as a view of shape {1} (src/Tensor.cpp:175-189).
+    Tensor operator[](size_t index) const;
 
     // ---- math (dispatched + recorded) ----
     Tensor matmul(const Tensor& other) const;
@@ -140,6 +152,23 @@ public:
     Tensor operator+(float s) const;
     Tensor operator*(float s) const;
     Tensor operator/(float s) const;
+    // Element-wise comparisons -> kBool tensors of this shape (src/Tensor.cpp:985-1309).  As in the
+    // reference the elements are taken in memory order, the two-tensor forms throw on a shape or
+    // dtype mismatch, and a non-float tensor compares to all-false.
+    Tensor operator>(float s) const;
+    Tensor operator<(float s) const;
+    Tensor operator==(float s) const;
+    Tensor operator>=(float s) const;
+    Tensor operator<=(float s) const;
+    Tensor operator!=(float s) const;
+    Tensor operator>(const Tensor& other) const;
+    Tensor operator<(const Tensor& other) const;
+    Tensor operator==(const Tensor& other) const;
+    Tensor operator>=(const Tensor& other) const;
+    Tensor operator<=(const Tensor& other) const;
+    Tensor operator!=(const Tensor& other) const;
+    // cmp: CTK_CMP_*; form: CTK_CMP_TENSOR (other), CTK_CMP_SCALAR_RIGHT (this cmp s), CTK_CMP_SCALAR_LEFT (s cmp this)
+    Tensor compare(int cmp, int form, const Tensor* other, float s) const;
     void backward() const;
 
     // In-place p -= g*lr on this tensor's device: the SGD loop that user code writes on raw host
@@ -157,6 +186,13 @@ Tensor operator+(float s, const Tensor& t);
 Tensor operator-(float s, const Tensor& t);
 Tensor operator*(float s, const Tensor& t);
 Tensor operator/(float s, const Tensor& t);
+// scalar cmp tensor (src/Tensor.cpp:1462-1591)
+Tensor operator>(float s, const Tensor& t);
+Tensor operator<(float s, const Tensor& t);
+Tensor operator==(float s, const Tensor& t);
+Tensor operator>=(float s, const Tensor& t);
+Tensor operator<=(float s, const Tensor& t);
+Tensor operator!=(float s, const Tensor& t);
 
 // Stream every kernel and copy of this thread's tensors is issued on (NULL = legacy default stream).
 void* current_stream();

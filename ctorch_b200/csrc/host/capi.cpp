@@ -530,6 +530,38 @@ int cth_tensor_fill(void* t, float v) {
     return guarded([&] { T(t)->fill(v); });
 }
 
+// ---- dtype-aware additions: comparisons, to(DType), ones, rand, operator[] ----
+int cth_tensor_empty(const int64_t* shape, int rank, int dtype, int device, void** out) {
+    return guarded([&] {
+        std::vector<size_t> s(shape, shape + rank);
+        *out = new Tensor(ShapeTag{}, s, static_cast<DType>(dtype), static_cast<DeviceType>(device), true);
+    });
+}
+int cth_tensor_dtype(void* t, int* dtype) {
+    return guarded([&] { *dtype = static_cast<int>(T(t)->dtype()); });
+}
+int cth_tensor_read_raw(void* t, void* dst, uint64_t nbytes) {
+    return guarded([&] { T(t)->copy_raw_to_host(dst, static_cast<size_t>(nbytes)); });
+}
+int cth_tensor_compare(void* a, void* b_or_null, float scalar, int cmp, int form, void** out) {
+    return guarded([&] { *out = new Tensor(T(a)->compare(cmp, form, b_or_null ? T(b_or_null) : nullptr, scalar)); });
+}
+int cth_tensor_to_dtype(void* t, int dtype, void** out) {
+    return guarded([&] { *out = new Tensor(T(t)->to(static_cast<DType>(dtype))); });
+}
+int cth_tensor_ones(void* t) {
+    return guarded([&] { T(t)->ones(); });
+}
+int cth_tensor_rand(void* t) {
+    return guarded([&] { T(t)->rand(); });
+}
+int cth_manual_seed(uint64_t seed) {
+    return guarded([&] { Tensor::manual_seed(seed); });
+}
+int cth_tensor_index(void* t, uint64_t index, void** out) {
+    return guarded([&] { *out = new Tensor((*T(t))[static_cast<size_t>(index)]); });
+}
+
 // ---- ops (the reference's Tensor methods / operators) ----
 // op codes: values of `enum class op`; Sum = 21, Softmax = 14 (param = dim), Neg = 2.
 int cth_unary(void* t, int opc, int param, void** out) {

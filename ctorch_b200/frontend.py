@@ -32,6 +32,14 @@ def set_quiet(q=True):
     lib.cth_set_quiet(1 if q else 0)
 
 
+FLOAT, DOUBLE, INT, LONG, BOOL = 0, 1, 2, 3, 4          # enum class DType
+NP_DTYPES = {0: np.float32, 1: np.float64, 2: np.int32, 3: np.int64, 4: np.bool_}
+
+
+def manual_seed(seed):
+    _chk(lib.cth_manual_seed(ctypes.c_uint64(seed)))
+
+
 class Tensor:
     def __init__(self, handle):
         self.h = handle
@@ -74,10 +82,66 @@ class Tensor:
     def shape(self):
         return self.info()["shape"]
 
+    @property
+    def dtype(self):
+        d = ctypes.c_int()
+        _chk(lib.cth_tensor_dtype(self.h, ctypes.byref(d)))
+        return d.value
+
     def numpy(self):
-        out = np.empty(self.shape, np.float32)
-        _chk(lib.cth_tensor_to_host(self.h, out.ctypes.data_as(_vp)))
+        dt = self.dtype
+        if dt == FLOAT:
+            out = np.empty(self.shape, np.float32)
+            _chk(lib.cth_tensor_to_host(self.h, out.ctypes.data_as(_vp)))
+            return out
+        out = np.empty(self.shape, NP_DTYPES[dt])      # other dtypes: memory order
+        _chk(lib.cth_tensor_read_raw(self.h, out.ctypes.data_as(_vp), ctypes.c_uint64(out.nbytes)))
         return out
+
+    @staticmethod
+    def empty(shape, dtype=0, device=CUDA):
+        s = np.asarray(shape, dtype=np.int64)
+        h = _vp()
+        _chk(lib.cth_tensor_empty(s.ctypes.data_as(_vp), len(shape), dtype, device, ctypes.byref(h)))
+        return Tensor(h)
+
+    def _cmp(self, cmp, other, scalar_left=False):
+        h = _vp()
+        if isinstance(other, Tensor):
+            _chk(lib.cth_tensor_compare(self.h, other.h, ctypes.c_float(0), cmp, 0, ctypes.byref(h)))
+        else:
+            _chk(lib.cth_tensor_compare(self.h, None, ctypes.c_float(other), cmp, 2 if scalar_left else 1, ctypes.byref(h)))
+        return Tensor(h)
+
+    def __gt__(self, o): return self._cmp(0, o)
+    def __lt__(self, o): return self._cmp(1, o)
+    def __eq__(self, o): return self._cmp(2, o)
+    def __ge__(self, o): return self._cmp(3, o)
+    def __le__(self, o): return self._cmp(4, o)
+    def __ne__(self, o): return self._cmp(5, o)
+    __hash__ = object.__hash__
+
+    def scalar_cmp(self, cmp, s):
+        """s cmp self: the free operators with the scalar on the left."""
+        return self._cmp(cmp, s, scalar_left=True)
+
+    def to_dtype(self, dtype):
+        h = _vp()
+        _chk(lib.cth_tensor_to_dtype(self.h, dtype, ctypes.byref(h)))
+        return Tensor(h)
+
+    def ones(self):
+        _chk(lib.cth_tensor_ones(self.h))
+        return self
+
+    def rand(self):
+        _chk(lib.cth_tensor_rand(self.h))
+        return self
+
+    def __getitem__(self, i):
+        h = _vp()
+        _chk(lib.cth_tensor_index(self.h, ctypes.c_uint64(i), ctypes.byref(h)))
+        return Tensor(h)
 
     def item(self):
         v = ctypes.c_float()

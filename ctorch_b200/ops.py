@@ -208,6 +208,39 @@ def sgd_update_split(p, g, lr, stream=None):
     return flat[pad:pad + outer * inner].reshape(outer, inner), flat[pad + outer * inner:pad + 2 * outer * inner].reshape(outer, inner)
 
 
+CMP = {"gt": 0, "lt": 1, "eq": 2, "ge": 3, "le": 4, "ne": 5}
+CMP_TENSOR, CMP_SCALAR_RIGHT, CMP_SCALAR_LEFT = 0, 1, 2
+DTYPES = {0: np.float32, 1: np.float64, 2: np.int32, 3: np.int64, 4: np.uint8}   # DType values; bool as bytes
+
+
+def compare(cmp, a, other, scalar_left=False, stream=None):
+    """a cmp other (other a DeviceArray or a float), or other cmp a when scalar_left; bytes 0/1."""
+    out = DeviceArray(a.shape, np.uint8)
+    if isinstance(other, DeviceArray):
+        check(lib.ctk_compare_f32(CMP[cmp], CMP_TENSOR, a.p, other.p, _f(0.0), out.p, _i64(a.size), _sh(stream)))
+    else:
+        form = CMP_SCALAR_LEFT if scalar_left else CMP_SCALAR_RIGHT
+        check(lib.ctk_compare_f32(CMP[cmp], form, a.p, None, _f(other), out.p, _i64(a.size), _sh(stream)))
+    return out
+
+
+def cast(a, dtype_code, stream=None):
+    out = DeviceArray(a.shape, DTYPES[dtype_code])
+    check(lib.ctk_cast_f32(int(dtype_code), a.p, out.p, _i64(a.size), _sh(stream)))
+    return out
+
+
+def fill_dtype(out, dtype_code, value, stream=None):
+    check(lib.ctk_fill_dtype(int(dtype_code), out.p, ctypes.c_double(value), _i64(out.size), _sh(stream)))
+    return out
+
+
+def rand_uniform(shape, seed, offset=0, out=None, stream=None):
+    out = out or DeviceArray(shape)
+    check(lib.ctk_rand_uniform_f32(out.p, _i64(out.size), ctypes.c_uint64(seed), ctypes.c_uint64(offset), _sh(stream)))
+    return out
+
+
 def matmul_path(a, b, ta=False, tb=False, mode=-1):
     mode = MODES.get(mode, mode)
     m, k = (a.shape[1], a.shape[0]) if ta else a.shape

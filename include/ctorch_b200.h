@@ -152,6 +152,30 @@ ctk_status ctk_u8_to_f32(const uint8_t* src, int64_t n, float divisor, float* ds
  * the labels they are compared with. */
 ctk_status ctk_argmax_rows_f32(const float* x, int64_t rows, int64_t cols, float init, float* out_index, void* stream);
 
+/* ---- comparisons, dtype conversion, typed fill, random numbers -------------------------------- */
+enum { CTK_CMP_GT = 0, CTK_CMP_LT = 1, CTK_CMP_EQ = 2, CTK_CMP_GE = 3, CTK_CMP_LE = 4, CTK_CMP_NE = 5 };
+enum { CTK_CMP_TENSOR = 0, CTK_CMP_SCALAR_RIGHT = 1, CTK_CMP_SCALAR_LEFT = 2 };
+/* the values of the reference's `enum class DType` (include/Ctools.h:163-169) */
+enum { CTK_DTYPE_F32 = 0, CTK_DTYPE_F64 = 1, CTK_DTYPE_I32 = 2, CTK_DTYPE_I64 = 3, CTK_DTYPE_BOOL = 4 };
+
+/* out[i] = a[i] cmp b[i] (form TENSOR: Tensor::operator>, <, ==, >=, <=, != on two tensors,
+ * src/Tensor.cpp:1119-1309), a[i] cmp scalar (SCALAR_RIGHT: the float forms, :985-1116) or
+ * scalar cmp a[i] (SCALAR_LEFT: the free operators, :1462-1591), as bytes 0/1 -- the reference's
+ * kBool tensors.  IEEE comparisons: anything against NaN is false except !=. */
+ctk_status ctk_compare_f32(int cmp, int form, const float* a, const float* b, float scalar,
+                           unsigned char* out, int64_t n, void* stream);
+/* dst[i] = static_cast<T>(src[i]) for T = double, int32_t, int64_t, bool: Tensor::to(DType) out of
+ * float (src/Tensor.cpp:199-243).  Integers truncate toward zero; values outside the target's range and
+ * NaN are undefined behaviour in the reference (x86 yields INT_MIN) and saturate / give 0 here. */
+ctk_status ctk_cast_f32(int dtype, const float* src, void* dst, int64_t n, void* stream);
+/* dst[i] = value converted to the dtype: Tensor::ones / zero for every dtype (src/Tensor.cpp:390-450). */
+ctk_status ctk_fill_dtype(int dtype, void* dst, double value, int64_t n, void* stream);
+/* dst[i] = uniform in [0, 1): Tensor::rand (src/Tensor.cpp:458-479).  The reference draws from a
+ * thread-local mt19937 seeded by std::random_device, so no sequence of it can be reproduced; here
+ * element i is a pure function of (seed, offset + i) -- a counter-based generator (one splitmix64
+ * finaliser per pair of counters, 24 bits of it each), identical for any launch shape, never 1.0. */
+ctk_status ctk_rand_uniform_f32(float* dst, int64_t n, uint64_t seed, uint64_t offset, void* stream);
+
 /* out = number of i with (int)a[i] == (int)b[i] (as a float): the comparison of predicted and true
  * labels of mnist/mnist.cpp:150-153.  Exact up to 2^24 matches. */
 ctk_status ctk_count_matches_f32(const float* a, const float* b, int64_t n, float* out, void* scratch, void* stream);

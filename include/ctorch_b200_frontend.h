@@ -49,6 +49,21 @@ int cth_binary(void* a, void* b, int op, void** out);
 int cth_scalar(void* tensor, float s, int kind, void** out);
 
 /* ---- AutoDiff (include/AutoDiff.h) ---- */
+/* Dtype-aware part of the Tensor API.  dtype: the values of `enum class DType` (include/Ctools.h:163-169:
+ * 0 float, 1 double, 2 int32, 3 int64, 4 bool). */
+int cth_tensor_empty(const int64_t* shape, int rank, int dtype, int device, void** out); /* zero-initialised, Tensor(ShapeTag, ...) include/Tensor.h:280-296 */
+int cth_tensor_dtype(void* tensor, int* dtype);
+int cth_tensor_read_raw(void* tensor, void* dst, uint64_t nbytes);   /* numel * sizeof(dtype) bytes in memory order */
+/* Tensor::operator>, <, ==, >=, <=, != (src/Tensor.cpp:985-1309) and the scalar-on-the-left free
+ * operators (:1462-1591): cmp = CTK_CMP_*, form = CTK_CMP_TENSOR (b given), CTK_CMP_SCALAR_RIGHT
+ * (a cmp scalar) or CTK_CMP_SCALAR_LEFT (scalar cmp a); the result is a kBool tensor. */
+int cth_tensor_compare(void* a, void* b_or_null, float scalar, int cmp, int form, void** out);
+int cth_tensor_to_dtype(void* tensor, int dtype, void** out);        /* Tensor::to(DType), src/Tensor.cpp:199-243 */
+int cth_tensor_ones(void* tensor);                                   /* Tensor::ones, src/Tensor.cpp:422-450 */
+int cth_tensor_rand(void* tensor);                                   /* Tensor::rand, src/Tensor.cpp:458-479 */
+int cth_manual_seed(uint64_t seed);                                  /* no counterpart: fixes rand's seed and restarts its counter */
+int cth_tensor_index(void* tensor, uint64_t index, void** out);      /* Tensor::operator[], src/Tensor.cpp:175-189 */
+
 int cth_ctx_create(void** ctx);
 int cth_ctx_destroy(void* ctx);
 int cth_ctx_set_current(void* ctx_or_null);           /* AutoDiffContext::current() of the calling thread */

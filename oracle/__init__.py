@@ -101,6 +101,48 @@ def idx_read_labels(path):
     return np.frombuffer(raw[8:8 + n], np.uint8).astype(np.float32)
 
 
+# ---- comparisons, dtype conversion, operator[] (plain numpy: byte / integer work) -----------------------
+CMP_NAMES = ("gt", "lt", "eq", "ge", "le", "ne")
+_CMP_FUN = dict(gt=np.greater, lt=np.less, eq=np.equal, ge=np.greater_equal, le=np.less_equal, ne=np.not_equal)
+NP_OF_DTYPE = {0: np.float32, 1: np.float64, 2: np.int32, 3: np.int64, 4: np.bool_}
+
+
+def compare(cmp, a, other, scalar_left=False):
+    """Tensor::operator>, <, ==, >=, <=, != (src/Tensor.cpp:985-1309) and the free operators with the
+    scalar on the left (:1462-1591): element by element in memory order, IEEE comparisons, a kBool
+    result of a's shape.  `other` is an array of a's shape or a float."""
+    a = _f32(a)
+    f = _CMP_FUN[cmp]
+    if isinstance(other, np.ndarray):
+        if other.shape != a.shape:
+            raise ValueError("tensor shapes differ")        # :1124-1126 throws
+        return f(a, _f32(other))
+    s = np.float32(other)
+    return f(s, a) if scalar_left else f(a, s)
+
+
+def cast_from_float(a, dtype_code):
+    """Tensor::to(DType) out of float (src/Tensor.cpp:199-243): static_cast per element -- exact to
+    double, truncation toward zero to int32 / int64 (inside the target's range; outside it the
+    reference's behaviour is undefined), != 0 to bool."""
+    a = _f32(a)
+    if dtype_code in (2, 3):
+        return np.trunc(a).astype(NP_OF_DTYPE[dtype_code])
+    if dtype_code == 4:
+        return a != 0
+    return a.astype(NP_OF_DTYPE[dtype_code])
+
+
+def index_1d(a, i):
+    """Tensor::operator[] (src/Tensor.cpp:175-189): 1-D only, range-checked, a view of one element."""
+    a = _f32(a)
+    if a.ndim != 1:
+        raise ValueError("1-D tensors only")
+    if not 0 <= i < a.shape[0]:
+        raise IndexError("index out of range")
+    return a[i:i + 1]
+
+
 def predicted_labels(probs):
     """The prediction loop of calculate_accuracy (mnist/mnist.cpp:140-147): per row the first class whose
     probability exceeds -1 and every earlier one (NaN never does); 0 if none."""
@@ -321,6 +363,37 @@ class Reference(Oracle):
         dx = np.empty_like(x)
         self._chk(self.L.ref_softmax_dim(_fp(x), s[1], s[2], int(dim), _fp(out), _fp(g), _fp(dx)))
         return out, dx
+
+    def compare(self, cmp, a, other, scalar_left=False):
+        """The reference's comparison operators; bool array of a's shape."""
+        a = _f32(a)
+        s = _shape(a)
+        out = np.empty(a.shape, np.uint8)
+        c = CMP_NAMES.index(cmp)
+        if isinstance(other, np.ndarray):
+            b = _f32(other)
+            self._chk(self.L.ref_compare(c, 0, _fp(a), _fp(b), ctypes.c_float(0), s[1], s[2], out.ctypes.data_as(ctypes.c_void_p)))
+        else:
+            self._chk(self.L.ref_compare(c, 2 if scalar_left else 1, _fp(a), None, ctypes.c_float(other), s[1], s[2], out.ctypes.data_as(ctypes.c_void_p)))
+        return out.astype(np.bool_)
+
+    def cast_from_float(self, a, dtype_code):
+        """The reference's Tensor::to(DType) on a 1-D float tensor."""
+        a = _f32(a).ravel()
+        out = np.empty(a.size, np.uint8 if dtype_code == 4 else NP_OF_DTYPE[dtype_code])
+        self._chk(self.L.ref_cast(int(dtype_code), _fp(a), ctypes.c_int64(a.size), out.ctypes.data_as(ctypes.c_void_p)))
+        return out.astype(np.bool_) if dtype_code == 4 else out
+
+    def index_1d(self, a, i):
+        a = _f32(a)
+        v = ctypes.c_float()
+        self._chk(self.L.ref_index(_fp(a), ctypes.c_int64(a.size), ctypes.c_int64(i), ctypes.byref(v)))
+        return np.float32(v.value)
+
+    def ones(self, dtype_code, n):
+        out = np.empty(n, np.float64)
+        self._chk(self.L.ref_ones(int(dtype_code), ctypes.c_int64(n), out.ctypes.data_as(ctypes.c_void_p)))
+        return out
 
     def mnist_load(self, directory, test=False):
         """The reference's own MNISTLoader on `directory`: (images [n, rows*cols], labels [n])."""

@@ -378,4 +378,92 @@ int ref_mnist_load(const char* dir, int test, float* images, int64_t cap_images,
     });
 }
 
+// The comparison operators of the reference (src/Tensor.cpp:985-1309 members, 1462-1591 free
+// functions): cmp 0 >, 1 <, 2 ==, 3 >=, 4 <=, 5 !=; form 0 tensor ? tensor, 1 tensor ? scalar,
+// 2 scalar ? tensor.  out: numel bytes of the kBool result.
+int ref_compare(int cmp, int form, const float* a, const float* b, float s, const int64_t* shape, int rank, unsigned char* out) {
+    return guarded([&] {
+        Tensor A = make(a, shape, rank);
+        Tensor R;
+        if (form == 0) {
+            Tensor B = make(b, shape, rank);
+            switch (cmp) {
+                case 0: R = A > B; break;
+                case 1: R = A < B; break;
+                case 2: R = A == B; break;
+                case 3: R = A >= B; break;
+                case 4: R = A <= B; break;
+                default: R = A != B; break;
+            }
+        } else if (form == 1) {
+            switch (cmp) {
+                case 0: R = A > s; break;
+                case 1: R = A < s; break;
+                case 2: R = A == s; break;
+                case 3: R = A >= s; break;
+                case 4: R = A <= s; break;
+                default: R = A != s; break;
+            }
+        } else {
+            switch (cmp) {
+                case 0: R = s > A; break;
+                case 1: R = s < A; break;
+                case 2: R = s == A; break;
+                case 3: R = s >= A; break;
+                case 4: R = s <= A; break;
+                default: R = s != A; break;
+            }
+        }
+        // (Tensor::data<bool>() does not link: the library instantiates checkDType for the four numeric
+        // types only, src/Tensor.cpp:1605-1608.  Storage::data is a header template.)
+        const bool* r = R.storage().data<bool>();
+        for (size_t i = 0; i < R.numel(); ++i) out[i] = r[i] ? 1 : 0;
+    });
+}
+
+// Tensor::to(DType) of the reference (src/Tensor.cpp:199-243) out of a float tensor; dtype 1 double,
+// 2 int32, 3 int64, 4 bool.  out: numel elements of the target type.
+int ref_cast(int dtype, const float* a, int64_t n, void* out) {
+    return guarded([&] {
+        int64_t shape[1] = {n};
+        Tensor A = make(a, shape, 1);
+        Tensor R = A.to(static_cast<DType>(dtype));
+        switch (dtype) {
+            case 1: std::memcpy(out, R.data<double>(), n * sizeof(double)); break;
+            case 2: std::memcpy(out, R.data<int32_t>(), n * sizeof(int32_t)); break;
+            case 3: std::memcpy(out, R.data<int64_t>(), n * sizeof(int64_t)); break;
+            default: {
+                const bool* r = R.storage().data<bool>();
+                for (int64_t i = 0; i < n; ++i) static_cast<unsigned char*>(out)[i] = r[i] ? 1 : 0;
+            }
+        }
+    });
+}
+
+// Tensor::operator[] (src/Tensor.cpp:175-189) on a 1-D tensor, read back through item().
+int ref_index(const float* a, int64_t n, int64_t index, float* out) {
+    return guarded([&] {
+        int64_t shape[1] = {n};
+        Tensor A = make(a, shape, 1);
+        *out = A[static_cast<size_t>(index)].item<float>();
+    });
+}
+
+// Tensor::ones (src/Tensor.cpp:422-450) on a tensor of the given dtype, returned as doubles.
+int ref_ones(int dtype, int64_t n, double* out) {
+    return guarded([&] {
+        Tensor A(ShapeTag{}, std::vector<size_t>{static_cast<size_t>(n)}, static_cast<DType>(dtype), DeviceType::kCPU);
+        A.ones();
+        for (int64_t i = 0; i < n; ++i) {
+            switch (dtype) {
+                case 0: out[i] = A.data<float>()[i]; break;
+                case 1: out[i] = A.data<double>()[i]; break;
+                case 2: out[i] = A.data<int32_t>()[i]; break;
+                case 3: out[i] = static_cast<double>(A.data<int64_t>()[i]); break;
+                default: out[i] = A.storage().data<bool>()[i] ? 1.0 : 0.0; break;
+            }
+        }
+    });
+}
+
 }  // extern "C"

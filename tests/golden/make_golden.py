@@ -140,6 +140,26 @@ def main():
     G["mnist.probs"] = probs
     G["mnist.pred"] = oracle.predicted_labels(probs)
     G["mnist.accuracy"] = np.asarray(oracle.accuracy(probs, lb), np.float32)
+    # ---- comparisons, Tensor::to(DType), operator[], ones (src/Tensor.cpp:985-1309, 1462-1591, 199-243, 175-189, 422-450)
+    rng = np.random.default_rng(77)
+    ca = rng.integers(-3, 4, (37, 21)).astype(np.float32)
+    cb_ = rng.integers(-3, 4, (37, 21)).astype(np.float32)
+    ca[0, :4] = [np.nan, np.inf, -np.inf, -0.0]
+    cb_[0, :4] = [1.0, np.inf, np.inf, 0.0]
+    cb_[1, 0] = np.nan
+    G["cmp.a"], G["cmp.b"], G["cmp.s"] = ca, cb_, np.asarray(1.0, np.float32)
+    for c in oracle.CMP_NAMES:
+        G[f"cmp.{c}.tt"] = R.compare(c, ca, cb_)
+        G[f"cmp.{c}.ts"] = R.compare(c, ca, 1.0)
+        G[f"cmp.{c}.st"] = R.compare(c, ca, 1.0, scalar_left=True)
+    x = (rng.standard_normal(1003) * 1000).astype(np.float32)
+    x[:8] = [0.0, -0.0, 0.5, -0.5, 0.99999994, -1.5, 16777216.0, -2147483648.0]
+    G["cast.x"] = x
+    for d in (1, 2, 3, 4):
+        G[f"cast.{d}"] = R.cast_from_float(x, d)
+    G["index.values"] = np.asarray([R.index_1d(x, i) for i in (0, 2, 1002)], np.float32)
+    for d in range(5):
+        G[f"ones.{d}"] = R.ones(d, 5)
     out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden.npz")
     np.savez_compressed(out, **G)
     print("wrote", out, os.path.getsize(out), "bytes,", len(G), "arrays")
