@@ -317,14 +317,17 @@ def run_mlp(args, cp):
                      serial_value=BATCH * world / (ms_e2e_serial / args.steps * 1e-3), serial_ms_per_step=ms_e2e_serial / args.steps,
                      serial_call="cth_mlp_step_host: upload, step and loss read-back in sequence"),
             gpu_launches=int(launches),
-            roofline=dict(bound="tensor", achieved=achieved, peak=peak, unit="TFLOP/s", frac=achieved / peak if peak else None, traffic=None,
+            roofline=dict(bound="tensor", achieved=achieved, peak=peak, unit="TFLOP/s", frac=achieved / peak if peak else None,
+                          # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant shape (8192 x 4096 x 4096, forward with
+                          # its fused epilogue), from the ncu capture summarised in profiles/tcgen05_matmul_pair_3xtf32_fused_epilogues_8192x4096x4096.md
+                          traffic=1.503e9 + 0.362e9, traffic_launch="forward 8192x4096x4096 + bias + ReLU + split (algorithmic: 402 MB of operand splits read, 402 MB written)",
                           kernel="tcgen05_matmul_pair_kernel / tcgen05_matmul_kernel (3xTF32)", launches=int(n), avg_launch_ms=tms / n if n else None,
                           peak_source=f"{peaks['source']}: {bf16_key} {bf16_val} / 2 (TF32 runs at half the bf16 rate; no TF32 figure was measured) / 3 (three TF32 products per fp32 product); algorithmic flops 2*M*N*K",
                           step_model_flops=flops_step, step_tflops=flops_step / (per_step * 1e-3) / 1e12,
                           # context for a fraction above 1: the measured ceiling is cuBLAS bf16 (73 % of the nominal 2250) scaled
                           # to TF32; against the nominal dense TF32 rate (1125 TFLOP/s, a third of it per fp32 product):
                           nominal_peak=375.0, frac_of_nominal=achieved / 375.0,
-                          tensor_pipe_active="97.5 % of active SM cycles (ncu, profiles/tcgen05_matmul_pair_3xtf32_4096.md)"),
+                          tensor_pipe_active="97.0 % of active and 91.5 % of elapsed SM cycles (ncu, profiles/tcgen05_matmul_pair_3xtf32_fused_epilogues_8192x4096x4096.md)"),
             cpu_baseline=cpu,
         )
         print(json.dumps(out))
@@ -570,7 +573,7 @@ def run_mnist_app(cb, args, rng):
 
 def run_one_kernel(cb, case, rng):
     """A few launches of ONE kernel on a small case (inputs larger than L2, a few hundred MB on the
-    device): the command profiler captures are taken from.  Cases: matmul_<mode>_<m>x<k>x<n>[_dA|_dB],
+    device): the command profiler captures are taken from.  Cases: matmul_<mode>_<m>x<k>x<n>[_dA|_dB|_fwdfused|_dAfused],
     add_<log2n>, relu_<log2n>, sum_<log2n>, softmax_<rows>x<cols>, ce_<rows>x<cols>."""
     parts = case.split("_")
     kind = parts[0]
@@ -584,7 +587,14 @@ def run_one_kernel(cb, case, rng):
         outs = dict(fwd=cb.empty((m, n)), dA=cb.empty((m, k)), dB=cb.empty((k, n)))
         fn = dict(fwd=lambda: cb.ops.matmul(A, B, mode=mode, out=outs["fwd"], workspace=ws),
                   dA=lambda: cb.ops.matmul(dC, B, tb=True, mode=mode, out=outs["dA"], workspace=ws),
-                  dB=lambda: cb.ops.matmul(A, dC, ta=True, mode=mode, out=outs["dB"], workspace=ws))[which]
+                  dB=lambda: cb.ops.matmul(A, dC, ta=True, mode=mode, out=outs["dB"], workspace=ws)).get(which)
+        if which in ("fwdfused", "dAfused"):
+            # the products of the training step with their epilogues: forward + bias + ReLU + split of the
+            # result; dX = dC.B^T with the ReLU-backward mask + split of the result
+            bias = cb.to_device(rng.standard_normal(n).astype(np.float32))
+            act = cb.to_device(np.maximum(rng.standard_normal((m, k)), 0).astype(np.float32))
+            fn = (lambda: cb.ops.matmul_fused(A, B, bias=bias, relu=True, want_split=False, keep_split=True)) if which == "fwdfused" else \
+                 (lambda: cb.ops.matmul_fused(dC, B, mask=act, tb=True, keep_split=True))
         work, unit = 2.0 * m * n * k, "TFLOP/s"
     elif kind in ("add", "relu", "sum"):
         n = 1 << int(parts[1])

@@ -173,18 +173,26 @@ def matmul(a, b, ta=False, tb=False, mode=-1, out=None, workspace=None, stream=N
     return out
 
 
-def matmul_fused(a, b, bias=None, relu=False, mask=None, want_split=False, ta=False, tb=False, stream=None):
+_fused_cache = {}
+
+
+def matmul_fused(a, b, bias=None, relu=False, mask=None, want_split=False, ta=False, tb=False, stream=None, keep_split=False):
     """[relu](a.b + bias) * (mask > 0), the epilogue forms of the 3xTF32 product in one launch.
-    Returns (c, c_hi, c_lo) when want_split (the split the epilogue wrote, as [m, n] arrays), else c."""
+    Returns (c, c_hi, c_lo) when want_split (the split the epilogue wrote, as [m, n] arrays), else c.
+    keep_split: write the split too, into buffers (and c) reused from call to call, and do not read it back."""
     m, k = (a.shape[1], a.shape[0]) if ta else a.shape
     n = b.shape[0] if tb else b.shape[1]
     sa = (1, m) if ta else (k, 1)
     sb = (1, k) if tb else (n, 1)
-    out = DeviceArray((m, n))
     split = None
-    if want_split:
-        nbytes = int(lib.ctk_matmul_split_bytes(m, n))
-        split = DeviceArray((nbytes // 4,))
+    if keep_split:
+        if (m, n) not in _fused_cache:
+            _fused_cache[(m, n)] = (DeviceArray((m, n)), DeviceArray((int(lib.ctk_matmul_split_bytes(m, n)) // 4,)))
+        out, split = _fused_cache[(m, n)]
+    else:
+        out = DeviceArray((m, n))
+        if want_split:
+            split = DeviceArray((int(lib.ctk_matmul_split_bytes(m, n)) // 4,))
     check(lib.ctk_matmul_3xtf32_fused_f32(a.p, b.p, out.p, _i64(m), _i64(n), _i64(k), _i64(sa[0]), _i64(sa[1]), _i64(sb[0]), _i64(sb[1]),
                                           None, None, None, None, bias.p if bias else None, int(bool(relu)), mask.p if mask else None,
                                           split.p if split else None, None, _sh(stream)))
