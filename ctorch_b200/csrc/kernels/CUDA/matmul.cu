@@ -32,7 +32,10 @@
 // operands TMA cannot address in place, and on request (mode FP32_SIMT).
 #include <cuda.h>
 #include <math.h>
+#include <cstdlib>
 
+#include <unordered_map>
+#include <atomic>
 #include <mutex>
 #include <vector>
 
@@ -222,6 +225,9 @@ struct Params {
     float* c;
     int vec_store;    // n % 4 == 0 and c 16-byte aligned
     int whole_tiles;  // tiles [0, whole_tiles) are computed whole; each later tile as two K-halves
+    // CTA-pair kernel, dynamic unit order: {next, done} counters (both 0 between launches), or NULL for
+    // the static order (pair i takes units i, i + pairs, ...).
+    unsigned int* sched;
     // Epilogue of the fused forms (all optional; whole tiles only): c = [relu](acc + bias[col]), then
     // c *= (mask > 0 ? 1 : 0) with mask an [m, n] array of pitch n (ReLU's backward rule applied to a
     // gradient product), and the hi/lo split of c written next to it ([m, split_pitch] each) for the
@@ -642,6 +648,12 @@ namespace pair {
 
 constexpr int BN = 256;     // tile width of the pair
 constexpr int BN_CTA = 128; // columns of B each CTA stages
+// Dynamic unit order: rank 0's producer draws the pair's next unit from a global counter and publishes
+// it in a ring of SCHED_SLOTS entries kept in both CTAs; the ten other roles that walk the units (rank
+// 0: MMA issuer, 4 epilogue warps; rank 1: producer, 4 epilogue warps) read it there.  The producer is
+// never more than three units ahead of the slowest role (one in the stage ring, two accumulators).
+constexpr int SCHED_SLOTS = 8;
+constexpr int SCHED_READERS = 10;
 
 template <int TERMS>
 struct Cfg {
@@ -673,6 +685,25 @@ __device__ __forceinline__ void cluster_sync_all() {
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Bounded wait that also orders this thread after the (possibly remote) arrivals' earlier writes.
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((i & 255u) == 255u) {
+            if (*abort_flag) return false;
+            __nanosleep(64);
+        }
+    }
+    *abort_flag = 1;
+    atomicCAS(&g_tc_status, 0, code);
+    return false;
 }
 __device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
     asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
@@ -722,6 +753,8 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
     using C = Cfg<TERMS>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bars[2 * 8 + 4];  // full[8], empty[8], tmem_full[2], tmem_empty[2]
+    __shared__ uint64_t sbars[2 * SCHED_SLOTS];  // dynamic order: slot published [SCHED_SLOTS], slot read by all (rank 0's) [SCHED_SLOTS]
+    __shared__ volatile uint32_t sched_unit[SCHED_SLOTS];
     __shared__ uint32_t tmem_base_slot;
     __shared__ __align__(16) EpilogueStage stages[4];  // one per epilogue warp
     __shared__ volatile int abort_flag;
@@ -736,12 +769,16 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
     auto a_addr = [&](int s, int part) { return smem_base + s * C::STAGE_BYTES + part * C::A_BYTES; };
     auto b_addr = [&](int s, int part) { return smem_base + s * C::STAGE_BYTES + C::PARTS * C::A_BYTES + part * C::B_BYTES; };
     const uint32_t peer_abort = map_to_cta(smem_u32(const_cast<int*>(&abort_flag)), rank ^ 1u);
+    const uint32_t sbar0 = smem_u32(sbars);
+    auto spub_bar = [&](int i) { return sbar0 + 8u * i; };
+    auto sread_bar = [&](int i) { return sbar0 + 8u * (SCHED_SLOTS + i); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 8); }
+        for (int i = 0; i < SCHED_SLOTS; ++i) { mbar_init(spub_bar(i), 1); mbar_init(sread_bar(i), SCHED_READERS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         prefetch_tmap(&map_a_hi);
         prefetch_tmap(&map_b_hi);
@@ -759,6 +796,31 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
 
     const int num_units = unit_count(P);
     const int first_unit = blockIdx.x >> 1, unit_step = gridDim.x >> 1;
+    const bool dynamic = P.sched != nullptr;
+    // Unit number `seq` of this pair, for every role but rank 0's producer (one lane calls this).
+    // Static order: first_unit + seq * unit_step.  Dynamic order: what rank 0's producer published.
+    auto unit_at = [&](uint32_t seq, int& u) -> bool {
+        if (!dynamic) {
+            const int64_t v = static_cast<int64_t>(first_unit) + static_cast<int64_t>(seq) * unit_step;
+            u = v < num_units ? static_cast<int>(v) : num_units;
+            return true;
+        }
+        const uint32_t slot = seq % SCHED_SLOTS, par = (seq / SCHED_SLOTS) & 1u;
+        if (!mbar_wait_cluster(spub_bar(slot), par, &abort_flag, 0x900 | slot)) return false;
+        u = static_cast<int>(sched_unit[slot]);
+        mbar_arrive_cluster(map_to_cta(sread_bar(slot), 0));
+        return true;
+    };
+    // rank 0's producer: unit `u` becomes number `seq` in both CTAs' rings.
+    auto publish = [&](uint32_t seq, int u) -> bool {
+        const uint32_t slot = seq % SCHED_SLOTS, par = (seq / SCHED_SLOTS) & 1u;
+        if (seq >= SCHED_SLOTS && !mbar_wait_cluster(sread_bar(slot), par ^ 1u, &abort_flag, 0x980 | slot)) return false;
+        sched_unit[slot] = static_cast<uint32_t>(u);
+        st_cluster_u32(map_to_cta(smem_u32(const_cast<uint32_t*>(&sched_unit[slot])), 1), static_cast<uint32_t>(u));
+        mbar_arrive_cluster(map_to_cta(spub_bar(slot), 0));
+        mbar_arrive_cluster(map_to_cta(spub_bar(slot), 1));
+        return true;
+    };
 
     if (warp == 0) {
         // ------------------------------ TMA producer (both CTAs) ------------------------------
@@ -767,7 +829,15 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
             uint32_t phase = 0;
             uint32_t issued = 0;
             bool ok = true;
-            for (int u = first_unit; u < num_units && ok; u += unit_step) {
+            const bool scheduler = dynamic && rank == 0;
+            int u = first_unit < num_units ? first_unit : num_units;
+            for (uint32_t seq = 0; ok; ++seq) {
+                unsigned int drawn = 0;
+                if (scheduler) {
+                    if (!publish(seq, u)) { ok = false; break; }
+                    if (u < num_units) drawn = atomicAdd(P.sched, 1u);  // the next unit, asked for now, needed after this unit's loads
+                } else if (!unit_at(seq, u)) { ok = false; break; }
+                if (u >= num_units) break;
                 const Unit U = unit_of(u, P);
                 const int m0 = (U.tile / P.tiles_n) * (2 * BM) + static_cast<int>(rank) * BM;
                 const int n0 = (U.tile % P.tiles_n) * BN + static_cast<int>(rank) * BN_CTA;
@@ -796,6 +866,10 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
                     ++issued;
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                 }
+                if (scheduler) {
+                    const unsigned int nxt = drawn + static_cast<unsigned int>(unit_step);
+                    u = nxt < static_cast<unsigned int>(num_units) ? static_cast<int>(nxt) : num_units;
+                }
             }
             if (ok) {
                 // Tail: every stage this CTA filled has been released, i.e. the MMAs that read it are
@@ -822,7 +896,10 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int u = first_unit; u < num_units && ok; u += unit_step) {
+            for (uint32_t seq = 0; ok; ++seq) {
+                int u;
+                if (!unit_at(seq, u)) { ok = false; break; }
+                if (u >= num_units) break;
                 const Unit U = unit_of(u, P);
                 if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, &abort_flag, 0x600 | (18 + acc))) { ok = false; break; }
                 tc_fence_after();
@@ -866,7 +943,13 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
-        for (int u = first_unit; u < num_units && ok; u += unit_step) {
+        for (uint32_t seq = 0; ok; ++seq) {
+            int u = 0, got = 1;
+            if (lane == 0) got = unit_at(seq, u) ? 1 : 0;
+            got = __shfl_sync(0xffffffffu, got, 0);
+            u = __shfl_sync(0xffffffffu, u, 0);
+            if (!got) { ok = false; break; }
+            if (u >= num_units) break;
             const Unit U = unit_of(u, P);
             const int64_t m0 = static_cast<int64_t>(U.tile / P.tiles_n) * (2 * BM) + static_cast<int64_t>(rank) * BM;
             const int64_t n0 = static_cast<int64_t>(U.tile % P.tiles_n) * BN;
@@ -896,6 +979,15 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc2(tmem_base, C::TMEM_COLS);
+    }
+    if (dynamic && rank == 0 && threadIdx.x == 0) {
+        // This pair has drawn its last unit (thread 0 is the lane that draws).  The pair that finishes
+        // last puts both counters back to zero for the next launch on this stream.
+        __threadfence();
+        if (atomicAdd(P.sched + 1, 1u) == static_cast<unsigned int>(unit_step) - 1u) {
+            atomicExch(P.sched, 0u);
+            atomicExch(P.sched + 1, 0u);
+        }
     }
 }
 
@@ -1108,6 +1200,52 @@ bool classify(const float* p, int64_t mn, int64_t k, int64_t s_mn, int64_t s_k, 
 int g_default_mode = CTK_MATMUL_3XTF32;
 int g_pairing = 0;  // 0: CTA pairs where the shape allows, 1: single-CTA kernel only
 int g_split_tail = 1;  // 1: K-halves for the tiles of a last wave that fills at most half the machine
+// 1: CTA pairs draw their units from a counter, 0: fixed assignment (CTORCH_MATMUL_FIXED_ORDER=1 in the
+// environment starts a process with 0)
+int g_dynamic_order = [] {
+    const char* e = std::getenv("CTORCH_MATMUL_FIXED_ORDER");
+    return (e && e[0] == '1') ? 0 : 1;
+}();
+
+// {next, done} counters of the pair kernel's dynamic unit order: one pair of words per stream (launches
+// on one stream follow one another, and each launch leaves its words at zero), zeroed when the block is
+// allocated and again after a launch that gave up on a wait.
+constexpr int kSchedStreams = 512;
+struct SchedBlock {
+    unsigned int* words = nullptr;
+    std::unordered_map<cudaStream_t, int> index;
+};
+SchedBlock g_sched[64];
+std::mutex g_sched_mu;
+std::atomic<bool> g_sched_dirty{false};
+
+ctk_status sched_words(cudaStream_t st, unsigned int** out) {
+    *out = nullptr;
+    int dev = 0;
+    CTK_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return CTK_OK;
+    std::lock_guard<std::mutex> lock(g_sched_mu);
+    SchedBlock& b = g_sched[dev];
+    if (!b.words) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        CTK_CUDA(cudaStreamIsCapturing(st, &cap));
+        if (cap != cudaStreamCaptureStatusNone) return CTK_OK;  // no allocation inside a capture: fixed order
+        CTK_CUDA(cudaMalloc(&b.words, kSchedStreams * 2 * sizeof(unsigned int)));
+        CTK_CUDA(cudaMemset(b.words, 0, kSchedStreams * 2 * sizeof(unsigned int)));
+    }
+    if (g_sched_dirty.exchange(false)) {
+        CTK_CUDA(cudaDeviceSynchronize());
+        for (int d = 0; d < 64; ++d)
+            if (g_sched[d].words && d == dev) CTK_CUDA(cudaMemset(g_sched[d].words, 0, kSchedStreams * 2 * sizeof(unsigned int)));
+    }
+    auto it = b.index.find(st);
+    if (it == b.index.end()) {
+        if (b.index.size() >= static_cast<size_t>(kSchedStreams)) return CTK_OK;  // fixed order for further streams
+        it = b.index.emplace(st, static_cast<int>(b.index.size())).first;
+    }
+    *out = b.words + 2 * it->second;
+    return CTK_OK;
+}
 
 // ---- optional per-launch timing of the tensor-core kernel ----
 struct TcProfile {
@@ -1208,6 +1346,12 @@ ctk_status ctk_set_matmul_tail_split(int on) {
     return CTK_OK;
 }
 
+ctk_status ctk_set_matmul_dynamic_order(int on) {
+    CTK_REQUIRE(on == 0 || on == 1, "ctk_set_matmul_dynamic_order: 0 or 1");
+    g_dynamic_order = on;
+    return CTK_OK;
+}
+
 ctk_status ctk_set_matmul_pairing(int pairing) {
     CTK_REQUIRE(pairing == 0 || pairing == 1, "ctk_set_matmul_pairing: 0 (CTA pairs where possible) or 1 (single-CTA kernel only)");
     g_pairing = pairing;
@@ -1281,6 +1425,7 @@ ctk_status ctk_matmul_status(int* status) {
     CTK_REQUIRE(status, "ctk_matmul_status: null");
     CTK_CUDA(cudaDeviceSynchronize());
     CTK_CUDA(cudaMemcpyFromSymbol(status, g_tc_status, sizeof(int)));
+    if (*status != 0) g_sched_dirty.store(true);  // a launch that gave up may have left its unit counters non-zero
     return CTK_OK;
 }
 
@@ -1298,6 +1443,7 @@ struct FusedEpilogue {
     int relu = 0;
     const float* mask = nullptr;
     void* c_split = nullptr;
+    bool fixed_order = false;  // never the dynamic unit order (whose counters are allocated on first use)
 };
 
 static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k, int64_t sa0,
@@ -1410,6 +1556,8 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
         int workers = ctk::sm_count();
         if (paired && (rc = tc::resident_pairs(&workers))) return rc;
         P.whole_tiles = tiles;
+        P.sched = nullptr;
+        if (paired && g_dynamic_order && !fe.fixed_order && (rc = sched_words(st, &P.sched))) return rc;
         const int tail = tiles % workers;
         if (g_split_tail && !fused && P.num_kb >= 16 && tail > 0 && 2 * tail <= workers) {  // (a fused epilogue needs the whole sum)
             P.whole_tiles = tiles - tail;
@@ -1529,7 +1677,9 @@ ctk_status ctk_matmul_3xtf32_noalloc_f32(const float* a, const float* b, float* 
     void* ws = nullptr;
     ctk_status rc = static_workspace(&ws);
     if (rc) return rc;
-    return ctk_matmul_f32(a, b, c, m, n, k, sa0, sa1, sb0, sb1, CTK_MATMUL_3XTF32, ws, stream);
+    FusedEpilogue opts;
+    opts.fixed_order = true;  // the dynamic order's counters would be allocated on first use
+    return matmul_impl(a, b, c, m, n, k, sa0, sa1, sb0, sb1, CTK_MATMUL_3XTF32, ws, KeptSplit{nullptr, nullptr}, KeptSplit{nullptr, nullptr}, stream, opts);
 }
 
 }  // extern "C"

@@ -282,6 +282,11 @@ ctk_status ctk_set_matmul_pairing(int pairing);
 /* tiles is computed as two halves of K that are added into the zeroed output (two addends: the    */
 /* result does not depend on their order).  0: every tile whole.                                   */
 ctk_status ctk_set_matmul_tail_split(int on);
+/* 1 (default): the CTA pairs of the pair kernel draw their output tiles from a counter as they go, so a */
+/* pair that starts late or runs slowly -- its SMs were held by another kernel, a collective's for      */
+/* instance -- takes fewer tiles instead of stretching the product by its whole fixed share.  0: pair i  */
+/* takes tiles i, i + pairs, ...  The result does not depend on the choice.                             */
+ctk_status ctk_set_matmul_dynamic_order(int on);
 /* Self-test of the kernels' bounded waits (no counterpart in the reference): one CTA waits with a  */
 /* short limit on a barrier nothing arrives on.  result = {first wait ok (expected 0), CTA abort     */
 /* flag (1), second waiter ok (0: it leaves as soon as it sees the flag), status word (0x7e57)}.    */
