@@ -261,7 +261,10 @@ Tensor AutoDiff::check_and_adjust_grad_shape(const Tensor& grad, const std::vect
     bool prefix = grad.is_contiguous();
     for (size_t i = 1; i <= target_rank && prefix; ++i) prefix = grad.sizes()[grad_rank - i] == target_shape[target_rank - i];
     if (prefix) {
-        cuda_check(ctk_memcpy_d2d(result.data<float>(), dev_ptr(grad), static_cast<size_t>(n) * sizeof(float), st), "grad gather");
+        if (exact_broadcast_grad)  // opt-in: the sum over the broadcast rows instead of row 0
+            cuda_check(ctk_colsum_f32(dev_ptr(grad), static_cast<int64_t>(grad.numel()) / n, n, result.data<float>(), st), "grad column sum");
+        else
+            cuda_check(ctk_memcpy_d2d(result.data<float>(), dev_ptr(grad), static_cast<size_t>(n) * sizeof(float), st), "grad gather");
         return result;
     }
     if (target_rank > 8) Ctorch_Error::throwException(ErrorPlatform::kAutoDiff, ErrorType::DIMENSION, "gradient shape adjustment: rank > 8");

@@ -68,6 +68,7 @@ class AutoDiff {
     std::mutex records_mutex;
     bool retain_graph = false;
     bool fuse_relu_backward = false;
+    bool exact_broadcast_grad = false;
     std::unordered_map<size_t, int> consumers;  // per tensor id, within the backward pass that is running
 
     Node* get_node_by_id(size_t id);
@@ -105,6 +106,10 @@ public:
     // ReLU output itself is then the masked gradient (the reference: the unmasked one), which is why
     // this is off unless asked for.
     void set_fuse_relu_backward(bool on) { fuse_relu_backward = on; }
+    // The gradient of an operand that was broadcast over leading dimensions ([H] in [N,H] + [H]) is, in
+    // the reference, the FIRST row of the upstream gradient (:690-757).  on: the sum over the broadcast
+    // rows, which is the derivative.  Off by default: it changes results away from the reference's.
+    void set_exact_broadcast_grad(bool on) { exact_broadcast_grad = on; }
     size_t node_count();
     // In-place access to a leaf's gradient buffer (nullptr if none).
     Tensor* grad_buffer(const Tensor& t);

@@ -249,6 +249,7 @@ public:
     DeviceType device() const { return _device; }
     bool empty() const { return _size == 0 || !_data; }
     bool has_split() const { return _data && _data->split; }
+    void drop_split() const { if (_data) _data->split.reset(); }
     void clear() { _data.reset(); _size = 0; }
     bool unique() const { return !_data || _data.use_count() == 1; }
 

@@ -791,6 +791,26 @@ void Tensor::backward() const {
     if (AutoDiffContext::current()) AutoDiffContext::current()->backward(const_cast<Tensor&>(*this));
 }
 
+void Tensor::sgd_update_shared_(const Tensor& g, float lr) {
+    if (g.numel() != numel()) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DIMENSION, "sgd_update_shared_: gradient has a different size");
+    if (_device != DeviceType::kCUDA || g.device() != DeviceType::kCUDA || _dtype != DType::kFloat)
+        Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DEVICE_COMPAT, "sgd_update_shared_: float device tensors expected");
+    float* p = static_cast<float*>(_storage.raw()) + _storage_offset;  // no detach: the sharers are meant to see it
+    const bool resplit = _storage.has_split() && _shape.size() == 2 && is_contiguous() && g.is_contiguous() && _shape[1] % 4 == 0 &&
+                         _storage_offset % 4 == 0 && g.storage_offset() % 4 == 0;
+    if (resplit) {
+        const int64_t outer = static_cast<int64_t>(_shape[0]), inner = static_cast<int64_t>(_shape[1]);
+        KeptSplit* ks = _storage.kept_split(static_cast<int64_t>(_storage_offset), outer, inner, inner, ctk_matmul_split_bytes(inner, outer));
+        if (ks) {
+            cuda_check(ctk_sgd_update_split_f32(p, g.data<float>(), lr, outer, inner, inner, ks->buf, t_stream), "sgd_update_shared_ (with split)");
+            ks->valid = 1;
+            return;
+        }
+    }
+    _storage.drop_split();  // a split of the old values, if any, is stale now
+    cuda_check(ctk_sgd_update_f32(p, g.data<float>(), lr, static_cast<int64_t>(numel()), t_stream), "sgd_update_shared_");
+}
+
 void Tensor::sgd_update_(const Tensor& g, float lr) {
     if (g.numel() != numel()) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DIMENSION, "sgd_update_: gradient has a different size");
     if (_device != DeviceType::kCUDA || g.device() != DeviceType::kCUDA)

@@ -174,6 +174,11 @@ public:
     // In-place p -= g*lr on this tensor's device: the SGD loop that user code writes on raw host
     // pointers in the reference (mnist/mnist.cpp:80-92).
     void sgd_update_(const Tensor& g, float lr);
+    // The same update written THROUGH to every tensor that shares this buffer -- in particular the copy
+    // the tape took when the parameter was registered, which the reference's backward keeps reading
+    // while the live weights move on (src/AutoDiff.cpp:286-290, :1651).  With this form backward sees
+    // the updated weights.  Opt-in, no counterpart in the reference.
+    void sgd_update_shared_(const Tensor& g, float lr);
 
     friend class AutoDiff;
 };

@@ -59,6 +59,7 @@ public:
     size_t pinned_x_bytes = 0;
     Tensor last_logits;
     bool keep_logits = false;
+    bool fresh_weights = false;  // corrected mode: backward reads the updated weights
     uint64_t steps_done = 0;
     // Input staging: up to two uploaded batches wait on the device, each with an event that says
     // its copy has landed, so the upload of batch k+1 (on its own stream) overlaps step k.
@@ -103,6 +104,20 @@ public:
         for (Staged& s : staged)
             if (s.ready) ctk_event_destroy(s.ready);
         if (copy_stream) ctk_stream_destroy(copy_stream);
+    }
+
+    // Opt-in departure from the reference's arithmetic (no counterpart there): bias gradients summed over
+    // the batch instead of taken from row 0, and backward products against the current weights instead
+    // of the copy the tape took at registration.  Switching fresh_weights on forgets the tape, so that the
+    // next step registers the parameters again and their copies share the live buffers from then on.
+    void set_corrected(bool exact_bias_grad, bool fresh) {
+        release_graph();
+        ctx.set_exact_broadcast_grad(exact_bias_grad);
+        if (fresh != fresh_weights) {
+            cuda_check(ctk_device_sync(), "set_corrected sync");
+            ctx.clear_graph();
+            fresh_weights = fresh;
+        }
     }
 
     int64_t n_params() const {
@@ -190,8 +205,13 @@ public:
             cuda_check(ctk_stream_wait_event(st, ev_comm), "wait");
         }
         for (size_t l = 0; l < W.size(); ++l) {
-            W[l].sgd_update_(grad(W[l]), lr);
-            b[l].sgd_update_(grad(b[l]), lr);
+            if (fresh_weights) {
+                W[l].sgd_update_shared_(grad(W[l]), lr);
+                b[l].sgd_update_shared_(grad(b[l]), lr);
+            } else {
+                W[l].sgd_update_(grad(W[l]), lr);
+                b[l].sgd_update_(grad(b[l]), lr);
+            }
         }
         if (keep_logits) last_logits = logits;
         if (!capturing) cuda_check(st ? ctk_stream_sync(st) : ctk_device_sync(), "step sync");
@@ -682,6 +702,9 @@ int cth_mlp_destroy(void* m) {
 }
 int cth_mlp_set_comm(void* m, void* comm) {
     return guarded([&] { static_cast<MlpTrainer*>(m)->set_comm(comm); });
+}
+int cth_mlp_set_corrected(void* m, int exact_bias_grad, int fresh_weights) {
+    return guarded([&] { static_cast<MlpTrainer*>(m)->set_corrected(exact_bias_grad != 0, fresh_weights != 0); });
 }
 int cth_mlp_keep_logits(void* m, int keep) {
     return guarded([&] { static_cast<MlpTrainer*>(m)->keep_logits = keep != 0; });

@@ -1200,11 +1200,13 @@ bool classify(const float* p, int64_t mn, int64_t k, int64_t s_mn, int64_t s_k, 
 int g_default_mode = CTK_MATMUL_3XTF32;
 int g_pairing = 0;  // 0: CTA pairs where the shape allows, 1: single-CTA kernel only
 int g_split_tail = 1;  // 1: K-halves for the tiles of a last wave that fills at most half the machine
-// 1: CTA pairs draw their units from a counter, 0: fixed assignment (CTORCH_MATMUL_FIXED_ORDER=1 in the
-// environment starts a process with 0)
+// 0 (default): pair i takes units i, i + pairs, ...; 1: CTA pairs draw their units from a counter
+// (CTORCH_MATMUL_DYNAMIC_ORDER=1 in the environment starts a process with 1).  Measured on B200: no
+// difference on one GPU, and 1-2 % SLOWER steps with 2 and 8 GPUs while NCCL's kernels share the SMs,
+// which is why it is not the default.
 int g_dynamic_order = [] {
-    const char* e = std::getenv("CTORCH_MATMUL_FIXED_ORDER");
-    return (e && e[0] == '1') ? 0 : 1;
+    const char* e = std::getenv("CTORCH_MATMUL_DYNAMIC_ORDER");
+    return (e && e[0] == '1') ? 1 : 0;
 }();
 
 // {next, done} counters of the pair kernel's dynamic unit order: one pair of words per stream (launches

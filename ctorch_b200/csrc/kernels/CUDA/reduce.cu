@@ -117,6 +117,56 @@ ctk_status launch_reduce(const char* name, const float* a, const float* b, int64
     return CTK_OK;
 }
 
+// ---- column sums: out[j] = sum over rows of x[r, j] -------------------------------------------------------
+// Pass 1: a CTA owns 256 rows x 128 columns; warp w adds rows w, w + 8, ... (one 128-bit load per lane
+// and row, 512 contiguous bytes per warp), the eight warps add up through shared memory in fixed order,
+// and the CTA writes one row of partial sums.  Pass 2 adds the partial rows in order.  No atomics: the
+// result is the same from call to call.
+constexpr int kColRows = 256, kColWarps = 8;
+__global__ void __launch_bounds__(kColWarps * 32) colsum_partial_kernel(const float* __restrict__ x, int64_t rows, int64_t cols, float* __restrict__ part) {
+    __shared__ float4 acc_sm[kColWarps][32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t col = (static_cast<int64_t>(blockIdx.x) * 32 + lane) * 4;
+    const int64_t r0 = static_cast<int64_t>(blockIdx.y) * kColRows;
+    const int64_t r1 = r0 + kColRows < rows ? r0 + kColRows : rows;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (col < cols) {
+        if (col + 4 <= cols && (cols & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0) {
+#pragma unroll 4
+            for (int64_t r = r0 + warp; r < r1; r += kColWarps) {
+                const float4 v = __ldcs(reinterpret_cast<const float4*>(x + r * cols + col));
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+        } else {
+            for (int64_t r = r0 + warp; r < r1; r += kColWarps) {
+                const float* p = x + r * cols + col;
+                acc.x += p[0];
+                if (col + 1 < cols) acc.y += p[1];
+                if (col + 2 < cols) acc.z += p[2];
+                if (col + 3 < cols) acc.w += p[3];
+            }
+        }
+    }
+    acc_sm[warp][lane] = acc;
+    __syncthreads();
+    if (warp == 0 && col < cols) {
+        float4 t = acc_sm[0][lane];
+        for (int w = 1; w < kColWarps; ++w) { const float4 v = acc_sm[w][lane]; t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w; }
+        float* o = part + static_cast<int64_t>(blockIdx.y) * cols + col;
+        o[0] = t.x;
+        if (col + 1 < cols) o[1] = t.y;
+        if (col + 2 < cols) o[2] = t.z;
+        if (col + 3 < cols) o[3] = t.w;
+    }
+}
+__global__ void __launch_bounds__(256) colsum_final_kernel(const float* __restrict__ part, int64_t chunks, int64_t cols, float* __restrict__ out) {
+    const int64_t j = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (j >= cols) return;
+    float t = 0.f;
+    for (int64_t c = 0; c < chunks; ++c) t += part[c * cols + j];
+    out[j] = t;
+}
+
 }  // namespace
 
 extern "C" {
@@ -136,6 +186,27 @@ ctk_status ctk_mse_f32(const float* a, const float* b, int64_t n, float* out, vo
 ctk_status ctk_mae_f32(const float* a, const float* b, int64_t n, float* out, void* scratch, void* stream) {
     CTK_REQUIRE(n > 0, "ctk_mae_f32: empty input");
     return launch_reduce<R_MAE>("mae", a, b, n, static_cast<float>(n), out, scratch, stream);
+}
+
+ctk_status ctk_colsum_f32(const float* x, int64_t rows, int64_t cols, float* out, void* stream) {
+    CTK_REQUIRE(rows >= 0 && cols >= 0, "ctk_colsum_f32: negative shape");
+    if (cols == 0) return CTK_OK;
+    CTK_REQUIRE(out && (x || rows == 0), "ctk_colsum_f32: null pointer");
+    cudaStream_t st = ctk::as_stream(stream);
+    const int64_t chunks = (rows + kColRows - 1) / kColRows;
+    if (chunks == 0) {
+        CTK_CUDA(cudaMemsetAsync(out, 0, static_cast<size_t>(cols) * sizeof(float), st));
+        return CTK_OK;
+    }
+    CTK_REQUIRE(chunks <= 65535, "ctk_colsum_f32: more than 65535 x 256 rows");
+    float* part = nullptr;
+    CTK_CUDA(cudaMallocAsync(reinterpret_cast<void**>(&part), static_cast<size_t>(chunks * cols) * sizeof(float), st));
+    colsum_partial_kernel<<<dim3(static_cast<unsigned>((cols + 127) / 128), static_cast<unsigned>(chunks)), kColWarps * 32, 0, st>>>(x, rows, cols, part);
+    CTK_LAUNCH_CHECK("colsum_partial_kernel");
+    colsum_final_kernel<<<static_cast<unsigned>((cols + 255) / 256), 256, 0, st>>>(part, chunks, cols, out);
+    CTK_LAUNCH_CHECK("colsum_final_kernel");
+    CTK_CUDA(cudaFreeAsync(part, st));
+    return CTK_OK;
 }
 
 ctk_status ctk_count_matches_f32(const float* a, const float* b, int64_t n, float* out, void* scratch, void* stream) {

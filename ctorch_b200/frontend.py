@@ -300,6 +300,10 @@ class MlpTrainer:
     def set_comm(self, comm_handle):
         _chk(lib.cth_mlp_set_comm(self.h, comm_handle))
 
+    def set_corrected(self, exact_bias_grad=True, fresh_weights=True):
+        """Opt-in: true bias gradients and backward against the current weights (not the reference's arithmetic)."""
+        _chk(lib.cth_mlp_set_corrected(self.h, 1 if exact_bias_grad else 0, 1 if fresh_weights else 0))
+
     def keep_logits(self, keep=True):
         _chk(lib.cth_mlp_keep_logits(self.h, 1 if keep else 0))
 

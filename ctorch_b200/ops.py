@@ -272,6 +272,13 @@ def argmax_rows(x, init=float("-inf")):
     return out
 
 
+def colsum(x):
+    r, c = _rc(x)
+    out = DeviceArray((c,))
+    check(lib.ctk_colsum_f32(x.p, _i64(r), _i64(c), out.p, None))
+    return out
+
+
 def count_matches(a, b):
     out = _scalar_out()
     check(lib.ctk_count_matches_f32(a.p, b.p, _i64(a.size), out.p, None, None))

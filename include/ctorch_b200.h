@@ -176,6 +176,12 @@ ctk_status ctk_fill_dtype(int dtype, void* dst, double value, int64_t n, void* s
  * finaliser per pair of counters, 24 bits of it each), identical for any launch shape, never 1.0. */
 ctk_status ctk_rand_uniform_f32(float* dst, int64_t n, uint64_t seed, uint64_t offset, void* stream);
 
+/* out[j] = sum over r of x[r, j] for a contiguous [rows, cols] array.  No counterpart in the reference,
+ * whose gradient of a broadcast [H] operand is row 0 of the upstream gradient (src/AutoDiff.cpp:690-757);
+ * this is the sum an opt-in "exact broadcast gradient" mode uses instead.  Two passes in fixed order:
+ * the same bits from call to call. */
+ctk_status ctk_colsum_f32(const float* x, int64_t rows, int64_t cols, float* out, void* stream);
+
 /* out = number of i with (int)a[i] == (int)b[i] (as a float): the comparison of predicted and true
  * labels of mnist/mnist.cpp:150-153.  Exact up to 2^24 matches. */
 ctk_status ctk_count_matches_f32(const float* a, const float* b, int64_t n, float* out, void* scratch, void* stream);
@@ -282,10 +288,9 @@ ctk_status ctk_set_matmul_pairing(int pairing);
 /* tiles is computed as two halves of K that are added into the zeroed output (two addends: the    */
 /* result does not depend on their order).  0: every tile whole.                                   */
 ctk_status ctk_set_matmul_tail_split(int on);
-/* 1 (default): the CTA pairs of the pair kernel draw their output tiles from a counter as they go, so a */
-/* pair that starts late or runs slowly -- its SMs were held by another kernel, a collective's for      */
-/* instance -- takes fewer tiles instead of stretching the product by its whole fixed share.  0: pair i  */
-/* takes tiles i, i + pairs, ...  The result does not depend on the choice.                             */
+/* 0 (default): pair i of the pair kernel takes tiles i, i + pairs, ...  1: the pairs draw their tiles  */
+/* from a counter as they go, so that a pair which starts late takes fewer.  The result does not depend */
+/* on the choice.  Measured: equal on one GPU, 1-2 % slower steps under a concurrent all-reduce.        */
 ctk_status ctk_set_matmul_dynamic_order(int on);
 /* Self-test of the kernels' bounded waits (no counterpart in the reference): one CTA waits with a  */
 /* short limit on a barrier nothing arrives on.  result = {first wait ok (expected 0), CTA abort     */

@@ -94,6 +94,12 @@ int cth_mlp_destroy(void* mlp);
  * communicator), started per gradient while backward is still running.  NULL switches it off. */
 int cth_mlp_set_comm(void* mlp, void* comm);
 int cth_mlp_keep_logits(void* mlp, int keep);
+/* No counterpart: an opt-in mode that leaves the reference's arithmetic on purpose.  exact_bias_grad: the
+ * gradient of a bias is the sum of the upstream gradient over the batch (the reference: its first row,
+ * src/AutoDiff.cpp:690-757).  fresh_weights: backward multiplies by the current weights (the reference: by
+ * the copy taken when the parameter was first registered, src/AutoDiff.cpp:286-290).  Both 0 by default;
+ * every parity test runs with both 0. */
+int cth_mlp_set_corrected(void* mlp, int exact_bias_grad, int fresh_weights);
 /* x_host [batch, dims[0]] and labels_host [batch] (class indices as floats) in HOST memory. */
 int cth_mlp_step_host(void* mlp, const float* x_host, const float* labels_host, int64_t batch, float* loss);
 /* The same step with the upload taken off the critical path, as an input pipeline would run it:

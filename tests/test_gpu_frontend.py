@@ -574,3 +574,68 @@ def test_relu_backward_fusion_is_skipped_when_the_activation_has_two_readers(F, 
             out[fused] = [F.grad(t).numpy() for t in (X, W, W2, W3, B)] + [F.grad(h).numpy()]
     for a, c in zip(out[False], out[True]):
         assert_exact(c, a, "two readers: nothing changes")
+
+
+@pytest.mark.parametrize("rows,cols", [(8192, 4096), (130, 132), (257, 10), (1, 5), (3000, 1)])
+def test_column_sum_kernel(cb, rows, cols):
+    rng = np.random.default_rng(rows + cols)
+    x = rng.standard_normal((rows, cols)).astype(np.float32)
+    d = cb.to_device(x)
+    got = cb.ops.colsum(d).numpy()
+    assert_close(got, x.astype(np.float64).sum(axis=0), 1e-5, 1e-4, "column sums")
+    assert_exact(cb.ops.colsum(d).numpy(), got, "fixed order: the same bits again")
+
+
+def _textbook_mlp_steps(Ws, bs, xs, labels, lr):
+    """Plain SGD on a ReLU MLP with cross entropy SUMMED over the batch, in float64: bias gradients
+    summed over the batch, backward against the current weights."""
+    Ws, bs = [w.astype(np.float64) for w in Ws], [b.astype(np.float64) for b in bs]
+    losses = []
+    for x, lab in zip(xs, labels):
+        hs = [x.astype(np.float64)]
+        for l, (W, b) in enumerate(zip(Ws, bs)):
+            z = hs[-1] @ W + b
+            hs.append(np.maximum(z, 0) if l + 1 < len(Ws) else z)
+        z = hs[-1]
+        p = np.exp(z - z.max(axis=1, keepdims=True))
+        p /= p.sum(axis=1, keepdims=True)
+        idx = lab.astype(int)
+        losses.append(-np.log(np.maximum(p[np.arange(len(idx)), idx], 1e-10)).sum())
+        g = p.copy()
+        g[np.arange(len(idx)), idx] -= 1
+        for l in range(len(Ws) - 1, -1, -1):
+            dW, db = hs[l].T @ g, g.sum(axis=0)
+            if l > 0:
+                g = (g @ Ws[l].T) * (hs[l] > 0)
+            Ws[l] -= lr * dW
+            bs[l] -= lr * db
+    return np.asarray(losses), np.concatenate([np.concatenate([W.ravel(), b]) for W, b in zip(Ws, bs)])
+
+
+def test_corrected_mode_is_textbook_sgd(F, cb):
+    """set_corrected(exact_bias_grad, fresh_weights): an opt-in mode outside the reference's arithmetic.
+    With both on the trainer follows plain SGD (float64 numpy) to 1e-4; with both off (the default, the
+    reference's arithmetic) it does not: the first-row bias gradient and the stale backward weights are
+    real differences."""
+    dims, batch, steps, lr = [20, 64, 32, 8], 48, 5, 0.01 / 48
+    rng = np.random.default_rng(8)
+    Ws = [(rng.standard_normal((i, j)) / np.sqrt(i)).astype(np.float32) for i, j in zip(dims[:-1], dims[1:])]
+    bs = [rng.uniform(-0.1, 0.1, j).astype(np.float32) for j in dims[1:]]
+    p0 = np.concatenate([np.concatenate([W.ravel(), b]) for W, b in zip(Ws, bs)])
+    xs = [rng.standard_normal((batch, dims[0])).astype(np.float32) for _ in range(steps)]
+    labs = [rng.integers(0, dims[-1], batch).astype(np.float32) for _ in range(steps)]
+    want_loss, want_p = _textbook_mlp_steps(Ws, bs, xs, labs, lr)
+    tr = F.MlpTrainer(dims, p0, lr)
+    tr.set_corrected(True, True)
+    got = [tr.step_host(x, l) for x, l in zip(xs, labs)]
+    assert_close(np.asarray(got, np.float64), want_loss, 1e-4, 0, "losses, corrected mode")
+    assert_matmul_close(tr.params(), want_p, 1e-4, "weights, corrected mode")
+    plain = F.MlpTrainer(dims, p0, lr)
+    for x, l in zip(xs, labs):
+        plain.step_host(x, l)
+    dev_plain = np.abs(plain.params() - want_p).max()
+    dev_corr = np.abs(tr.params() - want_p).max()
+    assert dev_plain > 100 * max(dev_corr, 1e-9), "the default mode keeps the reference's arithmetic"
+    # switching it off again returns to the reference's arithmetic from the current weights on
+    tr.set_corrected(False, False)
+    tr.step_host(xs[0], labs[0])

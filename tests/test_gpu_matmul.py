@@ -311,5 +311,5 @@ def test_dynamic_unit_order_equals_fixed_order(cb, mode, m, k, n, ta, tb):
         for i in range(4):
             assert_exact(cb.ops.matmul(dA, dB, ta, tb, mode).numpy(), fixed, f"dynamic order, call {i}")
     finally:
-        cb.ops.set_matmul_dynamic_order(1)
+        cb.ops.set_matmul_dynamic_order(0)
     _check_status(cb)
