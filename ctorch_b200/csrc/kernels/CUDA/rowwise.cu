@@ -535,7 +535,10 @@ __global__ void __launch_bounds__(kTileThreads) tile_rows_kernel(RowArgs A, Redu
     __shared__ double red_d[33];
     __shared__ __align__(8) uint64_t full[2];
     __shared__ volatile int gave_up;
-    const int cols = static_cast<int>(A.cols);
+    // MAXC = 10 is instantiated for exactly ten columns (the 10-class rows of the MNIST-shaped models):
+    // the column count is then a constant, and the per-element "k < cols" tests and row address
+    // multiplications fold away -- the kernel was bound by instruction issue, not by HBM, at this width.
+    const int cols = (MAXC == 10) ? 10 : static_cast<int>(A.cols);
     constexpr int kOperands = alg_two_operands<ALG>() ? 2 : 1;
     const int buf_floats = kTileRows * cols * kOperands;
     const uint32_t tile_bytes = static_cast<uint32_t>(kTileRows * cols * sizeof(float));
@@ -1137,6 +1140,7 @@ ctk_status launch_rows(const char* name, const RowArgs& A, float* loss_out, void
                               (alg_streams<ALG>() == 1 || (reinterpret_cast<uintptr_t>(A.t) & 15u) == 0);
     ctk_status rc = CTK_OK;
     if (c <= 8) rc = launch_tile<ALG, 8>(A, s, loss_out, st);
+    else if (c == 10) rc = launch_tile<ALG, 10>(A, s, loss_out, st);
     else if (c <= 12) rc = launch_tile<ALG, 12>(A, s, loss_out, st);
     else if (c <= 16) rc = launch_tile<ALG, 16>(A, s, loss_out, st);
     else if (c <= 32) launch_warp<ALG, 1>(A, s, loss_out, st);
