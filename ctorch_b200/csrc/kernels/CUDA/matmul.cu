@@ -377,12 +377,31 @@ using EpilogueStage = float[32][STAGE_PITCH];
 // writes its row there, and the warp reads it back with 8 lanes across a row, so that every store
 // instruction writes 4 complete 128-byte lines.  `row_base` is the chunk's first row, `lane` the
 // caller's lane (= its row within the chunk).
+// The mask values (the ReLU output whose backward rule the epilogue applies) a lane needs for one
+// whole chunk: the eight 16-byte pieces it stores.  Loaded one chunk ahead of their use, so that the
+// DRAM latency of this fourth array overlaps the TMEM load and staging of the chunk before.
+struct MaskRegs {
+    float4 v[8];
+};
+__device__ __forceinline__ bool chunk_is_whole(const Params& P, bool half, int64_t col0) {
+    return !half && P.vec_store && col0 + 32 <= P.n;
+}
+__device__ __forceinline__ void load_mask(const Params& P, bool half, int64_t row_base, int lane, int64_t col0, MaskRegs& mk) {
+    if (P.mask == nullptr || !chunk_is_whole(P, half, col0)) return;
+    const int sub = lane >> 3, c4 = (lane & 7) * 4;
+    const float* src = P.mask + (row_base + sub) * P.n + col0 + c4;
+    const int64_t step = 4 * P.n;
+    const int rows_left = static_cast<int>(P.m - row_base < 32 ? P.m - row_base : 32);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        mk.v[i] = (i * 4 + sub < rows_left) ? __ldcs(reinterpret_cast<const float4*>(src + i * step)) : make_float4(0.f, 0.f, 0.f, 0.f);
+}
+
 __device__ __forceinline__ void emit_chunk(const Params& P, bool half, int64_t row_base, int lane, int64_t col0, uint32_t (&r)[32],
-                                           EpilogueStage& stage) {
+                                           EpilogueStage& stage, const MaskRegs& mk) {
     if (col0 >= P.n) return;  // same for the whole warp
     const int64_t row = row_base + lane;
-    const bool full = P.vec_store && col0 + 32 <= P.n;
-    if (!half && full) {
+    if (chunk_is_whole(P, half, col0)) {
         if (P.bias != nullptr || P.relu) {
 #pragma unroll
             for (int v = 0; v < 32; ++v) {
@@ -397,25 +416,34 @@ __device__ __forceinline__ void emit_chunk(const Params& P, bool half, int64_t r
             *reinterpret_cast<float4*>(&stage[lane][4 * v]) =
                 make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
         __syncwarp();
+        // lane -> (row sub + 4i of the chunk, 16 bytes at column c4): addresses once, then a fixed step
         const int sub = lane >> 3, c4 = (lane & 7) * 4;
+        const int rows_left = static_cast<int>(P.m - row_base < 32 ? P.m - row_base : 32);
+        float* cdst = P.c + (row_base + sub) * P.n + col0 + c4;
+        const int64_t cstep = 4 * P.n;
+        if (P.mask == nullptr && P.out_hi == nullptr) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int rr = i * 4 + sub;
-            const int64_t grow = row_base + rr;
-            if (grow < P.m) {
-                float4 x = *reinterpret_cast<const float4*>(&stage[rr][c4]);
-                if (P.mask != nullptr) {  // g * (y > 0 ? 1 : 0): the backward rule of ReLU, y its output
-                    const float4 y = __ldcs(reinterpret_cast<const float4*>(P.mask + grow * P.n + col0 + c4));
+            for (int i = 0; i < 8; ++i)
+                if (i * 4 + sub < rows_left) __stcs(reinterpret_cast<float4*>(cdst + i * cstep), *reinterpret_cast<const float4*>(&stage[i * 4 + sub][c4]));
+        } else {
+            const bool masked = P.mask != nullptr, split = P.out_hi != nullptr;
+            const int64_t soff = (row_base + sub) * P.split_pitch + col0 + c4, sstep = 4 * P.split_pitch;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (i * 4 + sub >= rows_left) continue;
+                float4 x = *reinterpret_cast<const float4*>(&stage[i * 4 + sub][c4]);
+                if (masked) {  // g * (y > 0 ? 1 : 0): the backward rule of ReLU, y its output
+                    const float4 y = mk.v[i];
                     x.x *= y.x > 0.0f ? 1.0f : 0.0f; x.y *= y.y > 0.0f ? 1.0f : 0.0f;
                     x.z *= y.z > 0.0f ? 1.0f : 0.0f; x.w *= y.w > 0.0f ? 1.0f : 0.0f;
                 }
-                __stcs(reinterpret_cast<float4*>(P.c + grow * P.n + col0 + c4), x);
-                if (P.out_hi != nullptr) {
+                __stcs(reinterpret_cast<float4*>(cdst + i * cstep), x);
+                if (split) {
                     float4 h, l;
                     h.x = to_tf32_rna(x.x); h.y = to_tf32_rna(x.y); h.z = to_tf32_rna(x.z); h.w = to_tf32_rna(x.w);
                     l.x = to_tf32_rna(x.x - h.x); l.y = to_tf32_rna(x.y - h.y); l.z = to_tf32_rna(x.z - h.z); l.w = to_tf32_rna(x.w - h.w);
-                    __stcs(reinterpret_cast<float4*>(P.out_hi + grow * P.split_pitch + col0 + c4), h);
-                    __stcs(reinterpret_cast<float4*>(P.out_lo + grow * P.split_pitch + col0 + c4), l);
+                    __stcs(reinterpret_cast<float4*>(P.out_hi + soff + i * sstep), h);
+                    __stcs(reinterpret_cast<float4*>(P.out_lo + soff + i * sstep), l);
                 }
             }
         }
@@ -426,7 +454,7 @@ __device__ __forceinline__ void emit_chunk(const Params& P, bool half, int64_t r
     float* crow = P.c + row * P.n;
     if (half) {
         // one K-half of the tile: add into the zeroed C
-        if (full) {
+        if (P.vec_store && col0 + 32 <= P.n) {
 #pragma unroll
             for (int v = 0; v < 8; ++v)
                 atomicAdd(reinterpret_cast<float4*>(crow + col0) + v,
@@ -602,17 +630,21 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
         for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
             const Unit U = unit_of(u, P);
             const int64_t m0 = static_cast<int64_t>(U.tile / P.tiles_n) * BM, n0 = static_cast<int64_t>(U.tile % P.tiles_n) * BN;
+            const int64_t row_base = m0 + quarter * 32;
+            MaskRegs mk_now, mk_next;
+            load_mask(P, U.half, row_base, lane, n0, mk_next);  // chunk 0's, while the accumulator is still being computed
             if (!mbar_wait(tfull_bar(acc), acc_phase, &abort_flag, 0x300 | (16 + acc))) { ok = false; break; }
             tc_fence_after();
-            const int64_t row_base = m0 + quarter * 32;
 #pragma unroll 1
             for (int cc = 0; cc < BN / 32; ++cc) {
                 uint32_t r[32];
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN + cc * 32);
                 tmem_ld32(taddr, r);
-                tmem_ld_wait();
+                mk_now = mk_next;
                 const int64_t col0 = n0 + cc * 32;
-                emit_chunk(P, U.half, row_base, lane, col0, r, stages[warp - 2]);
+                if (cc + 1 < BN / 32) load_mask(P, U.half, row_base, lane, col0 + 32, mk_next);
+                tmem_ld_wait();
+                emit_chunk(P, U.half, row_base, lane, col0, r, stages[warp - 2], mk_now);
             }
             tc_fence_before();
             __syncwarp();
@@ -953,17 +985,21 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
             const Unit U = unit_of(u, P);
             const int64_t m0 = static_cast<int64_t>(U.tile / P.tiles_n) * (2 * BM) + static_cast<int64_t>(rank) * BM;
             const int64_t n0 = static_cast<int64_t>(U.tile % P.tiles_n) * BN;
+            const int64_t row_base = m0 + quarter * 32;
+            MaskRegs mk_now, mk_next;
+            load_mask(P, U.half, row_base, lane, n0, mk_next);  // chunk 0's, while the accumulator is still being computed
             if (!mbar_wait(tfull_bar(acc), acc_phase, &abort_flag, 0x700 | (16 + acc))) { ok = false; break; }
             tc_fence_after();
-            const int64_t row_base = m0 + quarter * 32;
 #pragma unroll 1
             for (int cc = 0; cc < BN / 32; ++cc) {
                 uint32_t r[32];
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN + cc * 32);
                 tmem_ld32(taddr, r);
-                tmem_ld_wait();
+                mk_now = mk_next;
                 const int64_t col0 = n0 + cc * 32;
-                emit_chunk(P, U.half, row_base, lane, col0, r, stages[warp - 2]);
+                if (cc + 1 < BN / 32) load_mask(P, U.half, row_base, lane, col0 + 32, mk_next);
+                tmem_ld_wait();
+                emit_chunk(P, U.half, row_base, lane, col0, r, stages[warp - 2], mk_now);
             }
             tc_fence_before();
             __syncwarp();
