@@ -524,8 +524,7 @@ def test_relu_backward_in_the_gradient_products_epilogue(F, cb, batch, dims):
     """set_fuse_relu_backward: the product g.W^T whose result only feeds a ReLU's backward rule applies
     the rule (and writes the hi/lo split the next two products read) in its epilogue.  Loss and every
     parameter gradient are bit for bit those of the unfused tape; the gradient stored for the hidden
-    activation itself is the masked one.  (Products with K < 256 -- here the last layer's -- keep the two
-    kernels; the first hidden activation's gradient product has K >= 256 in every case.)"""
+    activation itself is the masked one."""
     rng = np.random.default_rng(batch + dims[1])
     Ws = [(rng.standard_normal((i, j)) / np.sqrt(i)).astype(np.float32) for i, j in zip(dims[:-1], dims[1:])]
     bs = [rng.uniform(-0.1, 0.1, j).astype(np.float32) for j in dims[1:]]
