@@ -626,6 +626,14 @@ Tensor Tensor::shape_only(const std::vector<size_t>& shape, DType dtype, DeviceT
     return t;
 }
 
+KeptSplit* operand_split(const Tensor& t, int64_t mn, int64_t k, int64_t s_mn, int64_t s_k) {
+    int64_t outer, inner, pitch;
+    if (s_k == 1 && s_mn >= k) { outer = mn; inner = k; pitch = s_mn; }
+    else if (s_mn == 1 && s_k >= mn) { outer = k; inner = mn; pitch = s_k; }
+    else return nullptr;
+    return t.storage().kept_split(static_cast<int64_t>(t.storage_offset()), outer, inner, pitch, ctk_matmul_split_bytes(mn, k));
+}
+
 // y = [relu](A.B + bias) * (mask > 0) in one launch of the 3xTF32 product, operand splits kept with
 // their buffers and y's own split written by the epilogue.  False (nothing launched) when the fused
 // form does not apply: another device, dtype or mode, operands the tensor cores cannot take.
@@ -646,15 +654,8 @@ static bool fused_product(const Tensor& A, const Tensor& B, const Tensor* bias, 
     const int64_t sa0 = static_cast<int64_t>(A.strides()[0]), sa1 = static_cast<int64_t>(A.strides()[1]);
     const int64_t sb0 = static_cast<int64_t>(B.strides()[0]), sb1 = static_cast<int64_t>(B.strides()[1]);
     if (ctk_matmul_path(A.data<float>(), B.data<float>(), m, n, k, sa0, sa1, sb0, sb1, CTK_MATMUL_3XTF32) != 0) return false;
-    auto kept = [&](const Tensor& t, int64_t mn, int64_t s_mn, int64_t s_k) -> KeptSplit* {
-        int64_t outer, inner, pitch;
-        if (s_k == 1 && s_mn >= k) { outer = mn; inner = k; pitch = s_mn; }
-        else if (s_mn == 1 && s_k >= mn) { outer = k; inner = mn; pitch = s_k; }
-        else return nullptr;
-        return t.storage().kept_split(static_cast<int64_t>(t.storage_offset()), outer, inner, pitch, ctk_matmul_split_bytes(mn, k));
-    };
-    KeptSplit* ka = kept(A, m, sa0, sa1);
-    KeptSplit* kb = (B.storage().raw() == A.storage().raw()) ? nullptr : kept(B, n, sb1, sb0);
+    KeptSplit* ka = operand_split(A, m, k, sa0, sa1);
+    KeptSplit* kb = (B.storage().raw() == A.storage().raw()) ? nullptr : operand_split(B, n, k, sb1, sb0);  // one split per buffer
     y = Tensor(ShapeTag{}, {static_cast<size_t>(m), static_cast<size_t>(n)}, A.dtype(), DeviceType::kCUDA, false);
     float* yp = y.data<float>();  // (the mutable pointer first: asking for it drops a kept split)
     // y enters the next product as its K-major A operand and, transposed, a weight-gradient product:

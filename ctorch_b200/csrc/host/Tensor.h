@@ -199,6 +199,11 @@ Tensor operator>=(float s, const Tensor& t);
 Tensor operator<=(float s, const Tensor& t);
 Tensor operator!=(float s, const Tensor& t);
 
+// The kept hi/lo split of a MatMul operand `t` with extents (mn, k) and strides (s_mn, s_k): the view is
+// named by its contiguous ("inner") extent, the other extent and its pitch, so a t() view of the same
+// memory finds the same split.  nullptr for an operand without a unit stride (or a host tensor).
+KeptSplit* operand_split(const Tensor& t, int64_t mn, int64_t k, int64_t s_mn, int64_t s_k);
+
 // Stream every kernel and copy of this thread's tensors is issued on (NULL = legacy default stream).
 void* current_stream();
 void set_current_stream(void* stream);

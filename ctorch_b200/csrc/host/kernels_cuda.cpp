@@ -123,16 +123,9 @@ Tensor MatMul_CUDA_kernel(const Tensor& a, const Tensor& b) {
     // the buffer is written), so X in X.W and X^T.dY, dY in dY.W^T and X^T.dY, and the weights the
     // tape holds are each split once.  The view is named by its contiguous ("inner") extent, the
     // other extent and its pitch, so a t() view of the same memory finds the same split.
-    auto kept = [&](const Tensor& t, int64_t mn, int64_t s_mn, int64_t s_k) -> KeptSplit* {
-        int64_t outer, inner, pitch;
-        if (s_k == 1 && s_mn >= k) { outer = mn; inner = k; pitch = s_mn; }
-        else if (s_mn == 1 && s_k >= mn) { outer = k; inner = mn; pitch = s_k; }
-        else return nullptr;
-        return t.storage().kept_split(static_cast<int64_t>(t.storage_offset()), outer, inner, pitch, ctk_matmul_split_bytes(mn, k));
-    };
-    KeptSplit* ka = kept(a, m, sa0, sa1);
+    KeptSplit* ka = operand_split(a, m, k, sa0, sa1);
     // one split per buffer: when both operands are views of the same buffer only A's is kept
-    KeptSplit* kb = (b.storage().raw() == a.storage().raw()) ? nullptr : kept(b, n, sb1, sb0);
+    KeptSplit* kb = (b.storage().raw() == a.storage().raw()) ? nullptr : operand_split(b, n, k, sb1, sb0);
     cuda_check(ctk_matmul_3xtf32_kept_f32(a.data<float>(), b.data<float>(), r.data<float>(), m, n, k, sa0, sa1, sb0, sb1, ka ? ka->buf : nullptr,
                                           ka ? &ka->valid : nullptr, kb ? kb->buf : nullptr, kb ? &kb->valid : nullptr, nullptr, current_stream()),
                who);
