@@ -60,12 +60,18 @@ public:
     Tensor last_logits;
     bool keep_logits = false;
     bool fresh_weights = false;  // corrected mode: backward reads the updated weights
+    // Deferred losses: a step does not wait for the device.  Its loss is still copied to page-locked
+    // memory by the step itself (slot steps_done % kLossSlots); the host reads the slots in sync_losses().
+    bool deferred_loss = false;
+    static constexpr int kLossSlots = 16;
     uint64_t steps_done = 0;
+    uint64_t deferred_since = 0;
     // Input staging: up to two uploaded batches wait on the device, each with an event that says
     // its copy has landed, so the upload of batch k+1 (on its own stream) overlaps step k.
     struct Staged {
         Tensor x, labels;
-        void* ready = nullptr;
+        void* ready = nullptr;     // copy stream: the upload has landed
+        void* consumed = nullptr;  // compute stream: the step that read this batch is done with it
         int64_t batch = -1;
     };
     Staged staged[2];
@@ -101,8 +107,10 @@ public:
         if (ev_comm) ctk_event_destroy(ev_comm);
         if (pinned_loss) ctk_free_host(pinned_loss);
         if (pinned_x) ctk_free_host(pinned_x);
-        for (Staged& s : staged)
+        for (Staged& s : staged) {
             if (s.ready) ctk_event_destroy(s.ready);
+            if (s.consumed) ctk_event_destroy(s.consumed);
+        }
         if (copy_stream) ctk_stream_destroy(copy_stream);
     }
 
@@ -197,7 +205,8 @@ public:
         // the value is copied to a page-locked slot now and read once the step has been issued.
         {
             const Tensor& loss_value = loss;  // read-only access: the tape shares this buffer, a writable pointer would copy it
-            cuda_check(ctk_memcpy_d2h(pinned_loss, loss_value.data<float>(), sizeof(float), st), "loss read-back");
+            float* slot = static_cast<float*>(pinned_loss) + (deferred_loss ? steps_done % kLossSlots : 0);
+            cuda_check(ctk_memcpy_d2h(slot, loss_value.data<float>(), sizeof(float), st), "loss read-back");
         }
         backward(loss);
         if (comm) {
@@ -214,10 +223,30 @@ public:
             }
         }
         if (keep_logits) last_logits = logits;
-        if (!capturing) cuda_check(st ? ctk_stream_sync(st) : ctk_device_sync(), "step sync");
+        const bool wait = !capturing && !deferred_loss;
+        if (wait) cuda_check(st ? ctk_stream_sync(st) : ctk_device_sync(), "step sync");
         ctx.release_step_nodes();
         ++steps_done;
-        return capturing ? 0.0f : *static_cast<float*>(pinned_loss);
+        return wait ? *static_cast<float*>(pinned_loss) : 0.0f;
+    }
+
+    // Waits for every step issued so far and hands out the losses of the last min(cap, 16, steps since
+    // the mode was switched on) steps, oldest first.
+    int sync_losses(float* out, int cap) {
+        void* st = current_stream();
+        cuda_check(st ? ctk_stream_sync(st) : ctk_device_sync(), "sync_losses");
+        const uint64_t have = steps_done - deferred_since;
+        int n = static_cast<int>(have < static_cast<uint64_t>(kLossSlots) ? have : kLossSlots);
+        if (n > cap) n = cap;
+        for (int i = 0; i < n; ++i) out[i] = static_cast<float*>(pinned_loss)[(steps_done - n + i) % kLossSlots];
+        return n;
+    }
+    void set_deferred_loss(bool on) {
+        void* st = current_stream();
+        cuda_check(st ? ctk_stream_sync(st) : ctk_device_sync(), "set_deferred_loss");
+        release_graph();
+        deferred_loss = on;
+        deferred_since = steps_done;
     }
 
     // ---- the step as a CUDA graph -------------------------------------------------------------------
@@ -384,6 +413,8 @@ public:
         Staged& s = staged[n_staged % 2];
         if (!copy_stream) cuda_check(ctk_stream_create_ex(&copy_stream, 1), "copy stream");
         if (!s.ready) cuda_check(ctk_event_create(&s.ready), "event");
+        if (!s.consumed) cuda_check(ctk_event_create(&s.consumed), "event");
+        else cuda_check(ctk_stream_wait_event(copy_stream, s.consumed), "wait for the slot's last reader");  // (deferred losses: no host wait did it)
         if (s.batch != batch) {
             s.x = Tensor(ShapeTag{}, {static_cast<size_t>(batch), in}, DType::kFloat, DeviceType::kCUDA, false);
             s.labels = Tensor(ShapeTag{}, {static_cast<size_t>(batch)}, DType::kFloat, DeviceType::kCUDA, false);
@@ -420,7 +451,9 @@ public:
         Tensor y(ShapeTag{}, {static_cast<size_t>(s.batch), classes}, DType::kFloat, DeviceType::kCUDA, false);
         const Tensor& labels = s.labels;
         cuda_check(ctk_onehot_f32(labels.data<float>(), s.batch, static_cast<int64_t>(classes), y.data<float>(), st), "one-hot");
-        return step(s.x, y);
+        const float loss = step(s.x, y);
+        cuda_check(ctk_event_record(s.consumed, st), "record");
+        return loss;
     }
 
     // Class probabilities of a batch without recording anything: NeuralNetwork::predict of
@@ -453,6 +486,7 @@ public:
     // there).  Batches are views of the data set, not copies.  Returns the mean of the step losses.
     float train_epoch(const Tensor& images, const Tensor& labels, int64_t batch_size, bool use_graph = false) {
         if (batch_size <= 0) throw std::runtime_error("train_epoch: batch size must be positive");
+        if (deferred_loss) throw std::runtime_error("train_epoch adds up every step's loss: switch deferred losses off first");
         if (use_graph) {
             const int64_t n = static_cast<int64_t>(images.sizes()[0]);
             const int64_t num_batches = n / batch_size;
@@ -705,6 +739,12 @@ int cth_mlp_set_comm(void* m, void* comm) {
 }
 int cth_mlp_set_corrected(void* m, int exact_bias_grad, int fresh_weights) {
     return guarded([&] { static_cast<MlpTrainer*>(m)->set_corrected(exact_bias_grad != 0, fresh_weights != 0); });
+}
+int cth_mlp_set_deferred_loss(void* m, int on) {
+    return guarded([&] { static_cast<MlpTrainer*>(m)->set_deferred_loss(on != 0); });
+}
+int cth_mlp_sync_losses(void* m, float* out, int cap, int* n) {
+    return guarded([&] { *n = static_cast<MlpTrainer*>(m)->sync_losses(out, cap); });
 }
 int cth_mlp_keep_logits(void* m, int keep) {
     return guarded([&] { static_cast<MlpTrainer*>(m)->keep_logits = keep != 0; });

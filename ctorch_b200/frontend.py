@@ -304,6 +304,16 @@ class MlpTrainer:
         """Opt-in: true bias gradients and backward against the current weights (not the reference's arithmetic)."""
         _chk(lib.cth_mlp_set_corrected(self.h, 1 if exact_bias_grad else 0, 1 if fresh_weights else 0))
 
+    def set_deferred_loss(self, on=True):
+        """Steps return without waiting for the device (and report 0); sync_losses() reads the losses."""
+        _chk(lib.cth_mlp_set_deferred_loss(self.h, 1 if on else 0))
+
+    def sync_losses(self):
+        out = (ctypes.c_float * 16)()
+        n = ctypes.c_int()
+        _chk(lib.cth_mlp_sync_losses(self.h, out, 16, ctypes.byref(n)))
+        return np.asarray(out[:n.value], np.float32)
+
     def keep_logits(self, keep=True):
         _chk(lib.cth_mlp_keep_logits(self.h, 1 if keep else 0))
 

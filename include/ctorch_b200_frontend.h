@@ -94,6 +94,13 @@ int cth_mlp_destroy(void* mlp);
  * communicator), started per gradient while backward is still running.  NULL switches it off. */
 int cth_mlp_set_comm(void* mlp, void* comm);
 int cth_mlp_keep_logits(void* mlp, int keep);
+/* Deferred losses (no counterpart: the reference's loop reads loss.item() every step, mnist/mnist.cpp:255).
+ * on: the step calls return without waiting for the device and report 0; each step still copies its
+ * loss to page-locked memory, and cth_mlp_sync_losses waits for everything issued and returns the
+ * losses of the last n <= min(cap, 16) steps, oldest first.  Host buffers given to cth_mlp_stage_host
+ * must then stay unchanged until cth_mlp_sync_losses has returned.  The numbers do not change. */
+int cth_mlp_set_deferred_loss(void* mlp, int on);
+int cth_mlp_sync_losses(void* mlp, float* out, int cap, int* n);
 /* No counterpart: an opt-in mode that leaves the reference's arithmetic on purpose.  exact_bias_grad: the
  * gradient of a bias is the sum of the upstream gradient over the batch (the reference: its first row,
  * src/AutoDiff.cpp:690-757).  fresh_weights: backward multiplies by the current weights (the reference: by

@@ -638,3 +638,40 @@ def test_corrected_mode_is_textbook_sgd(F, cb):
     # switching it off again returns to the reference's arithmetic from the current weights on
     tr.set_corrected(False, False)
     tr.step_host(xs[0], labs[0])
+
+
+def test_deferred_losses_change_nothing_but_the_waiting(F, cb):
+    """set_deferred_loss: the step calls return without waiting and report 0; sync_losses() hands out the
+    same losses, and the weights end up bit for bit the same -- from device batches, from host batches
+    and through the staged uploads (whose slots are then guarded by events, not by the host's wait)."""
+    from ctorch_b200.device import PinnedArray
+    dims, batch, steps = [64, 96, 12], 128, 6
+    rng = np.random.default_rng(4)
+    p0 = np.concatenate([np.concatenate([(rng.standard_normal((i, j)) / np.sqrt(i)).astype(np.float32).ravel(),
+                                         rng.uniform(-0.1, 0.1, j).astype(np.float32)]) for i, j in zip(dims[:-1], dims[1:])])
+    xs = [rng.standard_normal((batch, dims[0])).astype(np.float32) for _ in range(steps)]
+    labs = [rng.integers(0, dims[-1], batch).astype(np.float32) for _ in range(steps)]
+    a, b, c = (F.MlpTrainer(dims, p0, 0.001) for _ in range(3))
+    want = [a.step_host(x, l) for x, l in zip(xs, labs)]
+    b.set_deferred_loss(True)
+    assert all(b.step_host(x, l) == 0.0 for x, l in zip(xs, labs))
+    assert_exact(b.sync_losses(), np.asarray(want, np.float32), "deferred losses, host batches")
+    b.set_deferred_loss(False)
+    assert_exact(b.params(), a.params(), "weights, host batches")
+    # staged uploads from page-locked buffers that stay unchanged until sync_losses()
+    px = [PinnedArray(x.shape) for x in xs]
+    pl = [PinnedArray(l.shape) for l in labs]
+    for q, x in zip(px, xs):
+        q.array[...] = x
+    for q, l in zip(pl, labs):
+        q.array[...] = l
+    c.set_deferred_loss(True)
+    c.stage_host(px[0].array, pl[0].array)
+    for k in range(steps):
+        if k + 1 < steps:
+            c.stage_host(px[k + 1].array, pl[k + 1].array)
+        assert c.step_staged() == 0.0
+    assert_exact(c.sync_losses(), np.asarray(want, np.float32), "deferred losses, staged uploads")
+    assert_exact(c.params(), a.params(), "weights, staged uploads")
+    with pytest.raises(F.FrontendError, match="deferred"):
+        c.train_epoch(F.Tensor.from_numpy(xs[0]), F.Tensor.from_numpy(labs[0]), 64)
