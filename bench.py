@@ -574,7 +574,8 @@ def run_mnist_app(cb, args, rng):
 def run_one_kernel(cb, case, rng):
     """A few launches of ONE kernel on a small case (inputs larger than L2, a few hundred MB on the
     device): the command profiler captures are taken from.  Cases: matmul_<mode>_<m>x<k>x<n>[_dA|_dB|_fwdfused|_dAfused],
-    add_<log2n>, relu_<log2n>, sum_<log2n>, softmax_<rows>x<cols>, ce_<rows>x<cols>."""
+    add_<log2n>, relu_<log2n>, sum_<log2n>, cmp_<log2n>, cast_<log2n>, rand_<log2n>, sgdsplit_<rows>x<cols>,
+    colsum_<rows>x<cols>, softmax_<rows>x<cols>, ce_<rows>x<cols>."""
     parts = case.split("_")
     kind = parts[0]
     if kind == "matmul":
@@ -601,6 +602,23 @@ def run_one_kernel(cb, case, rng):
         a = cb.to_device(rng.uniform(-4, 4, n).astype(np.float32)); b = cb.to_device(rng.uniform(-4, 4, n).astype(np.float32)); o = cb.empty((n,))
         fn = dict(add=lambda: cb.ops.binary("Add", a, b, out=o), relu=lambda: cb.ops.unary("ReLU", a, out=o), sum=lambda: cb.ops.sum(a))[kind]
         work, unit = dict(add=12, relu=8, sum=4)[kind] * n, "GB/s"
+    elif kind in ("cmp", "cast", "rand"):
+        n = 1 << int(parts[1])
+        a = cb.to_device(rng.uniform(-4, 4, n).astype(np.float32)); b = cb.to_device(rng.uniform(-4, 4, n).astype(np.float32))
+        ob, od, of = cb.DeviceArray((n,), np.uint8), cb.DeviceArray((n,), np.float64), cb.empty((n,))
+        i64 = ctypes.c_int64
+        fn = dict(cmp=lambda: cb.check(cb.lib.ctk_compare_f32(0, 0, a.p, b.p, ctypes.c_float(0), ob.p, i64(n), None)),
+                  cast=lambda: cb.check(cb.lib.ctk_cast_f32(1, a.p, od.p, i64(n), None)),
+                  rand=lambda: cb.check(cb.lib.ctk_rand_uniform_f32(of.p, i64(n), ctypes.c_uint64(1), ctypes.c_uint64(0), None)))[kind]
+        work, unit = dict(cmp=9, cast=12, rand=4)[kind] * n, "GB/s"
+    elif kind in ("sgdsplit", "colsum"):
+        rows, cols = (int(v) for v in parts[1].split("x"))
+        p_ = cb.to_device(rng.standard_normal((rows, cols)).astype(np.float32)); g = cb.to_device(rng.standard_normal((rows, cols)).astype(np.float32))
+        split = cb.empty((int(cb.lib.ctk_matmul_split_bytes(cols, rows)) // 4,))
+        i64 = ctypes.c_int64
+        fn = dict(sgdsplit=lambda: cb.check(cb.lib.ctk_sgd_update_split_f32(p_.p, g.p, ctypes.c_float(1e-3), i64(rows), i64(cols), i64(cols), split.p, None)),
+                  colsum=lambda: cb.ops.colsum(p_))[kind]
+        work, unit = dict(sgdsplit=20, colsum=4)[kind] * rows * cols, "GB/s"
     elif kind in ("softmax", "ce"):
         rows, cols = (int(v) for v in parts[1].split("x"))
         x = cb.to_device((2 * rng.standard_normal((rows, cols))).astype(np.float32)); y = cb.empty((rows, cols))
