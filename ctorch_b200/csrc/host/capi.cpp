@@ -137,7 +137,11 @@ public:
     void set_comm(void* c) {
         comm = c;
         if (c && !comm_stream) {
-            cuda_check(ctk_stream_create_ex(&comm_stream, 1), "comm stream");
+            // Highest priority: the MatMul kernels are persistent and hold every SM until they end, so
+            // an all-reduce gets SMs only at a product's boundary -- and only if its blocks are placed
+            // before the next product's (CTORCH_COMM_PRIORITY=0: default priority).
+            const char* cp = std::getenv("CTORCH_COMM_PRIORITY");
+            cuda_check(ctk_stream_create_priority(&comm_stream, 1, (cp && cp[0] == '0') ? 0 : 1), "comm stream");
             cuda_check(ctk_event_create(&ev_grad), "event");
             cuda_check(ctk_event_create(&ev_comm), "event");
         }

@@ -226,6 +226,15 @@ ctk_status ctk_stream_create_ex(void** s, int non_blocking) {
     *s = st;
     return CTK_OK;
 }
+ctk_status ctk_stream_create_priority(void** s, int non_blocking, int high_priority) {
+    CTK_REQUIRE(s, "ctk_stream_create_priority: null");
+    int least = 0, greatest = 0;
+    CTK_CUDA(cudaDeviceGetStreamPriorityRange(&least, &greatest));
+    cudaStream_t st;
+    CTK_CUDA(cudaStreamCreateWithPriority(&st, non_blocking ? cudaStreamNonBlocking : cudaStreamDefault, high_priority ? greatest : least));
+    *s = st;
+    return CTK_OK;
+}
 ctk_status ctk_stream_destroy(void* s) {
     if (s) CTK_CUDA(cudaStreamDestroy(as_stream(s)));
     return CTK_OK;

@@ -91,6 +91,9 @@ ctk_status ctk_memset(void* device_ptr, int byte_value, size_t bytes, void* stre
 ctk_status ctk_stream_create(void** stream);
 /* non_blocking != 0: the stream does not synchronise with the legacy default stream. */
 ctk_status ctk_stream_create_ex(void** stream, int non_blocking);
+/* The same with the device's greatest (high_priority != 0) or least stream priority: pending blocks of a
+ * higher-priority stream are placed first whenever SMs become free. */
+ctk_status ctk_stream_create_priority(void** stream, int non_blocking, int high_priority);
 ctk_status ctk_stream_destroy(void* stream);
 ctk_status ctk_stream_sync(void* stream);
 /* Stream capture (no counterpart in the reference): the work this thread issues to `stream` between
