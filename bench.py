@@ -319,7 +319,7 @@ def run_mlp(args, cp):
             gpu_launches=int(launches),
             roofline=dict(bound="tensor", achieved=achieved, peak=peak, unit="TFLOP/s", frac=achieved / peak if peak else None,
                           # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant shape (8192 x 4096 x 4096, forward with
-                          # its fused epilogue), from the ncu capture summarised in profiles/tcgen05_matmul_pair_3xtf32_fused_epilogues_8192x4096x4096.md
+                          # its fused epilogue), from one ncu capture of that launch (--workload kernel --case matmul_3xtf32_8192x4096x4096_fwdfused)
                           traffic=1.503e9 + 0.362e9, traffic_launch="forward 8192x4096x4096 + bias + ReLU + split (algorithmic: 402 MB of operand splits read, 402 MB written)",
                           kernel="tcgen05_matmul_pair_kernel / tcgen05_matmul_kernel (3xTF32)", launches=int(n), avg_launch_ms=tms / n if n else None,
                           peak_source=f"{peaks['source']}: {bf16_key} {bf16_val} / 2 (TF32 runs at half the bf16 rate; no TF32 figure was measured) / 3 (three TF32 products per fp32 product); algorithmic flops 2*M*N*K",
@@ -327,7 +327,7 @@ def run_mlp(args, cp):
                           # context for a fraction above 1: the measured ceiling is cuBLAS bf16 (73 % of the nominal 2250) scaled
                           # to TF32; against the nominal dense TF32 rate (1125 TFLOP/s, a third of it per fp32 product):
                           nominal_peak=375.0, frac_of_nominal=achieved / 375.0,
-                          tensor_pipe_active="97.0 % of active and 91.5 % of elapsed SM cycles (ncu, profiles/tcgen05_matmul_pair_3xtf32_fused_epilogues_8192x4096x4096.md)"),
+                          tensor_pipe_active="97.0 % of active and 91.5 % of elapsed SM cycles (ncu capture of --workload kernel --case matmul_3xtf32_8192x4096x4096_fwdfused)"),
             cpu_baseline=cpu,
         )
         print(json.dumps(out))
