@@ -653,9 +653,12 @@ static bool fused_product(const Tensor& A, const Tensor& B, const Tensor* bias, 
         return false;
     const int64_t sa0 = static_cast<int64_t>(A.strides()[0]), sa1 = static_cast<int64_t>(A.strides()[1]);
     const int64_t sb0 = static_cast<int64_t>(B.strides()[0]), sb1 = static_cast<int64_t>(B.strides()[1]);
-    if (ctk_matmul_path(A.data<float>(), B.data<float>(), m, n, k, sa0, sa1, sb0, sb1, CTK_MATMUL_3XTF32) != 0) return false;
-    KeptSplit* ka = operand_split(A, m, k, sa0, sa1);
-    KeptSplit* kb = (B.storage().raw() == A.storage().raw()) ? nullptr : operand_split(B, n, k, sb1, sb0);  // one split per buffer
+    // 0: tensor cores; 2: the short-contraction kernel, which reads the operands as they are (no splits)
+    // and has no bias / ReLU form
+    const int path = ctk_matmul_path(A.data<float>(), B.data<float>(), m, n, k, sa0, sa1, sb0, sb1, CTK_MATMUL_3XTF32);
+    if (path != 0 && !(path == 2 && !bias && !relu)) return false;
+    KeptSplit* ka = path == 0 ? operand_split(A, m, k, sa0, sa1) : nullptr;
+    KeptSplit* kb = (path != 0 || B.storage().raw() == A.storage().raw()) ? nullptr : operand_split(B, n, k, sb1, sb0);  // one split per buffer
     y = Tensor(ShapeTag{}, {static_cast<size_t>(m), static_cast<size_t>(n)}, A.dtype(), DeviceType::kCUDA, false);
     float* yp = y.data<float>();  // (the mutable pointer first: asking for it drops a kept split)
     // y enters the next product as its K-major A operand and, transposed, a weight-gradient product:

@@ -1233,6 +1233,64 @@ bool classify(const float* p, int64_t mn, int64_t k, int64_t s_mn, int64_t s_k, 
     return false;
 }
 
+// ---- a short contraction (K <= 16) with a large output: CUDA cores, bound by the output's bytes ------
+// dX of a layer with few outputs (the 10-class layer: [B,10].[10,H]) has one k-block per tile, so on the
+// tensor-core kernel nothing hides the epilogue and its four warps per SM cannot keep HBM busy.  Here a
+// thread keeps the K values of its four output columns in registers and walks down the rows: per row
+// one broadcast read of A's K values, 4K multiply-adds, one 16-byte store (plus the mask read and the
+// two split stores of the fused forms).  Products and sums are rounded one by one in l order -- the
+// arithmetic of MatMul_BASIC_kernel.cpp:41-50 as g++ compiles it, so this path is bit-identical to it.
+// A: [m, k] contiguous; B: [n, k] contiguous (the t() view of an [n, k] array as the right operand).
+constexpr int SK_MAXK = 16, SK_THREADS = 128, SK_ROWS = 32;
+__global__ void __launch_bounds__(SK_THREADS) skinny_k_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ c,
+                                                             int64_t m, int64_t n, int k, const float* __restrict__ mask,
+                                                             float* __restrict__ out_hi, float* __restrict__ out_lo, int64_t split_pitch) {
+    const int64_t j0 = (static_cast<int64_t>(blockIdx.x) * SK_THREADS + threadIdx.x) * 4;
+    if (j0 >= n) return;
+    float bw[4][SK_MAXK];
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int l = 0; l < SK_MAXK; ++l) bw[q][l] = l < k ? __ldg(b + (j0 + q) * k + l) : 0.0f;
+    const int64_t r0 = static_cast<int64_t>(blockIdx.y) * SK_ROWS;
+    const int64_t r1 = r0 + SK_ROWS < m ? r0 + SK_ROWS : m;
+#pragma unroll 4
+    for (int64_t r = r0; r < r1; ++r) {
+        float ar[SK_MAXK];
+#pragma unroll
+        for (int l = 0; l < SK_MAXK; ++l) ar[l] = l < k ? __ldg(a + r * k + l) : 0.0f;
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int l = 0; l < SK_MAXK; ++l)
+            if (l < k) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) acc[q] = __fadd_rn(acc[q], __fmul_rn(ar[l], bw[q][l]));
+            }
+        float4 x = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        if (mask != nullptr) {
+            const float4 y = __ldcs(reinterpret_cast<const float4*>(mask + r * n + j0));
+            x.x *= y.x > 0.0f ? 1.0f : 0.0f; x.y *= y.y > 0.0f ? 1.0f : 0.0f;
+            x.z *= y.z > 0.0f ? 1.0f : 0.0f; x.w *= y.w > 0.0f ? 1.0f : 0.0f;
+        }
+        __stcs(reinterpret_cast<float4*>(c + r * n + j0), x);
+        if (out_hi != nullptr) {
+            float4 h, l4;
+            h.x = to_tf32_rna(x.x); h.y = to_tf32_rna(x.y); h.z = to_tf32_rna(x.z); h.w = to_tf32_rna(x.w);
+            l4.x = to_tf32_rna(x.x - h.x); l4.y = to_tf32_rna(x.y - h.y); l4.z = to_tf32_rna(x.z - h.z); l4.w = to_tf32_rna(x.w - h.w);
+            __stcs(reinterpret_cast<float4*>(out_hi + r * split_pitch + j0), h);
+            __stcs(reinterpret_cast<float4*>(out_lo + r * split_pitch + j0), l4);
+        }
+    }
+}
+// The shapes that take it: 3xTF32 mode, K <= 16, both operands K-major and contiguous, whole 16-byte
+// pieces, and an output of at least 2^20 elements (small products stay on the tensor-core kernel).
+static bool skinny_k_ok(const float* a, const float* b, const float* c, int64_t m, int64_t n, int64_t k, int64_t sa0, int64_t sa1, int64_t sb0,
+                        int64_t sb1, int md) {
+    return md == CTK_MATMUL_3XTF32 && k >= 1 && k <= SK_MAXK && sa1 == 1 && sa0 == k && sb0 == 1 && sb1 == k && n % 4 == 0 &&
+           m * n >= (int64_t(1) << 20) && (m + SK_ROWS - 1) / SK_ROWS <= 65535 && (c == nullptr || (reinterpret_cast<uintptr_t>(c) & 15u) == 0) &&
+           a != nullptr && b != nullptr;
+}
+
 int g_default_mode = CTK_MATMUL_3XTF32;
 int g_pairing = 0;  // 0: CTA pairs where the shape allows, 1: single-CTA kernel only
 int g_split_tail = 1;  // 1: K-halves for the tiles of a last wave that fills at most half the machine
@@ -1409,6 +1467,7 @@ size_t ctk_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k, int mode) {
 
 int ctk_matmul_path(const float* a, const float* b, int64_t m, int64_t n, int64_t k, int64_t sa0, int64_t sa1,
                     int64_t sb0, int64_t sb1, int mode) {
+    if (skinny_k_ok(a, b, nullptr, m, n, k, sa0, sa1, sb0, sb1, resolve_mode(mode))) return 2;
     return choose_path(a, b, m, n, k, sa0, sa1, sb0, sb1, mode, nullptr, nullptr);
 }
 
@@ -1499,6 +1558,19 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
     const int md = resolve_mode(mode);
     CTK_REQUIRE(md >= CTK_MATMUL_3XTF32 && md <= CTK_MATMUL_FP32_SIMT, "ctk_matmul_f32: unknown mode");
     CTK_REQUIRE(m < (int64_t(1) << 31) && n < (int64_t(1) << 31) && k < (int64_t(1) << 31), "ctk_matmul_f32: extent >= 2^31");
+
+    if (fe.bias == nullptr && !fe.relu && skinny_k_ok(a, b, c, m, n, k, sa0, sa1, sb0, sb1, md) &&
+        (fe.mask == nullptr || (reinterpret_cast<uintptr_t>(fe.mask) & 15u) == 0)) {
+        float *hi = nullptr, *lo = nullptr;
+        if (fe.c_split) {
+            hi = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(fe.c_split) + 255u) & ~static_cast<uintptr_t>(255u));
+            lo = hi + m * n;  // (pitch = n, a multiple of 4)
+        }
+        dim3 grid(static_cast<unsigned>((n / 4 + SK_THREADS - 1) / SK_THREADS), static_cast<unsigned>((m + SK_ROWS - 1) / SK_ROWS));
+        skinny_k_kernel<<<grid, SK_THREADS, 0, st>>>(a, b, c, m, n, static_cast<int>(k), fe.mask, hi, lo, n);
+        CTK_LAUNCH_CHECK("skinny_k_kernel");
+        return CTK_OK;
+    }
 
     tc::Operand A, B;
     const bool fused = fe.bias != nullptr || fe.relu || fe.mask != nullptr || fe.c_split != nullptr;

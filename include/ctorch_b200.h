@@ -353,7 +353,11 @@ ctk_status ctk_sgd_update_split_f32(float* p, const float* g, float lr, int64_t 
  * the shared array; launch timing must be off. */
 ctk_status ctk_matmul_3xtf32_noalloc_f32(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
                                          int64_t sa0, int64_t sa1, int64_t sb0, int64_t sb1, void* stream);
-/* Which path the call above would take: 0 tcgen05, 1 SIMT. */
+/* Which path ctk_matmul_f32 would take: 0 tcgen05, 1 SIMT (an operand without a unit stride, or on
+ * request), 2 the short-contraction kernel (3xTF32 mode, K <= 16, both operands K-major and contiguous,
+ * n % 4 == 0, at least 2^20 outputs: one thread per four output columns on the CUDA cores, products and
+ * sums rounded one by one in l order -- bit-identical to MatMul_BASIC_kernel.cpp:41-50 -- and bound by
+ * the output's bytes; takes the mask and split forms of ctk_matmul_3xtf32_fused_f32, not bias / ReLU). */
 int ctk_matmul_path(const float* a, const float* b, int64_t m, int64_t n, int64_t k,
                     int64_t sa0, int64_t sa1, int64_t sb0, int64_t sb1, int mode);
 /* Per-launch timing of the tensor-core kernel with CUDA events on the launching stream (off by

@@ -313,3 +313,32 @@ def test_dynamic_unit_order_equals_fixed_order(cb, mode, m, k, n, ta, tb):
     finally:
         cb.ops.set_matmul_dynamic_order(0)
     _check_status(cb)
+
+
+@pytest.mark.parametrize("m,k,n", [(8192, 10, 4096), (2048, 16, 512), (4099, 1, 256), (1030, 7, 1020)])
+def test_short_contraction_kernel_is_the_reference_recurrence(cb, orc, m, k, n):
+    """K <= 16 with a large output (dX of the 10-class layer): the CUDA-core kernel, whose products and
+    sums are rounded one by one in l order -- bit-identical to the reference's MatMul loop -- plain, with
+    the ReLU-backward mask, and with the split of the result, each against the separate kernels."""
+    rng = np.random.default_rng(m + k)
+    g = rng.standard_normal((m, k)).astype(np.float32)
+    w = rng.standard_normal((n, k)).astype(np.float32)            # the right operand is w.t()
+    y_act = np.maximum(rng.standard_normal((m, n)), 0).astype(np.float32)
+    dG, dW, dM = cb.to_device(g), cb.to_device(w), cb.to_device(y_act)
+    assert cb.ops.matmul_path(dG, dW, False, True, "3xtf32") == 2
+    plain = cb.ops.matmul(dG, dW, tb=True, mode="3xtf32")
+    rows = np.asarray([0, 1, m // 2, m - 1])
+    assert_exact(plain.numpy()[rows], orc.matmul_rows(g, w, rows, tb=True), "sampled rows == the reference's recurrence")
+    assert_matmul_close(plain.numpy(), g.astype(np.float64) @ w.T.astype(np.float64), 1e-6, "vs fp64")
+    masked = cb.ops.unary_backward("ReLU", dM, plain).numpy()
+    f_mask, hi, lo = cb.ops.matmul_fused(dG, dW, mask=dM, want_split=True, tb=True)
+    assert_exact(f_mask.numpy(), masked, "product * (y > 0)")
+    eh, el = oracle_split(masked)
+    assert_exact(hi, eh, "hi part")
+    assert_exact(lo, el, "lo part")
+    _check_status(cb)
+    # below 2^20 outputs, with another major-ness, or in TF32 mode the tensor-core kernel keeps the product
+    small = cb.to_device(g[:64].copy())
+    assert cb.ops.matmul_path(small, dW, False, True, "3xtf32") == 0
+    assert cb.ops.matmul_path(dG, cb.to_device(w.T.copy()), False, False, "3xtf32") == 0
+    assert cb.ops.matmul_path(dG, dW, False, True, "tf32") != 2
