@@ -1246,39 +1246,55 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_k_kernel(const float* __res
                                                              int64_t m, int64_t n, int k, const float* __restrict__ mask,
                                                              float* __restrict__ out_hi, float* __restrict__ out_lo, int64_t split_pitch) {
     const int64_t j0 = (static_cast<int64_t>(blockIdx.x) * SK_THREADS + threadIdx.x) * 4;
-    if (j0 >= n) return;
+    const bool live = j0 < n;  // (no early return: every thread takes part in staging A)
     float bw[4][SK_MAXK];
 #pragma unroll
     for (int q = 0; q < 4; ++q)
 #pragma unroll
-        for (int l = 0; l < SK_MAXK; ++l) bw[q][l] = l < k ? __ldg(b + (j0 + q) * k + l) : 0.0f;
+        for (int l = 0; l < SK_MAXK; ++l) bw[q][l] = (live && l < k) ? __ldg(b + (j0 + q) * k + l) : 0.0f;
     const int64_t r0 = static_cast<int64_t>(blockIdx.y) * SK_ROWS;
-    const int64_t r1 = r0 + SK_ROWS < m ? r0 + SK_ROWS : m;
-#pragma unroll 4
-    for (int64_t r = r0; r < r1; ++r) {
-        float ar[SK_MAXK];
-#pragma unroll
-        for (int l = 0; l < SK_MAXK; ++l) ar[l] = l < k ? __ldg(a + r * k + l) : 0.0f;
-        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-        for (int l = 0; l < SK_MAXK; ++l)
-            if (l < k) {
-#pragma unroll
-                for (int q = 0; q < 4; ++q) acc[q] = __fadd_rn(acc[q], __fmul_rn(ar[l], bw[q][l]));
-            }
-        float4 x = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    const int rows_here = static_cast<int>(m - r0 < SK_ROWS ? m - r0 : SK_ROWS);
+    // this CTA's rows of A, once, through shared memory (every thread reads all of them)
+    __shared__ float a_sm[SK_ROWS][SK_MAXK];
+    for (int i = threadIdx.x; i < SK_ROWS * SK_MAXK; i += SK_THREADS) {
+        const int rr = i / SK_MAXK, l = i % SK_MAXK;
+        a_sm[rr][l] = (rr < rows_here && l < k) ? __ldg(a + (r0 + rr) * k + l) : 0.0f;
+    }
+    __syncthreads();
+    if (!live) return;
+    constexpr int G = 8;  // rows in flight per thread: their mask reads are issued together, then their stores
+    for (int rb = 0; rb < rows_here; rb += G) {
+        float4 y[G];
         if (mask != nullptr) {
-            const float4 y = __ldcs(reinterpret_cast<const float4*>(mask + r * n + j0));
-            x.x *= y.x > 0.0f ? 1.0f : 0.0f; x.y *= y.y > 0.0f ? 1.0f : 0.0f;
-            x.z *= y.z > 0.0f ? 1.0f : 0.0f; x.w *= y.w > 0.0f ? 1.0f : 0.0f;
+#pragma unroll
+            for (int g = 0; g < G; ++g)
+                if (rb + g < rows_here) y[g] = __ldcs(reinterpret_cast<const float4*>(mask + (r0 + rb + g) * n + j0));
         }
-        __stcs(reinterpret_cast<float4*>(c + r * n + j0), x);
-        if (out_hi != nullptr) {
-            float4 h, l4;
-            h.x = to_tf32_rna(x.x); h.y = to_tf32_rna(x.y); h.z = to_tf32_rna(x.z); h.w = to_tf32_rna(x.w);
-            l4.x = to_tf32_rna(x.x - h.x); l4.y = to_tf32_rna(x.y - h.y); l4.z = to_tf32_rna(x.z - h.z); l4.w = to_tf32_rna(x.w - h.w);
-            __stcs(reinterpret_cast<float4*>(out_hi + r * split_pitch + j0), h);
-            __stcs(reinterpret_cast<float4*>(out_lo + r * split_pitch + j0), l4);
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            if (rb + g >= rows_here) break;
+            const int64_t r = r0 + rb + g;
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int l = 0; l < SK_MAXK; ++l)
+                if (l < k) {
+                    const float av = a_sm[rb + g][l];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) acc[q] = __fadd_rn(acc[q], __fmul_rn(av, bw[q][l]));
+                }
+            float4 x = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            if (mask != nullptr) {
+                x.x *= y[g].x > 0.0f ? 1.0f : 0.0f; x.y *= y[g].y > 0.0f ? 1.0f : 0.0f;
+                x.z *= y[g].z > 0.0f ? 1.0f : 0.0f; x.w *= y[g].w > 0.0f ? 1.0f : 0.0f;
+            }
+            __stcs(reinterpret_cast<float4*>(c + r * n + j0), x);
+            if (out_hi != nullptr) {
+                float4 h, l4;
+                h.x = to_tf32_rna(x.x); h.y = to_tf32_rna(x.y); h.z = to_tf32_rna(x.z); h.w = to_tf32_rna(x.w);
+                l4.x = to_tf32_rna(x.x - h.x); l4.y = to_tf32_rna(x.y - h.y); l4.z = to_tf32_rna(x.z - h.z); l4.w = to_tf32_rna(x.w - h.w);
+                __stcs(reinterpret_cast<float4*>(out_hi + r * split_pitch + j0), h);
+                __stcs(reinterpret_cast<float4*>(out_lo + r * split_pitch + j0), l4);
+            }
         }
     }
 }
