@@ -11,6 +11,8 @@
 #include <string>
 #include <vector>
 
+#include <cstdio>
+
 #include "AutoDiff.h"
 #include "Ctorch_Error.h"
 #include "Ctorch_Scheduler.h"
@@ -54,11 +56,18 @@ public:
     void* comm_stream = nullptr;  // non-blocking stream for the gradient all-reduce
     void* ev_grad = nullptr;      // compute -> comm: "this gradient is final"
     void* ev_comm = nullptr;      // comm -> compute: "all gradients are reduced"
+    std::vector<void*> ev_param;  // comm -> compute, per parameter (W0, b0, W1, b1, ...): "this gradient is reduced"
+    std::vector<int> reduced_order;  // parameters in the order their all-reduces were issued this step
     void* pinned_loss = nullptr;  // page-locked slot the loss is copied into
     void* pinned_x = nullptr;     // page-locked staging for host inputs
     size_t pinned_x_bytes = 0;
     Tensor last_logits;
     bool keep_logits = false;
+    // CTORCH_DP_TRACE=1: device times of every all-reduce of step 10 relative to the step's start
+    bool trace = std::getenv("CTORCH_DP_TRACE") != nullptr;
+    void *tr_s[16] = {nullptr}, *tr_e[16] = {nullptr}, *tr_g[16] = {nullptr}, *tr_0 = nullptr, *tr_1 = nullptr, *tr_b = nullptr;
+    int64_t tr_elems[16] = {0};
+    int tr_n = 0;
     bool fresh_weights = false;  // corrected mode: backward reads the updated weights
     // Deferred losses: a step does not wait for the device.  Its loss is still copied to page-locked
     // memory by the step itself (slot steps_done % kLossSlots); the host reads the slots in sync_losses().
@@ -105,6 +114,8 @@ public:
         if (comm_stream) ctk_stream_destroy(comm_stream);
         if (ev_grad) ctk_event_destroy(ev_grad);
         if (ev_comm) ctk_event_destroy(ev_comm);
+        for (void* e : ev_param)
+            if (e) ctk_event_destroy(e);
         if (pinned_loss) ctk_free_host(pinned_loss);
         if (pinned_x) ctk_free_host(pinned_x);
         for (Staged& s : staged) {
@@ -146,13 +157,32 @@ public:
             cuda_check(ctk_event_create(&ev_comm), "event");
         }
         if (c) {
-            ctx.on_leaf_grad = [this](size_t, Tensor& g) {
+            ctx.on_leaf_grad = [this](size_t id, Tensor& g) {
                 // The gradient of this leaf just received its (only) contribution: reduce it across
                 // replicas on the communication stream while backward carries on.
                 void* compute = current_stream();
                 cuda_check(ctk_event_record(ev_grad, compute), "record");
                 cuda_check(ctk_stream_wait_event(comm_stream, ev_grad), "wait");
+                if (trace && tr_n < 16) {
+                    if (!tr_s[tr_n]) { ctk_event_create(&tr_s[tr_n]); ctk_event_create(&tr_e[tr_n]); ctk_event_create(&tr_g[tr_n]); }
+                    ctk_event_record(tr_g[tr_n], compute);
+                    ctk_event_record(tr_s[tr_n], comm_stream);
+                }
                 cuda_check(ctk_allreduce_sum_f32(comm, g.data<float>(), static_cast<int64_t>(g.numel()), comm_stream), "gradient all-reduce");
+                if (trace && tr_n < 16) {
+                    ctk_event_record(tr_e[tr_n], comm_stream);
+                    tr_elems[tr_n++] = static_cast<int64_t>(g.numel());
+                }
+                // which parameter this was, and an event of its own: its update waits for this
+                // all-reduce only, so the updates of the other layers run under the last all-reduce
+                for (size_t l = 0; l < W.size(); ++l) {
+                    const int p = id == W[l].id() ? static_cast<int>(2 * l) : id == b[l].id() ? static_cast<int>(2 * l + 1) : -1;
+                    if (p < 0) continue;
+                    if (ev_param.size() < 2 * W.size()) ev_param.resize(2 * W.size(), nullptr);
+                    if (!ev_param[p]) cuda_check(ctk_event_create(&ev_param[p]), "event");
+                    cuda_check(ctk_event_record(ev_param[p], comm_stream), "record");
+                    reduced_order.push_back(p);
+                }
             };
         } else {
             ctx.on_leaf_grad = nullptr;
@@ -191,6 +221,11 @@ public:
             if (graph.exec && st != graph.stream) release_graph();  // an eager step changes what the graph's buffers hold
             reserve_for(static_cast<int64_t>(x.sizes()[0]));
         }
+        if (trace) {
+            if (!tr_0) { ctk_event_create(&tr_0); ctk_event_create(&tr_1); ctk_event_create(&tr_b); }
+            tr_n = 0;
+            ctk_event_record(tr_0, st);
+        }
         for (size_t l = 0; l < W.size(); ++l) {
             ctx.make_leaf(W[l], true);
             ctx.make_leaf(b[l], true);
@@ -213,22 +248,45 @@ public:
             cuda_check(ctk_memcpy_d2h(slot, loss_value.data<float>(), sizeof(float), st), "loss read-back");
         }
         backward(loss);
+        if (trace) ctk_event_record(tr_b, st);
+        auto update = [&](Tensor& p) {
+            if (fresh_weights) p.sgd_update_shared_(grad(p), lr);
+            else p.sgd_update_(grad(p), lr);
+        };
+        std::vector<char> updated(2 * W.size(), 0);
         if (comm) {
+            // in the order the all-reduces were issued, each update behind its own all-reduce
+            for (int p : reduced_order) {
+                if (updated[p]) continue;
+                cuda_check(ctk_stream_wait_event(st, ev_param[p]), "wait");
+                update(p % 2 ? b[p / 2] : W[p / 2]);
+                updated[p] = 1;
+            }
+            reduced_order.clear();
             cuda_check(ctk_event_record(ev_comm, comm_stream), "record");
             cuda_check(ctk_stream_wait_event(st, ev_comm), "wait");
         }
         for (size_t l = 0; l < W.size(); ++l) {
-            if (fresh_weights) {
-                W[l].sgd_update_shared_(grad(W[l]), lr);
-                b[l].sgd_update_shared_(grad(b[l]), lr);
-            } else {
-                W[l].sgd_update_(grad(W[l]), lr);
-                b[l].sgd_update_(grad(b[l]), lr);
-            }
+            if (!updated[2 * l]) update(W[l]);
+            if (!updated[2 * l + 1]) update(b[l]);
         }
         if (keep_logits) last_logits = logits;
         const bool wait = !capturing && !deferred_loss;
+        if (trace) ctk_event_record(tr_1, st);
         if (wait) cuda_check(st ? ctk_stream_sync(st) : ctk_device_sync(), "step sync");
+        if (trace && wait && steps_done == 10) {
+            ctk_device_sync();
+            float t = 0, u = 0, v = 0;
+            ctk_event_elapsed_ms(tr_0, tr_b, &t);
+            ctk_event_elapsed_ms(tr_0, tr_1, &u);
+            std::fprintf(stderr, "[dp trace] backward issued-complete at %.3f ms, step end %.3f ms\n", t, u);
+            for (int i = 0; i < tr_n; ++i) {
+                ctk_event_elapsed_ms(tr_0, tr_g[i], &t);
+                ctk_event_elapsed_ms(tr_0, tr_s[i], &u);
+                ctk_event_elapsed_ms(tr_0, tr_e[i], &v);
+                std::fprintf(stderr, "[dp trace] all-reduce %d: %lld elems, gradient ready %.3f, starts %.3f, ends %.3f ms\n", i, static_cast<long long>(tr_elems[i]), t, u, v);
+            }
+        }
         ctx.release_step_nodes();
         ++steps_done;
         return wait ? *static_cast<float*>(pinned_loss) : 0.0f;
