@@ -56,6 +56,8 @@ public:
     void* comm_stream = nullptr;  // non-blocking stream for the gradient all-reduce
     void* ev_grad = nullptr;      // compute -> comm: "this gradient is final"
     void* ev_comm = nullptr;      // comm -> compute: "all gradients are reduced"
+    void* ev_go = nullptr;        // comm -> compute: "the all-reduce of the gradient just produced has been handed to the device"
+    bool headstart = std::getenv("CTORCH_DP_HEADSTART") != nullptr;
     std::vector<void*> ev_param;  // comm -> compute, per parameter (W0, b0, W1, b1, ...): "this gradient is reduced"
     std::vector<int> reduced_order;  // parameters in the order their all-reduces were issued this step
     void* pinned_loss = nullptr;  // page-locked slot the loss is copied into
@@ -114,6 +116,7 @@ public:
         if (comm_stream) ctk_stream_destroy(comm_stream);
         if (ev_grad) ctk_event_destroy(ev_grad);
         if (ev_comm) ctk_event_destroy(ev_comm);
+        if (ev_go) ctk_event_destroy(ev_go);
         for (void* e : ev_param)
             if (e) ctk_event_destroy(e);
         if (pinned_loss) ctk_free_host(pinned_loss);
@@ -163,6 +166,14 @@ public:
                 void* compute = current_stream();
                 cuda_check(ctk_event_record(ev_grad, compute), "record");
                 cuda_check(ctk_stream_wait_event(comm_stream, ev_grad), "wait");
+                if (headstart) {
+                    // The product that follows on the compute stream becomes eligible only once the
+                    // all-reduce stream has passed its wait, i.e. just after the all-reduce kernel was handed
+                    // to the device: the all-reduce's blocks are placed first instead of waiting for
+                    // a whole persistent product to end.
+                    if (!ev_go) cuda_check(ctk_event_create(&ev_go), "event");
+                    cuda_check(ctk_event_record(ev_go, comm_stream), "record");
+                }
                 if (trace && tr_n < 16) {
                     if (!tr_s[tr_n]) { ctk_event_create(&tr_s[tr_n]); ctk_event_create(&tr_e[tr_n]); ctk_event_create(&tr_g[tr_n]); }
                     ctk_event_record(tr_g[tr_n], compute);
@@ -173,6 +184,7 @@ public:
                     ctk_event_record(tr_e[tr_n], comm_stream);
                     tr_elems[tr_n++] = static_cast<int64_t>(g.numel());
                 }
+                if (headstart && g.numel() >= (1u << 20)) cuda_check(ctk_stream_wait_event(compute, ev_go), "wait");
                 // which parameter this was, and an event of its own: its update waits for this
                 // all-reduce only, so the updates of the other layers run under the last all-reduce
                 for (size_t l = 0; l < W.size(); ++l) {
