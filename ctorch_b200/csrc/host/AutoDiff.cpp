@@ -455,8 +455,25 @@ void AutoDiff::backward(Tensor& root, Tensor grad_output) {
         for (size_t input_id : node->input_ids) ++consumers[input_id];
     }
 
+    // A leaf's gradient is handed to on_leaf_grad once, after the LAST contribution of this pass: a
+    // leaf that enters several nodes (a shared weight, a bias used twice) is still being added to until
+    // every edge that ends in it has been walked.  `remaining` counts those edges down; the order is
+    // topological, so by the time a node is visited all of its own consumers have been.
+    std::unordered_map<size_t, int> remaining = consumers;
+    std::unordered_set<size_t> contributed;
+    auto edge_done = [&](size_t input_id) {
+        auto r = remaining.find(input_id);
+        if (r == remaining.end() || --r->second > 0) return;
+        if (!on_leaf_grad || !contributed.count(input_id)) return;
+        auto it = id_to_node.find(input_id);
+        if (it != id_to_node.end() && it->second && it->second->is_leaf && it->second->grad) on_leaf_grad(input_id, *it->second->grad);
+    };
+
     for (Node* node : order) {
-        if (!node->requires_grad || !node->grad) continue;
+        if (!node->requires_grad || !node->grad) {
+            for (size_t input_id : node->input_ids) edge_done(input_id);
+            continue;
+        }
         node->materialize_grad();  // an upstream gradient that was only flagged zero is read as zeros
         // The reference visits the inputs in recorded order (:1189).  The contributions of one node do
         // not depend on one another, so a product's second operand -- the weights, a leaf whose
@@ -466,7 +483,10 @@ void AutoDiff::backward(Tensor& root, Tensor grad_output) {
         if (node->operation == op::MatMul && visit.size() == 2 && visit[0] != visit[1]) std::swap(visit[0], visit[1]);
         for (size_t input_id : visit) {
             auto in_it = id_to_node.find(input_id);
-            if (in_it == id_to_node.end() || !in_it->second || !in_it->second->requires_grad) continue;
+            if (in_it == id_to_node.end() || !in_it->second || !in_it->second->requires_grad) {
+                edge_done(input_id);
+                continue;
+            }
             Node& input_node = *in_it->second;
             // The contribution, alone in its scope so that no temporary still shares its buffer when
             // it becomes the gradient (a hook that reduces the gradient in place would otherwise
@@ -475,7 +495,10 @@ void AutoDiff::backward(Tensor& root, Tensor grad_output) {
             {
                 bool skip = false;
                 Tensor val = rule(node, input_id, input_node, skip);
-                if (skip) continue;
+                if (skip) {
+                    edge_done(input_id);
+                    continue;
+                }
                 Tensor adjusted = check_and_adjust_grad_shape(val, input_node.tensor->sizes(), input_node.tensor->device());
                 if (adjusted.device() != input_node.tensor->device()) adjusted = adjusted.to(input_node.tensor->device());
                 contribution = std::make_unique<Tensor>(std::move(adjusted));
@@ -498,8 +521,8 @@ void AutoDiff::backward(Tensor& root, Tensor grad_output) {
                 const float* ap = add.data<float>();
                 for (size_t i = 0; i < acc.numel(); ++i) gp[i] += ap[i];
             }
-            Tensor& g = *input_node.grad;
-            if (input_node.is_leaf && on_leaf_grad) on_leaf_grad(input_id, g);
+            contributed.insert(input_id);
+            edge_done(input_id);
         }
     }
 }

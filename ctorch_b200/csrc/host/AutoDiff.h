@@ -92,7 +92,8 @@ public:
     void clear_graph();
 
     // ---- additions (no counterpart in the reference) ----
-    // Called during backward right after a leaf's gradient received a contribution; a data-parallel
+    // Called during backward once per leaf, right after that leaf's gradient received its LAST
+    // contribution of the pass (a leaf that enters several nodes is complete only then); a data-parallel
     // driver uses it to start that gradient's all-reduce while the rest of backward still runs.
     std::function<void(size_t tensor_id, Tensor& grad)> on_leaf_grad;
     // Drops every node that a future root can no longer reach: all non-leaf nodes and all leaves that

@@ -14,8 +14,8 @@
 #include <map>
 #include <memory>
 #include <mutex>
-#include <unordered_map>
 #include <unordered_set>
+#include <utility>
 #include <vector>
 
 #include "Ctools.h"
@@ -41,9 +41,12 @@ void* current_stream();                          // the calling thread's compute
 // private free list), never by anyone else.  A miss during capture is remembered -- the capture is
 // then abandoned by its owner -- because allocating in the middle of a capture is not allowed.
 class SizeKeyedCache {
+    // Buffers are parked per (device ordinal, size): a pointer handed out on one GPU is never handed
+    // to a tensor on another, however the calling thread switches devices in between.
+    using Key = std::pair<int, size_t>;
     std::mutex mu_;
-    std::unordered_map<size_t, std::vector<void*>> free_;      // anyone's
-    std::unordered_map<size_t, std::vector<void*>> pinned_free_;  // the graph's
+    std::map<Key, std::vector<void*>> free_;         // anyone's
+    std::map<Key, std::vector<void*>> pinned_free_;  // the graph's
     std::unordered_set<void*> pinned_;
     size_t parked_bytes_ = 0;
     bool capturing_ = false, missed_ = false;
@@ -52,24 +55,35 @@ protected:
     virtual ~SizeKeyedCache() = default;
     virtual size_t rounded(size_t bytes) const = 0;
     virtual size_t max_parked() const = 0;
-    virtual void* fresh(size_t bytes) = 0;
-    virtual void release(void* p) = 0;
+    virtual void* fresh(size_t bytes) = 0;            // on the current device
+    virtual void release(void* p, int device) = 0;
     virtual bool enabled() const { return true; }
 
 public:
-    void* get(size_t bytes) {
+    // Ordinal of the calling thread's current device (a subclass used in host-only tests overrides it).
+    virtual int current_device() const {
+        int dev = 0;
+        cuda_check(ctk_get_device(&dev), "current device");
+        return dev;
+    }
+    // A buffer of at least `bytes` on the current device; *device_out receives that device's ordinal,
+    // which put() wants back.
+    void* get(size_t bytes, int* device_out) {
         bytes = rounded(bytes);
+        const int dev = current_device();
+        if (device_out) *device_out = dev;
         if (enabled()) {
             std::lock_guard<std::mutex> lock(mu_);
+            const Key key(dev, bytes);
             if (capturing_) {
-                auto it = pinned_free_.find(bytes);
+                auto it = pinned_free_.find(key);
                 if (it != pinned_free_.end() && !it->second.empty()) {
                     void* p = it->second.back();
                     it->second.pop_back();
                     return p;
                 }
             }
-            auto it = free_.find(bytes);
+            auto it = free_.find(key);
             if (it != free_.end() && !it->second.empty()) {
                 void* p = it->second.back();
                 it->second.pop_back();
@@ -81,22 +95,23 @@ public:
         }
         return fresh(bytes);
     }
-    void put(void* p, size_t bytes) {
+    void put(void* p, size_t bytes, int device) {
         bytes = rounded(bytes);
         if (enabled()) {
             std::lock_guard<std::mutex> lock(mu_);
+            const Key key(device, bytes);
             if (capturing_) pinned_.insert(p);
             if (pinned_.count(p)) {
-                pinned_free_[bytes].push_back(p);
+                pinned_free_[key].push_back(p);
                 return;
             }
             if (parked_bytes_ + bytes <= max_parked()) {
-                free_[bytes].push_back(p);
+                free_[key].push_back(p);
                 parked_bytes_ += bytes;
                 return;
             }
         }
-        release(p);
+        release(p, device);
     }
     void begin_capture() {
         std::lock_guard<std::mutex> lock(mu_);
@@ -115,12 +130,21 @@ public:
         for (auto& kv : pinned_free_)
             for (void* p : kv.second) {
                 free_[kv.first].push_back(p);
-                parked_bytes_ += kv.first;
+                parked_bytes_ += kv.first.second;
             }
         pinned_free_.clear();
         pinned_.clear();
     }
 };
+
+// Frees on the device a buffer came from, whatever device the calling thread has current.
+inline void free_on_device(void* p, int device, bool longlived) {
+    int cur = -1;
+    const bool switched = ctk_get_device(&cur) == 0 && cur != device && ctk_set_device(device) == 0;
+    if (longlived) ctk_free_longlived(p);
+    else ctk_free(p);
+    if (switched) ctk_set_device(cur);
+}
 
 // Split buffers (hi/lo copies of MatMul operands) are large -- twice the operand -- and come and go
 // with every activation of every step.  They are plain device allocations, outside the
@@ -134,7 +158,7 @@ class SplitBufferCache : public SizeKeyedCache {
         cuda_check(ctk_malloc_longlived(&p, bytes), "Storage: split buffer");  // a miss: warm-up only
         return p;
     }
-    void release(void* p) override { ctk_free_longlived(p); }
+    void release(void* p, int device) override { free_on_device(p, device, true); }
 
 public:
     static SplitBufferCache& instance() {
@@ -155,7 +179,7 @@ class DeviceBlockCache : public SizeKeyedCache {
         cuda_check(ctk_malloc(&p, bytes), "Storage: device allocation");
         return p;
     }
-    void release(void* p) override { ctk_free(p); }
+    void release(void* p, int device) override { free_on_device(p, device, false); }
     bool enabled() const override {
         static const bool on = [] {
             const char* e = std::getenv("CTORCH_BLOCK_CACHE");
@@ -174,10 +198,11 @@ public:
 struct KeptSplit {
     void* buf = nullptr;
     size_t bytes = 0;
+    int device = 0;  // ordinal of the GPU the buffer lives on
     int valid = 0;
     int64_t view[4] = {0, 0, 0, 0};  // element offset, outer extent, inner (contiguous) extent, outer pitch
     ~KeptSplit() {
-        if (buf) SplitBufferCache::instance().put(buf, bytes);
+        if (buf) SplitBufferCache::instance().put(buf, bytes, device);
     }
 };
 
@@ -186,15 +211,16 @@ class Storage {
         void* ptr = nullptr;
         size_t bytes = 0;
         DeviceType device = DeviceType::kCPU;
+        int ordinal = 0;                   // kCUDA: which GPU (the one current when the block was made)
         std::unique_ptr<KeptSplit> split;  // dropped whenever the buffer is about to be written
         Block(size_t b, DeviceType d) : bytes(b), device(d) {
             if (b == 0) return;
-            if (d == DeviceType::kCUDA) ptr = DeviceBlockCache::instance().get(b);
+            if (d == DeviceType::kCUDA) ptr = DeviceBlockCache::instance().get(b, &ordinal);
             else ptr = ::operator new(b);
         }
         ~Block() {
             if (!ptr) return;
-            if (device == DeviceType::kCUDA) DeviceBlockCache::instance().put(ptr, bytes);
+            if (device == DeviceType::kCUDA) DeviceBlockCache::instance().put(ptr, bytes, ordinal);
             else ::operator delete(ptr);
         }
         Block(const Block&) = delete;
@@ -276,7 +302,7 @@ public:
         KeptSplit* k = _data->split.get();
         if (k && k->view[0] == offset && k->view[1] == outer && k->view[2] == inner && k->view[3] == pitch) return k;
         auto fresh = std::make_unique<KeptSplit>();
-        fresh->buf = SplitBufferCache::instance().get(bytes);
+        fresh->buf = SplitBufferCache::instance().get(bytes, &fresh->device);
         fresh->bytes = bytes;
         fresh->view[0] = offset; fresh->view[1] = outer; fresh->view[2] = inner; fresh->view[3] = pitch;
         _data->split = std::move(fresh);

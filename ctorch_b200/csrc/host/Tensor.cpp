@@ -820,21 +820,28 @@ void Tensor::sgd_update_(const Tensor& g, float lr) {
     if (g.numel() != numel()) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DIMENSION, "sgd_update_: gradient has a different size");
     if (_device != DeviceType::kCUDA || g.device() != DeviceType::kCUDA)
         Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DEVICE_COMPAT, "sgd_update_: device tensors expected");
+    if (!g.is_contiguous()) Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DIMENSION, "sgd_update_: contiguous gradient expected");
+    sgd_update_from_(g.data<float>(), lr);
+}
+
+void Tensor::sgd_update_from_(const float* g_device, float lr) {
+    if (_device != DeviceType::kCUDA || _dtype != DType::kFloat)
+        Ctorch_Error::throwException(ErrorPlatform::kGENERAL, ErrorType::DEVICE_COMPAT, "sgd_update_: float device tensor expected");
     // A weight matrix that enters products (its buffer carries a kept hi/lo split) gets the split of
     // its new value from the update kernel itself instead of a separate pass before the next product.
-    const bool resplit = _storage.has_split() && _shape.size() == 2 && is_contiguous() && g.is_contiguous() && _shape[1] % 4 == 0 &&
-                         _storage_offset % 4 == 0 && g.storage_offset() % 4 == 0;
+    const bool resplit = _storage.has_split() && _shape.size() == 2 && is_contiguous() && _shape[1] % 4 == 0 && _storage_offset % 4 == 0 &&
+                         (reinterpret_cast<uintptr_t>(g_device) & 15u) == 0;
     float* p = data<float>();  // detaches from sharers, drops the split of the old value
     if (resplit) {
         const int64_t outer = static_cast<int64_t>(_shape[0]), inner = static_cast<int64_t>(_shape[1]);
         KeptSplit* ks = _storage.kept_split(static_cast<int64_t>(_storage_offset), outer, inner, inner, ctk_matmul_split_bytes(inner, outer));
         if (ks) {
-            cuda_check(ctk_sgd_update_split_f32(p, g.data<float>(), lr, outer, inner, inner, ks->buf, t_stream), "sgd_update_ (with split)");
+            cuda_check(ctk_sgd_update_split_f32(p, g_device, lr, outer, inner, inner, ks->buf, t_stream), "sgd_update_ (with split)");
             ks->valid = 1;
             return;
         }
     }
-    cuda_check(ctk_sgd_update_f32(p, g.data<float>(), lr, static_cast<int64_t>(numel()), t_stream), "sgd_update_");
+    cuda_check(ctk_sgd_update_f32(p, g_device, lr, static_cast<int64_t>(numel()), t_stream), "sgd_update_");
 }
 
 // ---- free functions (src/Tensor.cpp:1373-1453) ---------------------------------------------------------------

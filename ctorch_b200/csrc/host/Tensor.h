@@ -174,6 +174,10 @@ public:
     // In-place p -= g*lr on this tensor's device: the SGD loop that user code writes on raw host
     // pointers in the reference (mnist/mnist.cpp:80-92).
     void sgd_update_(const Tensor& g, float lr);
+    // The same update with the gradient given as a raw device pointer to numel() contiguous floats
+    // (16-byte aligned for the form that also rewrites the kept split): gradients that live in a
+    // communicator's registered buffer instead of a Tensor.
+    void sgd_update_from_(const float* g_device, float lr);
     // The same update written THROUGH to every tensor that shares this buffer -- in particular the copy
     // the tape took when the parameter was registered, which the reference's backward keeps reading
     // while the live weights move on (src/AutoDiff.cpp:286-290, :1651).  With this form backward sees

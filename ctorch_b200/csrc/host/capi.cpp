@@ -9,6 +9,7 @@
 #include <cstring>
 #include <memory>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #include <cstdio>
@@ -43,6 +44,11 @@ int guarded(F&& f) {
 
 Tensor* T(void* h) { return static_cast<Tensor*>(h); }
 
+std::unordered_map<AutoDiff*, std::shared_ptr<std::unordered_map<size_t, uint64_t>>>& g_leaf_counts() {
+    static std::unordered_map<AutoDiff*, std::shared_ptr<std::unordered_map<size_t, uint64_t>>> m;
+    return m;
+}
+
 // ---------------------------------------------------------------------------------------------------
 // MlpTrainer: x -> (matmul W + b -> relu)* -> matmul W + b -> cross_entropy(one-hot) -> backward -> SGD
 // ---------------------------------------------------------------------------------------------------
@@ -56,20 +62,34 @@ public:
     void* comm_stream = nullptr;  // non-blocking stream for the gradient all-reduce
     void* ev_grad = nullptr;      // compute -> comm: "this gradient is final"
     void* ev_comm = nullptr;      // comm -> compute: "all gradients are reduced"
-    void* ev_go = nullptr;        // comm -> compute: "the all-reduce of the gradient just produced has been handed to the device"
-    bool headstart = std::getenv("CTORCH_DP_HEADSTART") != nullptr;
     std::vector<void*> ev_param;  // comm -> compute, per parameter (W0, b0, W1, b1, ...): "this gradient is reduced"
     std::vector<int> reduced_order;  // parameters in the order their all-reduces were issued this step
+    // How the gradients cross the ranks (cth_mlp_set_dp_mode):
+    //   DP_INPLACE  each gradient is all-reduced where backward left it, the moment it is complete;
+    //   DP_ARENA    gradients are copied into one buffer registered with the communicator (so NCCL can
+    //               reduce in the switch straight out of it with few CTAs) and all-reduced there, one
+    //               call per layer (weights and bias together), under backward;
+    //   DP_SERIAL   the same buffer, ONE all-reduce after backward: nothing shares the SMs with the
+    //               products, the exchange is fully exposed;
+    //   DP_SHARDED  reduce-scatter per parameter under backward, SGD on the shard this rank owns,
+    //               all-gather of the updated weights (parameters whose size is not a multiple of
+    //               4 * world -- the 10-class bias -- stay on the all-reduce path).
+    enum DpMode { DP_INPLACE = 0, DP_ARENA = 1, DP_SERIAL = 2, DP_SHARDED = 3 };
+    int dp_mode = DP_INPLACE;
+    int comm_world = 1, comm_rank = 0;
+    float* arena = nullptr;             // registered gradient buffer (modes 1-3), slots in parameter order
+    std::vector<int64_t> slot_off;      // per parameter (W0, b0, W1, ...): offset of its slot in floats
+    std::vector<int64_t> slot_len;      // ... and the slot's padded length (a multiple of 4 * world)
+    std::vector<void*> ev_upd, ev_ag;   // sharded: shard updated (compute -> comm), weights gathered (comm -> compute)
+    std::vector<char> in_arena;         // this step: the parameter's gradient has been copied to its slot
+    void* ev_done = nullptr;            // compute: end of the step (what the bounded wait watches)
+    int comm_timeout_ms = 30000;        // a step that has not completed by then has lost a peer
+    bool comm_failed = false;
     void* pinned_loss = nullptr;  // page-locked slot the loss is copied into
     void* pinned_x = nullptr;     // page-locked staging for host inputs
     size_t pinned_x_bytes = 0;
     Tensor last_logits;
     bool keep_logits = false;
-    // CTORCH_DP_TRACE=1: device times of every all-reduce of step 10 relative to the step's start
-    bool trace = std::getenv("CTORCH_DP_TRACE") != nullptr;
-    void *tr_s[16] = {nullptr}, *tr_e[16] = {nullptr}, *tr_g[16] = {nullptr}, *tr_0 = nullptr, *tr_1 = nullptr, *tr_b = nullptr;
-    int64_t tr_elems[16] = {0};
-    int tr_n = 0;
     bool fresh_weights = false;  // corrected mode: backward reads the updated weights
     // Deferred losses: a step does not wait for the device.  Its loss is still copied to page-locked
     // memory by the step itself (slot steps_done % kLossSlots); the host reads the slots in sync_losses().
@@ -116,9 +136,11 @@ public:
         if (comm_stream) ctk_stream_destroy(comm_stream);
         if (ev_grad) ctk_event_destroy(ev_grad);
         if (ev_comm) ctk_event_destroy(ev_comm);
-        if (ev_go) ctk_event_destroy(ev_go);
-        for (void* e : ev_param)
-            if (e) ctk_event_destroy(e);
+        for (auto* v : {&ev_param, &ev_upd, &ev_ag})
+            for (void* e : *v)
+                if (e) ctk_event_destroy(e);
+        if (ev_done) ctk_event_destroy(ev_done);
+        if (arena && comm) ctk_comm_free(comm, arena);
         if (pinned_loss) ctk_free_host(pinned_loss);
         if (pinned_x) ctk_free_host(pinned_x);
         for (Staged& s : staged) {
@@ -148,8 +170,34 @@ public:
         return n;
     }
 
+    Tensor& param(int p) { return p % 2 ? b[p / 2] : W[p / 2]; }
+    int param_index(size_t id) const {
+        for (size_t l = 0; l < W.size(); ++l) {
+            if (id == W[l].id()) return static_cast<int>(2 * l);
+            if (id == b[l].id()) return static_cast<int>(2 * l + 1);
+        }
+        return -1;
+    }
+    bool sharded_param(int p) { return dp_mode == DP_SHARDED && static_cast<int64_t>(param(p).numel()) % (4 * comm_world) == 0; }
+    void* event_in(std::vector<void*>& v, int p) {
+        if (v.size() < 2 * W.size()) v.resize(2 * W.size(), nullptr);
+        if (!v[p]) cuda_check(ctk_event_create(&v[p]), "event");
+        return v[p];
+    }
+
+    void set_dp_mode(int mode) {
+        if (mode < DP_INPLACE || mode > DP_SHARDED) throw std::runtime_error("cth_mlp_set_dp_mode: 0 in place, 1 registered buffer, 2 one all-reduce after backward, 3 sharded update");
+        if (comm) throw std::runtime_error("cth_mlp_set_dp_mode: choose the mode before cth_mlp_set_comm");
+        dp_mode = mode;
+    }
+
     void set_comm(void* c) {
+        if (!c && comm) {
+            cuda_check(ctk_device_sync(), "set_comm sync");
+            if (arena) { ctk_comm_free(comm, arena); arena = nullptr; }
+        }
         comm = c;
+        comm_failed = false;
         if (c && !comm_stream) {
             // Highest priority: the MatMul kernels are persistent and hold every SM until they end, so
             // an all-reduce gets SMs only at a product's boundary -- and only if its blocks are placed
@@ -159,46 +207,67 @@ public:
             cuda_check(ctk_event_create(&ev_grad), "event");
             cuda_check(ctk_event_create(&ev_comm), "event");
         }
-        if (c) {
-            ctx.on_leaf_grad = [this](size_t id, Tensor& g) {
-                // The gradient of this leaf just received its (only) contribution: reduce it across
-                // replicas on the communication stream while backward carries on.
-                void* compute = current_stream();
-                cuda_check(ctk_event_record(ev_grad, compute), "record");
-                cuda_check(ctk_stream_wait_event(comm_stream, ev_grad), "wait");
-                if (headstart) {
-                    // The product that follows on the compute stream becomes eligible only once the
-                    // all-reduce stream has passed its wait, i.e. just after the all-reduce kernel was handed
-                    // to the device: the all-reduce's blocks are placed first instead of waiting for
-                    // a whole persistent product to end.
-                    if (!ev_go) cuda_check(ctk_event_create(&ev_go), "event");
-                    cuda_check(ctk_event_record(ev_go, comm_stream), "record");
-                }
-                if (trace && tr_n < 16) {
-                    if (!tr_s[tr_n]) { ctk_event_create(&tr_s[tr_n]); ctk_event_create(&tr_e[tr_n]); ctk_event_create(&tr_g[tr_n]); }
-                    ctk_event_record(tr_g[tr_n], compute);
-                    ctk_event_record(tr_s[tr_n], comm_stream);
-                }
-                cuda_check(ctk_allreduce_sum_f32(comm, g.data<float>(), static_cast<int64_t>(g.numel()), comm_stream), "gradient all-reduce");
-                if (trace && tr_n < 16) {
-                    ctk_event_record(tr_e[tr_n], comm_stream);
-                    tr_elems[tr_n++] = static_cast<int64_t>(g.numel());
-                }
-                if (headstart && g.numel() >= (1u << 20)) cuda_check(ctk_stream_wait_event(compute, ev_go), "wait");
-                // which parameter this was, and an event of its own: its update waits for this
-                // all-reduce only, so the updates of the other layers run under the last all-reduce
-                for (size_t l = 0; l < W.size(); ++l) {
-                    const int p = id == W[l].id() ? static_cast<int>(2 * l) : id == b[l].id() ? static_cast<int>(2 * l + 1) : -1;
-                    if (p < 0) continue;
-                    if (ev_param.size() < 2 * W.size()) ev_param.resize(2 * W.size(), nullptr);
-                    if (!ev_param[p]) cuda_check(ctk_event_create(&ev_param[p]), "event");
-                    cuda_check(ctk_event_record(ev_param[p], comm_stream), "record");
-                    reduced_order.push_back(p);
-                }
-            };
-        } else {
+        if (c && !ev_done) cuda_check(ctk_event_create(&ev_done), "event");
+        if (!c) {
             ctx.on_leaf_grad = nullptr;
+            return;
         }
+        cuda_check(ctk_comm_info(c, &comm_world, &comm_rank, nullptr), "communicator info");
+        if (dp_mode != DP_INPLACE) {
+            // one slot per parameter, in parameter order, each padded to a multiple of 4 * world floats so
+            // that every rank's shard of it starts on a 16-byte boundary
+            slot_off.assign(2 * W.size(), 0);
+            slot_len.assign(2 * W.size(), 0);
+            int64_t total = 0;
+            const int64_t q = 4 * static_cast<int64_t>(comm_world);
+            for (size_t p = 0; p < 2 * W.size(); ++p) {
+                slot_off[p] = total;
+                slot_len[p] = (static_cast<int64_t>(param(static_cast<int>(p)).numel()) + q - 1) / q * q;
+                total += slot_len[p];
+            }
+            void* buf = nullptr;
+            const char* sym = std::getenv("CTORCH_DP_SYMMETRIC");
+            cuda_check(ctk_comm_alloc(c, static_cast<size_t>(total) * sizeof(float), (sym && sym[0] == '1') ? 1 : 0, &buf), "gradient buffer");
+            arena = static_cast<float*>(buf);
+            cuda_check(ctk_memset(arena, 0, static_cast<size_t>(total) * sizeof(float), nullptr), "gradient buffer clear");  // the pads stay zero for good
+            cuda_check(ctk_device_sync(), "gradient buffer clear");
+        }
+        ctx.on_leaf_grad = [this](size_t id, Tensor& g) {
+            // The gradient of this leaf is complete: exchange it on the communication stream while
+            // backward carries on.
+            const int p = param_index(id);
+            if (p < 0) return;
+            void* compute = current_stream();
+            cuda_check(ctk_event_record(ev_grad, compute), "record");
+            cuda_check(ctk_stream_wait_event(comm_stream, ev_grad), "wait");
+            const Tensor& gc = g;
+            const int64_t n = static_cast<int64_t>(g.numel());
+            if (dp_mode == DP_INPLACE) {
+                cuda_check(ctk_allreduce_sum_f32(comm, g.data<float>(), n, comm_stream), "gradient all-reduce");
+            } else {
+                float* slot = arena + slot_off[p];
+                cuda_check(ctk_memcpy_d2d(slot, gc.data<float>(), static_cast<size_t>(n) * sizeof(float), comm_stream), "gradient copy");
+                in_arena[p] = 1;
+                if (dp_mode == DP_SERIAL) return;  // one all-reduce of the whole buffer after backward
+                if (sharded_param(p)) {
+                    const int64_t chunk = slot_len[p] / comm_world;
+                    cuda_check(ctk_reduce_scatter_sum_f32(comm, slot, slot + comm_rank * chunk, chunk, comm_stream), "gradient reduce-scatter");
+                } else if (dp_mode == DP_ARENA && p % 2 == 0 && in_arena[p + 1]) {
+                    // the layer's bias (visited just before its weights) sits in the next slot: one call for both
+                    cuda_check(ctk_allreduce_sum_f32(comm, slot, slot_len[p] + slot_len[p + 1], comm_stream), "gradient all-reduce");
+                    cuda_check(ctk_event_record(event_in(ev_param, p + 1), comm_stream), "record");
+                    reduced_order.push_back(p + 1);
+                } else if (dp_mode == DP_ARENA && p % 2 == 1) {
+                    return;  // a bias: travels with its layer's weights (or, failing that, after backward)
+                } else {
+                    cuda_check(ctk_allreduce_sum_f32(comm, slot, slot_len[p], comm_stream), "gradient all-reduce");
+                }
+            }
+            // an event of its own: this parameter's update waits for its own exchange only, so the
+            // updates of the other layers run under the last exchange
+            cuda_check(ctk_event_record(event_in(ev_param, p), comm_stream), "record");
+            reduced_order.push_back(p);
+        };
     }
 
     Tensor forward(const Tensor& x) {
@@ -233,11 +302,8 @@ public:
             if (graph.exec && st != graph.stream) release_graph();  // an eager step changes what the graph's buffers hold
             reserve_for(static_cast<int64_t>(x.sizes()[0]));
         }
-        if (trace) {
-            if (!tr_0) { ctk_event_create(&tr_0); ctk_event_create(&tr_1); ctk_event_create(&tr_b); }
-            tr_n = 0;
-            ctk_event_record(tr_0, st);
-        }
+        if (comm_failed) throw std::runtime_error("the communicator of this trainer was aborted after a peer failed to take part; detach it (cth_mlp_set_comm(NULL)) or attach a new one");
+        in_arena.assign(2 * W.size(), 0);
         for (size_t l = 0; l < W.size(); ++l) {
             ctx.make_leaf(W[l], true);
             ctx.make_leaf(b[l], true);
@@ -260,44 +326,83 @@ public:
             cuda_check(ctk_memcpy_d2h(slot, loss_value.data<float>(), sizeof(float), st), "loss read-back");
         }
         backward(loss);
-        if (trace) ctk_event_record(tr_b, st);
-        auto update = [&](Tensor& p) {
-            if (fresh_weights) p.sgd_update_shared_(grad(p), lr);
-            else p.sgd_update_(grad(p), lr);
+        auto update = [&](int p) {
+            Tensor& t = param(p);
+            if (comm && dp_mode != DP_INPLACE && in_arena[p]) {
+                float* slot = arena + slot_off[p];
+                if (sharded_param(p)) {
+                    // SGD on the shard this rank owns (the same single fused multiply-add per element), then
+                    // every rank's shard travels to everyone.  The weights' kept split is dropped by the
+                    // write access; the next product that reads them makes it again.
+                    const int64_t chunk = slot_len[p] / comm_world, first = comm_rank * chunk;
+                    float* w = t.data<float>();
+                    cuda_check(ctk_sgd_update_f32(w + first, slot + first, lr, chunk, st), "sharded update");
+                    cuda_check(ctk_event_record(event_in(ev_upd, p), st), "record");
+                    cuda_check(ctk_stream_wait_event(comm_stream, ev_upd[p]), "wait");
+                    cuda_check(ctk_allgather_f32(comm, w + first, w, chunk, comm_stream), "weight all-gather");
+                    cuda_check(ctk_event_record(event_in(ev_ag, p), comm_stream), "record");
+                    return;
+                }
+                t.sgd_update_from_(slot, lr);
+                return;
+            }
+            if (fresh_weights) t.sgd_update_shared_(grad(t), lr);
+            else t.sgd_update_(grad(t), lr);
         };
         std::vector<char> updated(2 * W.size(), 0);
         if (comm) {
-            // in the order the all-reduces were issued, each update behind its own all-reduce
-            for (int p : reduced_order) {
-                if (updated[p]) continue;
-                cuda_check(ctk_stream_wait_event(st, ev_param[p]), "wait");
-                update(p % 2 ? b[p / 2] : W[p / 2]);
-                updated[p] = 1;
+            if (dp_mode == DP_SERIAL) {
+                // everything backward produced is in the buffer: one all-reduce, then the updates
+                cuda_check(ctk_event_record(ev_grad, st), "record");
+                cuda_check(ctk_stream_wait_event(comm_stream, ev_grad), "wait");
+                cuda_check(ctk_allreduce_sum_f32(comm, arena, slot_off.back() + slot_len.back(), comm_stream), "gradient all-reduce");
+                cuda_check(ctk_event_record(ev_comm, comm_stream), "record");
+                cuda_check(ctk_stream_wait_event(st, ev_comm), "wait");
+            } else {
+                // a gradient that is in the buffer but was not exchanged under backward (a bias whose
+                // weights produced no gradient) goes now
+                for (int p = 0; dp_mode == DP_ARENA && p < static_cast<int>(2 * W.size()); ++p) {
+                    bool sent = false;
+                    for (int q : reduced_order) sent = sent || q == p;
+                    if (!in_arena[p] || sent) continue;
+                    cuda_check(ctk_event_record(ev_grad, st), "record");
+                    cuda_check(ctk_stream_wait_event(comm_stream, ev_grad), "wait");
+                    cuda_check(ctk_allreduce_sum_f32(comm, arena + slot_off[p], slot_len[p], comm_stream), "gradient all-reduce");
+                    cuda_check(ctk_event_record(event_in(ev_param, p), comm_stream), "record");
+                    reduced_order.push_back(p);
+                }
+                // in the order the exchanges were issued, each update behind its own
+                for (int p : reduced_order) {
+                    if (updated[p]) continue;
+                    cuda_check(ctk_stream_wait_event(st, ev_param[p]), "wait");
+                    update(p);
+                    updated[p] = 1;
+                }
             }
             reduced_order.clear();
+        }
+        for (int p = 0; p < static_cast<int>(2 * W.size()); ++p)
+            if (!updated[p]) update(p);
+        if (comm) {
+            // the step ends when the communication stream has nothing left (sharded: the gathered weights)
             cuda_check(ctk_event_record(ev_comm, comm_stream), "record");
             cuda_check(ctk_stream_wait_event(st, ev_comm), "wait");
         }
-        for (size_t l = 0; l < W.size(); ++l) {
-            if (!updated[2 * l]) update(W[l]);
-            if (!updated[2 * l + 1]) update(b[l]);
-        }
         if (keep_logits) last_logits = logits;
         const bool wait = !capturing && !deferred_loss;
-        if (trace) ctk_event_record(tr_1, st);
-        if (wait) cuda_check(st ? ctk_stream_sync(st) : ctk_device_sync(), "step sync");
-        if (trace && wait && steps_done == 10) {
-            ctk_device_sync();
-            float t = 0, u = 0, v = 0;
-            ctk_event_elapsed_ms(tr_0, tr_b, &t);
-            ctk_event_elapsed_ms(tr_0, tr_1, &u);
-            std::fprintf(stderr, "[dp trace] backward issued-complete at %.3f ms, step end %.3f ms\n", t, u);
-            for (int i = 0; i < tr_n; ++i) {
-                ctk_event_elapsed_ms(tr_0, tr_g[i], &t);
-                ctk_event_elapsed_ms(tr_0, tr_s[i], &u);
-                ctk_event_elapsed_ms(tr_0, tr_e[i], &v);
-                std::fprintf(stderr, "[dp trace] all-reduce %d: %lld elems, gradient ready %.3f, starts %.3f, ends %.3f ms\n", i, static_cast<long long>(tr_elems[i]), t, u, v);
+        if (wait && comm) {
+            // Bounded: a peer that died or never joined leaves the collective spinning on the GPU; the wait
+            // polls the step's end and the communicator's health and gives up at the deadline (the
+            // communicator is aborted, which ends its kernels; the context stays usable).
+            cuda_check(ctk_event_record(ev_done, st), "record");
+            const int rc = ctk_comm_wait(comm, ev_done, comm_timeout_ms);
+            if (rc) {
+                comm_failed = true;
+                ctx.release_step_nodes();
+                throw std::runtime_error(std::string("data-parallel step: ") + ctk_last_error());
             }
+        } else if (wait) {
+            cuda_check(st ? ctk_stream_sync(st) : ctk_device_sync(), "step sync");
         }
         ctx.release_step_nodes();
         ++steps_done;
@@ -592,15 +697,21 @@ public:
             out += b[l].numel();
         }
     }
+    // The gradients the last step applied (data parallel: summed over the ranks).  Sharded mode: only
+    // this rank's shard of a sharded parameter is the sum; the rest of its slot holds local values.
     void get_grads(float* out) {
         AutoDiffContext::Guard guard(&ctx);
-        for (size_t l = 0; l < W.size(); ++l) {
-            Tensor gw = grad(W[l]);
-            gw.copy_to_host(out, gw.numel());
-            out += gw.numel();
-            Tensor gb = grad(b[l]);
-            gb.copy_to_host(out, gb.numel());
-            out += gb.numel();
+        for (int p = 0; p < static_cast<int>(2 * W.size()); ++p) {
+            Tensor& t = param(p);
+            if (comm && dp_mode != DP_INPLACE && arena) {
+                cuda_check(ctk_device_sync(), "get_grads sync");
+                cuda_check(ctk_memcpy_d2h(out, arena + slot_off[p], t.numel() * sizeof(float), nullptr), "gradient read-back");
+                cuda_check(ctk_device_sync(), "get_grads sync");
+            } else {
+                Tensor g = grad(t);
+                g.copy_to_host(out, g.numel());
+            }
+            out += t.numel();
         }
     }
 };
@@ -613,6 +724,60 @@ const char* cth_last_error(void) { return t_err.c_str(); }
 void cth_set_quiet(int q) { Ctorch_Error::setQuiet(q != 0); }
 uint64_t cth_error_count(void) { return Ctorch_Error::errorCount(); }
 int cth_cuda_available(void) { return Ctorch_Scheduler::isDeviceAvailable(DeviceType::kCUDA) ? 1 : 0; }
+
+// Host-only self-test of the buffer caches' keying (needs no GPU): a cache with a fake allocator and a
+// fake "current device" must never hand a buffer parked on one device to a request made on another,
+// must give a parked buffer back to a request on its own device, and must release overflow with the
+// device the buffer came from.  *failed receives the number of checks that did not hold.
+int cth_selftest_cache_keying(int* failed) {
+    return guarded([&] {
+        struct Fake : SizeKeyedCache {
+            int dev = 0, made = 0;
+            std::vector<std::pair<void*, int>> released;
+            size_t rounded(size_t b) const override { return (b + 511) & ~size_t(511); }
+            size_t max_parked() const override { return 2048; }
+            void* fresh(size_t) override { return reinterpret_cast<void*>(static_cast<uintptr_t>(dev + 1) * 0x10000000u + 0x1000u * static_cast<uintptr_t>(++made)); }
+            void release(void* p, int d) override { released.emplace_back(p, d); }
+            int current_device() const override { return dev; }
+        } c;
+        int bad = 0, d = -1;
+        c.dev = 0;
+        void* p0 = c.get(1000, &d);
+        bad += d != 0;
+        c.put(p0, 1000, d);
+        c.dev = 1;
+        void* q = c.get(1000, &d);            // same size, other device: must not be p0
+        bad += (q == p0) + (d != 1) + (c.made != 2);
+        c.put(q, 1000, d);
+        void* q2 = c.get(1000, &d);           // device 1's own buffer comes back
+        bad += q2 != q;
+        c.dev = 0;
+        void* p1 = c.get(1000, &d);           // and device 0's
+        bad += (p1 != p0) + (d != 0);
+        c.put(p1, 1000, 0);                   // parked: 1024 bytes
+        c.put(q2, 1000, 1);                   // parked: 2048 bytes = the limit
+        void* extra = c.get(3000, &d);        // another size: a miss
+        bad += c.made != 3;
+        c.put(extra, 3000, 0);                // over the limit: released, with its device
+        bad += !(c.released.size() == 1 && c.released[0].first == extra && c.released[0].second == 0);
+        // a captured sequence pins what it touches to the graph; after release_graph it is anyone's (of that device)
+        c.begin_capture();
+        void* g0 = c.get(1000, &d);
+        c.put(g0, 1000, 0);
+        void* g1 = c.get(1000, &d);
+        bad += (g0 != p0) + (g1 != g0);
+        c.put(g1, 1000, 0);
+        bad += !c.end_capture();
+        c.dev = 1;
+        c.begin_capture();
+        void* h = c.get(1000, &d);            // device 1 must not see device 0's pinned buffer
+        bad += h != q;
+        c.put(h, 1000, 1);
+        c.end_capture();
+        c.release_graph();
+        *failed = bad;
+    });
+}
 
 // ---- tensors ----
 int cth_tensor_from_host(const float* data, const int64_t* shape, int rank, int device, void** out) {
@@ -758,6 +923,7 @@ int cth_ctx_create(void** out) {
 int cth_ctx_destroy(void* c) {
     return guarded([&] {
         if (AutoDiffContext::current() == c) AutoDiffContext::current() = nullptr;
+        g_leaf_counts().erase(static_cast<AutoDiff*>(c));
         delete static_cast<AutoDiff*>(c);
     });
 }
@@ -775,6 +941,26 @@ int cth_ctx_release_step_nodes(void* c) {
 }
 int cth_ctx_set_fuse_relu_backward(void* c, int on) {
     return guarded([&] { static_cast<AutoDiff*>(c)->set_fuse_relu_backward(on != 0); });
+}
+// Installs a hook that only counts: how often on_leaf_grad fired, per tensor id (a debugging aid, and
+// what the test of "once per leaf, after its last contribution" reads).  on = 0 removes it.
+int cth_ctx_count_leaf_grads(void* c, int on) {
+    return guarded([&] {
+        auto* ctx = static_cast<AutoDiff*>(c);
+        if (!on) { ctx->on_leaf_grad = nullptr; return; }
+        auto counts = std::make_shared<std::unordered_map<size_t, uint64_t>>();
+        g_leaf_counts()[ctx] = counts;
+        ctx->on_leaf_grad = [counts](size_t id, Tensor&) { ++(*counts)[id]; };
+    });
+}
+int cth_ctx_leaf_grad_count(void* c, void* t, uint64_t* n) {
+    return guarded([&] {
+        auto it = g_leaf_counts().find(static_cast<AutoDiff*>(c));
+        *n = 0;
+        if (it == g_leaf_counts().end()) return;
+        auto f = it->second->find(T(t)->id());
+        if (f != it->second->end()) *n = f->second;
+    });
 }
 int cth_ctx_make_leaf(void* c, void* t, int requires_grad) {
     return guarded([&] { static_cast<AutoDiff*>(c)->make_leaf(*T(t), requires_grad != 0); });
@@ -810,6 +996,15 @@ int cth_mlp_destroy(void* m) {
 }
 int cth_mlp_set_comm(void* m, void* comm) {
     return guarded([&] { static_cast<MlpTrainer*>(m)->set_comm(comm); });
+}
+int cth_mlp_set_dp_mode(void* m, int mode) {
+    return guarded([&] { static_cast<MlpTrainer*>(m)->set_dp_mode(mode); });
+}
+int cth_mlp_set_comm_timeout_ms(void* m, int timeout_ms) {
+    return guarded([&] {
+        if (timeout_ms <= 0) throw std::runtime_error("cth_mlp_set_comm_timeout_ms: a positive number of milliseconds");
+        static_cast<MlpTrainer*>(m)->comm_timeout_ms = timeout_ms;
+    });
 }
 int cth_mlp_set_corrected(void* m, int exact_bias_grad, int fresh_weights) {
     return guarded([&] { static_cast<MlpTrainer*>(m)->set_corrected(exact_bias_grad != 0, fresh_weights != 0); });

@@ -1,6 +1,7 @@
 // Shared host/device helpers of the sm_100a kernel library.
 #pragma once
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 #include <stdint.h>
 #include <atomic>
 #include <string>
@@ -22,6 +23,30 @@ ctk_status device_scratch(int slot, size_t bytes, void** out);
 
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 
+// NVTX range around the host side of an entry point (header-only NVTX: a no-op costing a few
+// nanoseconds unless a profiler has injected itself), so a timeline shows which C-ABI call issued
+// which kernels.
+struct Range {
+    explicit Range(const char* name) { nvtxRangePushA(name); }
+    ~Range() { nvtxRangePop(); }
+    Range(const Range&) = delete;
+    Range& operator=(const Range&) = delete;
+};
+
+// One-time set-up that belongs to a (kernel, device) pair -- cudaFuncSetAttribute, occupancy queries --
+// is guarded by one of these per kernel instantiation: first() is true once per device ordinal, for
+// the device that is current at the call (a process may drive several GPUs through ctk_set_device).
+struct PerDeviceOnce {
+    bool done[64] = {false};
+    bool first() {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;  // unknown device: redo the set-up, it is idempotent
+        if (done[dev]) return false;
+        done[dev] = true;
+        return true;
+    }
+};
+
 }  // namespace ctk
 
 #define CTK_CUDA(call)                                                                          \
@@ -38,6 +63,8 @@ inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s
             return ctk::fail(CTK_ERR_CUDA, std::string(name) + " launch: " + cudaGetErrorString(_e)); \
         ctk::count_launch();                                                                      \
     } while (0)
+
+#define CTK_RANGE(name) ctk::Range _ctk_nvtx_range(name)
 
 #define CTK_REQUIRE(cond, msg)                                    \
     do {                                                          \

@@ -239,6 +239,7 @@ static uint64_t host_mix64(uint64_t z) {
 extern "C" {
 
 ctk_status ctk_compare_f32(int cmp, int form, const float* a, const float* b, float scalar, unsigned char* out, int64_t n, void* stream) {
+    CTK_RANGE("ctk_compare_f32");
     CTK_REQUIRE(n >= 0, "ctk_compare_f32: negative size");
     if (n == 0) return CTK_OK;
     CTK_REQUIRE(a && out && (form != CTK_CMP_TENSOR || b), "ctk_compare_f32: null pointer");
@@ -255,6 +256,7 @@ ctk_status ctk_compare_f32(int cmp, int form, const float* a, const float* b, fl
 }
 
 ctk_status ctk_cast_f32(int dtype, const float* src, void* dst, int64_t n, void* stream) {
+    CTK_RANGE("ctk_cast_f32");
     CTK_REQUIRE(n >= 0, "ctk_cast_f32: negative size");
     if (n == 0) return CTK_OK;
     CTK_REQUIRE(src && dst, "ctk_cast_f32: null pointer");
@@ -269,6 +271,7 @@ ctk_status ctk_cast_f32(int dtype, const float* src, void* dst, int64_t n, void*
 }
 
 ctk_status ctk_fill_dtype(int dtype, void* dst, double value, int64_t n, void* stream) {
+    CTK_RANGE("ctk_fill_dtype");
     CTK_REQUIRE(n >= 0, "ctk_fill_dtype: negative size");
     if (n == 0) return CTK_OK;
     CTK_REQUIRE(dst, "ctk_fill_dtype: null pointer");
@@ -287,6 +290,7 @@ ctk_status ctk_fill_dtype(int dtype, void* dst, double value, int64_t n, void* s
 }
 
 ctk_status ctk_rand_uniform_f32(float* dst, int64_t n, uint64_t seed, uint64_t offset, void* stream) {
+    CTK_RANGE("ctk_rand_uniform_f32");
     CTK_REQUIRE(n >= 0, "ctk_rand_uniform_f32: negative size");
     if (n == 0) return CTK_OK;
     CTK_REQUIRE(dst, "ctk_rand_uniform_f32: null pointer");

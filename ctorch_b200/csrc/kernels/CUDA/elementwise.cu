@@ -205,6 +205,7 @@ EwArgs<NIN, NOUT> make_args(int64_t n, int64_t inner = 1) {
 extern "C" {
 
 ctk_status ctk_binary_f32(int op, const float* a, const float* b, float* out, int64_t n, int layout, int64_t inner, void* stream) {
+    CTK_RANGE("ctk_binary_f32");
     CTK_REQUIRE(n >= 0, "ctk_binary_f32: negative size");
     if (n == 0) return CTK_OK;
     CTK_REQUIRE(a && b && out, "ctk_binary_f32: null pointer");
@@ -225,6 +226,7 @@ ctk_status ctk_binary_f32(int op, const float* a, const float* b, float* out, in
 }
 
 ctk_status ctk_unary_f32(int op, const float* a, float* out, int64_t n, void* stream) {
+    CTK_RANGE("ctk_unary_f32");
     CTK_REQUIRE(n >= 0, "ctk_unary_f32: negative size");
     if (n == 0) return CTK_OK;
     CTK_REQUIRE(a && out, "ctk_unary_f32: null pointer");
@@ -243,6 +245,7 @@ ctk_status ctk_unary_f32(int op, const float* a, float* out, int64_t n, void* st
 }
 
 ctk_status ctk_scalar_f32(int kind, const float* a, float s, float* out, int64_t n, void* stream) {
+    CTK_RANGE("ctk_scalar_f32");
     CTK_REQUIRE(n >= 0, "ctk_scalar_f32: negative size");
     if (n == 0) return CTK_OK;
     CTK_REQUIRE(a && out, "ctk_scalar_f32: null pointer");
@@ -260,6 +263,7 @@ ctk_status ctk_scalar_f32(int kind, const float* a, float s, float* out, int64_t
 }
 
 ctk_status ctk_fill_f32(float* p, float value, const float* value_device, int64_t n, void* stream) {
+    CTK_RANGE("ctk_fill_f32");
     CTK_REQUIRE(n >= 0, "ctk_fill_f32: negative size");
     if (n == 0) return CTK_OK;
     CTK_REQUIRE(p, "ctk_fill_f32: null pointer");
@@ -274,6 +278,7 @@ ctk_status ctk_fill_f32(float* p, float value, const float* value_device, int64_
 }
 
 ctk_status ctk_tile_f32(const float* src, int64_t src_n, float* dst, int64_t n, void* stream) {
+    CTK_RANGE("ctk_tile_f32");
     CTK_REQUIRE(n >= 0 && src_n > 0, "ctk_tile_f32: bad size");
     if (n == 0) return CTK_OK;
     CTK_REQUIRE(src && dst, "ctk_tile_f32: null pointer");
@@ -283,6 +288,7 @@ ctk_status ctk_tile_f32(const float* src, int64_t src_n, float* dst, int64_t n, 
 }
 
 ctk_status ctk_onehot_f32(const float* labels, int64_t rows, int64_t classes, float* onehot, void* stream) {
+    CTK_RANGE("ctk_onehot_f32");
     CTK_REQUIRE(rows >= 0 && classes >= 0, "ctk_onehot_f32: negative shape");
     if (rows == 0 || classes == 0) return CTK_OK;
     CTK_REQUIRE(labels && onehot, "ctk_onehot_f32: null pointer");
@@ -292,6 +298,7 @@ ctk_status ctk_onehot_f32(const float* labels, int64_t rows, int64_t classes, fl
 }
 
 ctk_status ctk_u8_to_f32(const uint8_t* src, int64_t n, float divisor, float* dst, void* stream) {
+    CTK_RANGE("ctk_u8_to_f32");
     CTK_REQUIRE(n >= 0, "ctk_u8_to_f32: negative size");
     if (n == 0) return CTK_OK;
     CTK_REQUIRE(src && dst, "ctk_u8_to_f32: null pointer");
@@ -302,6 +309,7 @@ ctk_status ctk_u8_to_f32(const uint8_t* src, int64_t n, float divisor, float* ds
 }
 
 ctk_status ctk_argmax_rows_f32(const float* x, int64_t rows, int64_t cols, float init, float* out_index, void* stream) {
+    CTK_RANGE("ctk_argmax_rows_f32");
     CTK_REQUIRE(rows >= 0 && cols >= 0, "ctk_argmax_rows_f32: negative shape");
     if (rows == 0) return CTK_OK;
     CTK_REQUIRE(out_index && (x || cols == 0), "ctk_argmax_rows_f32: null pointer");
@@ -311,6 +319,7 @@ ctk_status ctk_argmax_rows_f32(const float* x, int64_t rows, int64_t cols, float
 }
 
 ctk_status ctk_gather_nd_f32(const float* src, float* dst, int rank, const int64_t* dst_shape, const int64_t* src_strides, void* stream) {
+    CTK_RANGE("ctk_gather_nd_f32");
     CTK_REQUIRE(rank >= 0 && rank <= 8, "ctk_gather_nd_f32: rank must be 0..8");
     CTK_REQUIRE(src && dst && (rank == 0 || (dst_shape && src_strides)), "ctk_gather_nd_f32: null pointer");
     GatherArgs g{};
@@ -329,6 +338,7 @@ ctk_status ctk_gather_nd_f32(const float* src, float* dst, int rank, const int64
 }
 
 ctk_status ctk_unary_backward_f32(int op, const float* x, const float* g, float* dx, int64_t n, void* stream) {
+    CTK_RANGE("ctk_unary_backward_f32");
     CTK_REQUIRE(n >= 0, "ctk_unary_backward_f32: negative size");
     if (n == 0) return CTK_OK;
     CTK_REQUIRE(g && dx && (x || op == CTK_OP_NEG), "ctk_unary_backward_f32: null pointer");
@@ -352,6 +362,7 @@ ctk_status ctk_unary_backward_f32(int op, const float* x, const float* g, float*
 
 ctk_status ctk_binary_backward_f32(int op, const float* a, const float* b, const float* g, float* da, float* db,
                                    int64_t n, int layout, int64_t inner, void* stream) {
+    CTK_RANGE("ctk_binary_backward_f32");
     CTK_REQUIRE(n >= 0, "ctk_binary_backward_f32: negative size");
     if (n == 0 || (!da && !db)) return CTK_OK;
     CTK_REQUIRE(g, "ctk_binary_backward_f32: null gradient");
@@ -381,6 +392,7 @@ ctk_status ctk_binary_backward_f32(int op, const float* a, const float* b, const
 }
 
 ctk_status ctk_accumulate_f32(float* dst, const float* src, int64_t n, void* stream) {
+    CTK_RANGE("ctk_accumulate_f32");
     CTK_REQUIRE(n >= 0, "ctk_accumulate_f32: negative size");
     if (n == 0) return CTK_OK;
     CTK_REQUIRE(dst && src, "ctk_accumulate_f32: null pointer");
@@ -390,6 +402,7 @@ ctk_status ctk_accumulate_f32(float* dst, const float* src, int64_t n, void* str
 }
 
 ctk_status ctk_sgd_update_f32(float* p, const float* g, float lr, int64_t n, void* stream) {
+    CTK_RANGE("ctk_sgd_update_f32");
     CTK_REQUIRE(n >= 0, "ctk_sgd_update_f32: negative size");
     if (n == 0) return CTK_OK;
     CTK_REQUIRE(p && g, "ctk_sgd_update_f32: null pointer");

@@ -34,8 +34,6 @@
 #include <math.h>
 #include <cstdlib>
 
-#include <unordered_map>
-#include <atomic>
 #include <mutex>
 #include <vector>
 
@@ -225,9 +223,6 @@ struct Params {
     float* c;
     int vec_store;    // n % 4 == 0 and c 16-byte aligned
     int whole_tiles;  // tiles [0, whole_tiles) are computed whole; each later tile as two K-halves
-    // CTA-pair kernel, dynamic unit order: {next, done} counters (both 0 between launches), or NULL for
-    // the static order (pair i takes units i, i + pairs, ...).
-    unsigned int* sched;
     // Epilogue of the fused forms (all optional; whole tiles only): c = [relu](acc + bias[col]), then
     // c *= (mask > 0 ? 1 : 0) with mask an [m, n] array of pitch n (ReLU's backward rule applied to a
     // gradient product), and the hi/lo split of c written next to it ([m, split_pitch] each) for the
@@ -257,6 +252,21 @@ __device__ __forceinline__ Unit unit_of(int u, const Params& P) {
     const int v = u - P.whole_tiles;
     const int mid = (P.num_kb + 1) >> 1;
     return (v & 1) ? Unit{P.whole_tiles + (v >> 1), mid, P.num_kb, true} : Unit{P.whole_tiles + (v >> 1), 0, mid, true};
+}
+
+// Tile order.  Tiles are numbered band by band: a band is TILE_BAND tile columns wide and is walked
+// row after row, so the tiles that run at the same time (one wave of the persistent grid) form a
+// compact block of about 9 x 8 tiles instead of a few full tile rows.  A wave then reads ~17 instead
+// of ~21 operand panels, and -- what matters for DRAM -- a band's B panels (8 x 256 columns) stay in
+// L2 while A streams past them once per band, where row-major order re-read all of B for every wave.
+constexpr int TILE_BAND = 8;
+__host__ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+    const int band = tile / (TILE_BAND * tiles_m);
+    const int first_col = band * TILE_BAND;
+    const int width = tiles_n - first_col < TILE_BAND ? tiles_n - first_col : TILE_BAND;
+    const int r = tile - band * (TILE_BAND * tiles_m);
+    tm = r / width;
+    tn = first_col + r % width;
 }
 
 // ---- PTX wrappers --------------------------------------------------------------------------------
@@ -539,7 +549,9 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
             bool ok = true;
             for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
                 const Unit U = unit_of(u, P);
-                const int m0 = (U.tile / P.tiles_n) * BM, n0 = (U.tile % P.tiles_n) * BN;
+                int tm, tn;
+                tile_coords(U.tile, P.tiles_m, P.tiles_n, tm, tn);
+                const int m0 = tm * BM, n0 = tn * BN;
                 for (int kb = U.kb0; kb < U.kb1; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, &abort_flag, 0x100 | stage)) { ok = false; break; }
                     mbar_expect_tx(full_bar(stage), C::STAGE_BYTES);
@@ -629,7 +641,9 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
         bool ok = true;
         for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
             const Unit U = unit_of(u, P);
-            const int64_t m0 = static_cast<int64_t>(U.tile / P.tiles_n) * BM, n0 = static_cast<int64_t>(U.tile % P.tiles_n) * BN;
+            int tm, tn;
+            tile_coords(U.tile, P.tiles_m, P.tiles_n, tm, tn);
+            const int64_t m0 = static_cast<int64_t>(tm) * BM, n0 = static_cast<int64_t>(tn) * BN;
             const int64_t row_base = m0 + quarter * 32;
             MaskRegs mk_now, mk_next;
             load_mask(P, U.half, row_base, lane, n0, mk_next);  // chunk 0's, while the accumulator is still being computed
@@ -680,12 +694,6 @@ namespace pair {
 
 constexpr int BN = 256;     // tile width of the pair
 constexpr int BN_CTA = 128; // columns of B each CTA stages
-// Dynamic unit order: rank 0's producer draws the pair's next unit from a global counter and publishes
-// it in a ring of SCHED_SLOTS entries kept in both CTAs; the ten other roles that walk the units (rank
-// 0: MMA issuer, 4 epilogue warps; rank 1: producer, 4 epilogue warps) read it there.  The producer is
-// never more than three units ahead of the slowest role (one in the stage ring, two accumulators).
-constexpr int SCHED_SLOTS = 8;
-constexpr int SCHED_READERS = 10;
 
 template <int TERMS>
 struct Cfg {
@@ -785,8 +793,6 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
     using C = Cfg<TERMS>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t bars[2 * 8 + 4];  // full[8], empty[8], tmem_full[2], tmem_empty[2]
-    __shared__ uint64_t sbars[2 * SCHED_SLOTS];  // dynamic order: slot published [SCHED_SLOTS], slot read by all (rank 0's) [SCHED_SLOTS]
-    __shared__ volatile uint32_t sched_unit[SCHED_SLOTS];
     __shared__ uint32_t tmem_base_slot;
     __shared__ __align__(16) EpilogueStage stages[4];  // one per epilogue warp
     __shared__ volatile int abort_flag;
@@ -801,16 +807,12 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
     auto a_addr = [&](int s, int part) { return smem_base + s * C::STAGE_BYTES + part * C::A_BYTES; };
     auto b_addr = [&](int s, int part) { return smem_base + s * C::STAGE_BYTES + C::PARTS * C::A_BYTES + part * C::B_BYTES; };
     const uint32_t peer_abort = map_to_cta(smem_u32(const_cast<int*>(&abort_flag)), rank ^ 1u);
-    const uint32_t sbar0 = smem_u32(sbars);
-    auto spub_bar = [&](int i) { return sbar0 + 8u * i; };
-    auto sread_bar = [&](int i) { return sbar0 + 8u * (SCHED_SLOTS + i); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 8); }
-        for (int i = 0; i < SCHED_SLOTS; ++i) { mbar_init(spub_bar(i), 1); mbar_init(sread_bar(i), SCHED_READERS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         prefetch_tmap(&map_a_hi);
         prefetch_tmap(&map_b_hi);
@@ -828,30 +830,10 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
 
     const int num_units = unit_count(P);
     const int first_unit = blockIdx.x >> 1, unit_step = gridDim.x >> 1;
-    const bool dynamic = P.sched != nullptr;
-    // Unit number `seq` of this pair, for every role but rank 0's producer (one lane calls this).
-    // Static order: first_unit + seq * unit_step.  Dynamic order: what rank 0's producer published.
-    auto unit_at = [&](uint32_t seq, int& u) -> bool {
-        if (!dynamic) {
-            const int64_t v = static_cast<int64_t>(first_unit) + static_cast<int64_t>(seq) * unit_step;
-            u = v < num_units ? static_cast<int>(v) : num_units;
-            return true;
-        }
-        const uint32_t slot = seq % SCHED_SLOTS, par = (seq / SCHED_SLOTS) & 1u;
-        if (!mbar_wait_cluster(spub_bar(slot), par, &abort_flag, 0x900 | slot)) return false;
-        u = static_cast<int>(sched_unit[slot]);
-        mbar_arrive_cluster(map_to_cta(sread_bar(slot), 0));
-        return true;
-    };
-    // rank 0's producer: unit `u` becomes number `seq` in both CTAs' rings.
-    auto publish = [&](uint32_t seq, int u) -> bool {
-        const uint32_t slot = seq % SCHED_SLOTS, par = (seq / SCHED_SLOTS) & 1u;
-        if (seq >= SCHED_SLOTS && !mbar_wait_cluster(sread_bar(slot), par ^ 1u, &abort_flag, 0x980 | slot)) return false;
-        sched_unit[slot] = static_cast<uint32_t>(u);
-        st_cluster_u32(map_to_cta(smem_u32(const_cast<uint32_t*>(&sched_unit[slot])), 1), static_cast<uint32_t>(u));
-        mbar_arrive_cluster(map_to_cta(spub_bar(slot), 0));
-        mbar_arrive_cluster(map_to_cta(spub_bar(slot), 1));
-        return true;
+    // Unit number `seq` of this pair: first_unit + seq * unit_step (num_units once the pair has run out).
+    auto unit_at = [&](uint32_t seq) -> int {
+        const int64_t v = static_cast<int64_t>(first_unit) + static_cast<int64_t>(seq) * unit_step;
+        return v < num_units ? static_cast<int>(v) : num_units;
     };
 
     if (warp == 0) {
@@ -861,18 +843,14 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
             uint32_t phase = 0;
             uint32_t issued = 0;
             bool ok = true;
-            const bool scheduler = dynamic && rank == 0;
-            int u = first_unit < num_units ? first_unit : num_units;
             for (uint32_t seq = 0; ok; ++seq) {
-                unsigned int drawn = 0;
-                if (scheduler) {
-                    if (!publish(seq, u)) { ok = false; break; }
-                    if (u < num_units) drawn = atomicAdd(P.sched, 1u);  // the next unit, asked for now, needed after this unit's loads
-                } else if (!unit_at(seq, u)) { ok = false; break; }
+                const int u = unit_at(seq);
                 if (u >= num_units) break;
                 const Unit U = unit_of(u, P);
-                const int m0 = (U.tile / P.tiles_n) * (2 * BM) + static_cast<int>(rank) * BM;
-                const int n0 = (U.tile % P.tiles_n) * BN + static_cast<int>(rank) * BN_CTA;
+                int tm, tn;
+                tile_coords(U.tile, P.tiles_m, P.tiles_n, tm, tn);
+                const int m0 = tm * (2 * BM) + static_cast<int>(rank) * BM;
+                const int n0 = tn * BN + static_cast<int>(rank) * BN_CTA;
                 for (int kb = U.kb0; kb < U.kb1; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, &abort_flag, 0x500 | stage)) { ok = false; break; }
                     if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * C::STAGE_BYTES);
@@ -897,10 +875,6 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
                     }
                     ++issued;
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
-                }
-                if (scheduler) {
-                    const unsigned int nxt = drawn + static_cast<unsigned int>(unit_step);
-                    u = nxt < static_cast<unsigned int>(num_units) ? static_cast<int>(nxt) : num_units;
                 }
             }
             if (ok) {
@@ -929,8 +903,7 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
             uint32_t acc_phase = 0;
             bool ok = true;
             for (uint32_t seq = 0; ok; ++seq) {
-                int u;
-                if (!unit_at(seq, u)) { ok = false; break; }
+                const int u = unit_at(seq);
                 if (u >= num_units) break;
                 const Unit U = unit_of(u, P);
                 if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, &abort_flag, 0x600 | (18 + acc))) { ok = false; break; }
@@ -976,15 +949,13 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
         uint32_t acc_phase = 0;
         bool ok = true;
         for (uint32_t seq = 0; ok; ++seq) {
-            int u = 0, got = 1;
-            if (lane == 0) got = unit_at(seq, u) ? 1 : 0;
-            got = __shfl_sync(0xffffffffu, got, 0);
-            u = __shfl_sync(0xffffffffu, u, 0);
-            if (!got) { ok = false; break; }
+            const int u = unit_at(seq);
             if (u >= num_units) break;
             const Unit U = unit_of(u, P);
-            const int64_t m0 = static_cast<int64_t>(U.tile / P.tiles_n) * (2 * BM) + static_cast<int64_t>(rank) * BM;
-            const int64_t n0 = static_cast<int64_t>(U.tile % P.tiles_n) * BN;
+            int tm, tn;
+            tile_coords(U.tile, P.tiles_m, P.tiles_n, tm, tn);
+            const int64_t m0 = static_cast<int64_t>(tm) * (2 * BM) + static_cast<int64_t>(rank) * BM;
+            const int64_t n0 = static_cast<int64_t>(tn) * BN;
             const int64_t row_base = m0 + quarter * 32;
             MaskRegs mk_now, mk_next;
             load_mask(P, U.half, row_base, lane, n0, mk_next);  // chunk 0's, while the accumulator is still being computed
@@ -1015,15 +986,6 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc2(tmem_base, C::TMEM_COLS);
-    }
-    if (dynamic && rank == 0 && threadIdx.x == 0) {
-        // This pair has drawn its last unit (thread 0 is the lane that draws).  The pair that finishes
-        // last puts both counters back to zero for the next launch on this stream.
-        __threadfence();
-        if (atomicAdd(P.sched + 1, 1u) == static_cast<unsigned int>(unit_step) - 1u) {
-            atomicExch(P.sched, 0u);
-            atomicExch(P.sched + 1, 0u);
-        }
     }
 }
 
@@ -1109,11 +1071,8 @@ template <int BN, int TERMS, bool A_MN, bool B_MN>
 ctk_status launch_tc(const CUtensorMap maps[4], const Params& P, cudaStream_t st) {
     using C = Cfg<BN, TERMS>;
     auto kernel = tcgen05_matmul_kernel<BN, TERMS, A_MN, B_MN>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        CTK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-        attr_set = true;
-    }
+    static ctk::PerDeviceOnce attr;  // the attribute belongs to the (kernel, device) pair
+    if (attr.first()) CTK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     const int units = P.whole_tiles + 2 * (P.tiles_m * P.tiles_n - P.whole_tiles);
     const int sms = ctk::sm_count();
     const int grid = units < sms ? units : sms;  // persistent: one CTA per SM
@@ -1132,11 +1091,13 @@ ctk_status launch_tc_major(bool a_mn, bool b_mn, const CUtensorMap maps[4], cons
 
 int pick_bn(int64_t n) { return n > 128 ? 256 : (n > 64 ? 128 : 64); }
 
-// Zeroes the output tiles [first, first + count) (tile_m x tile_n each, row-major tile order):
+// Zeroes the output tiles [first, first + count) (tile_m x tile_n each, numbered as tile_coords does):
 // the tiles whose K-halves are added into C.
-__global__ void __launch_bounds__(256) zero_tiles_kernel(float* __restrict__ c, int64_t m, int64_t n, int tile_m, int tile_n, int tiles_n, int first, int parts) {
+__global__ void __launch_bounds__(256) zero_tiles_kernel(float* __restrict__ c, int64_t m, int64_t n, int tile_m, int tile_n, int tiles_m, int tiles_n, int first, int parts) {
     const int tile = first + blockIdx.x / parts, part = blockIdx.x % parts;
-    const int64_t m0 = static_cast<int64_t>(tile / tiles_n) * tile_m, n0 = static_cast<int64_t>(tile % tiles_n) * tile_n;
+    int tm, tn;
+    tile_coords(tile, tiles_m, tiles_n, tm, tn);
+    const int64_t m0 = static_cast<int64_t>(tm) * tile_m, n0 = static_cast<int64_t>(tn) * tile_n;
     const int rows_per = (tile_m + parts - 1) / parts;
     const int64_t r0 = m0 + static_cast<int64_t>(part) * rows_per;
     const int64_t r1 = r0 + rows_per < m0 + tile_m ? r0 + rows_per : m0 + tile_m;
@@ -1310,55 +1271,6 @@ static bool skinny_k_ok(const float* a, const float* b, const float* c, int64_t 
 int g_default_mode = CTK_MATMUL_3XTF32;
 int g_pairing = 0;  // 0: CTA pairs where the shape allows, 1: single-CTA kernel only
 int g_split_tail = 1;  // 1: K-halves for the tiles of a last wave that fills at most half the machine
-// 0 (default): pair i takes units i, i + pairs, ...; 1: CTA pairs draw their units from a counter
-// (CTORCH_MATMUL_DYNAMIC_ORDER=1 in the environment starts a process with 1).  Measured on B200: no
-// difference on one GPU, and 1-2 % SLOWER steps with 2 and 8 GPUs while NCCL's kernels share the SMs,
-// which is why it is not the default.
-int g_dynamic_order = [] {
-    const char* e = std::getenv("CTORCH_MATMUL_DYNAMIC_ORDER");
-    return (e && e[0] == '1') ? 1 : 0;
-}();
-
-// {next, done} counters of the pair kernel's dynamic unit order: one pair of words per stream (launches
-// on one stream follow one another, and each launch leaves its words at zero), zeroed when the block is
-// allocated and again after a launch that gave up on a wait.
-constexpr int kSchedStreams = 512;
-struct SchedBlock {
-    unsigned int* words = nullptr;
-    std::unordered_map<cudaStream_t, int> index;
-};
-SchedBlock g_sched[64];
-std::mutex g_sched_mu;
-std::atomic<bool> g_sched_dirty{false};
-
-ctk_status sched_words(cudaStream_t st, unsigned int** out) {
-    *out = nullptr;
-    int dev = 0;
-    CTK_CUDA(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64) return CTK_OK;
-    std::lock_guard<std::mutex> lock(g_sched_mu);
-    SchedBlock& b = g_sched[dev];
-    if (!b.words) {
-        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-        CTK_CUDA(cudaStreamIsCapturing(st, &cap));
-        if (cap != cudaStreamCaptureStatusNone) return CTK_OK;  // no allocation inside a capture: fixed order
-        CTK_CUDA(cudaMalloc(&b.words, kSchedStreams * 2 * sizeof(unsigned int)));
-        CTK_CUDA(cudaMemset(b.words, 0, kSchedStreams * 2 * sizeof(unsigned int)));
-    }
-    if (g_sched_dirty.exchange(false)) {
-        CTK_CUDA(cudaDeviceSynchronize());
-        for (int d = 0; d < 64; ++d)
-            if (g_sched[d].words && d == dev) CTK_CUDA(cudaMemset(g_sched[d].words, 0, kSchedStreams * 2 * sizeof(unsigned int)));
-    }
-    auto it = b.index.find(st);
-    if (it == b.index.end()) {
-        if (b.index.size() >= static_cast<size_t>(kSchedStreams)) return CTK_OK;  // fixed order for further streams
-        it = b.index.emplace(st, static_cast<int>(b.index.size())).first;
-    }
-    *out = b.words + 2 * it->second;
-    return CTK_OK;
-}
-
 // ---- optional per-launch timing of the tensor-core kernel ----
 struct TcProfile {
     static constexpr int kMax = 8192;
@@ -1458,12 +1370,6 @@ ctk_status ctk_set_matmul_tail_split(int on) {
     return CTK_OK;
 }
 
-ctk_status ctk_set_matmul_dynamic_order(int on) {
-    CTK_REQUIRE(on == 0 || on == 1, "ctk_set_matmul_dynamic_order: 0 or 1");
-    g_dynamic_order = on;
-    return CTK_OK;
-}
-
 ctk_status ctk_set_matmul_pairing(int pairing) {
     CTK_REQUIRE(pairing == 0 || pairing == 1, "ctk_set_matmul_pairing: 0 (CTA pairs where possible) or 1 (single-CTA kernel only)");
     g_pairing = pairing;
@@ -1516,6 +1422,7 @@ ctk_status ctk_matmul_profile_read(int64_t* launches, double* total_ms, double* 
 // (1 expected), second waiter ok (0 expected), status word (0x7e57 expected)} and clears the status
 // word again.  No MatMul may be in flight.
 ctk_status ctk_matmul_selftest_wait_timeout(int result[4]) {
+    CTK_RANGE("ctk_matmul_selftest_wait_timeout");
     CTK_REQUIRE(result, "ctk_matmul_selftest_wait_timeout: null");
     CTK_CUDA(cudaDeviceSynchronize());
     int saved = 0;
@@ -1538,7 +1445,6 @@ ctk_status ctk_matmul_status(int* status) {
     CTK_REQUIRE(status, "ctk_matmul_status: null");
     CTK_CUDA(cudaDeviceSynchronize());
     CTK_CUDA(cudaMemcpyFromSymbol(status, g_tc_status, sizeof(int)));
-    if (*status != 0) g_sched_dirty.store(true);  // a launch that gave up may have left its unit counters non-zero
     return CTK_OK;
 }
 
@@ -1556,7 +1462,6 @@ struct FusedEpilogue {
     int relu = 0;
     const float* mask = nullptr;
     void* c_split = nullptr;
-    bool fixed_order = false;  // never the dynamic unit order (whose counters are allocated on first use)
 };
 
 static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k, int64_t sa0,
@@ -1682,13 +1587,11 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
         int workers = ctk::sm_count();
         if (paired && (rc = tc::resident_pairs(&workers))) return rc;
         P.whole_tiles = tiles;
-        P.sched = nullptr;
-        if (paired && g_dynamic_order && !fe.fixed_order && (rc = sched_words(st, &P.sched))) return rc;
         const int tail = tiles % workers;
         if (g_split_tail && !fused && P.num_kb >= 16 && tail > 0 && 2 * tail <= workers) {  // (a fused epilogue needs the whole sum)
             P.whole_tiles = tiles - tail;
             const int parts = 4;
-            tc::zero_tiles_kernel<<<tail * parts, 256, 0, st>>>(c, m, n, tile_m, bn, P.tiles_n, P.whole_tiles, parts);
+            tc::zero_tiles_kernel<<<tail * parts, 256, 0, st>>>(c, m, n, tile_m, bn, P.tiles_m, P.tiles_n, P.whole_tiles, parts);
             CTK_LAUNCH_CHECK("zero_tiles_kernel");
         }
     }
@@ -1709,6 +1612,7 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
 
 ctk_status ctk_matmul_f32(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k, int64_t sa0,
                           int64_t sa1, int64_t sb0, int64_t sb1, int mode, void* workspace, void* stream) {
+    CTK_RANGE("ctk_matmul_f32");
     return matmul_impl(a, b, c, m, n, k, sa0, sa1, sb0, sb1, mode, workspace, KeptSplit{nullptr, nullptr}, KeptSplit{nullptr, nullptr}, stream);
 }
 
@@ -1727,6 +1631,7 @@ size_t ctk_matmul_split_bytes(int64_t mn, int64_t k) { return static_cast<size_t
 ctk_status ctk_matmul_3xtf32_kept_f32(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k, int64_t sa0,
                                       int64_t sa1, int64_t sb0, int64_t sb1, void* a_split, int* a_valid, void* b_split,
                                       int* b_valid, void* workspace, void* stream) {
+    CTK_RANGE("ctk_matmul_3xtf32_kept_f32");
     CTK_REQUIRE((!a_split || a_valid) && (!b_split || b_valid), "ctk_matmul_3xtf32_kept_f32: a split buffer needs its valid flag");
     return matmul_impl(a, b, c, m, n, k, sa0, sa1, sb0, sb1, CTK_MATMUL_3XTF32, workspace, KeptSplit{a_split, a_valid}, KeptSplit{b_split, b_valid}, stream);
 }
@@ -1744,6 +1649,7 @@ ctk_status ctk_matmul_3xtf32_fused_f32(const float* a, const float* b, float* c,
                                        int64_t sa1, int64_t sb0, int64_t sb1, void* a_split, int* a_valid, void* b_split,
                                        int* b_valid, const float* bias, int relu, const float* mask, void* c_split, void* workspace,
                                        void* stream) {
+    CTK_RANGE("ctk_matmul_3xtf32_fused_f32");
     CTK_REQUIRE((!a_split || a_valid) && (!b_split || b_valid), "ctk_matmul_3xtf32_fused_f32: a split buffer needs its valid flag");
     CTK_REQUIRE(m > 0 && n > 0 && k > 0, "ctk_matmul_3xtf32_fused_f32: empty product");
     FusedEpilogue fe;
@@ -1761,6 +1667,7 @@ ctk_status ctk_matmul_3xtf32_fused_f32(const float* a, const float* b, float* c,
 // aligned, inner and ld multiples of 4, g contiguous; anything else is refused (CTK_ERR_INVALID) and the
 // caller runs the plain update.
 ctk_status ctk_sgd_update_split_f32(float* p, const float* g, float lr, int64_t outer, int64_t inner, int64_t ld, void* split, void* stream) {
+    CTK_RANGE("ctk_sgd_update_split_f32");
     CTK_REQUIRE(outer >= 0 && inner >= 0 && ld >= inner, "ctk_sgd_update_split_f32: bad extents");
     if (outer == 0 || inner == 0) return CTK_OK;
     CTK_REQUIRE(p && g && split, "ctk_sgd_update_split_f32: null pointer");
@@ -1781,8 +1688,11 @@ ctk_status ctk_sgd_update_split_f32(float* p, const float* g, float lr, int64_t 
 // workspace that is allocated or passed in.
 //   - Operands whose split does not fit -- 2*(m*k + k*n) floats may take at most 16 MiB, which
 //     1024x1024 by 1024x1024 just reaches -- are refused with CTK_ERR_LIMIT; nothing is launched.
-//   - The first call on each device looks up the array's device address and sets the kernel's
-//     shared-memory attribute; make that first call outside any stream capture.
+//   - One-time set-up happens inside calls: the first call on a device looks up the array's device
+//     address; the first call of each shape class on a device (tile width from n, major-ness of each
+//     operand, CTA pairs or not) sets that kernel instantiation's shared-memory attribute and, for
+//     pairs, queries the occupancy.  Make one call per shape class outside any stream capture first.
+//   - `stream` must belong to the device that is current at the call.
 //   - No byte of the array has to be zero on entry: each call writes the part it reads before it
 //     reads it, so stale contents of the previous call do not matter.
 //   - All calls on one GPU share the one array: two calls whose kernels may overlap (different
@@ -1790,6 +1700,7 @@ ctk_status ctk_sgd_update_split_f32(float* p, const float* g, float lr, int64_t 
 //   - Launch timing (ctk_matmul_profile_enable) creates events on demand, so it must be off.
 ctk_status ctk_matmul_3xtf32_noalloc_f32(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
                                          int64_t sa0, int64_t sa1, int64_t sb0, int64_t sb1, void* stream) {
+    CTK_RANGE("ctk_matmul_3xtf32_noalloc_f32");
     CTK_REQUIRE(m >= 0 && n >= 0 && k >= 0, "ctk_matmul_3xtf32_noalloc_f32: negative extent");
     const size_t need = ctk_matmul_workspace_bytes(m, n, k, CTK_MATMUL_3XTF32);
     if (need > kStaticWorkspaceBytes)
@@ -1803,9 +1714,7 @@ ctk_status ctk_matmul_3xtf32_noalloc_f32(const float* a, const float* b, float* 
     void* ws = nullptr;
     ctk_status rc = static_workspace(&ws);
     if (rc) return rc;
-    FusedEpilogue opts;
-    opts.fixed_order = true;  // the dynamic order's counters would be allocated on first use
-    return matmul_impl(a, b, c, m, n, k, sa0, sa1, sb0, sb1, CTK_MATMUL_3XTF32, ws, KeptSplit{nullptr, nullptr}, KeptSplit{nullptr, nullptr}, stream, opts);
+    return matmul_impl(a, b, c, m, n, k, sa0, sa1, sb0, sb1, CTK_MATMUL_3XTF32, ws, KeptSplit{nullptr, nullptr}, KeptSplit{nullptr, nullptr}, stream);
 }
 
 }  // extern "C"

@@ -14,8 +14,12 @@
 
 namespace ctk {
 
-static std::atomic<bool> g_library_scratch_dirty{false};
-void mark_reduce_scratch_dirty() { g_library_scratch_dirty.store(true); }
+// One flag per device ordinal: the library's scratch block is per device, and a kernel that gave up is
+// reported through a status word that does not say where it ran, so every device's block is marked.
+static std::atomic<bool> g_library_scratch_dirty[64];
+void mark_reduce_scratch_dirty() {
+    for (auto& f : g_library_scratch_dirty) f.store(true);
+}
 
 ctk_status reduce_scratch(void* user, cudaStream_t st, ReduceScratch** out) {
     void* p = user;
@@ -28,7 +32,10 @@ ctk_status reduce_scratch(void* user, cudaStream_t st, ReduceScratch** out) {
     // The ticket must start at zero.  The library's own block is zeroed when it is allocated and every
     // kernel rewinds the ticket it used, so only a caller-supplied block (not trusted to be clean) or
     // a kernel that gave up on a bounded wait (reported through the status word) costs a memset.
-    if (user || g_library_scratch_dirty.exchange(false)) CTK_CUDA(cudaMemsetAsync(&(*out)->ticket, 0, sizeof(unsigned int), st));
+    int dev = 0;
+    CTK_CUDA(cudaGetDevice(&dev));
+    const bool dirty = dev >= 0 && dev < 64 && g_library_scratch_dirty[dev].exchange(false);
+    if (user || dirty) CTK_CUDA(cudaMemsetAsync(&(*out)->ticket, 0, sizeof(unsigned int), st));
     return CTK_OK;
 }
 
@@ -174,21 +181,26 @@ extern "C" {
 size_t ctk_reduce_scratch_bytes(void) { return sizeof(ctk::ReduceScratch); }
 
 ctk_status ctk_sum_f32(const float* a, int64_t n, float* out, void* scratch, void* stream) {
+    CTK_RANGE("ctk_sum_f32");
     return launch_reduce<R_SUM>("sum", a, nullptr, n, 0.0f, out, scratch, stream);
 }
 ctk_status ctk_dot_f32(const float* a, const float* b, int64_t n, float* out, void* scratch, void* stream) {
+    CTK_RANGE("ctk_dot_f32");
     return launch_reduce<R_DOT>("dot", a, b, n, 0.0f, out, scratch, stream);
 }
 ctk_status ctk_mse_f32(const float* a, const float* b, int64_t n, float* out, void* scratch, void* stream) {
+    CTK_RANGE("ctk_mse_f32");
     CTK_REQUIRE(n > 0, "ctk_mse_f32: empty input");
     return launch_reduce<R_MSE>("mse", a, b, n, static_cast<float>(n), out, scratch, stream);
 }
 ctk_status ctk_mae_f32(const float* a, const float* b, int64_t n, float* out, void* scratch, void* stream) {
+    CTK_RANGE("ctk_mae_f32");
     CTK_REQUIRE(n > 0, "ctk_mae_f32: empty input");
     return launch_reduce<R_MAE>("mae", a, b, n, static_cast<float>(n), out, scratch, stream);
 }
 
 ctk_status ctk_colsum_f32(const float* x, int64_t rows, int64_t cols, float* out, void* stream) {
+    CTK_RANGE("ctk_colsum_f32");
     CTK_REQUIRE(rows >= 0 && cols >= 0, "ctk_colsum_f32: negative shape");
     if (cols == 0) return CTK_OK;
     CTK_REQUIRE(out && (x || rows == 0), "ctk_colsum_f32: null pointer");
@@ -210,6 +222,7 @@ ctk_status ctk_colsum_f32(const float* x, int64_t rows, int64_t cols, float* out
 }
 
 ctk_status ctk_count_matches_f32(const float* a, const float* b, int64_t n, float* out, void* scratch, void* stream) {
+    CTK_RANGE("ctk_count_matches_f32");
     return launch_reduce<R_MATCH>("count_matches", a, b, n, 0.0f, out, scratch, stream);
 }
 
@@ -230,9 +243,11 @@ static ctk_status mean_loss_backward(bool mse, const float* p, const float* t, c
 }
 
 ctk_status ctk_mse_backward_f32(const float* p, const float* t, const float* g, float* dp, int64_t n, void* stream) {
+    CTK_RANGE("ctk_mse_backward_f32");
     return mean_loss_backward(true, p, t, g, dp, n, stream);
 }
 ctk_status ctk_mae_backward_f32(const float* p, const float* t, const float* g, float* dp, int64_t n, void* stream) {
+    CTK_RANGE("ctk_mae_backward_f32");
     return mean_loss_backward(false, p, t, g, dp, n, stream);
 }
 

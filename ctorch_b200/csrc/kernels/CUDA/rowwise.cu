@@ -649,11 +649,9 @@ ctk_status launch_tile_form(const RowArgs& A, ReduceScratch* s, float* loss_out,
     auto k = tile_rows_kernel<ALG, MAXC, ROT, PIPE>;
     constexpr int kOperands = alg_two_operands<ALG>() ? 2 : 1;
     const size_t smem = static_cast<size_t>(kTileRows) * A.cols * sizeof(float) * kOperands * (PIPE ? 2 : 1);
-    static bool attr_set = false;  // up to 128 KiB (two operands, two buffers, 16 columns): above the default limit
-    if (!attr_set) {
+    static ctk::PerDeviceOnce attr;  // up to 128 KiB (two operands, two buffers, 16 columns): above the default limit
+    if (attr.first())
         CTK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kTileRows * MAXC * kOperands * (PIPE ? 2 : 1) * static_cast<int>(sizeof(float))));
-        attr_set = true;
-    }
     int64_t grid = (A.rows + kTileRows - 1) / kTileRows;
     static int64_t resident[MAXC + 1] = {0};  // by column count (it sets the shared-memory need)
     if (!resident[A.cols]) resident[A.cols] = resident_ctas(k, kTileThreads, smem);
@@ -1052,11 +1050,8 @@ template <int ALG, int ITEMS>
 ctk_status launch_streamed(const RowArgs& A, ReduceScratch* s, float* loss_out, cudaStream_t st) {
     auto k = streamed_rows_kernel<ALG, ITEMS>;
     constexpr int smem = kRingSlots * kChunkBytes;
-    static bool attr_set = false;  // raises the opt-in shared-memory limit once per process, per instantiation
-    if (!attr_set) {
-        CTK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        attr_set = true;
-    }
+    static ctk::PerDeviceOnce attr;  // raises the opt-in shared-memory limit once per device, per instantiation
+    if (attr.first()) CTK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     const int64_t sms = ctk::sm_count();
     const int64_t grid = A.rows < sms ? A.rows : sms;
     k<<<static_cast<unsigned>(grid), kStreamThreads, smem, st>>>(A, s, loss_out);
@@ -1160,12 +1155,10 @@ ctk_status launch_rows(const char* name, const RowArgs& A, float* loss_out, void
         if (grid > kMaxReduceBlocks) grid = kMaxReduceBlocks;
         if (c <= kSmemRowMaxCols) {
             size_t bytes = static_cast<size_t>(c) * sizeof(float);
-            static bool attr_set = false;  // raises the opt-in limit once per process, per instantiation
-            if (!attr_set) {
+            static ctk::PerDeviceOnce attr;  // raises the opt-in limit once per device, per instantiation
+            if (attr.first())
                 CTK_CUDA(cudaFuncSetAttribute(cta_rows_kernel<ALG, SmemRow>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                               kSmemRowMaxCols * static_cast<int>(sizeof(float))));
-                attr_set = true;
-            }
             cta_rows_kernel<ALG, SmemRow><<<grid, kRowThreads, bytes, st>>>(A, s, loss_out);
         } else {
             cta_rows_kernel<ALG, GlobalRow><<<grid, kRowThreads, 0, st>>>(A, s, loss_out);
@@ -1189,12 +1182,14 @@ ctk_status ctk_rowwise_status(int* status) {
 }
 
 ctk_status ctk_softmax_rows_f32(const float* x, float* y, int64_t rows, int64_t cols, void* stream) {
+    CTK_RANGE("ctk_softmax_rows_f32");
     CTK_REQUIRE((x && y) || rows == 0 || cols == 0, "ctk_softmax_rows_f32: null pointer");
     RowArgs A{x, nullptr, y, nullptr, nullptr, rows, cols};
     return launch_rows<ALG_SOFTMAX>("softmax_rows", A, nullptr, nullptr, stream);
 }
 
 ctk_status ctk_softmax_cols_f32(const float* x, float* y, int64_t rows, int64_t cols, void* stream) {
+    CTK_RANGE("ctk_softmax_cols_f32");
     CTK_REQUIRE(rows >= 0 && cols >= 0, "ctk_softmax_cols_f32: negative shape");
     if (rows == 0 || cols == 0) return CTK_OK;
     CTK_REQUIRE(x && y, "ctk_softmax_cols_f32: null pointer");
@@ -1206,6 +1201,7 @@ ctk_status ctk_softmax_cols_f32(const float* x, float* y, int64_t rows, int64_t 
 }
 
 ctk_status ctk_softmax_backward_cols_f32(const float* y, const float* g, float* dx, int64_t rows, int64_t cols, void* stream) {
+    CTK_RANGE("ctk_softmax_backward_cols_f32");
     CTK_REQUIRE(rows >= 0 && cols >= 0, "ctk_softmax_backward_cols_f32: negative shape");
     if (rows == 0 || cols == 0) return CTK_OK;
     CTK_REQUIRE(y && g && dx, "ctk_softmax_backward_cols_f32: null pointer");
@@ -1217,6 +1213,7 @@ ctk_status ctk_softmax_backward_cols_f32(const float* y, const float* g, float* 
 }
 
 ctk_status ctk_softmax_backward_rows_f32(const float* y, const float* g, float* dx, int64_t rows, int64_t cols, void* stream) {
+    CTK_RANGE("ctk_softmax_backward_rows_f32");
     CTK_REQUIRE((y && g && dx) || rows == 0 || cols == 0, "ctk_softmax_backward_rows_f32: null pointer");
     RowArgs A{y, g, dx, nullptr, nullptr, rows, cols};
     return launch_rows<ALG_SOFTMAX_BWD>("softmax_backward_rows", A, nullptr, nullptr, stream);
@@ -1224,6 +1221,7 @@ ctk_status ctk_softmax_backward_rows_f32(const float* y, const float* g, float* 
 
 ctk_status ctk_ce_onehot_f32(const float* logits, const float* onehot, int64_t rows, int64_t cols, float* out,
                              void* scratch, void* stream) {
+    CTK_RANGE("ctk_ce_onehot_f32");
     CTK_REQUIRE((logits && onehot) || rows == 0 || cols == 0, "ctk_ce_onehot_f32: null pointer");
     RowArgs A{logits, onehot, nullptr, nullptr, nullptr, rows, cols};
     return launch_rows<ALG_CE_ONEHOT>("ce_onehot", A, out, scratch, stream);
@@ -1231,6 +1229,7 @@ ctk_status ctk_ce_onehot_f32(const float* logits, const float* onehot, int64_t r
 
 ctk_status ctk_ce_index_f32(const float* logits, const float* labels, int64_t rows, int64_t cols, float* out,
                             int* bad_label_flag, void* scratch, void* stream) {
+    CTK_RANGE("ctk_ce_index_f32");
     CTK_REQUIRE((logits && labels) || rows == 0 || cols == 0, "ctk_ce_index_f32: null pointer");
     RowArgs A{logits, labels, nullptr, nullptr, bad_label_flag, rows, cols};
     return launch_rows<ALG_CE_INDEX>("ce_index", A, out, scratch, stream);
@@ -1238,6 +1237,7 @@ ctk_status ctk_ce_index_f32(const float* logits, const float* labels, int64_t ro
 
 ctk_status ctk_ce_backward_f32(const float* logits, const float* onehot, const float* g_device, float* dlogits,
                                int64_t rows, int64_t cols, void* stream) {
+    CTK_RANGE("ctk_ce_backward_f32");
     CTK_REQUIRE((logits && onehot && dlogits) || rows == 0 || cols == 0, "ctk_ce_backward_f32: null pointer");
     RowArgs A{logits, onehot, dlogits, g_device, nullptr, rows, cols};
     return launch_rows<ALG_CE_BWD>("ce_backward", A, nullptr, nullptr, stream);
@@ -1245,6 +1245,7 @@ ctk_status ctk_ce_backward_f32(const float* logits, const float* onehot, const f
 
 ctk_status ctk_ce_fused_index_f32(const float* logits, const float* labels, int64_t rows, int64_t cols, float* out,
                                   float* dlogits, int* bad_label_flag, void* scratch, void* stream) {
+    CTK_RANGE("ctk_ce_fused_index_f32");
     CTK_REQUIRE((logits && labels && dlogits) || rows == 0 || cols == 0, "ctk_ce_fused_index_f32: null pointer");
     RowArgs A{logits, labels, dlogits, nullptr, bad_label_flag, rows, cols};
     return launch_rows<ALG_CE_FUSED>("ce_fused_index", A, out, scratch, stream);

@@ -5,7 +5,10 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <chrono>
+#include <cstring>
 #include <mutex>
+#include <thread>
 #include <vector>
 
 #include "common.cuh"
@@ -311,14 +314,66 @@ ctk_status ctk_stream_wait_event(void* s, void* e) {
     return CTK_OK;
 }
 
+}  // extern "C"
+
+// ---- bounded host-side wait -----------------------------------------------------------------------
+// The loop every blocking wait of the data-parallel path runs instead of an unbounded stream
+// synchronisation: poll "is the work done", poll "is the communicator healthy", give up at a deadline.
+// The three callbacks make the same loop testable without a GPU (ranks over gloo where one never
+// contributes): query returns 1 when done, 0 when pending, < 0 on an error of its own; health returns
+// 0 while fine; abort is called once before an error is returned.
+extern "C" ctk_status ctk_watchdog_wait(ctk_watch_fn query, ctk_watch_fn health, ctk_watch_fn abort_fn, void* user, int timeout_ms, int poll_us) {
+    CTK_REQUIRE(query && timeout_ms >= 0, "ctk_watchdog_wait: a query callback and a non-negative timeout are needed");
+    const auto t0 = std::chrono::steady_clock::now();
+    const auto limit = std::chrono::milliseconds(timeout_ms);
+    const auto nap = std::chrono::microseconds(poll_us > 0 ? poll_us : 50);
+    const auto spin_for = std::chrono::milliseconds(20);  // a step normally ends within this: poll hot, like a plain synchronisation
+    auto last_check = t0;
+    for (;;) {
+        const int q = query(user);
+        if (q > 0) return CTK_OK;
+        const auto now = std::chrono::steady_clock::now();
+        std::string why;
+        if (q < 0) {
+            why = "the awaited work reported an error (" + std::to_string(q) + ")";
+        } else if (now - last_check >= std::chrono::microseconds(500) || now - t0 > limit) {
+            // health and deadline twice a millisecond: the health call may take a lock inside the library
+            last_check = now;
+            if (health) {
+                const int h = health(user);
+                if (h != 0) why = "the communicator reported an asynchronous error (" + std::to_string(h) + ")";
+            }
+            if (why.empty() && now - t0 > limit) why = "no completion within " + std::to_string(timeout_ms) + " ms: a peer did not take part";
+        }
+        if (!why.empty()) {
+            if (abort_fn) abort_fn(user);
+            return fail(CTK_ERR_NCCL, "data-parallel wait gave up: " + why);
+        }
+        if (now - t0 < spin_for) std::this_thread::yield();
+        else std::this_thread::sleep_for(nap);
+    }
+}
+
 // ---- NCCL: loaded at first use so the library itself has no link-time NCCL dependency ----
 namespace {
 struct Nccl {
     void* h = nullptr;
     ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
     ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommInitRankConfig)(ncclComm_t*, int, ncclUniqueId, int, ncclConfig_t*) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
+    ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t*) = nullptr;
     ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*ReduceScatter)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*MemAlloc)(void**, size_t) = nullptr;
+    ncclResult_t (*MemFree)(void*) = nullptr;
+    ncclResult_t (*CommRegister)(const ncclComm_t, void*, size_t, void**) = nullptr;
+    ncclResult_t (*CommDeregister)(const ncclComm_t, void*) = nullptr;
+    ncclResult_t (*CommWindowRegister)(ncclComm_t, void*, size_t, ncclWindow_t*, int) = nullptr;  // optional (NCCL >= 2.27)
+    ncclResult_t (*CommWindowDeregister)(ncclComm_t, ncclWindow_t) = nullptr;
+    ncclResult_t (*GetVersion)(int*) = nullptr;
     const char* (*GetErrorString)(ncclResult_t) = nullptr;
 };
 Nccl g_nccl;
@@ -328,22 +383,53 @@ ctk_status load_nccl() {
     if (g_nccl.h) return CTK_OK;
     // An already loaded libnccl (e.g. the one a host framework brought) is reused by soname.
     const char* names[] = {"libnccl.so.2", "libnccl.so"};
+    void* h = nullptr;
     for (const char* n : names) {
-        g_nccl.h = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
-        if (g_nccl.h) break;
+        h = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+        if (h) break;
     }
-    if (!g_nccl.h) return fail(CTK_ERR_NCCL, std::string("dlopen libnccl.so.2: ") + dlerror());
-#define CTK_SYM(field, name)                                                         \
-    g_nccl.field = reinterpret_cast<decltype(g_nccl.field)>(dlsym(g_nccl.h, name)); \
+    if (!h) return fail(CTK_ERR_NCCL, std::string("dlopen libnccl.so.2: ") + dlerror());
+#define CTK_SYM(field, name)                                                  \
+    g_nccl.field = reinterpret_cast<decltype(g_nccl.field)>(dlsym(h, name)); \
     if (!g_nccl.field) return fail(CTK_ERR_NCCL, std::string("dlsym ") + name)
+#define CTK_SYM_OPT(field, name) g_nccl.field = reinterpret_cast<decltype(g_nccl.field)>(dlsym(h, name))
     CTK_SYM(GetUniqueId, "ncclGetUniqueId");
     CTK_SYM(CommInitRank, "ncclCommInitRank");
+    CTK_SYM(CommInitRankConfig, "ncclCommInitRankConfig");
     CTK_SYM(CommDestroy, "ncclCommDestroy");
+    CTK_SYM(CommAbort, "ncclCommAbort");
+    CTK_SYM(CommGetAsyncError, "ncclCommGetAsyncError");
     CTK_SYM(AllReduce, "ncclAllReduce");
+    CTK_SYM(ReduceScatter, "ncclReduceScatter");
+    CTK_SYM(AllGather, "ncclAllGather");
     CTK_SYM(GetErrorString, "ncclGetErrorString");
+    CTK_SYM_OPT(MemAlloc, "ncclMemAlloc");
+    CTK_SYM_OPT(MemFree, "ncclMemFree");
+    CTK_SYM_OPT(CommRegister, "ncclCommRegister");
+    CTK_SYM_OPT(CommDeregister, "ncclCommDeregister");
+    CTK_SYM_OPT(CommWindowRegister, "ncclCommWindowRegister");
+    CTK_SYM_OPT(CommWindowDeregister, "ncclCommWindowDeregister");
+    CTK_SYM_OPT(GetVersion, "ncclGetVersion");
 #undef CTK_SYM
+#undef CTK_SYM_OPT
+    g_nccl.h = h;
     return CTK_OK;
 }
+
+// What a `void* comm` of the C ABI points to.
+struct Comm {
+    ncclComm_t c = nullptr;
+    int world = 1, rank = 0;
+    bool aborted = false;
+    struct Buffer {
+        void* p = nullptr;
+        size_t bytes = 0;
+        void* handle = nullptr;       // ncclCommRegister
+        ncclWindow_t win = nullptr;   // ncclCommWindowRegister
+    };
+    std::vector<Buffer> buffers;
+};
+Comm* as_comm(void* h) { return static_cast<Comm*>(h); }
 }  // namespace
 
 #define CTK_NCCL(call)                                                                                   \
@@ -351,6 +437,8 @@ ctk_status load_nccl() {
         ncclResult_t _r = (call);                                                                        \
         if (_r != ncclSuccess) return fail(CTK_ERR_NCCL, std::string(#call) + ": " + g_nccl.GetErrorString(_r)); \
     } while (0)
+
+extern "C" {
 
 ctk_status ctk_comm_unique_id(void* id_out) {
     CTK_REQUIRE(id_out, "ctk_comm_unique_id: null");
@@ -360,27 +448,190 @@ ctk_status ctk_comm_unique_id(void* id_out) {
     CTK_NCCL(g_nccl.GetUniqueId(reinterpret_cast<ncclUniqueId*>(id_out)));
     return CTK_OK;
 }
-ctk_status ctk_comm_init_rank(void** comm, const void* id, int world, int rank) {
-    CTK_REQUIRE(comm && id && world > 0 && rank >= 0 && rank < world, "ctk_comm_init_rank: bad arguments");
+// max_ctas / nvls_ctas: upper bound on the CTAs one collective may occupy, and the CTAs of its
+// in-switch (NVLS) part; 0 leaves NCCL's own choice.  The collectives share the SMs with the persistent
+// MatMul kernels, so a communicator for gradient exchange under backward wants few of them.
+ctk_status ctk_comm_init_rank_config(void** comm, const void* id, int world, int rank, int max_ctas, int nvls_ctas) {
+    CTK_REQUIRE(comm && id && world > 0 && rank >= 0 && rank < world && max_ctas >= 0 && nvls_ctas >= 0, "ctk_comm_init_rank: bad arguments");
     ctk_status st = load_nccl();
     if (st) return st;
     ncclUniqueId uid;
     memcpy(&uid, id, sizeof(uid));
     ncclComm_t c;
-    CTK_NCCL(g_nccl.CommInitRank(&c, world, uid, rank));
-    *comm = c;
+    if (max_ctas == 0 && nvls_ctas == 0) {
+        CTK_NCCL(g_nccl.CommInitRank(&c, world, uid, rank));
+    } else {
+        ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
+        if (max_ctas > 0) cfg.maxCTAs = max_ctas;
+        if (nvls_ctas > 0) cfg.nvlsCTAs = nvls_ctas;
+        CTK_NCCL(g_nccl.CommInitRankConfig(&c, world, uid, rank, &cfg));
+    }
+    Comm* w = new Comm();
+    w->c = c;
+    w->world = world;
+    w->rank = rank;
+    *comm = w;
+    return CTK_OK;
+}
+ctk_status ctk_comm_init_rank(void** comm, const void* id, int world, int rank) { return ctk_comm_init_rank_config(comm, id, world, rank, 0, 0); }
+
+ctk_status ctk_comm_info(void* comm, int* world, int* rank, int* nccl_version) {
+    CTK_REQUIRE(comm, "ctk_comm_info: null communicator");
+    if (world) *world = as_comm(comm)->world;
+    if (rank) *rank = as_comm(comm)->rank;
+    if (nccl_version) {
+        *nccl_version = 0;
+        if (g_nccl.GetVersion) g_nccl.GetVersion(nccl_version);
+    }
+    return CTK_OK;
+}
+
+// Device memory the communicator knows: allocated by NCCL's allocator and registered with the
+// communicator (symmetric != 0: as a symmetric window, every rank registering the same size in the same
+// order -- a collective call), so that collectives on it can reduce in the switch straight out of
+// user memory with a handful of CTAs instead of staging through NCCL's own buffers.  Falls back to
+// unregistered memory where the loaded NCCL lacks the calls.  Collective: every rank calls it.
+ctk_status ctk_comm_alloc(void* comm, size_t bytes, int symmetric, void** ptr) {
+    CTK_REQUIRE(comm && ptr && bytes > 0, "ctk_comm_alloc: bad arguments");
+    Comm* w = as_comm(comm);
+    Comm::Buffer b;
+    b.bytes = bytes;
+    if (g_nccl.MemAlloc && g_nccl.MemFree) {
+        CTK_NCCL(g_nccl.MemAlloc(&b.p, bytes));
+        if (symmetric && g_nccl.CommWindowRegister && g_nccl.CommWindowDeregister) {
+            CTK_NCCL(g_nccl.CommWindowRegister(w->c, b.p, bytes, &b.win, NCCL_WIN_COLL_SYMMETRIC));
+        } else if (g_nccl.CommRegister && g_nccl.CommDeregister) {
+            CTK_NCCL(g_nccl.CommRegister(w->c, b.p, bytes, &b.handle));
+        }
+    } else {
+        CTK_CUDA(cudaMalloc(&b.p, bytes));
+    }
+    w->buffers.push_back(b);
+    *ptr = b.p;
+    return CTK_OK;
+}
+static ctk_status release_buffer(Comm* w, Comm::Buffer& b) {
+    if (!w->aborted) {
+        if (b.win) CTK_NCCL(g_nccl.CommWindowDeregister(w->c, b.win));
+        if (b.handle) CTK_NCCL(g_nccl.CommDeregister(w->c, b.handle));
+    }
+    if (g_nccl.MemAlloc && g_nccl.MemFree) CTK_NCCL(g_nccl.MemFree(b.p));
+    else CTK_CUDA(cudaFree(b.p));
+    return CTK_OK;
+}
+ctk_status ctk_comm_free(void* comm, void* ptr) {
+    CTK_REQUIRE(comm, "ctk_comm_free: null communicator");
+    if (!ptr) return CTK_OK;
+    Comm* w = as_comm(comm);
+    for (size_t i = 0; i < w->buffers.size(); ++i)
+        if (w->buffers[i].p == ptr) {
+            Comm::Buffer b = w->buffers[i];
+            w->buffers.erase(w->buffers.begin() + static_cast<long>(i));
+            return release_buffer(w, b);
+        }
+    return fail(CTK_ERR_INVALID, "ctk_comm_free: not a buffer of this communicator");
+}
+
+// Stops the communicator where it stands (ncclCommAbort): its kernels in flight end, later calls on
+// it fail.  What a rank does after ctk_comm_wait reported that a peer is gone.
+ctk_status ctk_comm_abort(void* comm) {
+    CTK_REQUIRE(comm, "ctk_comm_abort: null communicator");
+    Comm* w = as_comm(comm);
+    if (w->aborted) return CTK_OK;
+    w->aborted = true;
+    CTK_NCCL(g_nccl.CommAbort(w->c));
     return CTK_OK;
 }
 ctk_status ctk_comm_destroy(void* comm) {
     if (!comm) return CTK_OK;
-    CTK_NCCL(g_nccl.CommDestroy(reinterpret_cast<ncclComm_t>(comm)));
-    return CTK_OK;
+    Comm* w = as_comm(comm);
+    ctk_status rc = CTK_OK;
+    for (auto& b : w->buffers) {
+        ctk_status r = release_buffer(w, b);
+        if (r && !rc) rc = r;
+    }
+    w->buffers.clear();
+    if (!w->aborted) {
+        ncclResult_t r = g_nccl.CommDestroy(w->c);
+        if (r != ncclSuccess && !rc) rc = fail(CTK_ERR_NCCL, std::string("ncclCommDestroy: ") + g_nccl.GetErrorString(r));
+    }
+    delete w;
+    return rc;
 }
+
+// Waits, on the host, until `event` (recorded behind the step's last collective or kernel) has
+// completed -- but never longer than timeout_ms, and not past an asynchronous NCCL error: a peer that
+// died or never joined leaves a collective spinning on the GPU for ever, and an unbounded stream
+// synchronisation with it.  On giving up the communicator is aborted, which ends its kernels, and
+// CTK_ERR_NCCL is returned; the CUDA context stays usable.
+namespace {
+struct CommWait {
+    Comm* w;
+    cudaEvent_t ev;
+    int cuda_error;
+};
+int comm_wait_query(void* u) {
+    CommWait* x = static_cast<CommWait*>(u);
+    const cudaError_t e = cudaEventQuery(x->ev);
+    if (e == cudaSuccess) return 1;
+    if (e == cudaErrorNotReady) return 0;
+    x->cuda_error = static_cast<int>(e);
+    return -static_cast<int>(e);
+}
+int comm_wait_health(void* u) {
+    CommWait* x = static_cast<CommWait*>(u);
+    ncclResult_t async = ncclSuccess;
+    const ncclResult_t r = g_nccl.CommGetAsyncError(x->w->c, &async);
+    if (r != ncclSuccess) return static_cast<int>(r);
+    return (async == ncclSuccess || async == ncclInProgress) ? 0 : static_cast<int>(async);
+}
+int comm_wait_abort(void* u) {
+    CommWait* x = static_cast<CommWait*>(u);
+    if (!x->w->aborted) {
+        x->w->aborted = true;
+        g_nccl.CommAbort(x->w->c);
+    }
+    return 0;
+}
+}  // namespace
+ctk_status ctk_comm_wait(void* comm, void* event, int timeout_ms) {
+    CTK_REQUIRE(comm && event, "ctk_comm_wait: null argument");
+    Comm* w = as_comm(comm);
+    if (w->aborted) return fail(CTK_ERR_NCCL, "ctk_comm_wait: the communicator was aborted");
+    CommWait x{w, reinterpret_cast<cudaEvent_t>(event), 0};
+    return ctk_watchdog_wait(comm_wait_query, comm_wait_health, comm_wait_abort, &x, timeout_ms, 50);
+}
+
+#define CTK_COMM_LIVE(name)                                                                   \
+    Comm* w = as_comm(comm);                                                                  \
+    if (w->aborted) return fail(CTK_ERR_NCCL, std::string(name) + ": the communicator was aborted")
+
 ctk_status ctk_allreduce_sum_f32(void* comm, float* buf, int64_t n, void* stream) {
+    CTK_RANGE("ctk_allreduce_sum_f32");
     CTK_REQUIRE(comm && buf && n >= 0, "ctk_allreduce_sum_f32: bad arguments");
     if (n == 0) return CTK_OK;
-    CTK_NCCL(g_nccl.AllReduce(buf, buf, static_cast<size_t>(n), ncclFloat, ncclSum,
-                              reinterpret_cast<ncclComm_t>(comm), as_stream(stream)));
+    CTK_COMM_LIVE("ctk_allreduce_sum_f32");
+    CTK_NCCL(g_nccl.AllReduce(buf, buf, static_cast<size_t>(n), ncclFloat, ncclSum, w->c, as_stream(stream)));
+    return CTK_OK;
+}
+// recv[0, count) of this rank = sum over ranks of send[rank * count, (rank + 1) * count); send holds
+// world * count floats.  recv may point into send at rank * count (in place).
+ctk_status ctk_reduce_scatter_sum_f32(void* comm, const float* send, float* recv, int64_t count, void* stream) {
+    CTK_RANGE("ctk_reduce_scatter_sum_f32");
+    CTK_REQUIRE(comm && send && recv && count >= 0, "ctk_reduce_scatter_sum_f32: bad arguments");
+    if (count == 0) return CTK_OK;
+    CTK_COMM_LIVE("ctk_reduce_scatter_sum_f32");
+    CTK_NCCL(g_nccl.ReduceScatter(send, recv, static_cast<size_t>(count), ncclFloat, ncclSum, w->c, as_stream(stream)));
+    return CTK_OK;
+}
+// recv[r * count, (r + 1) * count) = rank r's send[0, count) for every r; send may point into recv at
+// rank * count (in place).
+ctk_status ctk_allgather_f32(void* comm, const float* send, float* recv, int64_t count, void* stream) {
+    CTK_RANGE("ctk_allgather_f32");
+    CTK_REQUIRE(comm && send && recv && count >= 0, "ctk_allgather_f32: bad arguments");
+    if (count == 0) return CTK_OK;
+    CTK_COMM_LIVE("ctk_allgather_f32");
+    CTK_NCCL(g_nccl.AllGather(send, recv, static_cast<size_t>(count), ncclFloat, w->c, as_stream(stream)));
     return CTK_OK;
 }
 

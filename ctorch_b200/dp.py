@@ -65,13 +65,31 @@ def shard_seed(base_seed, rank):
     return base_seed + 1000 * rank
 
 
-def make_comm(cb, cp):
-    """Creates the NCCL communicator of this rank (ctk_comm_init_rank) from an id made on rank 0."""
+def make_comm(cb, cp, max_ctas=0, nvls_ctas=0):
+    """Creates the NCCL communicator of this rank (ctk_comm_init_rank_config) from an id made on rank 0.
+    max_ctas / nvls_ctas bound the CTAs a collective may take from the MatMul kernels (0: NCCL's choice)."""
     import ctypes
     idbuf = np.zeros(128, np.uint8)
     if cp.rank == 0:
         cb.check(cb.lib.ctk_comm_unique_id(idbuf.ctypes.data_as(ctypes.c_void_p)))
     cp.broadcast_bytes(idbuf, 0)
     comm = ctypes.c_void_p()
-    cb.check(cb.lib.ctk_comm_init_rank(ctypes.byref(comm), idbuf.ctypes.data_as(ctypes.c_void_p), cp.world, cp.rank))
+    cb.check(cb.lib.ctk_comm_init_rank_config(ctypes.byref(comm), idbuf.ctypes.data_as(ctypes.c_void_p), cp.world, cp.rank, int(max_ctas), int(nvls_ctas)))
     return comm
+
+
+class Watchdog:
+    """The library's bounded wait (ctk_watchdog_wait) over Python callables: query() -> 1 done / 0 pending
+    / < 0 error, health() -> 0 while fine, abort() once before an error is reported.  The GPU path uses
+    the same loop with a CUDA event and ncclCommGetAsyncError behind it (ctk_comm_wait)."""
+
+    def __init__(self, cb):
+        import ctypes
+        self.cb = cb
+        self.FN = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p)
+
+    def wait(self, query, health=None, abort=None, timeout_ms=1000, poll_us=50):
+        q = self.FN(lambda _u: int(query()))
+        h = self.FN(lambda _u: int(health())) if health else None
+        a = self.FN(lambda _u: int(abort() or 0)) if abort else None
+        return self.cb.lib.ctk_watchdog_wait(q, h, a, None, int(timeout_ms), int(poll_us))

@@ -260,6 +260,13 @@ class AutoDiff:
     def clear_graph(self): _chk(lib.cth_ctx_clear(self.h))
     def release_step_nodes(self): _chk(lib.cth_ctx_release_step_nodes(self.h))
     def set_fuse_relu_backward(self, on): _chk(lib.cth_ctx_set_fuse_relu_backward(self.h, 1 if on else 0))
+    def count_leaf_grads(self, on=True): _chk(lib.cth_ctx_count_leaf_grads(self.h, 1 if on else 0))
+
+    def leaf_grad_count(self, t):
+        """How often the leaf-gradient hook fired for tensor t since count_leaf_grads()."""
+        n = ctypes.c_uint64()
+        _chk(lib.cth_ctx_leaf_grad_count(self.h, t.h, ctypes.byref(n)))
+        return n.value
 
     def node_count(self):
         n = ctypes.c_uint64()
@@ -299,6 +306,15 @@ class MlpTrainer:
 
     def set_comm(self, comm_handle):
         _chk(lib.cth_mlp_set_comm(self.h, comm_handle))
+
+    DP_MODES = {"inplace": 0, "arena": 1, "serial": 2, "sharded": 3}
+
+    def set_dp_mode(self, mode):
+        """How gradients cross the ranks (before set_comm): 'inplace' (default), 'arena', 'serial', 'sharded'."""
+        _chk(lib.cth_mlp_set_dp_mode(self.h, self.DP_MODES.get(mode, mode)))
+
+    def set_comm_timeout_ms(self, ms):
+        _chk(lib.cth_mlp_set_comm_timeout_ms(self.h, int(ms)))
 
     def set_corrected(self, exact_bias_grad=True, fresh_weights=True):
         """Opt-in: true bias gradients and backward against the current weights (not the reference's arithmetic)."""

@@ -296,10 +296,6 @@ def set_matmul_pairing(pairing):
     check(lib.ctk_set_matmul_pairing(int(pairing)))
 
 
-def set_matmul_dynamic_order(on):
-    check(lib.ctk_set_matmul_dynamic_order(int(on)))
-
-
 def set_matmul_tail_split(on):
     check(lib.ctk_set_matmul_tail_split(int(on)))
 

@@ -291,10 +291,6 @@ ctk_status ctk_set_matmul_pairing(int pairing);
 /* tiles is computed as two halves of K that are added into the zeroed output (two addends: the    */
 /* result does not depend on their order).  0: every tile whole.                                   */
 ctk_status ctk_set_matmul_tail_split(int on);
-/* 0 (default): pair i of the pair kernel takes tiles i, i + pairs, ...  1: the pairs draw their tiles  */
-/* from a counter as they go, so that a pair which starts late takes fewer.  The result does not depend */
-/* on the choice.  Measured: equal on one GPU, 1-2 % slower steps under a concurrent all-reduce.        */
-ctk_status ctk_set_matmul_dynamic_order(int on);
 /* Self-test of the kernels' bounded waits (no counterpart in the reference): one CTA waits with a  */
 /* short limit on a barrier nothing arrives on.  result = {first wait ok (expected 0), CTA abort     */
 /* flag (1), second waiter ok (0: it leaves as soon as it sees the flag), status word (0x7e57)}.    */
@@ -348,9 +344,13 @@ ctk_status ctk_sgd_update_split_f32(float* p, const float* g, float lr, int64_t 
  * that cannot afford a workspace growing under it): identical arguments and result to
  * ctk_matmul_f32(..., CTK_MATMUL_3XTF32, ...), but the hi/lo split lives in a fixed 16 MiB array that
  * is part of the library (held by every GPU that loads it).  Limit: the 2*(m*k + k*n) split floats
- * may take at most 16 MiB (1024x1024 by 1024x1024 just fits), otherwise CTK_ERR_LIMIT and nothing runs.  The first call per device does a
- * one-time set-up and belongs outside any stream capture; calls that may overlap on the GPU race on
- * the shared array; launch timing must be off. */
+ * may take at most 16 MiB (1024x1024 by 1024x1024 just fits), otherwise CTK_ERR_LIMIT and nothing runs.
+ * One-time set-up: the first call on a device looks up the array's address, and the first call of each
+ * SHAPE CLASS on a device (tile width 64 / 128 / 256 from n, each operand's major-ness, CTA pairs or
+ * not from m > 128) sets that kernel's shared-memory attribute and, for CTA pairs, asks the occupancy.
+ * Make one call per shape class you will use outside any stream capture first.  `stream` must belong
+ * to the device that is current at the call (the array's address is looked up for the current device).
+ * Calls that may overlap on the GPU race on the shared array; launch timing must be off. */
 ctk_status ctk_matmul_3xtf32_noalloc_f32(const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k,
                                          int64_t sa0, int64_t sa1, int64_t sb0, int64_t sb1, void* stream);
 /* Which path ctk_matmul_f32 would take: 0 tcgen05, 1 SIMT (an operand without a unit stride, or on
@@ -377,8 +377,34 @@ ctk_status ctk_matmul_status(int* status);
 #define CTK_COMM_ID_BYTES 128
 ctk_status ctk_comm_unique_id(void* id_out_128_bytes);
 ctk_status ctk_comm_init_rank(void** comm, const void* id_128_bytes, int world_size, int rank);
+/* The same with an upper bound on the CTAs a collective may occupy (max_ctas) and on those of its
+ * in-switch part (nvls_ctas); 0 = NCCL's choice.  The collectives share the SMs with the persistent
+ * MatMul kernels of backward. */
+ctk_status ctk_comm_init_rank_config(void** comm, const void* id_128_bytes, int world_size, int rank, int max_ctas, int nvls_ctas);
+ctk_status ctk_comm_info(void* comm, int* world_size, int* rank, int* nccl_version);
 ctk_status ctk_comm_destroy(void* comm);
+/* Device memory allocated by NCCL's allocator and registered with the communicator (symmetric != 0:
+ * as a symmetric window), so collectives on it run out of user memory.  Collective calls: every rank
+ * makes them, with the same sizes, in the same order. */
+ctk_status ctk_comm_alloc(void* comm, size_t bytes, int symmetric, void** device_ptr);
+ctk_status ctk_comm_free(void* comm, void* device_ptr);
 ctk_status ctk_allreduce_sum_f32(void* comm, float* device_buf, int64_t n, void* stream);
+/* recv[0, count) = sum over ranks of send[rank*count, (rank+1)*count); send holds world*count floats. */
+ctk_status ctk_reduce_scatter_sum_f32(void* comm, const float* send, float* recv, int64_t count, void* stream);
+/* recv[r*count, (r+1)*count) = rank r's send[0, count). */
+ctk_status ctk_allgather_f32(void* comm, const float* send, float* recv, int64_t count, void* stream);
+/* Failure detection.  ctk_comm_wait blocks the host until `event` has completed, polling the event and
+ * ncclCommGetAsyncError, for at most timeout_ms: a peer that died or never joined would otherwise leave
+ * the collective -- and a plain stream synchronisation -- waiting for ever.  On an asynchronous error
+ * or at the deadline the communicator is aborted (ncclCommAbort ends its kernels) and CTK_ERR_NCCL is
+ * returned; the CUDA context stays usable, the communicator does not.  ctk_comm_abort does the abort
+ * alone.  ctk_watchdog_wait is the loop underneath with the three steps as callbacks (query: 1 done,
+ * 0 pending, < 0 error; health: 0 fine; abort: called once before an error is returned), which is how
+ * the loop is tested without a GPU. */
+typedef int (*ctk_watch_fn)(void* user);
+ctk_status ctk_comm_wait(void* comm, void* event, int timeout_ms);
+ctk_status ctk_comm_abort(void* comm);
+ctk_status ctk_watchdog_wait(ctk_watch_fn query, ctk_watch_fn health, ctk_watch_fn abort_fn, void* user, int timeout_ms, int poll_us);
 
 #ifdef __cplusplus
 }

@@ -64,6 +64,10 @@ int cth_tensor_rand(void* tensor);                                   /* Tensor::
 int cth_manual_seed(uint64_t seed);                                  /* no counterpart: fixes rand's seed and restarts its counter */
 int cth_tensor_index(void* tensor, uint64_t index, void** out);      /* Tensor::operator[], src/Tensor.cpp:175-189 */
 
+/* Host-only self-test (no GPU needed, no counterpart in the reference): the caches that recycle     */
+/* device buffers are keyed by (device ordinal, size); *failed = number of checks that did not hold. */
+int cth_selftest_cache_keying(int* failed);
+
 int cth_ctx_create(void** ctx);
 int cth_ctx_destroy(void* ctx);
 int cth_ctx_set_current(void* ctx_or_null);           /* AutoDiffContext::current() of the calling thread */
@@ -72,6 +76,11 @@ int cth_ctx_zero_grad(void* ctx, void* tensor);
 int cth_ctx_clear(void* ctx);                         /* AutoDiff::clear_graph */
 int cth_ctx_release_step_nodes(void* ctx);            /* drop nodes no future root can reach (no counterpart) */
 int cth_ctx_node_count(void* ctx, uint64_t* n);
+/* AutoDiff::on_leaf_grad (no counterpart in the reference) fires once per leaf and backward pass,   */
+/* after the leaf's last contribution.  count_leaf_grads(1) installs a hook that only counts the     */
+/* calls per tensor, leaf_grad_count reads the count for one tensor.                                  */
+int cth_ctx_count_leaf_grads(void* ctx, int on);
+int cth_ctx_leaf_grad_count(void* ctx, void* tensor, uint64_t* n);
 /* No counterpart.  on != 0: a ReLU output that exactly one MatMul reads (as its first operand) gets its
  * backward rule (src/AutoDiff.cpp:1320-1371) applied in the epilogue of the product g.W^T that computes
  * its gradient.  Every gradient upstream is bit for bit the same; cth_grad of that ReLU output itself
@@ -93,6 +102,18 @@ int cth_mlp_destroy(void* mlp);
 /* Data parallel: all-reduce (sum) every parameter gradient over `comm` (a ctk_comm_init_rank
  * communicator), started per gradient while backward is still running.  NULL switches it off. */
 int cth_mlp_set_comm(void* mlp, void* comm);
+/* How the gradients cross the ranks; choose before cth_mlp_set_comm.  0 (default): each gradient is
+ * all-reduced in place the moment backward has completed it.  1: gradients are copied into one buffer
+ * registered with the communicator and all-reduced there, one call per layer, under backward.  2: the
+ * same buffer, one all-reduce after backward (nothing shares the SMs with the products; fully exposed).
+ * 3: reduce-scatter per parameter under backward, SGD on the shard this rank owns, all-gather of the
+ * updated weights -- the replicated update of mnist/mnist.cpp:80-92 done once per shard.  Every mode
+ * applies the same sums; they differ in the order NCCL adds the ranks' values. */
+int cth_mlp_set_dp_mode(void* mlp, int mode);
+/* A data-parallel step waits for its end with a deadline (default 30000 ms) and watches the
+ * communicator's health meanwhile; a step that runs out reports an error and the communicator is
+ * aborted (ctk_comm_wait). */
+int cth_mlp_set_comm_timeout_ms(void* mlp, int timeout_ms);
 int cth_mlp_keep_logits(void* mlp, int keep);
 /* Deferred losses (no counterpart: the reference's loop reads loss.item() every step, mnist/mnist.cpp:255).
  * on: the step calls return without waiting for the device and report 0; each step still copies its

@@ -42,9 +42,15 @@ def _shape(a):
     return s, s.ctypes.data_as(_i64p), a.ndim
 
 
-def build(ref_root="/root/reference"):
+def reference_root():
+    """Where the reference checkout is looked for: $CTORCH_REFERENCE_ROOT, else a directory named
+    `reference` beside this repository.  The path need not exist."""
+    return os.environ.get("CTORCH_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def build(ref_root=None):
     """Compile the C restatement (always) and the reference library (if its sources are there)."""
-    subprocess.run(["make", "-s", "-C", HERE, f"REF={ref_root}"], check=True)
+    subprocess.run(["make", "-s", "-C", HERE, f"REF={ref_root or reference_root()}"], check=True)
 
 
 def pack_params(Ws, bs):
@@ -164,6 +170,18 @@ def accuracy(probs, labels):
     return np.float32(correct) / np.float32(len(pred))
 
 
+_ORACLE_LIB = None
+
+
+def _oracle_lib():
+    global _ORACLE_LIB
+    if _ORACLE_LIB is None:
+        if not os.path.exists(ORACLE_SO):
+            build()
+        _ORACLE_LIB = ctypes.CDLL(ORACLE_SO)
+    return _ORACLE_LIB
+
+
 class Oracle:
     """ctypes face of ctorch_oracle.c."""
 
@@ -221,6 +239,22 @@ class Oracle:
         self.L.orc_matmul_rows(_fp(a), _fp(b), _fp(c), rows.ctypes.data_as(_i64p), i64(rows.size), i64(k), i64(n),
                                i64(sa[0]), i64(sa[1]), i64(sb[0]), i64(sb[1]))
         return c
+
+    def matmul_entries(self, a, b, rows, cols, ta=False, tb=False):
+        """(A.B)[rows[e], cols[e]] by the reference's recurrence, for products too large to evaluate in
+        full.  Always the C restatement (the reference library can only compute whole products)."""
+        a, b = _f32(a), _f32(b)
+        rows = np.ascontiguousarray(rows, dtype=np.int64)
+        cols = np.ascontiguousarray(cols, dtype=np.int64)
+        m, k = (a.shape[1], a.shape[0]) if ta else a.shape
+        n = b.shape[0] if tb else b.shape[1]
+        sa = (1, m) if ta else (k, 1)
+        sb = (1, k) if tb else (n, 1)
+        out = np.empty(rows.size, np.float32)
+        i64 = ctypes.c_int64
+        _oracle_lib().orc_matmul_entries(_fp(a), _fp(b), _fp(out), rows.ctypes.data_as(_i64p), cols.ctypes.data_as(_i64p),
+                                         i64(rows.size), i64(k), i64(sa[0]), i64(sa[1]), i64(sb[0]), i64(sb[1]))
+        return out
 
     def sum(self, a):
         a = _f32(a)

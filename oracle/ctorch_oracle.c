@@ -77,15 +77,43 @@ void orc_matmul(const float* a, const float* b, float* c, int64_t m, int64_t k, 
         }
 }
 
+/* Selected rows of the same product.  Every entry is the recurrence of MatMul_BASIC_kernel.cpp:42-54
+ * (sum = 0; for l ascending: sum += a*b, product and sum rounded separately).  Where B's rows are
+ * contiguous the loops are interchanged (l outside, j inside): each entry still sees exactly the
+ * same sequence of operations, only the entries of a row advance together, which lets a full row
+ * of an 8192^3 or 784 x 65536 x 4096 product finish in a fraction of a second. */
 void orc_matmul_rows(const float* a, const float* b, float* c_rows, const int64_t* rows, int64_t n_rows,
                      int64_t k, int64_t n, int64_t sa0, int64_t sa1, int64_t sb0, int64_t sb1) {
     for (int64_t r = 0; r < n_rows; ++r) {
         const int64_t i = rows[r];
+        float* out = c_rows + r * n;
+        if (sb1 == 1) {
+            for (int64_t j = 0; j < n; ++j) out[j] = 0.0f;
+            for (int64_t l = 0; l < k; ++l) {
+                const float av = a[i * sa0 + l * sa1];
+                const float* brow = b + l * sb0;
+                for (int64_t j = 0; j < n; ++j) out[j] += av * brow[j];
+            }
+            continue;
+        }
         for (int64_t j = 0; j < n; ++j) {
             float sum = 0.0f;
             for (int64_t l = 0; l < k; ++l) sum += a[i * sa0 + l * sa1] * b[l * sb0 + j * sb1];
-            c_rows[r * n + j] = sum;
+            out[j] = sum;
         }
+    }
+}
+
+/* Selected entries (rows[e], cols[e]) of the same product, the same recurrence per entry: the
+ * sampled check of products the CPU cannot finish in full (4096^3 and up). */
+void orc_matmul_entries(const float* a, const float* b, float* out, const int64_t* rows, const int64_t* cols,
+                        int64_t count, int64_t k, int64_t sa0, int64_t sa1, int64_t sb0, int64_t sb1) {
+    for (int64_t e = 0; e < count; ++e) {
+        const float* ap = a + rows[e] * sa0;
+        const float* bp = b + cols[e] * sb1;
+        float sum = 0.0f;
+        for (int64_t l = 0; l < k; ++l) sum += ap[l * sa1] * bp[l * sb0];
+        out[e] = sum;
     }
 }
 

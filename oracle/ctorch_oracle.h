@@ -46,6 +46,9 @@ void orc_matmul(const float* a, const float* b, float* c, int64_t m, int64_t k, 
 /* Selected rows of the same product: c_rows[r, :] = row rows[r] of A·B. */
 void orc_matmul_rows(const float* a, const float* b, float* c_rows, const int64_t* rows, int64_t n_rows,
                      int64_t k, int64_t n, int64_t sa0, int64_t sa1, int64_t sb0, int64_t sb1);
+/* Selected entries of the same product: out[e] = (A·B)[rows[e], cols[e]]. */
+void orc_matmul_entries(const float* a, const float* b, float* out, const int64_t* rows, const int64_t* cols,
+                        int64_t count, int64_t k, int64_t sa0, int64_t sa1, int64_t sb0, int64_t sb1);
 float orc_sum(const float* a, int64_t n);
 float orc_dot(const float* a, const float* b, int64_t n);
 float orc_mse(const float* a, const float* b, int64_t n);

@@ -575,6 +575,31 @@ def test_relu_backward_fusion_is_skipped_when_the_activation_has_two_readers(F, 
         assert_exact(c, a, "two readers: nothing changes")
 
 
+def test_leaf_gradient_hook_fires_once_after_the_last_contribution(F):
+    """AutoDiff::on_leaf_grad -- where a data-parallel driver starts a gradient's all-reduce -- is called
+    once per leaf and pass, also for a leaf that enters several nodes (a shared weight): its gradient is
+    complete only after the last of its contributions."""
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((32, 16)).astype(np.float32)
+    w = rng.standard_normal((16, 16)).astype(np.float32) / 4
+    v = rng.standard_normal((16, 8)).astype(np.float32) / 4
+    with F.AutoDiff() as ctx:
+        ctx.count_leaf_grads(True)
+        X, W, V = dev(F, x), dev(F, w).requires_grad(), dev(F, v).requires_grad()
+        h = X.matmul(W).relu().matmul(W)      # W enters two products
+        L = h.matmul(V).sum()
+        F.backward(L)
+        assert ctx.leaf_grad_count(W) == 1, "a leaf with two consumers: one call, after the second contribution"
+        assert ctx.leaf_grad_count(V) == 1
+        assert ctx.leaf_grad_count(X) == 0, "no gradient was asked for"
+        # and the gradient the hook saw complete is the sum of both contributions
+        a1 = np.maximum(x.astype(np.float64) @ w, 0)
+        g_h = np.ones((32, 8)) @ v.astype(np.float64).T
+        want = a1.T @ g_h + x.astype(np.float64).T @ ((g_h @ w.astype(np.float64).T) * (a1 > 0))
+        assert_matmul_close(F.grad(W).numpy(), want, 1e-4, "gradient of the shared weight")
+        ctx.count_leaf_grads(False)
+
+
 @pytest.mark.parametrize("rows,cols", [(8192, 4096), (130, 132), (257, 10), (1, 5), (3000, 1)])
 def test_column_sum_kernel(cb, rows, cols):
     rng = np.random.default_rng(rows + cols)

@@ -291,30 +291,6 @@ def test_sgd_update_with_split_equals_update_then_split(cb, outer, inner):
         cb.ops.sgd_update_split(cb.to_device(p0[:, :inner - 1].copy()), dg, 0.1)   # rows not 16-byte aligned
 
 
-@pytest.mark.parametrize("mode", ["tf32", "3xtf32"])
-@pytest.mark.parametrize("m,k,n,ta,tb", [
-    (256, 64, 256, False, False),          # one unit: 73 pairs draw nothing
-    (384, 520, 600, False, False),         # 4 tiles, all in K-halves: 8 units
-    (2560, 552, 2304, False, True),        # 90 tiles on 74 pairs
-    (8192, 256, 4096, True, False),        # 512 tiles: seven units per pair, the ring of published units wraps
-])
-def test_dynamic_unit_order_equals_fixed_order(cb, mode, m, k, n, ta, tb):
-    """The pair kernel with units drawn from a counter against the fixed assignment: the same bits
-    (which pair computes a tile does not enter the result), call after call -- every launch has to
-    leave its counters at zero for the next one."""
-    A, B, _ = _mats(m, k, n, 31)
-    dA, dB = cb.to_device(A.T.copy() if ta else A), cb.to_device(B.T.copy() if tb else B)
-    try:
-        cb.ops.set_matmul_dynamic_order(0)
-        fixed = cb.ops.matmul(dA, dB, ta, tb, mode).numpy()
-        cb.ops.set_matmul_dynamic_order(1)
-        for i in range(4):
-            assert_exact(cb.ops.matmul(dA, dB, ta, tb, mode).numpy(), fixed, f"dynamic order, call {i}")
-    finally:
-        cb.ops.set_matmul_dynamic_order(0)
-    _check_status(cb)
-
-
 @pytest.mark.parametrize("m,k,n", [(8192, 10, 4096), (2048, 16, 512), (4099, 1, 256), (1030, 7, 1020)])
 def test_short_contraction_kernel_is_the_reference_recurrence(cb, orc, m, k, n):
     """K <= 16 with a large output (dX of the 10-class layer): the CUDA-core kernel, whose products and

@@ -43,6 +43,15 @@ def test_argument_validation_needs_no_device():
     assert L.ctk_matmul_workspace_bytes(i64(8), i64(8), i64(8), 0) >= 2 * 128 * 4
 
 
+def test_buffer_caches_are_keyed_by_device():
+    """The caches that recycle device buffers never hand a buffer parked on one GPU to a request made
+    with another GPU current (a fake allocator and a fake current device: no GPU is touched)."""
+    import ctorch_b200 as cb
+    failed = ctypes.c_int(-1)
+    assert cb.lib.cth_selftest_cache_keying(ctypes.byref(failed)) == 0, cb.lib.cth_last_error()
+    assert failed.value == 0
+
+
 def test_oracle_is_not_reachable_from_the_product():
     """No file of the product package mentions the oracle."""
     import ctorch_b200 as cb

@@ -51,10 +51,43 @@ def test_same_result_as_the_allocating_entry_point_twice_in_a_row(cb, orc):
     assert cb.ops.matmul_status() == 0
 
 
+def _free_bytes(cb):
+    sms, total, free = ctypes.c_int(), ctypes.c_size_t(), ctypes.c_size_t()
+    cb.check(cb.lib.ctk_device_info(ctypes.byref(sms), ctypes.byref(total), ctypes.byref(free)))
+    return free.value
+
+
+def test_largest_admissible_shape_and_nothing_is_allocated(cb, orc):
+    """1024 x 1024 by 1024 x 1024 fills the fixed array to the last byte.  The first call may set
+    kernel attributes; across the second and third the device's free memory must not move (the
+    library neither grows a workspace nor takes anything from the driver on this path)."""
+    rng = np.random.default_rng(7)
+    A = rng.standard_normal((1024, 1024)).astype(np.float32)
+    B = rng.standard_normal((1024, 1024)).astype(np.float32)
+    dA, dB = cb.to_device(A), cb.to_device(B)
+    C = cb.empty((1024, 1024))
+    want = cb.ops.matmul(dA, dB, mode="3xtf32").numpy()
+    args = (dA.p, dB.p, C.p, i64(1024), i64(1024), i64(1024), i64(1024), i64(1), i64(1024), i64(1), None)
+    cb.check(cb.lib.ctk_matmul_3xtf32_noalloc_f32(*args))
+    cb.synchronize()
+    free0 = _free_bytes(cb)
+    for _ in range(2):
+        C.fill_bytes(0)
+        cb.check(cb.lib.ctk_matmul_3xtf32_noalloc_f32(*args))
+        cb.synchronize()
+        assert _free_bytes(cb) == free0, "the call changed the device's free memory"
+        got = C.numpy()
+        assert np.array_equal(got, want)
+    assert_matmul_close(got, orc.matmul(A, B), 1e-4, "1024^3 through the fixed scratch vs the oracle")
+    assert cb.ops.matmul_status() == 0
+
+
 def test_operands_beyond_the_fixed_scratch_are_refused(cb):
     m = n = k = 2048  # 2*(m*k + k*n)*4 bytes = 64 MiB of split scratch
     assert cb.lib.ctk_matmul_workspace_bytes(m, n, k, 0) > LIMIT_BYTES
-    a, b, c = cb.empty((8,)), cb.empty((8,)), cb.empty((8,))  # never touched: the call must stop at the size check
+    # real-size operands: should the size check ever move behind a launch, the call computes a product
+    # (and this test fails on the return code) instead of reading past small buffers
+    a, b, c = cb.empty((m, k)), cb.empty((k, n)), cb.empty((m, n))
     before = cb.launch_count()
     rc = cb.lib.ctk_matmul_3xtf32_noalloc_f32(a.p, b.p, c.p, i64(m), i64(n), i64(k), i64(k), i64(1), i64(n), i64(1), None)
     assert rc == 5, "CTK_ERR_LIMIT expected"
