@@ -13,9 +13,17 @@ with NCCL while backward runs.  Prints ONE JSON line (rank 0).
           the batch (from page-locked memory) and the device-to-host read of the loss are inside
           the timed region
   roofline  the dominant kernel (the tcgen05 MatMul): algorithmic flops (2*M*N*K per product) over
-          its launch durations, timed with CUDA events on the launching stream during the timed steps
+          its launch durations, timed with CUDA events on the launching stream during the timed steps;
+          `peak` is the nominal dense TF32 rate / 3 (three TF32 products per fp32 product), and
+          `ceilings` lists the measured alternatives (a TF32 GEMM of the vendor library timed in this
+          run as a comparator, the driver-measured bf16 figures) with the fraction against each
   cpu_baseline  the reference's own CPU path (single-threaded by construction) on a bounded sample
           of the same workload, N=1 only
+  parity_check  (N=1) after timing: logits of sampled rows of the full-size step against the oracle
+  dp_check  (N>1) before timing: one reduced-width step against the N-replica oracle; after timing:
+          the largest difference between any two ranks' weights (must be 0)
+  extras  (N=1) the single-op metrics of the other benchmark configurations, each with achieved rate,
+          roofline fraction and the reference's CPU rate on a bounded sample
 
 `--impl reference` times that CPU path alone (rank 0; other ranks exit).
 Other workloads (single GPU): elementwise, rowwise, matmul -- the single-op sweeps of the other
@@ -44,6 +52,13 @@ BATCH = 8192
 LR = 0.01
 WORKLOAD = "dp-mlp-784-4096-4096-4096-10_batch8192-per-gpu_fp32_sgd"
 CPU_SAMPLE_BATCH = 4  # rows per reference step: the reference's cost is linear in rows (~0.2 GFLOP/s)
+DEFAULT_DP_MODE, DEFAULT_MAX_CTAS = "inplace", 0
+NOMINAL_TF32 = 1125.0  # TFLOP/s, dense, the part's data sheet
+NOMINAL_HBM = 7700.0   # GB/s
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant shape from one ncu capture
+# (not re-measured by a benchmark run; the summary and its command are the named file)
+QUOTED_TRAFFIC = dict(bytes=1.503e9 + 0.362e9, launch="forward 8192x4096x4096 + bias + ReLU + split (algorithmic: 402 MB of operand splits read, 402 MB written)",
+                      **{"from": "profiles/tcgen05_matmul_pair_3xtf32_fused_epilogues_8192x4096x4096.md"})
 
 
 def measured_peaks():
@@ -70,6 +85,48 @@ def make_batch(rank, rows=BATCH, seed=1234):
     x = rng.integers(0, 256, (rows, DIMS[0])).astype(np.float32) / np.float32(255.0)
     labels = rng.integers(0, DIMS[-1], rows).astype(np.float32)
     return x, labels
+
+
+def measure_library_tf32(device_index):
+    """A TF32 GEMM of the vendor library (torch.matmul with TF32 allowed, 8192^3) timed with CUDA events:
+    best of 10 (burst) and back to back for ~1.5 s (sustained).  A comparator for the roofline only --
+    nothing in the product path uses it.  Returns None where torch or its CUDA build is unavailable."""
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            return None
+        dev = torch.device("cuda", device_index)
+        torch.backends.cuda.matmul.allow_tf32 = True
+        n = 8192
+        a = torch.randn(n, n, device=dev)
+        b = torch.randn(n, n, device=dev)
+        c = torch.empty(n, n, device=dev)
+        for _ in range(3):
+            torch.matmul(a, b, out=c)
+        torch.cuda.synchronize(dev)
+        fl = 2.0 * n ** 3
+        best = 1e9
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch.matmul(a, b, out=c)
+            e1.record()
+            e1.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        reps = max(10, int(1500.0 / best))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            torch.matmul(a, b, out=c)
+        e1.record()
+        e1.synchronize()
+        sustained = e0.elapsed_time(e1) / reps
+        del a, b, c
+        torch.cuda.empty_cache()
+        return dict(burst_tflops=fl / (best * 1e-3) / 1e12, sustained_tflops=fl / (sustained * 1e-3) / 1e12,
+                    how=f"torch.matmul fp32 with TF32 allowed, {n}^3, CUDA events: best of 10 and {reps} back to back")
+    except Exception as e:  # a comparator only: its absence must not fail the benchmark
+        return dict(error=repr(e)[:200])
 
 
 class ClockSampler:
@@ -200,6 +257,99 @@ def host_cpu():
 
 
 # ------------------------------------------------------------------------------------------------
+# checks that ride along with the timed run (the oracle is the checker here, never the thing timed)
+# ------------------------------------------------------------------------------------------------
+def _quiet_oracle(fn):
+    """Runs fn with stdout pointed at stderr: the reference library prints a banner and log lines."""
+    sys.stdout.flush()
+    saved = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        return fn()
+    finally:
+        sys.stdout.flush()
+        os.dup2(saved, 1)
+        os.close(saved)
+
+
+def parity_check_full_size(F, params, x, labels, rows=(0, 1, 4095, 4096, 8191, 777, 5000, 6001)):
+    """One full-size step of a freshly initialised network with the logits kept; the logits of a few rows
+    against the oracle's forward pass on those rows with the same weights (forward is row-independent).
+    (The timed trainer is not used: at the specified learning rate on a summed loss its weights have
+    long left the range where a comparison says anything -- the reference diverges the same way.)"""
+    import oracle
+    rows = np.asarray(rows)
+    tr = F.MlpTrainer(DIMS, params, LR)
+    tr.keep_logits(True)
+    loss = tr.step_host(x, labels)
+    got = tr.logits(x.shape[0])[rows]
+    del tr
+    ref = _quiet_oracle(lambda: oracle.Oracle().mlp_train(DIMS, x[rows][None, None], labels[rows][None, None], params, LR, 1))
+    err = float(np.abs(got - ref["logits"][0]).max() / max(np.abs(ref["logits"][0]).max(), 1e-30))
+    return dict(what="logits of 8 sampled rows of one full-size step (fresh weights) vs the oracle's forward pass on those rows", rows=[int(r) for r in rows],
+                normwise_err=err, tolerance=1e-4, ok=bool(err <= 1e-4), loss=float(loss))
+
+
+DP_CHECK_DIMS, DP_CHECK_BATCH = [784, 128, 64, 10], 64
+
+
+def dp_check_before(cb, F, cp, comm, dp_mode):
+    """One step of a reduced-width network through the same communicator and exchange mode, against the
+    oracle run as `world` replicas with summed gradients (rank 0 evaluates the oracle on every shard)."""
+    import oracle
+    from ctorch_b200.dp import shard_seed
+    dims, batch = DP_CHECK_DIMS, DP_CHECK_BATCH
+    rw = np.random.default_rng(4242)
+    parts = []
+    for i, j in zip(dims[:-1], dims[1:]):
+        lim = np.sqrt(6.0 / i)
+        parts += [rw.uniform(-lim, lim, (i, j)).astype(np.float32).ravel(), np.zeros(j, np.float32)]
+    p0 = np.concatenate(parts)
+
+    def shard(r):
+        rng = np.random.default_rng(shard_seed(99, r))
+        return (rng.integers(0, 256, (batch, dims[0])).astype(np.float32) / np.float32(255.0), rng.integers(0, dims[-1], batch).astype(np.float32))
+
+    x, lab = shard(cp.rank)
+    tr = F.MlpTrainer(dims, p0, 0.001)
+    tr.set_dp_mode(dp_mode)
+    tr.set_comm(comm)
+    tr.step_host(x, lab)
+    grads, params = tr.grads(), tr.params()
+    tr.set_comm(None)
+    del tr
+    cb.synchronize()
+    out = None
+    if cp.rank == 0:
+        xs = np.stack([shard(r)[0] for r in range(cp.world)])[:, None]
+        ls = np.stack([shard(r)[1] for r in range(cp.world)])[:, None]
+        ref = _quiet_oracle(lambda: oracle.Oracle().mlp_train(dims, xs, ls, p0, 0.001, 1, grad_steps=(0,), want_logits=False))
+        pe = float(np.abs(params - ref["params"]).max() / np.abs(ref["params"]).max())
+        out = dict(what=f"one step of {'-'.join(map(str, dims))} at batch {batch} per rank vs the oracle run as {cp.world} replicas with summed gradients",
+                   param_normwise_err=pe, tolerance=1e-4, ok=bool(pe <= 1e-4))
+        if dp_mode != "sharded":   # (sharded: a rank holds the summed gradient of its own shards only)
+            ge = float(np.abs(grads - ref["grads"][0]).max() / np.abs(ref["grads"][0]).max())
+            out.update(grad_normwise_err=ge, ok=bool(pe <= 1e-4 and ge <= 1e-4))
+    cp.barrier()
+    return out
+
+
+def weights_spread(cp, params):
+    """Largest difference between any two ranks' weights after the timed steps: 0 when every rank holds
+    the same bits (compared through a hash; the element-wise difference is only formed if they differ)."""
+    bits = params.view(np.uint32)
+    h = float(int(np.bitwise_xor.reduce(bits)) % (1 << 24)) + float(int(bits[::4097].astype(np.uint64).sum()) % (1 << 24)) * 2.0 ** -24
+    same = cp.max_over_ranks(h) == -cp.max_over_ranks(-h)
+    if same:
+        return 0.0
+    import torch
+    hi = torch.from_numpy(params.copy()); lo = torch.from_numpy(params.copy())
+    cp.dist.all_reduce(hi, op=cp.dist.ReduceOp.MAX)
+    cp.dist.all_reduce(lo, op=cp.dist.ReduceOp.MIN)
+    return float((hi - lo).abs().max())
+
+
+# ------------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------------
 def run_mlp(args, cp):
@@ -217,9 +367,12 @@ def run_mlp(args, cp):
         sampler.start()
 
     comm = None
+    dp_before = None
     if world > 1:
         from ctorch_b200 import dp
-        comm = dp.make_comm(cb, cp)
+        comm = dp.make_comm(cb, cp, max_ctas=args.max_ctas, nvls_ctas=args.nvls_ctas)
+        if not args.no_checks:
+            dp_before = dp_check_before(cb, F, cp, comm, args.dp_mode)
 
     params = make_params()
     x, labels = make_batch(rank)
@@ -227,6 +380,7 @@ def run_mlp(args, cp):
     onehot[np.arange(BATCH), labels.astype(int)] = 1
     trainer = F.MlpTrainer(DIMS, params, LR)
     if comm is not None:
+        trainer.set_dp_mode(args.dp_mode)
         trainer.set_comm(comm)
     X, Y = F.Tensor.from_numpy(x), F.Tensor.from_numpy(onehot)
     px, pl = PinnedArray(x.shape), PinnedArray(labels.shape)
@@ -285,6 +439,31 @@ def run_mlp(args, cp):
     ms_e2e, _, loss_e2e, _ = timed(pipelined_step, False)
     status = cb.ops.matmul_status()
 
+    # The specified learning rate (0.01 on a loss SUMMED over 8192 rows) drives the weights away within a
+    # few steps -- in the reference too -- so the timed steps above run on saturated activations.  The same
+    # step with the rate scaled to the mean loss keeps every operand well conditioned; it is timed beside
+    # the headline so that a reader can see whether the operands' values (through power and clocks) matter.
+    stable = None
+    if world == 1 and not args.no_checks:
+        t2 = F.MlpTrainer(DIMS, params, LR / BATCH)
+        ms_st, _, loss_st, _ = timed(lambda: t2.step_device(X, Y), False)
+        stable = dict(lr=LR / BATCH, ms_per_step=ms_st / args.steps, value=BATCH / (ms_st / args.steps * 1e-3), loss_last=float(loss_st),
+                      what="the same step on device-resident inputs with lr / batch (no divergence)")
+        del t2
+
+    parity = dp_after = None
+    if not args.no_checks:
+        if world == 1:
+            parity = parity_check_full_size(F, params, x, labels)
+        else:
+            spread = weights_spread(cp, trainer.params())
+            dp_after = dict(what=f"largest difference between any two ranks' weights after {3 * (args.warmup + args.steps)} steps", max_abs_diff=spread, ok=bool(spread == 0.0))
+    lib_tf32 = measure_library_tf32(local_rank) if rank == 0 and not args.no_comparator else None
+    extras = None
+    if rank == 0 and world == 1 and not args.no_extras:
+        del X, Y
+        extras = run_extras(cb, peaks, lib_tf32, with_cpu=not args.no_cpu_baseline)
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         kind, t_step, total, b = cpu_reference_step_time(2, 0)
@@ -297,19 +476,29 @@ def run_mlp(args, cp):
         e2e_v = BATCH * world / (ms_e2e / args.steps * 1e-3)
         n, tms, fl = prof
         achieved = fl / (tms * 1e-3) / 1e12 if tms > 0 else 0.0
-        # Ceiling: the burst figure while the SM clock stayed at its maximum over the timed region (a short
-        # run that never reaches the power cap), else the sustained one.
+        # Ceilings.  `peak` is the nominal dense TF32 rate of the part (1125 TFLOP/s) / 3: three TF32 products
+        # are issued per fp32 product, and nothing can exceed it.  Beside it: a TF32 GEMM of the vendor
+        # library timed in this run, and the driver-measured bf16 GEMM halved (TF32 issues at half the bf16
+        # rate) -- library kernels that a hand-written kernel can pass, so a fraction above 1 against them
+        # is possible and says how far the library itself is from the hardware.
         at_max = clocks and clocks.get("sm_mhz") and clocks.get("sm_max_mhz") and clocks["sm_mhz"] >= 0.95 * clocks["sm_max_mhz"]
         bf16_key, bf16_val = ("bf16_tflops (burst)", peaks["bf16"]) if at_max else ("bf16_tflops_sustained", peaks["bf16_sustained"])
-        tf32_peak = bf16_val / 2.0
-        peak = tf32_peak / 3.0
+        peak = NOMINAL_TF32 / 3.0
+        ceilings = {"nominal_tf32_over_3": dict(peak=peak, frac=achieved / peak),
+                    "measured_bf16_over_6": dict(peak=bf16_val / 6.0, frac=achieved / (bf16_val / 6.0), source=f"{peaks['source']}: {bf16_key} {bf16_val}")}
+        if lib_tf32 and "burst_tflops" in lib_tf32:
+            lib_peak = (lib_tf32["burst_tflops"] if at_max else lib_tf32["sustained_tflops"]) / 3.0
+            ceilings["library_tf32_gemm_over_3"] = dict(peak=lib_peak, frac=achieved / lib_peak, measured=lib_tf32)
+        elif lib_tf32:
+            ceilings["library_tf32_gemm_over_3"] = lib_tf32
         flops_step = sum(2.0 * BATCH * i * j for i, j in zip(DIMS[:-1], DIMS[1:])) * 2 + sum(2.0 * BATCH * i * j for i, j in zip(DIMS[1:-1], DIMS[2:]))
         out = dict(
             metric="mlp_train_samples_per_s", value=value, unit="samples/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
             ms_per_step=per_step, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",
             config=dict(workload=WORKLOAD, global_batch=BATCH * world, parallelism=f"dp{world}", matmul_mode="3xtf32",
+                        gradient_exchange=(args.dp_mode if world > 1 else None), nccl_max_ctas=args.max_ctas or None,
                         l2="per-step working set (weights 147 MB + activations 3x134 MB per layer pass) exceeds the 126 MB L2",
-                        loss_first=float(loss_dev) if loss_dev is not None else None, matmul_status=status),
+                        loss_last=float(loss_dev) if loss_dev is not None else None, matmul_status=status, stable_lr_run=stable),
             clocks=clocks,
             e2e=dict(value=e2e_v, unit="samples/s", ms_per_step=ms_e2e / args.steps,
                      h2d_bytes_per_step=int(x.nbytes + labels.nbytes), d2h_bytes_per_step=4,
@@ -317,17 +506,14 @@ def run_mlp(args, cp):
                      serial_value=BATCH * world / (ms_e2e_serial / args.steps * 1e-3), serial_ms_per_step=ms_e2e_serial / args.steps,
                      serial_call="cth_mlp_step_host: upload, step and loss read-back in sequence"),
             gpu_launches=int(launches),
-            roofline=dict(bound="tensor", achieved=achieved, peak=peak, unit="TFLOP/s", frac=achieved / peak if peak else None,
-                          # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant shape (8192 x 4096 x 4096, forward with
-                          # its fused epilogue), from one ncu capture of that launch (--workload kernel --case matmul_3xtf32_8192x4096x4096_fwdfused)
-                          traffic=1.503e9 + 0.362e9, traffic_launch="forward 8192x4096x4096 + bias + ReLU + split (algorithmic: 402 MB of operand splits read, 402 MB written)",
+            roofline=dict(bound="tensor", achieved=achieved, peak=peak, unit="TFLOP/s", frac=achieved / peak,
+                          peak_source="nominal dense TF32 rate 1125 TFLOP/s / 3 (three TF32 products per fp32 product); algorithmic flops 2*M*N*K; measured alternatives under `ceilings`",
+                          ceilings=ceilings,
+                          # not measured in this run: one ncu capture of one launch of the dominant shape, kept under profiles/
+                          traffic=QUOTED_TRAFFIC["bytes"], traffic_quoted_from=QUOTED_TRAFFIC["from"], traffic_launch=QUOTED_TRAFFIC["launch"],
                           kernel="tcgen05_matmul_pair_kernel / tcgen05_matmul_kernel (3xTF32)", launches=int(n), avg_launch_ms=tms / n if n else None,
-                          peak_source=f"{peaks['source']}: {bf16_key} {bf16_val} / 2 (TF32 runs at half the bf16 rate; no TF32 figure was measured) / 3 (three TF32 products per fp32 product); algorithmic flops 2*M*N*K",
-                          step_model_flops=flops_step, step_tflops=flops_step / (per_step * 1e-3) / 1e12,
-                          # context for a fraction above 1: the measured ceiling is cuBLAS bf16 (73 % of the nominal 2250) scaled
-                          # to TF32; against the nominal dense TF32 rate (1125 TFLOP/s, a third of it per fp32 product):
-                          nominal_peak=375.0, frac_of_nominal=achieved / 375.0,
-                          tensor_pipe_active="97.0 % of active and 91.5 % of elapsed SM cycles (ncu capture of --workload kernel --case matmul_3xtf32_8192x4096x4096_fwdfused)"),
+                          step_model_flops=flops_step, step_tflops=flops_step / (per_step * 1e-3) / 1e12, step_frac=flops_step / (per_step * 1e-3) / 1e12 / peak),
+            parity_check=parity, dp_check=dict(before=dp_before, after=dp_after) if world > 1 else None, extras=extras,
             cpu_baseline=cpu,
         )
         print(json.dumps(out))
@@ -336,6 +522,147 @@ def run_mlp(args, cp):
         del trainer
         cb.synchronize()
         cb.lib.ctk_comm_destroy(comm)
+
+
+def run_extras(cb, peaks, lib_tf32, with_cpu=True):
+    """The single-op metrics of the other benchmark configurations, bounded to a few tens of seconds:
+    elementwise Add / Mul-backward / Tanh at 2^28, softmax and cross entropy at C in {10, 1000, 32000},
+    Sum at 2^28, and the three products at 8192^3 and 65536 x 784 x 4096 in both tensor-core modes.
+    Every entry: achieved rate, fraction of the measured (HBM) or nominal (tensor) ceiling, and the
+    reference's own CPU rate on a bounded sample of the same operation (one thread: it has no others).
+    Operands are larger than the 126 MB L2 (C = 10 runs on 4 Mi rows for that reason)."""
+    import oracle
+    ref = None
+    if with_cpu:
+        ref = _quiet_oracle(lambda: oracle.Reference() if oracle.Reference.available() else oracle.Oracle())
+    hbm = peaks["hbm_gbs"]
+    i64 = ctypes.c_int64
+    out = []
+
+    def gpu_ms(fn, iters, warm=3):
+        for _ in range(warm):
+            fn()
+        e0, e1 = cb.Event(), cb.Event()
+        cb.synchronize()
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        e1.sync()
+        return e0.elapsed_ms(e1) / iters
+
+    def cpu_rate(fn, work, unit, sample, warm=True):
+        if ref is None:
+            return None
+        def run():
+            if warm:
+                fn()   # once untimed: page faults, the library's first-call set-up
+            t0 = time.perf_counter()
+            fn()
+            return time.perf_counter() - t0
+        dt = _quiet_oracle(run)
+        return dict(value=work / dt / (1e9 if unit == "GB/s" else 1e12), unit=unit, cores=1, kind=ref.kind, sample=sample)
+
+    def add(name, ms, work, unit, cpu, **extra):
+        ach = work / (ms * 1e-3) / (1e9 if unit == "GB/s" else 1e12)
+        d = dict(name=name, value=ach, unit=unit, ms=ms)
+        if unit == "GB/s":
+            d.update(bound="hbm", peak=hbm, frac=ach / hbm, frac_of_nominal=ach / NOMINAL_HBM, peak_source=peaks["source"] + " hbm_gbs")
+        d.update(extra)
+        d["cpu_baseline"] = cpu
+        out.append(d)
+
+    rng = np.random.default_rng(0)
+    # ---- elementwise, 2^28 (1 GiB per array; inputs U(-4, 4), second operand U(0.5, 4), generated on the device)
+    n = 1 << 28
+    a = cb.ops.rand_uniform((n,), seed=1); cb.ops.scalar(0, a, 8.0, out=a); cb.ops.scalar(1, a, -4.0, out=a)
+    b = cb.ops.rand_uniform((n,), seed=2); cb.ops.scalar(0, b, 3.5, out=b); cb.ops.scalar(1, b, 0.5, out=b)
+    g = cb.ops.rand_uniform((n,), seed=3)
+    o, o2 = cb.empty((n,)), cb.empty((n,))
+    ns = 1 << 22
+    ha, hb, hg = (v.view(0, (ns,)).numpy() for v in (a, b, g))
+    add("Add_fwd_2^28", gpu_ms(lambda: cb.ops.binary("Add", a, b, out=o), 10), 12 * n, "GB/s",
+        cpu_rate(lambda: ref.binary("Add", ha, hb), 12 * ns, "GB/s", "the same op on 2^22 elements"))
+    add("Mul_bwd_2^28", gpu_ms(lambda: lib_binary_bwd(cb, "Mul", a, b, g, o, o2), 10), 20 * n, "GB/s",
+        cpu_rate(lambda: ref.grad_binary("Mul", ha, hb, hg), 20 * ns, "GB/s", "the Mul rule of AutoDiff::backward on 2^22 elements"))
+    add("Tanh_fwd_2^28", gpu_ms(lambda: cb.ops.unary("Tanh", a, out=o), 10), 8 * n, "GB/s",
+        cpu_rate(lambda: ref.unary("Tanh", ha), 8 * ns, "GB/s", "the same op on 2^22 elements"))
+    s24 = a.view(0, (1 << 24,)).numpy()
+    add("Sum_2^28", gpu_ms(lambda: cb.ops.sum(a), 10), 4 * n, "GB/s",
+        cpu_rate(lambda: ref.sum(s24), 4 * (1 << 24), "GB/s", "Tensor::sum on 2^24 elements"))
+    del a, b, g, o, o2
+    # ---- row-wise
+    for C in (10, 1000, 32000):
+        rows = (1 << 22) if C == 10 else 65536
+        block = (2 * rng.standard_normal((64, C))).astype(np.float32)          # logits N(0, 2^2)
+        x = cb.ops.tile(cb.to_device(block), rows * C).reshape(rows, C)
+        y = cb.empty((rows, C))
+        labels = rng.integers(0, C, rows).astype(np.float32)
+        lab = cb.to_device(labels)
+        rs = max(32, (1 << 20) // C)
+        hx = np.tile(block, (rs // 64 + 1, 1))[:rs]
+        it = 10 if C < 32000 else 3
+        add(f"softmax_fwd_{rows}x{C}", gpu_ms(lambda: cb.ops.softmax(x, out=y), it), 8 * rows * C, "GB/s",
+            cpu_rate(lambda: ref.softmax(hx), 8 * rs * C, "GB/s", f"Tensor::softmax on [{rs}, {C}]"))
+        add(f"ce_index_fwd_{rows}x{C}", gpu_ms(lambda: cb.ops.cross_entropy(x, lab), it), 4 * rows * C + 4 * rows, "GB/s",
+            cpu_rate(lambda: ref.ce(hx, labels[:rs]), 4 * rs * C + 4 * rs, "GB/s", f"CrossEntropy_BASIC_kernel (index labels) on [{rs}, {C}]"))
+        add(f"ce_fused_fwd_bwd_{rows}x{C}", gpu_ms(lambda: lib_ce_fused(cb, x, lab, y, rows, C), it), 8 * rows * C + 4 * rows, "GB/s", None,
+            note="forward + gradient in one pass; the reference runs them as separate passes (its backward needs one-hot labels)")
+        del x, y, lab
+        _scratch.clear()
+    # ---- products (operands N(0, 1): one 2^24 block tiled on the device)
+    blk = cb.to_device(rng.standard_normal(1 << 24).astype(np.float32))
+    hblk = blk.numpy()
+
+    def mat(rows_, cols_, shift):
+        return cb.ops.tile(blk.view(shift, ((1 << 24) - shift,)), rows_ * cols_).reshape(rows_, cols_)
+
+    def host_rows(shift, nrows, cols_):        # the first rows of mat(., cols_, shift) as a host array
+        return np.resize(hblk[shift:], nrows * cols_).reshape(nrows, cols_)
+
+    def host_cols(shift, nrows, cols_, r):     # the first r columns of mat(nrows, cols_, shift)
+        idx = (np.arange(nrows, dtype=np.int64)[:, None] * cols_ + np.arange(r)[None, :]) % ((1 << 24) - shift) + shift
+        return np.ascontiguousarray(hblk[idx])
+
+    lib_tf32_peak = lib_tf32.get("burst_tflops") if lib_tf32 else None
+    for (m, k, nn) in ((8192, 8192, 8192), (65536, 784, 4096)):
+        A, B, dC = mat(m, k, 0), mat(k, nn, 1237), mat(m, nn, 40961)
+        Cc, dA, dB = cb.empty((m, nn)), cb.empty((m, k)), cb.empty((k, nn))
+        fl = 2.0 * m * nn * k
+        r = 4
+        cpus = {}
+        if ref is not None:
+            hB = host_rows(1237, k, nn)
+            a_rows, dc_rows = host_rows(0, r, k), host_rows(40961, r, nn)
+            cpus["fwd"] = cpu_rate(lambda: ref.matmul(a_rows, hB), 2.0 * r * k * nn, "TFLOP/s", f"{r} rows of C (MatMul_BASIC_kernel, cost linear in rows)", warm=False)
+            cpus["dA"] = cpu_rate(lambda: ref.matmul(dc_rows, hB, False, True), 2.0 * r * k * nn, "TFLOP/s", f"{r} rows of dA = dC.B^T", warm=False)
+            # rows of dB = A^T.dC: columns of A against all of dC
+            rb = r if m == 8192 else 1
+            a_cols, hdC = host_cols(0, m, k, rb), host_rows(40961, m, nn)
+            cpus["dB"] = cpu_rate(lambda: ref.matmul(a_cols, hdC, True, False), 2.0 * rb * m * nn, "TFLOP/s", f"{rb} row(s) of dB = A^T.dC", warm=False)
+            del a_cols, hdC, hB
+        for mode, nominal in (("3xtf32", NOMINAL_TF32 / 3.0), ("tf32", NOMINAL_TF32)):
+            for which, fn in (("fwd", lambda: cb.ops.matmul(A, B, mode=mode, out=Cc)),
+                              ("dA", lambda: cb.ops.matmul(dC, B, tb=True, mode=mode, out=dA)),
+                              ("dB", lambda: cb.ops.matmul(A, dC, ta=True, mode=mode, out=dB))):
+                ms = gpu_ms(fn, 5)
+                # the tensor-core kernel alone (without the operand-split passes of a 3xTF32 call), by the library's own events
+                cb.check(cb.lib.ctk_matmul_profile_enable(1))
+                fn(); fn()
+                cnt, tms, tfl = ctypes.c_int64(), ctypes.c_double(), ctypes.c_double()
+                cb.check(cb.lib.ctk_matmul_profile_read(ctypes.byref(cnt), ctypes.byref(tms), ctypes.byref(tfl)))
+                cb.check(cb.lib.ctk_matmul_profile_enable(0))
+                kern = tfl.value / (tms.value * 1e-3) / 1e12 if tms.value > 0 else None
+                ach = fl / (ms * 1e-3) / 1e12
+                d = dict(bound="tensor", peak=nominal, frac=ach / nominal, peak_source="nominal dense TF32 1125 TFLOP/s" + (" / 3" if mode == "3xtf32" else ""),
+                         kernel_alone_tflops=kern, kernel_alone_frac=(kern / nominal if kern else None),
+                         call="ctk_matmul_f32, operands split inside the call (3xTF32)" if mode == "3xtf32" else "ctk_matmul_f32, operands read in place")
+                if lib_tf32_peak:
+                    d["frac_of_library_tf32_gemm"] = ach / (lib_tf32_peak / (3.0 if mode == "3xtf32" else 1.0))
+                add(f"matmul_{which}_{mode}_{m}x{k}x{nn}", ms, fl, "TFLOP/s", cpus.get(which), **d)
+        del A, B, dC, Cc, dA, dB
+    out.append(dict(name="matmul_status", value=cb.ops.matmul_status()))
+    return out
 
 
 def run_single_op(args):
@@ -678,6 +1005,12 @@ def main():
     ap.add_argument("--workload", default="mlp", choices=["mlp", "mlp_small", "mnist", "elementwise", "rowwise", "matmul", "kernel"])
     ap.add_argument("--case", default="matmul_3xtf32_4096x4096x4096", help="for --workload kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the single-op metrics that ride along with the default N=1 run")
+    ap.add_argument("--no-checks", action="store_true", help="skip parity_check / dp_check")
+    ap.add_argument("--no-comparator", action="store_true", help="skip the vendor-library TF32 GEMM timed for the roofline's `ceilings`")
+    ap.add_argument("--dp-mode", default=DEFAULT_DP_MODE, choices=["inplace", "arena", "serial", "sharded"], help="how gradients cross the ranks (N > 1)")
+    ap.add_argument("--max-ctas", type=int, default=DEFAULT_MAX_CTAS, help="upper bound on the CTAs of one collective (0: NCCL's choice)")
+    ap.add_argument("--nvls-ctas", type=int, default=0, help="CTAs of a collective's in-switch part (0: NCCL's choice)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours" and args.workload == "mlp":
         args.warmup = 3  # timing rule: at least three warm-up steps

@@ -19,7 +19,11 @@
 //   major-ness goes into the instruction descriptor and the shared-memory descriptors, no
 //   transposed copy is made.  M/N/K tails are zero-filled by TMA and masked at the store.
 //   The tiles of a last wave that would occupy at most half the machine are computed as two halves
-//   of K each, added into the zeroed output.
+//   of K each, by two CTAs (pairs): the first half stores its sum, the second adds its own to it once
+//   a flag says the first is done -- a fixed order, so the result is the same from call to call.
+//   The sum over k is kept in TMEM for at most 2048 terms at a time (fewer for narrow tiles); longer
+//   sums are added up in fp32 by the epilogue (the tensor core truncates when it adds into its
+//   accumulator).
 //   TF32 mode multiplies the fp32 operands as they are (the tensor core reads the top 19 bits).
 //   3xTF32 mode first splits each operand x into hi = tf32(x) (round to nearest) and
 //   lo = tf32(x - hi) in a scratch buffer (or one the caller keeps with the operand), then
@@ -202,6 +206,16 @@ constexpr int UMMA_K = 8;            // K of one tcgen05.mma.kind::tf32
 constexpr int THREADS = 192;         // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
 constexpr int SMEM_BUDGET = 200 * 1024;
 constexpr uint32_t WAIT_LIMIT = 1u << 20;  // polls per bounded wait (each poll may itself block a few us)
+// Longest run of k accumulated in TMEM before the sum moves to fp32 (see Params::chunk_kb), by tile
+// width.  The error of a chunk grows with its length -- measured on N(0,1) operands, normwise against
+// the largest entry: 3.0e-5 at 4096, 1.5e-5 at 2048, 0.8e-5 at 1024; several times that where the
+// products of a sum share a sign or nearly cancel, as in the weight gradients of an untrained network.
+// Its cost is one more drain of the accumulator, during which the tensor pipe idles ~3.4 us per
+// 128 x 256 accumulator: one full training step of 784-4096-4096-4096-10 at batch 8192 ran 6.01 ms with
+// 4096, 6.29 ms with 2048 and 6.65 ms with 1024 for the wide tiles, its logits 6.2e-5 / 3.3e-5 / 1.9e-5
+// from float64.  2048 keeps every gradient of that step within 1e-4 with room to spare; narrow tiles
+// drain cheaply and use shorter chunks.
+constexpr int chunk_k_for(int bn) { return bn >= 256 ? 2048 : (bn >= 128 ? 512 : 256); }
 
 template <int BN, int TERMS>
 struct Cfg {
@@ -223,6 +237,17 @@ struct Params {
     float* c;
     int vec_store;    // n % 4 == 0 and c 16-byte aligned
     int whole_tiles;  // tiles [0, whole_tiles) are computed whole; each later tile as two K-halves
+    // One word per (halved tile, CTA of the pair, epilogue warp), zero at launch: the warp that owns
+    // these rows in the FIRST half sets it after its last store; the same warp of the second half
+    // waits for it before it reads C.
+    int* half_flags;
+    // The tensor core adds each K=8 step into its fp32 accumulator with truncation, so the error of a
+    // sum kept in TMEM grows in proportion to the number of steps (measured, normwise against the
+    // result's largest entry, N(0,1) operands: 3e-5 after 4096 terms, 5e-4 after 65536).  A tile's
+    // k-blocks are therefore accumulated in chunks of at most chunk_kb blocks; every chunk starts
+    // from a zero accumulator and the epilogue adds the chunks in fp32 with round-to-nearest
+    // (C += chunk, same thread, in order; the running sum waits in L2).
+    int chunk_kb;
     // Epilogue of the fused forms (all optional; whole tiles only): c = [relu](acc + bias[col]), then
     // c *= (mask > 0 ? 1 : 0) with mask an [m, n] array of pitch n (ReLU's backward rule applied to a
     // gradient product), and the hi/lo split of c written next to it ([m, split_pitch] each) for the
@@ -236,22 +261,53 @@ struct Params {
 };
 
 // A unit of work: a whole output tile, or one K-half of a tile of the last, partly filled wave.
-// Halves let twice as many SMs work on that wave; both halves add their accumulator into C, which
-// the launcher zeroed for those tiles.  Two addends commute, so the result does not depend on which
-// half lands first.
+// Halves let twice as many SMs work on that wave.  The first half (part 0) writes its sum to C like
+// a whole tile would; the second (part 1) adds its chunks to what part 0 left there, after part 0's
+// flag.  Units 2t and 2t+1 are neighbours in the unit order, so the two halves of a tile run on
+// different CTAs (pairs) at the same time whenever the grid has more than one; a wait never points
+// at work queued behind the waiter.
 struct Unit {
     int tile, kb0, kb1;
     bool half;
+    int part;   // halves: 0 = first half of K, 1 = second
+    int slot;   // halves: index of the tile among the halved ones
 };
 __device__ __forceinline__ int unit_count(const Params& P) {
     const int tiles = P.tiles_m * P.tiles_n;
     return P.whole_tiles + 2 * (tiles - P.whole_tiles);
 }
 __device__ __forceinline__ Unit unit_of(int u, const Params& P) {
-    if (u < P.whole_tiles) return Unit{u, 0, P.num_kb, false};
+    if (u < P.whole_tiles) return Unit{u, 0, P.num_kb, false, 0, 0};
     const int v = u - P.whole_tiles;
     const int mid = (P.num_kb + 1) >> 1;
-    return (v & 1) ? Unit{P.whole_tiles + (v >> 1), mid, P.num_kb, true} : Unit{P.whole_tiles + (v >> 1), 0, mid, true};
+    return (v & 1) ? Unit{P.whole_tiles + (v >> 1), mid, P.num_kb, true, 1, v >> 1} : Unit{P.whole_tiles + (v >> 1), 0, mid, true, 0, v >> 1};
+}
+// Second half: wait (bounded) until the first half's warp for the same rows has published its sum.
+__device__ __forceinline__ bool wait_first_half(const int* flag, int lane, volatile int* abort_flag, int code) {
+    int ok = 1;
+    if (lane == 0) {
+        ok = 0;
+        for (uint32_t i = 0; i < (1u << 22); ++i) {
+            int v;
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+            if (v != 0) { ok = 1; break; }
+            if ((i & 63u) == 63u) {
+                if (*abort_flag) break;
+                __nanosleep(128);
+            }
+        }
+        if (!ok && !*abort_flag) {
+            *abort_flag = 1;
+            atomicCAS(&g_tc_status, 0, code);
+        }
+    }
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+// First half: every lane's stores of this warp's rows are done; make them visible, then raise the flag.
+__device__ __forceinline__ void publish_first_half(int* flag, int lane) {
+    __threadfence();
+    __syncwarp();
+    if (lane == 0) asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(flag), "r"(1) : "memory");
 }
 
 // Tile order.  Tiles are numbered band by band: a band is TILE_BAND tile columns wide and is walked
@@ -381,73 +437,111 @@ __host__ __device__ constexpr uint32_t make_idesc(int n, bool a_mn_major, bool b
 constexpr int STAGE_PITCH = 36;  // floats per staged row: 16-byte aligned, conflict-free for 128-bit accesses
 using EpilogueStage = float[32][STAGE_PITCH];
 
-// One 32 x 32 chunk of an accumulator leaves the CTA.  Each lane holds 32 columns of ITS row (the
-// shape tcgen05.ld.32x32b delivers), so a direct store writes 16 bytes to each of 32 different lines
-// per instruction.  Whole chunks therefore go through `stage` (one per epilogue warp): the lane
-// writes its row there, and the warp reads it back with 8 lanes across a row, so that every store
-// instruction writes 4 complete 128-byte lines.  `row_base` is the chunk's first row, `lane` the
-// caller's lane (= its row within the chunk).
-// The mask values (the ReLU output whose backward rule the epilogue applies) a lane needs for one
-// whole chunk: the eight 16-byte pieces it stores.  Loaded one chunk ahead of their use, so that the
-// DRAM latency of this fourth array overlaps the TMEM load and staging of the chunk before.
-struct MaskRegs {
+// What a lane prefetches for one whole 32 x 32 chunk in the layout it STORES in (row sub + 4i of the
+// chunk, 16 bytes at column c4): the eight pieces of the fourth array the chunk's epilogue reads -- the
+// running sum of the earlier K-chunks, or else the mask (the ReLU output whose backward rule the
+// epilogue applies).  Loaded one chunk ahead of their use, so that their DRAM latency overlaps the
+// TMEM load and staging of the chunk before.
+struct SideRegs {
     float4 v[8];
 };
-__device__ __forceinline__ bool chunk_is_whole(const Params& P, bool half, int64_t col0) {
-    return !half && P.vec_store && col0 + 32 <= P.n;
+__device__ __forceinline__ bool chunk_is_whole(const Params& P, int64_t col0) {
+    return P.vec_store && col0 + 32 <= P.n;
 }
-__device__ __forceinline__ void load_mask(const Params& P, bool half, int64_t row_base, int lane, int64_t col0, MaskRegs& mk) {
-    if (P.mask == nullptr || !chunk_is_whole(P, half, col0)) return;
+// first / last: this is the unit's first / last K-chunk.  Which array the prefetch serves:
+// the running sum in C when there is one (!first), else the mask (only the last chunk applies it).
+__device__ __forceinline__ const float* side_array(const Params& P, bool first, bool last) {
+    return !first ? P.c : (last ? P.mask : nullptr);
+}
+__device__ __forceinline__ void load_side(const Params& P, bool first, bool last, int64_t row_base, int lane, int64_t col0, SideRegs& sd) {
+    const float* arr = side_array(P, first, last);
+    if (arr == nullptr || !chunk_is_whole(P, col0)) return;
     const int sub = lane >> 3, c4 = (lane & 7) * 4;
-    const float* src = P.mask + (row_base + sub) * P.n + col0 + c4;
+    const float* src = arr + (row_base + sub) * P.n + col0 + c4;
     const int64_t step = 4 * P.n;
     const int rows_left = static_cast<int>(P.m - row_base < 32 ? P.m - row_base : 32);
 #pragma unroll
     for (int i = 0; i < 8; ++i)
-        mk.v[i] = (i * 4 + sub < rows_left) ? __ldcs(reinterpret_cast<const float4*>(src + i * step)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        sd.v[i] = (i * 4 + sub < rows_left) ? __ldcg(reinterpret_cast<const float4*>(src + i * step)) : make_float4(0.f, 0.f, 0.f, 0.f);  // (L2: a running sum may come from another SM)
 }
 
-__device__ __forceinline__ void emit_chunk(const Params& P, bool half, int64_t row_base, int lane, int64_t col0, uint32_t (&r)[32],
-                                           EpilogueStage& stage, const MaskRegs& mk) {
+// One 32 x 32 chunk of an accumulator leaves the CTA.  Each lane holds 32 columns of ITS row (the
+// shape tcgen05.ld.32x32b delivers), so a direct store would write 16 bytes to each of 32 different
+// lines per instruction.  Whole chunks therefore go through `stage` (one per epilogue warp): the lane
+// writes its row there, and the warp reads it back with 8 lanes across a row, so that every store
+// instruction writes 4 complete 128-byte lines.  All epilogue arithmetic happens in that store
+// layout, one fp32 operation per element and step, in this order: + running sum of the earlier
+// K-chunks; on the last chunk + bias, ReLU, x (mask > 0), store, hi/lo split of what was stored.
+__device__ __forceinline__ void emit_chunk(const Params& P, bool half, bool first, bool last, int64_t row_base, int lane, int64_t col0,
+                                           uint32_t (&r)[32], EpilogueStage& stage, const SideRegs& sd) {
     if (col0 >= P.n) return;  // same for the whole warp
     const int64_t row = row_base + lane;
-    if (chunk_is_whole(P, half, col0)) {
-        if (P.bias != nullptr || P.relu) {
-#pragma unroll
-            for (int v = 0; v < 32; ++v) {
-                float x = __uint_as_float(r[v]);
-                if (P.bias != nullptr) x += __ldg(P.bias + col0 + v);  // Add_BASIC_kernel's [N,H] + [H]
-                if (P.relu) x = x > 0.0f ? x : 0.0f;                    // ReLU_BASIC_kernel (NaN -> 0)
-                r[v] = __float_as_uint(x);
-            }
-        }
-#pragma unroll
-        for (int v = 0; v < 8; ++v)
-            *reinterpret_cast<float4*>(&stage[lane][4 * v]) =
-                make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
-        __syncwarp();
+    if (chunk_is_whole(P, col0)) {
         // lane -> (row sub + 4i of the chunk, 16 bytes at column c4): addresses once, then a fixed step
         const int sub = lane >> 3, c4 = (lane & 7) * 4;
         const int rows_left = static_cast<int>(P.m - row_base < 32 ? P.m - row_base : 32);
         float* cdst = P.c + (row_base + sub) * P.n + col0 + c4;
         const int64_t cstep = 4 * P.n;
-        if (P.mask == nullptr && P.out_hi == nullptr) {
+        // A whole tile's running sum never leaves this warp before the last chunk, so it need not be in
+        // C's layout: piece i of a lane's OWN accumulator row is parked at the address the final store
+        // uses for its piece i -- the same coalesced lines, without the trip through shared memory (whose
+        // bandwidth the tensor core's operand reads need).  Only the last chunk transposes.
+        const bool parked = !half && rows_left == 32;
+        if (parked && !first) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                r[4 * i] = __float_as_uint(__fadd_rn(__uint_as_float(r[4 * i]), sd.v[i].x));
+                r[4 * i + 1] = __float_as_uint(__fadd_rn(__uint_as_float(r[4 * i + 1]), sd.v[i].y));
+                r[4 * i + 2] = __float_as_uint(__fadd_rn(__uint_as_float(r[4 * i + 2]), sd.v[i].z));
+                r[4 * i + 3] = __float_as_uint(__fadd_rn(__uint_as_float(r[4 * i + 3]), sd.v[i].w));
+            }
+        }
+        if (parked && !last) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                *reinterpret_cast<float4*>(cdst + i * cstep) =
+                    make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+            return;
+        }
+        const bool add_old = !first && !parked;  // (a parked sum has been added above)
+#pragma unroll
+        for (int v = 0; v < 8; ++v)
+            *reinterpret_cast<float4*>(&stage[lane][4 * v]) =
+                make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+        __syncwarp();
+        const bool plain = !add_old && (!last || (P.bias == nullptr && !P.relu && P.mask == nullptr && P.out_hi == nullptr));
+        if (plain && last) {
 #pragma unroll
             for (int i = 0; i < 8; ++i)
                 if (i * 4 + sub < rows_left) __stcs(reinterpret_cast<float4*>(cdst + i * cstep), *reinterpret_cast<const float4*>(&stage[i * 4 + sub][c4]));
+        } else if (plain) {  // the first of several chunks: read again by the next one, so no streaming hint
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (i * 4 + sub < rows_left) *reinterpret_cast<float4*>(cdst + i * cstep) = *reinterpret_cast<const float4*>(&stage[i * 4 + sub][c4]);
         } else {
-            const bool masked = P.mask != nullptr, split = P.out_hi != nullptr;
+            const bool biased = last && P.bias != nullptr, relu = last && P.relu, masked = last && P.mask != nullptr, split = last && P.out_hi != nullptr;
             const int64_t soff = (row_base + sub) * P.split_pitch + col0 + c4, sstep = 4 * P.split_pitch;
+            float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (biased) bv = __ldg(reinterpret_cast<const float4*>(P.bias + col0 + c4));  // Add_BASIC_kernel's [N,H] + [H]
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 if (i * 4 + sub >= rows_left) continue;
                 float4 x = *reinterpret_cast<const float4*>(&stage[i * 4 + sub][c4]);
+                if (add_old) {  // the chunks before this one
+                    const float4 o = sd.v[i];
+                    x.x = __fadd_rn(x.x, o.x); x.y = __fadd_rn(x.y, o.y); x.z = __fadd_rn(x.z, o.z); x.w = __fadd_rn(x.w, o.w);
+                }
+                if (biased) { x.x += bv.x; x.y += bv.y; x.z += bv.z; x.w += bv.w; }
+                if (relu) {    // ReLU_BASIC_kernel (NaN -> 0)
+                    x.x = x.x > 0.0f ? x.x : 0.0f; x.y = x.y > 0.0f ? x.y : 0.0f; x.z = x.z > 0.0f ? x.z : 0.0f; x.w = x.w > 0.0f ? x.w : 0.0f;
+                }
                 if (masked) {  // g * (y > 0 ? 1 : 0): the backward rule of ReLU, y its output
-                    const float4 y = mk.v[i];
+                    const float4 y = first ? sd.v[i] : __ldcs(reinterpret_cast<const float4*>(P.mask + (row_base + sub + 4 * i) * P.n + col0 + c4));
                     x.x *= y.x > 0.0f ? 1.0f : 0.0f; x.y *= y.y > 0.0f ? 1.0f : 0.0f;
                     x.z *= y.z > 0.0f ? 1.0f : 0.0f; x.w *= y.w > 0.0f ? 1.0f : 0.0f;
                 }
-                __stcs(reinterpret_cast<float4*>(cdst + i * cstep), x);
+                if (last) __stcs(reinterpret_cast<float4*>(cdst + i * cstep), x);
+                else *reinterpret_cast<float4*>(cdst + i * cstep) = x;  // read again by the next chunk: keep it in L2
                 if (split) {
                     float4 h, l;
                     h.x = to_tf32_rna(x.x); h.y = to_tf32_rna(x.y); h.z = to_tf32_rna(x.z); h.w = to_tf32_rna(x.w);
@@ -462,30 +556,19 @@ __device__ __forceinline__ void emit_chunk(const Params& P, bool half, int64_t r
     }
     if (row >= P.m) return;
     float* crow = P.c + row * P.n;
-    if (half) {
-        // one K-half of the tile: add into the zeroed C
-        if (P.vec_store && col0 + 32 <= P.n) {
-#pragma unroll
-            for (int v = 0; v < 8; ++v)
-                atomicAdd(reinterpret_cast<float4*>(crow + col0) + v,
-                          make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3])));
-        } else {
-#pragma unroll
-            for (int v = 0; v < 32; ++v)
-                if (col0 + v < P.n) atomicAdd(crow + col0 + v, __uint_as_float(r[v]));
-        }
-        return;
-    }
-    // a ragged chunk (or an unaligned C): element by element
+    // a ragged chunk (or an unaligned C): element by element, the same operations in the same order
 #pragma unroll
     for (int v = 0; v < 32; ++v)
         if (col0 + v < P.n) {
             float x = __uint_as_float(r[v]);
-            if (P.bias != nullptr) x += __ldg(P.bias + col0 + v);
-            if (P.relu) x = x > 0.0f ? x : 0.0f;
-            if (P.mask != nullptr) x *= P.mask[row * P.n + col0 + v] > 0.0f ? 1.0f : 0.0f;
+            if (!first) x = __fadd_rn(x, __ldcg(crow + col0 + v));
+            if (last) {
+                if (P.bias != nullptr) x += __ldg(P.bias + col0 + v);
+                if (P.relu) x = x > 0.0f ? x : 0.0f;
+                if (P.mask != nullptr) x *= P.mask[row * P.n + col0 + v] > 0.0f ? 1.0f : 0.0f;
+            }
             crow[col0 + v] = x;
-            if (P.out_hi != nullptr) {
+            if (last && P.out_hi != nullptr) {
                 const float h = to_tf32_rna(x);
                 P.out_hi[row * P.split_pitch + col0 + v] = h;
                 P.out_lo[row * P.split_pitch + col0 + v] = to_tf32_rna(x - h);
@@ -599,10 +682,13 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
             bool ok = true;
             for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
                 const Unit U = unit_of(u, P);
+                const int chunk_kb = P.chunk_kb;
+                for (int c0 = U.kb0; c0 < U.kb1 && ok; c0 += chunk_kb) {  // one accumulator per K-chunk
+                const int c1 = c0 + chunk_kb < U.kb1 ? c0 + chunk_kb : U.kb1;
                 if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, &abort_flag, 0x200 | (18 + acc))) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-                for (int kb = U.kb0; kb < U.kb1; ++kb) {
+                for (int kb = c0; kb < c1; ++kb) {
                     if (!mbar_wait(full_bar(stage), phase, &abort_flag, 0x200 | stage)) { ok = false; break; }
                     tc_fence_after();
 #pragma unroll
@@ -614,7 +700,7 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
                         const uint32_t a_sw = A_MN ? kSwizzle128BAtom32B : kSwizzle128B, b_sw = B_MN ? kSwizzle128BAtom32B : kSwizzle128B;
                         const uint64_t a_hi = make_desc(a_addr(stage, 0) + a_step, a_lbo, a_sbo, a_sw);
                         const uint64_t b_hi = make_desc(b_addr(stage, 0) + b_step, b_lbo, b_sbo, b_sw);
-                        const uint32_t first = (kb > U.kb0 || ks > 0) ? 1u : 0u;
+                        const uint32_t first = (kb > c0 || ks > 0) ? 1u : 0u;
                         if (TERMS == 3) {
                             const uint64_t a_lo = make_desc(a_addr(stage, 1) + a_step, a_lbo, a_sbo, a_sw);
                             const uint64_t b_lo = make_desc(b_addr(stage, 1) + b_step, b_lbo, b_sbo, b_sw);
@@ -629,8 +715,9 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
-                tc_commit(tfull_bar(acc));        // accumulator complete
+                tc_commit(tfull_bar(acc));        // this chunk's accumulator is complete
                 if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+                }
             }
         }
     } else {
@@ -645,8 +732,15 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
             tile_coords(U.tile, P.tiles_m, P.tiles_n, tm, tn);
             const int64_t m0 = static_cast<int64_t>(tm) * BM, n0 = static_cast<int64_t>(tn) * BN;
             const int64_t row_base = m0 + quarter * 32;
-            MaskRegs mk_now, mk_next;
-            load_mask(P, U.half, row_base, lane, n0, mk_next);  // chunk 0's, while the accumulator is still being computed
+            const int chunk_kb = P.chunk_kb;
+            int* half_flag = U.half ? P.half_flags + (U.slot * 2 + 0) * 4 + quarter : nullptr;
+            // second half of K: its sums are added to what the first half stored
+            if (U.half && U.part == 1 && !wait_first_half(half_flag, lane, &abort_flag, 0xA00 | quarter)) { ok = false; break; }
+#pragma unroll 1
+            for (int c0 = U.kb0; c0 < U.kb1 && ok; c0 += chunk_kb) {  // one accumulator per K-chunk
+            const bool first = c0 == U.kb0 && U.part == 0, last = c0 + chunk_kb >= U.kb1;
+            SideRegs sd_now, sd_next;
+            load_side(P, first, last, row_base, lane, n0, sd_next);  // column chunk 0's, while the accumulator is still being computed
             if (!mbar_wait(tfull_bar(acc), acc_phase, &abort_flag, 0x300 | (16 + acc))) { ok = false; break; }
             tc_fence_after();
 #pragma unroll 1
@@ -654,16 +748,18 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
                 uint32_t r[32];
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN + cc * 32);
                 tmem_ld32(taddr, r);
-                mk_now = mk_next;
+                sd_now = sd_next;
                 const int64_t col0 = n0 + cc * 32;
-                if (cc + 1 < BN / 32) load_mask(P, U.half, row_base, lane, col0 + 32, mk_next);
+                if (cc + 1 < BN / 32) load_side(P, first, last, row_base, lane, col0 + 32, sd_next);
                 tmem_ld_wait();
-                emit_chunk(P, U.half, row_base, lane, col0, r, stages[warp - 2], mk_now);
+                emit_chunk(P, U.half, first, last, row_base, lane, col0, r, stages[warp - 2], sd_now);
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(acc));
             if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            }
+            if (ok && U.half && U.part == 0) publish_first_half(half_flag, lane);
         }
     }
 
@@ -906,10 +1002,13 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
                 const int u = unit_at(seq);
                 if (u >= num_units) break;
                 const Unit U = unit_of(u, P);
+                const int chunk_kb = P.chunk_kb;
+                for (int c0 = U.kb0; c0 < U.kb1 && ok; c0 += chunk_kb) {  // one accumulator per K-chunk
+                const int c1 = c0 + chunk_kb < U.kb1 ? c0 + chunk_kb : U.kb1;
                 if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, &abort_flag, 0x600 | (18 + acc))) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-                for (int kb = U.kb0; kb < U.kb1; ++kb) {
+                for (int kb = c0; kb < c1; ++kb) {
                     if (!mbar_wait(full_bar(stage), phase, &abort_flag, 0x600 | stage)) { ok = false; break; }
                     tc_fence_after();
 #pragma unroll
@@ -921,7 +1020,7 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
                         const uint32_t a_sw = A_MN ? kSwizzle128BAtom32B : kSwizzle128B, b_sw = B_MN ? kSwizzle128BAtom32B : kSwizzle128B;
                         const uint64_t a_hi = make_desc(a_addr(stage, 0) + a_step, a_lbo, a_sbo, a_sw);
                         const uint64_t b_hi = make_desc(b_addr(stage, 0) + b_step, b_lbo, b_sbo, b_sw);
-                        const uint32_t first = (kb > U.kb0 || ks > 0) ? 1u : 0u;
+                        const uint32_t first = (kb > c0 || ks > 0) ? 1u : 0u;
                         if (TERMS == 3) {
                             const uint64_t a_lo = make_desc(a_addr(stage, 1) + a_step, a_lbo, a_sbo, a_sw);
                             const uint64_t b_lo = make_desc(b_addr(stage, 1) + b_step, b_lbo, b_sbo, b_sw);
@@ -936,8 +1035,9 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
-                tc_commit_both(tfull_bar(acc));        // accumulator complete, in both CTAs' TMEM
+                tc_commit_both(tfull_bar(acc));        // this chunk's accumulator is complete, in both CTAs' TMEM
                 if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+                }
             }
             if (!ok) st_cluster_u32(peer_abort, 1u);
         }
@@ -957,8 +1057,15 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
             const int64_t m0 = static_cast<int64_t>(tm) * (2 * BM) + static_cast<int64_t>(rank) * BM;
             const int64_t n0 = static_cast<int64_t>(tn) * BN;
             const int64_t row_base = m0 + quarter * 32;
-            MaskRegs mk_now, mk_next;
-            load_mask(P, U.half, row_base, lane, n0, mk_next);  // chunk 0's, while the accumulator is still being computed
+            const int chunk_kb = P.chunk_kb;
+            int* half_flag = U.half ? P.half_flags + (U.slot * 2 + static_cast<int>(rank)) * 4 + quarter : nullptr;
+            // second half of K: its sums are added to what the first half stored
+            if (U.half && U.part == 1 && !wait_first_half(half_flag, lane, &abort_flag, 0xA00 | quarter)) { ok = false; break; }
+#pragma unroll 1
+            for (int c0 = U.kb0; c0 < U.kb1 && ok; c0 += chunk_kb) {  // one accumulator per K-chunk
+            const bool first = c0 == U.kb0 && U.part == 0, last = c0 + chunk_kb >= U.kb1;
+            SideRegs sd_now, sd_next;
+            load_side(P, first, last, row_base, lane, n0, sd_next);  // column chunk 0's, while the accumulator is still being computed
             if (!mbar_wait(tfull_bar(acc), acc_phase, &abort_flag, 0x700 | (16 + acc))) { ok = false; break; }
             tc_fence_after();
 #pragma unroll 1
@@ -966,16 +1073,18 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
                 uint32_t r[32];
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN + cc * 32);
                 tmem_ld32(taddr, r);
-                mk_now = mk_next;
+                sd_now = sd_next;
                 const int64_t col0 = n0 + cc * 32;
-                if (cc + 1 < BN / 32) load_mask(P, U.half, row_base, lane, col0 + 32, mk_next);
+                if (cc + 1 < BN / 32) load_side(P, first, last, row_base, lane, col0 + 32, sd_next);
                 tmem_ld_wait();
-                emit_chunk(P, U.half, row_base, lane, col0, r, stages[warp - 2], mk_now);
+                emit_chunk(P, U.half, first, last, row_base, lane, col0, r, stages[warp - 2], sd_now);
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(acc ? tempty1 : tempty0);
             if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+            }
+            if (ok && U.half && U.part == 0) publish_first_half(half_flag, lane);
         }
         if (!ok && lane == 0) st_cluster_u32(peer_abort, 1u);
     }
@@ -1090,21 +1199,6 @@ ctk_status launch_tc_major(bool a_mn, bool b_mn, const CUtensorMap maps[4], cons
 }
 
 int pick_bn(int64_t n) { return n > 128 ? 256 : (n > 64 ? 128 : 64); }
-
-// Zeroes the output tiles [first, first + count) (tile_m x tile_n each, numbered as tile_coords does):
-// the tiles whose K-halves are added into C.
-__global__ void __launch_bounds__(256) zero_tiles_kernel(float* __restrict__ c, int64_t m, int64_t n, int tile_m, int tile_n, int tiles_m, int tiles_n, int first, int parts) {
-    const int tile = first + blockIdx.x / parts, part = blockIdx.x % parts;
-    int tm, tn;
-    tile_coords(tile, tiles_m, tiles_n, tm, tn);
-    const int64_t m0 = static_cast<int64_t>(tm) * tile_m, n0 = static_cast<int64_t>(tn) * tile_n;
-    const int rows_per = (tile_m + parts - 1) / parts;
-    const int64_t r0 = m0 + static_cast<int64_t>(part) * rows_per;
-    const int64_t r1 = r0 + rows_per < m0 + tile_m ? r0 + rows_per : m0 + tile_m;
-    const int64_t c1 = n0 + tile_n < n ? n0 + tile_n : n;
-    for (int64_t r = r0 + (threadIdx.x >> 6); r < r1 && r < m; r += 4)
-        for (int64_t j = n0 + (threadIdx.x & 63); j < c1; j += 64) c[r * n + j] = 0.0f;
-}
 
 // Number of CTA pairs resident on the device (all instantiations of the pair kernel use the same
 // threads and shared memory, so one of them is asked).
@@ -1320,6 +1414,32 @@ int choose_path(const float* a, const float* b, int64_t m, int64_t n, int64_t k,
     if (oa) *oa = A;
     if (ob) *ob = B;
     return 0;
+}
+
+// ---- flags of the K-halved tiles ------------------------------------------------------------------
+// A launch with halved tiles needs 8 words per such tile (2 CTAs x 4 epilogue warps), zero when it
+// starts.  They live in a ring of slots inside the module (no allocation: the entry point that must not
+// allocate uses them too); every launch takes the next slot and clears it on its own stream first.  A
+// slot comes round again after kHalfSlots launches with halved tiles -- far more than can be in flight.
+constexpr int kHalfTilesMax = 128, kHalfSlots = 256;
+static __device__ int g_half_flags[kHalfSlots][kHalfTilesMax * 8];
+int* g_half_flags_ptr[64] = {nullptr};
+std::mutex g_half_mu;
+unsigned g_half_next = 0;
+
+ctk_status half_flag_slot(int** out) {
+    int dev = 0;
+    CTK_CUDA(cudaGetDevice(&dev));
+    CTK_REQUIRE(dev >= 0 && dev < 64, "device ordinal out of range");
+    std::lock_guard<std::mutex> lock(g_half_mu);
+    if (!g_half_flags_ptr[dev]) {
+        void* p = nullptr;
+        CTK_CUDA(cudaGetSymbolAddress(&p, g_half_flags));
+        CTK_REQUIRE(p != nullptr, "cudaGetSymbolAddress returned a null address for the half-tile flags");
+        g_half_flags_ptr[dev] = static_cast<int*>(p);
+    }
+    *out = g_half_flags_ptr[dev] + static_cast<size_t>(g_half_next++ % kHalfSlots) * (kHalfTilesMax * 8);
+    return CTK_OK;
 }
 
 // ---- fixed scratch for callers that must not allocate -------------------------------------------
@@ -1567,6 +1687,7 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
     P.tiles_m = static_cast<int>((m + tile_m - 1) / tile_m);
     P.tiles_n = static_cast<int>((n + bn - 1) / bn);
     P.num_kb = static_cast<int>((k + tc::BK - 1) / tc::BK);
+    P.chunk_kb = tc::chunk_k_for(tc::pick_bn(n)) / tc::BK;
     P.c = c;
     P.vec_store = (n % 4 == 0) && ((reinterpret_cast<uintptr_t>(c) & 15u) == 0);
     P.bias = fe.bias;
@@ -1581,18 +1702,22 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
     }
     CTK_REQUIRE(static_cast<int64_t>(P.tiles_m) * P.tiles_n < (int64_t(1) << 30), "ctk_matmul_f32: too many tiles");
     // The last wave: when at most half of the SMs (or CTA pairs) would have a tile, its tiles are
-    // computed as two K-halves each, added into zeroed C, so that twice as many work on it.
+    // computed as two K-halves each (the second added to the first, in that order), so that twice as
+    // many work on it.
     {
         const int tiles = P.tiles_m * P.tiles_n;
         int workers = ctk::sm_count();
         if (paired && (rc = tc::resident_pairs(&workers))) return rc;
         P.whole_tiles = tiles;
         const int tail = tiles % workers;
-        if (g_split_tail && !fused && P.num_kb >= 16 && tail > 0 && 2 * tail <= workers) {  // (a fused epilogue needs the whole sum)
+        // (a fused epilogue needs the whole sum)
+        P.half_flags = nullptr;
+        if (g_split_tail && !fused && P.num_kb >= 16 && tail > 0 && 2 * tail <= workers && tail <= kHalfTilesMax) {
+            int* flags = nullptr;
+            if ((rc = half_flag_slot(&flags))) return rc;
+            CTK_CUDA(cudaMemsetAsync(flags, 0, static_cast<size_t>(tail) * 8 * sizeof(int), st));
+            P.half_flags = flags;
             P.whole_tiles = tiles - tail;
-            const int parts = 4;
-            tc::zero_tiles_kernel<<<tail * parts, 256, 0, st>>>(c, m, n, tile_m, bn, P.tiles_m, P.tiles_n, P.whole_tiles, parts);
-            CTK_LAUNCH_CHECK("zero_tiles_kernel");
         }
     }
 

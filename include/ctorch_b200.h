@@ -288,8 +288,8 @@ int ctk_get_matmul_mode(void);
 ctk_status ctk_set_matmul_pairing(int pairing);
 /* 1 (default): when the last wave of output tiles would occupy at most half of the SMs (or CTA    */
 /* pairs) -- which includes every product with few tiles, like the 10-class layer -- each of its   */
-/* tiles is computed as two halves of K that are added into the zeroed output (two addends: the    */
-/* result does not depend on their order).  0: every tile whole.                                   */
+/* tiles is computed as two halves of K by two CTAs (pairs); the second half is added to the first   */
+/* after a flag, always in that order, so repeated calls give the same bits.  0: every tile whole.  */
 ctk_status ctk_set_matmul_tail_split(int on);
 /* Self-test of the kernels' bounded waits (no counterpart in the reference): one CTA waits with a  */
 /* short limit on a barrier nothing arrives on.  result = {first wait ok (expected 0), CTA abort     */

@@ -67,14 +67,16 @@ def _oracle_samples(orc, sa, sb, ta, tb, rng):
     return (ri, ci, rows, cols), (e32, r32, c32), (e64, r64, c64)
 
 
-def _check_product(C, idx, ref32, ref64, tol, what):
+def _normwise(got, ref):
+    got, ref = np.asarray(got, np.float64), np.asarray(ref, np.float64)
+    return float(np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+
+def _product_errors(C, idx, ref32, ref64):
+    """Normwise errors of the sampled entries, rows and columns: (vs the reference recurrence, vs float64)."""
     ri, ci, rows, cols = idx
     got = (C[ri, ci], C[rows], C[:, cols].T)
-    worst = 0.0
-    for g, r32, r64, part in zip(got, ref32, ref64, ("entries", "rows", "columns")):
-        worst = max(worst, assert_matmul_close(g, r32, tol, f"{what} {part} vs the reference recurrence"))
-        worst = max(worst, assert_matmul_close(g, r64, tol, f"{what} {part} vs float64"))
-    return worst
+    return (max(_normwise(g, r) for g, r in zip(got, ref32)), max(_normwise(g, r) for g, r in zip(got, ref64)))
 
 
 def _projection_check(C, sa, sb, ta, tb, tol, rng, what):
@@ -105,7 +107,7 @@ def test_config3_products_at_full_size(cb, orc, m, k, n):
     products = (("C=A.B", A, B, False, False, dA_, dB_),
                 ("dA=dC.B^T", dC, B, False, True, dG, dB_),
                 ("dB=A^T.dC", A, dC, True, False, dA_, dG))
-    report = {}
+    report, bad = {}, []
     for name, sa, sb, ta, tb, da, db in products:
         idx, ref32, ref64 = _oracle_samples(orc, sa, sb, ta, tb, rng)
         for mode in ("3xtf32", "tf32"):
@@ -114,19 +116,28 @@ def test_config3_products_at_full_size(cb, orc, m, k, n):
             C = out.numpy()
             del out
             what = f"{name} {m}x{k}x{n} {mode}"
-            report[what] = _check_product(C, idx, ref32, ref64, TOL[mode], what)
+            e32, e64 = _product_errors(C, idx, ref32, ref64)
+            report[what] = f"{e32:.2e} vs the reference recurrence, {e64:.2e} vs float64"
+            if max(e32, e64) > TOL[mode]:
+                bad.append(what)
             _projection_check(C, sa, sb, ta, tb, TOL[mode], rng, what)
             del C
     _status_ok(cb)
-    print({k_: f"{v:.2e}" for k_, v in report.items()})
+    print("\nnormwise errors on 4096 entries + 2 rows + 2 columns:")
+    for k_, v in report.items():
+        print(f"  {k_}: {v}")
+    assert not bad, f"above tolerance: {bad}; all: {report}"
 
 
 # ---- config 5: one full-width training step -----------------------------------------------------------
-def _fp64_step(dims, x, labels, Ws, bs, lr):
+def _fp64_step(dims, x, labels, Ws, bs, lr, masks):
     """The training step of mnist/mnist.cpp:44-92 in float64 with the reference's semantics: summed
     cross entropy with the 1e-10 clamp, bias gradient = row 0 of the upstream gradient
     (src/AutoDiff.cpp:690-757), backward through the weights as registered (equal to the live ones at
-    the first step), p -= g*lr."""
+    the first step), p -= g*lr.  masks[l]: which hidden units of layer l the DEVICE found active.  ReLU's
+    derivative jumps at 0, so a pre-activation within rounding distance of 0 may fall on either side in
+    float32 and float64; one such unit moves a whole column of a weight gradient by ~1 % of its size.
+    Backward therefore uses the device's decisions (forward does not: it has no jump)."""
     h = [x.astype(np.float64)]
     for l, (W, b) in enumerate(zip(Ws, bs)):
         z = h[-1] @ W.astype(np.float64) + b.astype(np.float64)
@@ -140,14 +151,16 @@ def _fp64_step(dims, x, labels, Ws, bs, lr):
     loss = -(onehot * np.log(np.maximum(p, 1e-10))).sum()
     g = p - onehot
     gW, gb = [None] * len(Ws), [None] * len(Ws)
+    flips = 0
     for l in range(len(Ws) - 1, -1, -1):
         gb[l] = g[0].copy()
         gW[l] = h[l].T @ g
         if l > 0:
-            g = (g @ Ws[l].astype(np.float64).T) * (h[l] > 0)
+            flips += int(np.count_nonzero(masks[l - 1] != (h[l] > 0)))
+            g = (g @ Ws[l].astype(np.float64).T) * masks[l - 1]
     newW = [W.astype(np.float64) - lr * gw for W, gw in zip(Ws, gW)]
     newb = [b.astype(np.float64) - lr * g_ for b, g_ in zip(bs, gb)]
-    return logits, loss, gW, gb, newW, newb
+    return logits, loss, gW, gb, newW, newb, flips
 
 
 def test_config5_one_full_width_step(cb, orc):
@@ -181,24 +194,56 @@ def test_config5_one_full_width_step(cb, orc):
     ref = orc.mlp_train(dims, x[rows][None, None], labels[rows][None, None], params, lr, 1)
     assert_matmul_close(logits[rows], ref["logits"][0], 1e-4, "logits of sampled rows vs the oracle")
 
-    # (2) the whole step in float64
-    l64, loss64, gW, gb, newW, newb = _fp64_step(dims, x, labels, Ws, bs, lr)
-    assert_matmul_close(logits, l64, 1e-4, "all logits vs float64")
-    assert abs(loss - loss64) <= 1e-4 * abs(loss64), (loss, loss64)
+    # (2) the whole step in float64; the hidden units' on/off decisions come from the device (the same
+    # fused product + bias + ReLU kernel the trainer's forward runs, outside any tape)
+    h = F.Tensor.from_numpy(x)
+    masks = []
+    for l in range(len(Ws) - 1):
+        h = h.linear(F.Tensor.from_numpy(Ws[l]), F.Tensor.from_numpy(bs[l]), True)
+        masks.append(h.numpy() > 0)
+    del h
+    l64, loss64, gW, gb, newW, newb, flips = _fp64_step(dims, x, labels, Ws, bs, lr, masks)
+    print(f"\nhidden units whose on/off decision differs between the device and float64: {flips} of {sum(m.size for m in masks)}")
+    assert flips <= 1e-5 * sum(m.size for m in masks)
+    report = {"logits": _normwise(logits, l64), "loss (rel)": abs(loss - loss64) / abs(loss64)}
     gW_gpu, gb_gpu = oracle.unpack_params(grads, dims)
     W_gpu, b_gpu = oracle.unpack_params(new_params, dims)
     for l in range(len(Ws)):
-        assert_matmul_close(gW_gpu[l], gW[l], 1e-4, f"dW{l} vs float64")
-        assert_matmul_close(gb_gpu[l], gb[l], 1e-4, f"db{l} (row 0 of the upstream gradient) vs float64")
-        assert_matmul_close(W_gpu[l], newW[l], 1e-4, f"updated W{l} vs float64")
-        assert_matmul_close(b_gpu[l], newb[l], 1e-4, f"updated b{l} vs float64")
-        # the update really happened: the step size is far above the tolerance's resolution of W
+        report[f"dW{l}"] = _normwise(gW_gpu[l], gW[l])
+        report[f"db{l} (row 0 of the upstream gradient)"] = _normwise(gb_gpu[l], gb[l])
+        report[f"updated W{l}"] = _normwise(W_gpu[l], newW[l])
+        report[f"updated b{l}"] = _normwise(b_gpu[l], newb[l])
+        # the update really happened: the step is far above the resolution of the comparison
         assert np.abs(W_gpu[l].astype(np.float64) - Ws[l]).max() > 0
+    print("normwise errors of one full-width step against float64:")
+    for k_, v in report.items():
+        print(f"  {k_}: {v:.2e}")
+    bad = {k_: v for k_, v in report.items() if not v <= 1e-4}
+    assert not bad, f"above 1e-4: {bad}"
 
 
 # ---- config 4: [65536, 32000] row-wise kernels ----------------------------------------------------------
 def _rows_of(dev, rows, cols):
     return np.stack([dev.view(int(r) * cols, (cols,)).numpy() for r in rows])
+
+
+def _assert_rows_close_or_better(got, ref, exact, what, rel=1e-5, abs_=1e-12):
+    """Rows that contain a sum of tens of thousands of terms: the reference adds them one by one in
+    float32 and is itself ~1e-5 away from the exact value, so the device result passes if it is
+    within rel of the float64 value, or at least as close to it as the reference is (per row)."""
+    got, ref, exact = (np.asarray(v, np.float64) for v in (got, ref, exact))
+    scale = np.abs(exact).max(axis=1, keepdims=True)
+    eg = (np.abs(got - exact) / scale).max(axis=1)
+    er = (np.abs(ref - exact) / scale).max(axis=1)
+    bad = ~((eg <= rel + abs_) | (eg <= er))
+    assert not bad.any(), f"{what}: {np.count_nonzero(bad)} rows; device error {eg.max():.2e}, reference error {er.max():.2e} (both against float64, per-row normwise)"
+    return float(eg.max()), float(er.max())
+
+
+def _softmax64(x):
+    z = x.astype(np.float64)
+    e = np.exp(z - z.max(axis=1, keepdims=True))
+    return e / e.sum(axis=1, keepdims=True)
 
 
 def test_config4_rowwise_at_65536_x_32000(cb, orc):
@@ -220,10 +265,13 @@ def test_config4_rowwise_at_65536_x_32000(cb, orc):
     xs = _rows_of(x, rows, C)
     y = cb.ops.softmax(x)
     ys = _rows_of(y, rows, C)
-    assert_close(ys, orc.softmax(xs), 1e-5, 1e-9, "softmax rows")
-    # backward, with the logits themselves standing in for the upstream gradient
+    y64 = _softmax64(xs)
+    print("\nsoftmax rows (device, reference) vs float64:", _assert_rows_close_or_better(ys, orc.softmax(xs), y64, "softmax rows"))
+    # backward, with the logits themselves standing in for the upstream gradient: y * (g - sum(g * y))
     dx = cb.ops.softmax_backward(y, x)
-    assert_close(_rows_of(dx, rows, C), orc.grad_unary("Softmax", xs, xs), 1e-5, 1e-7, "softmax backward rows")
+    g64 = xs.astype(np.float64)
+    dx64 = y64 * (g64 - (g64 * y64).sum(axis=1, keepdims=True))
+    print("softmax backward rows:", _assert_rows_close_or_better(_rows_of(dx, rows, C), orc.grad_unary("Softmax", xs, xs), dx64, "softmax backward rows"))
     del dx, y
     assert cb.ops.rowwise_status() == 0
 
@@ -236,14 +284,17 @@ def test_config4_rowwise_at_65536_x_32000(cb, orc):
     s8 = (edge // slab) * slab                              # the slab that straddles byte offset 2^32
     xs8 = x.view(s8 * C, (slab, C)).numpy()
     ref8 = float(orc.ce(xs8, labels[s8:s8 + slab]))
-    assert abs(parts[edge // slab] - ref8) <= 1e-5 * abs(ref8), (parts[edge // slab], ref8)
-    del xs8
+    z8 = xs8.astype(np.float64)
+    zmax = z8.max(axis=1)
+    exact8 = float((zmax + np.log(np.exp(z8 - zmax[:, None]).sum(axis=1)) - z8[np.arange(slab), labels[s8:s8 + slab].astype(int)]).sum())
+    assert_sum_close(parts[edge // slab], ref8, exact8, "summed cross entropy of the slab across byte offset 2^32")
+    del xs8, z8
 
     loss_f, d = cb.ops.cross_entropy_fused(x, dl)
     assert abs(float(loss_f.numpy()) - total) <= 1e-5 * abs(total)
     onehot = np.zeros((len(rows), C), np.float32)
     onehot[np.arange(len(rows)), labels[rows].astype(int)] = 1
-    assert_close(_rows_of(d, rows, C), orc.grad_loss("CE", xs, onehot), 1e-5, 1e-9, "fused CE gradient rows")
+    print("fused CE gradient rows:", _assert_rows_close_or_better(_rows_of(d, rows, C), orc.grad_loss("CE", xs, onehot), y64 - onehot, "fused CE gradient rows"))
     assert cb.ops.rowwise_status() == 0
 
 
@@ -251,8 +302,8 @@ def test_config4_rowwise_at_65536_x_32000(cb, orc):
 def test_config2_elementwise_and_sum_at_2_to_28(cb, orc):
     n = 1 << 28
     rng = np.random.default_rng(11)
-    a = rng.uniform(-4, 4, n).astype(np.float32)
-    b = rng.uniform(0.5, 4, n).astype(np.float32)
+    a = rng.random(n, dtype=np.float32) * np.float32(8) - np.float32(4)         # U(-4, 4)
+    b = rng.random(n, dtype=np.float32) * np.float32(3.5) + np.float32(0.5)     # U(0.5, 4): no zero divisors
     da, db = cb.to_device(a), cb.to_device(b)
     slabs = [slice(0, 1 << 20), slice((n >> 1) - (1 << 19), (n >> 1) + (1 << 19)), slice(n - (1 << 20), n)]
     stride = np.arange(12345, n, 65521)
@@ -272,7 +323,7 @@ def test_config2_elementwise_and_sum_at_2_to_28(cb, orc):
     for op in ("Sigmoid", "Tanh", "Sin", "Cos"):
         assert_close(sample(cb.ops.unary(op, da, out=out).numpy()), orc.unary(op, sa), 1e-5, 1e-6, f"{op} at 2^28")
     # backward of Mul (the 20 B/element form) and of Tanh
-    g = rng.standard_normal(n).astype(np.float32)
+    g = rng.standard_normal(n, dtype=np.float32)
     dg = cb.to_device(g)
     sg = sample(g)
     dA, dB = cb.ops.binary_backward("Mul", da, db, dg)
@@ -280,7 +331,8 @@ def test_config2_elementwise_and_sum_at_2_to_28(cb, orc):
     assert_exact(sample(dA.numpy()), rA, "Mul backward da at 2^28")
     assert_exact(sample(dB.numpy()), rB, "Mul backward db at 2^28")
     del dA, dB
-    assert_close(sample(cb.ops.unary_backward("Tanh", da, dg).numpy()), orc.grad_unary("Tanh", sa, sg), 1e-5, 1e-6, "Tanh backward at 2^28")
+    # (1 - t^2) * g: the transcendental's 1e-6 absolute term scales with the upstream gradient (|g| up to ~6 here)
+    assert_close(sample(cb.ops.unary_backward("Tanh", da, dg).numpy()), orc.grad_unary("Tanh", sa, sg), 1e-5, 1e-6 * float(np.abs(sg).max()), "Tanh backward at 2^28")
     # Sum: against float64, and at least as accurate as the reference's sequential fp32 sum
     s_gpu = float(cb.ops.sum(da).numpy())
     assert_sum_close(s_gpu, orc.sum(a), a.sum(dtype=np.float64), "Sum at 2^28")
