@@ -53,6 +53,7 @@ LR = 0.01
 WORKLOAD = "dp-mlp-784-4096-4096-4096-10_batch8192-per-gpu_fp32_sgd"
 CPU_SAMPLE_BATCH = 4  # rows per reference step: the reference's cost is linear in rows (~0.2 GFLOP/s)
 DEFAULT_DP_MODE, DEFAULT_MAX_CTAS = "inplace", 0
+DEFAULT_CORRECTION = "tf32"
 NOMINAL_TF32 = 1125.0  # TFLOP/s, dense, the part's data sheet
 NOMINAL_HBM = 7700.0   # GB/s
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant shape from one ncu capture
@@ -359,6 +360,7 @@ def run_mlp(args, cp):
     from ctorch_b200.device import PinnedArray
     cb.check(cb.lib.ctk_set_device(local_rank))
     cb.ops.set_matmul_pairing(args.pairing)
+    cb.ops.set_matmul_correction(1 if args.correction == "bf16" else 0)
     F.set_quiet(True)
     peaks = measured_peaks()
 
@@ -378,7 +380,8 @@ def run_mlp(args, cp):
     x, labels = make_batch(rank)
     onehot = np.zeros((BATCH, DIMS[-1]), np.float32)
     onehot[np.arange(BATCH), labels.astype(int)] = 1
-    trainer = F.MlpTrainer(DIMS, params, LR)
+    lr = LR / BATCH if args.stable_lr else LR
+    trainer = F.MlpTrainer(DIMS, params, lr)
     if comm is not None:
         trainer.set_dp_mode(args.dp_mode)
         trainer.set_comm(comm)
@@ -495,8 +498,8 @@ def run_mlp(args, cp):
         out = dict(
             metric="mlp_train_samples_per_s", value=value, unit="samples/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
             ms_per_step=per_step, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",
-            config=dict(workload=WORKLOAD, global_batch=BATCH * world, parallelism=f"dp{world}", matmul_mode="3xtf32",
-                        gradient_exchange=(args.dp_mode if world > 1 else None), nccl_max_ctas=args.max_ctas or None,
+            config=dict(workload=WORKLOAD, global_batch=BATCH * world, parallelism=f"dp{world}", matmul_mode="3xtf32" if args.correction == "tf32" else "tf32 + 2 x bf16 correction terms",
+                        lr=lr, gradient_exchange=(args.dp_mode if world > 1 else None), nccl_max_ctas=args.max_ctas or None,
                         l2="per-step working set (weights 147 MB + activations 3x134 MB per layer pass) exceeds the 126 MB L2",
                         loss_last=float(loss_dev) if loss_dev is not None else None, matmul_status=status, stable_lr_run=stable),
             clocks=clocks,
@@ -670,6 +673,7 @@ def run_single_op(args):
     import ctorch_b200 as cb
     cb.check(cb.lib.ctk_set_device(0))
     cb.ops.set_matmul_pairing(args.pairing)
+    cb.ops.set_matmul_correction(1 if args.correction == "bf16" else 0)
     peaks = measured_peaks()
 
     def timeit(fn, iters, warm=3):
@@ -900,13 +904,14 @@ def run_mnist_app(cb, args, rng):
 
 def run_one_kernel(cb, case, rng):
     """A few launches of ONE kernel on a small case (inputs larger than L2, a few hundred MB on the
-    device): the command profiler captures are taken from.  Cases: matmul_<mode>_<m>x<k>x<n>[_dA|_dB|_fwdfused|_dAfused],
-    add_<log2n>, relu_<log2n>, sum_<log2n>, cmp_<log2n>, cast_<log2n>, rand_<log2n>, sgdsplit_<rows>x<cols>,
-    colsum_<rows>x<cols>, softmax_<rows>x<cols>, ce_<rows>x<cols>."""
+    device): the command profiler captures are taken from.  Cases: matmul_<mode>_<m>x<k>x<n>[_dA|_dB|_fwdfused|_dAfused]
+    (mode 3xtf32, tf32 or simt), add_<log2n>, relu_<log2n>, sum_<log2n>, cmp_<log2n>, cast_<log2n>, rand_<log2n>,
+    u8_<log2n>, sgdsplit_<rows>x<cols>, colsum_<rows>x<cols>, softmax_<rows>x<cols>, softmaxcols_<rows>x<cols>,
+    ce_<rows>x<cols>, argmax_<rows>x<cols>, gather_<rows>x<cols>."""
     parts = case.split("_")
     kind = parts[0]
     if kind == "matmul":
-        mode = parts[1]
+        mode = "fp32_simt" if parts[1] == "simt" else parts[1]
         m, k, n = (int(v) for v in parts[2].split("x"))
         which = parts[3] if len(parts) > 3 else "fwd"
         A = cb.to_device(rng.standard_normal((m, k)).astype(np.float32)); B = cb.to_device(rng.standard_normal((k, n)).astype(np.float32))
@@ -946,6 +951,30 @@ def run_one_kernel(cb, case, rng):
         fn = dict(sgdsplit=lambda: cb.check(cb.lib.ctk_sgd_update_split_f32(p_.p, g.p, ctypes.c_float(1e-3), i64(rows), i64(cols), i64(cols), split.p, None)),
                   colsum=lambda: cb.ops.colsum(p_))[kind]
         work, unit = dict(sgdsplit=20, colsum=4)[kind] * rows * cols, "GB/s"
+    elif kind == "u8":
+        n = 1 << int(parts[1])
+        src = cb.to_device(rng.integers(0, 256, n).astype(np.uint8), dtype=np.uint8); o = cb.empty((n,))
+        fn = lambda: cb.ops.u8_to_f32(src, 255.0, out=o)
+        work, unit = 5 * n, "GB/s"
+    elif kind in ("softmaxcols", "argmax", "gather"):
+        rows, cols = (int(v) for v in parts[1].split("x"))
+        x = cb.to_device((2 * rng.standard_normal((rows, cols))).astype(np.float32)); y = cb.empty((rows, cols))
+        i64 = ctypes.c_int64
+        if kind == "softmaxcols":
+            fn = lambda: cb.check(cb.lib.ctk_softmax_cols_f32(x.p, y.p, i64(rows), i64(cols), None))
+            work = 8 * rows * cols
+        elif kind == "argmax":
+            out = cb.empty((rows,))
+            fn = lambda: cb.check(cb.lib.ctk_argmax_rows_f32(x.p, i64(rows), i64(cols), ctypes.c_float(-1.0), out.p, None))
+            work = 4 * rows * cols + 4 * rows
+        else:
+            # the general gather of the gradient-shape adjustment: [rows, cols] -> [rows, 1], index 0 on the dimension the target has as 1
+            out = cb.empty((rows,))
+            dshape = (ctypes.c_int64 * 2)(rows, 1)
+            sstride = (ctypes.c_int64 * 2)(cols, 0)
+            fn = lambda: cb.check(cb.lib.ctk_gather_nd_f32(x.p, out.p, 2, dshape, sstride, None))
+            work = 8 * rows
+        unit = "GB/s"
     elif kind in ("softmax", "ce"):
         rows, cols = (int(v) for v in parts[1].split("x"))
         x = cb.to_device((2 * rng.standard_normal((rows, cols))).astype(np.float32)); y = cb.empty((rows, cols))
@@ -1010,6 +1039,9 @@ def main():
     ap.add_argument("--no-comparator", action="store_true", help="skip the vendor-library TF32 GEMM timed for the roofline's `ceilings`")
     ap.add_argument("--dp-mode", default=DEFAULT_DP_MODE, choices=["inplace", "arena", "serial", "sharded"], help="how gradients cross the ranks (N > 1)")
     ap.add_argument("--max-ctas", type=int, default=DEFAULT_MAX_CTAS, help="upper bound on the CTAs of one collective (0: NCCL's choice)")
+    ap.add_argument("--correction", default=DEFAULT_CORRECTION, choices=["tf32", "bf16"],
+                    help="which tensor-core path carries the two correction terms of the fp32-accurate MatMul mode")
+    ap.add_argument("--stable-lr", action="store_true", help="time the headline run itself at lr / batch (weights do not diverge); recorded in config")
     ap.add_argument("--nvls-ctas", type=int, default=0, help="CTAs of a collective's in-switch part (0: NCCL's choice)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours" and args.workload == "mlp":

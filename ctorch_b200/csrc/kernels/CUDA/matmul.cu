@@ -35,6 +35,7 @@
 // CUDA-core path: a plain fp32-FMA tiled kernel for operands without a unit stride, for TF32 mode on
 // operands TMA cannot address in place, and on request (mode FP32_SIMT).
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <math.h>
 #include <cstdlib>
 
@@ -116,14 +117,65 @@ __device__ __forceinline__ float to_tf32_rna(float x) {
     return __uint_as_float(r);
 }
 
-// x viewed as [outer, inner] with row pitch ld_in -> hi, lo of shape [outer, inner] with row pitch
-// ld_out (a multiple of 4, so the copies are addressable by TMA whatever the source pitch was; pad
-// columns are never read: the tensor map's extent stays `inner`).
+// Where the split of an [outer, inner] operand goes: three arrays of pitch `pitch` elements (a multiple
+// of 8, so that rows of every array start on 16 bytes whatever the source pitch was; pad columns are
+// never read: the tensor maps' extent stays `inner`).
+//   correction terms on the TF32 path (variant 0):  hi = tf32(x) and lo = tf32(x - hi), fp32 each;
+//   correction terms on the bf16 path (variant 1):  hi = tf32(x) as fp32, h16 = bf16(hi), l16 = bf16(x - hi).
+// Either way 8 bytes per element: [hi: 4 B][p2: lo 4 B | h16 2 B + l16 2 B].
+struct SplitOut {
+    float* hi = nullptr;
+    void* p2 = nullptr;  // lo (fp32) or h16 (bf16)
+    void* p3 = nullptr;  // l16 (bf16), variant 1 only
+    int variant = 0;
+    int64_t pitch = 0;
+};
+__device__ __forceinline__ uint2 pack_bf16x4(float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 r;
+    r.x = *reinterpret_cast<const uint32_t*>(&a);
+    r.y = *reinterpret_cast<const uint32_t*>(&b);
+    return r;
+}
+// The split of four consecutive elements x, stored at element offset `off` (a multiple of 4) of each array.
+template <bool STREAMING>
+__device__ __forceinline__ void store_split4(const SplitOut& o, int64_t off, float4 x) {
+    float4 h, l;
+    h.x = to_tf32_rna(x.x); h.y = to_tf32_rna(x.y); h.z = to_tf32_rna(x.z); h.w = to_tf32_rna(x.w);
+    l.x = x.x - h.x; l.y = x.y - h.y; l.z = x.z - h.z; l.w = x.w - h.w;  // exact in fp32
+    if (STREAMING) __stcs(reinterpret_cast<float4*>(o.hi + off), h);
+    else *reinterpret_cast<float4*>(o.hi + off) = h;
+    if (o.variant == 0) {
+        l.x = to_tf32_rna(l.x); l.y = to_tf32_rna(l.y); l.z = to_tf32_rna(l.z); l.w = to_tf32_rna(l.w);
+        if (STREAMING) __stcs(reinterpret_cast<float4*>(static_cast<float*>(o.p2) + off), l);
+        else *reinterpret_cast<float4*>(static_cast<float*>(o.p2) + off) = l;
+    } else {
+        const uint2 h16 = pack_bf16x4(h), l16 = pack_bf16x4(l);
+        if (STREAMING) {
+            __stcs(reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(o.p2) + off), h16);
+            __stcs(reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(o.p3) + off), l16);
+        } else {
+            *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(o.p2) + off) = h16;
+            *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(o.p3) + off) = l16;
+        }
+    }
+}
+__device__ __forceinline__ void store_split1(const SplitOut& o, int64_t off, float x) {
+    const float h = to_tf32_rna(x);
+    o.hi[off] = h;
+    if (o.variant == 0) {
+        static_cast<float*>(o.p2)[off] = to_tf32_rna(x - h);
+    } else {
+        static_cast<__nv_bfloat16*>(o.p2)[off] = __float2bfloat16_rn(h);
+        static_cast<__nv_bfloat16*>(o.p3)[off] = __float2bfloat16_rn(x - h);
+    }
+}
+
+// x viewed as [outer, inner] with row pitch ld_in -> its split with row pitch out.pitch.
 // One tile of 256 x 4 vectors per CTA: with this many bytes in flight per CTA and the hardware block
 // scheduler walking memory in order, streaming kernels on B200 run above the plain-copy rate.
 constexpr int SPLIT_THREADS = 256, SPLIT_UNROLL = 4;
-__global__ void __launch_bounds__(SPLIT_THREADS) split_tf32_vec_kernel(const float* __restrict__ x, float* __restrict__ hi, float* __restrict__ lo,
-                                                                       int64_t outer, int64_t inner4, int64_t ld_in, int64_t ld_out) {
+__global__ void __launch_bounds__(SPLIT_THREADS) split_tf32_vec_kernel(const float* __restrict__ x, SplitOut out, int64_t outer, int64_t inner4, int64_t ld_in) {
     const int64_t total = outer * inner4;
     const int64_t base = static_cast<int64_t>(blockIdx.x) * (SPLIT_THREADS * SPLIT_UNROLL) + threadIdx.x;
     float4 v[SPLIT_UNROLL];
@@ -140,20 +192,14 @@ __global__ void __launch_bounds__(SPLIT_THREADS) split_tf32_vec_kernel(const flo
 #pragma unroll
     for (int u = 0; u < SPLIT_UNROLL; ++u) {
         const int64_t i = base + u * SPLIT_THREADS;
-        if (i < total) {
-            float4 h, l;
-            h.x = to_tf32_rna(v[u].x); h.y = to_tf32_rna(v[u].y); h.z = to_tf32_rna(v[u].z); h.w = to_tf32_rna(v[u].w);
-            l.x = to_tf32_rna(v[u].x - h.x); l.y = to_tf32_rna(v[u].y - h.y); l.z = to_tf32_rna(v[u].z - h.z); l.w = to_tf32_rna(v[u].w - h.w);
-            reinterpret_cast<float4*>(hi + r[u] * ld_out)[c4[u]] = h;
-            reinterpret_cast<float4*>(lo + r[u] * ld_out)[c4[u]] = l;
-        }
+        if (i < total) store_split4<false>(out, r[u] * out.pitch + 4 * c4[u], v[u]);
     }
 }
-// The SGD update of a weight matrix with its hi/lo split rewritten in the same pass: p -= g*lr as in
+// The SGD update of a weight matrix with its split rewritten in the same pass: p -= g*lr as in
 // ctk_sgd_update_f32 (one fused multiply-add), then the split of the NEW value for the product the
 // weights enter next.  p viewed [outer, inner] with pitch ld_in, g contiguous.
-__global__ void __launch_bounds__(SPLIT_THREADS) sgd_split_vec_kernel(float* __restrict__ p, const float* __restrict__ g, float lr, float* __restrict__ hi,
-                                                                      float* __restrict__ lo, int64_t outer, int64_t inner4, int64_t ld_in, int64_t ld_out) {
+__global__ void __launch_bounds__(SPLIT_THREADS) sgd_split_vec_kernel(float* __restrict__ p, const float* __restrict__ g, float lr, SplitOut out,
+                                                                      int64_t outer, int64_t inner4, int64_t ld_in) {
     const int64_t total = outer * inner4;
     const int64_t base = static_cast<int64_t>(blockIdx.x) * (SPLIT_THREADS * SPLIT_UNROLL) + threadIdx.x;
     float4 v[SPLIT_UNROLL], d[SPLIT_UNROLL];
@@ -172,26 +218,19 @@ __global__ void __launch_bounds__(SPLIT_THREADS) sgd_split_vec_kernel(float* __r
     for (int u = 0; u < SPLIT_UNROLL; ++u) {
         const int64_t i = base + u * SPLIT_THREADS;
         if (i < total) {
-            float4 x, h, l;
+            float4 x;
             x.x = fmaf(-d[u].x, lr, v[u].x); x.y = fmaf(-d[u].y, lr, v[u].y); x.z = fmaf(-d[u].z, lr, v[u].z); x.w = fmaf(-d[u].w, lr, v[u].w);
-            h.x = to_tf32_rna(x.x); h.y = to_tf32_rna(x.y); h.z = to_tf32_rna(x.z); h.w = to_tf32_rna(x.w);
-            l.x = to_tf32_rna(x.x - h.x); l.y = to_tf32_rna(x.y - h.y); l.z = to_tf32_rna(x.z - h.z); l.w = to_tf32_rna(x.w - h.w);
             *(reinterpret_cast<float4*>(p + r[u] * ld_in) + c4[u]) = x;
-            reinterpret_cast<float4*>(hi + r[u] * ld_out)[c4[u]] = h;
-            reinterpret_cast<float4*>(lo + r[u] * ld_out)[c4[u]] = l;
+            store_split4<false>(out, r[u] * out.pitch + 4 * c4[u], x);
         }
     }
 }
 // Any pitch, any alignment (e.g. the 10-class layer's rows of 40 bytes): one element per thread.
-__global__ void __launch_bounds__(SPLIT_THREADS) split_tf32_scalar_kernel(const float* __restrict__ x, float* __restrict__ hi, float* __restrict__ lo,
-                                                                          int64_t outer, int64_t inner, int64_t ld_in, int64_t ld_out) {
+__global__ void __launch_bounds__(SPLIT_THREADS) split_tf32_scalar_kernel(const float* __restrict__ x, SplitOut out, int64_t outer, int64_t inner, int64_t ld_in) {
     const int64_t total = outer * inner;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
         const int64_t r = i / inner, c = i - r * inner;
-        const float v = __ldg(x + r * ld_in + c);
-        const float h = to_tf32_rna(v);
-        hi[r * ld_out + c] = h;
-        lo[r * ld_out + c] = to_tf32_rna(v - h);
+        store_split1(out, r * out.pitch + c, __ldg(x + r * ld_in + c));
     }
 }
 
@@ -216,13 +255,15 @@ constexpr uint32_t WAIT_LIMIT = 1u << 20;  // polls per bounded wait (each poll 
 // from float64.  2048 keeps every gradient of that step within 1e-4 with room to spare; narrow tiles
 // drain cheaply and use shorter chunks.
 constexpr int chunk_k_for(int bn) { return bn >= 256 ? 2048 : (bn >= 128 ? 512 : 256); }
+// (With the correction terms on the bf16 path an accumulator sees four instructions per 16 terms instead
+// of six -- K = 16 per bf16 instruction -- i.e. two thirds of the truncations: at 4096^3 its error is
+// 1.0e-5 where the TF32 corrections give 1.6e-5 with the same chunks.)
 
 template <int BN, int TERMS>
 struct Cfg {
     static constexpr int A_BYTES = BM * BK * 4;
     static constexpr int B_BYTES = BN * BK * 4;
-    static constexpr int PARTS = (TERMS == 1) ? 1 : 2;           // hi only / hi + lo
-    static constexpr int STAGE_BYTES = PARTS * (A_BYTES + B_BYTES);
+    static constexpr int STAGE_BYTES = (TERMS == 1 ? 1 : 2) * (A_BYTES + B_BYTES);  // fp32 tiles, plus as many bytes of lo / 16-bit copies
     static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;  // two accumulators, power of two
@@ -250,14 +291,12 @@ struct Params {
     int chunk_kb;
     // Epilogue of the fused forms (all optional; whole tiles only): c = [relu](acc + bias[col]), then
     // c *= (mask > 0 ? 1 : 0) with mask an [m, n] array of pitch n (ReLU's backward rule applied to a
-    // gradient product), and the hi/lo split of c written next to it ([m, split_pitch] each) for the
+    // gradient product), and the split of c written next to it (SplitOut: [m, out.pitch] arrays) for the
     // products c enters next.
     const float* bias;
     int relu;
     const float* mask;
-    float* out_hi;
-    float* out_lo;
-    int64_t split_pitch;
+    SplitOut out;  // out.hi == nullptr: no split
 };
 
 // A unit of work: a whole output tile, or one K-half of a tile of the last, partly filled wave.
@@ -390,6 +429,13 @@ __device__ __forceinline__ void tc_mma_tf32(uint32_t d_tmem, uint64_t a_desc, ui
         "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -414,7 +460,13 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 //                 XOR k%4, code 1; TMA writes it with SWIZZLE_128B_ATOM_32B): 4 k-rows (512 B) form
 //                 one atom -> SBO = 512, column groups are 4096 B apart -> LBO = 4096; a K=8 step
 //                 advances the start address by 1024 B.
-constexpr uint32_t kSwizzle128B = 2, kSwizzle128BAtom32B = 1;
+//   16-bit operands (the bf16 copies of the correction terms):
+//   K-major tile  [rows][32 bf16] = 64-byte rows, 64-byte swizzle (16-byte chunks XOR (row/2)%4, code
+//                 4): 8-row groups 512 B apart -> SBO = 512; a K=16 step advances the start address by 32 B.
+//   MN-major tile [k][64 bf16 of M/N] in 64-wide column groups, plain 128-byte swizzle (code 2): 8 k-rows
+//                 (1024 B) form one atom -> SBO = 1024, column groups are 4096 B apart -> LBO = 4096; a
+//                 K=16 step advances the start address by 2048 B.
+constexpr uint32_t kSwizzle128B = 2, kSwizzle128BAtom32B = 1, kSwizzle64B = 4;
 __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t swizzle_code) {
     uint64_t d = 0;
     d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
@@ -425,12 +477,110 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_b
     return d;
 }
 
-// Instruction descriptor for kind::tf32: D fp32 (bits [4,6) = 1), A/B TF32 (format 2 in [7,10) and
-// [10,13)), A/B major-ness in bits 15/16 (1 = MN-major), N >> 3 in [17,23), M >> 4 in [24,29).
-__host__ __device__ constexpr uint32_t make_idesc(int n, bool a_mn_major, bool b_mn_major) {
-    return (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
+// Instruction descriptor: D fp32 (bits [4,6) = 1), A/B format in [7,10) and [10,13) (kind::tf32: 2 =
+// TF32; kind::f16: 1 = BF16), A/B major-ness in bits 15/16 (1 = MN-major), N >> 3 in [17,23), M >> 4
+// in [24,29).
+constexpr uint32_t kFmtTF32 = 2, kFmtBF16 = 1;
+__host__ __device__ constexpr uint32_t make_idesc_fmt(uint32_t fmt, int m, int n, bool a_mn_major, bool b_mn_major) {
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
            (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(n >> 3) << 17) |
-           (static_cast<uint32_t>(BM >> 4) << 24);
+           (static_cast<uint32_t>(m >> 4) << 24);
+}
+__host__ __device__ constexpr uint32_t make_idesc(int n, bool a_mn_major, bool b_mn_major) { return make_idesc_fmt(kFmtTF32, BM, n, a_mn_major, b_mn_major); }
+
+// ---- one pipeline stage: where the operand tiles sit, how they are loaded, how they are multiplied ----
+// TERMS = 1: TF32, the fp32 operands as they are.
+// TERMS = 3: 3xTF32 -- hi = tf32(x), lo = tf32(x - hi) of both operands; lo.hi + hi.lo + hi.hi.
+// TERMS = 2: TF32 + 2 x BF16 -- hi as above, and 16-bit copies h16 = bf16(hi), l16 = bf16(x - hi):
+//            l16.h16 + h16.l16 on the bf16 path (twice the TF32 rate) + hi.hi on the TF32 path.  The two
+//            correction terms are 2^-11 of the main one, so rounding their factors to bf16 (2^-9) leaves
+//            2^-20 of the product, the order of the lo.lo term every variant drops; the stage holds the
+//            same 8 bytes per operand element as TERMS = 3, the tensor pipe does 2 units of work instead of 3.
+// Stage layout (A_B / B_B = bytes of one fp32 tile): TERMS 3: [A hi][A lo][B hi][B lo];
+// TERMS 2: [A hi][A h16][A l16][B hi][B h16][B l16]; TERMS 1: [A][B].
+template <int TERMS, int A_B, int B_B>
+struct StageLayout {
+    static constexpr int BYTES = (TERMS == 1 ? 1 : 2) * (A_B + B_B);
+    static constexpr uint32_t a_hi = 0, a_lo = A_B;                 // TERMS 3
+    static constexpr uint32_t a_h16 = A_B, a_l16 = A_B + A_B / 2;   // TERMS 2
+    static constexpr uint32_t b_hi = (TERMS == 1 ? 1 : 2) * A_B;
+    static constexpr uint32_t b_lo = b_hi + B_B;
+    static constexpr uint32_t b_h16 = b_hi + B_B, b_l16 = b_hi + B_B + B_B / 2;
+};
+
+// The loads of one stage.  maps: a[0..2], b[0..2] = {hi, lo, -} (TERMS 3) or {hi, h16, l16} (TERMS 2).
+// tma(dst, map, c0, c1) issues one tiled copy whose completion is counted on the stage's barrier.
+template <int TERMS, bool A_MN, bool B_MN, int A_ROWS, int B_ROWS, typename Tma>
+__device__ __forceinline__ void load_stage(uint32_t base, const CUtensorMap* const (&ma)[3], const CUtensorMap* const (&mb)[3], int m0, int n0, int k0, Tma tma) {
+    using L = StageLayout<TERMS, A_ROWS * BK * 4, B_ROWS * BK * 4>;
+    auto tile32 = [&](uint32_t dst, const CUtensorMap* map, bool mn, int rows, int r0) {
+        if (mn) {
+#pragma unroll
+            for (int g = 0; g < rows / 32; ++g) tma(dst + g * 4096, map, r0 + 32 * g, k0);
+        } else {
+            tma(dst, map, k0, r0);
+        }
+    };
+    auto tile16 = [&](uint32_t dst, const CUtensorMap* map, bool mn, int rows, int r0) {
+        if (mn) {
+#pragma unroll
+            for (int g = 0; g < rows / 64; ++g) tma(dst + g * 4096, map, r0 + 64 * g, k0);
+        } else {
+            tma(dst, map, k0, r0);
+        }
+    };
+    tile32(base + L::a_hi, ma[0], A_MN, A_ROWS, m0);
+    tile32(base + L::b_hi, mb[0], B_MN, B_ROWS, n0);
+    if (TERMS == 3) {
+        tile32(base + L::a_lo, ma[1], A_MN, A_ROWS, m0);
+        tile32(base + L::b_lo, mb[1], B_MN, B_ROWS, n0);
+    }
+    if (TERMS == 2) {
+        tile16(base + L::a_h16, ma[1], A_MN, A_ROWS, m0);
+        tile16(base + L::a_l16, ma[2], A_MN, A_ROWS, m0);
+        tile16(base + L::b_h16, mb[1], B_MN, B_ROWS, n0);
+        tile16(base + L::b_l16, mb[2], B_MN, B_ROWS, n0);
+    }
+}
+
+// The MMAs of one k-block (32 terms of the sum) into the accumulator at d_tmem; fresh: this k-block
+// opens a new accumulator (its first instruction overwrites).  The small terms go first.
+// mma32 / mma16(d, a_desc, b_desc, idesc, accumulate) issue kind::tf32 / kind::f16.
+template <int TERMS, bool A_MN, bool B_MN, int A_ROWS, int B_ROWS, typename Mma32, typename Mma16>
+__device__ __forceinline__ void issue_kblock(uint32_t base, uint32_t d_tmem, uint32_t idesc32, uint32_t idesc16, bool fresh, Mma32 mma32, Mma16 mma16) {
+    using L = StageLayout<TERMS, A_ROWS * BK * 4, B_ROWS * BK * 4>;
+    constexpr uint32_t a_lbo = A_MN ? 4096u : 0u, b_lbo = B_MN ? 4096u : 0u;
+    uint32_t acc = fresh ? 0u : 1u;
+    if (TERMS == 2) {
+        constexpr uint32_t a_sbo = A_MN ? 1024u : 512u, b_sbo = B_MN ? 1024u : 512u;
+        constexpr uint32_t a_sw = A_MN ? kSwizzle128B : kSwizzle64B, b_sw = B_MN ? kSwizzle128B : kSwizzle64B;
+#pragma unroll
+        for (int ks = 0; ks < BK / 16; ++ks) {
+            const uint32_t a_step = A_MN ? ks * 2048u : ks * 32u, b_step = B_MN ? ks * 2048u : ks * 32u;
+            const uint64_t a_h = make_desc(base + L::a_h16 + a_step, a_lbo, a_sbo, a_sw), a_l = make_desc(base + L::a_l16 + a_step, a_lbo, a_sbo, a_sw);
+            const uint64_t b_h = make_desc(base + L::b_h16 + b_step, b_lbo, b_sbo, b_sw), b_l = make_desc(base + L::b_l16 + b_step, b_lbo, b_sbo, b_sw);
+            mma16(d_tmem, a_l, b_h, idesc16, acc);
+            mma16(d_tmem, a_h, b_l, idesc16, 1u);
+            acc = 1u;
+        }
+    }
+    constexpr uint32_t a_sbo = A_MN ? 512u : 1024u, b_sbo = B_MN ? 512u : 1024u;
+    constexpr uint32_t a_sw = A_MN ? kSwizzle128BAtom32B : kSwizzle128B, b_sw = B_MN ? kSwizzle128BAtom32B : kSwizzle128B;
+#pragma unroll
+    for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+        const uint32_t a_step = A_MN ? ks * 1024u : ks * 32u, b_step = B_MN ? ks * 1024u : ks * 32u;
+        const uint64_t a_hi = make_desc(base + L::a_hi + a_step, a_lbo, a_sbo, a_sw);
+        const uint64_t b_hi = make_desc(base + L::b_hi + b_step, b_lbo, b_sbo, b_sw);
+        if (TERMS == 3) {
+            const uint64_t a_lo = make_desc(base + L::a_lo + a_step, a_lbo, a_sbo, a_sw);
+            const uint64_t b_lo = make_desc(base + L::b_lo + b_step, b_lbo, b_sbo, b_sw);
+            mma32(d_tmem, a_lo, b_hi, idesc32, acc);
+            mma32(d_tmem, a_hi, b_lo, idesc32, 1u);
+            acc = 1u;
+        }
+        mma32(d_tmem, a_hi, b_hi, idesc32, acc);
+        acc = 1u;
+    }
 }
 
 // One 32-column chunk of one accumulator row (this lane's) on its way to memory.
@@ -509,7 +659,7 @@ __device__ __forceinline__ void emit_chunk(const Params& P, bool half, bool firs
             *reinterpret_cast<float4*>(&stage[lane][4 * v]) =
                 make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
         __syncwarp();
-        const bool plain = !add_old && (!last || (P.bias == nullptr && !P.relu && P.mask == nullptr && P.out_hi == nullptr));
+        const bool plain = !add_old && (!last || (P.bias == nullptr && !P.relu && P.mask == nullptr && P.out.hi == nullptr));
         if (plain && last) {
 #pragma unroll
             for (int i = 0; i < 8; ++i)
@@ -519,8 +669,8 @@ __device__ __forceinline__ void emit_chunk(const Params& P, bool half, bool firs
             for (int i = 0; i < 8; ++i)
                 if (i * 4 + sub < rows_left) *reinterpret_cast<float4*>(cdst + i * cstep) = *reinterpret_cast<const float4*>(&stage[i * 4 + sub][c4]);
         } else {
-            const bool biased = last && P.bias != nullptr, relu = last && P.relu, masked = last && P.mask != nullptr, split = last && P.out_hi != nullptr;
-            const int64_t soff = (row_base + sub) * P.split_pitch + col0 + c4, sstep = 4 * P.split_pitch;
+            const bool biased = last && P.bias != nullptr, relu = last && P.relu, masked = last && P.mask != nullptr, split = last && P.out.hi != nullptr;
+            const int64_t soff = (row_base + sub) * P.out.pitch + col0 + c4, sstep = 4 * P.out.pitch;
             float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
             if (biased) bv = __ldg(reinterpret_cast<const float4*>(P.bias + col0 + c4));  // Add_BASIC_kernel's [N,H] + [H]
 #pragma unroll
@@ -542,13 +692,7 @@ __device__ __forceinline__ void emit_chunk(const Params& P, bool half, bool firs
                 }
                 if (last) __stcs(reinterpret_cast<float4*>(cdst + i * cstep), x);
                 else *reinterpret_cast<float4*>(cdst + i * cstep) = x;  // read again by the next chunk: keep it in L2
-                if (split) {
-                    float4 h, l;
-                    h.x = to_tf32_rna(x.x); h.y = to_tf32_rna(x.y); h.z = to_tf32_rna(x.z); h.w = to_tf32_rna(x.w);
-                    l.x = to_tf32_rna(x.x - h.x); l.y = to_tf32_rna(x.y - h.y); l.z = to_tf32_rna(x.z - h.z); l.w = to_tf32_rna(x.w - h.w);
-                    __stcs(reinterpret_cast<float4*>(P.out_hi + soff + i * sstep), h);
-                    __stcs(reinterpret_cast<float4*>(P.out_lo + soff + i * sstep), l);
-                }
+                if (split) store_split4<true>(P.out, soff + i * sstep, x);
             }
         }
         __syncwarp();  // the stage is free again
@@ -568,11 +712,7 @@ __device__ __forceinline__ void emit_chunk(const Params& P, bool half, bool firs
                 if (P.mask != nullptr) x *= P.mask[row * P.n + col0 + v] > 0.0f ? 1.0f : 0.0f;
             }
             crow[col0 + v] = x;
-            if (last && P.out_hi != nullptr) {
-                const float h = to_tf32_rna(x);
-                P.out_hi[row * P.split_pitch + col0 + v] = h;
-                P.out_lo[row * P.split_pitch + col0 + v] = to_tf32_rna(x - h);
-            }
+            if (last && P.out.hi != nullptr) store_split1(P.out, row * P.out.pitch + col0 + v, x);
         }
 }
 
@@ -582,8 +722,8 @@ __device__ __forceinline__ void emit_chunk(const Params& P, bool half, bool firs
 // {32, 32} per 32-wide column group for an MN-major one.
 template <int BN, int TERMS, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(THREADS, 1)
-tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
-                      const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ CUtensorMap map_a1, const __grid_constant__ CUtensorMap map_a2,
+                      const __grid_constant__ CUtensorMap map_b0, const __grid_constant__ CUtensorMap map_b1, const __grid_constant__ CUtensorMap map_b2,
                       const Params P) {
     using C = Cfg<BN, TERMS>;
     extern __shared__ uint8_t smem_raw[];
@@ -598,9 +738,9 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
     auto empty_bar = [&](int s) { return bar0 + 8u * (8 + s); };
     auto tfull_bar = [&](int a) { return bar0 + 8u * (16 + a); };
     auto tempty_bar = [&](int a) { return bar0 + 8u * (18 + a); };
-    // stage layout: [A_hi][A_lo?][B_hi][B_lo?]
-    auto a_addr = [&](int s, int part) { return smem_base + s * C::STAGE_BYTES + part * C::A_BYTES; };
-    auto b_addr = [&](int s, int part) { return smem_base + s * C::STAGE_BYTES + C::PARTS * C::A_BYTES + part * C::B_BYTES; };
+    auto stage_addr = [&](int s) { return smem_base + s * C::STAGE_BYTES; };  // (layout inside: StageLayout)
+    const CUtensorMap* const maps_a[3] = {&map_a0, &map_a1, &map_a2};
+    const CUtensorMap* const maps_b[3] = {&map_b0, &map_b1, &map_b2};
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -608,9 +748,10 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        prefetch_tmap(&map_a_hi);
-        prefetch_tmap(&map_b_hi);
-        if (TERMS == 3) { prefetch_tmap(&map_a_lo); prefetch_tmap(&map_b_lo); }
+        prefetch_tmap(&map_a0);
+        prefetch_tmap(&map_b0);
+        if (TERMS >= 2) { prefetch_tmap(&map_a1); prefetch_tmap(&map_b1); }
+        if (TERMS == 2) { prefetch_tmap(&map_a2); prefetch_tmap(&map_b2); }
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(&tmem_base_slot), C::TMEM_COLS);
@@ -638,24 +779,9 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
                 for (int kb = U.kb0; kb < U.kb1; ++kb) {
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, &abort_flag, 0x100 | stage)) { ok = false; break; }
                     mbar_expect_tx(full_bar(stage), C::STAGE_BYTES);
-                    const int k0 = kb * BK;
-#pragma unroll
-                    for (int part = 0; part < C::PARTS; ++part) {
-                        const CUtensorMap* ma = part ? &map_a_lo : &map_a_hi;
-                        const CUtensorMap* mb = part ? &map_b_lo : &map_b_hi;
-                        if (A_MN) {
-#pragma unroll
-                            for (int g = 0; g < BM / 32; ++g) tma_load_2d(a_addr(stage, part) + g * 4096, ma, full_bar(stage), m0 + 32 * g, k0);
-                        } else {
-                            tma_load_2d(a_addr(stage, part), ma, full_bar(stage), k0, m0);
-                        }
-                        if (B_MN) {
-#pragma unroll
-                            for (int g = 0; g < BN / 32; ++g) tma_load_2d(b_addr(stage, part) + g * 4096, mb, full_bar(stage), n0 + 32 * g, k0);
-                        } else {
-                            tma_load_2d(b_addr(stage, part), mb, full_bar(stage), k0, n0);
-                        }
-                    }
+                    const uint32_t fb = full_bar(stage);
+                    load_stage<TERMS, A_MN, B_MN, BM, BN>(stage_addr(stage), maps_a, maps_b, m0, n0, kb * BK,
+                                                         [&](uint32_t dst, const CUtensorMap* map, int c0, int c1) { tma_load_2d(dst, map, fb, c0, c1); });
                     ++issued;
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -674,7 +800,7 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
     } else if (warp == 1) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(BN, A_MN, B_MN);
+            constexpr uint32_t idesc = make_idesc(BN, A_MN, B_MN), idesc16 = make_idesc_fmt(kFmtBF16, BM, BN, A_MN, B_MN);
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
@@ -691,26 +817,7 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid
                 for (int kb = c0; kb < c1; ++kb) {
                     if (!mbar_wait(full_bar(stage), phase, &abort_flag, 0x200 | stage)) { ok = false; break; }
                     tc_fence_after();
-#pragma unroll
-                    for (int ks = 0; ks < BK / UMMA_K; ++ks) {
-                        const uint32_t a_step = A_MN ? ks * 1024u : ks * 32u;
-                        const uint32_t b_step = B_MN ? ks * 1024u : ks * 32u;
-                        const uint32_t a_lbo = A_MN ? 4096u : 0u, b_lbo = B_MN ? 4096u : 0u;
-                        const uint32_t a_sbo = A_MN ? 512u : 1024u, b_sbo = B_MN ? 512u : 1024u;
-                        const uint32_t a_sw = A_MN ? kSwizzle128BAtom32B : kSwizzle128B, b_sw = B_MN ? kSwizzle128BAtom32B : kSwizzle128B;
-                        const uint64_t a_hi = make_desc(a_addr(stage, 0) + a_step, a_lbo, a_sbo, a_sw);
-                        const uint64_t b_hi = make_desc(b_addr(stage, 0) + b_step, b_lbo, b_sbo, b_sw);
-                        const uint32_t first = (kb > c0 || ks > 0) ? 1u : 0u;
-                        if (TERMS == 3) {
-                            const uint64_t a_lo = make_desc(a_addr(stage, 1) + a_step, a_lbo, a_sbo, a_sw);
-                            const uint64_t b_lo = make_desc(b_addr(stage, 1) + b_step, b_lbo, b_sbo, b_sw);
-                            tc_mma_tf32(d_tmem, a_lo, b_hi, idesc, first);  // small terms first
-                            tc_mma_tf32(d_tmem, a_hi, b_lo, idesc, 1u);
-                            tc_mma_tf32(d_tmem, a_hi, b_hi, idesc, 1u);
-                        } else {
-                            tc_mma_tf32(d_tmem, a_hi, b_hi, idesc, first);
-                        }
-                    }
+                    issue_kblock<TERMS, A_MN, B_MN, BM, BN>(stage_addr(stage), d_tmem, idesc, idesc16, kb == c0, tc_mma_tf32, tc_mma_f16);
                     tc_commit(empty_bar(stage));  // arrives when the MMAs above have read the stage
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -795,8 +902,7 @@ template <int TERMS>
 struct Cfg {
     static constexpr int A_BYTES = BM * BK * 4;
     static constexpr int B_BYTES = BN_CTA * BK * 4;
-    static constexpr int PARTS = (TERMS == 1) ? 1 : 2;
-    static constexpr int STAGE_BYTES = PARTS * (A_BYTES + B_BYTES);  // per CTA
+    static constexpr int STAGE_BYTES = (TERMS == 1 ? 1 : 2) * (A_BYTES + B_BYTES);  // per CTA
     static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int TMEM_COLS = 512;  // two 256-column accumulators
@@ -873,18 +979,21 @@ __device__ __forceinline__ void tc_mma_tf32_pair(uint32_t d_tmem, uint64_t a_des
         "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
-// M = 256 across the pair.
-__host__ __device__ constexpr uint32_t make_idesc_pair(bool a_mn_major, bool b_mn_major) {
-    return (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
-           (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(BN >> 3) << 17) |
-           (static_cast<uint32_t>((2 * BM) >> 4) << 24);
+__device__ __forceinline__ void tc_mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// M = 256 across the pair.
+__host__ __device__ constexpr uint32_t make_idesc_pair(bool a_mn_major, bool b_mn_major) { return make_idesc_fmt(kFmtTF32, 2 * BM, BN, a_mn_major, b_mn_major); }
 
 // P.tiles_m / P.tiles_n count 256 x 256 tiles.  Grid = 2 x number of resident clusters.
 template <int TERMS, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(THREADS, 1)
-tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
-                           const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_constant__ CUtensorMap map_a1, const __grid_constant__ CUtensorMap map_a2,
+                           const __grid_constant__ CUtensorMap map_b0, const __grid_constant__ CUtensorMap map_b1, const __grid_constant__ CUtensorMap map_b2,
                            const Params P) {
     using C = Cfg<TERMS>;
     extern __shared__ uint8_t smem_raw[];
@@ -900,8 +1009,9 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
     auto empty_bar = [&](int s) { return bar0 + 8u * (8 + s); };
     auto tfull_bar = [&](int a) { return bar0 + 8u * (16 + a); };
     auto tempty_bar = [&](int a) { return bar0 + 8u * (18 + a); };
-    auto a_addr = [&](int s, int part) { return smem_base + s * C::STAGE_BYTES + part * C::A_BYTES; };
-    auto b_addr = [&](int s, int part) { return smem_base + s * C::STAGE_BYTES + C::PARTS * C::A_BYTES + part * C::B_BYTES; };
+    auto stage_addr = [&](int s) { return smem_base + s * C::STAGE_BYTES; };  // (layout inside: StageLayout)
+    const CUtensorMap* const maps_a[3] = {&map_a0, &map_a1, &map_a2};
+    const CUtensorMap* const maps_b[3] = {&map_b0, &map_b1, &map_b2};
     const uint32_t peer_abort = map_to_cta(smem_u32(const_cast<int*>(&abort_flag)), rank ^ 1u);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -910,9 +1020,10 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 8); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        prefetch_tmap(&map_a_hi);
-        prefetch_tmap(&map_b_hi);
-        if (TERMS == 3) { prefetch_tmap(&map_a_lo); prefetch_tmap(&map_b_lo); }
+        prefetch_tmap(&map_a0);
+        prefetch_tmap(&map_b0);
+        if (TERMS >= 2) { prefetch_tmap(&map_a1); prefetch_tmap(&map_b1); }
+        if (TERMS == 2) { prefetch_tmap(&map_a2); prefetch_tmap(&map_b2); }
     }
     if (warp == 1) {
         tmem_alloc2(smem_u32(&tmem_base_slot), C::TMEM_COLS);
@@ -951,24 +1062,8 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, &abort_flag, 0x500 | stage)) { ok = false; break; }
                     if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * C::STAGE_BYTES);
                     const uint32_t fb = map_to_cta(full_bar(stage), 0);
-                    const int k0 = kb * BK;
-#pragma unroll
-                    for (int part = 0; part < C::PARTS; ++part) {
-                        const CUtensorMap* ma = part ? &map_a_lo : &map_a_hi;
-                        const CUtensorMap* mb = part ? &map_b_lo : &map_b_hi;
-                        if (A_MN) {
-#pragma unroll
-                            for (int g = 0; g < BM / 32; ++g) tma_load_2d_pair(a_addr(stage, part) + g * 4096, ma, fb, m0 + 32 * g, k0);
-                        } else {
-                            tma_load_2d_pair(a_addr(stage, part), ma, fb, k0, m0);
-                        }
-                        if (B_MN) {
-#pragma unroll
-                            for (int g = 0; g < BN_CTA / 32; ++g) tma_load_2d_pair(b_addr(stage, part) + g * 4096, mb, fb, n0 + 32 * g, k0);
-                        } else {
-                            tma_load_2d_pair(b_addr(stage, part), mb, fb, k0, n0);
-                        }
-                    }
+                    load_stage<TERMS, A_MN, B_MN, BM, BN_CTA>(stage_addr(stage), maps_a, maps_b, m0, n0, kb * BK,
+                                                             [&](uint32_t dst, const CUtensorMap* map, int c0, int c1) { tma_load_2d_pair(dst, map, fb, c0, c1); });
                     ++issued;
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -992,7 +1087,7 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
     } else if (warp == 1) {
         // ------------------------------ MMA issuer (rank 0 only) ------------------------------
         if (lane == 0 && rank == 0) {
-            constexpr uint32_t idesc = make_idesc_pair(A_MN, B_MN);
+            constexpr uint32_t idesc = make_idesc_pair(A_MN, B_MN), idesc16 = make_idesc_fmt(kFmtBF16, 2 * BM, BN, A_MN, B_MN);
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
@@ -1011,26 +1106,7 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a_hi, const _
                 for (int kb = c0; kb < c1; ++kb) {
                     if (!mbar_wait(full_bar(stage), phase, &abort_flag, 0x600 | stage)) { ok = false; break; }
                     tc_fence_after();
-#pragma unroll
-                    for (int ks = 0; ks < BK / UMMA_K; ++ks) {
-                        const uint32_t a_step = A_MN ? ks * 1024u : ks * 32u;
-                        const uint32_t b_step = B_MN ? ks * 1024u : ks * 32u;
-                        const uint32_t a_lbo = A_MN ? 4096u : 0u, b_lbo = B_MN ? 4096u : 0u;
-                        const uint32_t a_sbo = A_MN ? 512u : 1024u, b_sbo = B_MN ? 512u : 1024u;
-                        const uint32_t a_sw = A_MN ? kSwizzle128BAtom32B : kSwizzle128B, b_sw = B_MN ? kSwizzle128BAtom32B : kSwizzle128B;
-                        const uint64_t a_hi = make_desc(a_addr(stage, 0) + a_step, a_lbo, a_sbo, a_sw);
-                        const uint64_t b_hi = make_desc(b_addr(stage, 0) + b_step, b_lbo, b_sbo, b_sw);
-                        const uint32_t first = (kb > c0 || ks > 0) ? 1u : 0u;
-                        if (TERMS == 3) {
-                            const uint64_t a_lo = make_desc(a_addr(stage, 1) + a_step, a_lbo, a_sbo, a_sw);
-                            const uint64_t b_lo = make_desc(b_addr(stage, 1) + b_step, b_lbo, b_sbo, b_sw);
-                            tc_mma_tf32_pair(d_tmem, a_lo, b_hi, idesc, first);  // small terms first
-                            tc_mma_tf32_pair(d_tmem, a_hi, b_lo, idesc, 1u);
-                            tc_mma_tf32_pair(d_tmem, a_hi, b_hi, idesc, 1u);
-                        } else {
-                            tc_mma_tf32_pair(d_tmem, a_hi, b_hi, idesc, first);
-                        }
-                    }
+                    issue_kblock<TERMS, A_MN, B_MN, BM, BN_CTA>(stage_addr(stage), d_tmem, idesc, idesc16, kb == c0, tc_mma_tf32_pair, tc_mma_f16_pair);
                     tc_commit_both(empty_bar(stage));  // both CTAs' stage is free once these MMAs have read it
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -1162,6 +1238,23 @@ ctk_status make_map(CUtensorMap* map, const float* base, int64_t inner, int64_t 
     return CTK_OK;
 }
 
+// The same operand as bf16 ([outer, ld] elements of 2 bytes): box {32, box_outer} with the 64-byte
+// swizzle for a K-major operand (a k-block is 32 elements = 64 bytes), {64, 32} with the 128-byte
+// swizzle per 64-wide column group for an MN-major one.
+ctk_status make_map16(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int64_t ld, int box_outer, bool mn_major) {
+    EncodeTiledFn enc;
+    ctk_status st = get_encoder(&enc);
+    if (st) return st;
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+    cuuint32_t box[2] = {mn_major ? 64u : 32u, static_cast<cuuint32_t>(mn_major ? 32 : box_outer)};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     mn_major ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(CTK_ERR_CUDA, "cuTensorMapEncodeTiled (bf16) failed with code " + std::to_string(static_cast<int>(r)));
+    return CTK_OK;
+}
+
 // One operand as the tensor-core path sees it.
 struct Operand {
     const float* p;
@@ -1177,7 +1270,7 @@ bool tma_ok(const Operand& o) {
 }
 
 template <int BN, int TERMS, bool A_MN, bool B_MN>
-ctk_status launch_tc(const CUtensorMap maps[4], const Params& P, cudaStream_t st) {
+ctk_status launch_tc(const CUtensorMap maps[6], const Params& P, cudaStream_t st) {
     using C = Cfg<BN, TERMS>;
     auto kernel = tcgen05_matmul_kernel<BN, TERMS, A_MN, B_MN>;
     static ctk::PerDeviceOnce attr;  // the attribute belongs to the (kernel, device) pair
@@ -1185,13 +1278,13 @@ ctk_status launch_tc(const CUtensorMap maps[4], const Params& P, cudaStream_t st
     const int units = P.whole_tiles + 2 * (P.tiles_m * P.tiles_n - P.whole_tiles);
     const int sms = ctk::sm_count();
     const int grid = units < sms ? units : sms;  // persistent: one CTA per SM
-    kernel<<<grid, THREADS, C::SMEM_BYTES, st>>>(maps[0], maps[1], maps[2], maps[3], P);
+    kernel<<<grid, THREADS, C::SMEM_BYTES, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], P);
     CTK_LAUNCH_CHECK("tcgen05_matmul_kernel");
     return CTK_OK;
 }
 
 template <int BN, int TERMS>
-ctk_status launch_tc_major(bool a_mn, bool b_mn, const CUtensorMap maps[4], const Params& P, cudaStream_t st) {
+ctk_status launch_tc_major(bool a_mn, bool b_mn, const CUtensorMap maps[6], const Params& P, cudaStream_t st) {
     if (a_mn && b_mn) return launch_tc<BN, TERMS, true, true>(maps, P, st);
     if (a_mn) return launch_tc<BN, TERMS, true, false>(maps, P, st);
     if (b_mn) return launch_tc<BN, TERMS, false, true>(maps, P, st);
@@ -1207,7 +1300,7 @@ ctk_status resident_pairs(int* out);
 // ---- CTA-pair launch ----
 // Resident clusters of two per device, asked of the driver once (the kernels differ only in code, not in resources).
 template <int TERMS, bool A_MN, bool B_MN>
-ctk_status launch_pair(const CUtensorMap maps[4], const Params& P, cudaStream_t st) {
+ctk_status launch_pair(const CUtensorMap maps[6], const Params& P, cudaStream_t st) {
     using C = pair::Cfg<TERMS>;
     auto kernel = pair::tcgen05_matmul_pair_kernel<TERMS, A_MN, B_MN>;
     static int max_clusters[64] = {0};
@@ -1236,7 +1329,7 @@ ctk_status launch_pair(const CUtensorMap maps[4], const Params& P, cudaStream_t 
     const int units = P.whole_tiles + 2 * (P.tiles_m * P.tiles_n - P.whole_tiles);
     const int clusters = units < max_clusters[dev] ? units : max_clusters[dev];
     cfg.gridDim = dim3(2 * static_cast<unsigned>(clusters));
-    CTK_CUDA(cudaLaunchKernelEx(&cfg, kernel, maps[0], maps[1], maps[2], maps[3], P));
+    CTK_CUDA(cudaLaunchKernelEx(&cfg, kernel, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], P));
     CTK_LAUNCH_CHECK("tcgen05_matmul_pair_kernel");
     return CTK_OK;
 }
@@ -1271,7 +1364,7 @@ ctk_status resident_pairs(int* out) {
 }
 
 template <int TERMS>
-ctk_status launch_pair_major(bool a_mn, bool b_mn, const CUtensorMap maps[4], const Params& P, cudaStream_t st) {
+ctk_status launch_pair_major(bool a_mn, bool b_mn, const CUtensorMap maps[6], const Params& P, cudaStream_t st) {
     if (a_mn && b_mn) return launch_pair<TERMS, true, true>(maps, P, st);
     if (a_mn) return launch_pair<TERMS, true, false>(maps, P, st);
     if (b_mn) return launch_pair<TERMS, false, true>(maps, P, st);
@@ -1299,7 +1392,7 @@ bool classify(const float* p, int64_t mn, int64_t k, int64_t s_mn, int64_t s_k, 
 constexpr int SK_MAXK = 16, SK_THREADS = 128, SK_ROWS = 32;
 __global__ void __launch_bounds__(SK_THREADS) skinny_k_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ c,
                                                              int64_t m, int64_t n, int k, const float* __restrict__ mask,
-                                                             float* __restrict__ out_hi, float* __restrict__ out_lo, int64_t split_pitch) {
+                                                             SplitOut out) {
     const int64_t j0 = (static_cast<int64_t>(blockIdx.x) * SK_THREADS + threadIdx.x) * 4;
     const bool live = j0 < n;  // (no early return: every thread takes part in staging A)
     float bw[4][SK_MAXK];
@@ -1343,13 +1436,7 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_k_kernel(const float* __res
                 x.z *= y[g].z > 0.0f ? 1.0f : 0.0f; x.w *= y[g].w > 0.0f ? 1.0f : 0.0f;
             }
             __stcs(reinterpret_cast<float4*>(c + r * n + j0), x);
-            if (out_hi != nullptr) {
-                float4 h, l4;
-                h.x = to_tf32_rna(x.x); h.y = to_tf32_rna(x.y); h.z = to_tf32_rna(x.z); h.w = to_tf32_rna(x.w);
-                l4.x = to_tf32_rna(x.x - h.x); l4.y = to_tf32_rna(x.y - h.y); l4.z = to_tf32_rna(x.z - h.z); l4.w = to_tf32_rna(x.w - h.w);
-                __stcs(reinterpret_cast<float4*>(out_hi + r * split_pitch + j0), h);
-                __stcs(reinterpret_cast<float4*>(out_lo + r * split_pitch + j0), l4);
-            }
+            if (out.hi != nullptr) store_split4<true>(out, r * out.pitch + j0, x);
         }
     }
 }
@@ -1363,6 +1450,15 @@ static bool skinny_k_ok(const float* a, const float* b, const float* c, int64_t 
 }
 
 int g_default_mode = CTK_MATMUL_3XTF32;
+// Which tensor-core path carries the two correction terms of mode CTK_MATMUL_3XTF32:
+// 0 = TF32 (three TF32 products), 1 = bf16 (one TF32 product + two bf16 products).
+// (CTORCH_MATMUL_CORRECTION=tf32 | bf16 in the environment sets the start value.)
+int g_correction = [] {
+    const char* e = std::getenv("CTORCH_MATMUL_CORRECTION");
+    if (e && e[0] == 't') return 0;
+    if (e && e[0] == 'b') return 1;
+    return 0;
+}();
 int g_pairing = 0;  // 0: CTA pairs where the shape allows, 1: single-CTA kernel only
 int g_split_tail = 1;  // 1: K-halves for the tiles of a last wave that fills at most half the machine
 // ---- optional per-launch timing of the tensor-core kernel ----
@@ -1415,6 +1511,23 @@ int choose_path(const float* a, const float* b, int64_t m, int64_t n, int64_t k,
     if (ob) *ob = B;
     return 0;
 }
+
+// The three arrays of a split inside one buffer (256-byte aligned start, `outer` rows of `pitch` elements).
+SplitOut split_layout(void* buf, int64_t outer, int64_t pitch, int variant) {
+    SplitOut o;
+    o.hi = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(buf) + 255u) & ~static_cast<uintptr_t>(255u));
+    o.variant = variant;
+    o.pitch = pitch;
+    if (variant == 0) {
+        o.p2 = o.hi + outer * pitch;
+    } else {
+        __nv_bfloat16* h16 = reinterpret_cast<__nv_bfloat16*>(o.hi + outer * pitch);
+        o.p2 = h16;
+        o.p3 = h16 + outer * pitch;
+    }
+    return o;
+}
+int64_t split_pitch_of(int64_t inner) { return (inner + 7) / 8 * 8; }
 
 // ---- flags of the K-halved tiles ------------------------------------------------------------------
 // A launch with halved tiles needs 8 words per such tile (2 CTAs x 4 epilogue warps), zero when it
@@ -1484,6 +1597,18 @@ ctk_status ctk_set_matmul_mode(int mode) {
 }
 int ctk_get_matmul_mode(void) { return g_default_mode; }
 
+// Which path carries the two correction terms of the fp32-accurate mode (CTK_MATMUL_3XTF32): 0 = TF32
+// (lo.hi + hi.lo + hi.hi, all TF32), 1 = bf16 (l16.h16 + h16.l16 in bf16 + hi.hi in TF32).  Process-wide;
+// a kept split made under the other setting is not reused (its valid flag holds the setting's tag).
+ctk_status ctk_set_matmul_correction(int bf16) {
+    CTK_REQUIRE(bf16 == 0 || bf16 == 1, "ctk_set_matmul_correction: 0 (TF32 correction terms) or 1 (bf16 correction terms)");
+    g_correction = bf16;
+    return CTK_OK;
+}
+int ctk_get_matmul_correction(void) { return g_correction; }
+// The value a kept split's valid flag has when the buffer holds a split made under the current setting.
+int ctk_matmul_split_tag(void) { return 1 + g_correction; }
+
 ctk_status ctk_set_matmul_tail_split(int on) {
     CTK_REQUIRE(on == 0 || on == 1, "ctk_set_matmul_tail_split: 0 or 1");
     g_split_tail = on;
@@ -1496,10 +1621,10 @@ ctk_status ctk_set_matmul_pairing(int pairing) {
     return CTK_OK;
 }
 
-// Split copies have their contiguous extent padded to a multiple of 4 floats; which extent that is
+// Split copies have their contiguous extent padded to a multiple of 8 elements; which extent that is
 // depends on the operand's major-ness, so the larger of the two possibilities is reserved.
 static int64_t padded_elems(int64_t mn, int64_t k) {
-    const int64_t a = mn * ((k + 3) / 4 * 4), b = k * ((mn + 3) / 4 * 4);
+    const int64_t a = mn * ((k + 7) / 8 * 8), b = k * ((mn + 7) / 8 * 8);
     return a > b ? a : b;
 }
 size_t ctk_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k, int mode) {
@@ -1602,13 +1727,10 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
 
     if (fe.bias == nullptr && !fe.relu && skinny_k_ok(a, b, c, m, n, k, sa0, sa1, sb0, sb1, md) &&
         (fe.mask == nullptr || (reinterpret_cast<uintptr_t>(fe.mask) & 15u) == 0)) {
-        float *hi = nullptr, *lo = nullptr;
-        if (fe.c_split) {
-            hi = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(fe.c_split) + 255u) & ~static_cast<uintptr_t>(255u));
-            lo = hi + m * n;  // (pitch = n, a multiple of 4)
-        }
+        SplitOut so;
+        if (fe.c_split) so = split_layout(fe.c_split, m, split_pitch_of(n), g_correction);
         dim3 grid(static_cast<unsigned>((n / 4 + SK_THREADS - 1) / SK_THREADS), static_cast<unsigned>((m + SK_ROWS - 1) / SK_ROWS));
-        skinny_k_kernel<<<grid, SK_THREADS, 0, st>>>(a, b, c, m, n, static_cast<int>(k), fe.mask, hi, lo, n);
+        skinny_k_kernel<<<grid, SK_THREADS, 0, st>>>(a, b, c, m, n, static_cast<int>(k), fe.mask, so);
         CTK_LAUNCH_CHECK("skinny_k_kernel");
         return CTK_OK;
     }
@@ -1624,62 +1746,76 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
         return CTK_OK;
     }
 
-    const int terms = (md == CTK_MATMUL_3XTF32) ? 3 : 1;
-    const float *a_hi = A.p, *a_lo = A.p, *b_hi = B.p, *b_lo = B.p;
+    const int variant = g_correction;
+    const int terms = (md == CTK_MATMUL_3XTF32) ? (variant == 1 ? 2 : 3) : 1;
+    const int tag = 1 + variant;  // what a kept split's valid flag says when it holds this variant's split
+    SplitOut sa, sb;
     int64_t a_ld = A.ld, b_ld = B.ld;
-    if (terms == 3) {
-        const int64_t a_pitch = (A.inner() + 3) / 4 * 4, b_pitch = (B.inner() + 3) / 4 * 4;
-        float *ah, *al, *bh, *bl;
-        auto aligned256 = [](void* p) { return reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(p) + 255u) & ~static_cast<uintptr_t>(255u)); };
-        if (!ka.buf || !kb.buf) {
+    if (terms != 1) {
+        const int64_t a_pitch = split_pitch_of(A.inner()), b_pitch = split_pitch_of(B.inner());
+        void *abuf = ka.buf, *bbuf = kb.buf;
+        if (!abuf || !bbuf) {
             void* ws = workspace;
             if (!ws) {
                 ctk_status rc = device_scratch(1, ctk_matmul_workspace_bytes(m, n, k, md), &ws);
                 if (rc) return rc;
             }
-            ah = aligned256(ws);
-            al = ah + A.outer() * a_pitch;
-            bh = al + A.outer() * a_pitch;
-            bl = bh + B.outer() * b_pitch;
+            const SplitOut first = split_layout(ws, A.outer(), a_pitch, variant);
+            if (!abuf) abuf = ws;
+            if (!bbuf) bbuf = first.hi + 2 * A.outer() * a_pitch;  // behind A's 8 bytes per element
         }
-        if (ka.buf) { ah = aligned256(ka.buf); al = ah + A.outer() * a_pitch; }
-        if (kb.buf) { bh = aligned256(kb.buf); bl = bh + B.outer() * b_pitch; }
-        auto split = [&](const tc::Operand& O, float* h, float* l, int64_t pitch) -> ctk_status {
+        sa = split_layout(abuf, A.outer(), a_pitch, variant);
+        sb = split_layout(bbuf, B.outer(), b_pitch, variant);
+        auto split = [&](const tc::Operand& O, const SplitOut& out) -> ctk_status {
             const bool vec = (reinterpret_cast<uintptr_t>(O.p) & 15u) == 0 && O.ld % 4 == 0 && O.inner() % 4 == 0;
             if (vec) {
                 const int64_t total = O.outer() * (O.inner() / 4);
                 const int64_t per_cta = SPLIT_THREADS * SPLIT_UNROLL;
-                split_tf32_vec_kernel<<<static_cast<unsigned>((total + per_cta - 1) / per_cta), SPLIT_THREADS, 0, st>>>(O.p, h, l, O.outer(), O.inner() / 4, O.ld, pitch);
+                split_tf32_vec_kernel<<<static_cast<unsigned>((total + per_cta - 1) / per_cta), SPLIT_THREADS, 0, st>>>(O.p, out, O.outer(), O.inner() / 4, O.ld);
             } else {
-                split_tf32_scalar_kernel<<<ctk_stream_grid(O.outer() * O.inner(), SPLIT_THREADS, 8), SPLIT_THREADS, 0, st>>>(O.p, h, l, O.outer(), O.inner(), O.ld, pitch);
+                split_tf32_scalar_kernel<<<ctk_stream_grid(O.outer() * O.inner(), SPLIT_THREADS, 8), SPLIT_THREADS, 0, st>>>(O.p, out, O.outer(), O.inner(), O.ld);
             }
             CTK_LAUNCH_CHECK("split_tf32_kernel");
             return CTK_OK;
         };
         ctk_status rc2;
-        if (!(ka.buf && ka.valid && *ka.valid)) {
-            if ((rc2 = split(A, ah, al, a_pitch))) return rc2;
-            if (ka.buf && ka.valid) *ka.valid = 1;
+        if (!(ka.buf && ka.valid && *ka.valid == tag)) {
+            if ((rc2 = split(A, sa))) return rc2;
+            if (ka.buf && ka.valid) *ka.valid = tag;
         }
-        if (!(kb.buf && kb.valid && *kb.valid)) {
-            if ((rc2 = split(B, bh, bl, b_pitch))) return rc2;
-            if (kb.buf && kb.valid) *kb.valid = 1;
+        if (!(kb.buf && kb.valid && *kb.valid == tag)) {
+            if ((rc2 = split(B, sb))) return rc2;
+            if (kb.buf && kb.valid) *kb.valid = tag;
         }
-        a_hi = ah; a_lo = al; b_hi = bh; b_lo = bl;
         a_ld = a_pitch; b_ld = b_pitch;
     }
 
     const int bn = tc::pick_bn(n);
     // Two CTAs per 256 x 256 tile once there is more than one 128-row block to pair up.
     const bool paired = (g_pairing == 0) && bn == 256 && m > tc::BM;
-    CUtensorMap maps[4];
+    CUtensorMap maps[6];  // a: {hi | x, lo | h16, l16}, b: the same
     const int a_box = A.mn_major ? tc::BK : tc::BM;
-    const int b_box = B.mn_major ? tc::BK : (paired ? tc::pair::BN_CTA : bn);
+    const int b_rows = paired ? tc::pair::BN_CTA : bn;
+    const int b_box = B.mn_major ? tc::BK : b_rows;
     ctk_status rc;
-    if ((rc = tc::make_map(&maps[0], a_hi, A.inner(), A.outer(), a_ld, a_box, A.mn_major))) return rc;
-    if ((rc = tc::make_map(&maps[1], a_lo, A.inner(), A.outer(), a_ld, a_box, A.mn_major))) return rc;
-    if ((rc = tc::make_map(&maps[2], b_hi, B.inner(), B.outer(), b_ld, b_box, B.mn_major))) return rc;
-    if ((rc = tc::make_map(&maps[3], b_lo, B.inner(), B.outer(), b_ld, b_box, B.mn_major))) return rc;
+    const float* a32 = terms == 1 ? A.p : sa.hi;
+    const float* b32 = terms == 1 ? B.p : sb.hi;
+    if ((rc = tc::make_map(&maps[0], a32, A.inner(), A.outer(), a_ld, a_box, A.mn_major))) return rc;
+    if ((rc = tc::make_map(&maps[3], b32, B.inner(), B.outer(), b_ld, b_box, B.mn_major))) return rc;
+    if (terms == 3) {
+        if ((rc = tc::make_map(&maps[1], static_cast<const float*>(sa.p2), A.inner(), A.outer(), a_ld, a_box, A.mn_major))) return rc;
+        if ((rc = tc::make_map(&maps[4], static_cast<const float*>(sb.p2), B.inner(), B.outer(), b_ld, b_box, B.mn_major))) return rc;
+        maps[2] = maps[1];
+        maps[5] = maps[4];
+    } else if (terms == 2) {
+        if ((rc = tc::make_map16(&maps[1], sa.p2, A.inner(), A.outer(), a_ld, tc::BM, A.mn_major))) return rc;
+        if ((rc = tc::make_map16(&maps[2], sa.p3, A.inner(), A.outer(), a_ld, tc::BM, A.mn_major))) return rc;
+        if ((rc = tc::make_map16(&maps[4], sb.p2, B.inner(), B.outer(), b_ld, b_rows, B.mn_major))) return rc;
+        if ((rc = tc::make_map16(&maps[5], sb.p3, B.inner(), B.outer(), b_ld, b_rows, B.mn_major))) return rc;
+    } else {
+        maps[1] = maps[2] = maps[0];
+        maps[4] = maps[5] = maps[3];
+    }
 
     tc::Params P;
     P.m = m; P.n = n; P.k = k;
@@ -1693,13 +1829,9 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
     P.bias = fe.bias;
     P.relu = fe.relu;
     P.mask = fe.mask;
-    P.out_hi = P.out_lo = nullptr;
-    P.split_pitch = (n + 3) / 4 * 4;
-    if (fe.c_split) {
-        float* h = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(fe.c_split) + 255u) & ~static_cast<uintptr_t>(255u));
-        P.out_hi = h;
-        P.out_lo = h + m * P.split_pitch;
-    }
+    P.out = SplitOut();
+    P.out.pitch = split_pitch_of(n);
+    if (fe.c_split) P.out = split_layout(fe.c_split, m, split_pitch_of(n), variant);
     CTK_REQUIRE(static_cast<int64_t>(P.tiles_m) * P.tiles_n < (int64_t(1) << 30), "ctk_matmul_f32: too many tiles");
     // The last wave: when at most half of the SMs (or CTA pairs) would have a tile, its tiles are
     // computed as two K-halves each (the second added to the first, in that order), so that twice as
@@ -1723,11 +1855,14 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
 
  #define CTK_TC(BN_)                                                                                 \
     (terms == 3 ? tc::launch_tc_major<BN_, 3>(A.mn_major, B.mn_major, maps, P, st)                  \
-                : tc::launch_tc_major<BN_, 1>(A.mn_major, B.mn_major, maps, P, st))
+     : terms == 2 ? tc::launch_tc_major<BN_, 2>(A.mn_major, B.mn_major, maps, P, st)                \
+                  : tc::launch_tc_major<BN_, 1>(A.mn_major, B.mn_major, maps, P, st))
     cudaEvent_t stop_ev;
     const bool timed = prof_begin(2.0 * static_cast<double>(m) * static_cast<double>(n) * static_cast<double>(k), st, &stop_ev);
     if (paired)
-        rc = terms == 3 ? tc::launch_pair_major<3>(A.mn_major, B.mn_major, maps, P, st) : tc::launch_pair_major<1>(A.mn_major, B.mn_major, maps, P, st);
+        rc = terms == 3   ? tc::launch_pair_major<3>(A.mn_major, B.mn_major, maps, P, st)
+             : terms == 2 ? tc::launch_pair_major<2>(A.mn_major, B.mn_major, maps, P, st)
+                          : tc::launch_pair_major<1>(A.mn_major, B.mn_major, maps, P, st);
     else
         rc = (bn == 256) ? CTK_TC(256) : (bn == 128) ? CTK_TC(128) : CTK_TC(64);
     if (timed) cudaEventRecord(stop_ev, st);
@@ -1798,12 +1933,11 @@ ctk_status ctk_sgd_update_split_f32(float* p, const float* g, float lr, int64_t 
     CTK_REQUIRE(p && g && split, "ctk_sgd_update_split_f32: null pointer");
     CTK_REQUIRE(((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g)) & 15u) == 0 && inner % 4 == 0 && ld % 4 == 0,
                 "ctk_sgd_update_split_f32: needs 16-byte aligned rows (use ctk_sgd_update_f32)");
-    float* hi = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(split) + 255u) & ~static_cast<uintptr_t>(255u));
-    float* lo = hi + outer * inner;  // (pitch of the copies = inner, already a multiple of 4)
+    const SplitOut out = split_layout(split, outer, split_pitch_of(inner), g_correction);
     const int64_t total = outer * (inner / 4);
     const int64_t per_cta = SPLIT_THREADS * SPLIT_UNROLL;
     sgd_split_vec_kernel<<<static_cast<unsigned>((total + per_cta - 1) / per_cta), SPLIT_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
-        p, g, lr, hi, lo, outer, inner / 4, ld, inner);
+        p, g, lr, out, outer, inner / 4, ld);
     CTK_LAUNCH_CHECK("sgd_split_vec_kernel");
     return CTK_OK;
 }

@@ -198,7 +198,7 @@ def matmul_fused(a, b, bias=None, relu=False, mask=None, want_split=False, ta=Fa
                                           split.p if split else None, None, _sh(stream)))
     if not want_split:
         return out
-    pitch = (n + 3) // 4 * 4
+    pitch = (n + 7) // 8 * 8
     pad = (-split.ptr) % 256 // 4          # the library aligns the buffer to 256 bytes
     flat = split.numpy()
     hi = flat[pad:pad + m * pitch].reshape(m, pitch)[:, :n]
@@ -212,8 +212,9 @@ def sgd_update_split(p, g, lr, stream=None):
     split = DeviceArray((int(lib.ctk_matmul_split_bytes(inner, outer)) // 4,))
     check(lib.ctk_sgd_update_split_f32(p.p, g.p, _f(lr), _i64(outer), _i64(inner), _i64(inner), split.p, _sh(stream)))
     pad = (-split.ptr) % 256 // 4
+    pitch = (inner + 7) // 8 * 8
     flat = split.numpy()
-    return flat[pad:pad + outer * inner].reshape(outer, inner), flat[pad + outer * inner:pad + 2 * outer * inner].reshape(outer, inner)
+    return flat[pad:pad + outer * pitch].reshape(outer, pitch)[:, :inner], flat[pad + outer * pitch:pad + 2 * outer * pitch].reshape(outer, pitch)[:, :inner]
 
 
 CMP = {"gt": 0, "lt": 1, "eq": 2, "ge": 3, "le": 4, "ne": 5}
@@ -294,6 +295,11 @@ def rowwise_status():
 def set_matmul_pairing(pairing):
     """0: 256 x 256 tiles on CTA pairs where the shape allows (default); 1: single-CTA kernel only."""
     check(lib.ctk_set_matmul_pairing(int(pairing)))
+
+
+def set_matmul_correction(bf16):
+    """Correction terms of the fp32-accurate mode: 0 on the TF32 path (3xTF32), 1 on the bf16 path."""
+    check(lib.ctk_set_matmul_correction(int(bf16)))
 
 
 def set_matmul_tail_split(on):

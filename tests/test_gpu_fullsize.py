@@ -130,11 +130,12 @@ def test_config3_products_at_full_size(cb, orc, m, k, n):
 
 
 # ---- config 5: one full-width training step -----------------------------------------------------------
-def _fp64_step(dims, x, labels, Ws, bs, lr, masks):
+def _fp64_step(dims, x, labels, Ws, bs, lr, masks, Ws_back=None):
     """The training step of mnist/mnist.cpp:44-92 in float64 with the reference's semantics: summed
     cross entropy with the 1e-10 clamp, bias gradient = row 0 of the upstream gradient
     (src/AutoDiff.cpp:690-757), backward through the weights as registered (equal to the live ones at
-    the first step), p -= g*lr.  masks[l]: which hidden units of layer l the DEVICE found active.  ReLU's
+    the first step; Ws_back: those registered weights at a later step), p -= g*lr.
+    masks[l]: which hidden units of layer l the DEVICE found active.  ReLU's
     derivative jumps at 0, so a pre-activation within rounding distance of 0 may fall on either side in
     float32 and float64; one such unit moves a whole column of a weight gradient by ~1 % of its size.
     Backward therefore uses the device's decisions (forward does not: it has no jump)."""
@@ -157,7 +158,7 @@ def _fp64_step(dims, x, labels, Ws, bs, lr, masks):
         gW[l] = h[l].T @ g
         if l > 0:
             flips += int(np.count_nonzero(masks[l - 1] != (h[l] > 0)))
-            g = (g @ Ws[l].astype(np.float64).T) * masks[l - 1]
+            g = (g @ (Ws_back or Ws)[l].astype(np.float64).T) * masks[l - 1]
     newW = [W.astype(np.float64) - lr * gw for W, gw in zip(Ws, gW)]
     newb = [b.astype(np.float64) - lr * g_ for b, g_ in zip(bs, gb)]
     return logits, loss, gW, gb, newW, newb, flips
