@@ -53,7 +53,7 @@ LR = 0.01
 WORKLOAD = "dp-mlp-784-4096-4096-4096-10_batch8192-per-gpu_fp32_sgd"
 CPU_SAMPLE_BATCH = 4  # rows per reference step: the reference's cost is linear in rows (~0.2 GFLOP/s)
 DEFAULT_DP_MODE, DEFAULT_MAX_CTAS = "inplace", 0
-DEFAULT_CORRECTION = "tf32"
+DEFAULT_CORRECTION = "bf16"
 NOMINAL_TF32 = 1125.0  # TFLOP/s, dense, the part's data sheet
 NOMINAL_HBM = 7700.0   # GB/s
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant shape from one ncu capture
@@ -465,7 +465,7 @@ def run_mlp(args, cp):
     extras = None
     if rank == 0 and world == 1 and not args.no_extras:
         del X, Y
-        extras = run_extras(cb, peaks, lib_tf32, with_cpu=not args.no_cpu_baseline)
+        extras = run_extras(cb, peaks, lib_tf32, with_cpu=not args.no_cpu_baseline, correction=args.correction)
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -486,14 +486,16 @@ def run_mlp(args, cp):
         # is possible and says how far the library itself is from the hardware.
         at_max = clocks and clocks.get("sm_mhz") and clocks.get("sm_max_mhz") and clocks["sm_mhz"] >= 0.95 * clocks["sm_max_mhz"]
         bf16_key, bf16_val = ("bf16_tflops (burst)", peaks["bf16"]) if at_max else ("bf16_tflops_sustained", peaks["bf16_sustained"])
-        peak = NOMINAL_TF32 / 3.0
-        ceilings = {"nominal_tf32_over_3": dict(peak=peak, frac=achieved / peak),
-                    "measured_bf16_over_6": dict(peak=bf16_val / 6.0, frac=achieved / (bf16_val / 6.0), source=f"{peaks['source']}: {bf16_key} {bf16_val}")}
+        # units of TF32-rate tensor work per fp32 product: three TF32 products, or one TF32 + two bf16 (each at twice the TF32 rate)
+        units = 3.0 if args.correction == "tf32" else 2.0
+        peak = NOMINAL_TF32 / units
+        ceilings = {f"nominal_tf32_over_{units:g}": dict(peak=peak, frac=achieved / peak),
+                    f"measured_bf16_over_{2 * units:g}": dict(peak=bf16_val / (2 * units), frac=achieved / (bf16_val / (2 * units)), source=f"{peaks['source']}: {bf16_key} {bf16_val}")}
         if lib_tf32 and "burst_tflops" in lib_tf32:
-            lib_peak = (lib_tf32["burst_tflops"] if at_max else lib_tf32["sustained_tflops"]) / 3.0
-            ceilings["library_tf32_gemm_over_3"] = dict(peak=lib_peak, frac=achieved / lib_peak, measured=lib_tf32)
+            lib_peak = (lib_tf32["burst_tflops"] if at_max else lib_tf32["sustained_tflops"]) / units
+            ceilings[f"library_tf32_gemm_over_{units:g}"] = dict(peak=lib_peak, frac=achieved / lib_peak, measured=lib_tf32)
         elif lib_tf32:
-            ceilings["library_tf32_gemm_over_3"] = lib_tf32
+            ceilings[f"library_tf32_gemm_over_{units:g}"] = lib_tf32
         flops_step = sum(2.0 * BATCH * i * j for i, j in zip(DIMS[:-1], DIMS[1:])) * 2 + sum(2.0 * BATCH * i * j for i, j in zip(DIMS[1:-1], DIMS[2:]))
         out = dict(
             metric="mlp_train_samples_per_s", value=value, unit="samples/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
@@ -510,11 +512,11 @@ def run_mlp(args, cp):
                      serial_call="cth_mlp_step_host: upload, step and loss read-back in sequence"),
             gpu_launches=int(launches),
             roofline=dict(bound="tensor", achieved=achieved, peak=peak, unit="TFLOP/s", frac=achieved / peak,
-                          peak_source="nominal dense TF32 rate 1125 TFLOP/s / 3 (three TF32 products per fp32 product); algorithmic flops 2*M*N*K; measured alternatives under `ceilings`",
+                          peak_source=f"nominal dense TF32 rate 1125 TFLOP/s / {units:g} ({'three TF32 products' if units == 3 else 'one TF32 product + two bf16 products at twice the TF32 rate = two units of TF32-rate work'} per fp32 product); algorithmic flops 2*M*N*K; measured alternatives under `ceilings`",
                           ceilings=ceilings,
                           # not measured in this run: one ncu capture of one launch of the dominant shape, kept under profiles/
                           traffic=QUOTED_TRAFFIC["bytes"], traffic_quoted_from=QUOTED_TRAFFIC["from"], traffic_launch=QUOTED_TRAFFIC["launch"],
-                          kernel="tcgen05_matmul_pair_kernel / tcgen05_matmul_kernel (3xTF32)", launches=int(n), avg_launch_ms=tms / n if n else None,
+                          kernel=f"tcgen05_matmul_pair_kernel / tcgen05_matmul_kernel (fp32-accurate mode, correction terms on the {args.correction} path)", launches=int(n), avg_launch_ms=tms / n if n else None,
                           step_model_flops=flops_step, step_tflops=flops_step / (per_step * 1e-3) / 1e12, step_frac=flops_step / (per_step * 1e-3) / 1e12 / peak),
             parity_check=parity, dp_check=dict(before=dp_before, after=dp_after) if world > 1 else None, extras=extras,
             cpu_baseline=cpu,
@@ -527,7 +529,7 @@ def run_mlp(args, cp):
         cb.lib.ctk_comm_destroy(comm)
 
 
-def run_extras(cb, peaks, lib_tf32, with_cpu=True):
+def run_extras(cb, peaks, lib_tf32, with_cpu=True, correction="bf16"):
     """The single-op metrics of the other benchmark configurations, bounded to a few tens of seconds:
     elementwise Add / Mul-backward / Tanh at 2^28, softmax and cross entropy at C in {10, 1000, 32000},
     Sum at 2^28, and the three products at 8192^3 and 65536 x 784 x 4096 in both tensor-core modes.
@@ -644,7 +646,8 @@ def run_extras(cb, peaks, lib_tf32, with_cpu=True):
             a_cols, hdC = host_cols(0, m, k, rb), host_rows(40961, m, nn)
             cpus["dB"] = cpu_rate(lambda: ref.matmul(a_cols, hdC, True, False), 2.0 * rb * m * nn, "TFLOP/s", f"{rb} row(s) of dB = A^T.dC", warm=False)
             del a_cols, hdC, hB
-        for mode, nominal in (("3xtf32", NOMINAL_TF32 / 3.0), ("tf32", NOMINAL_TF32)):
+        units = 3.0 if correction == "tf32" else 2.0
+        for mode, nominal in (("3xtf32", NOMINAL_TF32 / units), ("tf32", NOMINAL_TF32)):
             for which, fn in (("fwd", lambda: cb.ops.matmul(A, B, mode=mode, out=Cc)),
                               ("dA", lambda: cb.ops.matmul(dC, B, tb=True, mode=mode, out=dA)),
                               ("dB", lambda: cb.ops.matmul(A, dC, ta=True, mode=mode, out=dB))):
@@ -657,11 +660,11 @@ def run_extras(cb, peaks, lib_tf32, with_cpu=True):
                 cb.check(cb.lib.ctk_matmul_profile_enable(0))
                 kern = tfl.value / (tms.value * 1e-3) / 1e12 if tms.value > 0 else None
                 ach = fl / (ms * 1e-3) / 1e12
-                d = dict(bound="tensor", peak=nominal, frac=ach / nominal, peak_source="nominal dense TF32 1125 TFLOP/s" + (" / 3" if mode == "3xtf32" else ""),
+                d = dict(bound="tensor", peak=nominal, frac=ach / nominal, peak_source="nominal dense TF32 1125 TFLOP/s" + (f" / {units:g} (correction terms on the {correction} path)" if mode == "3xtf32" else ""),
                          kernel_alone_tflops=kern, kernel_alone_frac=(kern / nominal if kern else None),
                          call="ctk_matmul_f32, operands split inside the call (3xTF32)" if mode == "3xtf32" else "ctk_matmul_f32, operands read in place")
                 if lib_tf32_peak:
-                    d["frac_of_library_tf32_gemm"] = ach / (lib_tf32_peak / (3.0 if mode == "3xtf32" else 1.0))
+                    d["frac_of_library_tf32_gemm"] = ach / (lib_tf32_peak / (units if mode == "3xtf32" else 1.0))
                 add(f"matmul_{which}_{mode}_{m}x{k}x{nn}", ms, fl, "TFLOP/s", cpus.get(which), **d)
         del A, B, dC, Cc, dA, dB
     out.append(dict(name="matmul_status", value=cb.ops.matmul_status()))

@@ -178,7 +178,7 @@ _fused_cache = {}
 
 def matmul_fused(a, b, bias=None, relu=False, mask=None, want_split=False, ta=False, tb=False, stream=None, keep_split=False):
     """[relu](a.b + bias) * (mask > 0), the epilogue forms of the 3xTF32 product in one launch.
-    Returns (c, c_hi, c_lo) when want_split (the split the epilogue wrote, as [m, n] arrays), else c.
+    Returns (c, hi, rest) when want_split (the split the epilogue wrote, decoded by _decode_split), else c.
     keep_split: write the split too, into buffers (and c) reused from call to call, and do not read it back."""
     m, k = (a.shape[1], a.shape[0]) if ta else a.shape
     n = b.shape[0] if tb else b.shape[1]
@@ -198,23 +198,33 @@ def matmul_fused(a, b, bias=None, relu=False, mask=None, want_split=False, ta=Fa
                                           split.p if split else None, None, _sh(stream)))
     if not want_split:
         return out
-    pitch = (n + 7) // 8 * 8
+    hi, rest = _decode_split(split, m, n)
+    return out, hi, rest
+
+
+def _decode_split(split, outer, inner):
+    """The arrays of a split buffer as numpy: (hi, lo) as float32 [outer, inner] when the correction terms
+    run on the TF32 path, (hi, bits) with bits a uint16 [2, outer, inner] array holding the bf16 patterns
+    of h16 and l16 when they run on the bf16 path (see ctk_set_matmul_correction)."""
+    pitch = (inner + 7) // 8 * 8
     pad = (-split.ptr) % 256 // 4          # the library aligns the buffer to 256 bytes
     flat = split.numpy()
-    hi = flat[pad:pad + m * pitch].reshape(m, pitch)[:, :n]
-    lo = flat[pad + m * pitch:pad + 2 * m * pitch].reshape(m, pitch)[:, :n]
-    return out, hi, lo
+    hi = flat[pad:pad + outer * pitch].reshape(outer, pitch)[:, :inner]
+    if lib.ctk_get_matmul_correction() == 0:
+        return hi, flat[pad + outer * pitch:pad + 2 * outer * pitch].reshape(outer, pitch)[:, :inner]
+    u16 = flat.view(np.uint16)
+    o = 2 * (pad + outer * pitch)
+    h16 = u16[o:o + outer * pitch].reshape(outer, pitch)[:, :inner]
+    l16 = u16[o + outer * pitch:o + 2 * outer * pitch].reshape(outer, pitch)[:, :inner]
+    return hi, np.stack([h16, l16])
 
 
 def sgd_update_split(p, g, lr, stream=None):
-    """p -= g*lr on a 2-D array and the hi/lo split of the new p in the same pass; returns (hi, lo)."""
+    """p -= g*lr on a 2-D array and the split of the new p in the same pass; returns it as _decode_split does."""
     outer, inner = p.shape
     split = DeviceArray((int(lib.ctk_matmul_split_bytes(inner, outer)) // 4,))
     check(lib.ctk_sgd_update_split_f32(p.p, g.p, _f(lr), _i64(outer), _i64(inner), _i64(inner), split.p, _sh(stream)))
-    pad = (-split.ptr) % 256 // 4
-    pitch = (inner + 7) // 8 * 8
-    flat = split.numpy()
-    return flat[pad:pad + outer * pitch].reshape(outer, pitch)[:, :inner], flat[pad + outer * pitch:pad + 2 * outer * pitch].reshape(outer, pitch)[:, :inner]
+    return _decode_split(split, outer, inner)
 
 
 CMP = {"gt": 0, "lt": 1, "eq": 2, "ge": 3, "le": 4, "ne": 5}

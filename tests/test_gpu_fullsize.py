@@ -98,7 +98,8 @@ def _projection_check(C, sa, sb, ta, tb, tol, rng, what):
 
 @pytest.mark.parametrize("m,k,n", [(4096, 4096, 4096), (8192, 8192, 8192), (65536, 784, 4096)])
 def test_config3_products_at_full_size(cb, orc, m, k, n):
-    """C = A.B, dA = dC.B^T and dB = A^T.dC (contractions of 784 to 65536 terms) in both modes."""
+    """C = A.B, dA = dC.B^T and dB = A^T.dC (contractions of 784 to 65536 terms): the fp32-accurate mode with
+    its correction terms on the bf16 path (the default) and on the TF32 path ("3xTF32"), and the TF32 mode."""
     rng = np.random.default_rng(1000 + m + k)
     A = rng.standard_normal((m, k), dtype=np.float32)
     B = rng.standard_normal((k, n), dtype=np.float32)
@@ -108,14 +109,19 @@ def test_config3_products_at_full_size(cb, orc, m, k, n):
                 ("dA=dC.B^T", dC, B, False, True, dG, dB_),
                 ("dB=A^T.dC", A, dC, True, False, dA_, dG))
     report, bad = {}, []
+    start = cb.lib.ctk_get_matmul_correction()
     for name, sa, sb, ta, tb, da, db in products:
         idx, ref32, ref64 = _oracle_samples(orc, sa, sb, ta, tb, rng)
-        for mode in ("3xtf32", "tf32"):
+        for mode, corr, label in (("3xtf32", 1, "tf32+2xbf16"), ("3xtf32", 0, "3xtf32"), ("tf32", 1, "tf32")):
             assert cb.ops.matmul_path(da, db, ta, tb, mode) == 0, "tensor-core path expected"
-            out = cb.ops.matmul(da, db, ta, tb, mode)
+            cb.ops.set_matmul_correction(corr)
+            try:
+                out = cb.ops.matmul(da, db, ta, tb, mode)
+            finally:
+                cb.ops.set_matmul_correction(start)
             C = out.numpy()
             del out
-            what = f"{name} {m}x{k}x{n} {mode}"
+            what = f"{name} {m}x{k}x{n} {label}"
             e32, e64 = _product_errors(C, idx, ref32, ref64)
             report[what] = f"{e32:.2e} vs the reference recurrence, {e64:.2e} vs float64"
             if max(e32, e64) > TOL[mode]:

@@ -13,6 +13,15 @@ pytestmark = pytest.mark.gpu
 TOL = {"3xtf32": 1e-4, "tf32": 5e-3, "fp32_simt": 1e-5}
 
 
+@pytest.fixture(autouse=True, params=["tf32-corrections", "bf16-corrections"])
+def correction(cb, request):
+    """Every test of this file runs with the correction terms of the fp32-accurate mode on either path."""
+    before = cb.lib.ctk_get_matmul_correction()
+    cb.ops.set_matmul_correction(1 if request.param.startswith("bf16") else 0)
+    yield request.param
+    cb.ops.set_matmul_correction(before)
+
+
 def _mats(m, k, n, seed=0):
     rng = np.random.default_rng(seed)
     return (rng.standard_normal((m, k)).astype(np.float32), rng.standard_normal((k, n)).astype(np.float32),
@@ -260,7 +269,12 @@ def test_fused_epilogue_equals_the_separate_kernels(cb, m, k, n, ta, tb, pairing
 
 
 def oracle_split(x):
-    """cvt.rna.tf32.f32 of x and of x - hi: round to nearest, ties away from zero, 10 mantissa bits."""
+    """The split the library keeps of x, in the form ops._decode_split returns it.  hi = cvt.rna.tf32.f32
+    of x (round to nearest, ties away from zero, 10 mantissa bits).  Correction terms on the TF32 path:
+    lo = the same rounding of x - hi.  On the bf16 path: the bf16 bit patterns (round to nearest even)
+    of hi and of x - hi."""
+    import ctorch_b200 as cb_
+
     def rna(v):
         u = v.view(np.uint32).astype(np.uint64)
         r = ((u + 0x1000) & 0xFFFFE000).astype(np.uint32)
@@ -268,9 +282,20 @@ def oracle_split(x):
         special = ~np.isfinite(v)
         out[special] = v[special]
         return out
+
+    def bf16_bits(v):
+        u = np.ascontiguousarray(v, np.float32).view(np.uint32).astype(np.uint64)
+        r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+        nan = np.isnan(v)
+        r[nan] = ((u[nan] >> 16) | 0x40).astype(np.uint16)
+        return r
+
     x = np.ascontiguousarray(x, np.float32)
     hi = rna(x)
-    return hi, rna((x - hi).astype(np.float32))
+    lo = (x - hi).astype(np.float32)
+    if cb_.lib.ctk_get_matmul_correction() == 0:
+        return hi, rna(lo)
+    return hi, np.stack([bf16_bits(hi), bf16_bits(lo)])
 
 
 @pytest.mark.parametrize("outer,inner", [(784, 4096), (130, 132), (3, 4)])
