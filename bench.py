@@ -52,8 +52,9 @@ BATCH = 8192
 LR = 0.01
 WORKLOAD = "dp-mlp-784-4096-4096-4096-10_batch8192-per-gpu_fp32_sgd"
 CPU_SAMPLE_BATCH = 4  # rows per reference step: the reference's cost is linear in rows (~0.2 GFLOP/s)
-DEFAULT_DP_MODE, DEFAULT_MAX_CTAS = "inplace", 0
+DEFAULT_DP_MODE, DEFAULT_MAX_CTAS = "arena", 0
 DEFAULT_CORRECTION = "bf16"
+DEFAULT_NCCL_ALGO = "auto"
 NOMINAL_TF32 = 1125.0  # TFLOP/s, dense, the part's data sheet
 NOMINAL_HBM = 7700.0   # GB/s
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant shape from one ncu capture
@@ -370,9 +371,12 @@ def run_mlp(args, cp):
 
     comm = None
     dp_before = None
+    algo_used = ""
     if world > 1:
         from ctorch_b200 import dp
-        comm = dp.make_comm(cb, cp, max_ctas=args.max_ctas, nvls_ctas=args.nvls_ctas)
+        # NVLS (the reduction done inside the NVSwitch) from 4 GPUs up unless told otherwise; with fewer ranks NCCL's own choice
+        algo = args.nccl_algo if args.nccl_algo != "auto" else ("NVLS" if world >= 4 else "")
+        comm, algo_used = dp.make_comm(cb, cp, max_ctas=args.max_ctas, nvls_ctas=args.nvls_ctas, algo=algo)
         if not args.no_checks:
             dp_before = dp_check_before(cb, F, cp, comm, args.dp_mode)
 
@@ -501,7 +505,7 @@ def run_mlp(args, cp):
             metric="mlp_train_samples_per_s", value=value, unit="samples/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
             ms_per_step=per_step, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",
             config=dict(workload=WORKLOAD, global_batch=BATCH * world, parallelism=f"dp{world}", matmul_mode="3xtf32" if args.correction == "tf32" else "tf32 + 2 x bf16 correction terms",
-                        lr=lr, gradient_exchange=(args.dp_mode if world > 1 else None), nccl_max_ctas=args.max_ctas or None,
+                        lr=lr, gradient_exchange=(args.dp_mode if world > 1 else None), nccl_max_ctas=args.max_ctas or None, nccl_algo=(algo_used or "NCCL's choice") if world > 1 else None,
                         l2="per-step working set (weights 147 MB + activations 3x134 MB per layer pass) exceeds the 126 MB L2",
                         loss_last=float(loss_dev) if loss_dev is not None else None, matmul_status=status, stable_lr_run=stable),
             clocks=clocks,
@@ -1045,6 +1049,7 @@ def main():
     ap.add_argument("--correction", default=DEFAULT_CORRECTION, choices=["tf32", "bf16"],
                     help="which tensor-core path carries the two correction terms of the fp32-accurate MatMul mode")
     ap.add_argument("--stable-lr", action="store_true", help="time the headline run itself at lr / batch (weights do not diverge); recorded in config")
+    ap.add_argument("--nccl-algo", default=DEFAULT_NCCL_ALGO, help="NCCL_ALGO for the gradient exchange's communicator: a name, '' for NCCL's own choice, or 'auto' (NVLS from 4 ranks up, with a fall-back if a rank cannot run it)")
     ap.add_argument("--nvls-ctas", type=int, default=0, help="CTAs of a collective's in-switch part (0: NCCL's choice)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours" and args.workload == "mlp":

@@ -65,9 +65,7 @@ def shard_seed(base_seed, rank):
     return base_seed + 1000 * rank
 
 
-def make_comm(cb, cp, max_ctas=0, nvls_ctas=0):
-    """Creates the NCCL communicator of this rank (ctk_comm_init_rank_config) from an id made on rank 0.
-    max_ctas / nvls_ctas bound the CTAs a collective may take from the MatMul kernels (0: NCCL's choice)."""
+def _init_comm(cb, cp, max_ctas, nvls_ctas):
     import ctypes
     idbuf = np.zeros(128, np.uint8)
     if cp.rank == 0:
@@ -76,6 +74,42 @@ def make_comm(cb, cp, max_ctas=0, nvls_ctas=0):
     comm = ctypes.c_void_p()
     cb.check(cb.lib.ctk_comm_init_rank_config(ctypes.byref(comm), idbuf.ctypes.data_as(ctypes.c_void_p), cp.world, cp.rank, int(max_ctas), int(nvls_ctas)))
     return comm
+
+
+def make_comm(cb, cp, max_ctas=0, nvls_ctas=0, algo=""):
+    """Creates the NCCL communicator of this rank (ctk_comm_init_rank_config) from an id made on rank 0.
+    max_ctas / nvls_ctas bound the CTAs a collective may take from the MatMul kernels (0: NCCL's choice).
+    algo: "" leaves the algorithm to NCCL's tuner; a name (e.g. "NVLS": reduction inside the NVSwitch,
+    which the tuner of NCCL 2.27/2.28 does not pick by itself for these sizes on 4 GPUs although it is
+    the fastest under a running backward pass) is set as NCCL_ALGO for this communicator and tried
+    with one small all-reduce on every rank; if any rank cannot run it, all ranks fall back to NCCL's
+    choice.  Returns (communicator, algo in effect)."""
+    import ctypes
+    if algo:
+        saved = os.environ.get("NCCL_ALGO")
+        os.environ["NCCL_ALGO"] = algo
+        ok = 1.0
+        comm = None
+        try:
+            comm = _init_comm(cb, cp, max_ctas, nvls_ctas)
+            probe = cb.zeros((1 << 20,))
+            cb.check(cb.lib.ctk_allreduce_sum_f32(comm, probe.p, ctypes.c_int64(probe.size), None))
+            cb.synchronize()
+        except Exception:
+            ok = 0.0
+        if -cp.max_over_ranks(-ok) > 0.5:   # the minimum over ranks
+            return comm, algo
+        if comm is not None:
+            try:
+                cb.lib.ctk_comm_abort(comm)
+                cb.lib.ctk_comm_destroy(comm)
+            except Exception:
+                pass
+        if saved is None:
+            os.environ.pop("NCCL_ALGO", None)
+        else:
+            os.environ["NCCL_ALGO"] = saved
+    return _init_comm(cb, cp, max_ctas, nvls_ctas), ""
 
 
 class Watchdog:

@@ -87,7 +87,7 @@ def main():
     from ctorch_b200 import frontend as F
     cb.check(cb.lib.ctk_set_device(cp.local_rank))
     F.set_quiet(True)
-    comm = dp.make_comm(cb, cp)
+    comm, _ = dp.make_comm(cb, cp)
     tr = F.MlpTrainer(DIMS, p, LR)
     tr.set_dp_mode(os.environ.get("CTORCH_TEST_DP_MODE", "inplace"))
     tr.set_comm(comm)
