@@ -252,8 +252,22 @@ Tensor AutoDiff::check_and_adjust_grad_shape(const Tensor& grad, const std::vect
             break;
         }
     }
-    if (!can_broadcast)
-        Ctorch_Error::throwException(ErrorPlatform::kAutoDiff, ErrorType::DIMENSION, "gradient shape adjustment: folding incompatible shapes is not implemented on the device");
+    if (!can_broadcast) {
+        // Shapes that do not broadcast: the reference folds, result[i] = sum of grad[j] over j = i (mod n),
+        // n the target's element count (:910-966; its last-resort branch :971-1048 computes the same sums
+        // the slow way).  With grad read as rows of n elements that is a column sum over the whole rows
+        // plus the ragged last row added to the first elements.  The reference adds each class of j in
+        // ascending order in fp32; the device sums the column in a tree, at least as accurately.
+        if (!grad.is_contiguous()) Ctorch_Error::throwException(ErrorPlatform::kAutoDiff, ErrorType::DIMENSION, "gradient shape adjustment: folding needs a contiguous gradient");
+        Tensor result(ShapeTag{}, target_shape, grad.dtype(), dev, false);
+        const int64_t n = static_cast<int64_t>(result.numel()), total = static_cast<int64_t>(grad.numel());
+        if (n == 0) return result;
+        const int64_t rows = total / n, rem = total % n;
+        if (rows > 0) cuda_check(ctk_colsum_f32(dev_ptr(grad), rows, n, result.data<float>(), st), "grad fold");
+        else result.fill(0.0f);
+        if (rem > 0) cuda_check(ctk_accumulate_f32(result.data<float>(), dev_ptr(grad) + rows * n, rem, st), "grad fold (last row)");
+        return result;
+    }
     Tensor result(ShapeTag{}, target_shape, grad.dtype(), dev, false);
     const int64_t n = static_cast<int64_t>(result.numel());
     if (n == 0) return result;

@@ -575,6 +575,25 @@ def test_relu_backward_fusion_is_skipped_when_the_activation_has_two_readers(F, 
         assert_exact(c, a, "two readers: nothing changes")
 
 
+def test_gradient_of_a_shape_that_does_not_broadcast_is_folded(F):
+    """check_and_adjust_grad_shape's fall-back (src/AutoDiff.cpp:910-1048): a gradient whose shape neither
+    equals nor broadcasts to the tensor's is folded, result[i] = sum of grad[j] over j = i (mod n), added
+    in ascending j in fp32.  Reached by backward(root, grad_output) with a grad_output of another shape."""
+    rng = np.random.default_rng(17)
+    for gshape, n in (((4, 5), 6), ((3, 7), 21), ((2, 3, 5), 4), ((5,), 8)):
+        x = rng.standard_normal(n).astype(np.float32)
+        g = rng.standard_normal(gshape).astype(np.float32)
+        want = np.zeros(n, np.float32)
+        for j, v in enumerate(g.ravel()):            # the reference's loop (:921-923)
+            want[j % n] = np.float32(want[j % n] + v)
+        with F.AutoDiff():
+            X = dev(F, x).requires_grad()
+            y = -X
+            F.backward(y, dev(F, g))
+            got = F.grad(X).numpy()
+        assert_close(got, -want, 1e-5, 1e-6, f"fold {gshape} -> [{n}]")
+
+
 def test_leaf_gradient_hook_fires_once_after_the_last_contribution(F):
     """AutoDiff::on_leaf_grad -- where a data-parallel driver starts a gradient's all-reduce -- is called
     once per leaf and pass, also for a leaf that enters several nodes (a shared weight): its gradient is

@@ -114,7 +114,7 @@ def test_byte_to_float_kernel_all_values_and_tails(cb):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("rows,cols", [(1, 1), (513, 10), (64, 33), (7, 1000), (3, 40000)])
+@pytest.mark.parametrize("rows,cols", [(1, 1), (513, 10), (1000, 16), (100, 7), (9, 3), (64, 33), (7, 1000), (3, 40000)])
 def test_first_maximum_per_row(cb, rows, cols):
     rng = np.random.default_rng(rows * 7 + cols)
     p = rng.uniform(0, 1, (rows, cols)).astype(np.float32)
