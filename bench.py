@@ -465,11 +465,16 @@ def run_mlp(args, cp):
         else:
             spread = weights_spread(cp, trainer.params())
             dp_after = dict(what=f"largest difference between any two ranks' weights after {3 * (args.warmup + args.steps)} steps", max_abs_diff=spread, ok=bool(spread == 0.0))
-    lib_tf32 = measure_library_tf32(local_rank) if rank == 0 and not args.no_comparator else None
     extras = None
     if rank == 0 and world == 1 and not args.no_extras:
         del X, Y
-        extras = run_extras(cb, peaks, lib_tf32, with_cpu=not args.no_cpu_baseline, correction=args.correction)
+        extras = run_extras(cb, peaks, with_cpu=not args.no_cpu_baseline, correction=args.correction)
+    # last: its seconds-long loop leaves the chip hot and power-throttled for whatever follows
+    lib_tf32 = measure_library_tf32(local_rank) if rank == 0 and not args.no_comparator else None
+    if extras and lib_tf32 and "burst_tflops" in lib_tf32:
+        for e in extras:
+            if e.get("bound") == "tensor":
+                e["frac_of_library_tf32_gemm"] = e["value"] / (lib_tf32["burst_tflops"] / e["tf32_units"])
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -533,7 +538,7 @@ def run_mlp(args, cp):
         cb.lib.ctk_comm_destroy(comm)
 
 
-def run_extras(cb, peaks, lib_tf32, with_cpu=True, correction="bf16"):
+def run_extras(cb, peaks, with_cpu=True, correction="bf16"):
     """The single-op metrics of the other benchmark configurations, bounded to a few tens of seconds:
     elementwise Add / Mul-backward / Tanh at 2^28, softmax and cross entropy at C in {10, 1000, 32000},
     Sum at 2^28, and the three products at 8192^3 and 65536 x 784 x 4096 in both tensor-core modes.
@@ -633,7 +638,7 @@ def run_extras(cb, peaks, lib_tf32, with_cpu=True, correction="bf16"):
         idx = (np.arange(nrows, dtype=np.int64)[:, None] * cols_ + np.arange(r)[None, :]) % ((1 << 24) - shift) + shift
         return np.ascontiguousarray(hblk[idx])
 
-    lib_tf32_peak = lib_tf32.get("burst_tflops") if lib_tf32 else None
+    from ctorch_b200 import frontend as F
     for (m, k, nn) in ((8192, 8192, 8192), (65536, 784, 4096)):
         A, B, dC = mat(m, k, 0), mat(k, nn, 1237), mat(m, nn, 40961)
         Cc, dA, dB = cb.empty((m, nn)), cb.empty((m, k)), cb.empty((k, nn))
@@ -664,13 +669,28 @@ def run_extras(cb, peaks, lib_tf32, with_cpu=True, correction="bf16"):
                 cb.check(cb.lib.ctk_matmul_profile_enable(0))
                 kern = tfl.value / (tms.value * 1e-3) / 1e12 if tms.value > 0 else None
                 ach = fl / (ms * 1e-3) / 1e12
-                d = dict(bound="tensor", peak=nominal, frac=ach / nominal, peak_source="nominal dense TF32 1125 TFLOP/s" + (f" / {units:g} (correction terms on the {correction} path)" if mode == "3xtf32" else ""),
+                d = dict(bound="tensor", tf32_units=(units if mode == "3xtf32" else 1.0), peak=nominal, frac=ach / nominal, peak_source="nominal dense TF32 1125 TFLOP/s" + (f" / {units:g} (correction terms on the {correction} path)" if mode == "3xtf32" else ""),
                          kernel_alone_tflops=kern, kernel_alone_frac=(kern / nominal if kern else None),
                          call="ctk_matmul_f32, operands split inside the call (3xTF32)" if mode == "3xtf32" else "ctk_matmul_f32, operands read in place")
-                if lib_tf32_peak:
-                    d["frac_of_library_tf32_gemm"] = ach / (lib_tf32_peak / (units if mode == "3xtf32" else 1.0))
                 add(f"matmul_{which}_{mode}_{m}x{k}x{nn}", ms, fl, "TFLOP/s", cpus.get(which), **d)
-        del A, B, dC, Cc, dA, dB
+        del Cc, dA, dB
+        # the three products as user code gets them: C = A.matmul(B); backward(C, dC) through Tensor / AutoDiff,
+        # where every operand's split is made once and kept for the second product that reads it
+        tA, tB, tG = (F.Tensor.from_numpy(v.numpy()) for v in (A, B, dC))
+        del A, B, dC
+        with F.AutoDiff() as ctx:
+            ctx.make_leaf(tA, True); ctx.make_leaf(tB, True)
+            tA.requires_grad(); tB.requires_grad()
+
+            def fwd_bwd():
+                ctx.zero_grad(tA); ctx.zero_grad(tB)
+                F.backward(tA.matmul(tB), tG)
+                ctx.release_step_nodes()
+            ms = gpu_ms(fwd_bwd, 5)
+        add(f"matmul_fwd_bwd_frontend_{m}x{k}x{nn}", ms, 3 * fl, "TFLOP/s", None, bound="tensor", tf32_units=units, peak=NOMINAL_TF32 / units,
+            frac=3 * fl / (ms * 1e-3) / 1e12 / (NOMINAL_TF32 / units),
+            call="Tensor::matmul + backward(C, dC): C, dA and dB in the fp32-accurate mode, each operand split once")
+        del tA, tB, tG
     out.append(dict(name="matmul_status", value=cb.ops.matmul_status()))
     return out
 

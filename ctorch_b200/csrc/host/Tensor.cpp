@@ -34,26 +34,30 @@ void set_current_stream(void* s) { t_stream = s; }
 
 // ---- pinned staging for host <-> device copies --------------------------------------------------
 // Two page-locked buffers per thread: while one is in flight on the copy engine the host fills (or
-// drains) the other.
+// drains) the other.  The buffers serve every GPU; the events that guard them belong to a device, so
+// there is a pair per device ordinal (`ev` points at the pair of the device current at ensure()).
 namespace {
 struct Staging {
     static constexpr size_t kChunk = 8u << 20;
     void* buf[2] = {nullptr, nullptr};
-    void* ev[2] = {nullptr, nullptr};
-    bool ready = false;
+    void* ev_of[64][2] = {};
+    void** ev = ev_of[0];
     void ensure() {
-        if (ready) return;
+        int dev = 0;
+        cuda_check(ctk_get_device(&dev), "current device");
+        if (dev < 0 || dev >= 64) Ctorch_Error::throwException(ErrorPlatform::kCUDA, ErrorType::DEVICE_COMPAT, "device ordinal out of range");
         for (int i = 0; i < 2; ++i) {
-            cuda_check(ctk_malloc_host(&buf[i], kChunk), "pinned staging allocation");
-            cuda_check(ctk_event_create(&ev[i]), "staging event");
+            if (!buf[i]) cuda_check(ctk_malloc_host(&buf[i], kChunk), "pinned staging allocation");
+            if (!ev_of[dev][i]) cuda_check(ctk_event_create(&ev_of[dev][i]), "staging event");
         }
-        ready = true;
+        ev = ev_of[dev];
     }
     ~Staging() {
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < 2; ++i)
             if (buf[i]) ctk_free_host(buf[i]);
-            if (ev[i]) ctk_event_destroy(ev[i]);
-        }
+        for (auto& pair : ev_of)
+            for (void* e : pair)
+                if (e) ctk_event_destroy(e);
     }
 };
 thread_local Staging t_staging;

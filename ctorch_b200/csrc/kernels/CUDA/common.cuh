@@ -49,11 +49,15 @@ struct PerDeviceOnce {
 
 }  // namespace ctk
 
+// (A failed call also leaves its code as the thread's "last error"; it is taken back here, or the
+// next kernel launch check -- which reads that state -- would report this failure as its own.)
 #define CTK_CUDA(call)                                                                          \
     do {                                                                                        \
         cudaError_t _e = (call);                                                                \
-        if (_e != cudaSuccess)                                                                  \
+        if (_e != cudaSuccess) {                                                                \
+            (void)cudaGetLastError();                                                           \
             return ctk::fail(CTK_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(_e)); \
+        }                                                                                       \
     } while (0)
 
 #define CTK_LAUNCH_CHECK(name)                                                                    \

@@ -252,9 +252,10 @@ constexpr uint32_t WAIT_LIMIT = 1u << 20;  // polls per bounded wait (each poll 
 // Its cost is one more drain of the accumulator, during which the tensor pipe idles ~3.4 us per
 // 128 x 256 accumulator: one full training step of 784-4096-4096-4096-10 at batch 8192 ran 6.01 ms with
 // 4096, 6.29 ms with 2048 and 6.65 ms with 1024 for the wide tiles, its logits 6.2e-5 / 3.3e-5 / 1.9e-5
-// from float64.  2048 keeps every gradient of that step within 1e-4 with room to spare; narrow tiles
-// drain cheaply and use shorter chunks.
-constexpr int chunk_k_for(int bn) { return bn >= 256 ? 2048 : (bn >= 128 ? 512 : 256); }
+// from float64.  2048 keeps every gradient of that step within 1e-4 with room to spare; the narrow tiles
+// of the 10-class layer, whose weight gradient adds products of one sign that nearly cancel in the end,
+// use 1024 (at 256 the layer's two products cost 0.4 ms of a 5.3 ms step in drains alone).
+constexpr int chunk_k_for(int bn) { return bn >= 256 ? 2048 : 1024; }
 // (With the correction terms on the bf16 path an accumulator sees four instructions per 16 terms instead
 // of six -- K = 16 per bf16 instruction -- i.e. two thirds of the truncations: at 4096^3 its error is
 // 1.0e-5 where the TF32 corrections give 1.6e-5 with the same chunks.)
@@ -598,21 +599,28 @@ struct SideRegs {
 __device__ __forceinline__ bool chunk_is_whole(const Params& P, int64_t col0) {
     return P.vec_store && col0 + 32 <= P.n;
 }
-// first / last: this is the unit's first / last K-chunk.  Which array the prefetch serves:
-// the running sum in C when there is one (!first), else the mask (only the last chunk applies it).
-__device__ __forceinline__ const float* side_array(const Params& P, bool first, bool last) {
-    return !first ? P.c : (last ? P.mask : nullptr);
-}
-__device__ __forceinline__ void load_side(const Params& P, bool first, bool last, int64_t row_base, int lane, int64_t col0, SideRegs& sd) {
-    const float* arr = side_array(P, first, last);
-    if (arr == nullptr || !chunk_is_whole(P, col0)) return;
+// first / last: this is the unit's first / last K-chunk.  Two arrays may be read beside the accumulator:
+// the running sum parked in C by the chunks before (every chunk but the first) and the mask (the last
+// chunk).  Each has its own registers, so both are in flight a column chunk ahead.
+__device__ __forceinline__ void load_pieces(const float* arr, const Params& P, int64_t row_base, int lane, int64_t col0, SideRegs& out, bool coherent) {
     const int sub = lane >> 3, c4 = (lane & 7) * 4;
     const float* src = arr + (row_base + sub) * P.n + col0 + c4;
     const int64_t step = 4 * P.n;
     const int rows_left = static_cast<int>(P.m - row_base < 32 ? P.m - row_base : 32);
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
-        sd.v[i] = (i * 4 + sub < rows_left) ? __ldcg(reinterpret_cast<const float4*>(src + i * step)) : make_float4(0.f, 0.f, 0.f, 0.f);  // (L2: a running sum may come from another SM)
+    for (int i = 0; i < 8; ++i) {
+        if (i * 4 + sub < rows_left) {
+            // (a running sum may have been written by another SM -- the first half of a halved tile -- so it is read from L2)
+            out.v[i] = coherent ? __ldcg(reinterpret_cast<const float4*>(src + i * step)) : __ldcs(reinterpret_cast<const float4*>(src + i * step));
+        } else {
+            out.v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+}
+__device__ __forceinline__ void load_side(const Params& P, bool first, bool last, int64_t row_base, int lane, int64_t col0, SideRegs& sum, SideRegs& mask) {
+    if (!chunk_is_whole(P, col0)) return;
+    if (!first) load_pieces(P.c, P, row_base, lane, col0, sum, true);
+    if (last && P.mask != nullptr) load_pieces(P.mask, P, row_base, lane, col0, mask, false);
 }
 
 // One 32 x 32 chunk of an accumulator leaves the CTA.  Each lane holds 32 columns of ITS row (the
@@ -623,7 +631,7 @@ __device__ __forceinline__ void load_side(const Params& P, bool first, bool last
 // layout, one fp32 operation per element and step, in this order: + running sum of the earlier
 // K-chunks; on the last chunk + bias, ReLU, x (mask > 0), store, hi/lo split of what was stored.
 __device__ __forceinline__ void emit_chunk(const Params& P, bool half, bool first, bool last, int64_t row_base, int lane, int64_t col0,
-                                           uint32_t (&r)[32], EpilogueStage& stage, const SideRegs& sd) {
+                                           uint32_t (&r)[32], EpilogueStage& stage, const SideRegs& sd, const SideRegs& mk) {
     if (col0 >= P.n) return;  // same for the whole warp
     const int64_t row = row_base + lane;
     if (chunk_is_whole(P, col0)) {
@@ -686,7 +694,7 @@ __device__ __forceinline__ void emit_chunk(const Params& P, bool half, bool firs
                     x.x = x.x > 0.0f ? x.x : 0.0f; x.y = x.y > 0.0f ? x.y : 0.0f; x.z = x.z > 0.0f ? x.z : 0.0f; x.w = x.w > 0.0f ? x.w : 0.0f;
                 }
                 if (masked) {  // g * (y > 0 ? 1 : 0): the backward rule of ReLU, y its output
-                    const float4 y = first ? sd.v[i] : __ldcs(reinterpret_cast<const float4*>(P.mask + (row_base + sub + 4 * i) * P.n + col0 + c4));
+                    const float4 y = mk.v[i];
                     x.x *= y.x > 0.0f ? 1.0f : 0.0f; x.y *= y.y > 0.0f ? 1.0f : 0.0f;
                     x.z *= y.z > 0.0f ? 1.0f : 0.0f; x.w *= y.w > 0.0f ? 1.0f : 0.0f;
                 }
@@ -846,8 +854,8 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_c
 #pragma unroll 1
             for (int c0 = U.kb0; c0 < U.kb1 && ok; c0 += chunk_kb) {  // one accumulator per K-chunk
             const bool first = c0 == U.kb0 && U.part == 0, last = c0 + chunk_kb >= U.kb1;
-            SideRegs sd_now, sd_next;
-            load_side(P, first, last, row_base, lane, n0, sd_next);  // column chunk 0's, while the accumulator is still being computed
+            SideRegs sd_now, sd_next, mk_now, mk_next;
+            load_side(P, first, last, row_base, lane, n0, sd_next, mk_next);  // column chunk 0's, while the accumulator is still being computed
             if (!mbar_wait(tfull_bar(acc), acc_phase, &abort_flag, 0x300 | (16 + acc))) { ok = false; break; }
             tc_fence_after();
 #pragma unroll 1
@@ -856,10 +864,11 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_c
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN + cc * 32);
                 tmem_ld32(taddr, r);
                 sd_now = sd_next;
+                mk_now = mk_next;
                 const int64_t col0 = n0 + cc * 32;
-                if (cc + 1 < BN / 32) load_side(P, first, last, row_base, lane, col0 + 32, sd_next);
+                if (cc + 1 < BN / 32) load_side(P, first, last, row_base, lane, col0 + 32, sd_next, mk_next);
                 tmem_ld_wait();
-                emit_chunk(P, U.half, first, last, row_base, lane, col0, r, stages[warp - 2], sd_now);
+                emit_chunk(P, U.half, first, last, row_base, lane, col0, r, stages[warp - 2], sd_now, mk_now);
             }
             tc_fence_before();
             __syncwarp();
@@ -1140,8 +1149,8 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a0, const __g
 #pragma unroll 1
             for (int c0 = U.kb0; c0 < U.kb1 && ok; c0 += chunk_kb) {  // one accumulator per K-chunk
             const bool first = c0 == U.kb0 && U.part == 0, last = c0 + chunk_kb >= U.kb1;
-            SideRegs sd_now, sd_next;
-            load_side(P, first, last, row_base, lane, n0, sd_next);  // column chunk 0's, while the accumulator is still being computed
+            SideRegs sd_now, sd_next, mk_now, mk_next;
+            load_side(P, first, last, row_base, lane, n0, sd_next, mk_next);  // column chunk 0's, while the accumulator is still being computed
             if (!mbar_wait(tfull_bar(acc), acc_phase, &abort_flag, 0x700 | (16 + acc))) { ok = false; break; }
             tc_fence_after();
 #pragma unroll 1
@@ -1150,10 +1159,11 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a0, const __g
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN + cc * 32);
                 tmem_ld32(taddr, r);
                 sd_now = sd_next;
+                mk_now = mk_next;
                 const int64_t col0 = n0 + cc * 32;
-                if (cc + 1 < BN / 32) load_side(P, first, last, row_base, lane, col0 + 32, sd_next);
+                if (cc + 1 < BN / 32) load_side(P, first, last, row_base, lane, col0 + 32, sd_next, mk_next);
                 tmem_ld_wait();
-                emit_chunk(P, U.half, first, last, row_base, lane, col0, r, stages[warp - 2], sd_now);
+                emit_chunk(P, U.half, first, last, row_base, lane, col0, r, stages[warp - 2], sd_now, mk_now);
             }
             tc_fence_before();
             __syncwarp();
