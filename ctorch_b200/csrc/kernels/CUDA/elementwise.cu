@@ -191,30 +191,20 @@ __global__ void __launch_bounds__(kEwThreads) argmax_rows_kernel(const float* __
     }
 }
 
-// The same for short rows (cols <= 16, the class probabilities of the MNIST application): a group of
-// `group` lanes (a power of two >= cols) per row, so a warp takes 32 / group consecutive rows whose
-// elements are neighbours in memory, instead of one row on 10 of its 32 lanes.
-__global__ void __launch_bounds__(kEwThreads) argmax_short_rows_kernel(const float* __restrict__ x, int64_t rows, int cols, int group, float init, float* __restrict__ out) {
-    const int lane = threadIdx.x & 31, sub = lane & (group - 1), per_warp = 32 / group;
-    const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-    const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
-    for (int64_t r0 = warp * per_warp; r0 < rows; r0 += nwarps * per_warp) {
-        const int64_t r = r0 + lane / group;
+// The same for short rows (cols <= 16, the class probabilities of the MNIST application): a thread per
+// row walks its few elements in order -- exactly the reference's loop, no shuffles; the 32 rows of a warp
+// are neighbours in memory, so the lines one load instruction touches are used up by the next few.
+__global__ void __launch_bounds__(kEwThreads) argmax_short_rows_kernel(const float* __restrict__ x, int64_t rows, int cols, float init, float* __restrict__ out) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t r = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; r < rows; r += stride) {
+        const float* row = x + r * cols;
         float best = init;
         int idx = 0;
-        bool found = false;
-        if (r < rows && sub < cols) {
-            const float v = __ldg(x + r * cols + sub);
-            if (v > init) { best = v; idx = sub; found = true; }
+        for (int j = 0; j < cols; ++j) {
+            const float v = __ldg(row + j);
+            if (v > best) { best = v; idx = j; }
         }
-        for (int o = group >> 1; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-            const bool of = __shfl_xor_sync(0xffffffffu, found ? 1 : 0, o) != 0;
-            const bool take = of && (!found || ob > best || (ob == best && oi < idx));
-            if (take) { best = ob; idx = oi; found = true; }
-        }
-        if (sub == 0 && r < rows) out[r] = found ? static_cast<float>(idx) : 0.0f;
+        out[r] = static_cast<float>(idx);
     }
 }
 
@@ -341,9 +331,7 @@ ctk_status ctk_argmax_rows_f32(const float* x, int64_t rows, int64_t cols, float
     if (rows == 0) return CTK_OK;
     CTK_REQUIRE(out_index && (x || cols == 0), "ctk_argmax_rows_f32: null pointer");
     if (cols >= 1 && cols <= 16) {
-        int group = 1;
-        while (group < cols) group <<= 1;
-        argmax_short_rows_kernel<<<ctk_stream_grid(rows * group, kEwThreads, 8), kEwThreads, 0, as_stream(stream)>>>(x, rows, static_cast<int>(cols), group, init, out_index);
+        argmax_short_rows_kernel<<<ctk_stream_grid(rows, kEwThreads, 8), kEwThreads, 0, as_stream(stream)>>>(x, rows, static_cast<int>(cols), init, out_index);
     } else {
         argmax_rows_kernel<<<ctk_stream_grid(rows * 32, kEwThreads, 8), kEwThreads, 0, as_stream(stream)>>>(x, rows, cols, init, out_index);
     }
