@@ -1229,40 +1229,72 @@ ctk_status get_encoder(EncodeTiledFn* out) {
     return CTK_OK;
 }
 
+// Encoded tensor maps, remembered.  An encoding is a pure function of (base, extents, pitch, box, layout),
+// and cuTensorMapEncodeTiled costs about a microsecond -- six of them per product is most of the host time
+// of a small product called again and again on the same buffers (the layers of a small network).  A small
+// direct-mapped table per thread; a colliding or new key is simply encoded again.
+struct MapKey {
+    const void* base;
+    int64_t inner, outer, ld;
+    int box_outer, flags;  // flags: bit 0 MN-major, bit 1 bf16
+    bool operator==(const MapKey& o) const {
+        return base == o.base && inner == o.inner && outer == o.outer && ld == o.ld && box_outer == o.box_outer && flags == o.flags;
+    }
+};
+struct MapSlot {
+    MapKey key{nullptr, 0, 0, 0, 0, -1};
+    CUtensorMap map;
+};
+constexpr int kMapSlots = 256;
+thread_local MapSlot t_map_cache[kMapSlots];
+
+ctk_status encode_map(CUtensorMap* map, const MapKey& k) {
+    uint64_t h = reinterpret_cast<uintptr_t>(k.base) >> 4;
+    h ^= static_cast<uint64_t>(k.inner) * 0x9E3779B97F4A7C15ull ^ static_cast<uint64_t>(k.outer) * 0xC2B2AE3D27D4EB4Full ^
+         static_cast<uint64_t>(k.ld) * 0x165667B19E3779F9ull ^ static_cast<uint64_t>(k.box_outer * 4 + k.flags);
+    MapSlot& slot = t_map_cache[(h ^ (h >> 29)) % kMapSlots];
+    if (slot.key == k) {
+        *map = slot.map;
+        return CTK_OK;
+    }
+    EncodeTiledFn enc;
+    ctk_status st = get_encoder(&enc);
+    if (st) return st;
+    const bool mn_major = (k.flags & 1) != 0, bf16 = (k.flags & 2) != 0;
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(k.inner), static_cast<cuuint64_t>(k.outer)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(k.ld) * (bf16 ? 2 : 4)};
+    cuuint32_t estr[2] = {1u, 1u};
+    cuuint32_t box[2];
+    CUtensorMapSwizzle swz;
+    if (!bf16) {
+        box[0] = 32u;
+        box[1] = static_cast<cuuint32_t>(k.box_outer);
+        swz = mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
+    } else {
+        box[0] = mn_major ? 64u : 32u;
+        box[1] = static_cast<cuuint32_t>(mn_major ? 32 : k.box_outer);
+        swz = mn_major ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+    }
+    CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(k.base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(CTK_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(r)));
+    slot.key = k;
+    slot.map = *map;
+    return CTK_OK;
+}
+
 // 2-D fp32 tensor {inner (contiguous), outer} with row pitch ld elements; box {32, box_outer};
 // 128-byte swizzle (16-byte chunks for a K-major operand, 32-byte atoms for an MN-major one);
 // out-of-range elements read as zero.
 ctk_status make_map(CUtensorMap* map, const float* base, int64_t inner, int64_t outer, int64_t ld, int box_outer, bool mn_major) {
-    EncodeTiledFn enc;
-    ctk_status st = get_encoder(&enc);
-    if (st) return st;
-    cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
-    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 4};
-    cuuint32_t box[2] = {32u, static_cast<cuuint32_t>(box_outer)};
-    cuuint32_t estr[2] = {1u, 1u};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
-                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(CTK_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(r)));
-    return CTK_OK;
+    return encode_map(map, MapKey{base, inner, outer, ld, box_outer, mn_major ? 1 : 0});
 }
 
 // The same operand as bf16 ([outer, ld] elements of 2 bytes): box {32, box_outer} with the 64-byte
 // swizzle for a K-major operand (a k-block is 32 elements = 64 bytes), {64, 32} with the 128-byte
 // swizzle per 64-wide column group for an MN-major one.
 ctk_status make_map16(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int64_t ld, int box_outer, bool mn_major) {
-    EncodeTiledFn enc;
-    ctk_status st = get_encoder(&enc);
-    if (st) return st;
-    cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
-    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
-    cuuint32_t box[2] = {mn_major ? 64u : 32u, static_cast<cuuint32_t>(mn_major ? 32 : box_outer)};
-    cuuint32_t estr[2] = {1u, 1u};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     mn_major ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(CTK_ERR_CUDA, "cuTensorMapEncodeTiled (bf16) failed with code " + std::to_string(static_cast<int>(r)));
-    return CTK_OK;
+    return encode_map(map, MapKey{base, inner, outer, ld, box_outer, (mn_major ? 1 : 0) | 2});
 }
 
 // One operand as the tensor-core path sees it.

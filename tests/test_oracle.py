@@ -194,3 +194,27 @@ def test_softmax_down_the_columns_matches_reference_library(orc):
         y2, dx2 = orc.softmax_dim0(x, g)
         assert np.array_equal(y, y2) and np.array_equal(dx, dx2), shape
         assert np.array_equal(R.softmax_dim(x, 1), orc.softmax(x))
+
+
+@pytest.mark.skipif(not oracle.Reference.available(), reason="oracle/_ref not built (needs the reference checkout)")
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+def test_sampled_matmul_functions_match_whole_products_of_the_reference(orc, ta, tb):
+    """orc_matmul_entries and orc_matmul_rows (with its interchanged loops where B's rows are contiguous)
+    are what the full-size GPU tests compare with: each sampled value equals, bit for bit, the entry of
+    the whole product as the reference library computes it."""
+    ref = oracle.Reference()
+    rng = np.random.default_rng(40 + 2 * ta + tb)
+    m, k, n = 70, 130, 90
+    A = rng.standard_normal((m, k)).astype(np.float32)
+    B = rng.standard_normal((k, n)).astype(np.float32)
+    sa = A.T.copy() if ta else A
+    sb = B.T.copy() if tb else B
+    C = ref.matmul(sa, sb, ta, tb)
+    rows = np.array([0, 5, m - 1])
+    assert np.array_equal(orc.matmul_rows(sa, sb, rows, ta, tb), C[rows])
+    ri, ci = rng.integers(0, m, 300), rng.integers(0, n, 300)
+    assert np.array_equal(orc.matmul_entries(sa, sb, ri, ci, ta, tb), C[ri, ci])
+    # columns as rows of the transposed product on materialised operands (how the full-size tests take them)
+    cols = np.array([n - 1, 3])
+    got = orc.matmul_rows(np.ascontiguousarray(B[:, cols].T), np.ascontiguousarray(A.T), np.arange(2))
+    assert np.array_equal(got, C[:, cols].T)
