@@ -136,29 +136,36 @@ __global__ void __launch_bounds__(kEwThreads) onehot_kernel(const float* __restr
 
 // dst[i] = float(src[i]) / divisor, IEEE division: the pixel normalisation of the IDX image reader
 // (mnist/mnist_loader.cpp:38-40, `pixel / 255.0f`), done on the device so that images cross PCIe as
-// bytes.  16 pixels per thread where the pointers allow 128-bit accesses.
+// bytes.  A byte has 256 values: every CTA divides each of them once into a table in shared memory, so
+// the stream itself is one 4-byte load, four table reads and one 16-byte store per thread, with the
+// lanes of a warp on consecutive addresses on both sides (128 B read, 512 B written per instruction),
+// four of them in flight per thread.
 __global__ void __launch_bounds__(kEwThreads) u8_to_f32_kernel(const uint8_t* __restrict__ src, int64_t n, float divisor, float* __restrict__ dst, int vec) {
+    __shared__ float quotient[256];
+    for (int v = threadIdx.x; v < 256; v += blockDim.x) quotient[v] = __fdiv_rn(static_cast<float>(v), divisor);
+    __syncthreads();
     const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    int64_t done = 0;
     if (vec) {
-        const int64_t n16 = n >> 4;
-        for (int64_t i = tid; i < n16; i += stride) {
-            const uint4 w = __ldcs(reinterpret_cast<const uint4*>(src) + i);
-            const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+        const int64_t n4 = n >> 2;
+        const uint32_t* s = reinterpret_cast<const uint32_t*>(src);
+        float4* d = reinterpret_cast<float4*>(dst);
+        auto four = [&](uint32_t w) {
+            return make_float4(quotient[w & 0xffu], quotient[(w >> 8) & 0xffu], quotient[(w >> 16) & 0xffu], quotient[w >> 24]);
+        };
+        int64_t i = tid;
+        for (; i + 3 * stride < n4; i += 4 * stride) {
+            uint32_t w[4];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                float4 o;
-                o.x = __fdiv_rn(static_cast<float>(words[q] & 0xffu), divisor);
-                o.y = __fdiv_rn(static_cast<float>((words[q] >> 8) & 0xffu), divisor);
-                o.z = __fdiv_rn(static_cast<float>((words[q] >> 16) & 0xffu), divisor);
-                o.w = __fdiv_rn(static_cast<float>(words[q] >> 24), divisor);
-                __stcs(reinterpret_cast<float4*>(dst) + i * 4 + q, o);
-            }
+            for (int q = 0; q < 4; ++q) w[q] = __ldcs(s + i + q * stride);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) __stcs(d + i + q * stride, four(w[q]));
         }
-        for (int64_t i = (n16 << 4) + tid; i < n; i += stride) dst[i] = __fdiv_rn(static_cast<float>(src[i]), divisor);
-    } else {
-        for (int64_t i = tid; i < n; i += stride) dst[i] = __fdiv_rn(static_cast<float>(src[i]), divisor);
+        for (; i < n4; i += stride) __stcs(d + i, four(__ldcs(s + i)));
+        done = n4 << 2;
     }
+    for (int64_t i = done + tid; i < n; i += stride) dst[i] = quotient[src[i]];
 }
 
 // out[r] = index of the first element of row r that is strictly greater than everything before it,
@@ -319,7 +326,7 @@ ctk_status ctk_u8_to_f32(const uint8_t* src, int64_t n, float divisor, float* ds
     CTK_REQUIRE(n >= 0, "ctk_u8_to_f32: negative size");
     if (n == 0) return CTK_OK;
     CTK_REQUIRE(src && dst, "ctk_u8_to_f32: null pointer");
-    const int vec = ((reinterpret_cast<uintptr_t>(src) & 15u) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) ? 1 : 0;
+    const int vec = ((reinterpret_cast<uintptr_t>(src) & 3u) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) ? 1 : 0;
     u8_to_f32_kernel<<<ctk_stream_grid((n + 15) / 16, kEwThreads, 8), kEwThreads, 0, as_stream(stream)>>>(src, n, divisor, dst, vec);
     CTK_LAUNCH_CHECK("u8_to_f32_kernel");
     return CTK_OK;

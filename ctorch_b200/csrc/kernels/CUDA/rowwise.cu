@@ -1067,20 +1067,41 @@ ctk_status launch_streamed(const RowArgs& A, ReduceScratch* s, float* loss_out, 
 // a kernel that could keep its strip on chip: this form is not on any benchmark path.
 constexpr int kColTile = 32;
 
+constexpr int kColDepth = 8;   // independent row loads a thread keeps in flight
+
 __global__ void __launch_bounds__(kColTile * kColTile) softmax_cols_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t rows, int64_t cols) {
     __shared__ float sm_m[kColTile][kColTile + 1], sm_s[kColTile][kColTile + 1];
     const int tx = threadIdx.x, ty = threadIdx.y;
     const int64_t col = static_cast<int64_t>(blockIdx.x) * kColTile + tx;
+    const int64_t step = static_cast<int64_t>(kColTile) * cols;
     float m = -INFINITY, sum = 0.0f;
-    if (col < cols)
-        for (int64_t r = ty; r < rows; r += kColTile) {
-            const float v = __ldg(x + r * cols + col);
+    if (col < cols) {
+        int64_t r = ty;
+        const float* p = x + r * cols + col;
+        for (; r + (kColDepth - 1) * kColTile < rows; r += kColDepth * kColTile, p += kColDepth * step) {
+            float v[kColDepth];
+#pragma unroll
+            for (int u = 0; u < kColDepth; ++u) v[u] = __ldg(p + u * step);
+            float mn = m;
+#pragma unroll
+            for (int u = 0; u < kColDepth; ++u) mn = fmaxf(mn, v[u]);
+            if (mn > -INFINITY) {
+                float part = 0.0f;
+#pragma unroll
+                for (int u = 0; u < kColDepth; ++u) part += fast_exp(v[u] - mn);
+                sum = sum * fast_exp(m - mn) + part;
+                m = mn;
+            }
+        }
+        for (; r < rows; r += kColTile, p += step) {
+            const float v = __ldg(p);
             const float mn = fmaxf(m, v);
             if (mn > -INFINITY) {
                 sum = sum * fast_exp(m - mn) + fast_exp(v - mn);
                 m = mn;
             }
         }
+    }
     sm_m[ty][tx] = m;
     sm_s[ty][tx] = sum;
     __syncthreads();
@@ -1091,27 +1112,63 @@ __global__ void __launch_bounds__(kColTile * kColTile) softmax_cols_kernel(const
 #pragma unroll 8
     for (int i = 0; i < kColTile; ++i) cs += sm_m[i][tx] > -INFINITY ? sm_s[i][tx] * fast_exp(sm_m[i][tx] - cm) : 0.0f;
     const float inv = 1.0f / cs;
-    if (col < cols)
-        for (int64_t r = ty; r < rows; r += kColTile) y[r * cols + col] = fast_exp(__ldg(x + r * cols + col) - cm) * inv;
+    if (col < cols) {
+        int64_t r = ty;
+        const float* p = x + r * cols + col;
+        float* q = y + r * cols + col;
+        for (; r + (kColDepth - 1) * kColTile < rows; r += kColDepth * kColTile, p += kColDepth * step, q += kColDepth * step) {
+            float v[kColDepth];
+#pragma unroll
+            for (int u = 0; u < kColDepth; ++u) v[u] = __ldg(p + u * step);
+#pragma unroll
+            for (int u = 0; u < kColDepth; ++u) q[u * step] = fast_exp(v[u] - cm) * inv;
+        }
+        for (; r < rows; r += kColTile, p += step, q += step) *q = fast_exp(__ldg(p) - cm) * inv;
+    }
 }
 
 __global__ void __launch_bounds__(kColTile * kColTile) softmax_cols_backward_kernel(const float* __restrict__ y, const float* __restrict__ g, float* __restrict__ dx, int64_t rows, int64_t cols) {
     __shared__ float sm_d[kColTile][kColTile + 1];
     const int tx = threadIdx.x, ty = threadIdx.y;
     const int64_t col = static_cast<int64_t>(blockIdx.x) * kColTile + tx;
+    const int64_t step = static_cast<int64_t>(kColTile) * cols;
+    constexpr int D = kColDepth / 2;   // two arrays per row
     float dot = 0.0f;
-    if (col < cols)
-        for (int64_t r = ty; r < rows; r += kColTile) dot += __ldg(g + r * cols + col) * __ldg(y + r * cols + col);
+    if (col < cols) {
+        int64_t r = ty;
+        int64_t i = r * cols + col;
+        for (; r + (D - 1) * kColTile < rows; r += D * kColTile, i += D * step) {
+            float a[D], b[D];
+#pragma unroll
+            for (int u = 0; u < D; ++u) {
+                a[u] = __ldg(g + i + u * step);
+                b[u] = __ldg(y + i + u * step);
+            }
+#pragma unroll
+            for (int u = 0; u < D; ++u) dot += a[u] * b[u];
+        }
+        for (; r < rows; r += kColTile, i += step) dot += __ldg(g + i) * __ldg(y + i);
+    }
     sm_d[ty][tx] = dot;
     __syncthreads();
     float cd = 0.0f;
 #pragma unroll 8
     for (int i = 0; i < kColTile; ++i) cd += sm_d[i][tx];
-    if (col < cols)
-        for (int64_t r = ty; r < rows; r += kColTile) {
-            const int64_t i = r * cols + col;
-            dx[i] = __ldg(y + i) * (__ldg(g + i) - cd);
+    if (col < cols) {
+        int64_t r = ty;
+        int64_t i = r * cols + col;
+        for (; r + (D - 1) * kColTile < rows; r += D * kColTile, i += D * step) {
+            float a[D], b[D];
+#pragma unroll
+            for (int u = 0; u < D; ++u) {
+                a[u] = __ldg(g + i + u * step);
+                b[u] = __ldg(y + i + u * step);
+            }
+#pragma unroll
+            for (int u = 0; u < D; ++u) dx[i + u * step] = b[u] * (a[u] - cd);
         }
+        for (; r < rows; r += kColTile, i += step) dx[i] = __ldg(y + i) * (__ldg(g + i) - cd);
+    }
 }
 
 template <int ALG>

@@ -107,7 +107,7 @@ def test_against_golden_fixture(cb, golden):
     assert np.abs(cb.ops.cross_entropy_backward(z, t).numpy() - G["ka.ce.grad"]).max() < 1e-4
 
 
-@pytest.mark.parametrize("rows,cols", [(1, 1), (2, 3), (37, 19), (1000, 10), (64, 33), (5, 1000), (4099, 70)])
+@pytest.mark.parametrize("rows,cols", [(1, 1), (2, 3), (37, 19), (1000, 10), (64, 33), (5, 1000), (4099, 70), (257, 5), (8192, 64)])
 def test_softmax_down_the_columns(cb, orc, rows, cols):
     """Tensor::softmax(0) (src/Tensor.cpp:1728-1743) and its backward (src/AutoDiff.cpp:1473-1484),
     through the kernels and through the front end's tape."""

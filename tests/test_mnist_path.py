@@ -105,7 +105,7 @@ def test_loader_on_the_device_is_bit_exact(cb, mnist_dir, golden):
 
 @pytest.mark.gpu
 def test_byte_to_float_kernel_all_values_and_tails(cb):
-    for n, off in ((256, 0), (1000003, 0), (77, 1), (4099, 3)):
+    for n, off in ((256, 0), (1000003, 0), (77, 1), (4099, 3), (20000003, 0), (6000001, 4)):   # the last two reach the four-deep loop
         src = (np.arange(n + off) % 256).astype(np.uint8)
         d = cb.to_device(src, np.uint8)
         out = cb.ops.u8_to_f32(d.view(off, (n,)), 255.0).numpy()
