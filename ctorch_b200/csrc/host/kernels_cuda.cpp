@@ -115,7 +115,9 @@ Tensor MatMul_CUDA_kernel(const Tensor& a, const Tensor& b) {
         const char* e = std::getenv("CTORCH_KEEP_SPLITS");
         return !(e && e[0] == '0');
     }();
-    if (!keep_splits || ctk_get_matmul_mode() != CTK_MATMUL_3XTF32 || m < 2 || n < 2 || k < 2) {
+    // (path 3, a narrow output on the CUDA cores, reads the operands as they are: nothing to keep)
+    if (!keep_splits || ctk_get_matmul_mode() != CTK_MATMUL_3XTF32 || m < 2 || n < 2 || k < 2 ||
+        ctk_matmul_path(a.data<float>(), b.data<float>(), m, n, k, sa0, sa1, sb0, sb1, CTK_MATMUL_3XTF32) == 3) {
         cuda_check(ctk_matmul_f32(a.data<float>(), b.data<float>(), r.data<float>(), m, n, k, sa0, sa1, sb0, sb1, -1, nullptr, current_stream()), who);
         return r;
     }

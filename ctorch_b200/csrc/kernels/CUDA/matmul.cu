@@ -1491,6 +1491,198 @@ static bool skinny_k_ok(const float* a, const float* b, const float* c, int64_t 
            a != nullptr && b != nullptr;
 }
 
+// ---- a narrow output (N <= 16) over a long contraction: CUDA cores, bound by A's bytes ---------------
+// The 10-class layer: logits = H.W ([B,H].[H,10]) and dW = H^T.dY ([H,B].[B,10]).  On the tensor-core
+// kernel these are 64-wide tiles of which ten columns are used, a handful of tiles each walking the whole
+// contraction, and A has to be read as its 8-byte split.  Here A is read once as fp32 (16-byte loads,
+// several in flight per thread), B sits in shared memory, every product is an fp32 FMA and the sums are
+// fp32 -- closer to the float64 result than the reference's own sequential fp32 loop.
+//   narrow_rows_kernel: A [m, k] with unit stride along k.  A warp owns four rows; a lane walks k in
+//     steps of 128 with four consecutive k per load and B transposed in shared memory ([n][k-chunk], the
+//     same four k per 16-byte read); lanes are summed by shuffles at the end.
+//   narrow_cols_kernel: A [m, k] with unit stride along m (the t() view of a [k, m] array).  A thread owns
+//     four consecutive m and walks down a range of k, B's rows broadcast from shared memory; the grid's y
+//     dimension splits k, the partial results land in a workspace [parts][m][n] and narrow_sum_kernel adds
+//     them in part order (a fixed order: two calls give the same bits).
+constexpr int SN_MAXN = 16, SN_THREADS = 256, SN_WARP_ROWS = 4, SN_CTA_ROWS = (SN_THREADS / 32) * SN_WARP_ROWS;
+constexpr int SN_KC = 512, SN_PITCH = SN_KC + 4;   // (the pad spreads the transposed staging writes over the banks)
+template <int NP>
+__global__ void __launch_bounds__(SN_THREADS) narrow_rows_kernel(const float* __restrict__ a, int64_t lda, const float* __restrict__ b, int64_t sb0, int64_t sb1,
+                                                                float* __restrict__ c, int64_t m, int n, int64_t k) {
+    __shared__ __align__(16) float bt[NP * SN_PITCH];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t r0 = (static_cast<int64_t>(blockIdx.x) * (SN_THREADS / 32) + warp) * SN_WARP_ROWS;
+    float acc[SN_WARP_ROWS][NP];
+#pragma unroll
+    for (int r = 0; r < SN_WARP_ROWS; ++r)
+#pragma unroll
+        for (int j = 0; j < NP; ++j) acc[r][j] = 0.0f;
+    const float* rowp[SN_WARP_ROWS];
+#pragma unroll
+    for (int r = 0; r < SN_WARP_ROWS; ++r) rowp[r] = a + (r0 + r < m ? r0 + r : m - 1) * lda;   // (rows past the end re-read the last row; not stored)
+    for (int64_t k0 = 0; k0 < k; k0 += SN_KC) {
+        const int kc = static_cast<int>(k - k0 < SN_KC ? k - k0 : SN_KC);
+        __syncthreads();
+        for (int i = threadIdx.x; i < kc * NP; i += SN_THREADS) {
+            const int kk = i / NP, j = i - kk * NP;
+            bt[j * SN_PITCH + kk] = j < n ? __ldg(b + (k0 + kk) * sb0 + j * sb1) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll 2
+        for (int kk = 4 * lane; kk < kc; kk += 128) {
+            float4 av[SN_WARP_ROWS];
+#pragma unroll
+            for (int r = 0; r < SN_WARP_ROWS; ++r) av[r] = __ldcs(reinterpret_cast<const float4*>(rowp[r] + k0 + kk));
+#pragma unroll
+            for (int j = 0; j < NP; ++j) {
+                const float4 bv = *reinterpret_cast<const float4*>(&bt[j * SN_PITCH + kk]);
+#pragma unroll
+                for (int r = 0; r < SN_WARP_ROWS; ++r) {
+                    acc[r][j] = fmaf(av[r].x, bv.x, acc[r][j]);
+                    acc[r][j] = fmaf(av[r].y, bv.y, acc[r][j]);
+                    acc[r][j] = fmaf(av[r].z, bv.z, acc[r][j]);
+                    acc[r][j] = fmaf(av[r].w, bv.w, acc[r][j]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < SN_WARP_ROWS; ++r) {
+        float mine = 0.0f;
+#pragma unroll
+        for (int j = 0; j < NP; ++j) {
+            float v = acc[r][j];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == j) mine = v;
+        }
+        if (lane < n && r0 + r < m) c[(r0 + r) * n + lane] = mine;
+    }
+}
+
+constexpr int SG_THREADS = 128, SG_KC = 128, SG_DEPTH = 8;
+template <int NP>
+__global__ void __launch_bounds__(SG_THREADS) narrow_cols_kernel(const float* __restrict__ a, int64_t lda, const float* __restrict__ b, int64_t sb0, int64_t sb1,
+                                                                float* __restrict__ part, int64_t m, int n, int64_t k, int64_t k_per_part) {
+    __shared__ __align__(16) float bs[SG_KC * NP];
+    const int64_t i0 = (static_cast<int64_t>(blockIdx.x) * SG_THREADS + threadIdx.x) * 4;
+    const bool live = i0 < m;   // (m is a multiple of 4; no early return: every thread takes part in staging B)
+    const int64_t kb = static_cast<int64_t>(blockIdx.y) * k_per_part;
+    const int64_t ke = kb + k_per_part < k ? kb + k_per_part : k;
+    float acc[4][NP];
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int j = 0; j < NP; ++j) acc[q][j] = 0.0f;
+    auto fold = [&](const float4& av, int kk) {
+#pragma unroll
+        for (int j4 = 0; j4 < NP / 4; ++j4) {
+            const float4 bv = *reinterpret_cast<const float4*>(&bs[kk * NP + 4 * j4]);
+            const float bj[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                acc[0][4 * j4 + t] = fmaf(av.x, bj[t], acc[0][4 * j4 + t]);
+                acc[1][4 * j4 + t] = fmaf(av.y, bj[t], acc[1][4 * j4 + t]);
+                acc[2][4 * j4 + t] = fmaf(av.z, bj[t], acc[2][4 * j4 + t]);
+                acc[3][4 * j4 + t] = fmaf(av.w, bj[t], acc[3][4 * j4 + t]);
+            }
+        }
+    };
+    for (int64_t k0 = kb; k0 < ke; k0 += SG_KC) {
+        const int kc = static_cast<int>(ke - k0 < SG_KC ? ke - k0 : SG_KC);
+        __syncthreads();
+        for (int i = threadIdx.x; i < kc * NP; i += SG_THREADS) {
+            const int kk = i / NP, j = i - kk * NP;
+            bs[i] = j < n ? __ldg(b + (k0 + kk) * sb0 + j * sb1) : 0.0f;
+        }
+        __syncthreads();
+        if (live) {
+            const float* p = a + k0 * lda + i0;
+            int kk = 0;
+            for (; kk + SG_DEPTH <= kc; kk += SG_DEPTH) {
+                float4 av[SG_DEPTH];
+#pragma unroll
+                for (int u = 0; u < SG_DEPTH; ++u) av[u] = __ldcs(reinterpret_cast<const float4*>(p + (kk + u) * lda));
+#pragma unroll
+                for (int u = 0; u < SG_DEPTH; ++u) fold(av[u], kk + u);
+            }
+            for (; kk < kc; ++kk) fold(__ldcs(reinterpret_cast<const float4*>(p + kk * lda)), kk);
+        }
+    }
+    if (live) {
+        float* o = part + static_cast<int64_t>(blockIdx.y) * m * n + i0 * n;
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+#pragma unroll
+            for (int j = 0; j < NP; ++j)
+                if (j < n) o[q * n + j] = acc[q][j];
+    }
+}
+
+__global__ void __launch_bounds__(256) narrow_sum_kernel(const float* __restrict__ part, int parts, int64_t count, float* __restrict__ c) {
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        float v = __ldg(part + i);
+        for (int s = 1; s < parts; ++s) v += __ldg(part + s * count + i);
+        c[i] = v;
+    }
+}
+
+// The shapes that take it: fp32-accurate mode, N <= 16, A with a unit stride and whole 16-byte pieces
+// along it, and an A of at least 2^20 elements with a contraction of at least 256 (smaller products
+// stay on the tensor-core kernel).  Returns 0 (no), 1 (A along k: narrow_rows) or 2 (A along m: narrow_cols).
+static int narrow_n_form(const float* a, const float* b, int64_t m, int64_t n, int64_t k, int64_t sa0, int64_t sa1, int md) {
+    if (md != CTK_MATMUL_3XTF32 || n < 1 || n > SN_MAXN || k < 256 || m * k < (int64_t(1) << 20) || a == nullptr || b == nullptr) return 0;
+    if ((reinterpret_cast<uintptr_t>(a) & 15u) != 0) return 0;
+    if (sa1 == 1 && sa0 >= k && sa0 % 4 == 0 && k % 4 == 0 && (m + SN_CTA_ROWS - 1) / SN_CTA_ROWS < (int64_t(1) << 31)) return 1;
+    if (sa0 == 1 && sa1 >= m && sa1 % 4 == 0 && m % 4 == 0 && (m / 4 + SG_THREADS - 1) / SG_THREADS < (int64_t(1) << 31)) return 2;
+    return 0;
+}
+
+// How narrow_cols splits the contraction: enough parts for about four CTAs per SM, each at least 64 long
+// and a multiple of SG_DEPTH.
+static void narrow_cols_parts(int64_t m, int64_t k, int* parts, int64_t* k_per_part) {
+    const int64_t col_ctas = (m / 4 + SG_THREADS - 1) / SG_THREADS;
+    int64_t want = (4 * static_cast<int64_t>(ctk::sm_count()) + col_ctas - 1) / col_ctas;
+    if (want > k / 64) want = k / 64;
+    if (want < 1) want = 1;
+    if (want > 65535) want = 65535;
+    int64_t per = (k + want - 1) / want;
+    per = (per + SG_DEPTH - 1) / SG_DEPTH * SG_DEPTH;
+    *k_per_part = per;
+    *parts = static_cast<int>((k + per - 1) / per);
+}
+
+template <int NP>
+static ctk_status launch_narrow(int form, const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k, int64_t sa0, int64_t sa1,
+                                int64_t sb0, int64_t sb1, void* workspace, cudaStream_t st) {
+    if (form == 1) {
+        const int64_t grid = (m + SN_CTA_ROWS - 1) / SN_CTA_ROWS;
+        narrow_rows_kernel<NP><<<static_cast<unsigned>(grid), SN_THREADS, 0, st>>>(a, sa0, b, sb0, sb1, c, m, static_cast<int>(n), k);
+        CTK_LAUNCH_CHECK("narrow_rows_kernel");
+        return CTK_OK;
+    }
+    int parts = 1;
+    int64_t per = k;
+    narrow_cols_parts(m, k, &parts, &per);
+    float* part = c;
+    if (parts > 1) {
+        void* ws = workspace;   // (a caller's workspace is sized for the operands' splits: at least 8 bytes per element of A)
+        if (!ws) {
+            ctk_status rc = device_scratch(1, static_cast<size_t>(parts) * m * n * sizeof(float), &ws);
+            if (rc) return rc;
+        }
+        part = static_cast<float*>(ws);
+    }
+    dim3 grid(static_cast<unsigned>((m / 4 + SG_THREADS - 1) / SG_THREADS), static_cast<unsigned>(parts));
+    narrow_cols_kernel<NP><<<grid, SG_THREADS, 0, st>>>(a, sa1, b, sb0, sb1, part, m, static_cast<int>(n), k, per);
+    CTK_LAUNCH_CHECK("narrow_cols_kernel");
+    if (parts > 1) {
+        narrow_sum_kernel<<<ctk_stream_grid(m * n, 256, 8), 256, 0, st>>>(part, parts, m * n, c);
+        CTK_LAUNCH_CHECK("narrow_sum_kernel");
+    }
+    return CTK_OK;
+}
+
 int g_default_mode = CTK_MATMUL_3XTF32;
 // Which tensor-core path carries the two correction terms of mode CTK_MATMUL_3XTF32:
 // 0 = TF32 (three TF32 products), 1 = bf16 (one TF32 product + two bf16 products; the default).
@@ -1677,6 +1869,7 @@ size_t ctk_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k, int mode) {
 int ctk_matmul_path(const float* a, const float* b, int64_t m, int64_t n, int64_t k, int64_t sa0, int64_t sa1,
                     int64_t sb0, int64_t sb1, int mode) {
     if (skinny_k_ok(a, b, nullptr, m, n, k, sa0, sa1, sb0, sb1, resolve_mode(mode))) return 2;
+    if (narrow_n_form(a, b, m, n, k, sa0, sa1, resolve_mode(mode))) return 3;
     return choose_path(a, b, m, n, k, sa0, sa1, sb0, sb1, mode, nullptr, nullptr);
 }
 
@@ -1777,8 +1970,17 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
         return CTK_OK;
     }
 
-    tc::Operand A, B;
     const bool fused = fe.bias != nullptr || fe.relu || fe.mask != nullptr || fe.c_split != nullptr;
+    if (!fused) {
+        const int form = narrow_n_form(a, b, m, n, k, sa0, sa1, md);
+        if (form != 0) {
+            if (n <= 4) return launch_narrow<4>(form, a, b, c, m, n, k, sa0, sa1, sb0, sb1, workspace, st);
+            if (n <= 8) return launch_narrow<8>(form, a, b, c, m, n, k, sa0, sa1, sb0, sb1, workspace, st);
+            if (n <= 12) return launch_narrow<12>(form, a, b, c, m, n, k, sa0, sa1, sb0, sb1, workspace, st);
+            return launch_narrow<16>(form, a, b, c, m, n, k, sa0, sa1, sb0, sb1, workspace, st);
+        }
+    }
+    tc::Operand A, B;
     if (choose_path(a, b, m, n, k, sa0, sa1, sb0, sb1, md, &A, &B) == 1) {
         if (fused) return fail(CTK_ERR_INVALID, "fused MatMul: the operands need the tensor-core path (a unit stride each)");
         dim3 grid(static_cast<unsigned>((n + SM_TILE - 1) / SM_TILE), static_cast<unsigned>((m + SM_TILE - 1) / SM_TILE));

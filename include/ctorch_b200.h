@@ -368,7 +368,12 @@ ctk_status ctk_matmul_3xtf32_noalloc_f32(const float* a, const float* b, float* 
  * request), 2 the short-contraction kernel (3xTF32 mode, K <= 16, both operands K-major and contiguous,
  * n % 4 == 0, at least 2^20 outputs: one thread per four output columns on the CUDA cores, products and
  * sums rounded one by one in l order -- bit-identical to MatMul_BASIC_kernel.cpp:41-50 -- and bound by
- * the output's bytes; takes the mask and split forms of ctk_matmul_3xtf32_fused_f32, not bias / ReLU). */
+ * the output's bytes; takes the mask and split forms of ctk_matmul_3xtf32_fused_f32, not bias / ReLU),
+ * 3 the narrow-output kernels (3xTF32 mode, n <= 16, k >= 256, at least 2^20 elements of A, A 16-byte
+ * aligned with a unit stride and whole 16-byte pieces along it, no fused epilogue: A read once as fp32
+ * on the CUDA cores, fp32 FMAs and fp32 sums in a fixed order, bound by A's bytes -- the 10-class
+ * layer's logits and weight gradient; within the mode's 1e-4 of MatMul_BASIC_kernel.cpp:41-50, not
+ * bit-identical to it). */
 int ctk_matmul_path(const float* a, const float* b, int64_t m, int64_t n, int64_t k,
                     int64_t sa0, int64_t sa1, int64_t sb0, int64_t sb1, int mode);
 /* Per-launch timing of the tensor-core kernel with CUDA events on the launching stream (off by

@@ -316,6 +316,47 @@ def test_sgd_update_with_split_equals_update_then_split(cb, outer, inner):
         cb.ops.sgd_update_split(cb.to_device(p0[:, :inner - 1].copy()), dg, 0.1)   # rows not 16-byte aligned
 
 
+@pytest.mark.parametrize("m,k,n,ta,tb", [
+    (8192, 4096, 10, False, False),    # the logits of the 10-class layer
+    (4096, 8192, 10, True, False),     # its weight gradient: H^T.dY
+    (1027, 1028, 1, False, False), (2050, 516, 3, False, True), (4100, 260, 16, False, False), (33, 32768, 7, False, False),
+    (1028, 1027, 1, True, False), (516, 2050, 13, True, True), (4096, 257, 16, True, False), (2052, 70000, 4, True, False),
+])
+def test_narrow_output_kernels(cb, orc, m, k, n, ta, tb):
+    """N <= 16 over a long contraction (the 10-class layer's logits and weight gradient): the CUDA-core
+    kernels that read A once as fp32 -- against float64, against sampled rows of the oracle's recurrence,
+    and bit for bit against a second call (the partial sums over k are added in a fixed order)."""
+    A, B, _ = _mats(m, k, n, 11)
+    sa = A.T.copy() if ta else A
+    sb = B.T.copy() if tb else B
+    dA, dB = cb.to_device(sa), cb.to_device(sb)
+    assert cb.ops.matmul_path(dA, dB, ta, tb, "3xtf32") == 3
+    C = cb.ops.matmul(dA, dB, ta, tb, "3xtf32").numpy()
+    again = cb.ops.matmul(dA, dB, ta, tb, "3xtf32").numpy()
+    assert_exact(again, C, "two calls, same bits")
+    assert_matmul_close(C, A.astype(np.float64) @ B.astype(np.float64), 1e-5, f"{m}x{k}x{n} vs float64")
+    rows = np.asarray([0, m // 2, m - 1])
+    assert_matmul_close(C[rows], orc.matmul_rows(sa, sb, rows, ta, tb), 1e-4, "sampled rows of the reference's recurrence")
+    assert cb.ops.matmul_path(dA, dB, ta, tb, "tf32") != 3, "only the fp32-accurate mode"
+
+
+def test_narrow_output_kernels_leave_the_other_shapes_alone(cb, orc):
+    """An A that does not start on a 16-byte boundary, rows that are not whole 16-byte pieces, a short
+    contraction, a small A or a wider output stay on the tensor-core kernel -- with the same result."""
+    m, k, n = 2048, 1024, 10
+    A, B, _ = _mats(m, k, n, 12)
+    flat = cb.to_device(np.concatenate([np.zeros(1, np.float32), A.ravel()]))
+    shifted = flat.view(1, (m, k))
+    dB = cb.to_device(B)
+    assert cb.ops.matmul_path(cb.to_device(A), dB, False, False, "3xtf32") == 3
+    assert cb.ops.matmul_path(shifted, dB, False, False, "3xtf32") == 0
+    assert_matmul_close(cb.ops.matmul(shifted, dB, mode="3xtf32").numpy(), A.astype(np.float64) @ B.astype(np.float64), 1e-4, "unaligned A")
+    for mm, kk, nn in ((2048, 1022, 10), (8192, 128, 10), (512, 1024, 10), (2048, 1024, 17)):
+        a, b, _ = _mats(mm, kk, nn, 13)
+        assert cb.ops.matmul_path(cb.to_device(a), cb.to_device(b), False, False, "3xtf32") == 0, (mm, kk, nn)
+    _check_status(cb)
+
+
 @pytest.mark.parametrize("m,k,n", [(8192, 10, 4096), (2048, 16, 512), (4099, 1, 256), (1030, 7, 1020)])
 def test_short_contraction_kernel_is_the_reference_recurrence(cb, orc, m, k, n):
     """K <= 16 with a large output (dX of the 10-class layer): the CUDA-core kernel, whose products and
