@@ -1494,73 +1494,101 @@ static bool skinny_k_ok(const float* a, const float* b, const float* c, int64_t 
 // ---- a narrow output (N <= 16) over a long contraction: CUDA cores, bound by A's bytes ---------------
 // The 10-class layer: logits = H.W ([B,H].[H,10]) and dW = H^T.dY ([H,B].[B,10]).  On the tensor-core
 // kernel these are 64-wide tiles of which ten columns are used, a handful of tiles each walking the whole
-// contraction, and A has to be read as its 8-byte split.  Here A is read once as fp32 (16-byte loads,
-// several in flight per thread), B sits in shared memory, every product is an fp32 FMA and the sums are
-// fp32 -- closer to the float64 result than the reference's own sequential fp32 loop.
-//   narrow_rows_kernel: A [m, k] with unit stride along k.  A warp owns four rows; a lane walks k in
-//     steps of 128 with four consecutive k per load and B transposed in shared memory ([n][k-chunk], the
-//     same four k per 16-byte read); lanes are summed by shuffles at the end.
+// contraction, and A has to be read as its 8-byte split.  Here A is read once as fp32 (16-byte loads, the
+// next ones always in flight while the current ones are multiplied), B sits in shared memory, every
+// product is an fp32 FMA and the sums are fp32 -- closer to the float64 result than the reference's own
+// sequential fp32 loop.  Both kernels split the contraction over the grid's y dimension; the partial
+// results land in a workspace [parts][m][n] and narrow_sum_kernel adds them in part order (a fixed order:
+// two calls give the same bits).  With one part they write C themselves.
+//   narrow_rows_kernel: A [m, k] with unit stride along k.  A CTA keeps its 512 k of B transposed in shared
+//     memory for its whole life and walks down a range of rows; a warp takes four rows at a time, a lane
+//     four consecutive k per load (the same four k of B in one 16-byte read), and the lanes' sums are
+//     folded across the warp, halving the values a lane holds at every step.
 //   narrow_cols_kernel: A [m, k] with unit stride along m (the t() view of a [k, m] array).  A thread owns
-//     four consecutive m and walks down a range of k, B's rows broadcast from shared memory; the grid's y
-//     dimension splits k, the partial results land in a workspace [parts][m][n] and narrow_sum_kernel adds
-//     them in part order (a fixed order: two calls give the same bits).
-constexpr int SN_MAXN = 16, SN_THREADS = 256, SN_WARP_ROWS = 4, SN_CTA_ROWS = (SN_THREADS / 32) * SN_WARP_ROWS;
-constexpr int SN_KC = 512, SN_PITCH = SN_KC + 4;   // (the pad spreads the transposed staging writes over the banks)
+//     four consecutive m and walks down its part of k, B's rows broadcast from shared memory.
+constexpr int SN_MAXN = 16, SN_THREADS = 256, SN_WARPS = SN_THREADS / 32, SN_WARP_ROWS = 4;
+constexpr int SN_KS = 512, SN_PITCH = SN_KS + 4;   // k per CTA; the pad spreads the transposed staging writes over the banks
 template <int NP>
-__global__ void __launch_bounds__(SN_THREADS) narrow_rows_kernel(const float* __restrict__ a, int64_t lda, const float* __restrict__ b, int64_t sb0, int64_t sb1,
-                                                                float* __restrict__ c, int64_t m, int n, int64_t k) {
+__global__ void __launch_bounds__(SN_THREADS, NP <= 12 ? 2 : 1) narrow_rows_kernel(const float* __restrict__ a, int64_t lda, const float* __restrict__ b, int64_t sb0, int64_t sb1,
+                                                                float* __restrict__ part, int64_t m, int n, int64_t k, int64_t rows_per_cta) {
     __shared__ __align__(16) float bt[NP * SN_PITCH];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t r0 = (static_cast<int64_t>(blockIdx.x) * (SN_THREADS / 32) + warp) * SN_WARP_ROWS;
-    float acc[SN_WARP_ROWS][NP];
+    const int64_t k0 = static_cast<int64_t>(blockIdx.y) * SN_KS;
+    const int kc = static_cast<int>(k - k0 < SN_KS ? k - k0 : SN_KS);
+    const int64_t row_begin = static_cast<int64_t>(blockIdx.x) * rows_per_cta;
+    const int64_t row_end = row_begin + rows_per_cta < m ? row_begin + rows_per_cta : m;
+    float* out = part + static_cast<int64_t>(blockIdx.y) * m * n;
+    // rows [r, r + 4) at k-step t (k = k0 + 4 lane + 128 t): four 16-byte loads; past the end zeros / the last row again
+    auto load = [&](int64_t r, int t, float4 (&dst)[SN_WARP_ROWS]) {
+        const int kk = 4 * lane + 128 * t;
 #pragma unroll
-    for (int r = 0; r < SN_WARP_ROWS; ++r)
-#pragma unroll
-        for (int j = 0; j < NP; ++j) acc[r][j] = 0.0f;
-    const float* rowp[SN_WARP_ROWS];
-#pragma unroll
-    for (int r = 0; r < SN_WARP_ROWS; ++r) rowp[r] = a + (r0 + r < m ? r0 + r : m - 1) * lda;   // (rows past the end re-read the last row; not stored)
-    for (int64_t k0 = 0; k0 < k; k0 += SN_KC) {
-        const int kc = static_cast<int>(k - k0 < SN_KC ? k - k0 : SN_KC);
-        __syncthreads();
-        for (int i = threadIdx.x; i < kc * NP; i += SN_THREADS) {
-            const int kk = i / NP, j = i - kk * NP;
-            bt[j * SN_PITCH + kk] = j < n ? __ldg(b + (k0 + kk) * sb0 + j * sb1) : 0.0f;
+        for (int q = 0; q < SN_WARP_ROWS; ++q) {
+            const int64_t row = r + q < m ? r + q : m - 1;
+            dst[q] = (kk < kc && r < row_end) ? __ldcs(reinterpret_cast<const float4*>(a + row * lda + k0 + kk)) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        __syncthreads();
-#pragma unroll 2
-        for (int kk = 4 * lane; kk < kc; kk += 128) {
-            float4 av[SN_WARP_ROWS];
+    };
+    float4 a0[SN_WARP_ROWS], a1[SN_WARP_ROWS];
+    int64_t r = row_begin + warp * SN_WARP_ROWS;
+    load(r, 0, a0);   // in flight while B is staged
+    for (int i = threadIdx.x; i < SN_KS * NP; i += SN_THREADS) {
+        const int kk = i / NP, j = i - kk * NP;
+        bt[j * SN_PITCH + kk] = (j < n && kk < kc) ? __ldg(b + (k0 + kk) * sb0 + j * sb1) : 0.0f;
+    }
+    __syncthreads();
+    float acc[SN_WARP_ROWS * NP];
+    auto fold = [&](const float4 (&av)[SN_WARP_ROWS], int t) {
+        const int kk = 4 * lane + 128 * t;
 #pragma unroll
-            for (int r = 0; r < SN_WARP_ROWS; ++r) av[r] = __ldcs(reinterpret_cast<const float4*>(rowp[r] + k0 + kk));
+        for (int j = 0; j < NP; ++j) {
+            const float4 bv = *reinterpret_cast<const float4*>(&bt[j * SN_PITCH + kk]);
 #pragma unroll
-            for (int j = 0; j < NP; ++j) {
-                const float4 bv = *reinterpret_cast<const float4*>(&bt[j * SN_PITCH + kk]);
+            for (int q = 0; q < SN_WARP_ROWS; ++q) {
+                float v = acc[q * NP + j];
+                v = fmaf(av[q].x, bv.x, v);
+                v = fmaf(av[q].y, bv.y, v);
+                v = fmaf(av[q].z, bv.z, v);
+                v = fmaf(av[q].w, bv.w, v);
+                acc[q * NP + j] = v;
+            }
+        }
+    };
+    for (; r < row_end; r += SN_WARPS * SN_WARP_ROWS) {
 #pragma unroll
-                for (int r = 0; r < SN_WARP_ROWS; ++r) {
-                    acc[r][j] = fmaf(av[r].x, bv.x, acc[r][j]);
-                    acc[r][j] = fmaf(av[r].y, bv.y, acc[r][j]);
-                    acc[r][j] = fmaf(av[r].z, bv.z, acc[r][j]);
-                    acc[r][j] = fmaf(av[r].w, bv.w, acc[r][j]);
-                }
+        for (int i = 0; i < SN_WARP_ROWS * NP; ++i) acc[i] = 0.0f;
+        load(r, 1, a1); fold(a0, 0);
+        load(r, 2, a0); fold(a1, 1);
+        load(r, 3, a1); fold(a0, 2);
+        load(r + SN_WARPS * SN_WARP_ROWS, 0, a0); fold(a1, 3);   // the next four rows' first loads
+        // fold the lanes: at each step a lane hands half of its values to its partner and adds the partner's
+        // other half to the half it keeps; after four steps lane pair p holds values [p V/16, (p+1) V/16)
+        constexpr int V = SN_WARP_ROWS * NP;
+        int cnt = V;
+#pragma unroll
+        for (int o = 16; o >= 2; o >>= 1) {
+            cnt >>= 1;
+            const bool upper = (lane & o) != 0;
+#pragma unroll
+            for (int i = 0; i < cnt; ++i) {
+                const float send = upper ? acc[i] : acc[i + cnt];
+                const float keep = upper ? acc[i + cnt] : acc[i];
+                acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+            }
+        }
+        constexpr int MINE = V / 16;
+#pragma unroll
+        for (int i = 0; i < MINE; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 1);
+        if ((lane & 1) == 0) {
+#pragma unroll
+            for (int i = 0; i < MINE; ++i) {
+                const int idx = (lane >> 1) * MINE + i;
+                const int q = idx / NP, j = idx - q * NP;
+                if (j < n && r + q < row_end) out[(r + q) * n + j] = acc[i];
             }
         }
     }
-#pragma unroll
-    for (int r = 0; r < SN_WARP_ROWS; ++r) {
-        float mine = 0.0f;
-#pragma unroll
-        for (int j = 0; j < NP; ++j) {
-            float v = acc[r][j];
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            if (lane == j) mine = v;
-        }
-        if (lane < n && r0 + r < m) c[(r0 + r) * n + lane] = mine;
-    }
 }
 
-constexpr int SG_THREADS = 128, SG_KC = 128, SG_DEPTH = 8;
+constexpr int SG_THREADS = 128, SG_KC = 128, SG_DEPTH = 4;
 template <int NP>
 __global__ void __launch_bounds__(SG_THREADS) narrow_cols_kernel(const float* __restrict__ a, int64_t lda, const float* __restrict__ b, int64_t sb0, int64_t sb1,
                                                                 float* __restrict__ part, int64_t m, int n, int64_t k, int64_t k_per_part) {
@@ -1588,25 +1616,32 @@ __global__ void __launch_bounds__(SG_THREADS) narrow_cols_kernel(const float* __
             }
         }
     };
+    // rows [kr, kr + SG_DEPTH) of A (zeros past this part's end)
+    const float* col = a + (live ? i0 : 0);
+    auto load = [&](int64_t kr, float4 (&dst)[SG_DEPTH]) {
+#pragma unroll
+        for (int u = 0; u < SG_DEPTH; ++u)
+            dst[u] = (live && kr + u < ke) ? __ldcs(reinterpret_cast<const float4*>(col + (kr + u) * lda)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    };
+    float4 x0[SG_DEPTH], x1[SG_DEPTH];
+    load(kb, x0);   // in flight while B is staged
     for (int64_t k0 = kb; k0 < ke; k0 += SG_KC) {
         const int kc = static_cast<int>(ke - k0 < SG_KC ? ke - k0 : SG_KC);
         __syncthreads();
-        for (int i = threadIdx.x; i < kc * NP; i += SG_THREADS) {
+        for (int i = threadIdx.x; i < SG_KC * NP; i += SG_THREADS) {
             const int kk = i / NP, j = i - kk * NP;
-            bs[i] = j < n ? __ldg(b + (k0 + kk) * sb0 + j * sb1) : 0.0f;
+            bs[i] = (j < n && kk < kc) ? __ldg(b + (k0 + kk) * sb0 + j * sb1) : 0.0f;
         }
         __syncthreads();
-        if (live) {
-            const float* p = a + k0 * lda + i0;
-            int kk = 0;
-            for (; kk + SG_DEPTH <= kc; kk += SG_DEPTH) {
-                float4 av[SG_DEPTH];
+        // (rows past kc multiply zeros of A with zeros of B)
+        for (int kk = 0; kk < SG_KC; kk += 2 * SG_DEPTH) {
+            load(k0 + kk + SG_DEPTH, x1);
 #pragma unroll
-                for (int u = 0; u < SG_DEPTH; ++u) av[u] = __ldcs(reinterpret_cast<const float4*>(p + (kk + u) * lda));
+            for (int u = 0; u < SG_DEPTH; ++u) fold(x0[u], kk + u);
+            load(k0 + kk + 2 * SG_DEPTH, x0);
 #pragma unroll
-                for (int u = 0; u < SG_DEPTH; ++u) fold(av[u], kk + u);
-            }
-            for (; kk < kc; ++kk) fold(__ldcs(reinterpret_cast<const float4*>(p + kk * lda)), kk);
+            for (int u = 0; u < SG_DEPTH; ++u) fold(x1[u], kk + SG_DEPTH + u);
+            if (kk + 2 * SG_DEPTH >= kc) break;   // (x0 now holds zeros, or the next chunk's first rows)
         }
     }
     if (live) {
@@ -1621,8 +1656,16 @@ __global__ void __launch_bounds__(SG_THREADS) narrow_cols_kernel(const float* __
 
 __global__ void __launch_bounds__(256) narrow_sum_kernel(const float* __restrict__ part, int parts, int64_t count, float* __restrict__ c) {
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        float v = __ldg(part + i);
-        for (int s = 1; s < parts; ++s) v += __ldg(part + s * count + i);
+        float v = 0.0f;
+        int s = 0;
+        for (; s + 8 <= parts; s += 8) {   // eight loads in flight, added in part order
+            float x[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) x[u] = __ldcs(part + (s + u) * count + i);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v += x[u];
+        }
+        for (; s < parts; ++s) v += __ldcs(part + s * count + i);
         c[i] = v;
     }
 }
@@ -1633,13 +1676,13 @@ __global__ void __launch_bounds__(256) narrow_sum_kernel(const float* __restrict
 static int narrow_n_form(const float* a, const float* b, int64_t m, int64_t n, int64_t k, int64_t sa0, int64_t sa1, int md) {
     if (md != CTK_MATMUL_3XTF32 || n < 1 || n > SN_MAXN || k < 256 || m * k < (int64_t(1) << 20) || a == nullptr || b == nullptr) return 0;
     if ((reinterpret_cast<uintptr_t>(a) & 15u) != 0) return 0;
-    if (sa1 == 1 && sa0 >= k && sa0 % 4 == 0 && k % 4 == 0 && (m + SN_CTA_ROWS - 1) / SN_CTA_ROWS < (int64_t(1) << 31)) return 1;
+    if (sa1 == 1 && sa0 >= k && sa0 % 4 == 0 && k % 4 == 0 && (k + SN_KS - 1) / SN_KS <= 65535) return 1;
     if (sa0 == 1 && sa1 >= m && sa1 % 4 == 0 && m % 4 == 0 && (m / 4 + SG_THREADS - 1) / SG_THREADS < (int64_t(1) << 31)) return 2;
     return 0;
 }
 
 // How narrow_cols splits the contraction: enough parts for about four CTAs per SM, each at least 64 long
-// and a multiple of SG_DEPTH.
+// and a multiple of 2 * SG_DEPTH.
 static void narrow_cols_parts(int64_t m, int64_t k, int* parts, int64_t* k_per_part) {
     const int64_t col_ctas = (m / 4 + SG_THREADS - 1) / SG_THREADS;
     int64_t want = (4 * static_cast<int64_t>(ctk::sm_count()) + col_ctas - 1) / col_ctas;
@@ -1647,7 +1690,7 @@ static void narrow_cols_parts(int64_t m, int64_t k, int* parts, int64_t* k_per_p
     if (want < 1) want = 1;
     if (want > 65535) want = 65535;
     int64_t per = (k + want - 1) / want;
-    per = (per + SG_DEPTH - 1) / SG_DEPTH * SG_DEPTH;
+    per = (per + 2 * SG_DEPTH - 1) / (2 * SG_DEPTH) * (2 * SG_DEPTH);
     *k_per_part = per;
     *parts = static_cast<int>((k + per - 1) / per);
 }
@@ -1655,15 +1698,10 @@ static void narrow_cols_parts(int64_t m, int64_t k, int* parts, int64_t* k_per_p
 template <int NP>
 static ctk_status launch_narrow(int form, const float* a, const float* b, float* c, int64_t m, int64_t n, int64_t k, int64_t sa0, int64_t sa1,
                                 int64_t sb0, int64_t sb1, void* workspace, cudaStream_t st) {
-    if (form == 1) {
-        const int64_t grid = (m + SN_CTA_ROWS - 1) / SN_CTA_ROWS;
-        narrow_rows_kernel<NP><<<static_cast<unsigned>(grid), SN_THREADS, 0, st>>>(a, sa0, b, sb0, sb1, c, m, static_cast<int>(n), k);
-        CTK_LAUNCH_CHECK("narrow_rows_kernel");
-        return CTK_OK;
-    }
     int parts = 1;
     int64_t per = k;
-    narrow_cols_parts(m, k, &parts, &per);
+    if (form == 1) parts = static_cast<int>((k + SN_KS - 1) / SN_KS);
+    else narrow_cols_parts(m, k, &parts, &per);
     float* part = c;
     if (parts > 1) {
         void* ws = workspace;   // (a caller's workspace is sized for the operands' splits: at least 8 bytes per element of A)
@@ -1673,9 +1711,21 @@ static ctk_status launch_narrow(int form, const float* a, const float* b, float*
         }
         part = static_cast<float*>(ws);
     }
-    dim3 grid(static_cast<unsigned>((m / 4 + SG_THREADS - 1) / SG_THREADS), static_cast<unsigned>(parts));
-    narrow_cols_kernel<NP><<<grid, SG_THREADS, 0, st>>>(a, sa1, b, sb0, sb1, part, m, static_cast<int>(n), k, per);
-    CTK_LAUNCH_CHECK("narrow_cols_kernel");
+    if (form == 1) {
+        // row ranges: about two resident CTAs per SM in all, whole groups of SN_WARPS x SN_WARP_ROWS rows
+        constexpr int64_t kGroup = SN_WARPS * SN_WARP_ROWS;
+        int64_t row_ctas = (2 * static_cast<int64_t>(ctk::sm_count()) + parts - 1) / parts;
+        if (row_ctas < 1) row_ctas = 1;
+        int64_t rows_per_cta = ((m + row_ctas - 1) / row_ctas + kGroup - 1) / kGroup * kGroup;
+        row_ctas = (m + rows_per_cta - 1) / rows_per_cta;
+        dim3 grid(static_cast<unsigned>(row_ctas), static_cast<unsigned>(parts));
+        narrow_rows_kernel<NP><<<grid, SN_THREADS, 0, st>>>(a, sa0, b, sb0, sb1, part, m, static_cast<int>(n), k, rows_per_cta);
+        CTK_LAUNCH_CHECK("narrow_rows_kernel");
+    } else {
+        dim3 grid(static_cast<unsigned>((m / 4 + SG_THREADS - 1) / SG_THREADS), static_cast<unsigned>(parts));
+        narrow_cols_kernel<NP><<<grid, SG_THREADS, 0, st>>>(a, sa1, b, sb0, sb1, part, m, static_cast<int>(n), k, per);
+        CTK_LAUNCH_CHECK("narrow_cols_kernel");
+    }
     if (parts > 1) {
         narrow_sum_kernel<<<ctk_stream_grid(m * n, 256, 8), 256, 0, st>>>(part, parts, m * n, c);
         CTK_LAUNCH_CHECK("narrow_sum_kernel");
