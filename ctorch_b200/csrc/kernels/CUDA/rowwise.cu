@@ -126,6 +126,7 @@ template <int LANES, int ITEMS, bool VEC>
 struct StridedRow {
     static_assert(!VEC || ITEMS % 4 == 0, "vector form holds whole vectors");
     static constexpr bool kCached = true;
+    static constexpr bool kRawRow = false;
     static constexpr int kSteps = VEC ? ITEMS / 4 : ITEMS;
     float v[ITEMS];
     int cols;
@@ -256,6 +257,7 @@ __device__ __forceinline__ bool pick_by_each(const Row& r, int c, float& w) {
 
 struct SmemRow {
     static constexpr bool kCached = true;
+    static constexpr bool kRawRow = false;
     float* buf;       // cols floats of dynamic shared memory
     float* red_f;     // 33 floats
     double* red_d;    // 33 doubles
@@ -299,6 +301,7 @@ struct SmemRow {
 // Row too long for shared memory: every pass re-reads it (L2 absorbs most of the re-reads).
 struct GlobalRow {
     static constexpr bool kCached = false;
+    static constexpr bool kRawRow = false;
     const float* row;
     float* red_f;
     double* red_d;
@@ -397,6 +400,13 @@ __device__ __forceinline__ float process_loaded(Row& r, const RowArgs& A, int64_
     const int c = static_cast<int>(label);
     const bool ok = (c >= 0 && c < static_cast<int>(cols));
     if (!ok) poison = true;
+    if constexpr (ALG == ALG_CE_INDEX && Row::kRawRow) {
+        // The forward loss alone, with the row still readable: -log(max(e_c / s, 1e-10)) written as
+        // min(log s - (x_c - max), -log 1e-10) -- no division, no search for element c among the
+        // registers (the thread-per-row kernel is bound by instruction issue at ten columns).
+        const float xc = ok ? r.raw(c) : m;
+        return ok ? fminf(logf(s) - (xc - m), -logf(1e-10f)) : 0.0f;
+    }
     // The thread that holds element c contributes the row's loss: no dependent global read and no
     // per-row reduction on the critical path.
     // (Select the element first and take ONE logarithm per thread and row: written inside the loop,
@@ -440,6 +450,7 @@ constexpr int kTileRows = kTileThreads * kTileRowsPerThread;
 template <int MAXC, bool ROT>
 struct TileRow {
     static constexpr bool kCached = true;
+    static constexpr bool kRawRow = true;   // the row as loaded stays readable (raw()) while the holder works on its registers
     float v[MAXC];
     float* mine;        // this thread's row in the x / out tile
     const float* aux;   // this thread's row in the second operand's tile
@@ -450,9 +461,22 @@ struct TileRow {
         return j >= cols ? j - cols : j;
     }
     __device__ __forceinline__ void load(const float*) {
+        if constexpr (MAXC == 10 && !ROT) {
+            // exactly ten columns (rows 40 bytes apart, 8-byte aligned): five 8-byte reads; a half-warp's
+            // sixteen rows land on all 32 banks once
+            const float2* p = reinterpret_cast<const float2*>(mine);
 #pragma unroll
-        for (int k = 0; k < MAXC; ++k) v[k] = k < cols ? mine[col(k)] : -INFINITY;
+            for (int k = 0; k < 5; ++k) {
+                const float2 t = p[k];
+                v[2 * k] = t.x;
+                v[2 * k + 1] = t.y;
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < MAXC; ++k) v[k] = k < cols ? mine[col(k)] : -INFINITY;
+        }
     }
+    __device__ __forceinline__ float raw(int c) const { return mine[c]; }
     template <class F> __device__ __forceinline__ void each(F f) const {
 #pragma unroll
         for (int k = 0; k < MAXC; ++k)
