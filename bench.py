@@ -782,15 +782,16 @@ def run_single_op(args):
         a = cb.ops.tile(cb.to_device(rng.uniform(-4, 4, 1 << 20).astype(np.float32)), n)
         emit("sum_2^28", timeit(lambda: cb.ops.sum(a), 10), 4 * n, "GB/s", peaks["hbm_gbs"])
     elif args.workload == "matmul":
-        tf32_peak = peaks["bf16"] / 2.0
-        for mode, peak in (("tf32", tf32_peak), ("3xtf32", tf32_peak / 3.0)):
+        units = 2.0 if args.correction == "bf16" else 3.0   # TF32-rate units of tensor work per fp32 product
+        for mode, peak in (("tf32", NOMINAL_TF32), ("3xtf32", NOMINAL_TF32 / units)):
             for (m, k, n) in ((512, 512, 512), (1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096), (8192, 8192, 8192), (65536, 784, 4096)):
                 A = cb.to_device(rng.standard_normal((m, k)).astype(np.float32)); B = cb.to_device(rng.standard_normal((k, n)).astype(np.float32))
                 dC = cb.to_device(rng.standard_normal((m, n)).astype(np.float32))
                 C, dA, dB = cb.empty((m, n)), cb.empty((m, k)), cb.empty((k, n))
                 it = 20 if m <= 2048 else 5
                 fl = 2.0 * m * n * k
-                cfg = dict(m=m, n=n, k=k, mode=mode, peak_source=f"{peaks['source']} bf16_tflops/2" + ("/3" if mode == "3xtf32" else ""))
+                cfg = dict(m=m, n=n, k=k, mode=mode, correction=args.correction if mode == "3xtf32" else None,
+                           peak_source="nominal dense TF32 1125 TFLOP/s" + (f" / {units:g}" if mode == "3xtf32" else ""))
                 emit(f"matmul_fwd_{mode}_{m}x{k}x{n}", timeit(lambda: cb.ops.matmul(A, B, mode=mode, out=C), it), fl, "TFLOP/s", peak, cfg)
                 emit(f"matmul_dA_{mode}_{m}x{k}x{n}", timeit(lambda: cb.ops.matmul(dC, B, tb=True, mode=mode, out=dA), it), fl, "TFLOP/s", peak, cfg)
                 emit(f"matmul_dB_{mode}_{m}x{k}x{n}", timeit(lambda: cb.ops.matmul(A, dC, ta=True, mode=mode, out=dB), it), fl, "TFLOP/s", peak, cfg)

@@ -1744,7 +1744,7 @@ int g_correction = [] {
     return 1;  // measured on B200: 14-19 % faster training steps and a smaller error (1.0e-5 against 1.6e-5 at 4096^3)
 }();
 int g_pairing = 0;  // 0: CTA pairs where the shape allows, 1: single-CTA kernel only
-int g_split_tail = 1;  // 1: K-halves for the tiles of a last wave that fills at most half the machine
+int g_split_tail = 1;  // K-halves for the tiles of a last wave that fills at most half the machine: 0 never, 1 where the contraction is long enough to pay, 2 wherever the shape allows
 // ---- optional per-launch timing of the tensor-core kernel ----
 struct TcProfile {
     static constexpr int kMax = 8192;
@@ -1894,7 +1894,7 @@ int ctk_get_matmul_correction(void) { return g_correction; }
 int ctk_matmul_split_tag(void) { return 1 + g_correction; }
 
 ctk_status ctk_set_matmul_tail_split(int on) {
-    CTK_REQUIRE(on == 0 || on == 1, "ctk_set_matmul_tail_split: 0 or 1");
+    CTK_REQUIRE(on >= 0 && on <= 2, "ctk_set_matmul_tail_split: 0, 1 or 2");
     g_split_tail = on;
     return CTK_OK;
 }
@@ -2138,7 +2138,11 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
         const int tail = tiles % workers;
         // (a fused epilogue needs the whole sum)
         P.half_flags = nullptr;
-        if (g_split_tail && !fused && P.num_kb >= 16 && tail > 0 && 2 * tail <= workers && tail <= kHalfTilesMax) {
+        // (the second half's epilogue starts after the first's -- about 12 us more at the end of the kernel,
+        // and the flags are cleared by one more node on the stream -- so halves pay once half of the
+        // contraction takes longer than that: from 96 k-blocks of three or two terms, 192 of one)
+        const int min_kb = g_split_tail == 2 ? 16 : (terms == 1 ? 192 : 96);
+        if (g_split_tail && !fused && P.num_kb >= min_kb && tail > 0 && 2 * tail <= workers && tail <= kHalfTilesMax) {
             int* flags = nullptr;
             if ((rc = half_flag_slot(&flags))) return rc;
             CTK_CUDA(cudaMemsetAsync(flags, 0, static_cast<size_t>(tail) * 8 * sizeof(int), st));

@@ -300,7 +300,10 @@ int ctk_matmul_split_tag(void);
 /* 1 (default): when the last wave of output tiles would occupy at most half of the SMs (or CTA    */
 /* pairs) -- which includes every product with few tiles, like the 10-class layer -- each of its   */
 /* tiles is computed as two halves of K by two CTAs (pairs); the second half is added to the first   */
-/* after a flag, always in that order, so repeated calls give the same bits.  0: every tile whole.  */
+/* after a flag, always in that order, so repeated calls give the same bits -- where the contraction  */
+/* is long enough for that to pay (the second half's epilogue runs after the first's: from K = 3072 */
+/* in the fp32-accurate mode, 6144 in TF32 mode).  2: from K = 512, whatever it costs (tests).       */
+/* 0: every tile whole.                                                                              */
 ctk_status ctk_set_matmul_tail_split(int on);
 /* Self-test of the kernels' bounded waits (no counterpart in the reference): one CTA waits with a  */
 /* short limit on a barrier nothing arrives on.  result = {first wait ok (expected 0), CTA abort     */

@@ -117,8 +117,8 @@ def test_cta_pair_kernel_agrees_with_single_cta_kernel(cb, orc, mode, ta, tb):
     (0, 2560, 552, 2304, False, True),     # 90 pair tiles on 74 pairs: 74 whole + 16 halved
     (0, 2304, 1000, 2560, True, False),    # the weight-gradient shape: A^T.dC
     (1, 2560, 520, 2304, False, False),    # single-CTA kernel: 180 tiles on 148 SMs, 148 whole + 32 halved
-    (0, 8192, 640, 10, False, False),      # the 10-class layer forward: 64 tiles of 128 x 64, all halved
-    (0, 1024, 4100, 10, True, False),      # its weight gradient: 8 tiles, ragged K
+    (0, 8192, 640, 20, False, False),      # a 20-class layer forward: 64 tiles of 128 x 64, all halved
+    (0, 1024, 4100, 20, True, False),      # its weight gradient: 8 tiles, ragged K
 ])
 def test_last_wave_in_k_halves(cb, orc, mode, pairing, m, k, n, ta, tb):
     """Tiles of a last wave that would fill at most half the machine are computed as two K-halves added
@@ -134,7 +134,7 @@ def test_last_wave_in_k_halves(cb, orc, mode, pairing, m, k, n, ta, tb):
         cb.ops.set_matmul_pairing(pairing)
         cb.ops.set_matmul_tail_split(0)
         whole = cb.ops.matmul(dA, dB, ta, tb, mode).numpy()
-        cb.ops.set_matmul_tail_split(1)
+        cb.ops.set_matmul_tail_split(2)    # halves wherever the shape allows (the default asks for a long contraction)
         halves = cb.ops.matmul(dA, dB, ta, tb, mode, out=out).numpy()
         again = cb.ops.matmul(dA, dB, ta, tb, mode, out=out).numpy()
     finally:

@@ -67,10 +67,12 @@ def test_halves_chunks_and_pairs(cb, orc, pairing, m, k, n, ta, tb):
     dA, dB = cb.to_device(sa), cb.to_device(sb)
     try:
         cb.ops.set_matmul_pairing(pairing)
+        cb.ops.set_matmul_tail_split(2)    # halves wherever the shape allows
         C = cb.ops.matmul(dA, dB, ta, tb, "3xtf32").numpy()
         again = cb.ops.matmul(dA, dB, ta, tb, "3xtf32").numpy()
     finally:
         cb.ops.set_matmul_pairing(0)
+        cb.ops.set_matmul_tail_split(1)
     _ok(cb)
     assert_exact(again, C, "two calls, same bits")
     assert_matmul_close(C, A.astype(np.float64) @ B.astype(np.float64), TOL, f"{m}x{k}x{n} vs float64")
