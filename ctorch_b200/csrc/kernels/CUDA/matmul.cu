@@ -298,6 +298,10 @@ struct Params {
     int relu;
     const float* mask;
     SplitOut out;  // out.hi == nullptr: no split
+    // An MN-major operand whose contiguous extent is a multiple of 64 comes with 3-D tensor maps
+    // {128 bytes of the MN index, k, 128-byte group}: one copy per array and stage fetches all of a tile's
+    // column groups (box {32 | 64 elements, 32, groups}) where the 2-D maps need one copy per group.
+    int a_grouped, b_grouped;
 };
 
 // A unit of work: a whole output tile, or one K-half of a tile of the last, partly filled wave.
@@ -405,6 +409,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
     asm volatile("cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1) : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
@@ -511,36 +519,31 @@ struct StageLayout {
 
 // The loads of one stage.  maps: a[0..2], b[0..2] = {hi, lo, -} (TERMS 3) or {hi, h16, l16} (TERMS 2).
 // tma(dst, map, c0, c1) issues one tiled copy whose completion is counted on the stage's barrier.
-template <int TERMS, bool A_MN, bool B_MN, int A_ROWS, int B_ROWS, typename Tma>
-__device__ __forceinline__ void load_stage(uint32_t base, const CUtensorMap* const (&ma)[3], const CUtensorMap* const (&mb)[3], int m0, int n0, int k0, Tma tma) {
+template <int TERMS, bool A_MN, bool B_MN, int A_ROWS, int B_ROWS, typename Tma, typename Tma3>
+__device__ __forceinline__ void load_stage(uint32_t base, const CUtensorMap* const (&ma)[3], const CUtensorMap* const (&mb)[3], int m0, int n0, int k0,
+                                           bool a_grouped, bool b_grouped, Tma tma, Tma3 tma3) {
     using L = StageLayout<TERMS, A_ROWS * BK * 4, B_ROWS * BK * 4>;
-    auto tile32 = [&](uint32_t dst, const CUtensorMap* map, bool mn, int rows, int r0) {
-        if (mn) {
-#pragma unroll
-            for (int g = 0; g < rows / 32; ++g) tma(dst + g * 4096, map, r0 + 32 * g, k0);
-        } else {
+    // wide: elements per 128-byte column group (32 fp32, 64 bf16)
+    auto tile = [&](uint32_t dst, const CUtensorMap* map, bool mn, bool grouped, int rows, int r0, int wide) {
+        if (!mn) {
             tma(dst, map, k0, r0);
+        } else if (grouped) {
+            tma3(dst, map, 0, k0, r0 / wide);
+        } else {
+            for (int g = 0; g < rows / wide; ++g) tma(dst + g * 4096, map, r0 + wide * g, k0);
         }
     };
-    auto tile16 = [&](uint32_t dst, const CUtensorMap* map, bool mn, int rows, int r0) {
-        if (mn) {
-#pragma unroll
-            for (int g = 0; g < rows / 64; ++g) tma(dst + g * 4096, map, r0 + 64 * g, k0);
-        } else {
-            tma(dst, map, k0, r0);
-        }
-    };
-    tile32(base + L::a_hi, ma[0], A_MN, A_ROWS, m0);
-    tile32(base + L::b_hi, mb[0], B_MN, B_ROWS, n0);
+    tile(base + L::a_hi, ma[0], A_MN, a_grouped, A_ROWS, m0, 32);
+    tile(base + L::b_hi, mb[0], B_MN, b_grouped, B_ROWS, n0, 32);
     if (TERMS == 3) {
-        tile32(base + L::a_lo, ma[1], A_MN, A_ROWS, m0);
-        tile32(base + L::b_lo, mb[1], B_MN, B_ROWS, n0);
+        tile(base + L::a_lo, ma[1], A_MN, a_grouped, A_ROWS, m0, 32);
+        tile(base + L::b_lo, mb[1], B_MN, b_grouped, B_ROWS, n0, 32);
     }
     if (TERMS == 2) {
-        tile16(base + L::a_h16, ma[1], A_MN, A_ROWS, m0);
-        tile16(base + L::a_l16, ma[2], A_MN, A_ROWS, m0);
-        tile16(base + L::b_h16, mb[1], B_MN, B_ROWS, n0);
-        tile16(base + L::b_l16, mb[2], B_MN, B_ROWS, n0);
+        tile(base + L::a_h16, ma[1], A_MN, a_grouped, A_ROWS, m0, 64);
+        tile(base + L::a_l16, ma[2], A_MN, a_grouped, A_ROWS, m0, 64);
+        tile(base + L::b_h16, mb[1], B_MN, b_grouped, B_ROWS, n0, 64);
+        tile(base + L::b_l16, mb[2], B_MN, b_grouped, B_ROWS, n0, 64);
     }
 }
 
@@ -788,8 +791,9 @@ tcgen05_matmul_kernel(const __grid_constant__ CUtensorMap map_a0, const __grid_c
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, &abort_flag, 0x100 | stage)) { ok = false; break; }
                     mbar_expect_tx(full_bar(stage), C::STAGE_BYTES);
                     const uint32_t fb = full_bar(stage);
-                    load_stage<TERMS, A_MN, B_MN, BM, BN>(stage_addr(stage), maps_a, maps_b, m0, n0, kb * BK,
-                                                         [&](uint32_t dst, const CUtensorMap* map, int c0, int c1) { tma_load_2d(dst, map, fb, c0, c1); });
+                    load_stage<TERMS, A_MN, B_MN, BM, BN>(stage_addr(stage), maps_a, maps_b, m0, n0, kb * BK, P.a_grouped != 0, P.b_grouped != 0,
+                                                         [&](uint32_t dst, const CUtensorMap* map, int c0, int c1) { tma_load_2d(dst, map, fb, c0, c1); },
+                                                         [&](uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2) { tma_load_3d(dst, map, fb, c0, c1, c2); });
                     ++issued;
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -965,6 +969,10 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
     asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(c0), "r"(c1) : "memory");
 }
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
 __device__ __forceinline__ void tmem_alloc2(uint32_t dst_smem, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
 }
@@ -1071,8 +1079,9 @@ tcgen05_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_a0, const __g
                     if (!mbar_wait(empty_bar(stage), phase ^ 1u, &abort_flag, 0x500 | stage)) { ok = false; break; }
                     if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * C::STAGE_BYTES);
                     const uint32_t fb = map_to_cta(full_bar(stage), 0);
-                    load_stage<TERMS, A_MN, B_MN, BM, BN_CTA>(stage_addr(stage), maps_a, maps_b, m0, n0, kb * BK,
-                                                             [&](uint32_t dst, const CUtensorMap* map, int c0, int c1) { tma_load_2d_pair(dst, map, fb, c0, c1); });
+                    load_stage<TERMS, A_MN, B_MN, BM, BN_CTA>(stage_addr(stage), maps_a, maps_b, m0, n0, kb * BK, P.a_grouped != 0, P.b_grouped != 0,
+                                                             [&](uint32_t dst, const CUtensorMap* map, int c0, int c1) { tma_load_2d_pair(dst, map, fb, c0, c1); },
+                                                             [&](uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2) { tma_load_3d_pair(dst, map, fb, c0, c1, c2); });
                     ++issued;
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -1237,12 +1246,13 @@ struct MapKey {
     const void* base;
     int64_t inner, outer, ld;
     int box_outer, flags;  // flags: bit 0 MN-major, bit 1 bf16
+    int groups;            // > 0: an MN-major operand as a 3-D tensor, `groups` 128-byte column groups per box
     bool operator==(const MapKey& o) const {
-        return base == o.base && inner == o.inner && outer == o.outer && ld == o.ld && box_outer == o.box_outer && flags == o.flags;
+        return base == o.base && inner == o.inner && outer == o.outer && ld == o.ld && box_outer == o.box_outer && flags == o.flags && groups == o.groups;
     }
 };
 struct MapSlot {
-    MapKey key{nullptr, 0, 0, 0, 0, -1};
+    MapKey key{nullptr, 0, 0, 0, 0, -1, 0};
     CUtensorMap map;
 };
 constexpr int kMapSlots = 256;
@@ -1251,7 +1261,7 @@ thread_local MapSlot t_map_cache[kMapSlots];
 ctk_status encode_map(CUtensorMap* map, const MapKey& k) {
     uint64_t h = reinterpret_cast<uintptr_t>(k.base) >> 4;
     h ^= static_cast<uint64_t>(k.inner) * 0x9E3779B97F4A7C15ull ^ static_cast<uint64_t>(k.outer) * 0xC2B2AE3D27D4EB4Full ^
-         static_cast<uint64_t>(k.ld) * 0x165667B19E3779F9ull ^ static_cast<uint64_t>(k.box_outer * 4 + k.flags);
+         static_cast<uint64_t>(k.ld) * 0x165667B19E3779F9ull ^ static_cast<uint64_t>((k.box_outer * 4 + k.flags) * 16 + k.groups);
     MapSlot& slot = t_map_cache[(h ^ (h >> 29)) % kMapSlots];
     if (slot.key == k) {
         *map = slot.map;
@@ -1275,8 +1285,20 @@ ctk_status encode_map(CUtensorMap* map, const MapKey& k) {
         box[1] = static_cast<cuuint32_t>(mn_major ? 32 : k.box_outer);
         swz = mn_major ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
     }
-    CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(k.base), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r;
+    if (k.groups > 0) {
+        // {128 bytes along MN, k, column group}: group g of row kk starts g * 128 bytes into the row
+        const cuuint64_t wide = box[0];
+        cuuint64_t dims3[3] = {wide, static_cast<cuuint64_t>(k.outer), static_cast<cuuint64_t>(k.inner) / wide};
+        cuuint64_t strides3[2] = {strides[0], 128u};
+        cuuint32_t box3[3] = {box[0], box[1], static_cast<cuuint32_t>(k.groups)};
+        cuuint32_t estr3[3] = {1u, 1u, 1u};
+        r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(k.base), dims3, strides3, box3, estr3,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else {
+        r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(k.base), dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
     if (r != CUDA_SUCCESS) return fail(CTK_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(r)));
     slot.key = k;
     slot.map = *map;
@@ -1286,15 +1308,17 @@ ctk_status encode_map(CUtensorMap* map, const MapKey& k) {
 // 2-D fp32 tensor {inner (contiguous), outer} with row pitch ld elements; box {32, box_outer};
 // 128-byte swizzle (16-byte chunks for a K-major operand, 32-byte atoms for an MN-major one);
 // out-of-range elements read as zero.
-ctk_status make_map(CUtensorMap* map, const float* base, int64_t inner, int64_t outer, int64_t ld, int box_outer, bool mn_major) {
-    return encode_map(map, MapKey{base, inner, outer, ld, box_outer, mn_major ? 1 : 0});
+// groups > 0 (MN-major only): the 3-D form, `groups` column groups of 32 elements per box.
+ctk_status make_map(CUtensorMap* map, const float* base, int64_t inner, int64_t outer, int64_t ld, int box_outer, bool mn_major, int groups = 0) {
+    return encode_map(map, MapKey{base, inner, outer, ld, box_outer, mn_major ? 1 : 0, mn_major ? groups : 0});
 }
 
 // The same operand as bf16 ([outer, ld] elements of 2 bytes): box {32, box_outer} with the 64-byte
 // swizzle for a K-major operand (a k-block is 32 elements = 64 bytes), {64, 32} with the 128-byte
 // swizzle per 64-wide column group for an MN-major one.
-ctk_status make_map16(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int64_t ld, int box_outer, bool mn_major) {
-    return encode_map(map, MapKey{base, inner, outer, ld, box_outer, (mn_major ? 1 : 0) | 2});
+// groups > 0 (MN-major only): the 3-D form, `groups` column groups of 64 elements per box.
+ctk_status make_map16(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int64_t ld, int box_outer, bool mn_major, int groups = 0) {
+    return encode_map(map, MapKey{base, inner, outer, ld, box_outer, (mn_major ? 1 : 0) | 2, mn_major ? groups : 0});
 }
 
 // One operand as the tensor-core path sees it.
@@ -1744,6 +1768,11 @@ int g_correction = [] {
     return 1;  // measured on B200: 14-19 % faster training steps and a smaller error (1.0e-5 against 1.6e-5 at 4096^3)
 }();
 int g_pairing = 0;  // 0: CTA pairs where the shape allows, 1: single-CTA kernel only
+// MN-major operands as 3-D tensor maps (one copy per array and stage).  CTORCH_MATMUL_GROUPED_MAPS=0 keeps the 2-D maps.
+bool g_grouped_maps = [] {
+    const char* e = std::getenv("CTORCH_MATMUL_GROUPED_MAPS");
+    return !(e && e[0] == '0');
+}();
 int g_split_tail = 1;  // K-halves for the tiles of a last wave that fills at most half the machine: 0 never, 1 where the contraction is long enough to pay, 2 wherever the shape allows
 // ---- optional per-launch timing of the tensor-core kernel ----
 struct TcProfile {
@@ -2094,22 +2123,39 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
     ctk_status rc;
     const float* a32 = terms == 1 ? A.p : sa.hi;
     const float* b32 = terms == 1 ? B.p : sb.hi;
-    if ((rc = tc::make_map(&maps[0], a32, A.inner(), A.outer(), a_ld, a_box, A.mn_major))) return rc;
-    if ((rc = tc::make_map(&maps[3], b32, B.inner(), B.outer(), b_ld, b_box, B.mn_major))) return rc;
-    if (terms == 3) {
-        if ((rc = tc::make_map(&maps[1], static_cast<const float*>(sa.p2), A.inner(), A.outer(), a_ld, a_box, A.mn_major))) return rc;
-        if ((rc = tc::make_map(&maps[4], static_cast<const float*>(sb.p2), B.inner(), B.outer(), b_ld, b_box, B.mn_major))) return rc;
-        maps[2] = maps[1];
-        maps[5] = maps[4];
-    } else if (terms == 2) {
-        if ((rc = tc::make_map16(&maps[1], sa.p2, A.inner(), A.outer(), a_ld, tc::BM, A.mn_major))) return rc;
-        if ((rc = tc::make_map16(&maps[2], sa.p3, A.inner(), A.outer(), a_ld, tc::BM, A.mn_major))) return rc;
-        if ((rc = tc::make_map16(&maps[4], sb.p2, B.inner(), B.outer(), b_ld, b_rows, B.mn_major))) return rc;
-        if ((rc = tc::make_map16(&maps[5], sb.p3, B.inner(), B.outer(), b_ld, b_rows, B.mn_major))) return rc;
-    } else {
-        maps[1] = maps[2] = maps[0];
-        maps[4] = maps[5] = maps[3];
+    // MN-major operands with whole 128-byte groups along MN: one 3-D copy per array and stage instead of
+    // one per group (g_grouped_maps goes false for good if the driver refuses such a map)
+    bool a_grouped = g_grouped_maps && A.mn_major && A.inner() % 64 == 0;
+    bool b_grouped = g_grouped_maps && B.mn_major && B.inner() % 64 == 0 && b_rows >= 64;
+    auto encode_all = [&]() -> ctk_status {
+        const int ag32 = a_grouped ? tc::BM / 32 : 0, ag16 = a_grouped ? tc::BM / 64 : 0;
+        const int bg32 = b_grouped ? b_rows / 32 : 0, bg16 = b_grouped ? b_rows / 64 : 0;
+        ctk_status e;
+        if ((e = tc::make_map(&maps[0], a32, A.inner(), A.outer(), a_ld, a_box, A.mn_major, ag32))) return e;
+        if ((e = tc::make_map(&maps[3], b32, B.inner(), B.outer(), b_ld, b_box, B.mn_major, bg32))) return e;
+        if (terms == 3) {
+            if ((e = tc::make_map(&maps[1], static_cast<const float*>(sa.p2), A.inner(), A.outer(), a_ld, a_box, A.mn_major, ag32))) return e;
+            if ((e = tc::make_map(&maps[4], static_cast<const float*>(sb.p2), B.inner(), B.outer(), b_ld, b_box, B.mn_major, bg32))) return e;
+            maps[2] = maps[1];
+            maps[5] = maps[4];
+        } else if (terms == 2) {
+            if ((e = tc::make_map16(&maps[1], sa.p2, A.inner(), A.outer(), a_ld, tc::BM, A.mn_major, ag16))) return e;
+            if ((e = tc::make_map16(&maps[2], sa.p3, A.inner(), A.outer(), a_ld, tc::BM, A.mn_major, ag16))) return e;
+            if ((e = tc::make_map16(&maps[4], sb.p2, B.inner(), B.outer(), b_ld, b_rows, B.mn_major, bg16))) return e;
+            if ((e = tc::make_map16(&maps[5], sb.p3, B.inner(), B.outer(), b_ld, b_rows, B.mn_major, bg16))) return e;
+        } else {
+            maps[1] = maps[2] = maps[0];
+            maps[4] = maps[5] = maps[3];
+        }
+        return CTK_OK;
+    };
+    rc = encode_all();
+    if (rc && (a_grouped || b_grouped)) {
+        g_grouped_maps = false;
+        a_grouped = b_grouped = false;
+        rc = encode_all();
     }
+    if (rc) return rc;
 
     tc::Params P;
     P.m = m; P.n = n; P.k = k;
@@ -2123,6 +2169,8 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
     P.bias = fe.bias;
     P.relu = fe.relu;
     P.mask = fe.mask;
+    P.a_grouped = a_grouped ? 1 : 0;
+    P.b_grouped = b_grouped ? 1 : 0;
     P.out = SplitOut();
     P.out.pitch = split_pitch_of(n);
     if (fe.c_split) P.out = split_layout(fe.c_split, m, split_pitch_of(n), variant);
