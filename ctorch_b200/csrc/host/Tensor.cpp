@@ -673,7 +673,7 @@ static bool fused_product(const Tensor& A, const Tensor& B, const Tensor* bias, 
                                            bias ? bias->data<float>() : nullptr, relu ? 1 : 0, mask ? mask->data<float>() : nullptr,
                                            ky ? ky->buf : nullptr, nullptr, t_stream),
                "fused MatMul epilogue");
-    if (ky) ky->valid = ctk_matmul_split_tag();
+    if (ky) ky->valid = ctk_matmul_split_tag_for(yp, n, n);
     return true;
 }
 
@@ -812,7 +812,7 @@ void Tensor::sgd_update_shared_(const Tensor& g, float lr) {
         KeptSplit* ks = _storage.kept_split(static_cast<int64_t>(_storage_offset), outer, inner, inner, ctk_matmul_split_bytes(inner, outer));
         if (ks) {
             cuda_check(ctk_sgd_update_split_f32(p, g.data<float>(), lr, outer, inner, inner, ks->buf, t_stream), "sgd_update_shared_ (with split)");
-            ks->valid = ctk_matmul_split_tag();
+            ks->valid = ctk_matmul_split_tag_for(p, inner, inner);
             return;
         }
     }
@@ -841,7 +841,7 @@ void Tensor::sgd_update_from_(const float* g_device, float lr) {
         KeptSplit* ks = _storage.kept_split(static_cast<int64_t>(_storage_offset), outer, inner, inner, ctk_matmul_split_bytes(inner, outer));
         if (ks) {
             cuda_check(ctk_sgd_update_split_f32(p, g_device, lr, outer, inner, inner, ks->buf, t_stream), "sgd_update_ (with split)");
-            ks->valid = ctk_matmul_split_tag();
+            ks->valid = ctk_matmul_split_tag_for(p, inner, inner);
             return;
         }
     }

@@ -111,18 +111,26 @@ __global__ void __launch_bounds__(SM_THREADS) simt_matmul_kernel(const float* __
 // ================================================================================================
 // hi/lo split for 3xTF32
 // ================================================================================================
+// x with its low 13 mantissa bits cleared: the value the tensor core uses when it is handed x as a TF32 operand.
+__device__ __forceinline__ float to_tf32_trunc(float x) { return __uint_as_float(__float_as_uint(x) & 0xFFFFE000u); }
 __device__ __forceinline__ float to_tf32_rna(float x) {
     uint32_t r;
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
     return __uint_as_float(r);
 }
 
-// Where the split of an [outer, inner] operand goes: three arrays of pitch `pitch` elements (a multiple
+// Where the split of an [outer, inner] operand goes: arrays of pitch `pitch` elements (a multiple
 // of 8, so that rows of every array start on 16 bytes whatever the source pitch was; pad columns are
 // never read: the tensor maps' extent stays `inner`).
 //   correction terms on the TF32 path (variant 0):  hi = tf32(x) and lo = tf32(x - hi), fp32 each;
 //   correction terms on the bf16 path (variant 1):  hi = tf32(x) as fp32, h16 = bf16(hi), l16 = bf16(x - hi).
-// Either way 8 bytes per element: [hi: 4 B][p2: lo 4 B | h16 2 B + l16 2 B].
+// Where hi comes from.  The tensor core reads the top 19 bits of an fp32 operand and ignores the rest
+// (measured: a TF32 product of raw operands equals, bit for bit, the product of the same operands with
+// their low 13 mantissa bits cleared).  So where TMA can read the operand itself -- 16-byte aligned, rows a
+// multiple of 16 bytes apart -- hi needs no array: the operand IS hi = trunc(x), the split has
+// SplitOut::hi == nullptr and keeps only the small terms of x - trunc(x) (4 bytes per element written
+// instead of 8).  Elsewhere (the 10-wide layer's 40-byte rows) hi = x rounded to nearest is written to
+// an array of its own as before.  [hi: 4 B, or none][p2: lo 4 B | h16 2 B + l16 2 B].
 struct SplitOut {
     float* hi = nullptr;
     void* p2 = nullptr;  // lo (fp32) or h16 (bf16)
@@ -141,10 +149,14 @@ __device__ __forceinline__ uint2 pack_bf16x4(float4 v) {
 template <bool STREAMING>
 __device__ __forceinline__ void store_split4(const SplitOut& o, int64_t off, float4 x) {
     float4 h, l;
-    h.x = to_tf32_rna(x.x); h.y = to_tf32_rna(x.y); h.z = to_tf32_rna(x.z); h.w = to_tf32_rna(x.w);
+    if (o.hi != nullptr) {
+        h.x = to_tf32_rna(x.x); h.y = to_tf32_rna(x.y); h.z = to_tf32_rna(x.z); h.w = to_tf32_rna(x.w);
+        if (STREAMING) __stcs(reinterpret_cast<float4*>(o.hi + off), h);
+        else *reinterpret_cast<float4*>(o.hi + off) = h;
+    } else {  // the operand itself is read as hi: what the tensor core sees of it
+        h.x = to_tf32_trunc(x.x); h.y = to_tf32_trunc(x.y); h.z = to_tf32_trunc(x.z); h.w = to_tf32_trunc(x.w);
+    }
     l.x = x.x - h.x; l.y = x.y - h.y; l.z = x.z - h.z; l.w = x.w - h.w;  // exact in fp32
-    if (STREAMING) __stcs(reinterpret_cast<float4*>(o.hi + off), h);
-    else *reinterpret_cast<float4*>(o.hi + off) = h;
     if (o.variant == 0) {
         l.x = to_tf32_rna(l.x); l.y = to_tf32_rna(l.y); l.z = to_tf32_rna(l.z); l.w = to_tf32_rna(l.w);
         if (STREAMING) __stcs(reinterpret_cast<float4*>(static_cast<float*>(o.p2) + off), l);
@@ -161,8 +173,8 @@ __device__ __forceinline__ void store_split4(const SplitOut& o, int64_t off, flo
     }
 }
 __device__ __forceinline__ void store_split1(const SplitOut& o, int64_t off, float x) {
-    const float h = to_tf32_rna(x);
-    o.hi[off] = h;
+    const float h = o.hi != nullptr ? to_tf32_rna(x) : to_tf32_trunc(x);
+    if (o.hi != nullptr) o.hi[off] = h;
     if (o.variant == 0) {
         static_cast<float*>(o.p2)[off] = to_tf32_rna(x - h);
     } else {
@@ -297,7 +309,7 @@ struct Params {
     const float* bias;
     int relu;
     const float* mask;
-    SplitOut out;  // out.hi == nullptr: no split
+    SplitOut out;  // out.p2 == nullptr: no split
     // An MN-major operand whose contiguous extent is a multiple of 64 comes with 3-D tensor maps
     // {128 bytes of the MN index, k, 128-byte group}: one copy per array and stage fetches all of a tile's
     // column groups (box {32 | 64 elements, 32, groups}) where the 2-D maps need one copy per group.
@@ -670,7 +682,7 @@ __device__ __forceinline__ void emit_chunk(const Params& P, bool half, bool firs
             *reinterpret_cast<float4*>(&stage[lane][4 * v]) =
                 make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
         __syncwarp();
-        const bool plain = !add_old && (!last || (P.bias == nullptr && !P.relu && P.mask == nullptr && P.out.hi == nullptr));
+        const bool plain = !add_old && (!last || (P.bias == nullptr && !P.relu && P.mask == nullptr && P.out.p2 == nullptr));
         if (plain && last) {
 #pragma unroll
             for (int i = 0; i < 8; ++i)
@@ -680,7 +692,7 @@ __device__ __forceinline__ void emit_chunk(const Params& P, bool half, bool firs
             for (int i = 0; i < 8; ++i)
                 if (i * 4 + sub < rows_left) *reinterpret_cast<float4*>(cdst + i * cstep) = *reinterpret_cast<const float4*>(&stage[i * 4 + sub][c4]);
         } else {
-            const bool biased = last && P.bias != nullptr, relu = last && P.relu, masked = last && P.mask != nullptr, split = last && P.out.hi != nullptr;
+            const bool biased = last && P.bias != nullptr, relu = last && P.relu, masked = last && P.mask != nullptr, split = last && P.out.p2 != nullptr;
             const int64_t soff = (row_base + sub) * P.out.pitch + col0 + c4, sstep = 4 * P.out.pitch;
             float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
             if (biased) bv = __ldg(reinterpret_cast<const float4*>(P.bias + col0 + c4));  // Add_BASIC_kernel's [N,H] + [H]
@@ -723,7 +735,7 @@ __device__ __forceinline__ void emit_chunk(const Params& P, bool half, bool firs
                 if (P.mask != nullptr) x *= P.mask[row * P.n + col0 + v] > 0.0f ? 1.0f : 0.0f;
             }
             crow[col0 + v] = x;
-            if (last && P.out.hi != nullptr) store_split1(P.out, row * P.out.pitch + col0 + v, x);
+            if (last && P.out.p2 != nullptr) store_split1(P.out, row * P.out.pitch + col0 + v, x);
         }
 }
 
@@ -1502,7 +1514,7 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_k_kernel(const float* __res
                 x.z *= y[g].z > 0.0f ? 1.0f : 0.0f; x.w *= y[g].w > 0.0f ? 1.0f : 0.0f;
             }
             __stcs(reinterpret_cast<float4*>(c + r * n + j0), x);
-            if (out.hi != nullptr) store_split4<true>(out, r * out.pitch + j0, x);
+            if (out.p2 != nullptr) store_split4<true>(out, r * out.pitch + j0, x);
         }
     }
 }
@@ -1826,20 +1838,33 @@ int choose_path(const float* a, const float* b, int64_t m, int64_t n, int64_t k,
 }
 
 // The three arrays of a split inside one buffer (256-byte aligned start, `outer` rows of `pitch` elements).
-SplitOut split_layout(void* buf, int64_t outer, int64_t pitch, int variant) {
+// in_place: the operand itself serves as hi (see SplitOut): the first array's room stays unused.
+SplitOut split_layout(void* buf, int64_t outer, int64_t pitch, int variant, bool in_place) {
     SplitOut o;
-    o.hi = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(buf) + 255u) & ~static_cast<uintptr_t>(255u));
+    float* first = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(buf) + 255u) & ~static_cast<uintptr_t>(255u));
+    o.hi = in_place ? nullptr : first;
     o.variant = variant;
     o.pitch = pitch;
     if (variant == 0) {
-        o.p2 = o.hi + outer * pitch;
+        o.p2 = first + outer * pitch;
     } else {
-        __nv_bfloat16* h16 = reinterpret_cast<__nv_bfloat16*>(o.hi + outer * pitch);
+        __nv_bfloat16* h16 = reinterpret_cast<__nv_bfloat16*>(first + outer * pitch);
         o.p2 = h16;
         o.p3 = h16 + outer * pitch;
     }
     return o;
 }
+// Whether the array at p ([.., inner] with row pitch ld elements) can be read by TMA as it is, so that it
+// serves as the hi part of its own split.  CTORCH_MATMUL_HI_IN_PLACE=0 in the environment: never.
+bool g_hi_in_place = [] {
+    const char* e = std::getenv("CTORCH_MATMUL_HI_IN_PLACE");
+    return !(e && e[0] == '0');
+}();
+bool hi_in_place(const void* p, int64_t inner, int64_t ld) {
+    return g_hi_in_place && (reinterpret_cast<uintptr_t>(p) & 15u) == 0 && ld % 4 == 0 && ld >= inner && inner % 4 == 0;
+}
+// The value a kept split's valid flag has when it holds the split of this variant, with or without hi.
+int split_tag(int variant, bool in_place) { return 1 + variant + (in_place ? 2 : 0); }
 int64_t split_pitch_of(int64_t inner) { return (inner + 7) / 8 * 8; }
 
 // ---- flags of the K-halved tiles ------------------------------------------------------------------
@@ -1920,7 +1945,10 @@ ctk_status ctk_set_matmul_correction(int bf16) {
 }
 int ctk_get_matmul_correction(void) { return g_correction; }
 // The value a kept split's valid flag has when the buffer holds a split made under the current setting.
-int ctk_matmul_split_tag(void) { return 1 + g_correction; }
+int ctk_matmul_split_tag(void) { return split_tag(g_correction, false); }
+// The same for the split of the array at p ([.., inner], row pitch ld elements): 2 more when the array itself
+// serves as the split's hi part (16-byte aligned rows), which is how the epilogues and the SGD update write it.
+int ctk_matmul_split_tag_for(const void* p, int64_t inner, int64_t ld) { return split_tag(g_correction, hi_in_place(p, inner, ld)); }
 
 ctk_status ctk_set_matmul_tail_split(int on) {
     CTK_REQUIRE(on >= 0 && on <= 2, "ctk_set_matmul_tail_split: 0, 1 or 2");
@@ -2042,7 +2070,7 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
     if (fe.bias == nullptr && !fe.relu && skinny_k_ok(a, b, c, m, n, k, sa0, sa1, sb0, sb1, md) &&
         (fe.mask == nullptr || (reinterpret_cast<uintptr_t>(fe.mask) & 15u) == 0)) {
         SplitOut so;
-        if (fe.c_split) so = split_layout(fe.c_split, m, split_pitch_of(n), g_correction);
+        if (fe.c_split) so = split_layout(fe.c_split, m, split_pitch_of(n), g_correction, hi_in_place(c, n, n));
         dim3 grid(static_cast<unsigned>((n / 4 + SK_THREADS - 1) / SK_THREADS), static_cast<unsigned>((m + SK_ROWS - 1) / SK_ROWS));
         skinny_k_kernel<<<grid, SK_THREADS, 0, st>>>(a, b, c, m, n, static_cast<int>(k), fe.mask, so);
         CTK_LAUNCH_CHECK("skinny_k_kernel");
@@ -2071,9 +2099,11 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
 
     const int variant = g_correction;
     const int terms = (md == CTK_MATMUL_3XTF32) ? (variant == 1 ? 2 : 3) : 1;
-    const int tag = 1 + variant;  // what a kept split's valid flag says when it holds this variant's split
+    // the operand itself as the hi part of its split, where TMA can read it
+    const bool a_in_place = terms != 1 && hi_in_place(A.p, A.inner(), A.ld), b_in_place = terms != 1 && hi_in_place(B.p, B.inner(), B.ld);
+    const int a_tag = split_tag(variant, a_in_place), b_tag = split_tag(variant, b_in_place);  // what a kept split's valid flag must say
     SplitOut sa, sb;
-    int64_t a_ld = A.ld, b_ld = B.ld;
+    int64_t a_ld = A.ld, b_ld = B.ld;   // pitch of the split's arrays (of the operand itself in TF32 mode)
     if (terms != 1) {
         const int64_t a_pitch = split_pitch_of(A.inner()), b_pitch = split_pitch_of(B.inner());
         void *abuf = ka.buf, *bbuf = kb.buf;
@@ -2083,12 +2113,12 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
                 ctk_status rc = device_scratch(1, ctk_matmul_workspace_bytes(m, n, k, md), &ws);
                 if (rc) return rc;
             }
-            const SplitOut first = split_layout(ws, A.outer(), a_pitch, variant);
+            const SplitOut first = split_layout(ws, A.outer(), a_pitch, variant, false);
             if (!abuf) abuf = ws;
             if (!bbuf) bbuf = first.hi + 2 * A.outer() * a_pitch;  // behind A's 8 bytes per element
         }
-        sa = split_layout(abuf, A.outer(), a_pitch, variant);
-        sb = split_layout(bbuf, B.outer(), b_pitch, variant);
+        sa = split_layout(abuf, A.outer(), a_pitch, variant, a_in_place);
+        sb = split_layout(bbuf, B.outer(), b_pitch, variant, b_in_place);
         auto split = [&](const tc::Operand& O, const SplitOut& out) -> ctk_status {
             const bool vec = (reinterpret_cast<uintptr_t>(O.p) & 15u) == 0 && O.ld % 4 == 0 && O.inner() % 4 == 0;
             if (vec) {
@@ -2102,13 +2132,13 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
             return CTK_OK;
         };
         ctk_status rc2;
-        if (!(ka.buf && ka.valid && *ka.valid == tag)) {
+        if (!(ka.buf && ka.valid && *ka.valid == a_tag)) {
             if ((rc2 = split(A, sa))) return rc2;
-            if (ka.buf && ka.valid) *ka.valid = tag;
+            if (ka.buf && ka.valid) *ka.valid = a_tag;
         }
-        if (!(kb.buf && kb.valid && *kb.valid == tag)) {
+        if (!(kb.buf && kb.valid && *kb.valid == b_tag)) {
             if ((rc2 = split(B, sb))) return rc2;
-            if (kb.buf && kb.valid) *kb.valid = tag;
+            if (kb.buf && kb.valid) *kb.valid = b_tag;
         }
         a_ld = a_pitch; b_ld = b_pitch;
     }
@@ -2121,8 +2151,9 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
     const int b_rows = paired ? tc::pair::BN_CTA : bn;
     const int b_box = B.mn_major ? tc::BK : b_rows;
     ctk_status rc;
-    const float* a32 = terms == 1 ? A.p : sa.hi;
-    const float* b32 = terms == 1 ? B.p : sb.hi;
+    const float* a32 = (terms == 1 || a_in_place) ? A.p : sa.hi;
+    const float* b32 = (terms == 1 || b_in_place) ? B.p : sb.hi;
+    const int64_t a_ld32 = (terms == 1 || a_in_place) ? A.ld : a_ld, b_ld32 = (terms == 1 || b_in_place) ? B.ld : b_ld;
     // MN-major operands with whole 128-byte groups along MN: one 3-D copy per array and stage instead of
     // one per group (g_grouped_maps goes false for good if the driver refuses such a map)
     bool a_grouped = g_grouped_maps && A.mn_major && A.inner() % 64 == 0;
@@ -2131,8 +2162,8 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
         const int ag32 = a_grouped ? tc::BM / 32 : 0, ag16 = a_grouped ? tc::BM / 64 : 0;
         const int bg32 = b_grouped ? b_rows / 32 : 0, bg16 = b_grouped ? b_rows / 64 : 0;
         ctk_status e;
-        if ((e = tc::make_map(&maps[0], a32, A.inner(), A.outer(), a_ld, a_box, A.mn_major, ag32))) return e;
-        if ((e = tc::make_map(&maps[3], b32, B.inner(), B.outer(), b_ld, b_box, B.mn_major, bg32))) return e;
+        if ((e = tc::make_map(&maps[0], a32, A.inner(), A.outer(), a_ld32, a_box, A.mn_major, ag32))) return e;
+        if ((e = tc::make_map(&maps[3], b32, B.inner(), B.outer(), b_ld32, b_box, B.mn_major, bg32))) return e;
         if (terms == 3) {
             if ((e = tc::make_map(&maps[1], static_cast<const float*>(sa.p2), A.inner(), A.outer(), a_ld, a_box, A.mn_major, ag32))) return e;
             if ((e = tc::make_map(&maps[4], static_cast<const float*>(sb.p2), B.inner(), B.outer(), b_ld, b_box, B.mn_major, bg32))) return e;
@@ -2173,7 +2204,7 @@ static ctk_status matmul_impl(const float* a, const float* b, float* c, int64_t 
     P.b_grouped = b_grouped ? 1 : 0;
     P.out = SplitOut();
     P.out.pitch = split_pitch_of(n);
-    if (fe.c_split) P.out = split_layout(fe.c_split, m, split_pitch_of(n), variant);
+    if (fe.c_split) P.out = split_layout(fe.c_split, m, split_pitch_of(n), variant, hi_in_place(c, n, n));
     CTK_REQUIRE(static_cast<int64_t>(P.tiles_m) * P.tiles_n < (int64_t(1) << 30), "ctk_matmul_f32: too many tiles");
     // The last wave: when at most half of the SMs (or CTA pairs) would have a tile, its tiles are
     // computed as two K-halves each (the second added to the first, in that order), so that twice as
@@ -2279,7 +2310,7 @@ ctk_status ctk_sgd_update_split_f32(float* p, const float* g, float lr, int64_t 
     CTK_REQUIRE(p && g && split, "ctk_sgd_update_split_f32: null pointer");
     CTK_REQUIRE(((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g)) & 15u) == 0 && inner % 4 == 0 && ld % 4 == 0,
                 "ctk_sgd_update_split_f32: needs 16-byte aligned rows (use ctk_sgd_update_f32)");
-    const SplitOut out = split_layout(split, outer, split_pitch_of(inner), g_correction);
+    const SplitOut out = split_layout(split, outer, split_pitch_of(inner), g_correction, hi_in_place(p, inner, ld));
     const int64_t total = outer * (inner / 4);
     const int64_t per_cta = SPLIT_THREADS * SPLIT_UNROLL;
     sgd_split_vec_kernel<<<static_cast<unsigned>((total + per_cta - 1) / per_cta), SPLIT_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(

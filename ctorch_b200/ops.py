@@ -198,18 +198,23 @@ def matmul_fused(a, b, bias=None, relu=False, mask=None, want_split=False, ta=Fa
                                           split.p if split else None, None, _sh(stream)))
     if not want_split:
         return out
-    hi, rest = _decode_split(split, m, n)
+    hi, rest = _decode_split(split, m, n, out)
     return out, hi, rest
 
 
-def _decode_split(split, outer, inner):
+def _decode_split(split, outer, inner, source):
     """The arrays of a split buffer as numpy: (hi, lo) as float32 [outer, inner] when the correction terms
     run on the TF32 path, (hi, bits) with bits a uint16 [2, outer, inner] array holding the bf16 patterns
-    of h16 and l16 when they run on the bf16 path (see ctk_set_matmul_correction)."""
+    of h16 and l16 when they run on the bf16 path (see ctk_set_matmul_correction).  source: the contiguous
+    [outer, inner] device array the split belongs to; where it serves as the split's hi part itself (see
+    ctk_matmul_split_tag_for) hi is returned as the tensor core reads it: the low 13 mantissa bits cleared."""
     pitch = (inner + 7) // 8 * 8
     pad = (-split.ptr) % 256 // 4          # the library aligns the buffer to 256 bytes
     flat = split.numpy()
-    hi = flat[pad:pad + outer * pitch].reshape(outer, pitch)[:, :inner]
+    if lib.ctk_matmul_split_tag_for(source.p, _i64(inner), _i64(inner)) >= 3:
+        hi = (np.ascontiguousarray(source.numpy(), np.float32).reshape(outer, inner).view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32)
+    else:
+        hi = flat[pad:pad + outer * pitch].reshape(outer, pitch)[:, :inner]
     if lib.ctk_get_matmul_correction() == 0:
         return hi, flat[pad + outer * pitch:pad + 2 * outer * pitch].reshape(outer, pitch)[:, :inner]
     u16 = flat.view(np.uint16)
@@ -224,7 +229,7 @@ def sgd_update_split(p, g, lr, stream=None):
     outer, inner = p.shape
     split = DeviceArray((int(lib.ctk_matmul_split_bytes(inner, outer)) // 4,))
     check(lib.ctk_sgd_update_split_f32(p.p, g.p, _f(lr), _i64(outer), _i64(inner), _i64(inner), split.p, _sh(stream)))
-    return _decode_split(split, outer, inner)
+    return _decode_split(split, outer, inner, p)
 
 
 CMP = {"gt": 0, "lt": 1, "eq": 2, "ge": 3, "le": 4, "ne": 5}

@@ -294,9 +294,15 @@ ctk_status ctk_set_matmul_pairing(int pairing);
 /* element; measured error at 4096^3 against float64: 1.0e-5 (bf16 path) / 1.6e-5 (TF32 path), normwise.  */
 /* Process-wide; CTORCH_MATMUL_CORRECTION=tf32|bf16 in the environment sets the start value.  A split kept by the caller carries in its valid flag the tag of the setting it was made  */
 /* under (ctk_matmul_split_tag: 1 or 2); a buffer with another tag is filled again.                        */
+/* Where the operand itself can be read by TMA (16-byte aligned, rows a multiple of 16 bytes apart) it serves */
+/* as the hi part of its own split -- the tensor core reads the top 19 bits of an fp32 word, i.e. hi =     */
+/* x truncated -- and only the terms of x - hi are written (tag + 2; CTORCH_MATMUL_HI_IN_PLACE=0 switches   */
+/* that off).  ctk_matmul_split_tag_for(p, inner, ld): the tag of a split of the array at p ([.., inner]    */
+/* elements, row pitch ld) as ctk_matmul_3xtf32_fused_f32 and ctk_sgd_update_split_f32 write it.            */
 ctk_status ctk_set_matmul_correction(int bf16);
 int ctk_get_matmul_correction(void);
 int ctk_matmul_split_tag(void);
+int ctk_matmul_split_tag_for(const void* p, int64_t inner, int64_t ld);
 /* 1 (default): when the last wave of output tiles would occupy at most half of the SMs (or CTA    */
 /* pairs) -- which includes every product with few tiles, like the 10-class layer -- each of its   */
 /* tiles is computed as two halves of K by two CTAs (pairs); the second half is added to the first   */

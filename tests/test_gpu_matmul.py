@@ -3,6 +3,8 @@ core modes and the CUDA-core path, vs the oracle's fp32 recurrence.
 
 Tolerances (normwise, max|C - C_ref| / max|C_ref|): 1e-4 for 3xTF32, 5e-3 for TF32, 1e-5 for the
 fp32 CUDA-core path."""
+import ctypes
+
 import numpy as np
 import pytest
 
@@ -270,7 +272,8 @@ def test_fused_epilogue_equals_the_separate_kernels(cb, m, k, n, ta, tb, pairing
 
 def oracle_split(x):
     """The split the library keeps of x, in the form ops._decode_split returns it.  hi = cvt.rna.tf32.f32
-    of x (round to nearest, ties away from zero, 10 mantissa bits).  Correction terms on the TF32 path:
+    of x (round to nearest, ties away from zero, 10 mantissa bits) where hi is an array of its own, x
+    truncated to those bits where x itself is read as hi.  Correction terms on the TF32 path:
     lo = the same rounding of x - hi.  On the bf16 path: the bf16 bit patterns (round to nearest even)
     of hi and of x - hi."""
     import ctorch_b200 as cb_
@@ -291,7 +294,11 @@ def oracle_split(x):
         return r
 
     x = np.ascontiguousarray(x, np.float32)
-    hi = rna(x)
+    # rows a multiple of 16 bytes apart (device arrays start on 256): the array itself is the hi part, read
+    # by the tensor core with its low 13 mantissa bits ignored
+    inner = x.shape[-1]
+    in_place = cb_.lib.ctk_matmul_split_tag_for(None, ctypes.c_int64(inner), ctypes.c_int64(inner)) >= 3
+    hi = (x.view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32) if in_place else rna(x)
     lo = (x - hi).astype(np.float32)
     if cb_.lib.ctk_get_matmul_correction() == 0:
         return hi, rna(lo)
