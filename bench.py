@@ -980,7 +980,7 @@ def run_one_kernel(cb, case, rng):
         i64 = ctypes.c_int64
         fn = dict(sgdsplit=lambda: cb.check(cb.lib.ctk_sgd_update_split_f32(p_.p, g.p, ctypes.c_float(1e-3), i64(rows), i64(cols), i64(cols), split.p, None)),
                   colsum=lambda: cb.ops.colsum(p_))[kind]
-        work, unit = dict(sgdsplit=20, colsum=4)[kind] * rows * cols, "GB/s"
+        work, unit = dict(sgdsplit=16, colsum=4)[kind] * rows * cols, "GB/s"   # p and g read, p and the 4-byte small terms of its split written
     elif kind == "u8":
         n = 1 << int(parts[1])
         src = cb.to_device(rng.integers(0, 256, n).astype(np.uint8), dtype=np.uint8); o = cb.empty((n,))
