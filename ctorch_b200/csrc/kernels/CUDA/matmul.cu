@@ -25,10 +25,16 @@
 //   sums are added up in fp32 by the epilogue (the tensor core truncates when it adds into its
 //   accumulator).
 //   TF32 mode multiplies the fp32 operands as they are (the tensor core reads the top 19 bits).
-//   3xTF32 mode first splits each operand x into hi = tf32(x) (round to nearest) and
-//   lo = tf32(x - hi) in a scratch buffer (or one the caller keeps with the operand), then
-//   accumulates lo.hi + hi.lo + hi.hi in TMEM: the dropped term lo.lo is ~2^-22 of the product, i.e.
-//   fp32-level accuracy.
+//   The fp32-accurate mode (CTK_MATMUL_3XTF32) multiplies hi.hi + lo.hi + hi.lo, hi the TF32 part of an
+//   operand and lo = x - hi: hi.hi as kind::tf32, the two small terms as kind::tf32 too ("3xTF32") or, by
+//   default, as kind::f16 on bf16 roundings of their factors, into the same TMEM accumulator; the dropped
+//   term lo.lo is ~2^-20 of the product, i.e. fp32-level accuracy.  Where TMA can read the operand itself
+//   it IS hi (the tensor core ignores the low 13 mantissa bits) and only the small terms' arrays are
+//   written -- to a scratch buffer or one the caller keeps with the operand; elsewhere hi = tf32(x)
+//   rounded to nearest goes into an array of its own (see SplitOut).  MN-major operands whose contiguous
+//   extent is a multiple of 64 are fetched as 3-D tensors, one copy per array and stage.
+//   Narrow outputs (N <= 16, long K) and short contractions (K <= 16) do not use the tensor cores at all:
+//   see narrow_rows_kernel / narrow_cols_kernel and skinny_k_kernel.
 //   Every mbarrier wait is bounded; a wait that runs out sets a device status word, the CTA drains
 //   its copies, frees its TMEM and returns.
 //
