@@ -82,7 +82,8 @@ public:
     std::vector<int64_t> slot_len;      // ... and the slot's padded length (a multiple of 4 * world)
     std::vector<void*> ev_upd, ev_ag;   // sharded: shard updated (compute -> comm), weights gathered (comm -> compute)
     std::vector<char> in_arena;         // this step: the parameter's gradient has been copied to its slot
-    void* ev_done = nullptr;            // compute: end of the step (what the bounded wait watches)
+    void* ev_done = nullptr;            // compute: end of the step
+    void* ev_loss = nullptr;            // compute: the step's loss has reached the page-locked slot (what a step waits for)
     int comm_timeout_ms = 30000;        // a step that has not completed by then has lost a peer
     bool comm_failed = false;
     void* pinned_loss = nullptr;  // page-locked slot the loss is copied into
@@ -140,6 +141,7 @@ public:
             for (void* e : *v)
                 if (e) ctk_event_destroy(e);
         if (ev_done) ctk_event_destroy(ev_done);
+        if (ev_loss) ctk_event_destroy(ev_loss);
         if (arena && comm) ctk_comm_free(comm, arena);
         if (pinned_loss) ctk_free_host(pinned_loss);
         if (pinned_x) ctk_free_host(pinned_x);
@@ -324,6 +326,10 @@ public:
             const Tensor& loss_value = loss;  // read-only access: the tape shares this buffer, a writable pointer would copy it
             float* slot = static_cast<float*>(pinned_loss) + (deferred_loss ? steps_done % kLossSlots : 0);
             cuda_check(ctk_memcpy_d2h(slot, loss_value.data<float>(), sizeof(float), st), "loss read-back");
+            if (!capturing) {
+                if (!ev_loss) cuda_check(ctk_event_create(&ev_loss), "event");
+                cuda_check(ctk_event_record(ev_loss, st), "record");
+            }
         }
         backward(loss);
         auto update = [&](int p) {
@@ -389,20 +395,27 @@ public:
             cuda_check(ctk_stream_wait_event(st, ev_comm), "wait");
         }
         if (keep_logits) last_logits = logits;
+        // A step returns its loss -- which the forward pass has produced -- not the end of its backward pass
+        // and updates: those stay queued on the stream, the next step's kernels line up behind them, and the
+        // GPU never waits for the host between two steps.  Whatever reads the trainer's state afterwards is
+        // ordered on the same stream.  The host is never more than one step ahead: the next loss needs this
+        // step's updates.
         const bool wait = !capturing && !deferred_loss;
         if (wait && comm) {
-            // Bounded: a peer that died or never joined leaves the collective spinning on the GPU; the wait
-            // polls the step's end and the communicator's health and gives up at the deadline (the
-            // communicator is aborted, which ends its kernels; the context stays usable).
+            // Bounded: a peer that died or never joined leaves a collective spinning on the GPU -- the one of
+            // the step BEFORE this one keeps this step's forward pass, hence its loss, from ever arriving; the
+            // wait polls the loss event and the communicator's health and gives up at the deadline (the
+            // communicator is aborted, which ends its kernels; the context stays usable).  ev_done marks the
+            // end of this step for finish().
             cuda_check(ctk_event_record(ev_done, st), "record");
-            const int rc = ctk_comm_wait(comm, ev_done, comm_timeout_ms);
+            const int rc = ctk_comm_wait(comm, ev_loss, comm_timeout_ms);
             if (rc) {
                 comm_failed = true;
                 ctx.release_step_nodes();
                 throw std::runtime_error(std::string("data-parallel step: ") + ctk_last_error());
             }
         } else if (wait) {
-            cuda_check(st ? ctk_stream_sync(st) : ctk_device_sync(), "step sync");
+            cuda_check(ctk_event_sync(ev_loss), "step: wait for the loss");
         }
         ctx.release_step_nodes();
         ++steps_done;
