@@ -128,7 +128,12 @@ int cth_mlp_sync_losses(void* mlp, float* out, int cap, int* n);
  * the copy taken when the parameter was first registered, src/AutoDiff.cpp:286-290).  Both 0 by default;
  * every parity test runs with both 0. */
 int cth_mlp_set_corrected(void* mlp, int exact_bias_grad, int fresh_weights);
-/* x_host [batch, dims[0]] and labels_host [batch] (class indices as floats) in HOST memory. */
+/* x_host [batch, dims[0]] and labels_host [batch] (class indices as floats) in HOST memory.
+ * Every eager step call returns once the step's loss has arrived on the host (the forward pass is over and
+ * the host buffers have been read); its backward pass and updates may still be queued on the stream, in
+ * front of whatever is issued next -- cth_mlp_get_params / get_grads / predict and the next step are ordered
+ * behind them.  With a communicator set the wait is bounded (cth_mlp_set_comm_timeout_ms): a peer that
+ * never takes part in the previous step's exchange keeps this step's loss from arriving. */
 int cth_mlp_step_host(void* mlp, const float* x_host, const float* labels_host, int64_t batch, float* loss);
 /* The same step with the upload taken off the critical path, as an input pipeline would run it:
  * cth_mlp_stage_host starts the host-to-device copy of one batch on a copy stream and returns (page-locked
