@@ -131,6 +131,7 @@ public:
     }
 
     ~MlpTrainer() {
+        finish_exchange();
         ctk_device_sync();
         release_graph();
         if (graph.stream) ctk_stream_destroy(graph.stream);
@@ -193,8 +194,16 @@ public:
         dp_mode = mode;
     }
 
+    // Waits, bounded, for the last step's exchange (a step itself returns at its loss): a peer that dropped
+    // out of it is found here instead of in a device synchronisation that would never return.
+    void finish_exchange() {
+        if (!comm || comm_failed || !ev_done || steps_done == 0) return;
+        if (ctk_comm_wait(comm, ev_done, comm_timeout_ms)) comm_failed = true;   // (the communicator has been aborted: its kernels end)
+    }
+
     void set_comm(void* c) {
         if (!c && comm) {
+            finish_exchange();
             cuda_check(ctk_device_sync(), "set_comm sync");
             if (arena) { ctk_comm_free(comm, arena); arena = nullptr; }
         }
@@ -703,6 +712,7 @@ public:
     }
 
     void get_params(float* out) {
+        finish_exchange();
         for (size_t l = 0; l < W.size(); ++l) {
             W[l].copy_to_host(out, W[l].numel());
             out += W[l].numel();
@@ -717,6 +727,7 @@ public:
         for (int p = 0; p < static_cast<int>(2 * W.size()); ++p) {
             Tensor& t = param(p);
             if (comm && dp_mode != DP_INPLACE && arena) {
+                finish_exchange();
                 cuda_check(ctk_device_sync(), "get_grads sync");
                 cuda_check(ctk_memcpy_d2h(out, arena + slot_off[p], t.numel() * sizeof(float), nullptr), "gradient read-back");
                 cuda_check(ctk_device_sync(), "get_grads sync");
